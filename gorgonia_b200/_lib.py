@@ -1,0 +1,157 @@
+"""ctypes binding of libgorgonia_b200.so (the C ABI declared in include/gorgonia_b200.h).
+
+There is no fallback of any kind: if the shared library has not been built, importing this
+module raises, and every call that fails returns a non-zero status that `check` turns into
+a B200Error carrying the engine's error text.
+"""
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libgorgonia_b200.so")
+
+
+class B200Error(RuntimeError):
+    def __init__(self, code, text):
+        super().__init__(f"[b200 status {code}] {text}")
+        self.code = code
+        self.text = text
+
+
+OK, ERR_INVALID, ERR_OOM, ERR_CUDA, ERR_UNSUPPORTED, ERR_TIMEOUT, ERR_STATE = range(7)
+F32, F64, BF16 = 0, 1, 2
+VV, VS, SV = 0, 1, 2
+ENGINE_MANAGED, ENGINE_NO_DEFER = 1, 2
+
+# op codes (B200_OP_* of the header)
+_BIN = ["add", "sub", "mul", "div", "pow", "mod", "lt", "gt", "lte", "gte", "eq", "ne"]
+_UN = ["abs", "sign", "ceil", "floor", "sin", "cos", "exp", "ln", "log2", "neg", "square", "sqrt",
+       "inv", "invsqrt", "cube", "tanh", "sigmoid", "log1p", "expm1", "softplus"]
+OP = {name: i for i, name in enumerate(_BIN)}
+OP.update({name: 32 + i for i, name in enumerate(_UN)})
+BINARY_OPS = tuple(_BIN)
+UNARY_OPS = tuple(_UN)
+
+PW_MAX_INSTR, PW_MAX_SRC, PW_MAX_IMM, PW_MAX_OUT = 16, 6, 8, 4
+
+
+def REF_SRC(k):
+    return 0x00 | k
+
+
+def REF_IMM(k):
+    return 0x40 | k
+
+
+def REF_INS(k):
+    return 0x80 | k
+
+
+class PwInstr(C.Structure):
+    _fields_ = [("op", C.c_uint8), ("a", C.c_uint8), ("b", C.c_uint8), ("reserved", C.c_uint8)]
+
+
+class PwProg(C.Structure):
+    _fields_ = [
+        ("n_instr", C.c_uint32), ("n_src", C.c_uint32), ("n_imm", C.c_uint32), ("n_out", C.c_uint32),
+        ("instr", PwInstr * PW_MAX_INSTR),
+        ("imm", C.c_double * PW_MAX_IMM),
+        ("out_instr", C.c_uint8 * PW_MAX_OUT),
+        ("src_div", C.c_int64 * PW_MAX_SRC),
+        ("src_mod", C.c_int64 * PW_MAX_SRC),
+    ]
+
+
+class PwCall(C.Structure):
+    _fields_ = [
+        ("op", C.c_int32), ("dtype", C.c_int32), ("form", C.c_int32), ("bcast", C.c_int32),
+        ("dst", C.c_uint64), ("a", C.c_uint64), ("b", C.c_uint64), ("scalar_ptr", C.c_uint64),
+        ("scalar", C.c_double),
+        ("n", C.c_int64), ("bdiv", C.c_int64), ("bmod", C.c_int64),
+    ]
+
+
+def _load():
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `make -C gorgonia_b200/csrc` "
+            "(or __graft_entry__.build()); there is no CPU fallback")
+    return C.CDLL(LIB_PATH)
+
+
+lib = _load()
+
+_vp, _i, _i64, _d, _u = C.c_void_p, C.c_int, C.c_int64, C.c_double, C.c_uint
+_P = C.POINTER
+
+_SIGS = {
+    "b200_engine_create": (_i, [_i, C.c_size_t, _u, _P(_vp)]),
+    "b200_engine_destroy": (_i, [_vp]),
+    "b200_engine_device": (_i, [_vp]),
+    "b200_engine_stream": (C.c_size_t, [_vp]),
+    "b200_last_error": (C.c_char_p, [_vp]),
+    "b200_flush": (_i, [_vp]),
+    "b200_sync": (_i, [_vp]),
+    "b200_launch_count": (C.c_uint64, [_vp]),
+    "b200_event_create": (_i, [_vp, _P(_vp)]),
+    "b200_event_record": (_i, [_vp, _vp]),
+    "b200_event_elapsed_ms": (_i, [_vp, _vp, _vp, _P(C.c_float)]),
+    "b200_event_destroy": (_i, [_vp, _vp]),
+    "b200_get": (_i, [_vp, _i64, _P(_vp)]),
+    "b200_put": (_i, [_vp, _vp, _i64]),
+    "b200_reset": (_i, [_vp]),
+    "b200_arena_stats": (_i, [_vp, _P(_i64), _P(_i64), _P(_i64), _P(_i64)]),
+    "b200_bfc_create": (_vp, [_i64, _i64]),
+    "b200_bfc_destroy": (None, [_vp]),
+    "b200_bfc_alloc": (_i, [_vp, _i64, _P(_i64)]),
+    "b200_bfc_free": (_i, [_vp, _i64]),
+    "b200_bfc_reset": (None, [_vp]),
+    "b200_bfc_free_blocks": (_i64, [_vp]),
+    "b200_bfc_used": (_i64, [_vp]),
+    "b200_bfc_largest_free": (_i64, [_vp]),
+    "b200_memcpy_h2d": (_i, [_vp, _vp, _vp, _i64]),
+    "b200_memcpy_d2h": (_i, [_vp, _vp, _vp, _i64]),
+    "b200_memcpy_d2d": (_i, [_vp, _vp, _vp, _i64]),
+    "b200_memcpy_h2d_async": (_i, [_vp, _vp, _vp, _i64]),
+    "b200_memcpy_d2h_async": (_i, [_vp, _vp, _vp, _i64]),
+    "b200_memset": (_i, [_vp, _vp, _i, _i64]),
+    "b200_host_alloc": (_i, [_i64, _P(_vp)]),
+    "b200_host_free": (_i, [_vp]),
+    "b200_binary": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp, _d, _i, _i64]),
+    "b200_unary": (_i, [_vp, _i, _i, _vp, _vp, _i64]),
+    "b200_binary_bcast": (_i, [_vp, _i, _i, _vp, _vp, _vp, _i64, _i64, _i64, _i]),
+    "b200_pointwise": (_i, [_vp, _i, _P(PwProg), _P(_vp), _P(_vp), _i64]),
+    "b200_pending": (_i, [_vp, _P(_i), _P(_i)]),
+    "b200_fusion_plan": (_i, [_P(PwCall), _i, _P(_i), _P(_i), _P(_i), _P(_i), _P(_i)]),
+    "b200_has_nan": (_i, [_vp, _i, _vp, _i64, _P(_i)]),
+    "b200_has_inf": (_i, [_vp, _i, _vp, _i64, _P(_i)]),
+}
+
+
+def _bind():
+    for name, (res, args) in _SIGS.items():
+        fn = getattr(lib, name, None)
+        if fn is None:
+            continue  # entry points of a newer header than the built library: reported by the tests
+        fn.restype = res
+        fn.argtypes = args
+
+
+_bind()
+
+
+def declared_symbols(header_path=None):
+    """Names of all functions declared in include/gorgonia_b200.h."""
+    import re
+    if header_path is None:
+        header_path = os.path.join(os.path.dirname(_HERE), "include", "gorgonia_b200.h")
+    text = open(header_path).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(b200_[a-z0-9_]+)\s*\(", text)))
+
+
+def check(rc, handle=None):
+    if rc != OK:
+        text = lib.b200_last_error(handle)
+        raise B200Error(rc, text.decode() if text else "")
+    return rc

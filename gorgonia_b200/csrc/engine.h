@@ -1,0 +1,101 @@
+// Internal definition of the engine handle shared by the .cu files of the library.
+#pragma once
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "../../include/gorgonia_b200.h"
+#include "bfc.h"
+
+struct b200_engine {
+  int device = 0;
+  unsigned flags = 0;
+  cudaStream_t stream = nullptr;
+  int sm_count = 148;
+  size_t smem_optin = 0;
+
+  // arena
+  void *slab = nullptr;
+  int64_t slab_bytes = 0;
+  b200::Bfc bfc;
+
+  // deferred pointwise queue
+  std::vector<b200_pw_call> pending;
+  std::vector<void *> dead;  // (pointer, queue length) pairs: buffers returned to the arena while writes to them were queued
+
+  // small device scratch owned by the engine: flag words for has_nan/has_inf and the
+  // error word bounded waits report through
+  int *d_flags = nullptr;   // 16 ints
+  int *h_flags = nullptr;   // pinned mirror
+
+  // lazily created resources of other translation units (gemm.cu etc.)
+  void *gemm_state = nullptr;
+  void (*gemm_state_free)(void *) = nullptr;
+
+  uint64_t launches = 0;
+  std::string last_error;
+  std::recursive_mutex mu;
+};
+
+namespace b200 {
+
+extern thread_local std::string g_create_error;
+
+int set_error(b200_engine *e, int code, const char *fmt, ...);
+
+#define B200_CHECK_CUDA(e, call)                                                       \
+  do {                                                                                 \
+    cudaError_t err__ = (call);                                                        \
+    if (err__ != cudaSuccess)                                                          \
+      return b200::set_error((e), B200_ERR_CUDA, "%s failed: %s (%s:%d)", #call,       \
+                             cudaGetErrorString(err__), __FILE__, __LINE__);           \
+  } while (0)
+
+#define B200_REQUIRE(e, cond, ...)                                       \
+  do {                                                                   \
+    if (!(cond)) return b200::set_error((e), B200_ERR_INVALID, __VA_ARGS__); \
+  } while (0)
+
+// Makes the engine's device current for the calling thread.
+struct DeviceGuard {
+  int prev = -1;
+  bool ok = true;
+  explicit DeviceGuard(const b200_engine *e) {
+    if (cudaGetDevice(&prev) != cudaSuccess) prev = -1;
+    if (prev != e->device) ok = cudaSetDevice(e->device) == cudaSuccess;
+  }
+  ~DeviceGuard() {
+    if (prev >= 0) cudaSetDevice(prev);
+  }
+};
+
+// Launch-error check used after every <<<>>>.
+#define B200_CHECK_LAUNCH(e, name)                                                     \
+  do {                                                                                 \
+    cudaError_t err__ = cudaGetLastError();                                            \
+    if (err__ != cudaSuccess)                                                          \
+      return b200::set_error((e), B200_ERR_CUDA, "launch of %s failed: %s", (name),    \
+                             cudaGetErrorString(err__));                               \
+    (e)->launches++;                                                                   \
+  } while (0)
+
+inline size_t dtype_size(int dtype) {
+  switch (dtype) {
+    case B200_F32: return 4;
+    case B200_F64: return 8;
+    case B200_BF16: return 2;
+    default: return 0;
+  }
+}
+
+// implemented in pointwise.cu
+int flush_pending(b200_engine *e);
+int plan_pending(b200_engine *e, int *n_kernels);
+void note_put(b200_engine *e, void *ptr);
+
+}  // namespace b200

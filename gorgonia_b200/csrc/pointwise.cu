@@ -1,0 +1,860 @@
+// Pointwise kernels, the deferred queue and its run-time fusion pass.
+//
+// Takes over Engine.Add…Pow / Lt…ElNe (+Scalar) (gorgonia cuda/arith.go:14-701,
+// cuda/cmp.go:14-701), elemUnaryOp.CUDADo / elemBinOp.CUDADo (op_math_cuda.go:23-176) and the
+// kernels of "cuda modules/src/elembinop.cu" and "elemunaryop.cu". The reference runs one
+// thread per element, one launch (and often one device-to-device copy) per op, in place.
+//
+// Here one kernel evaluates a short program of pointwise instructions per pass over memory:
+//   - each thread owns 16-byte chunks (4 floats / 2 doubles), grid-stride, 64-bit indices;
+//   - all sources of a chunk are loaded first (independent 128-bit loads in flight), then the
+//     program runs on registers, then the outputs are stored with 128-bit stores;
+//   - the program is interpreted with warp-uniform branches: the instruction loop is unrolled,
+//     instruction k writes register slot k (a compile-time index) and its operands are picked
+//     by a switch whose selector is the same for every thread, so nothing diverges and no
+//     value leaves the register file;
+//   - multiplies and adds are never contracted into FMAs (the reference builds its kernels
+//     with -fmad=false and the Go CPU engine does not fuse either).
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+
+#include "engine.h"
+
+namespace b200 {
+
+// ------------------------------------------------------------------------------------------
+// device-side program
+// ------------------------------------------------------------------------------------------
+
+enum SrcMode : uint8_t {
+  SRC_FULL = 0,     // element i reads src[i]
+  SRC_ROWVEC = 1,   // div == 1 and mod % VEC == 0: chunk at i reads the chunk at i % mod
+  SRC_GENERAL = 2,  // element i reads src[(i / div) % mod], one element at a time
+  SRC_SCALAR = 3,   // every element reads src[0]
+  SRC_CHUNK = 4     // div % VEC == 0: all elements of a chunk read the same src[(i / div) % mod]
+};
+
+struct PwDev {
+  const void *src[B200_PW_MAX_SRC];
+  void *out[B200_PW_MAX_OUT];
+  long long n;
+  long long src_div[B200_PW_MAX_SRC];
+  long long src_mod[B200_PW_MAX_SRC];
+  double imm[B200_PW_MAX_IMM];
+  uint8_t n_instr, n_src, n_out, pad0;
+  uint8_t src_mode[B200_PW_MAX_SRC];
+  uint8_t op[B200_PW_MAX_INSTR];
+  uint8_t ra[B200_PW_MAX_INSTR];  // operand selectors: [0,NS) sources, [16,24) immediates, [32,48) results
+  uint8_t rb[B200_PW_MAX_INSTR];
+  uint8_t out_ins[B200_PW_MAX_OUT];
+};
+
+#define SEL_IMM 16
+#define SEL_INS 32
+
+template <typename T>
+struct Vec;
+template <>
+struct Vec<float> {
+  static constexpr int N = 4;
+};
+template <>
+struct Vec<double> {
+  static constexpr int N = 2;
+};
+
+// ---- scalar op semantics ---------------------------------------------------------------
+// f32 thresholds of sigmoid/softplus follow elemunaryop.cu:166-189, f64 ones :83-105.
+
+__device__ __forceinline__ float mul_rn(float a, float b) { return __fmul_rn(a, b); }
+__device__ __forceinline__ double mul_rn(double a, double b) { return __dmul_rn(a, b); }
+__device__ __forceinline__ float add_rn(float a, float b) { return __fadd_rn(a, b); }
+__device__ __forceinline__ double add_rn(double a, double b) { return __dadd_rn(a, b); }
+__device__ __forceinline__ float sub_rn(float a, float b) { return __fsub_rn(a, b); }
+__device__ __forceinline__ double sub_rn(double a, double b) { return __dsub_rn(a, b); }
+
+__device__ __forceinline__ float sigmoid_(float x) {
+  if (x < -88.f) return 0.f;
+  if (x > 15.f) return 1.f;
+  return 1.f / (1.f + expf(-x));
+}
+__device__ __forceinline__ double sigmoid_(double x) {
+  if (x < -709.0) return 0.0;
+  if (x > 19.0) return 1.0;
+  return 1.0 / (1.0 + exp(-x));
+}
+__device__ __forceinline__ float softplus_(float x) {
+  if (x < -103.f) return 0.f;
+  if (x > 14.f) return x;
+  return log1pf(expf(x));
+}
+__device__ __forceinline__ double softplus_(double x) {
+  if (x < -708.0) return 0.0;
+  if (x > 16.0) return x;
+  return log1p(exp(x));
+}
+
+#define PW_LOOP(expr)                 \
+  _Pragma("unroll") for (int j = 0; j < V; ++j) { \
+    const T x = a[j];                 \
+    const T y = b[j];                 \
+    (void)x; (void)y;                 \
+    r[j] = (expr);                    \
+  }                                   \
+  break;
+
+template <typename T, int V>
+__device__ __forceinline__ void pw_apply(int op, const T (&a)[V], const T (&b)[V], T (&r)[V]) {
+  const T one = T(1), zero = T(0);
+  switch (op) {
+    case B200_OP_ADD: PW_LOOP(add_rn(x, y))
+    case B200_OP_SUB: PW_LOOP(sub_rn(x, y))
+    case B200_OP_MUL: PW_LOOP(mul_rn(x, y))
+    case B200_OP_DIV: PW_LOOP(x / y)
+    case B200_OP_POW: PW_LOOP(pow(x, y))
+    case B200_OP_MOD: PW_LOOP(fmod(x, y))
+    case B200_OP_LT: PW_LOOP(x < y ? one : zero)
+    case B200_OP_GT: PW_LOOP(x > y ? one : zero)
+    case B200_OP_LTE: PW_LOOP(x <= y ? one : zero)
+    case B200_OP_GTE: PW_LOOP(x >= y ? one : zero)
+    case B200_OP_EQ: PW_LOOP(x == y ? one : zero)
+    case B200_OP_NE: PW_LOOP(x != y ? one : zero)
+    case B200_OP_ABS: PW_LOOP(fabs(x))
+    case B200_OP_SIGN: PW_LOOP(T((x > zero) - (x < zero)))
+    case B200_OP_CEIL: PW_LOOP(ceil(x))
+    case B200_OP_FLOOR: PW_LOOP(floor(x))
+    case B200_OP_SIN: PW_LOOP(sin(x))
+    case B200_OP_COS: PW_LOOP(cos(x))
+    case B200_OP_EXP: PW_LOOP(exp(x))
+    case B200_OP_LN: PW_LOOP(log(x))
+    case B200_OP_LOG2: PW_LOOP(log2(x))
+    case B200_OP_NEG: PW_LOOP(-x)
+    case B200_OP_SQUARE: PW_LOOP(mul_rn(x, x))
+    case B200_OP_SQRT: PW_LOOP(sqrt(x))
+    case B200_OP_INV: PW_LOOP(one / x)
+    case B200_OP_INVSQRT: PW_LOOP(one / sqrt(x))
+    case B200_OP_CUBE: PW_LOOP(mul_rn(mul_rn(x, x), x))
+    case B200_OP_TANH: PW_LOOP(tanh(x))
+    case B200_OP_SIGMOID: PW_LOOP(sigmoid_(x))
+    case B200_OP_LOG1P: PW_LOOP(log1p(x))
+    case B200_OP_EXPM1: PW_LOOP(expm1(x))
+    case B200_OP_SOFTPLUS: PW_LOOP(softplus_(x))
+    default:
+      _Pragma("unroll") for (int j = 0; j < V; ++j) r[j] = zero;
+      break;
+  }
+}
+
+template <typename T, int V>
+__device__ __forceinline__ void copyv(T (&d)[V], const T (&s)[V]) {
+#pragma unroll
+  for (int j = 0; j < V; ++j) d[j] = s[j];
+}
+
+// Picks operand `sel` for instruction K: a source, an immediate, or the result of an earlier
+// instruction. `sel` is uniform across the grid, so the switches never diverge.
+template <typename T, int V, int NS, int NI, int K>
+__device__ __forceinline__ void fetch(T (&d)[V], int sel, const T (&S)[NS][V], const T (&R)[NI][V],
+                                      const PwDev &p) {
+  if (sel >= SEL_INS) {
+    const int k = sel - SEL_INS;
+    bool hit = false;
+#pragma unroll
+    for (int q = 0; q < K; ++q)
+      if (k == q) {
+        copyv(d, R[q]);
+        hit = true;
+      }
+    if (!hit) {
+#pragma unroll
+      for (int j = 0; j < V; ++j) d[j] = T(0);
+    }
+  } else if (sel >= SEL_IMM) {
+    const T v = (T)p.imm[sel - SEL_IMM];
+#pragma unroll
+    for (int j = 0; j < V; ++j) d[j] = v;
+  } else {
+    bool hit = false;
+#pragma unroll
+    for (int q = 0; q < NS; ++q)
+      if (sel == q) {
+        copyv(d, S[q]);
+        hit = true;
+      }
+    if (!hit) {
+#pragma unroll
+      for (int j = 0; j < V; ++j) d[j] = T(0);
+    }
+  }
+}
+
+template <typename T, int V, int NS, int NI, int K>
+struct Step {
+  static __device__ __forceinline__ void run(const PwDev &p, const T (&S)[NS][V], T (&R)[NI][V]) {
+    if (K < p.n_instr) {
+      T a[V], b[V];
+      fetch<T, V, NS, NI, K>(a, p.ra[K], S, R, p);
+      fetch<T, V, NS, NI, K>(b, p.rb[K], S, R, p);
+      pw_apply<T, V>(p.op[K], a, b, R[K]);
+      Step<T, V, NS, NI, K + 1>::run(p, S, R);
+    }
+  }
+};
+template <typename T, int V, int NS, int NI>
+struct Step<T, V, NS, NI, NI> {
+  static __device__ __forceinline__ void run(const PwDev &, const T (&)[NS][V], T (&)[NI][V]) {}
+};
+
+template <typename T, int V>
+__device__ __forceinline__ void load_chunk(T (&d)[V], const T *p, long long i, int valid) {
+  if (V > 1 && valid == V) {
+    const uint4 raw = *reinterpret_cast<const uint4 *>(p + i);
+    memcpy(d, &raw, sizeof(uint4));
+  } else {
+#pragma unroll
+    for (int j = 0; j < V; ++j) d[j] = j < valid ? p[i + j] : T(0);
+  }
+}
+
+template <typename T, int V>
+__device__ __forceinline__ void store_chunk(T *p, long long i, const T (&s)[V], int valid) {
+  if (V > 1 && valid == V) {
+    uint4 raw;
+    memcpy(&raw, s, sizeof(uint4));
+    *reinterpret_cast<uint4 *>(p + i) = raw;
+  } else {
+#pragma unroll
+    for (int j = 0; j < V; ++j)
+      if (j < valid) p[i + j] = s[j];
+  }
+}
+
+// V = elements per chunk (16 bytes' worth, or 1 when some pointer is not 16-byte aligned),
+// NS / NI = compile-time capacity for sources and instructions.
+template <typename T, int V, int NS, int NI>
+__global__ void __launch_bounds__(256) pw_kernel(const __grid_constant__ PwDev p) {
+  const long long n = p.n;
+  const long long nchunks = (n + V - 1) / V;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long c = (long long)blockIdx.x * blockDim.x + threadIdx.x; c < nchunks; c += stride) {
+    const long long i = c * V;
+    const int valid = (n - i) >= V ? V : (int)(n - i);
+    T S[NS][V];
+    T R[NI][V];
+#pragma unroll
+    for (int s = 0; s < NS; ++s) {
+      if (s < p.n_src) {
+        const T *sp = reinterpret_cast<const T *>(p.src[s]);
+        const int mode = p.src_mode[s];
+        if (mode == SRC_FULL) {
+          load_chunk<T, V>(S[s], sp, i, valid);
+        } else if (mode == SRC_ROWVEC) {
+          load_chunk<T, V>(S[s], sp, i % p.src_mod[s], V);
+        } else if (mode == SRC_SCALAR) {
+          const T v = sp[0];
+#pragma unroll
+          for (int j = 0; j < V; ++j) S[s][j] = v;
+        } else if (mode == SRC_CHUNK) {
+          const T v = sp[(i / p.src_div[s]) % p.src_mod[s]];
+#pragma unroll
+          for (int j = 0; j < V; ++j) S[s][j] = v;
+        } else {
+#pragma unroll
+          for (int j = 0; j < V; ++j)
+            S[s][j] = j < valid ? sp[((i + j) / p.src_div[s]) % p.src_mod[s]] : T(0);
+        }
+      }
+    }
+    Step<T, V, NS, NI, 0>::run(p, S, R);
+#pragma unroll
+    for (int o = 0; o < B200_PW_MAX_OUT; ++o) {
+      if (o < p.n_out) {
+        T v[V];
+        fetch<T, V, NS, NI, NI>(v, SEL_INS + p.out_ins[o], S, R, p);
+        store_chunk<T, V>(reinterpret_cast<T *>(p.out[o]), i, v, valid);
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// host side: program checking, lowering, launch
+// ------------------------------------------------------------------------------------------
+
+static bool is_binary(int op) { return op >= B200_OP_ADD && op < B200_OP_BINARY_END; }
+static bool is_unary(int op) { return op >= B200_OP_ABS && op < B200_OP_UNARY_END; }
+
+static int lower_ref(b200_engine *e, const b200_pw_prog *prog, uint8_t ref, int k, uint8_t *sel) {
+  const int kind = ref & 0xC0, idx = ref & 0x3F;
+  if (kind == 0x00) {
+    B200_REQUIRE(e, (uint32_t)idx < prog->n_src, "pointwise: instr %d reads source %d of %u", k, idx,
+                 prog->n_src);
+    *sel = (uint8_t)idx;
+  } else if (kind == 0x40) {
+    B200_REQUIRE(e, (uint32_t)idx < prog->n_imm, "pointwise: instr %d reads immediate %d of %u", k, idx,
+                 prog->n_imm);
+    *sel = (uint8_t)(SEL_IMM + idx);
+  } else if (kind == 0x80) {
+    B200_REQUIRE(e, idx < k, "pointwise: instr %d reads the result of instr %d", k, idx);
+    *sel = (uint8_t)(SEL_INS + idx);
+  } else {
+    return set_error(e, B200_ERR_INVALID, "pointwise: bad operand reference 0x%02x", ref);
+  }
+  return B200_OK;
+}
+
+template <typename T, int V>
+static int launch_sized(b200_engine *e, const PwDev &d, int ns, int ni) {
+  const long long nchunks = (d.n + V - 1) / V;
+  const int threads = 256;
+  long long want = (nchunks + threads - 1) / threads;
+  long long cap = (long long)e->sm_count * 8;
+  int blocks = (int)std::max<long long>(1, std::min(want, cap));
+  if (ns <= 2 && ni <= 2)
+    pw_kernel<T, V, 2, 2><<<blocks, threads, 0, e->stream>>>(d);
+  else if (ns <= 3 && ni <= 4)
+    pw_kernel<T, V, 3, 4><<<blocks, threads, 0, e->stream>>>(d);
+  else if (ns <= 4 && ni <= 8)
+    pw_kernel<T, V, 4, 8><<<blocks, threads, 0, e->stream>>>(d);
+  else
+    pw_kernel<T, V, B200_PW_MAX_SRC, B200_PW_MAX_INSTR><<<blocks, threads, 0, e->stream>>>(d);
+  B200_CHECK_LAUNCH(e, "pw_kernel");
+  return B200_OK;
+}
+
+// Validates a program, lowers it to the device form and launches it (no queueing).
+static int run_program(b200_engine *e, int dtype, const b200_pw_prog *prog, void *const *outs,
+                       const void *const *srcs, int64_t n) {
+  B200_REQUIRE(e, prog && outs && (srcs || prog->n_src == 0), "pointwise: null argument");
+  B200_REQUIRE(e, dtype == B200_F32 || dtype == B200_F64, "pointwise: dtype %d not supported", dtype);
+  B200_REQUIRE(e, n >= 0, "pointwise: negative element count");
+  B200_REQUIRE(e, prog->n_instr >= 1 && prog->n_instr <= B200_PW_MAX_INSTR, "pointwise: %u instructions",
+               prog->n_instr);
+  B200_REQUIRE(e, prog->n_src <= B200_PW_MAX_SRC, "pointwise: %u sources", prog->n_src);
+  B200_REQUIRE(e, prog->n_imm <= B200_PW_MAX_IMM, "pointwise: %u immediates", prog->n_imm);
+  B200_REQUIRE(e, prog->n_out >= 1 && prog->n_out <= B200_PW_MAX_OUT, "pointwise: %u outputs", prog->n_out);
+  if (n == 0) return B200_OK;
+
+  const size_t es = dtype_size(dtype);
+  const int V = (int)(16 / es);
+  PwDev d;
+  memset(&d, 0, sizeof d);
+  d.n = n;
+  d.n_instr = (uint8_t)prog->n_instr;
+  d.n_src = (uint8_t)prog->n_src;
+  d.n_out = (uint8_t)prog->n_out;
+  bool aligned = true;
+  for (uint32_t s = 0; s < prog->n_src; ++s) {
+    B200_REQUIRE(e, srcs[s] != nullptr, "pointwise: source %u is null", s);
+    d.src[s] = srcs[s];
+    const int64_t div = prog->src_div[s], mod = prog->src_mod[s];
+    if (div == 0) {
+      d.src_mode[s] = SRC_FULL;
+      if ((uintptr_t)srcs[s] % 16) aligned = false;
+    } else {
+      B200_REQUIRE(e, div > 0 && mod > 0, "pointwise: source %u has div %lld mod %lld", s, (long long)div,
+                   (long long)mod);
+      d.src_div[s] = div;
+      d.src_mod[s] = mod;
+      if (mod == 1)
+        d.src_mode[s] = SRC_SCALAR;
+      else if (div == 1 && mod % V == 0 && (uintptr_t)srcs[s] % 16 == 0)
+        d.src_mode[s] = SRC_ROWVEC;
+      else if (div % V == 0)
+        d.src_mode[s] = SRC_CHUNK;
+      else
+        d.src_mode[s] = SRC_GENERAL;
+    }
+  }
+  for (uint32_t k = 0; k < prog->n_imm; ++k) d.imm[k] = prog->imm[k];
+  for (uint32_t k = 0; k < prog->n_instr; ++k) {
+    const b200_pw_instr &in = prog->instr[k];
+    B200_REQUIRE(e, is_binary(in.op) || is_unary(in.op), "pointwise: unknown op %d in instr %u", in.op, k);
+    d.op[k] = in.op;
+    int rc = lower_ref(e, prog, in.a, (int)k, &d.ra[k]);
+    if (rc) return rc;
+    if (is_binary(in.op)) {
+      rc = lower_ref(e, prog, in.b, (int)k, &d.rb[k]);
+      if (rc) return rc;
+    } else {
+      d.rb[k] = d.ra[k];
+    }
+  }
+  for (uint32_t o = 0; o < prog->n_out; ++o) {
+    B200_REQUIRE(e, outs[o] != nullptr, "pointwise: output %u is null", o);
+    B200_REQUIRE(e, prog->out_instr[o] < prog->n_instr, "pointwise: output %u names instr %u", o,
+                 prog->out_instr[o]);
+    d.out[o] = outs[o];
+    d.out_ins[o] = prog->out_instr[o];
+    if ((uintptr_t)outs[o] % 16) aligned = false;
+  }
+  // a ROWVEC source needs the chunk grid itself aligned, which `aligned` guarantees
+  if (!aligned)
+    for (uint32_t s = 0; s < prog->n_src; ++s)
+      if (d.src_mode[s] == SRC_ROWVEC || d.src_mode[s] == SRC_CHUNK) d.src_mode[s] = SRC_GENERAL;
+
+  const int ns = (int)prog->n_src, ni = (int)prog->n_instr;
+  if (dtype == B200_F32)
+    return aligned ? launch_sized<float, 4>(e, d, ns, ni) : launch_sized<float, 1>(e, d, ns, ni);
+  return aligned ? launch_sized<double, 2>(e, d, ns, ni) : launch_sized<double, 1>(e, d, ns, ni);
+}
+
+// ------------------------------------------------------------------------------------------
+// the fusion pass: turns a list of queued calls into programs
+// ------------------------------------------------------------------------------------------
+
+struct Range {
+  uint64_t lo, hi;  // [lo, hi)
+};
+static bool overlaps(const Range &x, const Range &y) { return x.lo < y.hi && y.lo < x.hi; }
+
+struct FusedKernel {
+  b200_pw_prog prog;
+  const void *srcs[B200_PW_MAX_SRC];
+  void *outs[B200_PW_MAX_OUT];
+  int dtype;
+  int64_t n;
+  int first, last;  // calls [first, last)
+  int loads, stores;
+};
+
+namespace {
+
+struct Builder {
+  // value currently held for a full-size buffer: a source slot or an instruction result
+  struct Loc {
+    uint64_t ptr;
+    uint8_t ref;
+    int writer;  // index of the call that last wrote it inside this kernel, -1 if only read
+  };
+  std::vector<Loc> locs;
+  struct Bsrc {
+    uint64_t ptr;
+    int64_t div, mod;
+    uint8_t ref;
+  };
+  std::vector<Bsrc> bsrcs;
+  std::vector<Range> read_ranges, write_ranges, bcast_ranges;
+  b200_pw_prog prog;
+  const void *srcs[B200_PW_MAX_SRC];
+  int dtype = 0;
+  int64_t n = 0;
+  int first = 0;
+
+  void start(const b200_pw_call &c, int idx) {
+    locs.clear();
+    bsrcs.clear();
+    read_ranges.clear();
+    write_ranges.clear();
+    bcast_ranges.clear();
+    memset(&prog, 0, sizeof prog);
+    dtype = c.dtype;
+    n = c.n;
+    first = idx;
+  }
+  Loc *find(uint64_t ptr) {
+    for (auto &l : locs)
+      if (l.ptr == ptr) return &l;
+    return nullptr;
+  }
+  int count_outputs() const {
+    int k = 0;
+    for (auto &l : locs)
+      if (l.writer >= 0) ++k;
+    return k;
+  }
+};
+
+// Number of new source slots / immediates / output buffers a call would add, and whether it
+// can legally join the kernel under construction.
+bool can_join(const Builder &b, const b200_pw_call &c, size_t es, int max_instr) {
+  if (c.dtype != b.dtype || c.n != b.n) return false;
+  if ((int)b.prog.n_instr + 1 > max_instr) return false;
+  const uint64_t bytes = (uint64_t)c.n * es;
+  int new_src = 0, new_imm = 0;
+  auto full_operand = [&](uint64_t ptr) -> bool {
+    for (auto &l : b.locs)
+      if (l.ptr == ptr) return true;
+    Range r{ptr, ptr + bytes};
+    // a buffer that partly overlaps something this kernel writes would see half-updated data
+    for (auto &w : b.write_ranges)
+      if (overlaps(r, w)) return false;
+    ++new_src;
+    return true;
+  };
+  auto small_operand = [&](uint64_t ptr, int64_t div, int64_t mod) -> bool {
+    for (auto &s : b.bsrcs)
+      if (s.ptr == ptr && s.div == div && s.mod == mod) return true;
+    Range r{ptr, ptr + (uint64_t)mod * es};
+    for (auto &w : b.write_ranges)
+      if (overlaps(r, w)) return false;
+    ++new_src;
+    return true;
+  };
+  const bool unary = c.form == 3;
+  const bool a_is_tensor = unary || c.form == B200_VV || c.form == B200_VS;
+  const bool b_is_tensor = !unary && (c.form == B200_VV || c.form == B200_SV);
+  if (a_is_tensor) {
+    if (c.bcast == 2) {
+      if (!small_operand(c.a, c.bdiv, c.bmod)) return false;
+    } else if (!full_operand(c.a))
+      return false;
+  }
+  if (b_is_tensor && !(c.a == c.b && c.bcast == 0)) {
+    if (c.bcast == 1) {
+      if (!small_operand(c.b, c.bdiv, c.bmod)) return false;
+    } else if (!full_operand(c.b))
+      return false;
+  }
+  if (!unary && c.form != B200_VV) {
+    if (c.scalar_ptr) {
+      if (!small_operand(c.scalar_ptr, 1, 1)) return false;
+    } else
+      ++new_imm;
+  }
+  if ((int)b.prog.n_src + new_src > B200_PW_MAX_SRC) return false;
+  if ((int)b.prog.n_imm + new_imm > B200_PW_MAX_IMM) return false;
+  // destination: must be a buffer already tracked, or disjoint from everything touched so far
+  bool known = false;
+  for (auto &l : b.locs)
+    if (l.ptr == c.dst) known = true;
+  Range d{c.dst, c.dst + bytes};
+  if (!known) {
+    for (auto &r : b.read_ranges)
+      if (overlaps(d, r)) return false;
+    for (auto &w : b.write_ranges)
+      if (overlaps(d, w)) return false;
+    // operands of this very call that are new and partly overlap dst
+    if (a_is_tensor && c.bcast != 2 && c.a != c.dst && overlaps(d, Range{c.a, c.a + bytes})) return false;
+    if (b_is_tensor && c.bcast != 1 && c.b != c.dst && overlaps(d, Range{c.b, c.b + bytes})) return false;
+  }
+  for (auto &r : b.bcast_ranges)
+    if (overlaps(d, r)) return false;
+  if (c.bcast == 1 && overlaps(d, Range{c.b, c.b + (uint64_t)c.bmod * es})) return false;
+  if (c.bcast == 2 && overlaps(d, Range{c.a, c.a + (uint64_t)c.bmod * es})) return false;
+  if (c.scalar_ptr && overlaps(d, Range{c.scalar_ptr, c.scalar_ptr + es})) return false;
+  int outs = b.count_outputs();
+  bool dst_written = false;
+  for (auto &l : b.locs)
+    if (l.ptr == c.dst && l.writer >= 0) dst_written = true;
+  if (!dst_written && outs + 1 > B200_PW_MAX_OUT) return false;
+  return true;
+}
+
+void join(Builder &b, const b200_pw_call &c, int idx, size_t es) {
+  const uint64_t bytes = (uint64_t)c.n * es;
+  auto full_operand = [&](uint64_t ptr) -> uint8_t {
+    if (auto *l = b.find(ptr)) return l->ref;
+    const int k = (int)b.prog.n_src++;
+    b.srcs[k] = (const void *)ptr;
+    b.prog.src_div[k] = 0;
+    b.prog.src_mod[k] = 0;
+    b.locs.push_back({ptr, B200_REF_SRC(k), -1});
+    b.read_ranges.push_back({ptr, ptr + bytes});
+    return B200_REF_SRC(k);
+  };
+  auto small_operand = [&](uint64_t ptr, int64_t div, int64_t mod) -> uint8_t {
+    for (auto &s : b.bsrcs)
+      if (s.ptr == ptr && s.div == div && s.mod == mod) return s.ref;
+    const int k = (int)b.prog.n_src++;
+    b.srcs[k] = (const void *)ptr;
+    b.prog.src_div[k] = div;
+    b.prog.src_mod[k] = mod;
+    b.bsrcs.push_back({ptr, div, mod, B200_REF_SRC(k)});
+    b.bcast_ranges.push_back({ptr, ptr + (uint64_t)mod * es});
+    return B200_REF_SRC(k);
+  };
+  auto scalar_operand = [&]() -> uint8_t {
+    if (c.scalar_ptr) return small_operand(c.scalar_ptr, 1, 1);
+    const int k = (int)b.prog.n_imm++;
+    b.prog.imm[k] = c.scalar;
+    return B200_REF_IMM(k);
+  };
+  const bool unary = c.form == 3;
+  uint8_t ra = 0, rb = 0;
+  if (unary) {
+    ra = c.bcast == 2 ? small_operand(c.a, c.bdiv, c.bmod) : full_operand(c.a);
+    rb = ra;
+  } else {
+    if (c.form == B200_SV)
+      ra = scalar_operand();
+    else
+      ra = c.bcast == 2 ? small_operand(c.a, c.bdiv, c.bmod) : full_operand(c.a);
+    if (c.form == B200_VS)
+      rb = scalar_operand();
+    else
+      rb = c.bcast == 1 ? small_operand(c.b, c.bdiv, c.bmod) : full_operand(c.b);
+  }
+  const int k = (int)b.prog.n_instr++;
+  b.prog.instr[k].op = (uint8_t)c.op;
+  b.prog.instr[k].a = ra;
+  b.prog.instr[k].b = rb;
+  if (auto *l = b.find(c.dst)) {
+    l->ref = B200_REF_INS(k);
+    l->writer = idx;
+  } else {
+    b.locs.push_back({c.dst, B200_REF_INS(k), idx});
+  }
+  b.write_ranges.push_back({c.dst, c.dst + bytes});
+}
+
+// Closes the kernel: every buffer written becomes an output unless it was released before
+// any call outside this kernel could have read it.
+void finish(Builder &b, int end, const int *released_at, FusedKernel *fk) {
+  fk->dtype = b.dtype;
+  fk->n = b.n;
+  fk->first = b.first;
+  fk->last = end;
+  fk->loads = 0;
+  for (auto &l : b.locs) (void)l;
+  for (uint32_t s = 0; s < b.prog.n_src; ++s)
+    if (b.prog.src_div[s] == 0) fk->loads++;
+  int nout = 0;
+  int last_out_candidate = -1;
+  for (size_t i = 0; i < b.locs.size(); ++i) {
+    auto &l = b.locs[i];
+    if (l.writer < 0) continue;
+    last_out_candidate = (int)i;
+    const int rel = released_at ? released_at[l.writer] : -1;
+    const bool dead = rel >= 0 && rel > l.writer && rel <= end;
+    if (dead) continue;
+    fk->outs[nout] = (void *)l.ptr;
+    b.prog.out_instr[nout] = (uint8_t)(l.ref & 0x3F);
+    ++nout;
+  }
+  if (nout == 0 && last_out_candidate >= 0) {
+    // every result was released unread: nothing observable remains, but keep one store so
+    // the program stays well-formed (the caller released that memory; writing it is harmless)
+    auto &l = b.locs[last_out_candidate];
+    fk->outs[0] = (void *)l.ptr;
+    b.prog.out_instr[0] = (uint8_t)(l.ref & 0x3F);
+    nout = 1;
+  }
+  b.prog.n_out = (uint32_t)nout;
+  fk->stores = nout;
+  fk->prog = b.prog;
+  for (int s = 0; s < B200_PW_MAX_SRC; ++s) fk->srcs[s] = b.srcs[s];
+}
+
+}  // namespace
+
+// The fused kernels never exceed this many instructions: it is the largest program that the
+// <4 sources, 8 instructions> instantiation holds entirely in registers.
+static const int kMaxFusedInstr = 8;
+
+static void plan(const b200_pw_call *calls, int n_calls, const int *released_at,
+                 std::vector<FusedKernel> *out) {
+  out->clear();
+  Builder b;
+  int i = 0;
+  while (i < n_calls) {
+    const size_t es = dtype_size(calls[i].dtype);
+    b.start(calls[i], i);
+    join(b, calls[i], i, es);
+    int j = i + 1;
+    while (j < n_calls && can_join(b, calls[j], es, kMaxFusedInstr)) {
+      join(b, calls[j], j, es);
+      ++j;
+    }
+    FusedKernel fk;
+    memset(&fk, 0, sizeof fk);
+    finish(b, j, released_at, &fk);
+    out->push_back(fk);
+    i = j;
+  }
+}
+
+static void released_positions(b200_engine *e, std::vector<int> *rel) {
+  rel->assign(e->pending.size(), -1);
+  // e->dead holds (pointer, queue length at release) pairs flattened as two entries
+  for (size_t k = 0; k + 1 < e->dead.size(); k += 2) {
+    const uint64_t ptr = (uint64_t)e->dead[k];
+    const int pos = (int)(uintptr_t)e->dead[k + 1];
+    // the release concerns the last write to ptr queued before `pos`
+    for (int c = std::min<int>(pos, (int)e->pending.size()) - 1; c >= 0; --c)
+      if (e->pending[c].dst == ptr) {
+        (*rel)[c] = pos;
+        break;
+      }
+  }
+}
+
+void note_put(b200_engine *e, void *ptr) {
+  if (e->pending.empty()) return;
+  for (auto &c : e->pending)
+    if (c.dst == (uint64_t)ptr) {
+      e->dead.push_back(ptr);
+      e->dead.push_back((void *)(uintptr_t)e->pending.size());
+      return;
+    }
+}
+
+int plan_pending(b200_engine *e, int *n_kernels) {
+  std::vector<int> rel;
+  released_positions(e, &rel);
+  std::vector<FusedKernel> ks;
+  plan(e->pending.data(), (int)e->pending.size(), rel.data(), &ks);
+  *n_kernels = (int)ks.size();
+  return B200_OK;
+}
+
+int flush_pending(b200_engine *e) {
+  if (e->pending.empty()) {
+    e->dead.clear();
+    return B200_OK;
+  }
+  std::vector<int> rel;
+  released_positions(e, &rel);
+  std::vector<FusedKernel> ks;
+  plan(e->pending.data(), (int)e->pending.size(), rel.data(), &ks);
+  e->pending.clear();
+  e->dead.clear();
+  for (auto &k : ks) {
+    int rc = run_program(e, k.dtype, &k.prog, k.outs, k.srcs, k.n);
+    if (rc != B200_OK) return rc;
+  }
+  return B200_OK;
+}
+
+static int enqueue(b200_engine *e, const b200_pw_call &c) {
+  e->pending.push_back(c);
+  if (e->flags & B200_ENGINE_NO_DEFER) return flush_pending(e);
+  // keep the queue bounded: a tape that never flushes would otherwise grow without limit
+  if (e->pending.size() >= 4096) return flush_pending(e);
+  return B200_OK;
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" {
+
+int b200_binary(b200_engine *e, int op, int dtype, int form, void *dst, const void *a, const void *b,
+                double scalar, int scalar_on_device, int64_t n) {
+  if (!e) return B200_ERR_INVALID;
+  std::lock_guard<std::recursive_mutex> lk(e->mu);
+  B200_REQUIRE(e, is_binary(op), "b200_binary: %d is not a binary op", op);
+  B200_REQUIRE(e, dtype == B200_F32 || dtype == B200_F64, "b200_binary: dtype %d not supported", dtype);
+  B200_REQUIRE(e, form == B200_VV || form == B200_VS || form == B200_SV, "b200_binary: bad form %d", form);
+  B200_REQUIRE(e, n >= 0, "b200_binary: negative element count");
+  if (n == 0) return B200_OK;
+  B200_REQUIRE(e, dst != nullptr, "b200_binary: dst is null");
+  b200_pw_call c;
+  memset(&c, 0, sizeof c);
+  c.op = op;
+  c.dtype = dtype;
+  c.form = form;
+  c.dst = (uint64_t)dst;
+  c.n = n;
+  c.scalar = scalar;
+  if (form == B200_VV) {
+    B200_REQUIRE(e, a && b, "b200_binary: null operand");
+    c.a = (uint64_t)a;
+    c.b = (uint64_t)b;
+  } else if (form == B200_VS) {
+    B200_REQUIRE(e, a != nullptr, "b200_binary: null operand");
+    c.a = (uint64_t)a;
+    if (scalar_on_device) {
+      B200_REQUIRE(e, b != nullptr, "b200_binary: device scalar is null");
+      c.scalar_ptr = (uint64_t)b;
+    }
+  } else {
+    B200_REQUIRE(e, b != nullptr, "b200_binary: null operand");
+    c.b = (uint64_t)b;
+    if (scalar_on_device) {
+      B200_REQUIRE(e, a != nullptr, "b200_binary: device scalar is null");
+      c.scalar_ptr = (uint64_t)a;
+    }
+  }
+  DeviceGuard g(e);
+  return enqueue(e, c);
+}
+
+int b200_unary(b200_engine *e, int op, int dtype, void *dst, const void *a, int64_t n) {
+  if (!e) return B200_ERR_INVALID;
+  std::lock_guard<std::recursive_mutex> lk(e->mu);
+  B200_REQUIRE(e, is_unary(op), "b200_unary: %d is not a unary op", op);
+  B200_REQUIRE(e, dtype == B200_F32 || dtype == B200_F64, "b200_unary: dtype %d not supported", dtype);
+  B200_REQUIRE(e, n >= 0, "b200_unary: negative element count");
+  if (n == 0) return B200_OK;
+  B200_REQUIRE(e, dst && a, "b200_unary: null pointer");
+  b200_pw_call c;
+  memset(&c, 0, sizeof c);
+  c.op = op;
+  c.dtype = dtype;
+  c.form = 3;
+  c.dst = (uint64_t)dst;
+  c.a = (uint64_t)a;
+  c.n = n;
+  DeviceGuard g(e);
+  return enqueue(e, c);
+}
+
+int b200_binary_bcast(b200_engine *e, int op, int dtype, void *dst, const void *a, const void *b, int64_t n,
+                      int64_t b_div, int64_t b_mod, int bcast_is_a) {
+  if (!e) return B200_ERR_INVALID;
+  std::lock_guard<std::recursive_mutex> lk(e->mu);
+  B200_REQUIRE(e, is_binary(op), "b200_binary_bcast: %d is not a binary op", op);
+  B200_REQUIRE(e, dtype == B200_F32 || dtype == B200_F64, "b200_binary_bcast: dtype %d not supported", dtype);
+  B200_REQUIRE(e, n >= 0, "b200_binary_bcast: negative element count");
+  B200_REQUIRE(e, b_div > 0 && b_mod > 0, "b200_binary_bcast: div %lld mod %lld", (long long)b_div,
+               (long long)b_mod);
+  if (n == 0) return B200_OK;
+  B200_REQUIRE(e, dst && a && b, "b200_binary_bcast: null pointer");
+  b200_pw_call c;
+  memset(&c, 0, sizeof c);
+  c.op = op;
+  c.dtype = dtype;
+  c.form = B200_VV;
+  c.dst = (uint64_t)dst;
+  c.a = (uint64_t)a;
+  c.b = (uint64_t)b;
+  c.n = n;
+  c.bcast = bcast_is_a ? 2 : 1;
+  c.bdiv = b_div;
+  c.bmod = b_mod;
+  DeviceGuard g(e);
+  return enqueue(e, c);
+}
+
+int b200_pointwise(b200_engine *e, int dtype, const b200_pw_prog *prog, void *const *outs,
+                   const void *const *srcs, int64_t n) {
+  if (!e) return B200_ERR_INVALID;
+  std::lock_guard<std::recursive_mutex> lk(e->mu);
+  DeviceGuard g(e);
+  int rc = flush_pending(e);
+  if (rc != B200_OK) return rc;
+  return run_program(e, dtype, prog, outs, srcs, n);
+}
+
+int b200_pending(b200_engine *e, int *n_calls, int *n_kernels) {
+  if (!e) return B200_ERR_INVALID;
+  std::lock_guard<std::recursive_mutex> lk(e->mu);
+  if (n_calls) *n_calls = (int)e->pending.size();
+  if (n_kernels) {
+    *n_kernels = 0;
+    if (!e->pending.empty()) return plan_pending(e, n_kernels);
+  }
+  return B200_OK;
+}
+
+int b200_fusion_plan(const b200_pw_call *calls, int n_calls, const int *released_at, int *kernel_of_call,
+                     int *n_kernels, int *loads, int *stores) {
+  if (!calls || n_calls < 0 || !n_kernels) return B200_ERR_INVALID;
+  std::vector<FusedKernel> ks;
+  plan(calls, n_calls, released_at, &ks);
+  *n_kernels = (int)ks.size();
+  for (size_t k = 0; k < ks.size(); ++k) {
+    if (kernel_of_call)
+      for (int c = ks[k].first; c < ks[k].last; ++c) kernel_of_call[c] = (int)k;
+    if (loads) loads[k] = ks[k].loads;
+    if (stores) stores[k] = ks[k].stores;
+  }
+  return B200_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,265 @@
+"""Host-side mirror of gorgonia's `cuda.Engine` over the C ABI.
+
+The method set, argument meaning and error behaviour follow gorgonia's cuda package
+(cuda/engine.go:17-35 lists the interfaces it implements): Add/Sub/Mul/Div/Pow/Mod,
+Lt/Lte/Gt/Gte/ElEq/ElNe with their *Scalar forms (cuda/arith.go, cuda/cmp.go),
+MatMul/MatVecMul/Outer (cuda/linalg.go), Get/Put/ResetAllocator (cuda/arena.go),
+HasNaN/HasInf (cuda/engine.go:144-191), Signal/DoWork/Sync (cuda/external.go:46-50,223-276).
+The Go shim a gorgonia build would use calls the same C functions through cgo; this Python
+class exists so the parity tests read like gorgonia's own tests.
+
+Nothing here computes on the host: every method forwards to libgorgonia_b200.so.
+"""
+import ctypes as C
+
+import numpy as np
+
+from . import _lib
+from ._lib import B200Error, check, lib
+
+_DT = {np.dtype(np.float32): _lib.F32, np.dtype(np.float64): _lib.F64}
+
+
+def dtype_code(dt):
+    dt = np.dtype(dt)
+    if dt not in _DT:
+        raise B200Error(_lib.ERR_UNSUPPORTED, f"dtype {dt} not supported")
+    return _DT[dt]
+
+
+class Tensor:
+    """A dense row-major tensor living in an engine's arena (the role `*tensor.Dense` with
+    manually managed memory plays in gorgonia, values.go:129-148)."""
+
+    def __init__(self, engine, ptr, shape, dtype, owned=True):
+        self.engine = engine
+        self.ptr = ptr
+        self.shape = tuple(int(s) for s in shape)
+        self.dtype = np.dtype(dtype)
+        self.owned = owned
+
+    @property
+    def size(self):
+        n = 1
+        for s in self.shape:
+            n *= s
+        return n
+
+    @property
+    def nbytes(self):
+        return self.size * self.dtype.itemsize
+
+    def numpy(self):
+        out = np.empty(self.shape, dtype=self.dtype)
+        if out.size:
+            check(lib.b200_memcpy_d2h(self.engine.h, out.ctypes.data, self.ptr, out.nbytes), self.engine.h)
+        return out
+
+    def set(self, arr):
+        arr = np.ascontiguousarray(arr, dtype=self.dtype)
+        assert arr.size == self.size
+        if arr.size:
+            check(lib.b200_memcpy_h2d(self.engine.h, self.ptr, arr.ctypes.data, arr.nbytes), self.engine.h)
+        return self
+
+    def reshape(self, *shape):
+        t = Tensor(self.engine, self.ptr, shape, self.dtype, owned=False)
+        assert t.size == self.size
+        return t
+
+    def free(self):
+        if self.owned and self.ptr:
+            self.engine.Put(self.ptr, self.nbytes)
+            self.ptr = None
+
+
+class Engine:
+    def __init__(self, device=0, arena_bytes=1 << 30, managed=False, defer=True):
+        flags = (_lib.ENGINE_MANAGED if managed else 0) | (0 if defer else _lib.ENGINE_NO_DEFER)
+        h = C.c_void_p()
+        rc = lib.b200_engine_create(device, arena_bytes, flags, C.byref(h))
+        if rc != _lib.OK:
+            raise B200Error(rc, (lib.b200_last_error(None) or b"").decode())
+        self.h = h
+        self.device = device
+
+    # ---- lifecycle -------------------------------------------------------------------
+    def Close(self):
+        if self.h:
+            lib.b200_engine_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.Close()
+        except Exception:
+            pass
+
+    def DoWork(self):
+        check(lib.b200_flush(self.h), self.h)
+
+    def Signal(self):
+        check(lib.b200_sync(self.h), self.h)
+
+    Sync = Signal
+
+    @property
+    def stream(self):
+        return int(lib.b200_engine_stream(self.h))
+
+    @property
+    def launches(self):
+        return int(lib.b200_launch_count(self.h))
+
+    def pending(self):
+        n, k = C.c_int(), C.c_int()
+        check(lib.b200_pending(self.h, C.byref(n), C.byref(k)), self.h)
+        return n.value, k.value
+
+    # ---- device timing -------------------------------------------------------------
+    def event(self):
+        ev = C.c_void_p()
+        check(lib.b200_event_create(self.h, C.byref(ev)), self.h)
+        return ev
+
+    def record(self, ev):
+        check(lib.b200_event_record(self.h, ev), self.h)
+
+    def elapsed_ms(self, ev0, ev1):
+        ms = C.c_float()
+        check(lib.b200_event_elapsed_ms(self.h, ev0, ev1, C.byref(ms)), self.h)
+        return ms.value
+
+    def host_alloc(self, nbytes):
+        p = C.c_void_p()
+        rc = lib.b200_host_alloc(int(nbytes), C.byref(p))
+        if rc != _lib.OK:
+            raise B200Error(rc, (lib.b200_last_error(None) or b"").decode())
+        return p.value
+
+    # ---- arena -----------------------------------------------------------------------
+    def Get(self, nbytes):
+        p = C.c_void_p()
+        check(lib.b200_get(self.h, int(nbytes), C.byref(p)), self.h)
+        return p.value
+
+    def Put(self, ptr, nbytes=0):
+        check(lib.b200_put(self.h, ptr, int(nbytes)), self.h)
+
+    def ResetAllocator(self):
+        check(lib.b200_reset(self.h), self.h)
+
+    def arena_stats(self):
+        v = [C.c_int64() for _ in range(4)]
+        check(lib.b200_arena_stats(self.h, *[C.byref(x) for x in v]), self.h)
+        return dict(zip(("used", "free", "largest_free", "free_blocks"), (x.value for x in v)))
+
+    # ---- tensors ---------------------------------------------------------------------
+    def empty(self, shape, dtype=np.float32):
+        if isinstance(shape, int):
+            shape = (shape,)
+        dtype = np.dtype(dtype)
+        n = int(np.prod(shape, dtype=np.int64)) if len(shape) else 1
+        ptr = self.Get(max(n, 1) * dtype.itemsize)
+        return Tensor(self, ptr, shape, dtype)
+
+    def tensor(self, arr, dtype=None):
+        arr = np.ascontiguousarray(arr, dtype=dtype)
+        return self.empty(arr.shape, arr.dtype).set(arr)
+
+    # ---- pointwise: Engine.<Op>(a, b, opts...) -----------------------------------------
+    def _dest(self, a, reuse, unsafe, who):
+        # cuda/arith.go:34-49: a reuse tensor, or unsafe; safe and incr are errors
+        if reuse is not None:
+            if reuse.size != a.size or reuse.dtype != a.dtype:
+                raise B200Error(_lib.ERR_INVALID, f"{who}: reuse tensor does not match the operand")
+            return reuse
+        if unsafe:
+            return a
+        raise B200Error(_lib.ERR_INVALID,
+                        f"{who}: a reuse tensor must be passed in, or the operation must be unsafe")
+
+    def _binary(self, op, a, b, reuse=None, unsafe=False):
+        if a.size != b.size or a.dtype != b.dtype:
+            raise B200Error(_lib.ERR_INVALID, f"{op}: operands differ in size or dtype")
+        dst = self._dest(a, reuse, unsafe, op)
+        check(lib.b200_binary(self.h, _lib.OP[op], dtype_code(a.dtype), _lib.VV, dst.ptr, a.ptr, b.ptr, 0.0, 0,
+                              a.size), self.h)
+        return dst
+
+    def _binary_scalar(self, op, t, s, leftTensor=True, reuse=None, unsafe=False):
+        dst = self._dest(t, reuse, unsafe, op + "Scalar")
+        on_dev = isinstance(s, Tensor)
+        sval = 0.0 if on_dev else float(s)
+        sptr = s.ptr if on_dev else None
+        if leftTensor:
+            rc = lib.b200_binary(self.h, _lib.OP[op], dtype_code(t.dtype), _lib.VS, dst.ptr, t.ptr, sptr, sval,
+                                 int(on_dev), t.size)
+        else:
+            rc = lib.b200_binary(self.h, _lib.OP[op], dtype_code(t.dtype), _lib.SV, dst.ptr, sptr, t.ptr, sval,
+                                 int(on_dev), t.size)
+        check(rc, self.h)
+        return dst
+
+    def BroadcastBinary(self, op, a, b, div, mod, bcast_is_a=False, reuse=None, unsafe=False):
+        full = b if bcast_is_a else a
+        dst = self._dest(full, reuse, unsafe, op)
+        check(lib.b200_binary_bcast(self.h, _lib.OP[op], dtype_code(full.dtype), dst.ptr, a.ptr, b.ptr, full.size,
+                                    int(div), int(mod), int(bcast_is_a)), self.h)
+        return dst
+
+    def Unary(self, op, a, reuse=None, unsafe=False):
+        dst = self._dest(a, reuse, unsafe, op)
+        check(lib.b200_unary(self.h, _lib.OP[op], dtype_code(a.dtype), dst.ptr, a.ptr, a.size), self.h)
+        return dst
+
+    def Pointwise(self, prog, outs, srcs, n, dtype=np.float32):
+        """prog: dict(instr=[(op, a_ref, b_ref)], imm=[...], out=[instr idx], bcast={src: (div, mod)})."""
+        p = _lib.PwProg()
+        p.n_instr = len(prog["instr"])
+        p.n_src = len(srcs)
+        p.n_imm = len(prog.get("imm", []))
+        p.n_out = len(prog["out"])
+        for k, (op, ra, rb) in enumerate(prog["instr"]):
+            p.instr[k].op = _lib.OP[op]
+            p.instr[k].a = ra
+            p.instr[k].b = rb
+        for k, v in enumerate(prog.get("imm", [])):
+            p.imm[k] = v
+        for k, v in enumerate(prog["out"]):
+            p.out_instr[k] = v
+        for s, (d, m) in prog.get("bcast", {}).items():
+            p.src_div[s] = d
+            p.src_mod[s] = m
+        o = (C.c_void_p * len(outs))(*[t.ptr for t in outs])
+        s = (C.c_void_p * max(len(srcs), 1))(*[t.ptr for t in srcs])
+        check(lib.b200_pointwise(self.h, dtype_code(dtype), C.byref(p), o, s, int(n)), self.h)
+
+    def HasNaN(self, t):
+        r = C.c_int()
+        check(lib.b200_has_nan(self.h, dtype_code(t.dtype), t.ptr, t.size, C.byref(r)), self.h)
+        return bool(r.value)
+
+    def HasInf(self, t):
+        r = C.c_int()
+        check(lib.b200_has_inf(self.h, dtype_code(t.dtype), t.ptr, t.size, C.byref(r)), self.h)
+        return bool(r.value)
+
+
+def _mk(op, name):
+    def f(self, a, b, reuse=None, unsafe=False):
+        return self._binary(op, a, b, reuse, unsafe)
+
+    def fs(self, t, s, leftTensor=True, reuse=None, unsafe=False):
+        return self._binary_scalar(op, t, s, leftTensor, reuse, unsafe)
+
+    f.__name__ = name
+    fs.__name__ = name + "Scalar"
+    setattr(Engine, name, f)
+    setattr(Engine, name + "Scalar", fs)
+
+
+for _op, _name in [("add", "Add"), ("sub", "Sub"), ("mul", "Mul"), ("div", "Div"), ("pow", "Pow"),
+                   ("mod", "Mod"), ("lt", "Lt"), ("lte", "Lte"), ("gt", "Gt"), ("gte", "Gte"),
+                   ("eq", "ElEq"), ("ne", "ElNe")]:
+    _mk(_op, _name)

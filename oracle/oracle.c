@@ -1,0 +1,517 @@
+/*
+ * oracle.c — CPU restatement of the semantics of gorgonia's CPU engine for the ops that the
+ * B200 engine executes. TEST INFRASTRUCTURE ONLY: it is the checker for tests/, for
+ * __graft_entry__.smoke() and for bench.py's CPU-baseline legs. Nothing in the product
+ * (gorgonia_b200/, libgorgonia_b200.so) links, imports or calls it.
+ *
+ * What it follows. gorgonia's own repository holds the dispatch and the nn kernels; the
+ * arithmetic of the dense ops lives in modules that the repository pins but does not vendor:
+ *   gorgonia.org/tensor v0.9.23 (StdEng Add..Pow, Lt..ElNe, MatMul/MatVecMul/Outer, SoftMax,
+ *   Repeat, Transpose, Sum/Max, ByIndices), gonum.org/v1/gonum v0.11.0 (blas/gonum Sgemm,
+ *   Sgemv, Sger), github.com/chewxy/math32 v1.10.1 (float32 Exp/Log/Pow/...).
+ * Those are restated from their published behaviour: IEEE arithmetic per element without
+ * FMA contraction; BLAS-3/2 as plain sums of products. Each function cites the gorgonia
+ * file:line whose call it stands for.
+ *
+ * Pinned against: the golden tables of gorgonia's tests (tests/golden/, extracted from
+ * op_math_test.go, op_softmax_test.go, nn_test.go, known_issues_test.go,
+ * op_by_indices_test.go, example_*_test.go and others; tests/test_oracle_golden.py).
+ * PARITY UNPINNED for: last-ulp behaviour of math32's float32 transcendentals, gonum's
+ * Sgemm summation order, and tensor.SoftMax's internal formulation; no bit-level vector
+ * exists for them in gorgonia. Here float32 transcendentals are computed in double and
+ * rounded once, and sums of products are accumulated in double.
+ *
+ * Build: make -C oracle   (gcc -O3 -fopenmp -ffp-contract=off).
+ */
+#include <math.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+#include <float.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+/* op codes: identical to B200_OP_* of include/gorgonia_b200.h */
+enum {
+  OP_ADD = 0, OP_SUB, OP_MUL, OP_DIV, OP_POW, OP_MOD, OP_LT, OP_GT, OP_LTE, OP_GTE, OP_EQ, OP_NE,
+  OP_ABS = 32, OP_SIGN, OP_CEIL, OP_FLOOR, OP_SIN, OP_COS, OP_EXP, OP_LN, OP_LOG2, OP_NEG, OP_SQUARE,
+  OP_SQRT, OP_INV, OP_INVSQRT, OP_CUBE, OP_TANH, OP_SIGMOID, OP_LOG1P, OP_EXPM1, OP_SOFTPLUS
+};
+
+int oracle_threads(void) {
+#ifdef _OPENMP
+  return omp_get_max_threads();
+#else
+  return 1;
+#endif
+}
+
+/* ---- scalar semantics -----------------------------------------------------------------
+ * binary: operatorPointwise_binary.go:40-293 (scalar lambdas) and
+ *         operatorPointwise_binary_const.go:5-22 (tensor.Add.. / tensor.Lt..); compare ops
+ *         as used by the graphs of nn.go:104-112,154-155 (retSame: 1/0 in operand dtype).
+ * unary:  operatorPointwise_unary_const.go:10-71, math_nooptim.go:18-51 (tanh f32 through
+ *         float64, sigmoid f32 thresholds -88/15 through float64, invsqrt = 1/sqrt),
+ *         operatorPointwise_unary.go (sign, square, cube, softplus lambdas). */
+
+static inline float bin_f32(int op, float x, float y) {
+  switch (op) {
+    case OP_ADD: return x + y;
+    case OP_SUB: return x - y;
+    case OP_MUL: return x * y;
+    case OP_DIV: return x / y;
+    case OP_POW: return (float)pow((double)x, (double)y);
+    case OP_MOD: return (float)fmod((double)x, (double)y);
+    case OP_LT: return x < y ? 1.f : 0.f;
+    case OP_GT: return x > y ? 1.f : 0.f;
+    case OP_LTE: return x <= y ? 1.f : 0.f;
+    case OP_GTE: return x >= y ? 1.f : 0.f;
+    case OP_EQ: return x == y ? 1.f : 0.f;
+    case OP_NE: return x != y ? 1.f : 0.f;
+  }
+  return NAN;
+}
+static inline double bin_f64(int op, double x, double y) {
+  switch (op) {
+    case OP_ADD: return x + y;
+    case OP_SUB: return x - y;
+    case OP_MUL: return x * y;
+    case OP_DIV: return x / y;
+    case OP_POW: return pow(x, y);
+    case OP_MOD: return fmod(x, y);
+    case OP_LT: return x < y ? 1. : 0.;
+    case OP_GT: return x > y ? 1. : 0.;
+    case OP_LTE: return x <= y ? 1. : 0.;
+    case OP_GTE: return x >= y ? 1. : 0.;
+    case OP_EQ: return x == y ? 1. : 0.;
+    case OP_NE: return x != y ? 1. : 0.;
+  }
+  return NAN;
+}
+static inline double un_f64(int op, double x) {
+  switch (op) {
+    case OP_ABS: return fabs(x);
+    case OP_SIGN: return (double)((x > 0) - (x < 0));
+    case OP_CEIL: return ceil(x);
+    case OP_FLOOR: return floor(x);
+    case OP_SIN: return sin(x);
+    case OP_COS: return cos(x);
+    case OP_EXP: return exp(x);
+    case OP_LN: return log(x);
+    case OP_LOG2: return log2(x);
+    case OP_NEG: return -x;
+    case OP_SQUARE: return x * x;
+    case OP_SQRT: return sqrt(x);
+    case OP_INV: return 1.0 / x;
+    case OP_INVSQRT: return 1.0 / sqrt(x);
+    case OP_CUBE: return x * x * x;
+    case OP_TANH: return tanh(x);
+    case OP_SIGMOID: /* math_nooptim.go:24-33 */
+      if (x < -709) return 0;
+      if (x > 19) return 1;
+      return 1.0 / (1.0 + exp(-x));
+    case OP_LOG1P: return log1p(x);
+    case OP_EXPM1: return expm1(x);
+    case OP_SOFTPLUS: /* operatorPointwise_unary.go softplus lambda; thresholds as the kernels */
+      if (x < -708) return 0;
+      if (x > 16) return x;
+      return log1p(exp(x));
+  }
+  return NAN;
+}
+static inline float un_f32(int op, float x) {
+  switch (op) {
+    case OP_ABS: return fabsf(x);
+    case OP_SIGN: return (float)((x > 0) - (x < 0));
+    case OP_CEIL: return ceilf(x);
+    case OP_FLOOR: return floorf(x);
+    case OP_NEG: return -x;
+    case OP_SQUARE: return x * x;
+    case OP_SQRT: return sqrtf(x);
+    case OP_INV: return 1.0f / x;
+    case OP_INVSQRT: return 1.0f / sqrtf(x);
+    case OP_CUBE: return x * x * x;
+    case OP_SIGMOID: /* math_nooptim.go:36-45 */
+      if (x < -88) return 0;
+      if (x > 15) return 1;
+      return (float)(1.0 / (1.0 + exp((double)(-x))));
+    case OP_SOFTPLUS:
+      if (x < -103) return 0;
+      if (x > 14) return x;
+      return (float)log1p(exp((double)x));
+    default: /* transcendental: evaluate in double, round once */
+      return (float)un_f64(op, (double)x);
+  }
+}
+
+/* dst[i] = a[ai] op b[bi]; stride 0 on an operand makes it a scalar (vs / sv forms of
+ * cuda/arith.go:67-130). dst may alias a or b. */
+void oracle_binary_f32(int op, float *dst, const float *a, const float *b, int64_t n, int a_scalar, int b_scalar) {
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < n; ++i) dst[i] = bin_f32(op, a[a_scalar ? 0 : i], b[b_scalar ? 0 : i]);
+}
+void oracle_binary_f64(int op, double *dst, const double *a, const double *b, int64_t n, int a_scalar,
+                       int b_scalar) {
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < n; ++i) dst[i] = bin_f64(op, a[a_scalar ? 0 : i], b[b_scalar ? 0 : i]);
+}
+void oracle_unary_f32(int op, float *dst, const float *a, int64_t n) {
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < n; ++i) dst[i] = un_f32(op, a[i]);
+}
+void oracle_unary_f64(int op, double *dst, const double *a, int64_t n) {
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < n; ++i) dst[i] = un_f64(op, a[i]);
+}
+
+/* Broadcast binary: gorgonia materialises the small operand with repeatOp and then runs the
+ * plain op (broadcast.go:69-129, op_tensor.go:354-473); element i of the repeated operand is
+ * small[(i / div) % mod]. */
+void oracle_binary_bcast_f32(int op, float *dst, const float *a, const float *b, int64_t n, int64_t div,
+                             int64_t mod, int bcast_is_a) {
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < n; ++i) {
+    int64_t k = (i / div) % mod;
+    dst[i] = bcast_is_a ? bin_f32(op, a[k], b[i]) : bin_f32(op, a[i], b[k]);
+  }
+}
+void oracle_binary_bcast_f64(int op, double *dst, const double *a, const double *b, int64_t n, int64_t div,
+                             int64_t mod, int bcast_is_a) {
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < n; ++i) {
+    int64_t k = (i / div) % mod;
+    dst[i] = bcast_is_a ? bin_f64(op, a[k], b[i]) : bin_f64(op, a[i], b[k]);
+  }
+}
+
+/* ---- linear algebra ---------------------------------------------------------------------
+ * C[M,N] = op(A) op(B), row-major with leading dimensions, alpha=1 beta=0: the result of
+ * linAlgBinOp.do -> tensor.MatMul -> gonum Sgemm (op_math.go:745-795, blas.go:54-56), with
+ * the trans flags of op_math.go:752-768. Products are accumulated in double. */
+void oracle_gemm_f32(int transA, int transB, int64_t M, int64_t N, int64_t K, const float *A, int64_t lda,
+                     const float *B, int64_t ldb, float *C, int64_t ldc) {
+#pragma omp parallel
+  {
+    double *acc = (double *)malloc(sizeof(double) * (size_t)(N > 0 ? N : 1));
+#pragma omp for schedule(static)
+    for (int64_t i = 0; i < M; ++i) {
+      for (int64_t j = 0; j < N; ++j) acc[j] = 0.0;
+      if (!transB) {
+        for (int64_t k = 0; k < K; ++k) {
+          const double a = transA ? A[k * lda + i] : A[i * lda + k];
+          const float *brow = B + k * ldb;
+          for (int64_t j = 0; j < N; ++j) acc[j] += a * (double)brow[j];
+        }
+      } else {
+        for (int64_t j = 0; j < N; ++j) {
+          const float *brow = B + j * ldb;
+          double s = 0.0;
+          if (!transA)
+            for (int64_t k = 0; k < K; ++k) s += (double)A[i * lda + k] * (double)brow[k];
+          else
+            for (int64_t k = 0; k < K; ++k) s += (double)A[k * lda + i] * (double)brow[k];
+          acc[j] = s;
+        }
+      }
+      for (int64_t j = 0; j < N; ++j) C[i * ldc + j] = (float)acc[j];
+    }
+    free(acc);
+  }
+}
+void oracle_gemm_f64(int transA, int transB, int64_t M, int64_t N, int64_t K, const double *A, int64_t lda,
+                     const double *B, int64_t ldb, double *C, int64_t ldc) {
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < M; ++i)
+    for (int64_t j = 0; j < N; ++j) {
+      long double s = 0;
+      for (int64_t k = 0; k < K; ++k) {
+        const double a = transA ? A[k * lda + i] : A[i * lda + k];
+        const double b = transB ? B[j * ldb + k] : B[k * ldb + j];
+        s += (long double)a * b;
+      }
+      C[i * ldc + j] = (double)s;
+    }
+}
+/* The same contraction with float32 products and a float32 running sum in k order: what a
+ * straightforward float32 BLAS does. Used only to show how far summation order alone moves
+ * the result relative to the tolerance. */
+void oracle_gemm_f32_naive(int64_t M, int64_t N, int64_t K, const float *A, const float *B, float *C) {
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < M; ++i)
+    for (int64_t j = 0; j < N; ++j) {
+      float s = 0.f;
+      for (int64_t k = 0; k < K; ++k) s += A[i * K + k] * B[k * N + j];
+      C[i * N + j] = s;
+    }
+}
+
+/* y = A x or A^T x (A is M x N row-major): tensor.MatVecMul -> Sgemv
+ * (cuda/linalg.go:47-107 for the flag handling; operatorLinAlg.go for the op). */
+void oracle_gemv_f32(int transA, int64_t M, int64_t N, const float *A, int64_t lda, const float *x, float *y) {
+  if (!transA) {
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < M; ++i) {
+      double s = 0;
+      for (int64_t j = 0; j < N; ++j) s += (double)A[i * lda + j] * (double)x[j];
+      y[i] = (float)s;
+    }
+  } else {
+#pragma omp parallel for schedule(static)
+    for (int64_t j = 0; j < N; ++j) {
+      double s = 0;
+      for (int64_t i = 0; i < M; ++i) s += (double)A[i * lda + j] * (double)x[i];
+      y[j] = (float)s;
+    }
+  }
+}
+void oracle_gemv_f64(int transA, int64_t M, int64_t N, const double *A, int64_t lda, const double *x,
+                     double *y) {
+  if (!transA) {
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < M; ++i) {
+      long double s = 0;
+      for (int64_t j = 0; j < N; ++j) s += (long double)A[i * lda + j] * x[j];
+      y[i] = (double)s;
+    }
+  } else {
+#pragma omp parallel for schedule(static)
+    for (int64_t j = 0; j < N; ++j) {
+      long double s = 0;
+      for (int64_t i = 0; i < M; ++i) s += (long double)A[i * lda + j] * x[i];
+      y[j] = (double)s;
+    }
+  }
+}
+/* A[M,N] = x y^T, overwriting (tensor.Outer with reuse; cuda/linalg.go:245-265 row-major path). */
+void oracle_outer_f32(int64_t M, int64_t N, const float *x, const float *y, float *A) {
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < M; ++i)
+    for (int64_t j = 0; j < N; ++j) A[i * N + j] = x[i] * y[j];
+}
+void oracle_outer_f64(int64_t M, int64_t N, const double *x, const double *y, double *A) {
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < M; ++i)
+    for (int64_t j = 0; j < N; ++j) A[i * N + j] = x[i] * y[j];
+}
+
+/* ---- nn ops ---------------------------------------------------------------------------- */
+
+/* im2colOp.do / f32s (op_nn.go:317-444): input (B,C,H,W) -> col (B, Ho, Wo, C*kh*kw), inner
+ * order channel, kernel row, kernel col; taps outside the image are 0.
+ * Ho = (H + 2 padH - (dilH (kh-1) + 1)) / strideH + 1 (op_nn.go:311-315). */
+void oracle_im2col_f32(const float *im, float *col, int64_t B, int64_t C, int64_t H, int64_t W, int kh, int kw,
+                       int padH, int padW, int sH, int sW, int dH, int dW) {
+  const int64_t Ho = (H + 2 * padH - (dH * (kh - 1) + 1)) / sH + 1;
+  const int64_t Wo = (W + 2 * padW - (dW * (kw - 1) + 1)) / sW + 1;
+  const int64_t kk = C * kh * kw;
+#pragma omp parallel for schedule(static)
+  for (int64_t b = 0; b < B; ++b) {
+    const float *imb = im + b * C * H * W;
+    float *colb = col + b * Ho * Wo * kk;
+    int64_t idx = 0;
+    for (int64_t oh = 0; oh < Ho; ++oh)
+      for (int64_t ow = 0; ow < Wo; ++ow)
+        for (int64_t c = 0; c < C; ++c)
+          for (int r = 0; r < kh; ++r) {
+            const int64_t ih = -padH + (int64_t)r * dH + oh * sH;
+            for (int s = 0; s < kw; ++s) {
+              const int64_t iw = -padW + (int64_t)s * dW + ow * sW;
+              colb[idx++] = (ih < 0 || ih >= H || iw < 0 || iw >= W) ? 0.f : imb[c * H * W + ih * W + iw];
+            }
+          }
+  }
+}
+
+/* Conv2d (nn.go:211-305): im2col, then (B*Ho*Wo, C*kh*kw) x filter(K, C*kh*kw)^T, then the
+ * (B,Ho,Wo,K) result transposed to (B,K,Ho,Wo). The col buffer is not materialised here; the
+ * sum runs over (c, r, s) in im2col order with a double accumulator. */
+void oracle_conv2d_f32(const float *x, const float *w, float *y, int64_t B, int64_t C, int64_t H, int64_t W,
+                       int64_t K, int kh, int kw, int padH, int padW, int sH, int sW, int dH, int dW) {
+  const int64_t Ho = (H + 2 * padH - (dH * (kh - 1) + 1)) / sH + 1;
+  const int64_t Wo = (W + 2 * padW - (dW * (kw - 1) + 1)) / sW + 1;
+#pragma omp parallel for collapse(2) schedule(static)
+  for (int64_t b = 0; b < B; ++b)
+    for (int64_t k = 0; k < K; ++k) {
+      const float *xb = x + b * C * H * W;
+      const float *wk = w + k * C * kh * kw;
+      float *yk = y + (b * K + k) * Ho * Wo;
+      for (int64_t oh = 0; oh < Ho; ++oh)
+        for (int64_t ow = 0; ow < Wo; ++ow) {
+          double s = 0;
+          for (int64_t c = 0; c < C; ++c)
+            for (int r = 0; r < kh; ++r) {
+              const int64_t ih = -padH + (int64_t)r * dH + oh * sH;
+              if (ih < 0 || ih >= H) continue;
+              for (int q = 0; q < kw; ++q) {
+                const int64_t iw = -padW + (int64_t)q * dW + ow * sW;
+                if (iw < 0 || iw >= W) continue;
+                s += (double)xb[c * H * W + ih * W + iw] * (double)wk[(c * kh + r) * kw + q];
+              }
+            }
+          yk[oh * Wo + ow] = (float)s;
+        }
+    }
+}
+
+/* maxPoolOp.f32s (op_nn.go:858-907): accumulator starts at -MaxFloat32, strict '>' so the
+ * first maximum in row-major window order wins; the window is clipped to the image; with
+ * explicit 4-way padding the window origin uses the south/east pads (op_nn.go:870-875).
+ * Output size (H + padN + padS - kh) / sH + 1 (op_nn.go:810-816). mask holds the winning
+ * index inside the (H,W) plane, or -1. pad = {north, south, west, east}. */
+void oracle_maxpool2d_f32(const float *x, float *y, int64_t *mask, int64_t B, int64_t C, int64_t H, int64_t W,
+                          int kh, int kw, int padN, int padS, int padW_, int padE, int explicit_padding, int sH,
+                          int sW) {
+  const int64_t Ho = (H + padS + padN - (kh - 1) - 1) / sH + 1;
+  const int64_t Wo = (W + padE + padW_ - (kw - 1) - 1) / sW + 1;
+  const int64_t ph0 = explicit_padding ? padS : padN;
+  const int64_t pw0 = explicit_padding ? padE : padW_;
+#pragma omp parallel for schedule(static)
+  for (int64_t bc = 0; bc < B * C; ++bc) {
+    const float *in = x + bc * H * W;
+    float *out = y + bc * Ho * Wo;
+    int64_t *mk = mask ? mask + bc * Ho * Wo : 0;
+    for (int64_t ph = 0; ph < Ho; ++ph)
+      for (int64_t pw = 0; pw < Wo; ++pw) {
+        int64_t hs = ph * sH - ph0, ws = pw * sW - pw0;
+        int64_t he = hs + kh < H ? hs + kh : H, we = ws + kw < W ? ws + kw : W;
+        if (hs < 0) hs = 0;
+        if (ws < 0) ws = 0;
+        float best = -FLT_MAX;
+        int64_t arg = -1;
+        for (int64_t hi = hs; hi < he; ++hi)
+          for (int64_t wi = ws; wi < we; ++wi)
+            if (in[hi * W + wi] > best) {
+              best = in[hi * W + wi];
+              arg = hi * W + wi;
+            }
+        out[ph * Wo + pw] = best;
+        if (mk) mk[ph * Wo + pw] = arg;
+      }
+  }
+}
+
+/* softmaxOp.Do -> tensor.SoftMax / LogSoftMax along `axis` of a tensor viewed as
+ * (outer, len, inner) (op_softmax.go:99-128). exp(x - max) / sum, evaluated in double. */
+void oracle_softmax_f32(const float *x, float *y, int64_t outer, int64_t len, int64_t inner, int is_log) {
+#pragma omp parallel for schedule(static)
+  for (int64_t oi = 0; oi < outer * inner; ++oi) {
+    const int64_t o = oi / inner, in = oi % inner;
+    const float *xp = x + o * len * inner + in;
+    float *yp = y + o * len * inner + in;
+    double mx = -INFINITY;
+    for (int64_t k = 0; k < len; ++k)
+      if ((double)xp[k * inner] > mx) mx = xp[k * inner];
+    double s = 0;
+    for (int64_t k = 0; k < len; ++k) s += exp((double)xp[k * inner] - mx);
+    const double ls = log(s);
+    for (int64_t k = 0; k < len; ++k) {
+      const double d = (double)xp[k * inner] - mx;
+      yp[k * inner] = (float)(is_log ? d - ls : exp(d) / s);
+    }
+  }
+}
+void oracle_softmax_f64(const double *x, double *y, int64_t outer, int64_t len, int64_t inner, int is_log) {
+#pragma omp parallel for schedule(static)
+  for (int64_t oi = 0; oi < outer * inner; ++oi) {
+    const int64_t o = oi / inner, in = oi % inner;
+    const double *xp = x + o * len * inner + in;
+    double *yp = y + o * len * inner + in;
+    double mx = -INFINITY;
+    for (int64_t k = 0; k < len; ++k)
+      if (xp[k * inner] > mx) mx = xp[k * inner];
+    long double s = 0;
+    for (int64_t k = 0; k < len; ++k) s += expl((long double)xp[k * inner] - mx);
+    const long double ls = logl(s);
+    for (int64_t k = 0; k < len; ++k) {
+      const long double d = (long double)xp[k * inner] - mx;
+      yp[k * inner] = (double)(is_log ? d - ls : expl(d) / s);
+    }
+  }
+}
+
+/* reductionDo -> tensor.Sum / tensor.Max along one axis (op_reduction.go:70-99), tensor
+ * viewed as (outer, len, inner); kind 0 = sum, 1 = max. argmax (first maximum) as int64. */
+void oracle_reduce_f32(int kind, const float *x, float *y, int64_t outer, int64_t len, int64_t inner) {
+#pragma omp parallel for schedule(static)
+  for (int64_t oi = 0; oi < outer * inner; ++oi) {
+    const int64_t o = oi / inner, in = oi % inner;
+    const float *xp = x + o * len * inner + in;
+    if (kind == 0) {
+      double s = 0;
+      for (int64_t k = 0; k < len; ++k) s += xp[k * inner];
+      y[oi] = (float)s;
+    } else {
+      float m = xp[0];
+      for (int64_t k = 1; k < len; ++k)
+        if (xp[k * inner] > m) m = xp[k * inner];
+      y[oi] = m;
+    }
+  }
+}
+void oracle_reduce_f64(int kind, const double *x, double *y, int64_t outer, int64_t len, int64_t inner) {
+#pragma omp parallel for schedule(static)
+  for (int64_t oi = 0; oi < outer * inner; ++oi) {
+    const int64_t o = oi / inner, in = oi % inner;
+    const double *xp = x + o * len * inner + in;
+    if (kind == 0) {
+      long double s = 0;
+      for (int64_t k = 0; k < len; ++k) s += xp[k * inner];
+      y[oi] = (double)s;
+    } else {
+      double m = xp[0];
+      for (int64_t k = 1; k < len; ++k)
+        if (xp[k * inner] > m) m = xp[k * inner];
+      y[oi] = m;
+    }
+  }
+}
+void oracle_argmax_f32(const float *x, int64_t *y, int64_t outer, int64_t len, int64_t inner) {
+#pragma omp parallel for schedule(static)
+  for (int64_t oi = 0; oi < outer * inner; ++oi) {
+    const int64_t o = oi / inner, in = oi % inner;
+    const float *xp = x + o * len * inner + in;
+    int64_t arg = 0;
+    float m = xp[0];
+    for (int64_t k = 1; k < len; ++k)
+      if (xp[k * inner] > m) {
+        m = xp[k * inner];
+        arg = k;
+      }
+    y[oi] = arg;
+  }
+}
+
+/* transposeOp.Do -> tensor.Transpose (op_tensor.go:937-952): out dim d is in dim perm[d];
+ * elem is the element size in bytes. */
+void oracle_transpose(const void *x, void *y, int ndim, const int64_t *shape, const int *perm, int elem) {
+  int64_t in_stride[8], out_shape[8], n = 1;
+  int64_t s = 1;
+  for (int d = ndim - 1; d >= 0; --d) {
+    in_stride[d] = s;
+    s *= shape[d];
+  }
+  for (int d = 0; d < ndim; ++d) {
+    out_shape[d] = shape[perm[d]];
+    n *= out_shape[d];
+  }
+  const char *xi = (const char *)x;
+  char *yo = (char *)y;
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < n; ++i) {
+    int64_t rem = i, src = 0;
+    for (int d = ndim - 1; d >= 0; --d) {
+      const int64_t c = rem % out_shape[d];
+      rem /= out_shape[d];
+      src += c * in_stride[perm[d]];
+    }
+    memcpy(yo + i * elem, xi + src * elem, (size_t)elem);
+  }
+}
+
+/* byIndicesOp.Do -> tensor.ByIndices along axis 0 (op_by_indices.go:90-97): out[i,:] = x[idx[i],:]. */
+void oracle_gather_rows(const void *x, const int64_t *idx, void *y, int64_t n_idx, int64_t row_bytes) {
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < n_idx; ++i)
+    memcpy((char *)y + i * row_bytes, (const char *)x + idx[i] * row_bytes, (size_t)row_bytes);
+}
