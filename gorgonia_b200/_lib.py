@@ -32,7 +32,7 @@ OP.update({name: 32 + i for i, name in enumerate(_UN)})
 BINARY_OPS = tuple(_BIN)
 UNARY_OPS = tuple(_UN)
 
-PW_MAX_INSTR, PW_MAX_SRC, PW_MAX_IMM, PW_MAX_OUT = 16, 6, 8, 4
+PW_MAX_INSTR, PW_MAX_SRC, PW_MAX_IMM, PW_MAX_OUT = 8, 6, 8, 4
 
 
 def REF_SRC(k):

@@ -141,6 +141,20 @@ int b200_sync(b200_engine *e) {
   DeviceGuard g(e);
   int rc = flush_pending(e);
   if (rc != B200_OK) return rc;
+  if (e->flags_dirty) {
+    // kernels with bounded waits report a wait that ran out through d_flags[2]
+    B200_CHECK_CUDA(e, cudaMemcpyAsync(e->h_flags + 2, e->d_flags + 2, sizeof(int), cudaMemcpyDeviceToHost,
+                                       e->stream));
+    B200_CHECK_CUDA(e, cudaStreamSynchronize(e->stream));
+    e->flags_dirty = false;
+    if (e->h_flags[2] != 0) {
+      e->h_flags[2] = 0;
+      cudaMemsetAsync(e->d_flags + 2, 0, sizeof(int), e->stream);
+      return set_error(e, B200_ERR_TIMEOUT, "a device-side wait ran out of time; results of the last "
+                       "kernels are incomplete");
+    }
+    return B200_OK;
+  }
   B200_CHECK_CUDA(e, cudaStreamSynchronize(e->stream));
   return B200_OK;
 }

@@ -32,6 +32,7 @@ struct b200_engine {
   // error word bounded waits report through
   int *d_flags = nullptr;   // 16 ints
   int *h_flags = nullptr;   // pinned mirror
+  bool flags_dirty = false; // a kernel that may raise d_flags[2] (bounded wait ran out) was launched
 
   // lazily created resources of other translation units (gemm.cu etc.)
   void *gemm_state = nullptr;

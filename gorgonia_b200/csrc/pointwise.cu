@@ -22,6 +22,7 @@
 #include <cstring>
 
 #include "engine.h"
+#include "ptx.cuh"
 
 namespace b200 {
 
@@ -50,6 +51,8 @@ struct PwDev {
   uint8_t ra[B200_PW_MAX_INSTR];  // operand selectors: [0,NS) sources, [16,24) immediates, [32,48) results
   uint8_t rb[B200_PW_MAX_INSTR];
   uint8_t out_ins[B200_PW_MAX_OUT];
+  uint8_t n_full;                      // number of SRC_FULL sources
+  uint8_t full_slot[B200_PW_MAX_SRC];  // for a SRC_FULL source: its index among the full ones
 };
 
 #define SEL_IMM 16
@@ -209,7 +212,7 @@ struct Step<T, V, NS, NI, NI> {
 };
 
 template <typename T, int V>
-__device__ __forceinline__ void load_chunk(T (&d)[V], const T *p, long long i, int valid) {
+__device__ __forceinline__ void load_chunk(T *d, const T *p, long long i, int valid) {
   if (V > 1 && valid == V) {
     const uint4 raw = *reinterpret_cast<const uint4 *>(p + i);
     memcpy(d, &raw, sizeof(uint4));
@@ -220,7 +223,7 @@ __device__ __forceinline__ void load_chunk(T (&d)[V], const T *p, long long i, i
 }
 
 template <typename T, int V>
-__device__ __forceinline__ void store_chunk(T *p, long long i, const T (&s)[V], int valid) {
+__device__ __forceinline__ void store_chunk(T *p, long long i, const T *s, int valid) {
   if (V > 1 && valid == V) {
     uint4 raw;
     memcpy(&raw, s, sizeof(uint4));
@@ -281,6 +284,162 @@ __global__ void __launch_bounds__(256) pw_kernel(const __grid_constant__ PwDev p
 }
 
 // ------------------------------------------------------------------------------------------
+// The streaming variant for large tensors: full-size sources are staged through shared memory
+// with bulk asynchronous copies (TMA engine, no tensor map) in a multi-stage ring.
+//
+// A pointwise kernel is bound by HBM, and what limits a plain load/compute/store loop is how
+// many bytes its threads can keep in flight: every outstanding 16-byte load pins registers.
+// Here ONE thread per CTA queues whole tiles (16 KB per source) several stages ahead, so a CTA
+// keeps up to ~190 KB in flight per SM regardless of how many registers the interpreter needs.
+// One persistent CTA of 512 threads per SM walks the tiles; results go straight from
+// registers to global memory with 16-byte stores.
+// ------------------------------------------------------------------------------------------
+constexpr int PW_STREAM_THREADS = 512;
+constexpr int PW_MAX_STAGES = 16;
+
+template <typename T, int V, int NS, int NI, int U>
+__global__ void __launch_bounds__(PW_STREAM_THREADS, 1)
+    pw_stream_kernel(const __grid_constant__ PwDev p, int stages, int *err_flag) {
+  constexpr int W = U * V;
+  constexpr int TILE_CHUNKS = PW_STREAM_THREADS * U;
+  constexpr int TILE_BYTES = TILE_CHUNKS * 16;
+  extern __shared__ __align__(128) unsigned char pw_smem[];
+  __shared__ __align__(8) uint64_t full_bar[PW_MAX_STAGES];
+  __shared__ int s_fail;
+
+  const int tid = threadIdx.x;
+  const long long n = p.n;
+  const long long nchunks_full = n / V;  // chunks that lie entirely inside the tensor
+  const long long nchunks = (n + V - 1) / V;
+  const long long ntiles = (nchunks + TILE_CHUNKS - 1) / TILE_CHUNKS;
+  const long long my_count = blockIdx.x < ntiles ? (ntiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+  const int nfull = p.n_full;
+
+  if (tid == 0) {
+    for (int s = 0; s < stages; ++s) ptx::mbar_init(&full_bar[s], 1);
+    ptx::fence_mbar_init();
+    s_fail = 0;
+  }
+  __syncthreads();
+
+  // thread 0: queue the copies of this CTA's k-th tile into ring slot k % stages
+  auto issue = [&](long long k) {
+    const long long t = blockIdx.x + k * (long long)gridDim.x;
+    const int stage = (int)(k % stages);
+    const long long c_begin = t * TILE_CHUNKS;
+    long long nfc = nchunks_full - c_begin;
+    nfc = nfc < 0 ? 0 : (nfc > TILE_CHUNKS ? TILE_CHUNKS : nfc);
+    const uint32_t bytes = (uint32_t)nfc * 16u;
+    ptx::mbar_arrive_expect_tx(&full_bar[stage], bytes * (uint32_t)nfull);
+    if (bytes) {
+#pragma unroll
+      for (int s = 0; s < NS; ++s)
+        if (s < p.n_src && p.src_mode[s] == SRC_FULL)
+          ptx::bulk_g2s(pw_smem + ((size_t)stage * nfull + p.full_slot[s]) * TILE_BYTES,
+                        reinterpret_cast<const unsigned char *>(p.src[s]) + c_begin * 16, bytes,
+                        &full_bar[stage]);
+    }
+  };
+  if (tid == 0) {
+    const long long pre = my_count < stages ? my_count : stages;
+    for (long long k = 0; k < pre; ++k) issue(k);
+  }
+
+  long long k = 0;
+  for (; k < my_count; ++k) {
+    const long long t = blockIdx.x + k * (long long)gridDim.x;
+    const int stage = (int)(k % stages);
+    const uint32_t parity = (uint32_t)((k / stages) & 1);
+    const long long c_tile = t * TILE_CHUNKS;
+    if (!ptx::mbar_wait(&full_bar[stage], parity)) s_fail = 1;
+
+    T S[NS][W];
+    T R[NI][W];
+    int valid[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long left = n - (c_tile + u * PW_STREAM_THREADS + tid) * V;
+      valid[u] = left >= V ? V : (left > 0 ? (int)left : 0);
+    }
+#pragma unroll
+    for (int s = 0; s < NS; ++s) {
+      if (s < p.n_src) {
+        const T *sp = reinterpret_cast<const T *>(p.src[s]);
+        const int mode = p.src_mode[s];
+        if (mode == SRC_FULL) {
+          const unsigned char *buf = pw_smem + ((size_t)stage * nfull + p.full_slot[s]) * TILE_BYTES;
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            const int cl = u * PW_STREAM_THREADS + tid;
+            if (valid[u] == V) {
+              const uint4 raw = *reinterpret_cast<const uint4 *>(buf + (size_t)cl * 16);
+              memcpy(&S[s][u * V], &raw, sizeof(uint4));
+            } else {
+              // the ragged last chunk of the tensor is not part of the bulk copy
+#pragma unroll
+              for (int j = 0; j < V; ++j) S[s][u * V + j] = j < valid[u] ? sp[(c_tile + cl) * V + j] : T(0);
+            }
+          }
+        } else if (mode == SRC_ROWVEC) {
+#pragma unroll
+          for (int u = 0; u < U; ++u)
+            load_chunk<T, V>(&S[s][u * V], sp, ((c_tile + u * PW_STREAM_THREADS + tid) * V) % p.src_mod[s],
+                             valid[u] > 0 ? V : 0);
+        } else if (mode == SRC_SCALAR) {
+          const T v = sp[0];
+#pragma unroll
+          for (int j = 0; j < W; ++j) S[s][j] = v;
+        } else if (mode == SRC_CHUNK) {
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            const T v = valid[u] > 0
+                            ? sp[(((c_tile + u * PW_STREAM_THREADS + tid) * V) / p.src_div[s]) % p.src_mod[s]]
+                            : T(0);
+#pragma unroll
+            for (int j = 0; j < V; ++j) S[s][u * V + j] = v;
+          }
+        } else {
+#pragma unroll
+          for (int u = 0; u < U; ++u)
+#pragma unroll
+            for (int j = 0; j < V; ++j)
+              S[s][u * V + j] =
+                  j < valid[u]
+                      ? sp[(((c_tile + u * PW_STREAM_THREADS + tid) * V + j) / p.src_div[s]) % p.src_mod[s]]
+                      : T(0);
+        }
+      }
+    }
+    __syncthreads();  // every thread has taken its chunks out of this ring slot
+    if (s_fail) break;  // uniform: s_fail was written before the barrier
+    if (tid == 0 && k + stages < my_count) issue(k + stages);
+
+    Step<T, W, NS, NI, 0>::run(p, S, R);
+#pragma unroll
+    for (int o = 0; o < B200_PW_MAX_OUT; ++o) {
+      if (o < p.n_out) {
+        T v[W];
+        fetch<T, W, NS, NI, NI>(v, SEL_INS + p.out_ins[o], S, R, p);
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+          store_chunk<T, V>(reinterpret_cast<T *>(p.out[o]), (c_tile + u * PW_STREAM_THREADS + tid) * V,
+                            &v[u * V], valid[u]);
+      }
+    }
+  }
+  if (k < my_count) {
+    // A wait ran out. Report it, then give copies that are still queued a last bounded chance to
+    // land before this CTA's shared memory goes away.
+    if (tid == 0) {
+      atomicExch(err_flag, 1);
+      const long long last = (k + stages < my_count ? k + stages : my_count);
+      for (long long q = k; q < last; ++q)
+        ptx::mbar_wait(&full_bar[q % stages], (uint32_t)((q / stages) & 1), 100000000ull);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------
 // host side: program checking, lowering, launch
 // ------------------------------------------------------------------------------------------
 
@@ -306,9 +465,47 @@ static int lower_ref(b200_engine *e, const b200_pw_prog *prog, uint8_t ref, int 
   return B200_OK;
 }
 
+template <typename T, int V, int NS, int NI, int U>
+static int launch_stream(b200_engine *e, const PwDev &d) {
+  constexpr int TILE_CHUNKS = PW_STREAM_THREADS * U;
+  constexpr int TILE_BYTES = TILE_CHUNKS * 16;
+  const long long nchunks = (d.n + V - 1) / V;
+  const long long ntiles = (nchunks + TILE_CHUNKS - 1) / TILE_CHUNKS;
+  const size_t budget = std::min<size_t>(e->smem_optin > 8192 ? e->smem_optin - 8192 : 0, 200 * 1024);
+  int stages = (int)(budget / ((size_t)d.n_full * TILE_BYTES));
+  stages = std::min(stages, PW_MAX_STAGES);
+  if (stages < 2) return -1;  // not enough shared memory for a ring: caller uses the plain kernel
+  const size_t smem = (size_t)stages * d.n_full * TILE_BYTES;
+  auto kern = pw_stream_kernel<T, V, NS, NI, U>;
+  static bool attr_set = false;  // per instantiation
+  static size_t attr_val = 0;
+  if (!attr_set || attr_val < smem) {
+    B200_CHECK_CUDA(e, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)budget));
+    attr_set = true;
+    attr_val = budget;
+  }
+  const int blocks = (int)std::min<long long>(ntiles, e->sm_count);
+  kern<<<blocks, PW_STREAM_THREADS, smem, e->stream>>>(d, stages, e->d_flags + 2);
+  B200_CHECK_LAUNCH(e, "pw_stream_kernel");
+  e->flags_dirty = true;
+  return B200_OK;
+}
+
 template <typename T, int V>
 static int launch_sized(b200_engine *e, const PwDev &d, int ns, int ni) {
   const long long nchunks = (d.n + V - 1) / V;
+  // Large, 16-byte aligned tensors take the streaming kernel. Below ~2 tiles per SM the ring
+  // never fills and the plain kernel, with its many small blocks, spreads the work better.
+  if (V > 1 && d.n_full >= 1 && nchunks >= (long long)e->sm_count * PW_STREAM_THREADS * 2 * 2) {
+    int rc;
+    if (ns <= 2 && ni <= 2)
+      rc = launch_stream<T, V, 2, 2, 2>(e, d);
+    else if (ns <= 3 && ni <= 4)
+      rc = launch_stream<T, V, 3, 4, 1>(e, d);
+    else
+      rc = launch_stream<T, V, B200_PW_MAX_SRC, B200_PW_MAX_INSTR, 1>(e, d);
+    if (rc >= 0) return rc;
+  }
   const int threads = 256;
   long long want = (nchunks + threads - 1) / threads;
   long long cap = (long long)e->sm_count * 8;
@@ -317,8 +514,6 @@ static int launch_sized(b200_engine *e, const PwDev &d, int ns, int ni) {
     pw_kernel<T, V, 2, 2><<<blocks, threads, 0, e->stream>>>(d);
   else if (ns <= 3 && ni <= 4)
     pw_kernel<T, V, 3, 4><<<blocks, threads, 0, e->stream>>>(d);
-  else if (ns <= 4 && ni <= 8)
-    pw_kernel<T, V, 4, 8><<<blocks, threads, 0, e->stream>>>(d);
   else
     pw_kernel<T, V, B200_PW_MAX_SRC, B200_PW_MAX_INSTR><<<blocks, threads, 0, e->stream>>>(d);
   B200_CHECK_LAUNCH(e, "pw_kernel");
@@ -353,6 +548,7 @@ static int run_program(b200_engine *e, int dtype, const b200_pw_prog *prog, void
     const int64_t div = prog->src_div[s], mod = prog->src_mod[s];
     if (div == 0) {
       d.src_mode[s] = SRC_FULL;
+      d.full_slot[s] = d.n_full++;
       if ((uintptr_t)srcs[s] % 16) aligned = false;
     } else {
       B200_REQUIRE(e, div > 0 && mod > 0, "pointwise: source %u has div %lld mod %lld", s, (long long)div,
@@ -641,9 +837,8 @@ void finish(Builder &b, int end, const int *released_at, FusedKernel *fk) {
 
 }  // namespace
 
-// The fused kernels never exceed this many instructions: it is the largest program that the
-// <4 sources, 8 instructions> instantiation holds entirely in registers.
-static const int kMaxFusedInstr = 8;
+// The fused kernels never exceed the program capacity of the largest kernel instantiation.
+static const int kMaxFusedInstr = B200_PW_MAX_INSTR;
 
 static void plan(const b200_pw_call *calls, int n_calls, const int *released_at,
                  std::vector<FusedKernel> *out) {

@@ -151,7 +151,7 @@ int b200_binary_bcast(b200_engine *e, int op, int dtype, void *dst, const void *
                       int64_t n, int64_t b_div, int64_t b_mod, int bcast_is_a);
 
 /* A fused chain of pointwise instructions evaluated in one pass over memory. */
-#define B200_PW_MAX_INSTR 16
+#define B200_PW_MAX_INSTR 8
 #define B200_PW_MAX_SRC 6
 #define B200_PW_MAX_IMM 8
 #define B200_PW_MAX_OUT 4

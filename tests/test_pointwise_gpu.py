@@ -39,7 +39,7 @@ def _operands(op, seed, n, dt):
 @pytest.mark.parametrize("op", util.ARITH_OPS + util.CMP_OPS)
 def test_binary_vv_reuse_and_unsafe(fresh, op, dt):
     e = fresh
-    for n in util.EDGE_SIZES + (1 << 20,):
+    for n in util.EDGE_SIZES + (1 << 20, util.STREAM_SIZE):
         a, b = _operands(op, 11 + n, n, dt)
         want = oracle.binary(op, a, b)
         ta, tb, tr = e.tensor(a), e.tensor(b), e.empty(n, dt)
@@ -58,7 +58,7 @@ def test_binary_vv_reuse_and_unsafe(fresh, op, dt):
 @pytest.mark.parametrize("op", util.ARITH_OPS + util.CMP_OPS)
 def test_binary_scalar_forms(fresh, op, dt):
     e = fresh
-    for n in (1, 5, 1025, 65536 + 3):
+    for n in (1, 5, 1025, 65536 + 3, util.STREAM_SIZE):
         a, _ = _operands(op, 7 + n, n, dt)
         s = dt(0.75)
         ta, tr = e.tensor(a), e.empty(n, dt)
@@ -92,7 +92,7 @@ def test_scalar_scalar(fresh):
 @pytest.mark.parametrize("op", util.UNARY_OPS)
 def test_unary(fresh, op, dt):
     e = fresh
-    for n in util.EDGE_SIZES + (1 << 20,):
+    for n in util.EDGE_SIZES + (1 << 20, util.STREAM_SIZE):
         x = util.unary_input(op, 3 + n, n, dt)
         if op in ("sigmoid", "softplus") and n >= 1023:
             x[:8] = np.array([-200, -104, -103, -89, -88, 14.5, 15.5, 30], dtype=dt)  # threshold branches
@@ -161,6 +161,14 @@ def test_broadcast_forms(fresh, dt):
     assert_bits_equal(tr2.numpy(), a2 * row2[None, :])
     e.BroadcastBinary("div", t2, e.tensor(col2), C2, R2, reuse=tr2)
     assert_bits_equal(tr2.numpy(), a2 / col2[:, None])
+    # large enough for the streaming kernel: row operand (vector loads) and column operand
+    R3, C3 = 4099, 1024
+    a3, row3, col3 = util.normal(13, (R3, C3), dt), util.normal(14, C3, dt), util.normal(15, R3, dt)
+    t3, tr3 = e.tensor(a3), e.empty((R3, C3), dt)
+    e.BroadcastBinary("add", t3, e.tensor(row3), 1, C3, reuse=tr3)
+    assert_bits_equal(tr3.numpy(), a3 + row3[None, :])
+    e.BroadcastBinary("mul", e.tensor(col3), t3, C3, R3, bcast_is_a=True, reuse=tr3)
+    assert_bits_equal(tr3.numpy(), col3[:, None] * a3)
     # per-channel operand over (B, C, H, W)
     x = util.normal(11, (3, 5, 4, 4), dt)
     ch = util.normal(12, 5, dt)
@@ -170,9 +178,9 @@ def test_broadcast_forms(fresh, dt):
     assert_bits_equal(oracle.binary_bcast("add", x, ch, 16, 5), x + ch[None, :, None, None])
 
 
-def test_deferred_chain_fuses_into_one_launch(fresh):
+@pytest.mark.parametrize("n", [1 << 20, util.STREAM_SIZE, (1 << 23) + 3])
+def test_deferred_chain_fuses_into_one_launch(fresh, n):
     e = fresh
-    n = 1 << 20
     x, w, b = util.normal(1, n), util.normal(2, n), util.normal(3, n)
     tx, tw, tb = e.tensor(x), e.tensor(w), e.tensor(b)
     e.Signal()
@@ -202,7 +210,7 @@ def test_deferred_chain_fuses_into_one_launch(fresh):
 def test_released_intermediates_and_leaky_relu(fresh):
     # LeakyRelu exactly as gorgonia's graph spells it (nn.go:104-130), temporaries released
     e = fresh
-    n = 300_003
+    n = 3_000_003
     x = util.normal(21, n)
     tx = e.tensor(x)
     e.Signal()

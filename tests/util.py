@@ -15,6 +15,9 @@ UNARY_OPS = ("abs", "sign", "ceil", "floor", "sin", "cos", "exp", "ln", "log2", 
              "inv", "invsqrt", "cube", "tanh", "sigmoid", "log1p", "expm1", "softplus")
 POSITIVE_DOMAIN = ("ln", "log2", "sqrt", "invsqrt", "log1p")
 EDGE_SIZES = (1, 3, 4, 5, 31, 1023, 1024, 1025, 4099)
+# above the size where the engine switches to its shared-memory-staged streaming kernel; not a
+# multiple of the vector width, so the ragged tail is exercised too
+STREAM_SIZE = (1 << 21) + 5
 
 
 def rng(seed):
@@ -41,7 +44,12 @@ def assert_bits_equal(g, r):
     r = np.ascontiguousarray(r)
     assert g.shape == r.shape and g.dtype == r.dtype
     u = {4: np.uint32, 8: np.uint64, 2: np.uint16}[g.dtype.itemsize]
-    bad = np.nonzero(g.view(u) != r.view(u))
+    differ = g.view(u) != r.view(u)
+    if g.dtype.kind == "f":
+        # NaN has many encodings and IEEE 754 does not say which one an operation returns:
+        # x86 and the GPU differ in sign and payload. Any NaN matches any NaN.
+        differ &= ~(np.isnan(g) & np.isnan(r))
+    bad = np.nonzero(differ)
     assert bad[0].size == 0, f"{bad[0].size} elements differ, first at {tuple(b[0] for b in bad)}"
 
 
