@@ -51,8 +51,21 @@ struct PwDev {
   uint8_t ra[B200_PW_MAX_INSTR];  // operand selectors: [0,NS) sources, [16,24) immediates, [32,48) results
   uint8_t rb[B200_PW_MAX_INSTR];
   uint8_t out_ins[B200_PW_MAX_OUT];
-  uint8_t n_full;                      // number of SRC_FULL sources
-  uint8_t full_slot[B200_PW_MAX_SRC];  // for a SRC_FULL source: its index among the full ones
+  // ---- streaming kernel only: operands addressed in shared memory
+  uint8_t n_full;                      // number of SRC_FULL sources (they travel through the ring)
+  uint8_t n_file;                      // number of per-thread slots outside the ring
+  uint8_t src_slot[B200_PW_MAX_SRC];   // SRC_FULL: index inside a ring stage; otherwise: file slot
+  uint8_t ka[B200_PW_MAX_INSTR], xa[B200_PW_MAX_INSTR];  // operand kind (OperandKind) and index
+  uint8_t kb[B200_PW_MAX_INSTR], xb[B200_PW_MAX_INSTR];
+  uint8_t keep_slot[B200_PW_MAX_INSTR];  // file slot that keeps the result for later, or 0xFF
+  uint8_t out_of[B200_PW_MAX_INSTR];     // output index this instruction's result is stored to, or 0xFF
+};
+
+enum OperandKind : uint8_t {
+  K_ACC = 0,   // the result of the previous instruction, still in registers
+  K_IMM = 1,   // immediate xa
+  K_RING = 2,  // full-size source: slot xa of the current ring stage
+  K_FILE = 3   // file slot xa: a broadcast source or a kept result
 };
 
 #define SEL_IMM 16
@@ -284,36 +297,197 @@ __global__ void __launch_bounds__(256) pw_kernel(const __grid_constant__ PwDev p
 }
 
 // ------------------------------------------------------------------------------------------
-// The streaming variant for large tensors: full-size sources are staged through shared memory
-// with bulk asynchronous copies (TMA engine, no tensor map) in a multi-stage ring.
+// The streaming kernel for large tensors.
 //
-// A pointwise kernel is bound by HBM, and what limits a plain load/compute/store loop is how
-// many bytes its threads can keep in flight: every outstanding 16-byte load pins registers.
-// Here ONE thread per CTA queues whole tiles (16 KB per source) several stages ahead, so a CTA
-// keeps up to ~190 KB in flight per SM regardless of how many registers the interpreter needs.
-// One persistent CTA of 512 threads per SM walks the tiles; results go straight from
-// registers to global memory with 16-byte stores.
+// A pointwise kernel is bound by HBM, and two things keep a plain load/compute/store loop off
+// that bound: every outstanding 16-byte load pins registers of a thread, so bytes in flight are
+// tied to occupancy; and a register-resident interpreter pays for operand selection with long
+// chains of predicated moves. This kernel removes both:
+//   - full-size sources are staged through shared memory with bulk asynchronous copies (the TMA
+//     engine, no tensor map) in a multi-stage ring. ONE thread per CTA queues whole tiles
+//     (16 bytes x U x 512 threads per source) several stages ahead, so bytes in flight are set
+//     by the ring depth, not by registers;
+//   - operands are addressed, not selected: an operand is the previous result (registers), an
+//     immediate, a ring slot or a per-thread "file" slot in shared memory (broadcast sources
+//     and results needed again later). Fetching one is a uniform branch and a 16-byte shared
+//     load, whatever the program length, so the instruction loop is a plain run-time loop.
+// One persistent CTA of 512 threads per SM walks the tiles; results go straight from registers
+// to global memory with 16-byte stores.
 // ------------------------------------------------------------------------------------------
 constexpr int PW_STREAM_THREADS = 512;
-constexpr int PW_MAX_STAGES = 16;
+constexpr int PW_MAX_STAGES = 12;
 
-template <typename T, int V, int NS, int NI, int U>
-__global__ void __launch_bounds__(PW_STREAM_THREADS, 1)
-    pw_stream_kernel(const __grid_constant__ PwDev p, int stages, int *err_flag) {
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ void sts128(uint32_t addr, const uint4 &v) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
+
+// One tile of the streaming kernel. INSIDE = the whole tile lies inside the tensor and is made
+// of complete 16-byte chunks, which is every tile but possibly the last one: no bounds logic.
+// ring_s / file_s: shared-memory addresses of this stage's ring slots and of the file slots,
+// already offset by this thread's lane (tid * 16).
+template <typename T, int V, int U, bool INSIDE>
+__device__ __forceinline__ void pw_tile(const PwDev &p, uint32_t ring_s, uint32_t file_s, long long c_tile,
+                                        int tid) {
   constexpr int W = U * V;
+  constexpr uint32_t SLOT_BYTES = PW_STREAM_THREADS * U * 16;
+  constexpr uint32_t USTRIDE = PW_STREAM_THREADS * 16;  // bytes between a thread's consecutive chunks
+  int valid[U];
+#pragma unroll
+  for (int u = 0; u < U; ++u) {
+    if (INSIDE) {
+      valid[u] = V;
+    } else {
+      const long long left = p.n - (c_tile + u * PW_STREAM_THREADS + tid) * V;
+      valid[u] = left >= V ? V : (left > 0 ? (int)left : 0);
+    }
+  }
+  // sources that are not full-size: fetch this thread's elements into its file slot
+  if (p.n_file) {
+    for (int s = 0; s < p.n_src; ++s) {
+      const int mode = p.src_mode[s];
+      if (mode == SRC_FULL) continue;
+      const T *sp = reinterpret_cast<const T *>(p.src[s]);
+      const uint32_t slot = file_s + p.src_slot[s] * SLOT_BYTES;
+      if (mode == SRC_ROWVEC) {
+        // the row offset of the tile start, once; the rest is 32-bit arithmetic
+        const uint32_t mod = (uint32_t)p.src_mod[s];
+        const uint32_t base = (uint32_t)((c_tile * V) % p.src_mod[s]);
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const uint32_t off = (base + (uint32_t)(u * PW_STREAM_THREADS + tid) * V) % mod;
+          uint4 raw = make_uint4(0, 0, 0, 0);
+          if (valid[u] > 0) raw = *reinterpret_cast<const uint4 *>(sp + off);
+          sts128(slot + u * USTRIDE, raw);
+        }
+      } else {
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const long long i = (c_tile + u * PW_STREAM_THREADS + tid) * V;
+          T v[V];
+          if (mode == SRC_SCALAR) {
+            const T x = sp[0];
+#pragma unroll
+            for (int j = 0; j < V; ++j) v[j] = x;
+          } else if (mode == SRC_CHUNK) {
+            const T x = valid[u] > 0 ? sp[(i / p.src_div[s]) % p.src_mod[s]] : T(0);
+#pragma unroll
+            for (int j = 0; j < V; ++j) v[j] = x;
+          } else {
+#pragma unroll
+            for (int j = 0; j < V; ++j)
+              v[j] = j < valid[u] ? sp[((i + j) / p.src_div[s]) % p.src_mod[s]] : T(0);
+          }
+          uint4 raw;
+          memcpy(&raw, v, sizeof raw);
+          sts128(slot + u * USTRIDE, raw);
+        }
+      }
+    }
+  }
+  if (!INSIDE) {
+    // the ragged last chunk of the tensor is not part of the bulk copy: its owner patches it in
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (valid[u] > 0 && valid[u] < V) {
+        for (int s = 0; s < p.n_src; ++s)
+          if (p.src_mode[s] == SRC_FULL) {
+            const T *sp = reinterpret_cast<const T *>(p.src[s]);
+            T v[V];
+#pragma unroll
+            for (int j = 0; j < V; ++j)
+              v[j] = j < valid[u] ? sp[(c_tile + u * PW_STREAM_THREADS + tid) * V + j] : T(0);
+            uint4 raw;
+            memcpy(&raw, v, sizeof raw);
+            sts128(ring_s + p.src_slot[s] * SLOT_BYTES + u * USTRIDE, raw);
+          }
+      }
+    }
+  }
+
+  T acc[W];
+#pragma unroll
+  for (int j = 0; j < W; ++j) acc[j] = T(0);
+  const int n_instr = p.n_instr;
+#pragma unroll 1
+  for (int q = 0; q < n_instr; ++q) {
+    T a[W], b[W];
+    auto fetch_op = [&](T(&d)[W], int kind, int idx) {
+      if (kind >= K_RING) {
+        const uint32_t base = (kind == K_RING ? ring_s : file_s) + (uint32_t)idx * SLOT_BYTES;
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const uint4 raw = lds128(base + u * USTRIDE);
+          memcpy(&d[u * V], &raw, sizeof raw);
+        }
+      } else if (kind == K_ACC) {
+#pragma unroll
+        for (int j = 0; j < W; ++j) d[j] = acc[j];
+      } else {
+        const T x = (T)p.imm[idx];
+#pragma unroll
+        for (int j = 0; j < W; ++j) d[j] = x;
+      }
+    };
+    const int op = p.op[q];
+    fetch_op(a, p.ka[q], p.xa[q]);
+    if (op < B200_OP_ABS) {
+      fetch_op(b, p.kb[q], p.xb[q]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < W; ++j) b[j] = a[j];
+    }
+    pw_apply<T, W>(op, a, b, acc);
+    const int keep = p.keep_slot[q];
+    if (keep != 0xFF) {
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        uint4 raw;
+        memcpy(&raw, &acc[u * V], sizeof raw);
+        sts128(file_s + (uint32_t)keep * SLOT_BYTES + u * USTRIDE, raw);
+      }
+    }
+    const int o = p.out_of[q];
+    if (o != 0xFF) {
+      unsigned char *op_ = reinterpret_cast<unsigned char *>(p.out[o]) + (c_tile + tid) * 16;
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (INSIDE) {
+          uint4 raw;
+          memcpy(&raw, &acc[u * V], sizeof raw);
+          *reinterpret_cast<uint4 *>(op_ + (size_t)u * USTRIDE) = raw;
+        } else {
+          store_chunk<T, V>(reinterpret_cast<T *>(p.out[o]), (c_tile + u * PW_STREAM_THREADS + tid) * V,
+                            &acc[u * V], valid[u]);
+        }
+      }
+    }
+  }
+}
+
+template <typename T, int V, int U>
+__global__ void __launch_bounds__(PW_STREAM_THREADS, 2)
+    pw_stream_kernel(const __grid_constant__ PwDev p, int stages, int *err_flag) {
   constexpr int TILE_CHUNKS = PW_STREAM_THREADS * U;
-  constexpr int TILE_BYTES = TILE_CHUNKS * 16;
+  constexpr int SLOT_BYTES = TILE_CHUNKS * 16;
   extern __shared__ __align__(128) unsigned char pw_smem[];
   __shared__ __align__(8) uint64_t full_bar[PW_MAX_STAGES];
   __shared__ int s_fail;
 
   const int tid = threadIdx.x;
-  const long long n = p.n;
-  const long long nchunks_full = n / V;  // chunks that lie entirely inside the tensor
-  const long long nchunks = (n + V - 1) / V;
+  const long long nchunks_full = p.n / V;  // chunks that lie entirely inside the tensor
+  const long long nchunks = (p.n + V - 1) / V;
   const long long ntiles = (nchunks + TILE_CHUNKS - 1) / TILE_CHUNKS;
   const long long my_count = blockIdx.x < ntiles ? (ntiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
   const int nfull = p.n_full;
+  const uint32_t stage_bytes = (uint32_t)nfull * SLOT_BYTES;
+  const uint32_t smem_s = ptx::smem_addr(pw_smem);
+  const uint32_t file_s = smem_s + (uint32_t)stages * stage_bytes + (uint32_t)tid * 16;
 
   if (tid == 0) {
     for (int s = 0; s < stages; ++s) ptx::mbar_init(&full_bar[s], 1);
@@ -322,109 +496,43 @@ __global__ void __launch_bounds__(PW_STREAM_THREADS, 1)
   }
   __syncthreads();
 
-  // thread 0: queue the copies of this CTA's k-th tile into ring slot k % stages
-  auto issue = [&](long long k) {
-    const long long t = blockIdx.x + k * (long long)gridDim.x;
-    const int stage = (int)(k % stages);
-    const long long c_begin = t * TILE_CHUNKS;
+  // thread 0: queue the copies of this CTA's k-th tile into ring stage `stage`
+  auto issue = [&](long long k, int stage) {
+    const long long c_begin = (blockIdx.x + k * (long long)gridDim.x) * TILE_CHUNKS;
     long long nfc = nchunks_full - c_begin;
     nfc = nfc < 0 ? 0 : (nfc > TILE_CHUNKS ? TILE_CHUNKS : nfc);
     const uint32_t bytes = (uint32_t)nfc * 16u;
     ptx::mbar_arrive_expect_tx(&full_bar[stage], bytes * (uint32_t)nfull);
     if (bytes) {
-#pragma unroll
-      for (int s = 0; s < NS; ++s)
-        if (s < p.n_src && p.src_mode[s] == SRC_FULL)
-          ptx::bulk_g2s(pw_smem + ((size_t)stage * nfull + p.full_slot[s]) * TILE_BYTES,
+      for (int s = 0; s < p.n_src; ++s)
+        if (p.src_mode[s] == SRC_FULL)
+          ptx::bulk_g2s(pw_smem + (size_t)stage * stage_bytes + (size_t)p.src_slot[s] * SLOT_BYTES,
                         reinterpret_cast<const unsigned char *>(p.src[s]) + c_begin * 16, bytes,
                         &full_bar[stage]);
     }
   };
   if (tid == 0) {
     const long long pre = my_count < stages ? my_count : stages;
-    for (long long k = 0; k < pre; ++k) issue(k);
+    for (long long k = 0; k < pre; ++k) issue(k, (int)k);
   }
 
   long long k = 0;
+  int stage = 0;
+  uint32_t parity = 0;
   for (; k < my_count; ++k) {
-    const long long t = blockIdx.x + k * (long long)gridDim.x;
-    const int stage = (int)(k % stages);
-    const uint32_t parity = (uint32_t)((k / stages) & 1);
-    const long long c_tile = t * TILE_CHUNKS;
+    const long long c_tile = (blockIdx.x + k * (long long)gridDim.x) * TILE_CHUNKS;
+    const uint32_t ring_s = smem_s + (uint32_t)stage * stage_bytes + (uint32_t)tid * 16;
     if (!ptx::mbar_wait(&full_bar[stage], parity)) s_fail = 1;
-
-    T S[NS][W];
-    T R[NI][W];
-    int valid[U];
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const long long left = n - (c_tile + u * PW_STREAM_THREADS + tid) * V;
-      valid[u] = left >= V ? V : (left > 0 ? (int)left : 0);
-    }
-#pragma unroll
-    for (int s = 0; s < NS; ++s) {
-      if (s < p.n_src) {
-        const T *sp = reinterpret_cast<const T *>(p.src[s]);
-        const int mode = p.src_mode[s];
-        if (mode == SRC_FULL) {
-          const unsigned char *buf = pw_smem + ((size_t)stage * nfull + p.full_slot[s]) * TILE_BYTES;
-#pragma unroll
-          for (int u = 0; u < U; ++u) {
-            const int cl = u * PW_STREAM_THREADS + tid;
-            if (valid[u] == V) {
-              const uint4 raw = *reinterpret_cast<const uint4 *>(buf + (size_t)cl * 16);
-              memcpy(&S[s][u * V], &raw, sizeof(uint4));
-            } else {
-              // the ragged last chunk of the tensor is not part of the bulk copy
-#pragma unroll
-              for (int j = 0; j < V; ++j) S[s][u * V + j] = j < valid[u] ? sp[(c_tile + cl) * V + j] : T(0);
-            }
-          }
-        } else if (mode == SRC_ROWVEC) {
-#pragma unroll
-          for (int u = 0; u < U; ++u)
-            load_chunk<T, V>(&S[s][u * V], sp, ((c_tile + u * PW_STREAM_THREADS + tid) * V) % p.src_mod[s],
-                             valid[u] > 0 ? V : 0);
-        } else if (mode == SRC_SCALAR) {
-          const T v = sp[0];
-#pragma unroll
-          for (int j = 0; j < W; ++j) S[s][j] = v;
-        } else if (mode == SRC_CHUNK) {
-#pragma unroll
-          for (int u = 0; u < U; ++u) {
-            const T v = valid[u] > 0
-                            ? sp[(((c_tile + u * PW_STREAM_THREADS + tid) * V) / p.src_div[s]) % p.src_mod[s]]
-                            : T(0);
-#pragma unroll
-            for (int j = 0; j < V; ++j) S[s][u * V + j] = v;
-          }
-        } else {
-#pragma unroll
-          for (int u = 0; u < U; ++u)
-#pragma unroll
-            for (int j = 0; j < V; ++j)
-              S[s][u * V + j] =
-                  j < valid[u]
-                      ? sp[(((c_tile + u * PW_STREAM_THREADS + tid) * V + j) / p.src_div[s]) % p.src_mod[s]]
-                      : T(0);
-        }
-      }
-    }
-    __syncthreads();  // every thread has taken its chunks out of this ring slot
+    if (c_tile + TILE_CHUNKS <= nchunks_full)
+      pw_tile<T, V, U, true>(p, ring_s, file_s, c_tile, tid);
+    else
+      pw_tile<T, V, U, false>(p, ring_s, file_s, c_tile, tid);
+    __syncthreads();    // every thread is done reading this ring stage
     if (s_fail) break;  // uniform: s_fail was written before the barrier
-    if (tid == 0 && k + stages < my_count) issue(k + stages);
-
-    Step<T, W, NS, NI, 0>::run(p, S, R);
-#pragma unroll
-    for (int o = 0; o < B200_PW_MAX_OUT; ++o) {
-      if (o < p.n_out) {
-        T v[W];
-        fetch<T, W, NS, NI, NI>(v, SEL_INS + p.out_ins[o], S, R, p);
-#pragma unroll
-        for (int u = 0; u < U; ++u)
-          store_chunk<T, V>(reinterpret_cast<T *>(p.out[o]), (c_tile + u * PW_STREAM_THREADS + tid) * V,
-                            &v[u * V], valid[u]);
-      }
+    if (tid == 0 && k + stages < my_count) issue(k + stages, stage);
+    if (++stage == stages) {
+      stage = 0;
+      parity ^= 1;
     }
   }
   if (k < my_count) {
@@ -465,30 +573,40 @@ static int lower_ref(b200_engine *e, const b200_pw_prog *prog, uint8_t ref, int 
   return B200_OK;
 }
 
-template <typename T, int V, int NS, int NI, int U>
-static int launch_stream(b200_engine *e, const PwDev &d) {
+template <typename T, int V, int U>
+static int launch_stream_u(b200_engine *e, const PwDev &d, size_t budget, int stages) {
   constexpr int TILE_CHUNKS = PW_STREAM_THREADS * U;
-  constexpr int TILE_BYTES = TILE_CHUNKS * 16;
+  constexpr int SLOT_BYTES = TILE_CHUNKS * 16;
   const long long nchunks = (d.n + V - 1) / V;
   const long long ntiles = (nchunks + TILE_CHUNKS - 1) / TILE_CHUNKS;
-  const size_t budget = std::min<size_t>(e->smem_optin > 8192 ? e->smem_optin - 8192 : 0, 200 * 1024);
-  int stages = (int)(budget / ((size_t)d.n_full * TILE_BYTES));
-  stages = std::min(stages, PW_MAX_STAGES);
-  if (stages < 2) return -1;  // not enough shared memory for a ring: caller uses the plain kernel
-  const size_t smem = (size_t)stages * d.n_full * TILE_BYTES;
-  auto kern = pw_stream_kernel<T, V, NS, NI, U>;
-  static bool attr_set = false;  // per instantiation
-  static size_t attr_val = 0;
-  if (!attr_set || attr_val < smem) {
+  const size_t smem = ((size_t)stages * d.n_full + d.n_file) * SLOT_BYTES;
+  auto kern = pw_stream_kernel<T, V, U>;
+  static int attr_dev_mask = 0;  // per instantiation: devices on which the attribute is set
+  if (!(attr_dev_mask & (1 << (e->device & 31)))) {
     B200_CHECK_CUDA(e, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)budget));
-    attr_set = true;
-    attr_val = budget;
+    attr_dev_mask |= 1 << (e->device & 31);
   }
-  const int blocks = (int)std::min<long long>(ntiles, e->sm_count);
+  const int blocks = (int)std::min<long long>(ntiles, 2LL * e->sm_count);  // two resident CTAs per SM
   kern<<<blocks, PW_STREAM_THREADS, smem, e->stream>>>(d, stages, e->d_flags + 2);
   B200_CHECK_LAUNCH(e, "pw_stream_kernel");
   e->flags_dirty = true;
   return B200_OK;
+}
+
+// Picks the tile width and ring depth that fit shared memory; -1 if the program does not fit.
+template <typename T, int V>
+static int launch_stream(b200_engine *e, const PwDev &d) {
+  // two CTAs share an SM: each gets just under half of its shared memory
+  const size_t budget = std::min<size_t>(e->smem_optin > 4096 ? e->smem_optin - 4096 : 0, 220 * 1024) / 2;
+  for (int u = 2; u >= 1; --u) {
+    const size_t slot = (size_t)PW_STREAM_THREADS * u * 16;
+    if (budget < d.n_file * slot) continue;
+    int stages = (int)((budget - d.n_file * slot) / ((size_t)d.n_full * slot));
+    stages = std::min(stages, PW_MAX_STAGES);
+    if (stages >= (u == 2 ? 3 : 2))
+      return u == 2 ? launch_stream_u<T, V, 2>(e, d, budget, stages) : launch_stream_u<T, V, 1>(e, d, budget, stages);
+  }
+  return -1;
 }
 
 template <typename T, int V>
@@ -496,15 +614,11 @@ static int launch_sized(b200_engine *e, const PwDev &d, int ns, int ni) {
   const long long nchunks = (d.n + V - 1) / V;
   // Large, 16-byte aligned tensors take the streaming kernel. Below ~2 tiles per SM the ring
   // never fills and the plain kernel, with its many small blocks, spreads the work better.
-  if (V > 1 && d.n_full >= 1 && nchunks >= (long long)e->sm_count * PW_STREAM_THREADS * 2 * 2) {
-    int rc;
-    if (ns <= 2 && ni <= 2)
-      rc = launch_stream<T, V, 2, 2, 2>(e, d);
-    else if (ns <= 3 && ni <= 4)
-      rc = launch_stream<T, V, 3, 4, 1>(e, d);
-    else
-      rc = launch_stream<T, V, B200_PW_MAX_SRC, B200_PW_MAX_INSTR, 1>(e, d);
-    if (rc >= 0) return rc;
+  if constexpr (V > 1) {
+    if (d.n_full >= 1 && nchunks >= (long long)e->sm_count * PW_STREAM_THREADS * 2 * 2) {
+      const int rc = launch_stream<T, V>(e, d);
+      if (rc >= 0) return rc;
+    }
   }
   const int threads = 256;
   long long want = (nchunks + threads - 1) / threads;
@@ -548,7 +662,7 @@ static int run_program(b200_engine *e, int dtype, const b200_pw_prog *prog, void
     const int64_t div = prog->src_div[s], mod = prog->src_mod[s];
     if (div == 0) {
       d.src_mode[s] = SRC_FULL;
-      d.full_slot[s] = d.n_full++;
+      d.src_slot[s] = d.n_full++;
       if ((uintptr_t)srcs[s] % 16) aligned = false;
     } else {
       B200_REQUIRE(e, div > 0 && mod > 0, "pointwise: source %u has div %lld mod %lld", s, (long long)div,
@@ -557,7 +671,7 @@ static int run_program(b200_engine *e, int dtype, const b200_pw_prog *prog, void
       d.src_mod[s] = mod;
       if (mod == 1)
         d.src_mode[s] = SRC_SCALAR;
-      else if (div == 1 && mod % V == 0 && (uintptr_t)srcs[s] % 16 == 0)
+      else if (div == 1 && mod % V == 0 && mod < (1LL << 30) && (uintptr_t)srcs[s] % 16 == 0)
         d.src_mode[s] = SRC_ROWVEC;
       else if (div % V == 0)
         d.src_mode[s] = SRC_CHUNK;
@@ -586,6 +700,42 @@ static int run_program(b200_engine *e, int dtype, const b200_pw_prog *prog, void
     d.out[o] = outs[o];
     d.out_ins[o] = prog->out_instr[o];
     if ((uintptr_t)outs[o] % 16) aligned = false;
+  }
+  // operand addressing of the streaming kernel
+  for (uint32_t s2 = 0; s2 < prog->n_src; ++s2)
+    if (d.src_mode[s2] != SRC_FULL) d.src_slot[s2] = d.n_file++;
+  {
+    auto classify = [&](uint8_t sel, int k, uint8_t *kind, uint8_t *idx) {
+      if (sel >= SEL_INS) {
+        const int j = sel - SEL_INS;
+        if (j == k - 1) {
+          *kind = K_ACC;
+          *idx = 0;
+        } else {
+          if (d.keep_slot[j] == 0xFF) d.keep_slot[j] = d.n_file++;
+          *kind = K_FILE;
+          *idx = d.keep_slot[j];
+        }
+      } else if (sel >= SEL_IMM) {
+        *kind = K_IMM;
+        *idx = (uint8_t)(sel - SEL_IMM);
+      } else {
+        *kind = d.src_mode[sel] == SRC_FULL ? K_RING : K_FILE;
+        *idx = d.src_slot[sel];
+      }
+    };
+    memset(d.keep_slot, 0xFF, sizeof d.keep_slot);
+    memset(d.out_of, 0xFF, sizeof d.out_of);
+    for (uint32_t k = 0; k < prog->n_instr; ++k) {
+      classify(d.ra[k], (int)k, &d.ka[k], &d.xa[k]);
+      classify(d.rb[k], (int)k, &d.kb[k], &d.xb[k]);
+    }
+    for (uint32_t o = 0; o < prog->n_out; ++o) {
+      // one instruction may feed several outputs only through the plain kernel; the streaming
+      // kernel stores each result once, which is all the engine's own planner ever asks for
+      if (d.out_of[d.out_ins[o]] != 0xFF) d.n_full = 0;
+      d.out_of[d.out_ins[o]] = (uint8_t)o;
+    }
   }
   // a ROWVEC source needs the chunk grid itself aligned, which `aligned` guarantees
   if (!aligned)

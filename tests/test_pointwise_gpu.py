@@ -196,7 +196,7 @@ def test_deferred_chain_fuses_into_one_launch(fresh, n):
     assert_pointwise_close(got, want)
     # the unfused engine gives the same bits
     from gorgonia_b200 import Engine
-    e2 = Engine(0, 64 << 20, defer=False)
+    e2 = Engine(0, 3 * 4 * n + (1 << 20), defer=False)
     ux, uw, ub = e2.tensor(x), e2.tensor(w), e2.tensor(b)
     l0 = e2.launches
     e2.Mul(ux, uw, unsafe=True)
