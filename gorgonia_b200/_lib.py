@@ -62,6 +62,14 @@ class PwProg(C.Structure):
     ]
 
 
+class Epilogue(C.Structure):
+    _fields_ = [("bias_kind", C.c_int32), ("act", C.c_int32), ("bias", C.c_void_p), ("alpha", C.c_double)]
+
+
+BIAS_NONE, BIAS_COL, BIAS_ROW = 0, 1, 2
+ACT_NONE, ACT_RECTIFY, ACT_LEAKY = 0, 1, 2
+
+
 class PwCall(C.Structure):
     _fields_ = [
         ("op", C.c_int32), ("dtype", C.c_int32), ("form", C.c_int32), ("bcast", C.c_int32),
@@ -123,6 +131,21 @@ _SIGS = {
     "b200_pointwise": (_i, [_vp, _i, _P(PwProg), _P(_vp), _P(_vp), _i64]),
     "b200_pending": (_i, [_vp, _P(_i), _P(_i)]),
     "b200_fusion_plan": (_i, [_P(PwCall), _i, _P(_i), _P(_i), _P(_i), _P(_i), _P(_i)]),
+    "b200_gemm": (_i, [_vp, _i, _i, _i, _i64, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _i64,
+                       _P(Epilogue)]),
+    "b200_gemm_path": (_i, [_vp, _i, _i, _i, _i64, _i64, _i64, _i64, _i64, _i64, _vp, _vp, _vp]),
+    "b200_gemv": (_i, [_vp, _i, _i, _i64, _i64, _vp, _i64, _vp, _vp]),
+    "b200_ger": (_i, [_vp, _i, _i64, _i64, _vp, _vp, _vp]),
+    "b200_softmax": (_i, [_vp, _i, _vp, _vp, _i64, _i64, _i64, _i]),
+    "b200_reduce": (_i, [_vp, _i, _i, _vp, _vp, _i64, _i64, _i64]),
+    "b200_reduce_all": (_i, [_vp, _i, _i, _vp, _i64, _vp]),
+    "b200_argmax": (_i, [_vp, _i, _vp, _vp, _i64, _i64, _i64]),
+    "b200_conv2d_fwd": (_i, [_vp, _i, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _i, _i, _i, _i, _i,
+                             _P(Epilogue)]),
+    "b200_im2col": (_i, [_vp, _i, _vp, _vp, _i64, _i64, _i64, _i64, _i, _i, _i, _i, _i, _i, _i, _i]),
+    "b200_maxpool2d_fwd": (_i, [_vp, _i, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i, _i, _i, _i, _i, _i, _i, _i, _i]),
+    "b200_transpose": (_i, [_vp, _i, _vp, _vp, _i, _P(_i64), _P(_i)]),
+    "b200_gather_rows": (_i, [_vp, _vp, _vp, _vp, _i64, _i64, _i64]),
     "b200_has_nan": (_i, [_vp, _i, _vp, _i64, _P(_i)]),
     "b200_has_inf": (_i, [_vp, _i, _vp, _i64, _P(_i)]),
 }

@@ -1,0 +1,307 @@
+// BLAS-2 kernels (matrix-vector, outer product) and the general CUDA-core matrix multiply.
+//
+// Engine.MatVecMul and Engine.Outer of gorgonia (cuda/linalg.go:47-107, 232-285) call cuBLAS
+// Sgemv / Sger; both are bound by HBM, not by arithmetic, so they are written here as streaming
+// kernels: 128-bit loads, one warp per matrix row with a shuffle reduction (A x), column strips
+// with a deterministic two-pass reduction through arena scratch (A^T x), 128-bit stores (x y^T).
+//
+// gemm_simt is the matrix multiply for everything the tensor-core path (gemm_tc.cu) does not
+// take: float64, shapes whose leading dimensions break TMA's 16-byte rule, and problems too
+// small to fill a 128-row tile. Row-major operands with leading dimensions, either operand
+// transposed, batched with strides, the same fused epilogue as the tensor-core kernel.
+#include <algorithm>
+
+#include "engine.h"
+#include "epilogue.cuh"
+
+namespace b200 {
+
+__device__ __forceinline__ float fma_(float a, float b, float c) { return fmaf(a, b, c); }
+__device__ __forceinline__ double fma_(double a, double b, double c) { return fma(a, b, c); }
+
+// ---- y = A x : one warp per row ---------------------------------------------------------------
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(256) gemv_n_kernel(const T *__restrict__ A, long long lda, const T *__restrict__ x,
+                                                     T *__restrict__ y, long long M, long long N) {
+  constexpr int V = 16 / sizeof(T);
+  const int lane = threadIdx.x & 31;
+  const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+  for (long long r = warp; r < M; r += nwarps) {
+    const T *a = A + r * lda;
+    T acc[V];
+#pragma unroll
+    for (int j = 0; j < V; ++j) acc[j] = T(0);
+    if (VEC) {
+      const long long nv = N / V;
+      for (long long c = lane; c < nv; c += 32) {
+        const uint4 ra = *reinterpret_cast<const uint4 *>(a + c * V);
+        const uint4 rx = __ldg(reinterpret_cast<const uint4 *>(x + c * V));
+        T av[V], xv[V];
+        memcpy(av, &ra, 16);
+        memcpy(xv, &rx, 16);
+#pragma unroll
+        for (int j = 0; j < V; ++j) acc[j] = fma_(av[j], xv[j], acc[j]);
+      }
+      for (long long c = nv * V + lane; c < N; c += 32) acc[0] = fma_(a[c], x[c], acc[0]);
+    } else {
+      for (long long c = lane; c < N; c += 32) acc[0] = fma_(a[c], x[c], acc[0]);
+    }
+    T s = acc[0];
+#pragma unroll
+    for (int j = 1; j < V; ++j) s += acc[j];
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (lane == 0) y[r] = s;
+  }
+}
+
+// ---- y = A^T x : column strips, partial sums per row chunk, then a fold ---------------------------
+template <typename T>
+__global__ void __launch_bounds__(256) gemv_t_partial_kernel(const T *__restrict__ A, long long lda,
+                                                             const T *__restrict__ x, T *__restrict__ part,
+                                                             long long M, long long N, long long rows_per_chunk) {
+  const long long col = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long r0 = (long long)blockIdx.y * rows_per_chunk;
+  const long long r1 = r0 + rows_per_chunk < M ? r0 + rows_per_chunk : M;
+  if (col >= N) return;
+  T p0 = 0, p1 = 0, p2 = 0, p3 = 0;
+  long long r = r0;
+  for (; r + 3 < r1; r += 4) {
+    p0 = fma_(A[r * lda + col], x[r], p0);
+    p1 = fma_(A[(r + 1) * lda + col], x[r + 1], p1);
+    p2 = fma_(A[(r + 2) * lda + col], x[r + 2], p2);
+    p3 = fma_(A[(r + 3) * lda + col], x[r + 3], p3);
+  }
+  for (; r < r1; ++r) p0 = fma_(A[r * lda + col], x[r], p0);
+  part[(long long)blockIdx.y * N + col] = (p0 + p1) + (p2 + p3);
+}
+template <typename T>
+__global__ void __launch_bounds__(256) fold_rows_kernel(const T *__restrict__ part, T *__restrict__ y, long long N,
+                                                        int chunks) {
+  const long long col = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (col >= N) return;
+  T s = 0;
+  for (int c = 0; c < chunks; ++c) s += part[(long long)c * N + col];
+  y[col] = s;
+}
+
+// ---- A = x y^T ------------------------------------------------------------------------------------
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(256) ger_kernel(const T *__restrict__ x, const T *__restrict__ y, T *__restrict__ A,
+                                                  long long M, long long N) {
+  constexpr int V = 16 / sizeof(T);
+  if (VEC) {
+    const long long nv = N / V;
+    const long long total = M * nv;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += stride) {
+      const long long i = t / nv, c = t % nv;
+      const T xi = x[i];
+      const uint4 ry = __ldg(reinterpret_cast<const uint4 *>(y + c * V));
+      T yv[V], o[V];
+      memcpy(yv, &ry, 16);
+#pragma unroll
+      for (int j = 0; j < V; ++j) o[j] = xi * yv[j];
+      uint4 ro;
+      memcpy(&ro, o, 16);
+      *reinterpret_cast<uint4 *>(A + i * N + c * V) = ro;
+    }
+  } else {
+    const long long total = M * N;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += stride)
+      A[t] = x[t / N] * y[t % N];
+  }
+}
+
+// ---- general matrix multiply on CUDA cores -----------------------------------------------------
+// 64x64 tile of C per CTA, 16-deep k slices through shared memory, 4x4 accumulators per thread.
+template <typename T>
+__global__ void __launch_bounds__(256) gemm_simt_kernel(int transA, int transB, long long M, long long N,
+                                                        long long K, const T *__restrict__ A, long long lda,
+                                                        const T *__restrict__ B, long long ldb, T *__restrict__ C,
+                                                        long long ldc, long long strideA, long long strideB,
+                                                        long long strideC, Epilogue ep) {
+  constexpr int BM = 64, BN = 64, BK = 16;
+  __shared__ T As[BK][BM + 1];
+  __shared__ T Bs[BK][BN + 1];
+  A += (long long)blockIdx.z * strideA;
+  B += (long long)blockIdx.z * strideB;
+  C += (long long)blockIdx.z * strideC;
+  const long long m0 = (long long)blockIdx.y * BM, n0 = (long long)blockIdx.x * BN;
+  const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
+  T acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = T(0);
+  for (long long k0 = 0; k0 < K; k0 += BK) {
+    // A tile: BM x BK. Consecutive threads walk the contiguous direction of the operand.
+    for (int t = threadIdx.x; t < BM * BK; t += 256) {
+      int mi, ki;
+      if (!transA) {
+        ki = t % BK;
+        mi = t / BK;
+      } else {
+        mi = t % BM;
+        ki = t / BM;
+      }
+      const long long m = m0 + mi, k = k0 + ki;
+      T v = T(0);
+      if (m < M && k < K) v = transA ? A[k * lda + m] : A[m * lda + k];
+      As[ki][mi] = v;
+    }
+    for (int t = threadIdx.x; t < BN * BK; t += 256) {
+      int ni, ki;
+      if (!transB) {
+        ni = t % BN;
+        ki = t / BN;
+      } else {
+        ki = t % BK;
+        ni = t / BK;
+      }
+      const long long n = n0 + ni, k = k0 + ki;
+      T v = T(0);
+      if (n < N && k < K) v = transB ? B[n * ldb + k] : B[k * ldb + n];
+      Bs[ki][ni] = v;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < BK; ++kk) {
+      T a[4], b[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] = As[kk][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) b[j] = Bs[kk][tx * 4 + j];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fma_(a[i], b[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const long long m = m0 + ty * 4 + i;
+    if (m >= M) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const long long n = n0 + tx * 4 + j;
+      if (n < N) C[m * ldc + n] = apply_epilogue<T>(acc[i][j], ep, m, n);
+    }
+  }
+}
+
+int gemm_simt(b200_engine *e, int dtype, int transA, int transB, long long M, long long N, long long K,
+              const void *A, long long lda, const void *B, long long ldb, void *C, long long ldc, long long batch,
+              long long strideA, long long strideB, long long strideC, const Epilogue &ep) {
+  dim3 grid((unsigned)((N + 63) / 64), (unsigned)((M + 63) / 64), (unsigned)batch);
+  if (dtype == B200_F32)
+    gemm_simt_kernel<float><<<grid, 256, 0, e->stream>>>(transA, transB, M, N, K, (const float *)A, lda,
+                                                        (const float *)B, ldb, (float *)C, ldc, strideA, strideB,
+                                                        strideC, ep);
+  else
+    gemm_simt_kernel<double><<<grid, 256, 0, e->stream>>>(transA, transB, M, N, K, (const double *)A, lda,
+                                                         (const double *)B, ldb, (double *)C, ldc, strideA, strideB,
+                                                         strideC, ep);
+  B200_CHECK_LAUNCH(e, "gemm_simt_kernel");
+  return B200_OK;
+}
+
+template <typename T>
+static int gemv_typed(b200_engine *e, int transA, long long M, long long N, const T *A, long long lda, const T *x,
+                      T *y) {
+  const long long cap = (long long)e->sm_count * 8;
+  if (!transA) {
+    const bool vec = lda % (16 / sizeof(T)) == 0 && (uintptr_t)A % 16 == 0 && (uintptr_t)x % 16 == 0;
+    const int blocks = (int)std::max<long long>(1, std::min((M + 7) / 8, cap));
+    if (vec)
+      gemv_n_kernel<T, true><<<blocks, 256, 0, e->stream>>>(A, lda, x, y, M, N);
+    else
+      gemv_n_kernel<T, false><<<blocks, 256, 0, e->stream>>>(A, lda, x, y, M, N);
+    B200_CHECK_LAUNCH(e, "gemv_n_kernel");
+    return B200_OK;
+  }
+  // y (length N) = A^T x (x length M): split the rows so that the grid fills the machine
+  const long long col_blocks = (N + 255) / 256;
+  long long chunks = std::max<long long>(1, std::min<long long>((cap + col_blocks - 1) / col_blocks, (M + 63) / 64));
+  chunks = std::min<long long>(chunks, 65535);
+  const long long rows_per_chunk = (M + chunks - 1) / chunks;
+  chunks = (M + rows_per_chunk - 1) / rows_per_chunk;
+  void *part = nullptr;
+  int rc = b200_get(e, (int64_t)(chunks * N * sizeof(T)), &part);
+  if (rc != B200_OK) return rc;
+  dim3 grid((unsigned)col_blocks, (unsigned)chunks);
+  gemv_t_partial_kernel<T><<<grid, 256, 0, e->stream>>>(A, lda, x, (T *)part, M, N, rows_per_chunk);
+  cudaError_t le = cudaGetLastError();
+  if (le == cudaSuccess) {
+    e->launches++;
+    fold_rows_kernel<T><<<(unsigned)col_blocks, 256, 0, e->stream>>>((const T *)part, y, N, (int)chunks);
+    le = cudaGetLastError();
+    if (le == cudaSuccess) e->launches++;
+  }
+  // stream order makes handing the block back safe: whoever gets it next runs after the fold
+  b200_put(e, part, 0);
+  if (le != cudaSuccess) return set_error(e, B200_ERR_CUDA, "gemv launch failed: %s", cudaGetErrorString(le));
+  return B200_OK;
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" {
+
+int b200_gemv(b200_engine *e, int dtype, int transA, int64_t M, int64_t N, const void *A, int64_t lda, const void *x,
+              void *y) {
+  if (!e) return B200_ERR_INVALID;
+  std::lock_guard<std::recursive_mutex> lk(e->mu);
+  B200_REQUIRE(e, dtype == B200_F32 || dtype == B200_F64, "b200_gemv: dtype %d not supported", dtype);
+  B200_REQUIRE(e, M >= 0 && N >= 0, "b200_gemv: negative extent");
+  B200_REQUIRE(e, lda >= N, "b200_gemv: lda %lld < N %lld", (long long)lda, (long long)N);
+  const int64_t ylen = transA ? N : M, xlen = transA ? M : N;
+  if (ylen == 0) return B200_OK;
+  B200_REQUIRE(e, y != nullptr, "b200_gemv: null pointer");
+  DeviceGuard g(e);
+  int rc = flush_pending(e);
+  if (rc != B200_OK) return rc;
+  if (xlen == 0) {  // empty sum
+    B200_CHECK_CUDA(e, cudaMemsetAsync(y, 0, (size_t)ylen * dtype_size(dtype), e->stream));
+    return B200_OK;
+  }
+  B200_REQUIRE(e, A && x, "b200_gemv: null pointer");
+  if (dtype == B200_F32) return gemv_typed<float>(e, transA, M, N, (const float *)A, lda, (const float *)x, (float *)y);
+  return gemv_typed<double>(e, transA, M, N, (const double *)A, lda, (const double *)x, (double *)y);
+}
+
+int b200_ger(b200_engine *e, int dtype, int64_t M, int64_t N, const void *x, const void *y, void *A) {
+  if (!e) return B200_ERR_INVALID;
+  std::lock_guard<std::recursive_mutex> lk(e->mu);
+  B200_REQUIRE(e, dtype == B200_F32 || dtype == B200_F64, "b200_ger: dtype %d not supported", dtype);
+  B200_REQUIRE(e, M >= 0 && N >= 0, "b200_ger: negative extent");
+  if (M == 0 || N == 0) return B200_OK;
+  B200_REQUIRE(e, x && y && A, "b200_ger: null pointer");
+  DeviceGuard g(e);
+  int rc = flush_pending(e);
+  if (rc != B200_OK) return rc;
+  const size_t es = dtype_size(dtype);
+  const bool vec = N % (16 / es) == 0 && (uintptr_t)A % 16 == 0 && (uintptr_t)y % 16 == 0;
+  const long long work = vec ? M * (N / (16 / (long long)es)) : M * N;
+  const int blocks = (int)std::max<long long>(1, std::min<long long>((work + 255) / 256, (long long)e->sm_count * 16));
+  if (dtype == B200_F32) {
+    if (vec)
+      ger_kernel<float, true><<<blocks, 256, 0, e->stream>>>((const float *)x, (const float *)y, (float *)A, M, N);
+    else
+      ger_kernel<float, false><<<blocks, 256, 0, e->stream>>>((const float *)x, (const float *)y, (float *)A, M, N);
+  } else {
+    if (vec)
+      ger_kernel<double, true><<<blocks, 256, 0, e->stream>>>((const double *)x, (const double *)y, (double *)A, M, N);
+    else
+      ger_kernel<double, false><<<blocks, 256, 0, e->stream>>>((const double *)x, (const double *)y, (double *)A, M,
+                                                              N);
+  }
+  B200_CHECK_LAUNCH(e, "ger_kernel");
+  return B200_OK;
+}
+
+}  // extern "C"

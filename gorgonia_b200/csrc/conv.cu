@@ -1,0 +1,124 @@
+// 2-D convolution, forward. Gives gorgonia's Conv2d (nn.go:211-305: Im2Col -> Reshape -> MatMul
+// with the filters transposed -> Reshape -> Transpose(0,3,1,2)) one device entry point in place of
+// five tape instructions, three of which are CPU-only in the reference.
+//
+// Formulation. For every image b:  Y_b (K x Ho*Wo)  =  Wf (K x C*kh*kw)  .  col_b^T,
+// with col_b the im2col matrix of that image (Ho*Wo rows, C*kh*kw columns, column order channel,
+// kernel row, kernel column: op_nn.go:418-441). Written that way the product of each image lands
+// directly in NCHW order, the filters are used untouched (they are already K x C*kh*kw row-major),
+// the bias is a per-row vector and the activation fuses into the store: no transpose pass.
+//
+// Execution. Images are processed in chunks whose im2col scratch (TF32 head + tail) stays within
+// a fixed budget well below the L2 size, so the matrix multiply reads the col data of a chunk from
+// L2, not HBM: HBM sees x once and y once. Per chunk: one im2col+split launch, one batched
+// tensor-core launch (3xTF32, fp32 accumulate). float64, and shapes the tensor-core path does not
+// take, run im2col + the CUDA-core multiply with the same formulation.
+#include <algorithm>
+
+#include "engine.h"
+#include "epilogue.cuh"
+#include "tc_operand.h"
+
+namespace b200 {
+
+int gemm_tc_core(b200_engine *e, int terms, bool a_mn, bool b_mn, long long M, long long N, long long K,
+                 const TcOperand &a, const TcOperand &b, void *C, long long ldc, long long batch, long long strideC,
+                 const Epilogue &ep);
+int split_operand_tf32(b200_engine *e, const float *src, long long rows, long long cols, long long ld,
+                       long long batch, long long batch_stride, TcOperand *out, void **blk_hi, void **blk_lo);
+int gemm_simt(b200_engine *e, int dtype, int transA, int transB, long long M, long long N, long long K,
+              const void *A, long long lda, const void *B, long long ldb, void *C, long long ldc, long long batch,
+              long long strideA, long long strideB, long long strideC, const Epilogue &ep);
+int launch_im2col_split(b200_engine *e, const float *x, float *hi, float *lo, long long B, int C, int H, int W,
+                        int Ho, int Wo, int kh, int kw, int padH, int padW, int sH, int sW, int dH, int dW, int ld);
+
+// scratch budget for the col data of one chunk (head + tail together)
+static const long long kColChunkBytes = 64LL << 20;
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" {
+
+int b200_conv2d_fwd(b200_engine *e, int dtype, const void *x, const void *w, void *y, int64_t B, int64_t C,
+                    int64_t H, int64_t W, int64_t K, int kh, int kw, int pad_h, int pad_w, int stride_h,
+                    int stride_w, int dil_h, int dil_w, const b200_epilogue *epi) {
+  if (!e) return B200_ERR_INVALID;
+  std::lock_guard<std::recursive_mutex> lk(e->mu);
+  B200_REQUIRE(e, dtype == B200_F32 || dtype == B200_F64, "b200_conv2d_fwd: dtype %d not supported", dtype);
+  B200_REQUIRE(e, B >= 0 && C > 0 && H > 0 && W > 0 && K > 0, "b200_conv2d_fwd: bad shape");
+  B200_REQUIRE(e, kh > 0 && kw > 0 && stride_h > 0 && stride_w > 0 && dil_h > 0 && dil_w > 0 && pad_h >= 0 &&
+                      pad_w >= 0,
+               "b200_conv2d_fwd: bad kernel, stride, dilation or pad");
+  B200_REQUIRE(e, C * (long long)kh * kw < (1LL << 30) && H < (1LL << 30) && W < (1LL << 30),
+               "b200_conv2d_fwd: too large");
+  const long long Ho = (H + 2 * pad_h - (dil_h * (kh - 1) + 1)) / stride_h + 1;
+  const long long Wo = (W + 2 * pad_w - (dil_w * (kw - 1) + 1)) / stride_w + 1;
+  B200_REQUIRE(e, Ho > 0 && Wo > 0, "b200_conv2d_fwd: kernel larger than the padded image");
+  if (epi) {
+    B200_REQUIRE(e, epi->bias_kind == B200_BIAS_NONE || epi->bias_kind == B200_BIAS_ROW,
+                 "b200_conv2d_fwd: the bias is one value per output channel (B200_BIAS_ROW)");
+    B200_REQUIRE(e, epi->act >= 0 && epi->act <= 2, "b200_conv2d_fwd: bad activation");
+    B200_REQUIRE(e, epi->bias_kind == 0 || epi->bias != nullptr, "b200_conv2d_fwd: bias is null");
+  }
+  if (B == 0) return B200_OK;
+  B200_REQUIRE(e, x && w && y, "b200_conv2d_fwd: null pointer");
+  DeviceGuard g(e);
+  int rc = flush_pending(e);
+  if (rc != B200_OK) return rc;
+  Epilogue ep = make_epilogue(epi);
+
+  const long long crs = C * kh * kw, hw = Ho * Wo;
+  const size_t es = dtype_size(dtype);
+  const bool tc = dtype == B200_F32 && hw >= 16 && K * hw * crs >= 64LL * 64 * 64;
+  const long long ld = tc ? (crs + 3) / 4 * 4 : crs;
+  const long long img_bytes = hw * ld * (long long)es * (tc ? 2 : 1);
+  long long chunk = std::max<long long>(1, std::min<long long>(B, kColChunkBytes / std::max<long long>(1, img_bytes)));
+
+  if (tc) {
+    TcOperand wf, col;
+    void *wblk[2] = {nullptr, nullptr};
+    rc = split_operand_tf32(e, (const float *)w, K, crs, crs, 1, 0, &wf, &wblk[0], &wblk[1]);
+    if (rc != B200_OK) return rc;
+    wf.shared = true;
+    void *chi = nullptr, *clo = nullptr;
+    rc = b200_get(e, chunk * hw * ld * 4, &chi);
+    if (rc == B200_OK) rc = b200_get(e, chunk * hw * ld * 4, &clo);
+    for (long long b0 = 0; rc == B200_OK && b0 < B; b0 += chunk) {
+      const long long nb = std::min(chunk, B - b0);
+      rc = launch_im2col_split(e, (const float *)x + b0 * C * H * W, (float *)chi, (float *)clo, nb, (int)C, (int)H,
+                               (int)W, (int)Ho, (int)Wo, kh, kw, pad_h, pad_w, stride_h, stride_w, dil_h, dil_w,
+                               (int)ld);
+      if (rc != B200_OK) break;
+      col.p0 = chi;
+      col.p1 = clo;
+      col.ld = ld;
+      col.batch_stride = hw * ld;
+      // A = filters (K x crs, k contiguous), B = col_b stored (hw x crs): both K-major
+      rc = gemm_tc_core(e, 3, false, false, K, hw, crs, wf, col, (float *)y + b0 * K * hw, hw, nb, K * hw, ep);
+    }
+    if (chi) b200_put(e, chi, 0);
+    if (clo) b200_put(e, clo, 0);
+    b200_put(e, wblk[0], 0);
+    b200_put(e, wblk[1], 0);
+    return rc;
+  }
+
+  // CUDA-core path: plain im2col of a chunk, then Y_b = Wf . col_b^T per image
+  void *colbuf = nullptr;
+  rc = b200_get(e, chunk * hw * crs * (long long)es, &colbuf);
+  if (rc != B200_OK) return rc;
+  for (long long b0 = 0; rc == B200_OK && b0 < B; b0 += chunk) {
+    const long long nb = std::min(chunk, B - b0);
+    rc = b200_im2col(e, dtype, (const char *)x + b0 * C * H * W * es, colbuf, nb, C, H, W, kh, kw, pad_h, pad_w,
+                     stride_h, stride_w, dil_h, dil_w);
+    if (rc != B200_OK) break;
+    rc = gemm_simt(e, dtype, 0, 1, K, hw, crs, w, crs, colbuf, crs, (char *)y + b0 * K * hw * es, hw, nb, 0, hw * crs,
+                   K * hw, ep);
+  }
+  b200_put(e, colbuf, 0);
+  return rc;
+}
+
+}  // extern "C"

@@ -113,6 +113,7 @@ int b200_engine_destroy(b200_engine *e) {
     if (e->gemm_state && e->gemm_state_free) e->gemm_state_free(e->gemm_state);
     if (e->slab) cudaFree(e->slab);
     if (e->d_flags) cudaFree(e->d_flags);
+    if (e->reduce_scratch) cudaFree(e->reduce_scratch);
     if (e->h_flags) cudaFreeHost(e->h_flags);
     cudaStreamDestroy(e->stream);
   }

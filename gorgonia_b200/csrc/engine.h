@@ -34,6 +34,8 @@ struct b200_engine {
   int *h_flags = nullptr;   // pinned mirror
   bool flags_dirty = false; // a kernel that may raise d_flags[2] (bounded wait ran out) was launched
 
+  void *reduce_scratch = nullptr;  // partials + ticket of the whole-tensor reduction (reduce.cu)
+
   // lazily created resources of other translation units (gemm.cu etc.)
   void *gemm_state = nullptr;
   void (*gemm_state_free)(void *) = nullptr;

@@ -1,0 +1,63 @@
+// The fused tail of a matrix multiply or convolution: bias add and activation applied to the
+// accumulator before it is stored, with exactly the arithmetic the unfused graph would do.
+//   bias:  t = acc + bias[n] (per output column / conv channel) or bias[m] (per row)
+//   act 1: Rectify as gorgonia builds it, t * (t >= 0 ? 1 : 0)            (nn.go:136-163)
+//   act 2: LeakyRelu, t*(t>=0) + (t*(t<0))*alpha in that association        (nn.go:83-131)
+#pragma once
+#include "../../include/gorgonia_b200.h"
+
+namespace b200 {
+
+struct Epilogue {
+  int bias_kind = 0;  // B200_BIAS_NONE / _COL / _ROW
+  const void *bias = nullptr;
+  int act = 0;        // B200_ACT_NONE / _RECTIFY / _LEAKY
+  double alpha = 0.0;
+};
+
+inline Epilogue make_epilogue(const b200_epilogue *ep) {
+  Epilogue r;
+  if (ep) {
+    r.bias_kind = ep->bias_kind;
+    r.bias = ep->bias;
+    r.act = ep->act;
+    r.alpha = ep->alpha;
+  }
+  return r;
+}
+
+template <typename T>
+__device__ __forceinline__ T epi_add(T a, T b);
+template <>
+__device__ __forceinline__ float epi_add<float>(float a, float b) { return __fadd_rn(a, b); }
+template <>
+__device__ __forceinline__ double epi_add<double>(double a, double b) { return __dadd_rn(a, b); }
+template <typename T>
+__device__ __forceinline__ T epi_mul(T a, T b);
+template <>
+__device__ __forceinline__ float epi_mul<float>(float a, float b) { return __fmul_rn(a, b); }
+template <>
+__device__ __forceinline__ double epi_mul<double>(double a, double b) { return __dmul_rn(a, b); }
+
+template <typename T>
+__device__ __forceinline__ T apply_act(T t, int act, T alpha) {
+  if (act == B200_ACT_RECTIFY) return epi_mul<T>(t, t >= T(0) ? T(1) : T(0));
+  if (act == B200_ACT_LEAKY) {
+    const T pos = epi_mul<T>(t, t >= T(0) ? T(1) : T(0));
+    const T neg = epi_mul<T>(epi_mul<T>(t, t < T(0) ? T(1) : T(0)), alpha);
+    return epi_add<T>(pos, neg);
+  }
+  return t;
+}
+
+template <typename T>
+__device__ __forceinline__ T apply_epilogue(T acc, const Epilogue &ep, long long m, long long n) {
+  T t = acc;
+  if (ep.bias_kind == B200_BIAS_COL)
+    t = epi_add<T>(t, reinterpret_cast<const T *>(ep.bias)[n]);
+  else if (ep.bias_kind == B200_BIAS_ROW)
+    t = epi_add<T>(t, reinterpret_cast<const T *>(ep.bias)[m]);
+  return apply_act<T>(t, ep.act, (T)ep.alpha);
+}
+
+}  // namespace b200

@@ -1,0 +1,637 @@
+// Matrix multiply on the 5th-generation tensor cores (tcgen05), operands fed by TMA, accumulators
+// in tensor memory. Stands where Engine.MatMul calls cuBLAS Sgemm in gorgonia
+// (cuda/linalg.go:110-229) and where batchedMatMul loops over slices (operatorLinAlg.go:435-502).
+//
+// One persistent CTA per SM, 6 warps with fixed roles:
+//   warp 0     TMA producer: one lane queues the A and B boxes of each k-block into a ring of
+//              shared-memory stages (128-byte swizzle) and arms the stage's "full" mbarrier;
+//   warp 1     MMA issuer: one lane issues tcgen05.mma for each 32-byte k-slice of a stage,
+//              commits the stage's "empty" mbarrier when the tensor core has read it, and commits
+//              the accumulator's "full" mbarrier after the last k-block. Owns the TMEM allocation;
+//   warps 2-5  epilogue: each drains its 32-lane quarter of the accumulator with tcgen05.ld,
+//              applies the fused bias/activation and stores rows of C with 128-bit stores.
+// The accumulator is double-buffered in TMEM (2 x BN columns), so the epilogue of tile i runs
+// while the MMAs of tile i+1 are issued.
+//
+// Operand layouts. tcgen05 takes either operand K-major (k contiguous in memory) or MN-major
+// (m resp. n contiguous). Row-major A (M x K) is K-major, row-major B (K x N) is MN-major; the
+// transposed storages swap that. All four combinations run without a transposing pass: only the
+// TMA box shape and two fields of the shared-memory descriptor differ.
+//
+// float32 runs as 3xTF32: each operand is split once into a TF32 head and a TF32 tail
+// (x = hi + lo up to 2^-22 relative), and three products hi*lo, lo*hi, hi*hi are accumulated in
+// fp32 into the same accumulator, smallest terms first. The split is one streaming pass into
+// arena scratch; the main loop then loads four tiles per stage and issues three MMAs per slice.
+//
+// No TMA multicast and no cluster launch anywhere: every CTA loads its own tiles from local HBM.
+// Every mbarrier wait is bounded; a wait that runs out raises the engine's error word and all
+// roles leave their loops, TMEM is released and the kernel returns.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstring>
+
+#include "engine.h"
+#include "epilogue.cuh"
+#include "ptx.cuh"
+#include "tc_operand.h"
+
+namespace b200 {
+
+int gemm_simt(b200_engine *e, int dtype, int transA, int transB, long long M, long long N, long long K,
+              const void *A, long long lda, const void *B, long long ldb, void *C, long long ldc, long long batch,
+              long long strideA, long long strideB, long long strideC, const Epilogue &ep);
+
+// ------------------------------------------------------------------------------------------
+// descriptors
+// ------------------------------------------------------------------------------------------
+
+// Shared-memory matrix descriptor, 128-byte swizzle. Fields (bits): start address >> 4 [0,14),
+// leading byte offset >> 4 [16,30), stride byte offset >> 4 [32,46), version = 1 [46,48),
+// layout type [61,64) with 2 = 128-byte swizzle.
+//   K-major tile:  rows of 128 bytes, 8-row groups 1024 bytes apart  -> SBO = 1024, LBO unused (1)
+//   MN-major tile: blocks of (k rows x 128 bytes); 8-row k groups 1024 bytes apart -> SBO = 1024,
+//                  consecutive 128-byte-wide blocks along m/n `lbo_bytes` apart     -> LBO
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr >> 4) & 0x3FFF);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
+// Instruction descriptor of kind::f16 / kind::tf32: D format F32 (1) at [4,6), A format [7,10),
+// B format [10,13) (1 = BF16, 2 = TF32), A major [15], B major [16] (1 = MN-major),
+// N >> 3 at [17,23), M >> 4 at [24,29).
+__host__ __device__ constexpr uint32_t make_idesc(int fmt, int a_mn, int b_mn, int M, int N) {
+  return (1u << 4) | ((uint32_t)fmt << 7) | ((uint32_t)fmt << 10) | ((uint32_t)a_mn << 15) |
+         ((uint32_t)b_mn << 16) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+
+// ------------------------------------------------------------------------------------------
+// kernel
+// ------------------------------------------------------------------------------------------
+
+constexpr int TC_BM = 128;
+constexpr int TC_THREADS = 192;
+constexpr int TC_ROW_BYTES = 128;  // one swizzle row: 64 bf16 or 32 fp32 along the contiguous dim
+
+struct GemmTcParams {
+  long long M, N, K, batch;
+  void *C;
+  long long ldc, strideC;
+  int tiles_m, tiles_n, num_k;  // num_k = k-blocks of BK elements
+  int group_m;                  // rasterisation: m-blocks per group
+  int stages;
+  int c_vec;                    // 1: rows of C can be stored with 128-bit stores
+  int a_zmul, b_zmul;           // 0: the operand is shared by all batch entries (z coordinate 0)
+  Epilogue ep;
+  int *err_flag;
+};
+
+// TERMS = 1: bf16 operands (kind::f16). TERMS = 3: fp32 as 3xTF32 (kind::tf32), tensor maps
+// 0/1 = head/tail of A, 2/3 = head/tail of B.
+template <int TERMS, int BN, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+    gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmA1,
+                   const __grid_constant__ CUtensorMap tmB0, const __grid_constant__ CUtensorMap tmB1,
+                   const __grid_constant__ GemmTcParams p) {
+  constexpr int ES = TERMS == 1 ? 2 : 4;           // operand element size
+  constexpr int BK = TC_ROW_BYTES / ES;            // k elements per stage: 64 bf16 / 32 fp32
+  constexpr int UK = 32 / ES;                      // k elements per MMA: 16 / 8
+  constexpr int NSPLIT = TERMS == 1 ? 1 : 2;       // copies of each operand per stage (head, tail)
+  constexpr int A_BYTES = TC_BM * TC_ROW_BYTES;    // 16 KB
+  constexpr int B_BYTES = BN * TC_ROW_BYTES;
+  constexpr int STAGE_BYTES = NSPLIT * (A_BYTES + B_BYTES);
+  constexpr int MN_PER_BOX = TC_ROW_BYTES / ES;    // m/n elements covered by one MN-major box
+  constexpr uint32_t IDESC = make_idesc(TERMS == 1 ? 1 : 2, A_MN, B_MN, TC_BM, BN);
+  constexpr int MAX_STAGES = 8;
+
+  extern __shared__ __align__(1024) unsigned char tc_smem_raw[];
+  __shared__ __align__(8) uint64_t full_bar[MAX_STAGES], empty_bar[MAX_STAGES], acc_full[2], acc_empty[2];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int s_fail;
+
+  // the ring must start on a 1024-byte boundary for the 128-byte swizzle
+  unsigned char *smem = reinterpret_cast<unsigned char *>(((uintptr_t)tc_smem_raw + 1023) & ~(uintptr_t)1023);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int stages = p.stages;
+  const long long tiles_per_batch = (long long)p.tiles_m * p.tiles_n;
+  const long long total_tiles = tiles_per_batch * p.batch;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      ptx::mbar_init(&full_bar[s], 1);
+      ptx::mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      ptx::mbar_init(&acc_full[b], 1);
+      ptx::mbar_init(&acc_empty[b], 4);  // one arrival per epilogue warp
+    }
+    ptx::fence_mbar_init();
+    s_fail = 0;
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(&tmem_base_s, 2 * BN >= 32 ? 2 * BN : 32);
+    ptx::tmem_relinquish();
+  }
+  if (warp == 0 && lane == 0) {
+    ptx::prefetch_tmap(&tmA0);
+    ptx::prefetch_tmap(&tmB0);
+    if (TERMS == 3) {
+      ptx::prefetch_tmap(&tmA1);
+      ptx::prefetch_tmap(&tmB1);
+    }
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = tmem_base_s;
+
+  // tile index -> (batch, m block, n block); m blocks are walked in groups so that the CTAs of
+  // one wave share B columns and A rows in L2
+  auto decode = [&](long long tile, int &bz, int &mb, int &nb) {
+    bz = (int)(tile / tiles_per_batch);
+    const int t = (int)(tile % tiles_per_batch);
+    const int per_group = p.group_m * p.tiles_n;
+    const int g = t / per_group;
+    const int first_m = g * p.group_m;
+    const int gm = (p.tiles_m - first_m) < p.group_m ? (p.tiles_m - first_m) : p.group_m;
+    const int r = t % per_group;
+    mb = first_m + r % gm;
+    nb = r / gm;
+  };
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (long long tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        int bz, mb, nb;
+        decode(tile, bz, mb, nb);
+        for (int kb = 0; kb < p.num_k; ++kb) {
+          if (!ptx::mbar_wait(&empty_bar[stage], phase ^ 1)) {
+            ok = false;
+            break;
+          }
+          unsigned char *st = smem + (size_t)stage * STAGE_BYTES;
+          ptx::mbar_arrive_expect_tx(&full_bar[stage], STAGE_BYTES);
+          const int k0 = kb * BK;
+#pragma unroll
+          for (int h = 0; h < NSPLIT; ++h) {
+            const CUtensorMap *ta = h == 0 ? &tmA0 : &tmA1;
+            const CUtensorMap *tb = h == 0 ? &tmB0 : &tmB1;
+            unsigned char *sa = st + h * A_BYTES;
+            unsigned char *sb = st + NSPLIT * A_BYTES + h * B_BYTES;
+            if (!A_MN) {
+              ptx::tma_load_3d(sa, ta, k0, mb * TC_BM, bz * p.a_zmul, &full_bar[stage]);
+            } else {
+#pragma unroll
+              for (int q = 0; q < TC_BM / MN_PER_BOX; ++q)
+                ptx::tma_load_3d(sa + q * (BK * TC_ROW_BYTES), ta, mb * TC_BM + q * MN_PER_BOX, k0,
+                                 bz * p.a_zmul, &full_bar[stage]);
+            }
+            if (!B_MN) {
+              ptx::tma_load_3d(sb, tb, k0, nb * BN, bz * p.b_zmul, &full_bar[stage]);
+            } else {
+#pragma unroll
+              for (int q = 0; q < BN / MN_PER_BOX; ++q)
+                ptx::tma_load_3d(sb + q * (BK * TC_ROW_BYTES), tb, nb * BN + q * MN_PER_BOX, k0,
+                                 bz * p.b_zmul, &full_bar[stage]);
+            }
+          }
+          if (++stage == stages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+      if (!ok) s_fail = 1;
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int local = 0;
+      bool ok = true;
+      for (long long tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
+        const int buf = local & 1;
+        const uint32_t acc_phase = (uint32_t)((local >> 1) & 1);
+        // the epilogue must have drained this accumulator buffer (first use passes at once)
+        if (!ptx::mbar_wait(&acc_empty[buf], acc_phase ^ 1)) {
+          ok = false;
+          break;
+        }
+        ptx::tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
+        for (int kb = 0; kb < p.num_k; ++kb) {
+          if (!ptx::mbar_wait(&full_bar[stage], phase)) {
+            ok = false;
+            break;
+          }
+          ptx::tc_fence_after_sync();
+          const uint32_t st = ptx::smem_addr(smem + (size_t)stage * STAGE_BYTES);
+#pragma unroll
+          for (int kk = 0; kk < BK / UK; ++kk) {
+            // k-slice kk: 32 bytes further along a K-major row, UK k-rows further in an MN-major block
+            const uint32_t a_off = A_MN ? kk * UK * TC_ROW_BYTES : kk * 32;
+            const uint32_t b_off = B_MN ? kk * UK * TC_ROW_BYTES : kk * 32;
+            const uint32_t a_lbo = A_MN ? BK * TC_ROW_BYTES : 16;
+            const uint32_t b_lbo = B_MN ? BK * TC_ROW_BYTES : 16;
+            uint64_t ad[NSPLIT], bd[NSPLIT];
+#pragma unroll
+            for (int h = 0; h < NSPLIT; ++h) {
+              ad[h] = make_smem_desc(st + h * A_BYTES + a_off, a_lbo, 1024);
+              bd[h] = make_smem_desc(st + NSPLIT * A_BYTES + h * B_BYTES + b_off, b_lbo, 1024);
+            }
+            const uint32_t first = (kb > 0 || kk > 0) ? 1u : 0u;
+            if (TERMS == 1) {
+              ptx::mma_f16(d_tmem, ad[0], bd[0], IDESC, first);
+            } else {
+              // smallest terms first: hi*lo, lo*hi, then hi*hi
+              ptx::mma_tf32(d_tmem, ad[0], bd[NSPLIT - 1], IDESC, first);
+              ptx::mma_tf32(d_tmem, ad[NSPLIT - 1], bd[0], IDESC, 1u);
+              ptx::mma_tf32(d_tmem, ad[0], bd[0], IDESC, 1u);
+            }
+          }
+          ptx::mma_commit(&empty_bar[stage]);  // the stage is free once these MMAs have read it
+          if (++stage == stages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (ok) ptx::mma_commit(&acc_full[buf]);  // accumulator complete
+      }
+      if (!ok) s_fail = 1;
+    }
+  } else {
+    // ---------------- epilogue: warps 2..5 ----------------
+    const int quarter = warp & 3;  // the TMEM lanes this warp may read: 32*quarter .. +31
+    int local = 0;
+    bool ok = true;
+    for (long long tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
+      int bz, mb, nb;
+      decode(tile, bz, mb, nb);
+      const int buf = local & 1;
+      const uint32_t acc_phase = (uint32_t)((local >> 1) & 1);
+      if (!ptx::mbar_wait(&acc_full[buf], acc_phase)) {
+        ok = false;
+        break;
+      }
+      ptx::tc_fence_after_sync();
+      const long long m = (long long)mb * TC_BM + quarter * 32 + lane;
+      float *crow = reinterpret_cast<float *>(p.C) + (long long)bz * p.strideC + m * p.ldc;
+      const long long n0 = (long long)nb * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 32) {
+        uint32_t r[32];
+        ptx::tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + c), r);
+        ptx::tmem_ld_wait();
+        if (m < p.M) {
+          const long long nbase = n0 + c;
+          if (p.c_vec && nbase + 32 <= p.N) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              float4 o;
+              o.x = apply_epilogue<float>(__uint_as_float(r[j + 0]), p.ep, m, nbase + j + 0);
+              o.y = apply_epilogue<float>(__uint_as_float(r[j + 1]), p.ep, m, nbase + j + 1);
+              o.z = apply_epilogue<float>(__uint_as_float(r[j + 2]), p.ep, m, nbase + j + 2);
+              o.w = apply_epilogue<float>(__uint_as_float(r[j + 3]), p.ep, m, nbase + j + 3);
+              *reinterpret_cast<float4 *>(crow + nbase + j) = o;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (nbase + j < p.N) crow[nbase + j] = apply_epilogue<float>(__uint_as_float(r[j]), p.ep, m, nbase + j);
+          }
+        }
+      }
+      // hand the accumulator buffer back to the MMA issuer
+      ptx::tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(&acc_empty[buf]);
+    }
+    if (!ok) s_fail = 1;
+  }
+
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if (threadIdx.x == 0 && s_fail) atomicExch(p.err_flag, 1);
+  if (warp == 1) {
+    ptx::tc_fence_after_sync();
+    ptx::tmem_dealloc(tmem_base, 2 * BN >= 32 ? 2 * BN : 32);
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// TF32 split: x -> (head, tail), both TF32 values in fp32 containers, written densely with the
+// row length padded to a multiple of 4 elements (so that TMA row pitches stay 16-byte multiples)
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ float to_tf32(float x) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+  return __uint_as_float(r);
+}
+
+__global__ void __launch_bounds__(256) split_tf32_kernel(const float *__restrict__ src, long long ld_in,
+                                                         long long stride_in, float *__restrict__ hi,
+                                                         float *__restrict__ lo, long long rows, long long cols,
+                                                         long long ld_out, long long batch) {
+  const long long per = rows * ld_out;
+  const long long total = per * batch;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += stride) {
+    const long long b = t / per, rem = t % per;
+    const long long r = rem / ld_out, c = rem % ld_out;
+    float x = 0.f;
+    if (c < cols) x = src[b * stride_in + r * ld_in + c];
+    const float h = to_tf32(x);
+    hi[t] = h;
+    lo[t] = to_tf32(__fsub_rn(x, h));
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// host side
+// ------------------------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void *sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)sym;
+  }
+  return fn;
+}
+
+// A 3-D map (contiguous dim, rows, batch) over a row-major matrix with `ld` elements per row.
+static int encode_map(b200_engine *e, CUtensorMap *map, int es, const void *base, long long inner, long long rows,
+                      long long batch, long long ld, long long batch_stride, int box_inner, int box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return set_error(e, B200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  cuuint64_t dims[3] = {(cuuint64_t)inner, (cuuint64_t)rows, (cuuint64_t)batch};
+  cuuint64_t strides[2] = {(cuuint64_t)ld * es, (cuuint64_t)(batch > 1 ? batch_stride : rows * ld) * es};
+  cuuint32_t box[3] = {(cuuint32_t)box_inner, (cuuint32_t)box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, es == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3,
+                  const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return set_error(e, B200_ERR_CUDA,
+                     "cuTensorMapEncodeTiled failed (%d): dims %lld x %lld x %lld, ld %lld, box %d x %d", (int)r,
+                     inner, rows, batch, ld, box_inner, box_rows);
+  return B200_OK;
+}
+
+static bool tc_eligible(int dtype, long long M, long long N, long long K, long long lda, long long ldb,
+                        long long ldc, long long batch, long long strideA, long long strideB, const void *A,
+                        const void *B, const void *C) {
+  if (dtype != B200_F32 && dtype != B200_BF16) return false;
+  if (M < 1 || N < 1 || K < 1) return false;
+  // tiny problems: a 128-row tile would be mostly padding and the launch is latency-bound anyway
+  if (M * N * K < 64LL * 64 * 64) return false;
+  if (N < 16) return false;
+  if ((uintptr_t)C % 4 != 0) return false;
+  if (dtype == B200_BF16) {
+    if (((uintptr_t)A | (uintptr_t)B) % 16 != 0) return false;
+    // TMA reads the caller's buffers directly: row pitch and batch pitch in bytes must be 16-byte multiples
+    if ((lda * 2) % 16 || (ldb * 2) % 16) return false;
+    if (batch > 1 && ((strideA * 2) % 16 || (strideB * 2) % 16)) return false;
+  }
+  // float32 goes through the split pass, which re-pitches rows itself: no constraint on lda / ldb
+  (void)ldc;
+  return true;
+}
+
+template <int TERMS, int BN, bool A_MN, bool B_MN>
+static int launch_tc(b200_engine *e, const CUtensorMap *tm, const GemmTcParams &p, int grid) {
+  constexpr int ES = TERMS == 1 ? 2 : 4;
+  constexpr int NSPLIT = TERMS == 1 ? 1 : 2;
+  constexpr int STAGE_BYTES = NSPLIT * (TC_BM + BN) * TC_ROW_BYTES;
+  (void)ES;
+  auto kern = gemm_tc_kernel<TERMS, BN, A_MN, B_MN>;
+  const size_t smem = (size_t)p.stages * STAGE_BYTES + 1024;
+  static int attr_dev_mask = 0;
+  if (!(attr_dev_mask & (1 << (e->device & 31)))) {
+    B200_CHECK_CUDA(e, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                            (int)std::min<size_t>(e->smem_optin, 227 * 1024)));
+    attr_dev_mask |= 1 << (e->device & 31);
+  }
+  kern<<<grid, TC_THREADS, smem, e->stream>>>(tm[0], tm[1], tm[2], tm[3], p);
+  B200_CHECK_LAUNCH(e, "gemm_tc_kernel");
+  e->flags_dirty = true;
+  return B200_OK;
+}
+
+template <int TERMS, int BN>
+static int launch_tc_layout(b200_engine *e, bool a_mn, bool b_mn, const CUtensorMap *tm, const GemmTcParams &p,
+                            int grid) {
+  if (!a_mn && !b_mn) return launch_tc<TERMS, BN, false, false>(e, tm, p, grid);
+  if (!a_mn && b_mn) return launch_tc<TERMS, BN, false, true>(e, tm, p, grid);
+  if (a_mn && !b_mn) return launch_tc<TERMS, BN, true, false>(e, tm, p, grid);
+  return launch_tc<TERMS, BN, true, true>(e, tm, p, grid);
+}
+
+
+// terms = 1 (bf16) or 3 (fp32 split into head/tail). a_mn / b_mn: the operand is stored with its
+// m / n index contiguous (see the file comment).
+int gemm_tc_core(b200_engine *e, int terms, bool a_mn, bool b_mn, long long M, long long N, long long K,
+                 const TcOperand &a, const TcOperand &b, void *C, long long ldc, long long batch, long long strideC,
+                 const Epilogue &ep) {
+  const int es = terms == 1 ? 2 : 4;
+  const int bk = TC_ROW_BYTES / es;
+  // tile width: the widest that still gives every SM a tile, to keep small problems spread out
+  const int tiles_m = (int)((M + TC_BM - 1) / TC_BM);
+  int bn = terms == 1 ? 256 : 128;
+  while (bn > 64 && (long long)tiles_m * ((N + bn - 1) / bn) * batch < e->sm_count) bn /= 2;
+  while (bn > 64 && bn / 2 >= N) bn /= 2;
+  const int tiles_n = (int)((N + bn - 1) / bn);
+
+  CUtensorMap tm[4];
+  memset(tm, 0, sizeof tm);
+  const int mn_box = TC_ROW_BYTES / es;
+  const long long a_batch = a.shared ? 1 : batch, b_batch = b.shared ? 1 : batch;
+  for (int h = 0; h < (terms == 1 ? 1 : 2); ++h) {
+    const void *ap = h == 0 ? a.p0 : a.p1, *bp = h == 0 ? b.p0 : b.p1;
+    int rc;
+    if (!a_mn)
+      rc = encode_map(e, &tm[h], es, ap, K, M, a_batch, a.ld, a.batch_stride, bk, TC_BM);
+    else
+      rc = encode_map(e, &tm[h], es, ap, M, K, a_batch, a.ld, a.batch_stride, mn_box, bk);
+    if (rc != B200_OK) return rc;
+    if (!b_mn)
+      rc = encode_map(e, &tm[2 + h], es, bp, K, N, b_batch, b.ld, b.batch_stride, bk, bn);
+    else
+      rc = encode_map(e, &tm[2 + h], es, bp, N, K, b_batch, b.ld, b.batch_stride, mn_box, bk);
+    if (rc != B200_OK) return rc;
+  }
+  if (terms == 1) {
+    tm[1] = tm[0];
+    tm[3] = tm[2];
+  }
+
+  GemmTcParams p;
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.batch = batch;
+  p.C = C;
+  p.ldc = ldc;
+  p.strideC = strideC;
+  p.tiles_m = tiles_m;
+  p.tiles_n = tiles_n;
+  p.num_k = (int)((K + bk - 1) / bk);
+  p.group_m = std::min(tiles_m, 8);
+  p.c_vec = (ldc % 4 == 0 && (uintptr_t)C % 16 == 0 && (batch == 1 || strideC % 4 == 0)) ? 1 : 0;
+  p.a_zmul = a.shared ? 0 : 1;
+  p.b_zmul = b.shared ? 0 : 1;
+  p.ep = ep;
+  p.err_flag = e->d_flags + 2;
+  const int nsplit = terms == 1 ? 1 : 2;
+  const size_t stage_bytes = (size_t)nsplit * (TC_BM + bn) * TC_ROW_BYTES;
+  const size_t budget = std::min<size_t>(e->smem_optin, 227 * 1024) - 2048;
+  p.stages = (int)std::max<size_t>(2, std::min<size_t>(8, budget / stage_bytes));
+  const long long total_tiles = (long long)tiles_m * tiles_n * batch;
+  const int grid = (int)std::min<long long>(total_tiles, e->sm_count);
+
+  if (terms == 1) {
+    if (bn == 256) return launch_tc_layout<1, 256>(e, a_mn, b_mn, tm, p, grid);
+    if (bn == 128) return launch_tc_layout<1, 128>(e, a_mn, b_mn, tm, p, grid);
+    return launch_tc_layout<1, 64>(e, a_mn, b_mn, tm, p, grid);
+  }
+  if (bn == 128) return launch_tc_layout<3, 128>(e, a_mn, b_mn, tm, p, grid);
+  return launch_tc_layout<3, 64>(e, a_mn, b_mn, tm, p, grid);
+}
+
+// Splits a row-major fp32 matrix (rows x cols, pitch ld, `batch` of them) into TF32 head and tail
+// in arena scratch with a pitch that is a multiple of 4 elements. The caller hands the two
+// blocks back with b200_put once the consuming kernel has been launched.
+int split_operand_tf32(b200_engine *e, const float *src, long long rows, long long cols, long long ld,
+                       long long batch, long long batch_stride, TcOperand *out, void **blk_hi, void **blk_lo) {
+  const long long ldo = (cols + 3) / 4 * 4;
+  const long long elems = rows * ldo * batch;
+  *blk_hi = *blk_lo = nullptr;
+  int rc = b200_get(e, elems * 4, blk_hi);
+  if (rc != B200_OK) return rc;
+  rc = b200_get(e, elems * 4, blk_lo);
+  if (rc != B200_OK) {
+    b200_put(e, *blk_hi, 0);
+    *blk_hi = nullptr;
+    return rc;
+  }
+  const int blocks = (int)std::max<long long>(1, std::min<long long>((elems + 255) / 256, e->sm_count * 16LL));
+  split_tf32_kernel<<<blocks, 256, 0, e->stream>>>(src, ld, batch_stride, (float *)*blk_hi, (float *)*blk_lo, rows,
+                                                   cols, ldo, batch);
+  cudaError_t le = cudaGetLastError();
+  if (le != cudaSuccess) {
+    b200_put(e, *blk_hi, 0);
+    b200_put(e, *blk_lo, 0);
+    *blk_hi = *blk_lo = nullptr;
+    return set_error(e, B200_ERR_CUDA, "launch of split_tf32_kernel failed: %s", cudaGetErrorString(le));
+  }
+  e->launches++;
+  out->p0 = *blk_hi;
+  out->p1 = *blk_lo;
+  out->ld = ldo;
+  out->batch_stride = rows * ldo;
+  out->shared = false;
+  return B200_OK;
+}
+
+static int gemm_tc(b200_engine *e, int dtype, int transA, int transB, long long M, long long N, long long K,
+                   const void *A, long long lda, const void *B, long long ldb, void *C, long long ldc,
+                   long long batch, long long strideA, long long strideB, long long strideC, const Epilogue &ep) {
+  const bool a_mn = transA != 0;   // stored K x M: m contiguous
+  const bool b_mn = transB == 0;   // stored K x N: n contiguous
+  TcOperand a, b;
+  if (dtype == B200_BF16) {
+    a.p0 = A;
+    a.ld = lda;
+    a.batch_stride = strideA;
+    b.p0 = B;
+    b.ld = ldb;
+    b.batch_stride = strideB;
+    return gemm_tc_core(e, 1, a_mn, b_mn, M, N, K, a, b, C, ldc, batch, strideC, ep);
+  }
+  // stored shapes (rows x contiguous)
+  const long long a_rows = transA ? K : M, a_cols = transA ? M : K;
+  const long long b_rows = transB ? N : K, b_cols = transB ? K : N;
+  void *blk[4] = {nullptr, nullptr, nullptr, nullptr};
+  int rc = split_operand_tf32(e, (const float *)A, a_rows, a_cols, lda, batch, strideA, &a, &blk[0], &blk[1]);
+  if (rc == B200_OK) rc = split_operand_tf32(e, (const float *)B, b_rows, b_cols, ldb, batch, strideB, &b, &blk[2], &blk[3]);
+  if (rc == B200_OK) rc = gemm_tc_core(e, 3, a_mn, b_mn, M, N, K, a, b, C, ldc, batch, strideC, ep);
+  // stream order makes handing the scratch back safe: later users run after this kernel
+  for (void *s2 : blk)
+    if (s2) b200_put(e, s2, 0);
+  return rc;
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" {
+
+int b200_gemm_path(b200_engine *e, int dtype, int transA, int transB, int64_t M, int64_t N, int64_t K, int64_t lda,
+                   int64_t ldb, int64_t ldc, const void *A, const void *B, const void *C) {
+  (void)e;
+  (void)transA;
+  (void)transB;
+  return tc_eligible(dtype, M, N, K, lda, ldb, ldc, 1, 0, 0, A, B, C) ? 1 : 0;
+}
+
+int b200_gemm(b200_engine *e, int dtype, int transA, int transB, int64_t M, int64_t N, int64_t K, const void *A,
+              int64_t lda, const void *B, int64_t ldb, void *C, int64_t ldc, int64_t batch, int64_t strideA,
+              int64_t strideB, int64_t strideC, const b200_epilogue *epi) {
+  if (!e) return B200_ERR_INVALID;
+  std::lock_guard<std::recursive_mutex> lk(e->mu);
+  B200_REQUIRE(e, dtype == B200_F32 || dtype == B200_F64 || dtype == B200_BF16, "b200_gemm: dtype %d not supported",
+               dtype);
+  B200_REQUIRE(e, M >= 0 && N >= 0 && K >= 0 && batch >= 0, "b200_gemm: negative extent");
+  if (M == 0 || N == 0 || batch == 0) return B200_OK;
+  B200_REQUIRE(e, C != nullptr, "b200_gemm: C is null");
+  const int64_t a_cols = transA ? M : K, b_cols = transB ? K : N;
+  B200_REQUIRE(e, lda >= a_cols && ldb >= b_cols && ldc >= N, "b200_gemm: leading dimension too small (%lld %lld %lld)",
+               (long long)lda, (long long)ldb, (long long)ldc);
+  if (epi) {
+    B200_REQUIRE(e, epi->bias_kind >= 0 && epi->bias_kind <= 2 && epi->act >= 0 && epi->act <= 2,
+                 "b200_gemm: bad epilogue");
+    B200_REQUIRE(e, epi->bias_kind == 0 || epi->bias != nullptr, "b200_gemm: bias is null");
+  }
+  DeviceGuard g(e);
+  int rc = flush_pending(e);
+  if (rc != B200_OK) return rc;
+  Epilogue ep = make_epilogue(epi);
+  if (K == 0) {
+    // empty sum: C = epilogue(0); the CUDA-core kernel handles it with a zero-trip k loop
+    if (dtype == B200_BF16) return set_error(e, B200_ERR_UNSUPPORTED, "b200_gemm: bf16 with K = 0");
+    return gemm_simt(e, dtype, transA, transB, M, N, 0, C, lda, C, ldb, C, ldc, batch, 0, 0, strideC, ep);
+  }
+  B200_REQUIRE(e, A && B, "b200_gemm: null operand");
+  if (tc_eligible(dtype, M, N, K, lda, ldb, ldc, batch, strideA, strideB, A, B, C))
+    return gemm_tc(e, dtype, transA, transB, M, N, K, A, lda, B, ldb, C, ldc, batch, strideA, strideB, strideC, ep);
+  if (dtype == B200_BF16)
+    return set_error(e, B200_ERR_UNSUPPORTED,
+                     "b200_gemm: bf16 operands need 16-byte aligned bases and row pitches (lda %lld, ldb %lld) and "
+                     "at least 64^3 work",
+                     (long long)lda, (long long)ldb);
+  return gemm_simt(e, dtype, transA, transB, M, N, K, A, lda, B, ldb, C, ldc, batch, strideA, strideB, strideC, ep);
+}
+
+}  // extern "C"

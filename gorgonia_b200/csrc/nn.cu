@@ -1,0 +1,372 @@
+// Max-pooling, im2col, N-d transpose and row gather.
+//
+// In gorgonia these are CPU ops (maxPoolOp.do, op_nn.go:828-907; im2colOp.do, op_nn.go:317-444;
+// transposeOp.Do, op_tensor.go:937-952; byIndicesOp.Do, op_by_indices.go:90-97): the tape bounces
+// every one of them through host memory. Here they are device kernels, so a whole forward tape
+// stays resident. All of them are pure data movement, bound by HBM; the kernels are laid out so
+// that consecutive threads write consecutive addresses.
+#include <algorithm>
+#include <cfloat>
+
+#include "engine.h"
+
+namespace b200 {
+
+// ---- max-pool --------------------------------------------------------------------------------
+// One thread per output element. The window is clipped to the image; the accumulator starts at
+// -FLT_MAX and only a strictly larger value replaces it, so the first maximum in row-major window
+// order wins and an all-NaN window yields -FLT_MAX, as in the reference loop (op_nn.go:877-900).
+// (oh0, ow0) is the offset of the window origin: gorgonia uses the north/west pads, or, with
+// explicit 4-way padding, the south/east pads (op_nn.go:870-875).
+template <typename T>
+__device__ __forceinline__ T lowest();
+template <>
+__device__ __forceinline__ float lowest<float>() { return -FLT_MAX; }
+template <>
+__device__ __forceinline__ double lowest<double>() { return -DBL_MAX; }
+
+template <typename T>
+__global__ void __launch_bounds__(256) maxpool_kernel(const T *__restrict__ x, T *__restrict__ y,
+                                                      long long *__restrict__ mask, long long planes, int H, int W,
+                                                      int Ho, int Wo, int kh, int kw, int sH, int sW, int oh0,
+                                                      int ow0) {
+  const long long total = planes * Ho * Wo;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += stride) {
+    const int pw = (int)(t % Wo);
+    const int ph = (int)((t / Wo) % Ho);
+    const long long plane = t / ((long long)Wo * Ho);
+    const T *in = x + plane * H * W;
+    int hs = ph * sH - oh0, ws = pw * sW - ow0;
+    const int he = min(hs + kh, H), we = min(ws + kw, W);
+    hs = max(hs, 0);
+    ws = max(ws, 0);
+    T best = lowest<T>();
+    long long arg = -1;
+    for (int hi = hs; hi < he; ++hi)
+      for (int wi = ws; wi < we; ++wi) {
+        const T v = in[hi * W + wi];
+        if (v > best) {
+          best = v;
+          arg = (long long)hi * W + wi;
+        }
+      }
+    y[t] = best;
+    if (mask) mask[t] = arg;
+  }
+}
+
+// ---- im2col ------------------------------------------------------------------------------------
+// col[(b, oh, ow), (c, r, s)] = x[b, c, oh*sH - padH + r*dH, ow*sW - padW + s*dW], 0 outside.
+// One thread per column element; consecutive threads write consecutive (c, r, s), which makes
+// the big side (the col buffer) perfectly coalesced while reads of x hit L1/L2.
+// SPLIT: write the TF32 head and tail of each value instead (feeds the 3xTF32 matrix multiply
+// without a second pass over the col buffer); the row pitch `ld` may exceed C*kh*kw (padding = 0).
+__device__ __forceinline__ float to_tf32_rna(float v) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(v));
+  return __uint_as_float(r);
+}
+
+template <typename T, bool SPLIT>
+__global__ void __launch_bounds__(256) im2col_kernel(const T *__restrict__ x, T *__restrict__ col,
+                                                     T *__restrict__ col_lo, long long B, int C, int H, int W,
+                                                     int Ho, int Wo, int kh, int kw, int padH, int padW, int sH,
+                                                     int sW, int dH, int dW, int ld) {
+  const int crs = C * kh * kw;
+  const long long total = B * Ho * Wo * (long long)ld;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += stride) {
+    const int q = (int)(t % ld);
+    const long long row = t / ld;
+    T v = T(0);
+    if (q < crs) {
+      const int s = q % kw;
+      const int r = (q / kw) % kh;
+      const int c = q / (kw * kh);
+      const int ow = (int)(row % Wo);
+      const int oh = (int)((row / Wo) % Ho);
+      const long long b = row / ((long long)Wo * Ho);
+      const int ih = oh * sH - padH + r * dH;
+      const int iw = ow * sW - padW + s * dW;
+      if (ih >= 0 && ih < H && iw >= 0 && iw < W) v = x[((b * C + c) * H + ih) * (long long)W + iw];
+    }
+    if (SPLIT) {
+      const float h = to_tf32_rna((float)v);
+      col[t] = (T)h;
+      col_lo[t] = (T)to_tf32_rna(__fsub_rn((float)v, h));
+    } else {
+      col[t] = v;
+    }
+  }
+}
+
+// ---- transpose ---------------------------------------------------------------------------------
+struct TransposeDesc {
+  int ndim;
+  long long out_shape[8];
+  long long in_stride_of_out_dim[8];  // stride, in the input, of the input axis that output axis d reads
+};
+
+// General N-d permutation: one thread per output element (writes coalesced).
+template <typename T>
+__global__ void __launch_bounds__(256) transpose_kernel(const T *__restrict__ x, T *__restrict__ y, long long n,
+                                                        TransposeDesc d) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    long long rem = i, src = 0;
+#pragma unroll 1
+    for (int k = d.ndim - 1; k >= 0; --k) {
+      const long long c = rem % d.out_shape[k];
+      rem /= d.out_shape[k];
+      src += c * d.in_stride_of_out_dim[k];
+    }
+    y[i] = x[src];
+  }
+}
+
+// Batched 2-D transpose through a padded shared-memory tile: y[b][c][r] = x[b][r][c]. Both the
+// reads and the writes are coalesced. Covers (0,3,1,2)/(0,2,3,1)-style permutations of 4-D
+// tensors, which collapse to this form.
+template <typename T>
+__global__ void __launch_bounds__(256) transpose2d_kernel(const T *__restrict__ x, T *__restrict__ y, long long R,
+                                                          long long Cc) {
+  __shared__ T tile[32][33];
+  const long long b = blockIdx.z;
+  const T *xb = x + b * R * Cc;
+  T *yb = y + b * R * Cc;
+  const long long c0 = (long long)blockIdx.x * 32, r0 = (long long)blockIdx.y * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
+  for (int j = ty; j < 32; j += 8) {
+    const long long r = r0 + j, c = c0 + tx;
+    if (r < R && c < Cc) tile[j][tx] = xb[r * Cc + c];
+  }
+  __syncthreads();
+  for (int j = ty; j < 32; j += 8) {
+    const long long c = c0 + j, r = r0 + tx;
+    if (r < R && c < Cc) yb[c * R + r] = tile[tx][j];
+  }
+}
+
+// ---- gather of rows ------------------------------------------------------------------------------
+// y[i, :] = x[idx[i], :]; rows are copied in 16-byte words when the row size and the bases allow.
+// An index outside [0, n_rows) raises the flag and leaves the row untouched.
+template <typename W>
+__global__ void __launch_bounds__(256) gather_rows_kernel(const W *__restrict__ x, const long long *__restrict__ idx,
+                                                          W *__restrict__ y, long long n_idx, long long row_words,
+                                                          long long n_rows, int *bad) {
+  const long long total = n_idx * row_words;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += stride) {
+    const long long i = t / row_words, w = t % row_words;
+    const long long src = idx[i];
+    if (src < 0 || src >= n_rows) {
+      if (w == 0) atomicExch(bad, 1);
+      continue;
+    }
+    y[t] = x[src * row_words + w];
+  }
+}
+
+static int grid_for(b200_engine *e, long long work) {
+  return (int)std::max<long long>(1, std::min<long long>((work + 255) / 256, (long long)e->sm_count * 16));
+}
+
+// used by conv.cu
+int launch_im2col_split(b200_engine *e, const float *x, float *hi, float *lo, long long B, int C, int H, int W,
+                        int Ho, int Wo, int kh, int kw, int padH, int padW, int sH, int sW, int dH, int dW, int ld) {
+  const long long total = B * Ho * Wo * (long long)ld;
+  im2col_kernel<float, true><<<grid_for(e, total), 256, 0, e->stream>>>(x, hi, lo, B, C, H, W, Ho, Wo, kh, kw, padH,
+                                                                       padW, sH, sW, dH, dW, ld);
+  B200_CHECK_LAUNCH(e, "im2col_kernel");
+  return B200_OK;
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" {
+
+int b200_maxpool2d_fwd(b200_engine *e, int dtype, const void *x, void *y, int64_t *mask, int64_t B, int64_t C,
+                       int64_t H, int64_t W, int kh, int kw, int pad_north, int pad_south, int pad_west,
+                       int pad_east, int explicit_padding, int stride_h, int stride_w) {
+  if (!e) return B200_ERR_INVALID;
+  std::lock_guard<std::recursive_mutex> lk(e->mu);
+  B200_REQUIRE(e, dtype == B200_F32 || dtype == B200_F64, "b200_maxpool2d_fwd: dtype %d not supported", dtype);
+  B200_REQUIRE(e, B >= 0 && C >= 0 && H > 0 && W > 0, "b200_maxpool2d_fwd: bad input shape");
+  B200_REQUIRE(e, kh > 0 && kw > 0 && stride_h > 0 && stride_w > 0, "b200_maxpool2d_fwd: bad kernel or stride");
+  B200_REQUIRE(e, pad_north >= 0 && pad_south >= 0 && pad_west >= 0 && pad_east >= 0, "b200_maxpool2d_fwd: bad pad");
+  B200_REQUIRE(e, H < (1LL << 30) && W < (1LL << 30), "b200_maxpool2d_fwd: image too large");
+  const long long Ho = (H + pad_south + pad_north - (kh - 1) - 1) / stride_h + 1;
+  const long long Wo = (W + pad_east + pad_west - (kw - 1) - 1) / stride_w + 1;
+  B200_REQUIRE(e, Ho > 0 && Wo > 0, "b200_maxpool2d_fwd: window larger than the padded image");
+  if (B * C == 0) return B200_OK;
+  B200_REQUIRE(e, x && y, "b200_maxpool2d_fwd: null pointer");
+  DeviceGuard g(e);
+  int rc = flush_pending(e);
+  if (rc != B200_OK) return rc;
+  const int oh0 = explicit_padding ? pad_south : pad_north;
+  const int ow0 = explicit_padding ? pad_east : pad_west;
+  const long long total = B * C * Ho * Wo;
+  if (dtype == B200_F32)
+    maxpool_kernel<float><<<grid_for(e, total), 256, 0, e->stream>>>((const float *)x, (float *)y, (long long *)mask,
+                                                                    B * C, (int)H, (int)W, (int)Ho, (int)Wo, kh, kw,
+                                                                    stride_h, stride_w, oh0, ow0);
+  else
+    maxpool_kernel<double><<<grid_for(e, total), 256, 0, e->stream>>>((const double *)x, (double *)y,
+                                                                     (long long *)mask, B * C, (int)H, (int)W,
+                                                                     (int)Ho, (int)Wo, kh, kw, stride_h, stride_w,
+                                                                     oh0, ow0);
+  B200_CHECK_LAUNCH(e, "maxpool_kernel");
+  return B200_OK;
+}
+
+int b200_im2col(b200_engine *e, int dtype, const void *x, void *col, int64_t B, int64_t C, int64_t H, int64_t W,
+                int kh, int kw, int pad_h, int pad_w, int stride_h, int stride_w, int dil_h, int dil_w) {
+  if (!e) return B200_ERR_INVALID;
+  std::lock_guard<std::recursive_mutex> lk(e->mu);
+  B200_REQUIRE(e, dtype == B200_F32 || dtype == B200_F64, "b200_im2col: dtype %d not supported", dtype);
+  B200_REQUIRE(e, B >= 0 && C > 0 && H > 0 && W > 0, "b200_im2col: bad input shape");
+  B200_REQUIRE(e, kh > 0 && kw > 0 && stride_h > 0 && stride_w > 0 && dil_h > 0 && dil_w > 0 && pad_h >= 0 &&
+                      pad_w >= 0,
+               "b200_im2col: bad kernel, stride, dilation or pad");
+  B200_REQUIRE(e, C * (long long)kh * kw < (1LL << 30) && H < (1LL << 30) && W < (1LL << 30), "b200_im2col: too large");
+  const long long Ho = (H + 2 * pad_h - (dil_h * (kh - 1) + 1)) / stride_h + 1;
+  const long long Wo = (W + 2 * pad_w - (dil_w * (kw - 1) + 1)) / stride_w + 1;
+  B200_REQUIRE(e, Ho > 0 && Wo > 0, "b200_im2col: kernel larger than the padded image");
+  if (B == 0) return B200_OK;
+  B200_REQUIRE(e, x && col, "b200_im2col: null pointer");
+  DeviceGuard g(e);
+  int rc = flush_pending(e);
+  if (rc != B200_OK) return rc;
+  const int crs = (int)(C * kh * kw);
+  const long long total = B * Ho * Wo * crs;
+  if (dtype == B200_F32)
+    im2col_kernel<float, false><<<grid_for(e, total), 256, 0, e->stream>>>(
+        (const float *)x, (float *)col, nullptr, B, (int)C, (int)H, (int)W, (int)Ho, (int)Wo, kh, kw, pad_h, pad_w,
+        stride_h, stride_w, dil_h, dil_w, crs);
+  else
+    im2col_kernel<double, false><<<grid_for(e, total), 256, 0, e->stream>>>(
+        (const double *)x, (double *)col, nullptr, B, (int)C, (int)H, (int)W, (int)Ho, (int)Wo, kh, kw, pad_h, pad_w,
+        stride_h, stride_w, dil_h, dil_w, crs);
+  B200_CHECK_LAUNCH(e, "im2col_kernel");
+  return B200_OK;
+}
+
+int b200_transpose(b200_engine *e, int elem_bytes, const void *x, void *y, int ndim, const int64_t *shape,
+                   const int *perm) {
+  if (!e) return B200_ERR_INVALID;
+  std::lock_guard<std::recursive_mutex> lk(e->mu);
+  B200_REQUIRE(e, elem_bytes == 4 || elem_bytes == 8 || elem_bytes == 2, "b200_transpose: element size %d", elem_bytes);
+  B200_REQUIRE(e, ndim >= 1 && ndim <= 8 && shape && perm, "b200_transpose: bad rank or null shape");
+  long long in_stride[8], n = 1;
+  bool seen[8] = {false, false, false, false, false, false, false, false};
+  for (int d = ndim - 1; d >= 0; --d) {
+    B200_REQUIRE(e, shape[d] >= 0, "b200_transpose: negative extent");
+    in_stride[d] = n;
+    n *= shape[d];
+  }
+  for (int d = 0; d < ndim; ++d) {
+    B200_REQUIRE(e, perm[d] >= 0 && perm[d] < ndim && !seen[perm[d]], "b200_transpose: perm is not a permutation");
+    seen[perm[d]] = true;
+  }
+  if (n == 0) return B200_OK;
+  B200_REQUIRE(e, x && y, "b200_transpose: null pointer");
+  DeviceGuard g(e);
+  int rc = flush_pending(e);
+  if (rc != B200_OK) return rc;
+
+  // Collapse: drop axes of extent 1 and merge output axes that are adjacent in the input too.
+  long long oshape[8], ostride[8];
+  int m = 0;
+  for (int d = 0; d < ndim; ++d) {
+    const long long ext = shape[perm[d]], st = in_stride[perm[d]];
+    if (ext == 1) continue;
+    if (m > 0 && ostride[m - 1] == st * ext) {
+      oshape[m - 1] *= ext;
+      ostride[m - 1] = st;
+    } else {
+      oshape[m] = ext;
+      ostride[m] = st;
+      ++m;
+    }
+  }
+  if (m <= 1) {  // the permutation moves nothing
+    B200_CHECK_CUDA(e, cudaMemcpyAsync(y, x, (size_t)n * elem_bytes, cudaMemcpyDeviceToDevice, e->stream));
+    return B200_OK;
+  }
+  // batched 2-D form: output (b, c, r) reading input (b, r, c)
+  bool is2d = false;
+  long long Bt = 1, R = 0, Cc = 0;
+  if (m == 2 && ostride[1] == oshape[0] && ostride[0] == 1) {
+    is2d = true;
+    Cc = oshape[0];
+    R = oshape[1];
+  } else if (m == 3 && ostride[0] == oshape[1] * oshape[2] && ostride[2] == oshape[1] && ostride[1] == 1) {
+    is2d = true;
+    Bt = oshape[0];
+    Cc = oshape[1];
+    R = oshape[2];
+  }
+  if (is2d && Bt <= 65535 && (R + 31) / 32 <= 65535) {
+    dim3 grid((unsigned)((Cc + 31) / 32), (unsigned)((R + 31) / 32), (unsigned)Bt);
+    if (elem_bytes == 4)
+      transpose2d_kernel<uint32_t><<<grid, 256, 0, e->stream>>>((const uint32_t *)x, (uint32_t *)y, R, Cc);
+    else if (elem_bytes == 8)
+      transpose2d_kernel<uint64_t><<<grid, 256, 0, e->stream>>>((const uint64_t *)x, (uint64_t *)y, R, Cc);
+    else
+      transpose2d_kernel<uint16_t><<<grid, 256, 0, e->stream>>>((const uint16_t *)x, (uint16_t *)y, R, Cc);
+    B200_CHECK_LAUNCH(e, "transpose2d_kernel");
+    return B200_OK;
+  }
+  TransposeDesc d;
+  d.ndim = m;
+  for (int k = 0; k < m; ++k) {
+    d.out_shape[k] = oshape[k];
+    d.in_stride_of_out_dim[k] = ostride[k];
+  }
+  if (elem_bytes == 4)
+    transpose_kernel<uint32_t><<<grid_for(e, n), 256, 0, e->stream>>>((const uint32_t *)x, (uint32_t *)y, n, d);
+  else if (elem_bytes == 8)
+    transpose_kernel<uint64_t><<<grid_for(e, n), 256, 0, e->stream>>>((const uint64_t *)x, (uint64_t *)y, n, d);
+  else
+    transpose_kernel<uint16_t><<<grid_for(e, n), 256, 0, e->stream>>>((const uint16_t *)x, (uint16_t *)y, n, d);
+  B200_CHECK_LAUNCH(e, "transpose_kernel");
+  return B200_OK;
+}
+
+int b200_gather_rows(b200_engine *e, const void *x, const int64_t *idx, void *y, int64_t n_idx, int64_t row_bytes,
+                     int64_t n_rows) {
+  if (!e) return B200_ERR_INVALID;
+  std::lock_guard<std::recursive_mutex> lk(e->mu);
+  B200_REQUIRE(e, n_idx >= 0 && row_bytes >= 0 && n_rows >= 0, "b200_gather_rows: negative extent");
+  if (n_idx == 0 || row_bytes == 0) return B200_OK;
+  B200_REQUIRE(e, x && idx && y, "b200_gather_rows: null pointer");
+  DeviceGuard g(e);
+  int rc = flush_pending(e);
+  if (rc != B200_OK) return rc;
+  int *bad = e->d_flags + 3;
+  B200_CHECK_CUDA(e, cudaMemsetAsync(bad, 0, sizeof(int), e->stream));
+  const bool w16 = row_bytes % 16 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)y % 16 == 0;
+  const bool w4 = row_bytes % 4 == 0 && (uintptr_t)x % 4 == 0 && (uintptr_t)y % 4 == 0;
+  if (w16) {
+    const long long words = row_bytes / 16;
+    gather_rows_kernel<uint4><<<grid_for(e, n_idx * words), 256, 0, e->stream>>>(
+        (const uint4 *)x, (const long long *)idx, (uint4 *)y, n_idx, words, n_rows, bad);
+  } else if (w4) {
+    const long long words = row_bytes / 4;
+    gather_rows_kernel<uint32_t><<<grid_for(e, n_idx * words), 256, 0, e->stream>>>(
+        (const uint32_t *)x, (const long long *)idx, (uint32_t *)y, n_idx, words, n_rows, bad);
+  } else {
+    gather_rows_kernel<unsigned char><<<grid_for(e, n_idx * row_bytes), 256, 0, e->stream>>>(
+        (const unsigned char *)x, (const long long *)idx, (unsigned char *)y, n_idx, row_bytes, n_rows, bad);
+  }
+  B200_CHECK_LAUNCH(e, "gather_rows_kernel");
+  B200_CHECK_CUDA(e, cudaMemcpyAsync(e->h_flags + 3, bad, sizeof(int), cudaMemcpyDeviceToHost, e->stream));
+  B200_CHECK_CUDA(e, cudaStreamSynchronize(e->stream));
+  if (e->h_flags[3]) return set_error(e, B200_ERR_INVALID, "b200_gather_rows: an index lies outside [0, %lld)", (long long)n_rows);
+  return B200_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,426 @@
+// Softmax, axis reductions and argmax.
+//
+// Give gorgonia's softmaxOp (op_softmax.go:99-128 -> tensor.SoftMax / LogSoftMax), sumOp /
+// maxOp (op_reduction.go:70-99 -> tensor.Sum / tensor.Max) a device implementation; in the
+// reference they are CPU-only ops and force a device->host->device round trip. A tensor is
+// viewed as (outer, len, inner) around the reduced axis.
+//
+// Kernels
+//   rows (inner == 1, len <= 2048): one warp per row, the row held in registers, max and sum by
+//     warp shuffles, 128-bit loads when the row length allows. 10-class outputs (MLP, LeNet)
+//     pack several rows per warp-sized group of lanes instead of wasting 22 lanes out of 32.
+//   columns (inner > 1) and long rows: one thread per (outer, inner) column walking the axis
+//     with stride `inner` (coalesced across threads), or one CTA per row with a shared-memory
+//     tree for long rows.
+// Sums are pairwise (lane partials, then a butterfly), so their error grows with log(len).
+#include <algorithm>
+#include <cfloat>
+
+#include "engine.h"
+
+namespace b200 {
+
+template <typename T>
+__device__ __forceinline__ T neg_inf();
+template <>
+__device__ __forceinline__ float neg_inf<float>() {
+  return -INFINITY;
+}
+template <>
+__device__ __forceinline__ double neg_inf<double>() {
+  return -(double)INFINITY;
+}
+
+template <typename T>
+__device__ __forceinline__ T group_max(T v, int width) {
+  for (int o = width / 2; o > 0; o >>= 1) v = fmax(v, __shfl_xor_sync(0xffffffffu, v, o, width));
+  return v;
+}
+template <typename T>
+__device__ __forceinline__ T group_sum(T v, int width) {
+  for (int o = width / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o, width);
+  return v;
+}
+
+// mode: 0 softmax, 1 log-softmax, 2 sum, 3 max. A row of `len` contiguous elements is handled by
+// a group of G lanes (G = 32, or a smaller power of two for short rows); PER = elements per lane.
+template <typename T, int PER, int MODE>
+__global__ void __launch_bounds__(256) row_kernel(const T *__restrict__ x, T *__restrict__ y, long long rows,
+                                                  int len, int G) {
+  const int lane_in_group = threadIdx.x % G;
+  const int group_in_warp = (threadIdx.x & 31) / G;
+  const int groups_per_warp = 32 / G;
+  const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+  // all lanes of a warp run the same number of iterations (the shuffles below need every lane);
+  // a group whose row falls past the end computes on padding and stores nothing
+  for (long long r0 = warp * groups_per_warp; r0 < rows; r0 += nwarps * groups_per_warp) {
+    const long long r = r0 + group_in_warp;
+    const bool live = r < rows;
+    const T *xr = x + (live ? r : 0) * len;
+    T v[PER];
+    T mx = neg_inf<T>();
+#pragma unroll
+    for (int k = 0; k < PER; ++k) {
+      const int i = lane_in_group + k * G;
+      v[k] = (live && i < len) ? xr[i] : neg_inf<T>();
+      mx = fmax(mx, v[k]);
+    }
+    mx = group_max(mx, G);
+    if (MODE == 3) {
+      if (live && lane_in_group == 0) y[r] = mx;
+      continue;
+    }
+    T s = T(0);
+    if (MODE == 2) {
+#pragma unroll
+      for (int k = 0; k < PER; ++k) s += (live && lane_in_group + k * G < len) ? v[k] : T(0);
+      s = group_sum(s, G);
+      if (live && lane_in_group == 0) y[r] = s;
+      continue;
+    }
+    T ex[PER];
+#pragma unroll
+    for (int k = 0; k < PER; ++k) {
+      ex[k] = (live && lane_in_group + k * G < len) ? exp(v[k] - mx) : T(0);
+      s += ex[k];
+    }
+    s = group_sum(s, G);
+    if (!live) continue;
+    T *yr = y + r * len;
+    if (MODE == 0) {
+      const T inv = T(1) / s;
+#pragma unroll
+      for (int k = 0; k < PER; ++k) {
+        const int i = lane_in_group + k * G;
+        if (i < len) yr[i] = ex[k] * inv;
+      }
+    } else {
+      const T ls = log(s);
+#pragma unroll
+      for (int k = 0; k < PER; ++k) {
+        const int i = lane_in_group + k * G;
+        if (i < len) yr[i] = (v[k] - mx) - ls;
+      }
+    }
+  }
+}
+
+// One thread per (outer, inner) column; consecutive threads take consecutive `inner`, so each
+// step along the axis is a coalesced access. Sums use 4 interleaved partials.
+template <typename T, int MODE>
+__global__ void __launch_bounds__(256) col_kernel(const T *__restrict__ x, T *__restrict__ y, long long outer,
+                                                  long long len, long long inner) {
+  const long long total = outer * inner;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long c = (long long)blockIdx.x * blockDim.x + threadIdx.x; c < total; c += stride) {
+    const long long o = c / inner, in = c % inner;
+    const T *xp = x + o * len * inner + in;
+    T mx = neg_inf<T>();
+    if (MODE != 2)
+      for (long long k = 0; k < len; ++k) mx = fmax(mx, xp[k * inner]);
+    if (MODE == 3) {
+      y[c] = mx;
+      continue;
+    }
+    T p0 = 0, p1 = 0, p2 = 0, p3 = 0;
+    long long k = 0;
+    if (MODE == 2) {
+      for (; k + 3 < len; k += 4) {
+        p0 += xp[k * inner];
+        p1 += xp[(k + 1) * inner];
+        p2 += xp[(k + 2) * inner];
+        p3 += xp[(k + 3) * inner];
+      }
+      for (; k < len; ++k) p0 += xp[k * inner];
+      y[c] = (p0 + p1) + (p2 + p3);
+      continue;
+    }
+    for (; k + 3 < len; k += 4) {
+      p0 += exp(xp[k * inner] - mx);
+      p1 += exp(xp[(k + 1) * inner] - mx);
+      p2 += exp(xp[(k + 2) * inner] - mx);
+      p3 += exp(xp[(k + 3) * inner] - mx);
+    }
+    for (; k < len; ++k) p0 += exp(xp[k * inner] - mx);
+    const T s = (p0 + p1) + (p2 + p3);
+    T *yp = y + o * len * inner + in;
+    if (MODE == 0) {
+      const T inv = T(1) / s;
+      for (long long q = 0; q < len; ++q) yp[q * inner] = exp(xp[q * inner] - mx) * inv;
+    } else {
+      const T ls = log(s);
+      for (long long q = 0; q < len; ++q) yp[q * inner] = (xp[q * inner] - mx) - ls;
+    }
+  }
+}
+
+// Long rows (inner == 1, len > 2048): one CTA per row, shared-memory tree.
+template <typename T, int MODE>
+__global__ void __launch_bounds__(256) long_row_kernel(const T *__restrict__ x, T *__restrict__ y, long long rows,
+                                                       long long len) {
+  __shared__ T red[256 / 32];
+  __shared__ T bcast;
+  auto block_reduce = [&](T v, bool is_max) -> T {
+    v = is_max ? group_max(v, 32) : group_sum(v, 32);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+      T w = threadIdx.x < 256 / 32 ? red[threadIdx.x] : (is_max ? neg_inf<T>() : T(0));
+      w = is_max ? group_max(w, 32) : group_sum(w, 32);
+      if (threadIdx.x == 0) bcast = w;
+    }
+    __syncthreads();
+    const T r = bcast;
+    __syncthreads();
+    return r;
+  };
+  for (long long r = blockIdx.x; r < rows; r += gridDim.x) {
+    const T *xr = x + r * len;
+    T mx = neg_inf<T>();
+    if (MODE != 2) {
+      for (long long i = threadIdx.x; i < len; i += blockDim.x) mx = fmax(mx, xr[i]);
+      mx = block_reduce(mx, true);
+    }
+    if (MODE == 3) {
+      if (threadIdx.x == 0) y[r] = mx;
+      continue;
+    }
+    T s = 0;
+    for (long long i = threadIdx.x; i < len; i += blockDim.x) s += MODE == 2 ? xr[i] : exp(xr[i] - mx);
+    s = block_reduce(s, false);
+    if (MODE == 2) {
+      if (threadIdx.x == 0) y[r] = s;
+      continue;
+    }
+    T *yr = y + r * len;
+    const T inv = T(1) / s, ls = log(s);
+    for (long long i = threadIdx.x; i < len; i += blockDim.x)
+      yr[i] = MODE == 0 ? exp(xr[i] - mx) * inv : (xr[i] - mx) - ls;
+  }
+}
+
+// First maximum along the axis, as an int64 index (strict '>' keeps the earliest).
+template <typename T>
+__global__ void __launch_bounds__(256) argmax_kernel(const T *__restrict__ x, long long *__restrict__ y,
+                                                     long long outer, long long len, long long inner) {
+  const long long total = outer * inner;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long c = (long long)blockIdx.x * blockDim.x + threadIdx.x; c < total; c += stride) {
+    const long long o = c / inner, in = c % inner;
+    const T *xp = x + o * len * inner + in;
+    T m = xp[0];
+    long long arg = 0;
+    for (long long k = 1; k < len; ++k) {
+      const T v = xp[k * inner];
+      if (v > m) {
+        m = v;
+        arg = k;
+      }
+    }
+    y[c] = arg;
+  }
+}
+
+// Whole-tensor sum / max into one element. Every CTA reduces a grid-stride share and leaves its
+// partial in scratch memory; the CTA that takes the last ticket folds the partials in index
+// order (so the result does not depend on which CTA finished last) and re-arms the ticket.
+// scratch layout: [0, REDUCE_ALL_MAX_BLOCKS) partials of type T, then the ticket word.
+constexpr int REDUCE_ALL_MAX_BLOCKS = 1024;
+constexpr size_t REDUCE_ALL_TICKET_OFFSET = REDUCE_ALL_MAX_BLOCKS * sizeof(double);
+constexpr size_t REDUCE_ALL_SCRATCH_BYTES = REDUCE_ALL_TICKET_OFFSET + 256;
+
+template <typename T, bool IS_MAX>
+__global__ void __launch_bounds__(256) reduce_all_kernel(const T *__restrict__ x, long long n,
+                                                         unsigned char *__restrict__ scratch, T *__restrict__ y) {
+  T *partials = reinterpret_cast<T *>(scratch);
+  unsigned int *ticket = reinterpret_cast<unsigned int *>(scratch + REDUCE_ALL_TICKET_OFFSET);
+  __shared__ T red[256 / 32];
+  __shared__ bool is_last;
+  auto block_reduce = [&](T v) -> T {
+    v = IS_MAX ? group_max(v, 32) : group_sum(v, 32);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    T w = IS_MAX ? neg_inf<T>() : T(0);
+    if (threadIdx.x < 32) {
+      if (threadIdx.x < 256 / 32) w = red[threadIdx.x];
+      w = IS_MAX ? group_max(w, 32) : group_sum(w, 32);
+    }
+    __syncthreads();
+    return w;  // valid in thread 0
+  };
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  T p0 = IS_MAX ? neg_inf<T>() : T(0), p1 = p0, p2 = p0, p3 = p0;
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  for (; i + 3 * stride < n; i += 4 * stride) {
+    const T a = x[i], b = x[i + stride], c = x[i + 2 * stride], d = x[i + 3 * stride];
+    if (IS_MAX) {
+      p0 = fmax(p0, a); p1 = fmax(p1, b); p2 = fmax(p2, c); p3 = fmax(p3, d);
+    } else {
+      p0 += a; p1 += b; p2 += c; p3 += d;
+    }
+  }
+  for (; i < n; i += stride) p0 = IS_MAX ? fmax(p0, x[i]) : p0 + x[i];
+  T v = IS_MAX ? fmax(fmax(p0, p1), fmax(p2, p3)) : (p0 + p1) + (p2 + p3);
+  v = block_reduce(v);
+  if (threadIdx.x == 0) {
+    partials[blockIdx.x] = v;
+    __threadfence();
+    is_last = atomicAdd(ticket, 1u) == gridDim.x - 1;
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  // fold the partials: thread t takes partials t, t+256, ... in order, then the block tree
+  T w = IS_MAX ? neg_inf<T>() : T(0);
+  for (int b = threadIdx.x; b < (int)gridDim.x; b += blockDim.x) {
+    const T q = *reinterpret_cast<volatile T *>(&partials[b]);
+    w = IS_MAX ? fmax(w, q) : w + q;
+  }
+  w = block_reduce(w);
+  if (threadIdx.x == 0) {
+    y[0] = w;
+    *ticket = 0;  // ready for the next call
+  }
+}
+
+template <typename T>
+static int launch_reduce_all(b200_engine *e, int kind, const T *x, long long n, unsigned char *scratch, T *y) {
+  long long want = (n + 1023) / 1024;
+  want = std::min<long long>(want, (long long)e->sm_count * 4);
+  want = std::min<long long>(want, REDUCE_ALL_MAX_BLOCKS);
+  const int blocks = (int)std::max<long long>(1, want);
+  if (kind == 0)
+    reduce_all_kernel<T, false><<<blocks, 256, 0, e->stream>>>(x, n, scratch, y);
+  else
+    reduce_all_kernel<T, true><<<blocks, 256, 0, e->stream>>>(x, n, scratch, y);
+  B200_CHECK_LAUNCH(e, "reduce_all_kernel");
+  return B200_OK;
+}
+
+template <typename T, int MODE>
+static int launch_mode(b200_engine *e, const T *x, T *y, long long outer, long long len, long long inner) {
+  const int threads = 256;
+  const long long cap = (long long)e->sm_count * 8;
+  if (inner == 1 && len <= 2048) {
+    int G = 32;
+    while (G > 1 && G / 2 >= len) G /= 2;  // smallest power of two >= len, at most 32
+    const int per = (int)((len + G - 1) / G);
+    const long long groups_per_block = threads / G;
+    const int blocks = (int)std::max<long long>(1, std::min((outer + groups_per_block - 1) / groups_per_block, cap));
+#define B200_ROW(P)                                                                           \
+  row_kernel<T, P, MODE><<<blocks, threads, 0, e->stream>>>(x, y, outer, (int)len, G)
+    if (per <= 1) B200_ROW(1);
+    else if (per <= 2) B200_ROW(2);
+    else if (per <= 4) B200_ROW(4);
+    else if (per <= 8) B200_ROW(8);
+    else if (per <= 16) B200_ROW(16);
+    else if (per <= 32) B200_ROW(32);
+    else B200_ROW(64);
+#undef B200_ROW
+    B200_CHECK_LAUNCH(e, "row_kernel");
+  } else if (inner == 1) {
+    const int blocks = (int)std::max<long long>(1, std::min(outer, cap));
+    long_row_kernel<T, MODE><<<blocks, threads, 0, e->stream>>>(x, y, outer, len);
+    B200_CHECK_LAUNCH(e, "long_row_kernel");
+  } else {
+    const long long total = outer * inner;
+    const int blocks = (int)std::max<long long>(1, std::min((total + threads - 1) / threads, cap));
+    col_kernel<T, MODE><<<blocks, threads, 0, e->stream>>>(x, y, outer, len, inner);
+    B200_CHECK_LAUNCH(e, "col_kernel");
+  }
+  return B200_OK;
+}
+
+static int axis_op(b200_engine *e, int dtype, int mode, const void *x, void *y, int64_t outer, int64_t len,
+                   int64_t inner, const char *who) {
+  if (!e) return B200_ERR_INVALID;
+  std::lock_guard<std::recursive_mutex> lk(e->mu);
+  B200_REQUIRE(e, dtype == B200_F32 || dtype == B200_F64, "%s: dtype %d not supported", who, dtype);
+  B200_REQUIRE(e, outer >= 0 && len >= 0 && inner >= 0, "%s: negative extent", who);
+  if (outer == 0 || inner == 0) return B200_OK;
+  B200_REQUIRE(e, len > 0, "%s: cannot reduce an axis of length 0", who);
+  B200_REQUIRE(e, x && y, "%s: null pointer", who);
+  DeviceGuard g(e);
+  int rc = flush_pending(e);
+  if (rc != B200_OK) return rc;
+#define B200_MODE(T, M) return launch_mode<T, M>(e, (const T *)x, (T *)y, outer, len, inner)
+  if (dtype == B200_F32) {
+    switch (mode) {
+      case 0: B200_MODE(float, 0);
+      case 1: B200_MODE(float, 1);
+      case 2: B200_MODE(float, 2);
+      default: B200_MODE(float, 3);
+    }
+  }
+  switch (mode) {
+    case 0: B200_MODE(double, 0);
+    case 1: B200_MODE(double, 1);
+    case 2: B200_MODE(double, 2);
+    default: B200_MODE(double, 3);
+  }
+#undef B200_MODE
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" {
+
+int b200_softmax(b200_engine *e, int dtype, const void *x, void *y, int64_t outer, int64_t len, int64_t inner,
+                 int is_log) {
+  return axis_op(e, dtype, is_log ? 1 : 0, x, y, outer, len, inner, "b200_softmax");
+}
+
+int b200_reduce(b200_engine *e, int dtype, int kind, const void *x, void *y, int64_t outer, int64_t len,
+                int64_t inner) {
+  if (e && kind != 0 && kind != 1) {
+    std::lock_guard<std::recursive_mutex> lk(e->mu);
+    return set_error(e, B200_ERR_INVALID, "b200_reduce: kind %d (0 = sum, 1 = max)", kind);
+  }
+  return axis_op(e, dtype, kind == 0 ? 2 : 3, x, y, outer, len, inner, "b200_reduce");
+}
+
+int b200_reduce_all(b200_engine *e, int dtype, int kind, const void *x, int64_t n, void *y) {
+  if (!e) return B200_ERR_INVALID;
+  std::lock_guard<std::recursive_mutex> lk(e->mu);
+  B200_REQUIRE(e, dtype == B200_F32 || dtype == B200_F64, "b200_reduce_all: dtype %d not supported", dtype);
+  B200_REQUIRE(e, kind == 0 || kind == 1, "b200_reduce_all: kind %d (0 = sum, 1 = max)", kind);
+  B200_REQUIRE(e, n > 0, "b200_reduce_all: needs at least one element");
+  B200_REQUIRE(e, x && y, "b200_reduce_all: null pointer");
+  DeviceGuard g(e);
+  int rc = flush_pending(e);
+  if (rc != B200_OK) return rc;
+  if (!e->reduce_scratch) {
+    // once per engine; the ticket word must start at zero and every launch leaves it at zero
+    B200_CHECK_CUDA(e, cudaMalloc(&e->reduce_scratch, REDUCE_ALL_SCRATCH_BYTES));
+    B200_CHECK_CUDA(e, cudaMemsetAsync(e->reduce_scratch, 0, REDUCE_ALL_SCRATCH_BYTES, e->stream));
+  }
+  unsigned char *scratch = (unsigned char *)e->reduce_scratch;
+  if (dtype == B200_F32) return launch_reduce_all<float>(e, kind, (const float *)x, n, scratch, (float *)y);
+  return launch_reduce_all<double>(e, kind, (const double *)x, n, scratch, (double *)y);
+}
+
+int b200_argmax(b200_engine *e, int dtype, const void *x, int64_t *y, int64_t outer, int64_t len, int64_t inner) {
+  if (!e) return B200_ERR_INVALID;
+  std::lock_guard<std::recursive_mutex> lk(e->mu);
+  B200_REQUIRE(e, dtype == B200_F32 || dtype == B200_F64, "b200_argmax: dtype %d not supported", dtype);
+  B200_REQUIRE(e, outer >= 0 && len >= 0 && inner >= 0, "b200_argmax: negative extent");
+  if (outer == 0 || inner == 0) return B200_OK;
+  B200_REQUIRE(e, len > 0, "b200_argmax: cannot reduce an axis of length 0");
+  B200_REQUIRE(e, x && y, "b200_argmax: null pointer");
+  DeviceGuard g(e);
+  int rc = flush_pending(e);
+  if (rc != B200_OK) return rc;
+  const long long total = outer * inner;
+  const int blocks = (int)std::max<long long>(1, std::min<long long>((total + 255) / 256, (long long)e->sm_count * 8));
+  if (dtype == B200_F32)
+    argmax_kernel<float><<<blocks, 256, 0, e->stream>>>((const float *)x, (long long *)y, outer, len, inner);
+  else
+    argmax_kernel<double><<<blocks, 256, 0, e->stream>>>((const double *)x, (long long *)y, outer, len, inner);
+  B200_CHECK_LAUNCH(e, "argmax_kernel");
+  return B200_OK;
+}
+
+}  // extern "C"

@@ -18,6 +18,29 @@ from . import _lib
 from ._lib import B200Error, check, lib
 
 _DT = {np.dtype(np.float32): _lib.F32, np.dtype(np.float64): _lib.F64}
+BF16 = "bf16"  # dtype tag of bfloat16 tensors (held as uint16 on the host side)
+
+
+def to_bf16(a):
+    """float32 array -> bfloat16 bit patterns (uint16), round to nearest even."""
+    u = np.ascontiguousarray(a, dtype=np.float32).view(np.uint32)
+    r = ((u >> 16) & 1) + 0x7FFF
+    return ((u + r) >> 16).astype(np.uint16)
+
+
+def from_bf16(u16):
+    return (u16.astype(np.uint32) << 16).view(np.float32)
+
+
+def _epilogue(bias=None, bias_kind=None, act=None, alpha=0.0):
+    if bias is None and act is None:
+        return None
+    ep = _lib.Epilogue()
+    ep.bias_kind = 0 if bias is None else {"col": _lib.BIAS_COL, "row": _lib.BIAS_ROW}[bias_kind]
+    ep.bias = None if bias is None else bias.ptr
+    ep.act = {None: 0, "rectify": _lib.ACT_RECTIFY, "leaky": _lib.ACT_LEAKY}[act]
+    ep.alpha = alpha
+    return ep
 
 
 def dtype_code(dt):
@@ -234,6 +257,129 @@ class Engine:
         o = (C.c_void_p * len(outs))(*[t.ptr for t in outs])
         s = (C.c_void_p * max(len(srcs), 1))(*[t.ptr for t in srcs])
         check(lib.b200_pointwise(self.h, dtype_code(dtype), C.byref(p), o, s, int(n)), self.h)
+
+    # ---- linear algebra: Engine.MatMul / MatVecMul / Outer (cuda/linalg.go) ---------------------
+    def MatMul(self, a, b, prealloc, transA=False, transB=False, bias=None, bias_kind="col", act=None, alpha=0.0):
+        """prealloc = op(a) @ op(b). a, b are 2-D (or N-D with equal leading dims: batched, as
+        batchedMatMul, operatorLinAlg.go:435-502). bf16 operands (tensors made by tensor_bf16)
+        give a float32 result."""
+        bf = getattr(a, "is_bf16", False)
+        if bf != getattr(b, "is_bf16", False):
+            raise B200Error(_lib.ERR_INVALID, "MatMul: operand dtypes differ")
+        if not bf and a.dtype != b.dtype:
+            raise B200Error(_lib.ERR_INVALID, "MatMul: operand dtypes differ")
+        if len(a.shape) != len(b.shape) or len(a.shape) < 2 or a.shape[:-2] != b.shape[:-2]:
+            raise B200Error(_lib.ERR_INVALID, f"MatMul: shapes {a.shape} and {b.shape} do not match")
+        batch = 1
+        for d in a.shape[:-2]:
+            batch *= d
+        ar, ac = a.shape[-2:]
+        br, bc = b.shape[-2:]
+        M, K = (ac, ar) if transA else (ar, ac)
+        K2, N = (bc, br) if transB else (br, bc)
+        if K != K2:
+            raise B200Error(_lib.ERR_INVALID, f"MatMul: inner dimensions differ ({K} vs {K2})")
+        if prealloc.size != batch * M * N:
+            raise B200Error(_lib.ERR_INVALID, "MatMul: prealloc has the wrong size")
+        dt = _lib.BF16 if bf else dtype_code(a.dtype)
+        ep = _epilogue(bias, bias_kind, act, alpha)
+        check(lib.b200_gemm(self.h, dt, int(transA), int(transB), M, N, K, a.ptr, ac, b.ptr, bc, prealloc.ptr, N,
+                            batch, ar * ac, br * bc, M * N, C.byref(ep) if ep else None), self.h)
+        return prealloc
+
+    def gemm_path(self, a, b, c, transA=False, transB=False):
+        bf = getattr(a, "is_bf16", False)
+        ar, ac = a.shape[-2:]
+        br, bc = b.shape[-2:]
+        M, K = (ac, ar) if transA else (ar, ac)
+        N = br if transB else bc
+        return lib.b200_gemm_path(self.h, _lib.BF16 if bf else dtype_code(a.dtype), int(transA), int(transB), M, N, K,
+                                  ac, bc, N, a.ptr, b.ptr, c.ptr)
+
+    def MatVecMul(self, a, x, prealloc, transA=False):
+        M, N = a.shape
+        check(lib.b200_gemv(self.h, dtype_code(a.dtype), int(transA), M, N, a.ptr, N, x.ptr, prealloc.ptr), self.h)
+        return prealloc
+
+    def Outer(self, x, y, prealloc):
+        check(lib.b200_ger(self.h, dtype_code(x.dtype), x.size, y.size, x.ptr, y.ptr, prealloc.ptr), self.h)
+        return prealloc
+
+    def tensor_bf16(self, arr):
+        """Uploads a float32 array rounded to bfloat16."""
+        u = to_bf16(arr)
+        t = self.empty(u.shape, np.uint16).set(u)
+        t.is_bf16 = True
+        return t
+
+    # ---- softmax / reductions ---------------------------------------------------------------
+    @staticmethod
+    def _oli(shape, axis):
+        axis %= len(shape)
+        o = int(np.prod(shape[:axis], dtype=np.int64))
+        i = int(np.prod(shape[axis + 1:], dtype=np.int64))
+        return o, shape[axis], i, axis
+
+    def SoftMax(self, x, prealloc, axis=-1, log=False):
+        o, l, i, _ = self._oli(x.shape, axis)
+        check(lib.b200_softmax(self.h, dtype_code(x.dtype), x.ptr, prealloc.ptr, o, l, i, int(log)), self.h)
+        return prealloc
+
+    def Reduce(self, kind, x, prealloc, axis):
+        o, l, i, _ = self._oli(x.shape, axis)
+        check(lib.b200_reduce(self.h, dtype_code(x.dtype), {"sum": 0, "max": 1}[kind], x.ptr, prealloc.ptr, o, l, i),
+              self.h)
+        return prealloc
+
+    def ReduceAll(self, kind, x, prealloc):
+        check(lib.b200_reduce_all(self.h, dtype_code(x.dtype), {"sum": 0, "max": 1}[kind], x.ptr, x.size,
+                                  prealloc.ptr), self.h)
+        return prealloc
+
+    def Argmax(self, x, prealloc, axis):
+        o, l, i, _ = self._oli(x.shape, axis)
+        check(lib.b200_argmax(self.h, dtype_code(x.dtype), x.ptr, prealloc.ptr, o, l, i), self.h)
+        return prealloc
+
+    # ---- nn -----------------------------------------------------------------------------------
+    def Conv2d(self, x, w, prealloc, pad=(0, 0), stride=(1, 1), dil=(1, 1), bias=None, act=None, alpha=0.0):
+        B, Cc, H, W = x.shape
+        K, _, kh, kw = w.shape
+        ep = _epilogue(bias, "row", act, alpha)
+        check(lib.b200_conv2d_fwd(self.h, dtype_code(x.dtype), x.ptr, w.ptr, prealloc.ptr, B, Cc, H, W, K, kh, kw,
+                                  pad[0], pad[1], stride[0], stride[1], dil[0], dil[1],
+                                  C.byref(ep) if ep else None), self.h)
+        return prealloc
+
+    def Im2Col(self, x, prealloc, kernel, pad=(0, 0), stride=(1, 1), dil=(1, 1)):
+        B, Cc, H, W = x.shape
+        check(lib.b200_im2col(self.h, dtype_code(x.dtype), x.ptr, prealloc.ptr, B, Cc, H, W, kernel[0], kernel[1],
+                              pad[0], pad[1], stride[0], stride[1], dil[0], dil[1]), self.h)
+        return prealloc
+
+    def MaxPool2D(self, x, prealloc, kernel, pad, stride, mask=None):
+        """pad: (ph, pw), or (north, south, west, east) = gorgonia's explicit padding."""
+        B, Cc, H, W = x.shape
+        if len(pad) == 2:
+            pn, ps, pw, pe, explicit = pad[0], pad[0], pad[1], pad[1], 0
+        else:
+            pn, ps, pw, pe = pad
+            explicit = 1
+        check(lib.b200_maxpool2d_fwd(self.h, dtype_code(x.dtype), x.ptr, prealloc.ptr, mask.ptr if mask else None,
+                                     B, Cc, H, W, kernel[0], kernel[1], pn, ps, pw, pe, explicit, stride[0],
+                                     stride[1]), self.h)
+        return prealloc
+
+    def Transpose(self, x, prealloc, perm):
+        shape = (C.c_int64 * len(x.shape))(*x.shape)
+        pm = (C.c_int * len(perm))(*perm)
+        check(lib.b200_transpose(self.h, x.dtype.itemsize, x.ptr, prealloc.ptr, len(x.shape), shape, pm), self.h)
+        return prealloc
+
+    def ByIndices(self, x, idx, prealloc):
+        row = int(np.prod(x.shape[1:], dtype=np.int64)) * x.dtype.itemsize
+        check(lib.b200_gather_rows(self.h, x.ptr, idx.ptr, prealloc.ptr, idx.size, row, x.shape[0]), self.h)
+        return prealloc
 
     def HasNaN(self, t):
         r = C.c_int()

@@ -209,6 +209,92 @@ int b200_fusion_plan(const b200_pw_call *calls, int n_calls, const int *released
 int b200_has_nan(b200_engine *e, int dtype, const void *x, int64_t n, int *result);
 int b200_has_inf(b200_engine *e, int dtype, const void *x, int64_t n, int *result);
 
+/* ---- linear algebra -------------------------------------------------------------------------
+ * All matrices are row-major with a leading dimension (elements between consecutive rows).
+ *
+ * b200_gemm: Engine.MatMul (cuda/linalg.go:110-229; cuBLAS Sgemm/Dgemm in the reference) as
+ *   reached from linAlgBinOp.CUDADo (op_math_cuda.go:182-240), and batchedMatMul
+ *   (operatorLinAlg.go:435-502) in one launch. C[b] = op(A[b]) op(B[b]), alpha = 1, beta = 0;
+ *   op(A) is M x K, op(B) is K x N; transX != 0 means the stored matrix is the transpose
+ *   (K x M, resp. N x K). batch >= 1 matrices lie strideX elements apart.
+ *   dtype B200_F32: float32 in and out; large aligned problems run on the tensor cores as
+ *     3xTF32 (each operand split into a TF32 head and tail, three products, fp32 accumulate),
+ *     the rest on CUDA cores in fp32.
+ *   dtype B200_BF16: bfloat16 A and B, float32 C, fp32 accumulate on the tensor cores.
+ *   dtype B200_F64: CUDA cores.
+ *   `ep` (may be NULL) fuses a bias add and an activation into the store.
+ * b200_gemv: Engine.MatVecMul (cuda/linalg.go:47-107): y = A x, or y = A^T x with transA; A is
+ *   M x N as stored.
+ * b200_ger: Engine.Outer (cuda/linalg.go:232-285): A = x y^T, overwriting A (what tensor.Outer
+ *   with a reuse tensor does; the reference's cuBLAS path accumulates instead, for lack of a beta). */
+enum { B200_BIAS_NONE = 0, B200_BIAS_COL = 1, B200_BIAS_ROW = 2 };
+enum { B200_ACT_NONE = 0, B200_ACT_RECTIFY = 1, B200_ACT_LEAKY = 2 };
+typedef struct {
+  int32_t bias_kind;  /* B200_BIAS_*: COL = one value per output column (n), ROW = per row (m) */
+  int32_t act;        /* B200_ACT_*: Rectify x*(x>=0) (nn.go:136-163), LeakyRelu (nn.go:83-131) */
+  const void *bias;   /* device vector in the output dtype */
+  double alpha;       /* LeakyRelu slope */
+} b200_epilogue;
+int b200_gemm(b200_engine *e, int dtype, int transA, int transB, int64_t M, int64_t N, int64_t K,
+              const void *A, int64_t lda, const void *B, int64_t ldb, void *C, int64_t ldc,
+              int64_t batch, int64_t strideA, int64_t strideB, int64_t strideC,
+              const b200_epilogue *ep);
+int b200_gemv(b200_engine *e, int dtype, int transA, int64_t M, int64_t N, const void *A,
+              int64_t lda, const void *x, void *y);
+int b200_ger(b200_engine *e, int dtype, int64_t M, int64_t N, const void *x, const void *y, void *A);
+/* Which kernel b200_gemm would pick for a problem: 0 = CUDA cores, 1 = tensor cores.
+ * Needs no device work; lets tests assert that the tensor-core path is the one exercised. */
+int b200_gemm_path(b200_engine *e, int dtype, int transA, int transB, int64_t M, int64_t N, int64_t K,
+                   int64_t lda, int64_t ldb, int64_t ldc, const void *A, const void *B, const void *C);
+
+/* ---- softmax, reductions, argmax ----------------------------------------------------------
+ * A tensor is viewed as (outer, len, inner) around the axis that is reduced.
+ * b200_softmax: softmaxOp.Do -> tensor.SoftMax / LogSoftMax (op_softmax.go:99-128); y has x's shape.
+ * b200_reduce:  reductionDo -> tensor.Sum / tensor.Max along one axis (op_reduction.go:70-99);
+ *               kind 0 = sum, 1 = max; y has outer*inner elements.
+ * b200_reduce_all: the same ops over every axis at once (sumOp / maxOp with along = all axes);
+ *               y is one element on the device.
+ * b200_argmax:  index of the first maximum along the axis, as int64 (tensor.Argmax as used by
+ *               the examples' accuracy loops, examples/convnet/main.go). */
+int b200_softmax(b200_engine *e, int dtype, const void *x, void *y, int64_t outer, int64_t len,
+                 int64_t inner, int is_log);
+int b200_reduce(b200_engine *e, int dtype, int kind, const void *x, void *y, int64_t outer,
+                int64_t len, int64_t inner);
+int b200_reduce_all(b200_engine *e, int dtype, int kind, const void *x, int64_t n, void *y);
+int b200_argmax(b200_engine *e, int dtype, const void *x, int64_t *y, int64_t outer, int64_t len,
+                int64_t inner);
+
+/* ---- convolution, pooling, data movement ------------------------------------------------------
+ * Tensors are NCHW, dense.
+ * b200_conv2d_fwd: Conv2d (nn.go:211-305) as one call: x (B,C,H,W) * w (K,C,kh,kw) -> y (B,K,Ho,Wo),
+ *   Ho = (H + 2 pad_h - (dil_h (kh-1) + 1)) / stride_h + 1 (op_nn.go:311-315). The reference builds it
+ *   from Im2Col, Reshape, MatMul, Reshape, Transpose; float32 runs on the tensor cores (3xTF32).
+ *   `ep` (may be NULL): per-output-channel bias (B200_BIAS_ROW) and activation fused into the store.
+ * b200_im2col: im2colOp.do (op_nn.go:317-444): col (B, Ho, Wo, C*kh*kw), inner order channel, kernel
+ *   row, kernel column; taps outside the image are 0.
+ * b200_maxpool2d_fwd: maxPoolOp.do (op_nn.go:828-907). Output (H + pad_north + pad_south - kh) /
+ *   stride_h + 1 (op_nn.go:810-816). explicit_padding != 0 reproduces gorgonia's 4-value padding,
+ *   whose window origin uses the south / east pads (op_nn.go:870-875). mask (may be NULL) receives
+ *   the winning index inside the (H,W) plane as int64, -1 for an empty window.
+ * b200_transpose: transposeOp.Do -> tensor.Transpose (op_tensor.go:937-952): output axis d is input
+ *   axis perm[d]; elem_bytes 2, 4 or 8; rank <= 8.
+ * b200_gather_rows: byIndicesOp.Do -> tensor.ByIndices along axis 0 (op_by_indices.go:90-97):
+ *   y[i,:] = x[idx[i],:], idx int64 on the device. An index outside [0, n_rows) is an error
+ *   (checked on the device, reported by this call). */
+int b200_conv2d_fwd(b200_engine *e, int dtype, const void *x, const void *w, void *y, int64_t B,
+                    int64_t C, int64_t H, int64_t W, int64_t K, int kh, int kw, int pad_h, int pad_w,
+                    int stride_h, int stride_w, int dil_h, int dil_w, const b200_epilogue *ep);
+int b200_im2col(b200_engine *e, int dtype, const void *x, void *col, int64_t B, int64_t C, int64_t H,
+                int64_t W, int kh, int kw, int pad_h, int pad_w, int stride_h, int stride_w, int dil_h,
+                int dil_w);
+int b200_maxpool2d_fwd(b200_engine *e, int dtype, const void *x, void *y, int64_t *mask, int64_t B,
+                       int64_t C, int64_t H, int64_t W, int kh, int kw, int pad_north, int pad_south,
+                       int pad_west, int pad_east, int explicit_padding, int stride_h, int stride_w);
+int b200_transpose(b200_engine *e, int elem_bytes, const void *x, void *y, int ndim,
+                   const int64_t *shape, const int *perm);
+int b200_gather_rows(b200_engine *e, const void *x, const int64_t *idx, void *y, int64_t n_idx,
+                     int64_t row_bytes, int64_t n_rows);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,205 @@
+"""Parity of softmax, reductions, argmax, conv, im2col, max-pool, transpose and gather against the
+CPU oracle (GPU tests). Index-valued results (argmax, pool masks, gathers, transposes) are
+bit-exact; softmax is held to the pointwise tolerance, sums and convolutions to the GEMM one."""
+import numpy as np
+import pytest
+
+from oracle import oracle
+from tests import util
+from tests.util import assert_bits_equal, assert_gemm_close, assert_pointwise_close
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("dt", [np.float32, np.float64])
+@pytest.mark.parametrize("shape,axis", [((1, 1), 1), ((256, 10), 1), ((8192, 10), -1), ((7, 3), 1), ((33, 100), 1),
+                                        ((5, 1000), 1), ((3, 2048), 1), ((2, 5000), 1), ((10,), 0), ((6, 5, 4), 1),
+                                        ((64, 10, 13, 13), 1), ((300, 7), 0)])
+@pytest.mark.parametrize("log", [False, True])
+def test_softmax(fresh, shape, axis, log, dt):
+    e = fresh
+    x = util.normal(51, shape, dt, 2.0)
+    y = e.empty(shape, dt)
+    e.SoftMax(e.tensor(x), y, axis, log)
+    want = oracle.softmax(x, axis, log)
+    if dt == np.float32:
+        # the sum of `len` float32 terms carries log2(len) roundings (pairwise order)
+        assert_pointwise_close(y.numpy(), want, 2e-6 if not log else None if False else 2e-6)
+    else:
+        assert_pointwise_close(y.numpy(), want, 1e-13)
+
+
+def test_softmax_extremes(fresh):
+    e = fresh
+    x = np.array([[1000.0, 1000.0, -1000.0], [-1e30, 0.0, 1e30], [0.0, 0.0, 0.0]], dtype=np.float32)
+    y = e.empty(x.shape)
+    e.SoftMax(e.tensor(x), y)
+    assert_pointwise_close(y.numpy(), oracle.softmax(x))
+
+
+@pytest.mark.parametrize("dt", [np.float32, np.float64])
+@pytest.mark.parametrize("shape,axis", [((1, 1), 0), ((256, 10), 1), ((256, 10), 0), ((33, 1000), 1), ((4, 5000), 1),
+                                        ((6, 5, 4), 1), ((6, 5, 4), 0), ((2, 3, 4, 5), 2), ((100000,), 0)])
+def test_reduce_axis(fresh, shape, axis, dt):
+    e = fresh
+    x = util.normal(61, shape, dt)
+    out_shape = shape[:axis] + shape[axis + 1:]
+    for kind in ("sum", "max"):
+        y = e.empty(out_shape if out_shape else (1,), dt)
+        e.Reduce(kind, e.tensor(x), y, axis)
+        want = oracle.reduce(kind, x, axis)
+        got = y.numpy().reshape(want.shape)
+        if kind == "max":
+            assert_bits_equal(got, want)
+        else:
+            scale = np.abs(x).sum(axis=axis)   # a sum is judged against the magnitude it summed
+            assert np.all(np.abs(got.astype(np.float64) - want) <= (1e-6 if dt == np.float32 else 1e-14) * scale + 0)
+
+
+@pytest.mark.parametrize("dt", [np.float32, np.float64])
+@pytest.mark.parametrize("n", [1, 31, 1024, 1025, 100_003, 1 << 22])
+def test_reduce_all(fresh, n, dt):
+    e = fresh
+    x = util.normal(71, n, dt)
+    tx, y = e.tensor(x), e.empty(1, dt)
+    for _ in range(2):                      # twice: the ticket in scratch must re-arm itself
+        e.ReduceAll("sum", tx, y)
+        want = np.sum(x.astype(np.float64))
+        assert abs(float(y.numpy()[0]) - want) <= (1e-6 if dt == np.float32 else 1e-14) * np.abs(x).sum()
+        e.ReduceAll("max", tx, y)
+        assert y.numpy()[0] == x.max()
+
+
+def test_argmax_bit_exact(fresh):
+    e = fresh
+    x = util.normal(81, (4096, 10))
+    x[5] = 1.0                              # ties: the first maximum wins
+    x[6, 3] = x[6, 7] = 9.0
+    y = e.empty((4096,), np.int64)
+    e.Argmax(e.tensor(x), y, 1)
+    assert np.array_equal(y.numpy(), oracle.argmax(x, 1))
+    assert y.numpy()[5] == 0 and y.numpy()[6] == 3
+    x3 = util.normal(82, (7, 9, 11))
+    y3 = e.empty((7, 11), np.int64)
+    e.Argmax(e.tensor(x3), y3, 1)
+    assert np.array_equal(y3.numpy(), oracle.argmax(x3, 1))
+
+
+CONV_CASES = [
+    # B, C, H, W, K, kh, kw, pad, stride, dil
+    (2, 1, 28, 28, 32, 3, 3, (1, 1), (1, 1), (1, 1)),      # LeNet conv0 shape
+    (3, 32, 14, 14, 64, 3, 3, (1, 1), (1, 1), (1, 1)),     # LeNet conv1 shape
+    (2, 64, 7, 7, 128, 3, 3, (1, 1), (1, 1), (1, 1)),      # LeNet conv2 shape
+    (1, 3, 52, 52, 16, 3, 3, (1, 1), (1, 1), (1, 1)),      # YOLO first-layer shape, small image
+    (2, 8, 13, 13, 125, 1, 1, (0, 0), (1, 1), (1, 1)),     # YOLO head: 1x1
+    (2, 5, 17, 19, 7, 3, 5, (2, 1), (2, 3), (1, 1)),       # odd everything
+    (1, 4, 20, 20, 6, 3, 3, (2, 2), (1, 1), (2, 2)),       # dilation
+    (1, 2, 5, 5, 3, 3, 3, (0, 0), (1, 1), (1, 1)),         # tiny: CUDA-core path
+    (70, 3, 12, 12, 20, 3, 3, (1, 1), (1, 1), (1, 1)),     # more images than one scratch chunk holds? (small)
+]
+
+
+@pytest.mark.parametrize("case", CONV_CASES)
+def test_conv2d(fresh, case):
+    e = fresh
+    B, Cc, H, W, K, kh, kw, pad, stride, dil = case
+    x = util.uniform(91, (B, Cc, H, W))
+    w = util.normal(92, (K, Cc, kh, kw), scale=float(np.sqrt(2.0 / (Cc * kh * kw))))
+    want = oracle.conv2d(x, w, pad, stride, dil)
+    y = e.empty(want.shape)
+    e.Conv2d(e.tensor(x), e.tensor(w), y, pad, stride, dil)
+    assert_gemm_close(y.numpy(), want, 1e-5)
+    # fused bias + leaky relu equals oracle conv -> add -> LeakyRelu
+    bias = util.normal(93, K, scale=0.1)
+    e.Conv2d(e.tensor(x), e.tensor(w), y, pad, stride, dil, bias=e.tensor(bias), act="leaky", alpha=0.1)
+    want2 = oracle.leaky_relu((want + bias[None, :, None, None]).astype(np.float32), 0.1)
+    assert_gemm_close(y.numpy(), want2, 1e-5)
+
+
+def test_conv2d_matches_reference_pipeline(fresh):
+    # Conv2d as gorgonia spells it (nn.go:264-298): Im2Col -> MatMul(transB) -> Transpose(0,3,1,2)
+    e = fresh
+    B, Cc, H, W, K = 2, 3, 9, 8, 5
+    x, w = util.uniform(1, (B, Cc, H, W)), util.normal(2, (K, Cc, 3, 3))
+    tx, tw = e.tensor(x), e.tensor(w)
+    col = e.empty((B, H, W, Cc * 9))
+    e.Im2Col(tx, col, (3, 3), (1, 1))
+    assert_bits_equal(col.numpy(), oracle.im2col(x, 3, 3, (1, 1)))
+    prod = e.empty((B * H * W, K))
+    e.MatMul(col.reshape(B * H * W, Cc * 9), tw.reshape(K, Cc * 9), prod, transB=True)
+    out = e.empty((B, K, H, W))
+    e.Transpose(prod.reshape(B, H, W, K), out, (0, 3, 1, 2))
+    fused = e.empty((B, K, H, W))
+    e.Conv2d(tx, tw, fused, (1, 1))
+    assert_gemm_close(out.numpy(), oracle.conv2d(x, w, (1, 1)), 1e-5)
+    assert_gemm_close(fused.numpy(), out.numpy(), 1e-5)
+
+
+def test_im2col_variants(fresh):
+    e = fresh
+    for (B, Cc, H, W, kh, kw, pad, stride, dil) in [(2, 3, 7, 6, 3, 3, (1, 1), (1, 1), (1, 1)),
+                                                    (1, 2, 9, 9, 2, 4, (0, 2), (2, 1), (1, 1)),
+                                                    (2, 1, 10, 10, 3, 3, (2, 2), (1, 1), (2, 2))]:
+        x = util.normal(3, (B, Cc, H, W))
+        want = oracle.im2col(x, kh, kw, pad, stride, dil)
+        col = e.empty(want.shape)
+        e.Im2Col(e.tensor(x), col, (kh, kw), pad, stride, dil)
+        assert_bits_equal(col.numpy(), want)
+
+
+POOL_CASES = [
+    ((2, 3, 28, 28), (2, 2), (0, 0), (2, 2)),
+    ((2, 3, 7, 7), (2, 2), (0, 0), (2, 2)),            # 7 -> 3: the last row and column are dropped
+    ((1, 2, 13, 13), (2, 2), (1, 0, 1, 0), (1, 1)),    # tiny-YOLO's last pool: explicit padding, 13 -> 13
+    ((1, 1, 4, 4), (2, 2), (0, 0), (1, 1)),
+    ((2, 2, 9, 11), (3, 2), (1, 1), (2, 3)),
+    ((1, 1, 5, 5), (3, 3), (0, 1, 1, 0), (2, 2)),
+]
+
+
+@pytest.mark.parametrize("shape,kernel,pad,stride", POOL_CASES)
+def test_maxpool(fresh, shape, kernel, pad, stride):
+    e = fresh
+    x = util.normal(5, shape)
+    x[0, 0, 0, :2] = 3.0                    # a tie inside the first window
+    want, wmask = oracle.maxpool2d(x, kernel, pad, stride)
+    y, mask = e.empty(want.shape), e.empty(want.shape, np.int64)
+    e.MaxPool2D(e.tensor(x), y, kernel, pad, stride, mask=mask)
+    assert_bits_equal(y.numpy(), want)
+    assert np.array_equal(mask.numpy(), wmask)
+
+
+def test_maxpool_all_nan_window(fresh):
+    e = fresh
+    x = np.full((1, 1, 2, 2), np.nan, np.float32)
+    y = e.empty((1, 1, 1, 1))
+    e.MaxPool2D(e.tensor(x), y, (2, 2), (0, 0), (2, 2))
+    assert y.numpy().item() == -np.finfo(np.float32).max      # op_nn.go:862,890: nothing beats -MaxFloat32
+
+
+@pytest.mark.parametrize("dt", [np.float32, np.float64, np.int64])
+@pytest.mark.parametrize("shape,perm", [((3, 5), (1, 0)), ((2, 3, 4), (2, 0, 1)), ((4, 6, 5, 7), (0, 3, 1, 2)),
+                                        ((4, 6, 5, 7), (0, 2, 3, 1)), ((2, 3, 4, 5), (3, 2, 1, 0)),
+                                        ((100, 257), (1, 0)), ((1, 7, 1, 9), (3, 2, 1, 0)), ((6,), (0,)),
+                                        ((3, 4, 5), (0, 1, 2))])
+def test_transpose(fresh, shape, perm, dt):
+    e = fresh
+    x = (util.normal(6, shape, np.float64) * 100).astype(dt)
+    want = oracle.transpose(x, perm)
+    y = e.empty(want.shape, dt)
+    e.Transpose(e.tensor(x), y, perm)
+    assert np.array_equal(y.numpy(), want)
+    assert np.array_equal(want, np.transpose(x, perm))
+
+
+def test_by_indices(fresh):
+    from gorgonia_b200 import B200Error
+    e = fresh
+    for shape in [(10, 4), (33, 7), (5, 3, 2), (100,)]:
+        x = util.normal(7, shape)
+        idx = util.rng(8).integers(0, shape[0], size=17).astype(np.int64)
+        y = e.empty((17,) + shape[1:])
+        e.ByIndices(e.tensor(x), e.tensor(idx), y)
+        assert_bits_equal(y.numpy(), oracle.gather_rows(x, idx))
+    with pytest.raises(B200Error):
+        e.ByIndices(e.tensor(x), e.tensor(np.array([0, 100], np.int64)), e.empty((2,)))
