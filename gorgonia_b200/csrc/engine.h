@@ -54,9 +54,11 @@ int set_error(b200_engine *e, int code, const char *fmt, ...);
 #define B200_CHECK_CUDA(e, call)                                                       \
   do {                                                                                 \
     cudaError_t err__ = (call);                                                        \
-    if (err__ != cudaSuccess)                                                          \
+    if (err__ != cudaSuccess) {                                                        \
+      cudaGetLastError(); /* do not let it resurface at the next launch check */       \
       return b200::set_error((e), B200_ERR_CUDA, "%s failed: %s (%s:%d)", #call,       \
                              cudaGetErrorString(err__), __FILE__, __LINE__);           \
+    }                                                                                  \
   } while (0)
 
 #define B200_REQUIRE(e, cond, ...)                                       \

@@ -54,13 +54,19 @@ int gemm_simt(b200_engine *e, int dtype, int transA, int transB, long long M, lo
 //   K-major tile:  rows of 128 bytes, 8-row groups 1024 bytes apart  -> SBO = 1024, LBO unused (1)
 //   MN-major tile: blocks of (k rows x 128 bytes); 8-row k groups 1024 bytes apart -> SBO = 1024,
 //                  consecutive 128-byte-wide blocks along m/n `lbo_bytes` apart     -> LBO
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+//
+// 32-bit operands stored MN-major cannot use that swizzle: transposing 4-byte elements needs a
+// 32-byte swizzle atom. Their layout type is 1 ("128-byte swizzle, 32-byte base"): the pattern
+// repeats every 4 k-rows (512 bytes), so SBO = 512, and TMA writes it with
+// CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes,
+                                                   uint32_t layout_type) {
   uint64_t d = 0;
   d |= (uint64_t)((saddr >> 4) & 0x3FFF);
   d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
   d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
   d |= (uint64_t)1 << 46;
-  d |= (uint64_t)2 << 61;
+  d |= (uint64_t)layout_type << 61;
   return d;
 }
 
@@ -85,6 +91,7 @@ struct GemmTcParams {
   void *C;
   long long ldc, strideC;
   int tiles_m, tiles_n, num_k;  // num_k = k-blocks of BK elements
+  int chunk_k;                  // k-blocks accumulated in tensor memory before the epilogue folds them
   int group_m;                  // rasterisation: m-blocks per group
   int stages;
   int c_vec;                    // 1: rows of C can be stored with 128-bit stores
@@ -110,6 +117,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
   constexpr int MN_PER_BOX = TC_ROW_BYTES / ES;    // m/n elements covered by one MN-major box
   constexpr uint32_t IDESC = make_idesc(TERMS == 1 ? 1 : 2, A_MN, B_MN, TC_BM, BN);
   constexpr int MAX_STAGES = 8;
+  // TMEM columns of one accumulator buffer: 3xTF32 keeps the cross terms in a second accumulator
+  constexpr int ACC_COLS = TERMS == 1 ? BN : 2 * BN;
+  constexpr int TMEM_COLS = 2 * ACC_COLS;  // double-buffered; a power of two >= 32 for every BN used
 
   extern __shared__ __align__(1024) unsigned char tc_smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[MAX_STAGES], empty_bar[MAX_STAGES], acc_full[2], acc_empty[2];
@@ -136,7 +146,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
     s_fail = 0;
   }
   if (warp == 1) {
-    ptx::tmem_alloc(&tmem_base_s, 2 * BN >= 32 ? 2 * BN : 32);
+    ptx::tmem_alloc(&tmem_base_s, TMEM_COLS);
     ptx::tmem_relinquish();
   }
   if (warp == 0 && lane == 0) {
@@ -219,104 +229,160 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
-      int local = 0;
+      int use = 0;  // accumulator-buffer uses so far (one per k-chunk)
       bool ok = true;
-      for (long long tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
-        const int buf = local & 1;
-        const uint32_t acc_phase = (uint32_t)((local >> 1) & 1);
-        // the epilogue must have drained this accumulator buffer (first use passes at once)
-        if (!ptx::mbar_wait(&acc_empty[buf], acc_phase ^ 1)) {
-          ok = false;
-          break;
-        }
-        ptx::tc_fence_after_sync();
-        const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
-        for (int kb = 0; kb < p.num_k; ++kb) {
-          if (!ptx::mbar_wait(&full_bar[stage], phase)) {
+      for (long long tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        for (int kc = 0; kc < p.num_k && ok; kc += p.chunk_k, ++use) {
+          const int buf = use & 1;
+          const uint32_t acc_phase = (uint32_t)((use >> 1) & 1);
+          // the epilogue must have drained this accumulator buffer (first use passes at once)
+          if (!ptx::mbar_wait(&acc_empty[buf], acc_phase ^ 1)) {
             ok = false;
             break;
           }
           ptx::tc_fence_after_sync();
-          const uint32_t st = ptx::smem_addr(smem + (size_t)stage * STAGE_BYTES);
-#pragma unroll
-          for (int kk = 0; kk < BK / UK; ++kk) {
-            // k-slice kk: 32 bytes further along a K-major row, UK k-rows further in an MN-major block
-            const uint32_t a_off = A_MN ? kk * UK * TC_ROW_BYTES : kk * 32;
-            const uint32_t b_off = B_MN ? kk * UK * TC_ROW_BYTES : kk * 32;
-            const uint32_t a_lbo = A_MN ? BK * TC_ROW_BYTES : 16;
-            const uint32_t b_lbo = B_MN ? BK * TC_ROW_BYTES : 16;
-            uint64_t ad[NSPLIT], bd[NSPLIT];
-#pragma unroll
-            for (int h = 0; h < NSPLIT; ++h) {
-              ad[h] = make_smem_desc(st + h * A_BYTES + a_off, a_lbo, 1024);
-              bd[h] = make_smem_desc(st + NSPLIT * A_BYTES + h * B_BYTES + b_off, b_lbo, 1024);
+          const uint32_t d_main = tmem_base + (uint32_t)(buf * ACC_COLS);
+          const uint32_t d_tail = d_main + BN;  // 3xTF32 only: the small cross terms
+          const int kend = kc + p.chunk_k < p.num_k ? kc + p.chunk_k : p.num_k;
+          for (int kb = kc; kb < kend; ++kb) {
+            if (!ptx::mbar_wait(&full_bar[stage], phase)) {
+              ok = false;
+              break;
             }
-            const uint32_t first = (kb > 0 || kk > 0) ? 1u : 0u;
-            if (TERMS == 1) {
-              ptx::mma_f16(d_tmem, ad[0], bd[0], IDESC, first);
-            } else {
-              // smallest terms first: hi*lo, lo*hi, then hi*hi
-              ptx::mma_tf32(d_tmem, ad[0], bd[NSPLIT - 1], IDESC, first);
-              ptx::mma_tf32(d_tmem, ad[NSPLIT - 1], bd[0], IDESC, 1u);
-              ptx::mma_tf32(d_tmem, ad[0], bd[0], IDESC, 1u);
+            ptx::tc_fence_after_sync();
+            const uint32_t st = ptx::smem_addr(smem + (size_t)stage * STAGE_BYTES);
+#pragma unroll
+            for (int kk = 0; kk < BK / UK; ++kk) {
+              // k-slice kk: 32 bytes further along a K-major row, UK k-rows further in an MN-major block
+              const uint32_t a_off = A_MN ? kk * UK * TC_ROW_BYTES : kk * 32;
+              const uint32_t b_off = B_MN ? kk * UK * TC_ROW_BYTES : kk * 32;
+              const uint32_t a_lbo = A_MN ? BK * TC_ROW_BYTES : 16;
+              const uint32_t b_lbo = B_MN ? BK * TC_ROW_BYTES : 16;
+              uint64_t ad[NSPLIT], bd[NSPLIT];
+#pragma unroll
+              for (int h = 0; h < NSPLIT; ++h) {
+                ad[h] = make_smem_desc(st + h * A_BYTES + a_off, a_lbo, (A_MN && ES == 4) ? 512 : 1024,
+                                       (A_MN && ES == 4) ? 1 : 2);
+                bd[h] = make_smem_desc(st + NSPLIT * A_BYTES + h * B_BYTES + b_off, b_lbo,
+                                       (B_MN && ES == 4) ? 512 : 1024, (B_MN && ES == 4) ? 1 : 2);
+              }
+              const uint32_t accumulate = (kb > kc || kk > 0) ? 1u : 0u;
+              if (TERMS == 1) {
+                ptx::mma_f16(d_main, ad[0], bd[0], IDESC, accumulate);
+              } else {
+                ptx::mma_tf32(d_main, ad[0], bd[0], IDESC, accumulate);            // hi * hi
+                ptx::mma_tf32(d_tail, ad[0], bd[NSPLIT - 1], IDESC, accumulate);   // hi * lo
+                ptx::mma_tf32(d_tail, ad[NSPLIT - 1], bd[0], IDESC, 1u);           // lo * hi
+              }
+            }
+            ptx::mma_commit(&empty_bar[stage]);  // the stage is free once these MMAs have read it
+            if (++stage == stages) {
+              stage = 0;
+              phase ^= 1;
             }
           }
-          ptx::mma_commit(&empty_bar[stage]);  // the stage is free once these MMAs have read it
-          if (++stage == stages) {
-            stage = 0;
-            phase ^= 1;
-          }
+          if (ok) ptx::mma_commit(&acc_full[buf]);  // this chunk's accumulators are complete
         }
-        if (ok) ptx::mma_commit(&acc_full[buf]);  // accumulator complete
       }
       if (!ok) s_fail = 1;
     }
   } else {
     // ---------------- epilogue: warps 2..5 ----------------
     const int quarter = warp & 3;  // the TMEM lanes this warp may read: 32*quarter .. +31
-    int local = 0;
+    int use = 0;
     bool ok = true;
-    for (long long tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
+    for (long long tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
       int bz, mb, nb;
       decode(tile, bz, mb, nb);
-      const int buf = local & 1;
-      const uint32_t acc_phase = (uint32_t)((local >> 1) & 1);
-      if (!ptx::mbar_wait(&acc_full[buf], acc_phase)) {
-        ok = false;
-        break;
-      }
-      ptx::tc_fence_after_sync();
       const long long m = (long long)mb * TC_BM + quarter * 32 + lane;
       float *crow = reinterpret_cast<float *>(p.C) + (long long)bz * p.strideC + m * p.ldc;
       const long long n0 = (long long)nb * BN;
-#pragma unroll 1
-      for (int c = 0; c < BN; c += 32) {
-        uint32_t r[32];
-        ptx::tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + c), r);
-        ptx::tmem_ld_wait();
-        if (m < p.M) {
-          const long long nbase = n0 + c;
-          if (p.c_vec && nbase + 32 <= p.N) {
+      const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+
+      auto store32 = [&](const float(&v)[32], int c) {
+        if (m >= p.M) return;
+        const long long nbase = n0 + c;
+        if (p.c_vec && nbase + 32 <= p.N) {
 #pragma unroll
-            for (int j = 0; j < 32; j += 4) {
-              float4 o;
-              o.x = apply_epilogue<float>(__uint_as_float(r[j + 0]), p.ep, m, nbase + j + 0);
-              o.y = apply_epilogue<float>(__uint_as_float(r[j + 1]), p.ep, m, nbase + j + 1);
-              o.z = apply_epilogue<float>(__uint_as_float(r[j + 2]), p.ep, m, nbase + j + 2);
-              o.w = apply_epilogue<float>(__uint_as_float(r[j + 3]), p.ep, m, nbase + j + 3);
-              *reinterpret_cast<float4 *>(crow + nbase + j) = o;
-            }
-          } else {
+          for (int j = 0; j < 32; j += 4) {
+            float4 o;
+            o.x = apply_epilogue<float>(v[j + 0], p.ep, m, nbase + j + 0);
+            o.y = apply_epilogue<float>(v[j + 1], p.ep, m, nbase + j + 1);
+            o.z = apply_epilogue<float>(v[j + 2], p.ep, m, nbase + j + 2);
+            o.w = apply_epilogue<float>(v[j + 3], p.ep, m, nbase + j + 3);
+            *reinterpret_cast<float4 *>(crow + nbase + j) = o;
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (nbase + j < p.N) crow[nbase + j] = apply_epilogue<float>(v[j], p.ep, m, nbase + j);
+        }
+      };
+
+      if (TERMS == 1) {
+        // one chunk per tile: straight from tensor memory to C
+        const int buf = use & 1;
+        const uint32_t acc_phase = (uint32_t)((use >> 1) & 1);
+        ++use;
+        if (!ptx::mbar_wait(&acc_full[buf], acc_phase)) {
+          ok = false;
+          break;
+        }
+        ptx::tc_fence_after_sync();
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+          uint32_t r[32];
+          ptx::tmem_ld_32x32(lane_addr + (uint32_t)(buf * ACC_COLS + c), r);
+          ptx::tmem_ld_wait();
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+          store32(v, c);
+        }
+        ptx::tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(&acc_empty[buf]);
+      } else {
+        // 3xTF32: the tensor core adds into its accumulator with truncation, a bias that grows
+        // with the length of the accumulation chain. Chains are therefore cut into k-chunks; each
+        // chunk's two accumulators (main and cross terms) are folded here into fp32 registers
+        // with round-to-nearest adds while the next chunk is being multiplied.
+        float acc[TERMS == 3 ? BN : 1];
+#pragma unroll
+        for (int j = 0; j < (TERMS == 3 ? BN : 1); ++j) acc[j] = 0.f;
+        for (int kc = 0; kc < p.num_k && ok; kc += p.chunk_k) {
+          const int buf = use & 1;
+          const uint32_t acc_phase = (uint32_t)((use >> 1) & 1);
+          ++use;
+          if (!ptx::mbar_wait(&acc_full[buf], acc_phase)) {
+            ok = false;
+            break;
+          }
+          ptx::tc_fence_after_sync();
+#pragma unroll
+          for (int c = 0; c < (TERMS == 3 ? BN : 0); c += 32) {
+            uint32_t rm[32], rt[32];
+            ptx::tmem_ld_32x32(lane_addr + (uint32_t)(buf * ACC_COLS + c), rm);
+            ptx::tmem_ld_32x32(lane_addr + (uint32_t)(buf * ACC_COLS + BN + c), rt);
+            ptx::tmem_ld_wait();
 #pragma unroll
             for (int j = 0; j < 32; ++j)
-              if (nbase + j < p.N) crow[nbase + j] = apply_epilogue<float>(__uint_as_float(r[j]), p.ep, m, nbase + j);
+              acc[c + j] = __fadd_rn(acc[c + j], __fadd_rn(__uint_as_float(rm[j]), __uint_as_float(rt[j])));
+          }
+          ptx::tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(&acc_empty[buf]);
+        }
+        if (ok) {
+#pragma unroll
+          for (int c = 0; c < (TERMS == 3 ? BN : 0); c += 32) {
+            float v[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = acc[c + j];
+            store32(v, c);
           }
         }
       }
-      // hand the accumulator buffer back to the MMA issuer
-      ptx::tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(&acc_empty[buf]);
     }
     if (!ok) s_fail = 1;
   }
@@ -326,7 +392,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
   if (threadIdx.x == 0 && s_fail) atomicExch(p.err_flag, 1);
   if (warp == 1) {
     ptx::tc_fence_after_sync();
-    ptx::tmem_dealloc(tmem_base, 2 * BN >= 32 ? 2 * BN : 32);
+    ptx::tmem_dealloc(tmem_base, TMEM_COLS);
   }
 }
 
@@ -382,7 +448,8 @@ static EncodeTiledFn get_encode_fn() {
 
 // A 3-D map (contiguous dim, rows, batch) over a row-major matrix with `ld` elements per row.
 static int encode_map(b200_engine *e, CUtensorMap *map, int es, const void *base, long long inner, long long rows,
-                      long long batch, long long ld, long long batch_stride, int box_inner, int box_rows) {
+                      long long batch, long long ld, long long batch_stride, int box_inner, int box_rows,
+                      bool atom32 = false) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return set_error(e, B200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
   cuuint64_t dims[3] = {(cuuint64_t)inner, (cuuint64_t)rows, (cuuint64_t)batch};
@@ -391,7 +458,8 @@ static int encode_map(b200_engine *e, CUtensorMap *map, int es, const void *base
   cuuint32_t estr[3] = {1, 1, 1};
   CUresult r = fn(map, es == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3,
                   const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                  atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS)
     return set_error(e, B200_ERR_CUDA,
                      "cuTensorMapEncodeTiled failed (%d): dims %lld x %lld x %lld, ld %lld, box %d x %d", (int)r,
@@ -429,8 +497,12 @@ static int launch_tc(b200_engine *e, const CUtensorMap *tm, const GemmTcParams &
   const size_t smem = (size_t)p.stages * STAGE_BYTES + 1024;
   static int attr_dev_mask = 0;
   if (!(attr_dev_mask & (1 << (e->device & 31)))) {
+    // opt in to the large dynamic carve-out: what the SM offers minus this kernel's static part
+    cudaFuncAttributes fa;
+    B200_CHECK_CUDA(e, cudaFuncGetAttributes(&fa, kern));
+    const size_t optin = std::min<size_t>(e->smem_optin, 227 * 1024);
     B200_CHECK_CUDA(e, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                            (int)std::min<size_t>(e->smem_optin, 227 * 1024)));
+                                            (int)(optin - fa.sharedSizeBytes)));
     attr_dev_mask |= 1 << (e->device & 31);
   }
   kern<<<grid, TC_THREADS, smem, e->stream>>>(tm[0], tm[1], tm[2], tm[3], p);
@@ -473,12 +545,12 @@ int gemm_tc_core(b200_engine *e, int terms, bool a_mn, bool b_mn, long long M, l
     if (!a_mn)
       rc = encode_map(e, &tm[h], es, ap, K, M, a_batch, a.ld, a.batch_stride, bk, TC_BM);
     else
-      rc = encode_map(e, &tm[h], es, ap, M, K, a_batch, a.ld, a.batch_stride, mn_box, bk);
+      rc = encode_map(e, &tm[h], es, ap, M, K, a_batch, a.ld, a.batch_stride, mn_box, bk, es == 4);
     if (rc != B200_OK) return rc;
     if (!b_mn)
       rc = encode_map(e, &tm[2 + h], es, bp, K, N, b_batch, b.ld, b.batch_stride, bk, bn);
     else
-      rc = encode_map(e, &tm[2 + h], es, bp, N, K, b_batch, b.ld, b.batch_stride, mn_box, bk);
+      rc = encode_map(e, &tm[2 + h], es, bp, N, K, b_batch, b.ld, b.batch_stride, mn_box, bk, es == 4);
     if (rc != B200_OK) return rc;
   }
   if (terms == 1) {
@@ -497,6 +569,9 @@ int gemm_tc_core(b200_engine *e, int terms, bool a_mn, bool b_mn, long long M, l
   p.tiles_m = tiles_m;
   p.tiles_n = tiles_n;
   p.num_k = (int)((K + bk - 1) / bk);
+  // bf16: one chain per tile. 3xTF32: 8 k-blocks = 256 k = 32 accumulation steps per chain, which
+  // keeps the truncation bias of the tensor core's adder near 5e-7 relative.
+  p.chunk_k = terms == 1 ? p.num_k : 8;
   p.group_m = std::min(tiles_m, 8);
   p.c_vec = (ldc % 4 == 0 && (uintptr_t)C % 16 == 0 && (batch == 1 || strideC % 4 == 0)) ? 1 : 0;
   p.a_zmul = a.shared ? 0 : 1;
@@ -505,7 +580,7 @@ int gemm_tc_core(b200_engine *e, int terms, bool a_mn, bool b_mn, long long M, l
   p.err_flag = e->d_flags + 2;
   const int nsplit = terms == 1 ? 1 : 2;
   const size_t stage_bytes = (size_t)nsplit * (TC_BM + bn) * TC_ROW_BYTES;
-  const size_t budget = std::min<size_t>(e->smem_optin, 227 * 1024) - 2048;
+  const size_t budget = std::min<size_t>(e->smem_optin, 227 * 1024) - 4096;  // static part + alignment slack
   p.stages = (int)std::max<size_t>(2, std::min<size_t>(8, budget / stage_bytes));
   const long long total_tiles = (long long)tiles_m * tiles_n * batch;
   const int grid = (int)std::min<long long>(total_tiles, e->sm_count);

@@ -38,7 +38,7 @@ def test_matmul_f32_tensor_core_path(fresh, shape, transA, transB):
 
 
 @pytest.mark.parametrize("transA,transB", [(False, False), (False, True), (True, False), (True, True)])
-@pytest.mark.parametrize("shape", [(128, 256, 64), (512, 512, 512), (300, 264, 200), (1024, 2048, 768)])
+@pytest.mark.parametrize("shape", [(128, 256, 64), (512, 512, 512), (304, 264, 200), (1024, 2048, 768)])
 def test_matmul_bf16(fresh, shape, transA, transB):
     e = fresh
     M, N, K = shape
@@ -51,6 +51,17 @@ def test_matmul_bf16(fresh, shape, transA, transB):
     assert_gemm_close(tc.numpy(), want, 1e-2)
     # bf16 products are exact in fp32 and the accumulator is fp32: far inside the bf16 budget
     assert_gemm_close(tc.numpy(), want, 1e-4)
+
+
+def test_matmul_bf16_unaligned_pitch_is_refused(fresh):
+    # TMA reads bf16 operands in place: a row pitch that is not a multiple of 16 bytes is an error,
+    # not a silent detour through another kernel
+    from gorgonia_b200 import B200Error
+    e = fresh
+    a, b = _mats(1, 128, 128, 100, False, False)       # pitch of A = 100 * 2 bytes
+    with pytest.raises(B200Error) as ei:
+        e.MatMul(e.tensor_bf16(a), e.tensor_bf16(b), e.empty((128, 128)))
+    assert ei.value.code == 4
 
 
 def test_matmul_large_k_accuracy(fresh):
