@@ -139,6 +139,7 @@ _SIGS = {
     "b200_softmax": (_i, [_vp, _i, _vp, _vp, _i64, _i64, _i64, _i]),
     "b200_reduce": (_i, [_vp, _i, _i, _vp, _vp, _i64, _i64, _i64]),
     "b200_reduce_all": (_i, [_vp, _i, _i, _vp, _i64, _vp]),
+    "b200_reduce_all_static": (_i, [_vp, _i, _i, _vp, _i64, _vp]),
     "b200_argmax": (_i, [_vp, _i, _vp, _vp, _i64, _i64, _i64]),
     "b200_conv2d_fwd": (_i, [_vp, _i, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _i, _i, _i, _i, _i,
                              _P(Epilogue)]),

@@ -15,6 +15,7 @@
 // Sums are pairwise (lane partials, then a butterfly), so their error grows with log(len).
 #include <algorithm>
 #include <cfloat>
+#include <mutex>
 
 #include "engine.h"
 
@@ -298,6 +299,32 @@ static int launch_reduce_all(b200_engine *e, int kind, const T *x, long long n, 
   return B200_OK;
 }
 
+// ---- whole-tensor reduction that allocates nothing ---------------------------------------------
+// Scratch for b200_reduce_all_static: a fixed array that lives in the library image, one copy on
+// every GPU that loads the library, held until the process exits. Layout as above, for at most
+// REDUCE_STATIC_MAX_BLOCKS partials. In HOST code the name of this array is only a handle for
+// cudaGetSymbolAddress; it is never a device address and is never passed to a kernel.
+constexpr int REDUCE_STATIC_MAX_BLOCKS = 256;
+constexpr size_t REDUCE_STATIC_TICKET_OFFSET = REDUCE_ALL_TICKET_OFFSET;  // the kernel's fixed layout
+static __device__ __align__(256) unsigned char g_reduce_static_scratch[REDUCE_ALL_SCRATCH_BYTES];
+
+// Device address of the array on each device, looked up once per device with that device current.
+static unsigned char *g_reduce_static_ptr[64];
+static std::mutex g_reduce_static_mu;
+
+static int reduce_static_scratch(b200_engine *e, unsigned char **out) {
+  const int dev = e->device;
+  if (dev < 0 || dev >= 64) return set_error(e, B200_ERR_UNSUPPORTED, "b200_reduce_all_static: device %d", dev);
+  std::lock_guard<std::mutex> lk(g_reduce_static_mu);
+  if (!g_reduce_static_ptr[dev]) {
+    void *ptr = nullptr;
+    B200_CHECK_CUDA(e, cudaGetSymbolAddress(&ptr, g_reduce_static_scratch));
+    g_reduce_static_ptr[dev] = (unsigned char *)ptr;
+  }
+  *out = g_reduce_static_ptr[dev];
+  return B200_OK;
+}
+
 template <typename T, int MODE>
 static int launch_mode(b200_engine *e, const T *x, T *y, long long outer, long long len, long long inner) {
   const int threads = 256;
@@ -400,6 +427,44 @@ int b200_reduce_all(b200_engine *e, int dtype, int kind, const void *x, int64_t 
   unsigned char *scratch = (unsigned char *)e->reduce_scratch;
   if (dtype == B200_F32) return launch_reduce_all<float>(e, kind, (const float *)x, n, scratch, (float *)y);
   return launch_reduce_all<double>(e, kind, (const double *)x, n, scratch, (double *)y);
+}
+
+int b200_reduce_all_static(b200_engine *e, int dtype, int kind, const void *x, int64_t n, void *y) {
+  if (!e) return B200_ERR_INVALID;
+  std::lock_guard<std::recursive_mutex> lk(e->mu);
+  B200_REQUIRE(e, dtype == B200_F32 || dtype == B200_F64, "b200_reduce_all_static: dtype %d not supported", dtype);
+  B200_REQUIRE(e, kind == 0 || kind == 1, "b200_reduce_all_static: kind %d (0 = sum, 1 = max)", kind);
+  B200_REQUIRE(e, n > 0, "b200_reduce_all_static: needs at least one element");
+  if (n > B200_REDUCE_ALL_STATIC_MAX_N)
+    return set_error(e, B200_ERR_UNSUPPORTED,
+                     "b200_reduce_all_static: %lld elements exceed the limit of %lld that its fixed scratch is "
+                     "sized for; use b200_reduce_all",
+                     (long long)n, (long long)B200_REDUCE_ALL_STATIC_MAX_N);
+  B200_REQUIRE(e, x && y, "b200_reduce_all_static: null pointer");
+  DeviceGuard g(e);
+  int rc = flush_pending(e);
+  if (rc != B200_OK) return rc;
+  unsigned char *scratch = nullptr;
+  rc = reduce_static_scratch(e, &scratch);  // first call on this device: looks the address up
+  if (rc != B200_OK) return rc;
+  // the array keeps whatever the previous call (or an aborted one) left: the ticket must be zero
+  B200_CHECK_CUDA(e, cudaMemsetAsync(scratch + REDUCE_STATIC_TICKET_OFFSET, 0, sizeof(unsigned int), e->stream));
+  long long want = (n + 1023) / 1024;
+  want = std::min<long long>(want, REDUCE_STATIC_MAX_BLOCKS);
+  const int blocks = (int)std::max<long long>(1, want);
+  if (dtype == B200_F32) {
+    if (kind == 0)
+      reduce_all_kernel<float, false><<<blocks, 256, 0, e->stream>>>((const float *)x, n, scratch, (float *)y);
+    else
+      reduce_all_kernel<float, true><<<blocks, 256, 0, e->stream>>>((const float *)x, n, scratch, (float *)y);
+  } else {
+    if (kind == 0)
+      reduce_all_kernel<double, false><<<blocks, 256, 0, e->stream>>>((const double *)x, n, scratch, (double *)y);
+    else
+      reduce_all_kernel<double, true><<<blocks, 256, 0, e->stream>>>((const double *)x, n, scratch, (double *)y);
+  }
+  B200_CHECK_LAUNCH(e, "reduce_all_kernel");
+  return B200_OK;
 }
 
 int b200_argmax(b200_engine *e, int dtype, const void *x, int64_t *y, int64_t outer, int64_t len, int64_t inner) {

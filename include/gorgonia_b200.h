@@ -264,6 +264,29 @@ int b200_reduce_all(b200_engine *e, int dtype, int kind, const void *x, int64_t 
 int b200_argmax(b200_engine *e, int dtype, const void *x, int64_t *y, int64_t outer, int64_t len,
                 int64_t inner);
 
+/* b200_reduce_all for callers that must not allocate. It has no counterpart in gorgonia.
+ *
+ * Who needs it: code that runs where device allocation is off limits once set-up is over, e.g. a
+ * serving loop that has handed all free device memory to its own pools, a host thread that must
+ * not take the driver's allocation lock on its latency path, or a process whose memory budget is
+ * fixed at start-up. b200_reduce_all reserves its scratch (per-CTA partial results and a ticket
+ * word) with cudaMalloc on its first call per engine; this entry point keeps the same scratch in
+ * a fixed array inside the library image instead, so it calls no cudaMalloc, no cudaFree and no
+ * allocating library routine, ever. The cost: that array (8448 bytes) sits on every GPU that
+ * loads the library until the process exits.
+ *
+ * Same arguments and result as b200_reduce_all (kind 0 = sum, 1 = max; y is one element on the
+ * device, written on the engine's stream), with these limits:
+ *   - at most B200_REDUCE_ALL_STATIC_MAX_N elements; more is refused with B200_ERR_UNSUPPORTED;
+ *   - the first call on each device looks up the array's device address (cudaGetSymbolAddress):
+ *     make that first call before any stream capture begins;
+ *   - all calls on one GPU share the one array, whatever engine they come through. Two calls
+ *     whose kernels overlap on the GPU (different engines, i.e. different streams) race on it and
+ *     both results are undefined; calls through one engine are ordered by its stream and safe.
+ *     The array keeps the last call's contents; each call clears the word that must start at zero. */
+#define B200_REDUCE_ALL_STATIC_MAX_N ((int64_t)1 << 32)
+int b200_reduce_all_static(b200_engine *e, int dtype, int kind, const void *x, int64_t n, void *y);
+
 /* ---- convolution, pooling, data movement ------------------------------------------------------
  * Tensors are NCHW, dense.
  * b200_conv2d_fwd: Conv2d (nn.go:211-305) as one call: x (B,C,H,W) * w (K,C,kh,kw) -> y (B,K,Ho,Wo),
