@@ -101,6 +101,10 @@ _SIGS = {
     "b200_flush": (_i, [_vp]),
     "b200_sync": (_i, [_vp]),
     "b200_launch_count": (C.c_uint64, [_vp]),
+    "b200_tape_begin": (_i, [_vp]),
+    "b200_tape_end": (_i, [_vp, _P(_vp)]),
+    "b200_tape_launch": (_i, [_vp, _vp]),
+    "b200_tape_destroy": (_i, [_vp, _vp]),
     "b200_event_create": (_i, [_vp, _P(_vp)]),
     "b200_event_record": (_i, [_vp, _vp]),
     "b200_event_elapsed_ms": (_i, [_vp, _vp, _vp, _P(C.c_float)]),

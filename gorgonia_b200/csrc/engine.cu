@@ -139,6 +139,7 @@ int b200_flush(b200_engine *e) {
 int b200_sync(b200_engine *e) {
   if (!e) return B200_ERR_INVALID;
   std::lock_guard<std::recursive_mutex> lk(e->mu);
+  B200_NOT_WHILE_CAPTURING(e, "b200_sync");
   DeviceGuard g(e);
   int rc = flush_pending(e);
   if (rc != B200_OK) return rc;
@@ -157,6 +158,88 @@ int b200_sync(b200_engine *e) {
     return B200_OK;
   }
   B200_CHECK_CUDA(e, cudaStreamSynchronize(e->stream));
+  return B200_OK;
+}
+
+/* ---- tapes: a recorded sequence of engine calls replayed with one call ---- */
+
+struct b200_tape {
+  cudaGraph_t graph = nullptr;
+  cudaGraphExec_t exec = nullptr;
+  uint64_t launches = 0;  // kernels recorded, so that replays keep the launch counter honest
+};
+
+int b200_tape_begin(b200_engine *e) {
+  if (!e) return B200_ERR_INVALID;
+  std::lock_guard<std::recursive_mutex> lk(e->mu);
+  if (e->capturing) return set_error(e, B200_ERR_STATE, "b200_tape_begin: a tape is already being recorded");
+  DeviceGuard g(e);
+  int rc = flush_pending(e);
+  if (rc != B200_OK) return rc;
+  B200_CHECK_CUDA(e, cudaStreamBeginCapture(e->stream, cudaStreamCaptureModeRelaxed));
+  e->capturing = true;
+  e->capture_launch_base = e->launches;
+  return B200_OK;
+}
+
+int b200_tape_end(b200_engine *e, b200_tape **out) {
+  if (!e) return B200_ERR_INVALID;
+  std::lock_guard<std::recursive_mutex> lk(e->mu);
+  if (!e->capturing) return set_error(e, B200_ERR_STATE, "b200_tape_end: no tape is being recorded");
+  B200_REQUIRE(e, out != nullptr, "b200_tape_end: out is null");
+  *out = nullptr;
+  DeviceGuard g(e);
+  int rc = flush_pending(e);  // queued pointwise calls belong to the tape
+  cudaGraph_t graph = nullptr;
+  cudaError_t ce = cudaStreamEndCapture(e->stream, &graph);
+  e->capturing = false;
+  if (rc != B200_OK) {
+    if (graph) cudaGraphDestroy(graph);
+    return rc;
+  }
+  if (ce != cudaSuccess) {
+    cudaGetLastError();
+    return set_error(e, B200_ERR_CUDA, "cudaStreamEndCapture failed: %s", cudaGetErrorString(ce));
+  }
+  b200_tape *t = new b200_tape();
+  t->graph = graph;
+  t->launches = e->launches - e->capture_launch_base;
+  e->launches = e->capture_launch_base;  // nothing ran yet
+  ce = cudaGraphInstantiate(&t->exec, graph, 0);
+  if (ce != cudaSuccess) {
+    cudaGetLastError();
+    cudaGraphDestroy(graph);
+    delete t;
+    return set_error(e, B200_ERR_CUDA, "cudaGraphInstantiate failed: %s", cudaGetErrorString(ce));
+  }
+  *out = t;
+  return B200_OK;
+}
+
+int b200_tape_launch(b200_engine *e, b200_tape *t) {
+  if (!e) return B200_ERR_INVALID;
+  std::lock_guard<std::recursive_mutex> lk(e->mu);
+  B200_REQUIRE(e, t && t->exec, "b200_tape_launch: null tape");
+  if (e->capturing) return set_error(e, B200_ERR_STATE, "b200_tape_launch: a tape is being recorded");
+  DeviceGuard g(e);
+  int rc = flush_pending(e);
+  if (rc != B200_OK) return rc;
+  B200_CHECK_CUDA(e, cudaGraphLaunch(t->exec, e->stream));
+  e->launches += t->launches;
+  e->flags_dirty = true;
+  return B200_OK;
+}
+
+int b200_tape_destroy(b200_engine *e, b200_tape *t) {
+  if (!t) return B200_OK;
+  if (e) {
+    std::lock_guard<std::recursive_mutex> lk(e->mu);
+    DeviceGuard g(e);
+    cudaStreamSynchronize(e->stream);
+    if (t->exec) cudaGraphExecDestroy(t->exec);
+    if (t->graph) cudaGraphDestroy(t->graph);
+  }
+  delete t;
   return B200_OK;
 }
 
@@ -291,6 +374,7 @@ static int copy_common(b200_engine *e, void *dst, const void *src, int64_t bytes
   B200_REQUIRE(e, bytes >= 0, "%s: negative size", who);
   if (bytes == 0) return B200_OK;
   B200_REQUIRE(e, dst && src, "%s: null pointer", who);
+  if (wait) B200_NOT_WHILE_CAPTURING(e, who);
   DeviceGuard g(e);
   int rc = flush_pending(e);
   if (rc != B200_OK) return rc;

@@ -40,7 +40,9 @@ struct b200_engine {
   void *gemm_state = nullptr;
   void (*gemm_state_free)(void *) = nullptr;
 
+  bool capturing = false;   // between b200_tape_begin and b200_tape_end
   uint64_t launches = 0;
+  uint64_t capture_launch_base = 0;
   std::string last_error;
   std::recursive_mutex mu;
 };
@@ -97,6 +99,14 @@ inline size_t dtype_size(int dtype) {
     default: return 0;
   }
 }
+
+// Entry points that must wait for the device cannot run while a tape is being recorded.
+#define B200_NOT_WHILE_CAPTURING(e, who)                                                          \
+  do {                                                                                            \
+    if ((e)->capturing)                                                                           \
+      return b200::set_error((e), B200_ERR_STATE, "%s waits for the device and cannot be recorded " \
+                             "into a tape", (who));                                               \
+  } while (0)
 
 // implemented in pointwise.cu
 int flush_pending(b200_engine *e);

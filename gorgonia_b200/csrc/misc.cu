@@ -28,6 +28,7 @@ static int has_special(b200_engine *e, int dtype, const void *x, int64_t n, int 
   B200_REQUIRE(e, n >= 0, "%s: negative element count", who);
   if (n == 0) return B200_OK;
   B200_REQUIRE(e, x != nullptr, "%s: null pointer", who);
+  B200_NOT_WHILE_CAPTURING(e, who);
   DeviceGuard g(e);
   int rc = flush_pending(e);
   if (rc != B200_OK) return rc;

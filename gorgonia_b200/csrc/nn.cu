@@ -363,6 +363,7 @@ int b200_gather_rows(b200_engine *e, const void *x, const int64_t *idx, void *y,
         (const unsigned char *)x, (const long long *)idx, (unsigned char *)y, n_idx, row_bytes, n_rows, bad);
   }
   B200_CHECK_LAUNCH(e, "gather_rows_kernel");
+  if (e->capturing) return B200_OK;  // a recorded gather cannot report bad indices; it skips those rows
   B200_CHECK_CUDA(e, cudaMemcpyAsync(e->h_flags + 3, bad, sizeof(int), cudaMemcpyDeviceToHost, e->stream));
   B200_CHECK_CUDA(e, cudaStreamSynchronize(e->stream));
   if (e->h_flags[3]) return set_error(e, B200_ERR_INVALID, "b200_gather_rows: an index lies outside [0, %lld)", (long long)n_rows);

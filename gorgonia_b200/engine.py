@@ -139,6 +139,27 @@ class Engine:
         check(lib.b200_pending(self.h, C.byref(n), C.byref(k)), self.h)
         return n.value, k.value
 
+    # ---- tapes: record once, replay with one call ----------------------------------------
+    def tape_begin(self):
+        check(lib.b200_tape_begin(self.h), self.h)
+
+    def tape_end(self):
+        t = C.c_void_p()
+        check(lib.b200_tape_end(self.h, C.byref(t)), self.h)
+        return t
+
+    def tape_launch(self, t):
+        check(lib.b200_tape_launch(self.h, t), self.h)
+
+    def tape_destroy(self, t):
+        lib.b200_tape_destroy(self.h, t)
+
+    def copy_h2d_async(self, t, host_ptr, nbytes=None):
+        check(lib.b200_memcpy_h2d_async(self.h, t.ptr, host_ptr, t.nbytes if nbytes is None else nbytes), self.h)
+
+    def copy_d2h_async(self, host_ptr, t, nbytes=None):
+        check(lib.b200_memcpy_d2h_async(self.h, host_ptr, t.ptr, t.nbytes if nbytes is None else nbytes), self.h)
+
     # ---- device timing -------------------------------------------------------------
     def event(self):
         ev = C.c_void_p()

@@ -84,6 +84,22 @@ int b200_sync(b200_engine *e);
 /* Number of kernels this engine has launched since creation (tests and bench count with it). */
 uint64_t b200_launch_count(const b200_engine *e);
 
+/* ---- tapes -------------------------------------------------------------------------------------
+ * The per-instruction launch path of the tape VM (execOp.exec, vm_tape_cuda.go:66-150; RunAll,
+ * vm_tape.go:213-347) costs one host call per instruction. A forward tape whose shapes and buffers
+ * do not change between runs can instead be recorded once and replayed with ONE call:
+ * between b200_tape_begin and b200_tape_end every engine call is recorded (into a CUDA graph on
+ * the engine's stream) instead of executed; b200_tape_launch replays it. The buffers the recorded
+ * calls named must stay allocated, at the same addresses, for as long as the tape is used.
+ * Entry points that wait for the device (b200_sync, the synchronous copies, b200_has_nan/inf)
+ * return B200_ERR_STATE while recording; the _async copies can be recorded. Run the sequence once
+ * unrecorded first, so that one-time set-up (kernel attributes, lazily created scratch) is done. */
+typedef struct b200_tape b200_tape;
+int b200_tape_begin(b200_engine *e);
+int b200_tape_end(b200_engine *e, b200_tape **out);
+int b200_tape_launch(b200_engine *e, b200_tape *t);
+int b200_tape_destroy(b200_engine *e, b200_tape *t);
+
 /* CUDA events on the engine's stream, for callers that time device work without linking the
  * CUDA runtime themselves (no counterpart in gorgonia, which has no device timing).
  * b200_event_elapsed_ms waits for `stop` to complete. */
