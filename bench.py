@@ -3,19 +3,24 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
 
-Prints ONE JSON line (rank 0). Workloads:
-  elementwise  the float32 elementwise/broadcast/fused-chain sweep on vectors of 2^29 elements
-               (default; metric GB/s of algorithmic bytes). One step = Add, Mul, Sub, Div, Pow,
-               Gt (12 B/elem each), Exp, Tanh, Sigmoid (8 B/elem), broadcast Add of
-               (B,1024)+(1,1024) (8 B/elem) and the fused chain tanh(x*w+b) (16 B/elem).
+Prints ONE JSON line (rank 0). Workloads (--workload):
+  elementwise  (default) the float32 elementwise / broadcast / fused-chain sweep on vectors of 2^29
+               elements. One step = Add, Mul, Sub, Div, Pow, Gt (12 B/elem each), Exp, Tanh, Sigmoid
+               (8 B/elem), broadcast Add of (B,1024)+(1,1024) (8 B/elem) and the fused chain
+               tanh(x*w+b) (16 B/elem). Metric: GB/s of algorithmic bytes. N GPUs = N replicas.
+  gemm         MatMul M=N=K=8192, float32 (3xTF32). Metric: TFLOP/s (2*M*N*K). Replicas.
+  mlp | lenet | yolo   forward pass of the inference graph, batch 256 / 8192 / 64 sharded by batch
+               over the ranks, weights replicated, no collective. Metric: samples/s.
+Unless --no-others is given, the line also carries short measurements of the other workloads
+under "other_workloads" (so one run reports GB/s, TFLOP/s and samples/s).
 
-`value` is measured with the inputs resident in HBM; `e2e` is the same step driven through
-the C ABI from host buffers: pinned host -> device copies of the step's inputs and a device
--> host read of the step's last result inside the timed region.
+`value` is measured with the inputs resident in HBM; `e2e` is the same step driven through the
+C ABI from pinned host buffers: host->device copies of the step's inputs and a device->host read
+of the step's result inside the timed region.
 
 With --impl reference the same step runs on the host cores through the CPU oracle (the
-restatement of gorgonia's CPU engine; the Go reference itself cannot be built here), on a
-bounded sample of the workload.
+restatement of gorgonia's CPU engine; the Go reference itself cannot be built here), on a bounded
+sample of the workload.
 """
 import argparse
 import ctypes as C
@@ -37,6 +42,9 @@ ELEMENTWISE_OPS = [  # (name, kind, algorithmic bytes per element)
     ("bcast_add", "bcast", 8), ("chain_tanh_xw_b", "chain", 16),
 ]
 BYTES_PER_ELEM_STEP = sum(b for _, _, b in ELEMENTWISE_OPS)
+MODEL_BATCH = {"mlp": 256, "lenet": 8192, "yolo": 64}
+REF_NOTE = ("CPU restatement of gorgonia's CPU-engine semantics (oracle/); the Go reference cannot be built here "
+            "(no Go toolchain, dependencies not vendored)")
 
 
 def peaks():
@@ -62,7 +70,8 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                 "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            time.sleep(0.05)
         except OSError:
             self.proc = None
 
@@ -90,10 +99,81 @@ class ClockSampler:
             for k, nm in enumerate(names):
                 if f[3 + k].lower().startswith("active"):
                     reasons.add(nm)
-        # the busiest half of the samples stands for "under load"
-        load = sorted(sm)[len(sm) // 2:] if sm else []
+        load = sorted(sm)[len(sm) // 2:] if sm else []   # the busiest half stands for "under load"
         return {"sm_mhz": statistics.median(load) if load else None, "sm_max_mhz": max(mx) if mx else None,
                 "power_w_max": max(pw) if pw else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+class Ctx:
+    """One rank: its engine, the rendezvous with the other ranks, device timing."""
+
+    def __init__(self, args):
+        import torch
+        self.torch = torch
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.dist = None
+        if self.world > 1:
+            import torch.distributed as dist
+            torch.cuda.set_device(self.local_rank)
+            dist.init_process_group("nccl", device_id=torch.device("cuda", self.local_rank))
+            self.dist = dist
+        self.engine = None
+
+    def make_engine(self, arena_bytes):
+        from gorgonia_b200 import Engine
+        if self.engine is not None:
+            self.engine.Close()
+        self.engine = Engine(device=self.local_rank, arena_bytes=int(arena_bytes))
+        self.ev = (self.engine.event(), self.engine.event())
+        return self.engine
+
+    def barrier(self):
+        self.engine.Signal()
+        if self.dist is not None:
+            self.dist.barrier()
+        self.torch.cuda.synchronize()
+
+    def max_over_ranks(self, v):
+        if self.dist is None:
+            return v
+        t = self.torch.tensor([v], dtype=self.torch.float64, device="cuda")
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def timed(self, step, steps, warmup, sampler=None):
+        """W untimed steps, then exactly K steps between barriers; CUDA events on the engine's
+        stream; max over ranks. Returns (seconds per step, kernel launches in the timed region)."""
+        e = self.engine
+        for _ in range(warmup):
+            step()
+        self.barrier()
+        if sampler is not None and self.rank == 0:
+            sampler.start()
+        l0 = e.launches
+        e.record(self.ev[0])
+        for _ in range(steps):
+            step()
+        e.record(self.ev[1])
+        self.barrier()
+        ms = self.max_over_ranks(e.elapsed_ms(*self.ev))
+        return ms / 1e3 / steps, e.launches - l0
+
+    def pinned(self, arr):
+        e = self.engine
+        p = e.host_alloc(arr.nbytes)
+        ct = {4: C.c_float, 8: C.c_double}[arr.dtype.itemsize]
+        v = np.ctypeslib.as_array(C.cast(p, C.POINTER(ct)), shape=arr.shape)
+        v[...] = arr
+        return p, v
+
+    def close(self):
+        if self.dist is not None:
+            self.dist.barrier()
+            self.dist.destroy_process_group()
+        if self.engine is not None:
+            self.engine.Close()
 
 
 # ------------------------------------------------------------------------------------------
@@ -101,7 +181,7 @@ class ClockSampler:
 # ------------------------------------------------------------------------------------------
 
 def make_inputs(n, seed=2024):
-    """x, y ~ N(0,1); base = |x| + 0.1 for Pow; w, b rows of 1024 for the broadcast forms."""
+    """x, y ~ N(0,1); Pow base = |x| + 0.1; a row of 1024 for the broadcast form."""
     g = np.random.Generator(np.random.Philox(seed))
     x = g.standard_normal(n, dtype=np.float32)
     y = g.standard_normal(n, dtype=np.float32)
@@ -109,25 +189,27 @@ def make_inputs(n, seed=2024):
     return x, y, row
 
 
-def gpu_sweep_step(e, T, n):
-    """One step of the sweep on device-resident tensors: 11 engine calls, flushed per op so that
-    every op is its own kernel except the chain, which is the point of that entry."""
+def gpu_sweep_ops(e, T):
     x, y, base, row, r = T["x"], T["y"], T["base"], T["row"], T["r"]
-    e.Add(x, y, reuse=r); e.DoWork()
-    e.Mul(x, y, reuse=r); e.DoWork()
-    e.Sub(x, y, reuse=r); e.DoWork()
-    e.Div(x, y, reuse=r); e.DoWork()
-    e.Pow(base, y, reuse=r); e.DoWork()
-    e.Gt(x, y, reuse=r); e.DoWork()
-    e.Unary("exp", x, reuse=r); e.DoWork()
-    e.Unary("tanh", x, reuse=r); e.DoWork()
-    e.Unary("sigmoid", x, reuse=r); e.DoWork()
-    e.BroadcastBinary("add", x, row, 1, 1024, reuse=r); e.DoWork()
-    # tanh(x*w+b) with full-size w, b: three engine calls, one kernel
-    e.Mul(x, y, reuse=r)
-    e.Add(r, base, unsafe=True)
-    e.Unary("tanh", r, unsafe=True)
-    e.DoWork()
+    return {
+        "add": lambda: e.Add(x, y, reuse=r), "mul": lambda: e.Mul(x, y, reuse=r),
+        "sub": lambda: e.Sub(x, y, reuse=r), "div": lambda: e.Div(x, y, reuse=r),
+        "pow": lambda: e.Pow(base, y, reuse=r), "gt": lambda: e.Gt(x, y, reuse=r),
+        "exp": lambda: e.Unary("exp", x, reuse=r), "tanh": lambda: e.Unary("tanh", x, reuse=r),
+        "sigmoid": lambda: e.Unary("sigmoid", x, reuse=r),
+        "bcast_add": lambda: e.BroadcastBinary("add", x, row, 1, 1024, reuse=r),
+        # tanh(x*w+b) with full-size w, b: three engine calls, one kernel
+        "chain_tanh_xw_b": lambda: (e.Mul(x, y, reuse=r), e.Add(r, base, unsafe=True),
+                                    e.Unary("tanh", r, unsafe=True)),
+    }
+
+
+def gpu_sweep_step(e, ops):
+    """One step: 11 engine-level operations, flushed one by one so that each is its own kernel
+    (the chain's three calls fuse into one)."""
+    for name, _, _ in ELEMENTWISE_OPS:
+        ops[name]()
+        e.DoWork()
 
 
 def cpu_sweep_step(oracle, x, y, base, row):
@@ -138,7 +220,7 @@ def cpu_sweep_step(oracle, x, y, base, row):
     return oracle.unary("tanh", oracle.binary("add", oracle.binary("mul", x, y), base))
 
 
-def time_cpu(n_sample, steps, warmup):
+def cpu_elementwise(steps, warmup, n_sample=1 << 24):
     from oracle import oracle
     x, y, row = make_inputs(n_sample)
     base = (np.abs(x) + np.float32(0.1)).astype(np.float32)
@@ -148,174 +230,302 @@ def time_cpu(n_sample, steps, warmup):
     for _ in range(steps):
         cpu_sweep_step(oracle, x, y, base, row)
     dt = (time.perf_counter() - t0) / steps
-    return BYTES_PER_ELEM_STEP * n_sample / dt / 1e9, dt, oracle.threads()
+    return {"value": BYTES_PER_ELEM_STEP * n_sample / dt / 1e9, "unit": "GB/s", "cores": oracle.threads(),
+            "kind": "port", "sample": f"{steps} steps of the same 11-op sweep on vectors of 2^24 float32 elements",
+            "ms_per_step": dt * 1e3}
 
 
-def run_reference(args, rank, world):
+def wl_elementwise(ctx, args, main):
+    n = args.elements if main else min(args.elements, 1 << 27)
+    steps, warmup = (args.steps, args.warmup) if main else (5, 3)
+    e = ctx.make_engine(4.25 * 4 * n + (64 << 20))
+    x, y, row = make_inputs(n, seed=2024 + ctx.rank)
+    base = (np.abs(x) + np.float32(0.1)).astype(np.float32)
+    T = {"x": e.empty(n), "y": e.empty(n), "base": e.empty(n), "r": e.empty(n), "row": e.tensor(row)}
+    host = {}
+    for k, a in (("x", x), ("y", y), ("base", base)):
+        host[k], _ = ctx.pinned(a)
+        e.copy_h2d_async(T[k], host[k])
+    hout = e.host_alloc(4 * n)
+    del x, y, base
+    ops = gpu_sweep_ops(e, T)
+    sampler = ClockSampler(ctx.local_rank) if main else None
+    step_s, launches = ctx.timed(lambda: gpu_sweep_step(e, ops), steps, warmup, sampler)
+    clocks = sampler.stop() if (main and ctx.rank == 0) else None
+    bytes_step = BYTES_PER_ELEM_STEP * n
+    res = {"metric": "elementwise sweep throughput (algorithmic bytes)", "unit": "GB/s",
+           "value": ctx.world * bytes_step / step_s / 1e9, "ms_per_step": step_s * 1e3, "dtype": "f32",
+           "config": {"workload": "elementwise_sweep_f32", "elements": n, "ops": [o for o, _, _ in ELEMENTWISE_OPS],
+                      "bytes_per_element_step": BYTES_PER_ELEM_STEP, "l2": "inputs larger than L2",
+                      "parallelism": f"replicas x{ctx.world}" if ctx.world > 1 else "single GPU"},
+           "gpu_launches": launches, "clocks": clocks, "steps": steps, "warmup": warmup}
+    pk = peaks()
+    achieved = bytes_step / step_s / 1e9     # 11 launches back to back: bytes per launch / time per launch
+    res["roofline"] = {"bound": "hbm", "kernel": "pw_stream_kernel", "achieved": achieved, "peak": pk["hbm_gbs"],
+                       "unit": "GB/s", "frac": achieved / pk["hbm_gbs"], "peak_source": pk["source"],
+                       "frac_of_nominal_8TBs": achieved / 8000.0, "traffic": None}
+    if args.profile or not main:
+        return res
+    # per-op breakdown (outside the headline region; each op bracketed by its own events)
+    per_op = {}
+    if ctx.rank == 0:
+        for name, _, bpe in ELEMENTWISE_OPS:
+            ops[name](); e.DoWork()
+            e.record(ctx.ev[0])
+            for _ in range(5):
+                ops[name](); e.DoWork()
+            e.record(ctx.ev[1])
+            per_op[name] = round(bpe * n / (e.elapsed_ms(*ctx.ev) / 5 / 1e3) / 1e9, 1)
+    res["per_op_gbs"] = per_op
+
+    # end to end: host buffers in, host result out, copies inside the timed region
+    def e2e_step():
+        for k in ("x", "y", "base"):
+            e.copy_h2d_async(T[k], host[k])
+        gpu_sweep_step(e, ops)
+        e.copy_d2h_async(hout, T["r"])
+
+    e2e_steps = max(2, min(steps, 5))
+    e2e_s, _ = ctx.timed(e2e_step, e2e_steps, 1)
+    res["e2e"] = {"value": ctx.world * bytes_step / e2e_s / 1e9, "unit": "GB/s", "h2d_bytes_per_step": 3 * 4 * n,
+                  "d2h_bytes_per_step": 4 * n, "steps": e2e_steps}
+    return res
+
+
+# ------------------------------------------------------------------------------------------
+# GEMM
+# ------------------------------------------------------------------------------------------
+
+def wl_gemm(ctx, args, main):
+    n = 8192
+    steps, warmup = (args.steps, args.warmup) if main else (5, 3)
+    e = ctx.make_engine(8 * 4 * n * n + (256 << 20))
+    g = np.random.Generator(np.random.Philox(3 + ctx.rank))
+    a = (g.standard_normal((n, n), dtype=np.float32) * np.float32(0.02))
+    b = (g.standard_normal((n, n), dtype=np.float32) * np.float32(0.02))
+    ta, tb, tc = e.empty((n, n)), e.empty((n, n)), e.empty((n, n))
+    ha, _ = ctx.pinned(a)
+    hb, _ = ctx.pinned(b)
+    hc = e.host_alloc(4 * n * n)
+    e.copy_h2d_async(ta, ha)
+    e.copy_h2d_async(tb, hb)
+    sampler = ClockSampler(ctx.local_rank) if main else None
+    step_s, launches = ctx.timed(lambda: e.MatMul(ta, tb, tc), steps, warmup, sampler)
+    clocks = sampler.stop() if (main and ctx.rank == 0) else None
+    flops = 2.0 * n ** 3
+    pk = peaks()
+    tf = flops / step_s / 1e12
+    res = {"metric": "MatMul float32 (3xTF32) throughput, 2*M*N*K", "unit": "TFLOP/s", "value": ctx.world * tf,
+           "ms_per_step": step_s * 1e3, "dtype": "f32 (3xTF32 on tensor cores, fp32 accumulate)",
+           "config": {"workload": "gemm_f32_8192", "M": n, "N": n, "K": n, "l2": "operands larger than L2",
+                      "parallelism": f"replicas x{ctx.world}" if ctx.world > 1 else "single GPU"},
+           "gpu_launches": launches, "clocks": clocks, "steps": steps, "warmup": warmup,
+           "roofline": {"bound": "tensor", "kernel": "gemm_tc_kernel<3,128>", "achieved": 3 * tf,
+                        "peak": pk["bf16_tflops"] / 2, "unit": "TFLOP/s (TF32 issued = 3 x algorithmic)",
+                        "frac": 3 * tf / (pk["bf16_tflops"] / 2), "peak_source": pk["source"] + " bf16 burst / 2",
+                        "traffic": None}}
+    if not main or args.profile:
+        # bf16 beside it, same shape
+        tab, tbb = e.tensor_bf16(a), e.tensor_bf16(b)
+        s2, _ = ctx.timed(lambda: e.MatMul(tab, tbb, tc), steps, warmup)
+        res["bf16_tflops"] = ctx.world * flops / s2 / 1e12
+        res["bf16_frac_of_measured_peak"] = flops / s2 / 1e12 / pk["bf16_tflops"]
+        return res
+
+    def e2e_step():
+        e.copy_h2d_async(ta, ha)
+        e.copy_h2d_async(tb, hb)
+        e.MatMul(ta, tb, tc)
+        e.copy_d2h_async(hc, tc)
+
+    e2e_s, _ = ctx.timed(e2e_step, max(2, min(steps, 5)), 1)
+    res["e2e"] = {"value": ctx.world * flops / e2e_s / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": 8 * n * n,
+                  "d2h_bytes_per_step": 4 * n * n}
+    return res
+
+
+# ------------------------------------------------------------------------------------------
+# inference graphs
+# ------------------------------------------------------------------------------------------
+
+def model_input(name, batch, seed):
+    g = np.random.Generator(np.random.Philox(seed))
+    shape = {"mlp": (batch, 784), "lenet": (batch, 1, 28, 28), "yolo": (batch, 3, 416, 416)}[name]
+    return g.random(shape, dtype=np.float32)
+
+
+def make_model(name, e, batch):
+    from gorgonia_b200 import tapes
+    return {"mlp": tapes.MLP, "lenet": tapes.LeNet, "yolo": tapes.TinyYolo}[name](e, batch)
+
+
+def wl_model(ctx, args, name, main):
+    total = MODEL_BATCH[name]
+    if total % ctx.world:
+        raise SystemExit(f"batch {total} does not divide over {ctx.world} ranks")
+    b = total // ctx.world                       # this rank's shard: strong scaling of a fixed batch
+    steps, warmup = (args.steps, args.warmup) if main else (5, 3)
+    arena = {"mlp": 1 << 30, "lenet": 8 << 30, "yolo": 24 << 30}[name]
+    e = ctx.make_engine(arena)
+    m = make_model(name, e, b)
+    x = model_input(name, b, 77 + ctx.rank)
+    hx, _ = ctx.pinned(x)
+    hy = e.host_alloc(m.out.nbytes)
+    e.copy_h2d_async(m.x, hx)
+    # device-resident: one recorded tape per step
+    m.record()
+    sampler = ClockSampler(ctx.local_rank) if main else None
+    step_s, launches = ctx.timed(m.replay, steps, warmup, sampler)
+    clocks = sampler.stop() if (main and ctx.rank == 0) else None
+    pk = peaks()
+    tf = m.flops_per_sample * b / step_s / 1e12
+    res = {"metric": f"{name} forward throughput", "unit": "samples/s", "value": total / step_s,
+           "ms_per_step": step_s * 1e3, "dtype": "f32 (matrix products as 3xTF32, fp32 accumulate)",
+           "config": {"workload": f"{name}_forward", "global_batch": total, "batch_per_gpu": b,
+                      "parallelism": f"batch-sharded x{ctx.world}, weights replicated, no collective",
+                      "l2": "activations larger than L2" if name != "mlp" else "flush not needed: launch-bound"},
+           "gpu_launches": launches, "clocks": clocks, "steps": steps, "warmup": warmup, "scaling": "strong",
+           "roofline": {"bound": "tensor", "kernel": "gemm_tc_kernel (conv / dense layers)", "achieved": 3 * tf,
+                        "peak": pk["bf16_tflops"] / 2, "unit": "TFLOP/s (TF32 issued = 3 x algorithmic)",
+                        "frac": 3 * tf / (pk["bf16_tflops"] / 2), "peak_source": pk["source"] + " bf16 burst / 2",
+                        "traffic": None}}
+    if args.profile:
+        m.close()
+        return res
+
+    # end to end: input from pinned host memory, result back to the host, every step
+    m.close()
+    e.Signal()
+    e.tape_begin()
+    e.copy_h2d_async(m.x, hx)
+    m.forward()
+    e.copy_d2h_async(hy, m.out)
+    t = e.tape_end()
+    e2e_s, _ = ctx.timed(lambda: e.tape_launch(t), max(2, min(steps, 10)), 2)
+    e.tape_destroy(t)
+    res["e2e"] = {"value": total / e2e_s, "unit": "samples/s", "h2d_bytes_per_step": int(x.nbytes),
+                  "d2h_bytes_per_step": int(m.out.nbytes)}
+    return res
+
+
+def cpu_model(name, steps=1):
+    from gorgonia_b200 import tapes  # host-side weight draws only; no engine is created
+    from oracle import graphs, oracle
+    sample = {"mlp": 256, "lenet": 128, "yolo": 1}[name]
+
+    class Host:  # a tape object without a device: just the seeded host weights
+        pass
+
+    g = np.random.Generator(np.random.Philox({"mlp": 286, "lenet": 5, "yolo": 9}[name]))
+    h = Host()
+    if name == "mlp":
+        h.w_host = [tapes.glorot_uniform(g, (tapes.MLP.DIMS[i], tapes.MLP.DIMS[i + 1])) for i in range(3)]
+        h.b_host = [np.zeros(tapes.MLP.DIMS[i + 1], np.float32) for i in range(3)]
+        fn = graphs.mlp
+    elif name == "lenet":
+        ch = tapes.LeNet.CH
+        h.wc_host = [tapes.he_normal(g, (ch[i + 1], ch[i], 3, 3), ch[i] * 9) for i in range(3)]
+        h.wd_host = [tapes.he_normal(g, (1152, 625), 1152), tapes.he_normal(g, (625, 10), 625)]
+        fn = graphs.lenet
+    else:
+        ch = tapes.TinyYolo.CH
+        h.k = [3] * 8 + [1]
+        h.w_host = [tapes.he_normal(g, (ch[i + 1], ch[i], h.k[i], h.k[i]), ch[i] * h.k[i] ** 2) for i in range(9)]
+        h.b_host = [(g.standard_normal(ch[i + 1]) * 0.1).astype(np.float32) for i in range(9)]
+        fn = graphs.tiny_yolo
+    x = model_input(name, sample, 77)
+    fn(h, x[:max(1, sample // 8)])           # warm-up on a slice
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        fn(h, x)
+    dt = (time.perf_counter() - t0) / steps
+    return {"value": sample / dt, "unit": "samples/s", "cores": oracle.threads(), "kind": "port",
+            "sample": f"{steps} forward pass(es) of {sample} samples of the same graph", "ms_per_step": dt * 1e3}
+
+
+def cpu_gemm(steps=1, n=1024):
+    from oracle import oracle
+    g = np.random.Generator(np.random.Philox(3))
+    a = (g.standard_normal((n, n), dtype=np.float32) * np.float32(0.02))
+    b = (g.standard_normal((n, n), dtype=np.float32) * np.float32(0.02))
+    oracle.gemm(a[:128], b)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        oracle.gemm(a, b)
+    dt = (time.perf_counter() - t0) / steps
+    return {"value": 2.0 * n ** 3 / dt / 1e12, "unit": "TFLOP/s", "cores": oracle.threads(), "kind": "port",
+            "sample": f"{steps} MatMul(s) of {n}^3 float32 (double accumulation)", "ms_per_step": dt * 1e3}
+
+
+def cpu_leg(workload, steps, warmup):
+    if workload == "elementwise":
+        return cpu_elementwise(steps, warmup)
+    if workload == "gemm":
+        return cpu_gemm(steps)
+    return cpu_model(workload, steps)
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    n_sample = 1 << 24
-    gbs, dt, cores = time_cpu(n_sample, args.steps, min(args.warmup, 1))
-    sample = f"{args.steps} steps of the same 11-op sweep on vectors of 2^24 float32 elements"
-    line = {
-        "impl": "reference", "metric": "elementwise sweep throughput (algorithmic bytes)", "value": gbs,
-        "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "elementwise_sweep_f32", "elements": n_sample, "full_workload_elements": 1 << 29},
-        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample},
-        "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-        "note": "CPU restatement of gorgonia's CPU-engine semantics (oracle/); the Go reference cannot be built "
-                "here (no Go toolchain, dependencies not vendored)",
-    }
+    steps = max(1, min(args.steps, 3))
+    c = cpu_leg(args.workload, steps, 1 if args.workload == "elementwise" else 0)
+    line = {"impl": "reference", "metric": c.pop("metric", None), "value": c["value"], "unit": c["unit"],
+            "n_gpus": args.gpus, "steps": steps, "warmup": args.warmup, "ms_per_step": c.pop("ms_per_step"),
+            "higher_is_better": True, "scaling": "weak" if args.workload in ("elementwise", "gemm") else "strong",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": args.workload, "sample": c["sample"]},
+            "cpu_baseline": c, "e2e": {"value": c["value"], "unit": c["unit"], "h2d_bytes_per_step": 0,
+                                       "d2h_bytes_per_step": 0}, "note": REF_NOTE}
+    line["metric"] = {"elementwise": "elementwise sweep throughput (algorithmic bytes)",
+                      "gemm": "MatMul float32 throughput, 2*M*N*K"}.get(args.workload,
+                                                                         f"{args.workload} forward throughput")
     print(json.dumps(line), flush=True)
 
 
-def run_ours(args, rank, local_rank, world):
-    import torch
-    from gorgonia_b200 import Engine
+def run_workload(ctx, args, name, main):
+    if name == "elementwise":
+        return wl_elementwise(ctx, args, main)
+    if name == "gemm":
+        return wl_gemm(ctx, args, main)
+    return wl_model(ctx, args, name, main)
 
-    dist = None
-    if world > 1:
-        import torch.distributed as dist
-        torch.cuda.set_device(local_rank)
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
-    n = args.elements
-    e = Engine(device=local_rank, arena_bytes=int(4.25 * 4 * n) + (64 << 20))
-    x, y, row = make_inputs(n, seed=2024 + rank)
-    base = (np.abs(x) + np.float32(0.1)).astype(np.float32)
-
-    # pinned host copies (the e2e leg copies from these every step)
-    def pinned(a):
-        p = e.host_alloc(a.nbytes)
-        v = np.ctypeslib.as_array(C.cast(p, C.POINTER(C.c_float)), shape=a.shape)
-        v[...] = a
-        return p, v
-
-    hx, _ = pinned(x)
-    hy, _ = pinned(y)
-    hb, _ = pinned(base)
-    hout_p = e.host_alloc(4 * n)
-    T = {"x": e.empty(n), "y": e.empty(n), "base": e.empty(n), "r": e.empty(n), "row": e.tensor(row)}
-    from gorgonia_b200._lib import lib, check
-    for t, hp in ((T["x"], hx), (T["y"], hy), (T["base"], hb)):
-        check(lib.b200_memcpy_h2d(e.h, t.ptr, hp, 4 * n), e.h)
-    del x, y, base
-
-    def barrier():
-        e.Signal()
-        if dist is not None:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    def max_over_ranks(v):
-        if dist is None:
-            return v
-        t = torch.tensor([v], dtype=torch.float64, device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
-
-    ev0, ev1 = e.event(), e.event()
-
-    # ---- device-resident leg: `value`
-    for _ in range(args.warmup):
-        gpu_sweep_step(e, T, n)
-    sampler = ClockSampler(local_rank)
-    barrier()
-    if rank == 0:
-        sampler.start()
-    l0 = e.launches
-    e.record(ev0)
-    for _ in range(args.steps):
-        gpu_sweep_step(e, T, n)
-    e.record(ev1)
-    barrier()
-    ms = max_over_ranks(e.elapsed_ms(ev0, ev1))
-    launches = e.launches - l0
-    clocks = sampler.stop() if rank == 0 else None
-    step_s = ms / 1e3 / args.steps
-    bytes_step = BYTES_PER_ELEM_STEP * n
-    value = world * bytes_step / step_s / 1e9
-
-    # ---- per-op breakdown (untimed for the headline; each op bracketed by its own events)
-    per_op = {}
-    if rank == 0 and not args.profile:
-        evs = [e.event() for _ in range(2)]
-        x_, y_, b_, row_, r_ = T["x"], T["y"], T["base"], T["row"], T["r"]
-        ops = {
-            "add": lambda: e.Add(x_, y_, reuse=r_), "mul": lambda: e.Mul(x_, y_, reuse=r_),
-            "sub": lambda: e.Sub(x_, y_, reuse=r_), "div": lambda: e.Div(x_, y_, reuse=r_),
-            "pow": lambda: e.Pow(b_, y_, reuse=r_), "gt": lambda: e.Gt(x_, y_, reuse=r_),
-            "exp": lambda: e.Unary("exp", x_, reuse=r_), "tanh": lambda: e.Unary("tanh", x_, reuse=r_),
-            "sigmoid": lambda: e.Unary("sigmoid", x_, reuse=r_),
-            "bcast_add": lambda: e.BroadcastBinary("add", x_, row_, 1, 1024, reuse=r_),
-            "chain_tanh_xw_b": lambda: (e.Mul(x_, y_, reuse=r_), e.Add(r_, b_, unsafe=True),
-                                        e.Unary("tanh", r_, unsafe=True)),
-        }
-        reps = 5
-        for name, _, bpe in ELEMENTWISE_OPS:
-            ops[name](); e.DoWork()
-            e.record(evs[0])
-            for _ in range(reps):
-                ops[name](); e.DoWork()
-            e.record(evs[1])
-            t = e.elapsed_ms(evs[0], evs[1]) / reps / 1e3
-            per_op[name] = round(bpe * n / t / 1e9, 1)
-
-    # ---- end-to-end leg: host buffers in, host result out, copies inside the timed region
-    def e2e_step():
-        check(lib.b200_memcpy_h2d_async(e.h, T["x"].ptr, hx, 4 * n), e.h)
-        check(lib.b200_memcpy_h2d_async(e.h, T["y"].ptr, hy, 4 * n), e.h)
-        check(lib.b200_memcpy_h2d_async(e.h, T["base"].ptr, hb, 4 * n), e.h)
-        gpu_sweep_step(e, T, n)
-        check(lib.b200_memcpy_d2h_async(e.h, hout_p, T["r"].ptr, 4 * n), e.h)
-
-    e2e_steps = max(2, min(args.steps, 5))
-    e2e_value = None
-    if not args.profile:
-        e2e_step()
-        barrier()
-        e.record(ev0)
-        for _ in range(e2e_steps):
-            e2e_step()
-        e.record(ev1)
-        barrier()
-        e2e_ms = max_over_ranks(e.elapsed_ms(ev0, ev1))
-        e2e_value = world * bytes_step / (e2e_ms / 1e3 / e2e_steps) / 1e9
-
-    if rank == 0:
-        pk = peaks()
-        kernel_s = step_s / len(ELEMENTWISE_OPS)      # 11 launches per step, back to back
-        achieved = bytes_step / len(ELEMENTWISE_OPS) / kernel_s / 1e9
-        cpu = None
-        if world == 1 and not args.no_cpu and not args.profile:
-            gbs, dt, cores = time_cpu(1 << 24, 3, 1)
-            cpu = {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port",
-                   "sample": "3 steps of the same 11-op sweep on vectors of 2^24 float32 elements"}
-        line = {
-            "metric": "elementwise sweep throughput (algorithmic bytes)", "value": value, "unit": "GB/s",
-            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_s * 1e3,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
-            "data": "synthetic",
-            "config": {"workload": "elementwise_sweep_f32", "elements": n, "ops": [o for o, _, _ in ELEMENTWISE_OPS],
-                       "bytes_per_element_step": BYTES_PER_ELEM_STEP, "l2": "inputs larger than L2",
-                       "parallelism": f"replicas x{world}" if world > 1 else "single GPU"},
-            "roofline": {"bound": "hbm", "kernel": "pw_kernel", "achieved": achieved, "peak": pk["hbm_gbs"],
-                         "unit": "GB/s", "frac": achieved / pk["hbm_gbs"], "peak_source": pk["source"],
-                         "frac_of_nominal_8TBs": achieved / 8000.0, "traffic": None},
-            "per_op_gbs": per_op,
-            "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": 3 * 4 * n,
-                    "d2h_bytes_per_step": 4 * n, "steps": e2e_steps},
-            "gpu_launches": launches,
-            "clocks": clocks,
-            "cpu_baseline": cpu,
-        }
+def run_ours(args):
+    ctx = Ctx(args)
+    res = run_workload(ctx, args, args.workload, True)
+    others = {}
+    if not args.no_others and not args.profile:
+        for name in ("elementwise", "gemm", "mlp", "lenet", "yolo"):
+            if name == args.workload:
+                continue
+            try:
+                r = run_workload(ctx, args, name, False)
+                keep = {k: r[k] for k in ("metric", "value", "unit", "ms_per_step", "config", "roofline") if k in r}
+                for k in ("bf16_tflops", "bf16_frac_of_measured_peak"):
+                    if k in r:
+                        keep[k] = r[k]
+                others[name] = keep
+            except Exception as ex:  # a side measurement must not cost the headline
+                others[name] = {"error": str(ex)[:200]}
+    if ctx.rank == 0:
+        line = {"metric": res["metric"], "value": res["value"], "unit": res["unit"], "n_gpus": ctx.world,
+                "steps": res["steps"], "warmup": res["warmup"], "ms_per_step": res["ms_per_step"],
+                "higher_is_better": True, "scaling": res.get("scaling", "weak"), "vs_baseline": None,
+                "dtype": res["dtype"], "data": "synthetic", "config": res["config"], "roofline": res["roofline"],
+                "e2e": res.get("e2e"), "gpu_launches": res["gpu_launches"], "clocks": res["clocks"]}
+        if "per_op_gbs" in res:
+            line["per_op_gbs"] = res["per_op_gbs"]
+        if ctx.world == 1 and not args.no_cpu and not args.profile:
+            line["cpu_baseline"] = cpu_leg(args.workload, 3 if args.workload == "elementwise" else 1, 1)
+            line["cpu_baseline"].pop("ms_per_step", None)
+        else:
+            line["cpu_baseline"] = None
+        if others:
+            line["other_workloads"] = others
         print(json.dumps(line), flush=True)
-    if dist is not None:
-        dist.barrier()
-        dist.destroy_process_group()
-    e.Close()
+    ctx.close()
 
 
 def main():
@@ -324,20 +534,18 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="elementwise", choices=["elementwise"])
+    ap.add_argument("--workload", default="elementwise", choices=["elementwise", "gemm", "mlp", "lenet", "yolo"])
     ap.add_argument("--elements", type=int, default=1 << 29)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
+    ap.add_argument("--no-others", action="store_true", help="measure only the chosen workload")
     ap.add_argument("--profile", action="store_true",
                     help="only warm-up and the device-resident timed steps (for runs under a profiler)")
     args = ap.parse_args()
-    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
     if args.impl == "reference":
-        run_reference(args, rank, world)
+        run_reference(args)
     else:
-        run_ours(args, rank, local_rank, world)
+        args.warmup = max(args.warmup, 3)
+        run_ours(args)
 
 
 if __name__ == "__main__":

@@ -5,44 +5,11 @@ import numpy as np
 import pytest
 
 from gorgonia_b200 import tapes
-from oracle import oracle
+from oracle import graphs
 from tests import util
 from tests.util import assert_bits_equal, assert_gemm_close
 
 pytestmark = pytest.mark.gpu
-
-
-def oracle_mlp(m, x):
-    a = x
-    for i in range(3):
-        a = oracle.gemm(a, m.w_host[i])
-        a = oracle.binary_bcast("add", a, m.b_host[i], 1, a.shape[1])
-        if i < 2:
-            a = oracle.rectify(a)
-    return oracle.softmax(a)
-
-
-def oracle_lenet(m, x):
-    a = x
-    for i in range(3):
-        a = oracle.rectify(oracle.conv2d(a, m.wc_host[i], (1, 1)))
-        a, _ = oracle.maxpool2d(a, (2, 2), (0, 0), (2, 2))
-    a = a.reshape(a.shape[0], 1152)
-    a = oracle.rectify(oracle.gemm(a, m.wd_host[0]))
-    return oracle.softmax(oracle.gemm(a, m.wd_host[1]))
-
-
-def oracle_yolo(m, x):
-    a = x
-    for i in range(9):
-        a = oracle.conv2d(a, m.w_host[i], (m.k[i] // 2,) * 2)
-        a = (a + m.b_host[i][None, :, None, None]).astype(np.float32)
-        a = oracle.leaky_relu(a, 1.0 if i == 8 else 0.1)
-        if i < 5:
-            a, _ = oracle.maxpool2d(a, (2, 2), (0, 0), (2, 2))
-        elif i == 5:
-            a, _ = oracle.maxpool2d(a, (2, 2), (1, 0, 1, 0), (1, 1))
-    return a
 
 
 def test_mlp_forward(fresh):
@@ -54,7 +21,7 @@ def test_mlp_forward(fresh):
         t.set(b)
     m.x.set(x)
     got = m.forward().numpy()
-    want = oracle_mlp(m, x)
+    want = graphs.mlp(m, x)
     assert_gemm_close(got, want, 1e-5)
     assert np.array_equal(got.argmax(1), want.argmax(1))
     # instruction-by-instruction form: same bits
@@ -86,7 +53,7 @@ def test_lenet_forward(fresh):
     m = tapes.LeNet(e, B)
     m.x.set(x)
     got = m.forward().numpy()
-    want = oracle_lenet(m, x)
+    want = graphs.lenet(m, x)
     assert_gemm_close(got, want, 1e-5)
     assert np.array_equal(got.argmax(1), want.argmax(1))
     u = tapes.LeNet(e, B, fused=False)
@@ -104,7 +71,7 @@ def test_tiny_yolo_forward(fresh):
     m = tapes.TinyYolo(e, 2, size=128)
     m.x.set(x)
     got = m.forward().numpy()
-    want = oracle_yolo(m, x)
+    want = graphs.tiny_yolo(m, x)
     assert got.shape == (2, 125, 4, 4)
     assert_gemm_close(got, want, 1e-5)
 
