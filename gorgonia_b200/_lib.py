@@ -150,6 +150,7 @@ _SIGS = {
     "b200_im2col": (_i, [_vp, _i, _vp, _vp, _i64, _i64, _i64, _i64, _i, _i, _i, _i, _i, _i, _i, _i]),
     "b200_maxpool2d_fwd": (_i, [_vp, _i, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i, _i, _i, _i, _i, _i, _i, _i, _i]),
     "b200_transpose": (_i, [_vp, _i, _vp, _vp, _i, _P(_i64), _P(_i)]),
+    "b200_gather_axis": (_i, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64]),
     "b200_gather_rows": (_i, [_vp, _vp, _vp, _vp, _i64, _i64, _i64]),
     "b200_has_nan": (_i, [_vp, _i, _vp, _i64, _P(_i)]),
     "b200_has_inf": (_i, [_vp, _i, _vp, _i64, _P(_i)]),

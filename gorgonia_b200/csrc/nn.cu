@@ -151,20 +151,23 @@ __global__ void __launch_bounds__(256) transpose2d_kernel(const T *__restrict__ 
 // ---- gather of rows ------------------------------------------------------------------------------
 // y[i, :] = x[idx[i], :]; rows are copied in 16-byte words when the row size and the bases allow.
 // An index outside [0, n_rows) raises the flag and leaves the row untouched.
+// With outer > 1 the same gather is applied to every leading slice: y[o, i, :] = x[o, idx[i], :].
 template <typename W>
 __global__ void __launch_bounds__(256) gather_rows_kernel(const W *__restrict__ x, const long long *__restrict__ idx,
-                                                          W *__restrict__ y, long long n_idx, long long row_words,
-                                                          long long n_rows, int *bad) {
-  const long long total = n_idx * row_words;
+                                                          W *__restrict__ y, long long outer, long long n_idx,
+                                                          long long row_words, long long n_rows, int *bad) {
+  const long long total = outer * n_idx * row_words;
   const long long stride = (long long)gridDim.x * blockDim.x;
   for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += stride) {
-    const long long i = t / row_words, w = t % row_words;
+    const long long w = t % row_words;
+    const long long i = (t / row_words) % n_idx;
+    const long long o = t / (row_words * n_idx);
     const long long src = idx[i];
     if (src < 0 || src >= n_rows) {
       if (w == 0) atomicExch(bad, 1);
       continue;
     }
-    y[t] = x[src * row_words + w];
+    y[t] = x[(o * n_rows + src) * row_words + w];
   }
 }
 
@@ -336,13 +339,13 @@ int b200_transpose(b200_engine *e, int elem_bytes, const void *x, void *y, int n
   return B200_OK;
 }
 
-int b200_gather_rows(b200_engine *e, const void *x, const int64_t *idx, void *y, int64_t n_idx, int64_t row_bytes,
-                     int64_t n_rows) {
+int b200_gather_axis(b200_engine *e, const void *x, const int64_t *idx, void *y, int64_t outer, int64_t n_rows,
+                     int64_t n_idx, int64_t row_bytes) {
   if (!e) return B200_ERR_INVALID;
   std::lock_guard<std::recursive_mutex> lk(e->mu);
-  B200_REQUIRE(e, n_idx >= 0 && row_bytes >= 0 && n_rows >= 0, "b200_gather_rows: negative extent");
-  if (n_idx == 0 || row_bytes == 0) return B200_OK;
-  B200_REQUIRE(e, x && idx && y, "b200_gather_rows: null pointer");
+  B200_REQUIRE(e, outer >= 0 && n_idx >= 0 && row_bytes >= 0 && n_rows >= 0, "b200_gather_axis: negative extent");
+  if (outer == 0 || n_idx == 0 || row_bytes == 0) return B200_OK;
+  B200_REQUIRE(e, x && idx && y, "b200_gather_axis: null pointer");
   DeviceGuard g(e);
   int rc = flush_pending(e);
   if (rc != B200_OK) return rc;
@@ -352,22 +355,28 @@ int b200_gather_rows(b200_engine *e, const void *x, const int64_t *idx, void *y,
   const bool w4 = row_bytes % 4 == 0 && (uintptr_t)x % 4 == 0 && (uintptr_t)y % 4 == 0;
   if (w16) {
     const long long words = row_bytes / 16;
-    gather_rows_kernel<uint4><<<grid_for(e, n_idx * words), 256, 0, e->stream>>>(
-        (const uint4 *)x, (const long long *)idx, (uint4 *)y, n_idx, words, n_rows, bad);
+    gather_rows_kernel<uint4><<<grid_for(e, outer * n_idx * words), 256, 0, e->stream>>>(
+        (const uint4 *)x, (const long long *)idx, (uint4 *)y, outer, n_idx, words, n_rows, bad);
   } else if (w4) {
     const long long words = row_bytes / 4;
-    gather_rows_kernel<uint32_t><<<grid_for(e, n_idx * words), 256, 0, e->stream>>>(
-        (const uint32_t *)x, (const long long *)idx, (uint32_t *)y, n_idx, words, n_rows, bad);
+    gather_rows_kernel<uint32_t><<<grid_for(e, outer * n_idx * words), 256, 0, e->stream>>>(
+        (const uint32_t *)x, (const long long *)idx, (uint32_t *)y, outer, n_idx, words, n_rows, bad);
   } else {
-    gather_rows_kernel<unsigned char><<<grid_for(e, n_idx * row_bytes), 256, 0, e->stream>>>(
-        (const unsigned char *)x, (const long long *)idx, (unsigned char *)y, n_idx, row_bytes, n_rows, bad);
+    gather_rows_kernel<unsigned char><<<grid_for(e, outer * n_idx * row_bytes), 256, 0, e->stream>>>(
+        (const unsigned char *)x, (const long long *)idx, (unsigned char *)y, outer, n_idx, row_bytes, n_rows, bad);
   }
   B200_CHECK_LAUNCH(e, "gather_rows_kernel");
   if (e->capturing) return B200_OK;  // a recorded gather cannot report bad indices; it skips those rows
   B200_CHECK_CUDA(e, cudaMemcpyAsync(e->h_flags + 3, bad, sizeof(int), cudaMemcpyDeviceToHost, e->stream));
   B200_CHECK_CUDA(e, cudaStreamSynchronize(e->stream));
-  if (e->h_flags[3]) return set_error(e, B200_ERR_INVALID, "b200_gather_rows: an index lies outside [0, %lld)", (long long)n_rows);
+  if (e->h_flags[3])
+    return set_error(e, B200_ERR_INVALID, "b200_gather_axis: an index lies outside [0, %lld)", (long long)n_rows);
   return B200_OK;
+}
+
+int b200_gather_rows(b200_engine *e, const void *x, const int64_t *idx, void *y, int64_t n_idx, int64_t row_bytes,
+                     int64_t n_rows) {
+  return b200_gather_axis(e, x, idx, y, 1, n_rows, n_idx, row_bytes);
 }
 
 }  // extern "C"

@@ -397,9 +397,10 @@ class Engine:
         check(lib.b200_transpose(self.h, x.dtype.itemsize, x.ptr, prealloc.ptr, len(x.shape), shape, pm), self.h)
         return prealloc
 
-    def ByIndices(self, x, idx, prealloc):
-        row = int(np.prod(x.shape[1:], dtype=np.int64)) * x.dtype.itemsize
-        check(lib.b200_gather_rows(self.h, x.ptr, idx.ptr, prealloc.ptr, idx.size, row, x.shape[0]), self.h)
+    def ByIndices(self, x, idx, prealloc, axis=0):
+        outer, n_rows, inner, _ = self._oli(x.shape, axis)
+        check(lib.b200_gather_axis(self.h, x.ptr, idx.ptr, prealloc.ptr, outer, n_rows, idx.size,
+                                   inner * x.dtype.itemsize), self.h)
         return prealloc
 
     def HasNaN(self, t):

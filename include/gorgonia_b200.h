@@ -317,9 +317,10 @@ int b200_reduce_all_static(b200_engine *e, int dtype, int kind, const void *x, i
  *   the winning index inside the (H,W) plane as int64, -1 for an empty window.
  * b200_transpose: transposeOp.Do -> tensor.Transpose (op_tensor.go:937-952): output axis d is input
  *   axis perm[d]; elem_bytes 2, 4 or 8; rank <= 8.
- * b200_gather_rows: byIndicesOp.Do -> tensor.ByIndices along axis 0 (op_by_indices.go:90-97):
- *   y[i,:] = x[idx[i],:], idx int64 on the device. An index outside [0, n_rows) is an error
- *   (checked on the device, reported by this call). */
+ * b200_gather_axis: byIndicesOp.Do -> tensor.ByIndices along any axis (op_by_indices.go:90-97), the
+ *   tensor viewed as (outer, n_rows, row): y[o,i,:] = x[o,idx[i],:], idx int64 on the device. An
+ *   index outside [0, n_rows) is an error (checked on the device, reported by this call).
+ *   b200_gather_rows is the axis-0 form (outer = 1). */
 int b200_conv2d_fwd(b200_engine *e, int dtype, const void *x, const void *w, void *y, int64_t B,
                     int64_t C, int64_t H, int64_t W, int64_t K, int kh, int kw, int pad_h, int pad_w,
                     int stride_h, int stride_w, int dil_h, int dil_w, const b200_epilogue *ep);
@@ -331,6 +332,8 @@ int b200_maxpool2d_fwd(b200_engine *e, int dtype, const void *x, void *y, int64_
                        int pad_west, int pad_east, int explicit_padding, int stride_h, int stride_w);
 int b200_transpose(b200_engine *e, int elem_bytes, const void *x, void *y, int ndim,
                    const int64_t *shape, const int *perm);
+int b200_gather_axis(b200_engine *e, const void *x, const int64_t *idx, void *y, int64_t outer,
+                     int64_t n_rows, int64_t n_idx, int64_t row_bytes);
 int b200_gather_rows(b200_engine *e, const void *x, const int64_t *idx, void *y, int64_t n_idx,
                      int64_t row_bytes, int64_t n_rows);
 

@@ -510,6 +510,14 @@ void oracle_transpose(const void *x, void *y, int ndim, const int64_t *shape, co
 }
 
 /* byIndicesOp.Do -> tensor.ByIndices along axis 0 (op_by_indices.go:90-97): out[i,:] = x[idx[i],:]. */
+/* the same along an inner axis, tensor viewed as (outer, n_rows, row): y[o,i,:] = x[o,idx[i],:] */
+void oracle_gather_axis(const void *x, const int64_t *idx, void *y, int64_t outer, int64_t n_rows, int64_t n_idx,
+                        int64_t row_bytes) {
+  for (int64_t o = 0; o < outer; ++o)
+    for (int64_t i = 0; i < n_idx; ++i)
+      memcpy((char *)y + (o * n_idx + i) * row_bytes, (const char *)x + (o * n_rows + idx[i]) * row_bytes,
+             (size_t)row_bytes);
+}
 void oracle_gather_rows(const void *x, const int64_t *idx, void *y, int64_t n_idx, int64_t row_bytes) {
 #pragma omp parallel for schedule(static)
   for (int64_t i = 0; i < n_idx; ++i)

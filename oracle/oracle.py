@@ -218,6 +218,16 @@ def gather_rows(x, idx):
     return y
 
 
+def gather_axis(x, idx, axis):
+    x = np.ascontiguousarray(x)
+    idx = np.ascontiguousarray(idx, dtype=np.int64)
+    axis %= x.ndim
+    o, l, i = _oli(x.shape, axis)
+    y = np.empty(x.shape[:axis] + (idx.size,) + x.shape[axis + 1:], dtype=x.dtype)
+    _lib.oracle_gather_axis(_p(x), _p(idx), _p(y), _i64(o), _i64(l), _i64(idx.size), _i64(i * x.dtype.itemsize))
+    return y
+
+
 def rectify(x):
     """Rectify (nn.go:136-163): x * (x >= 0)."""
     return binary("mul", x.reshape(-1), binary("gte", x.reshape(-1), x.dtype.type(0))).reshape(x.shape)

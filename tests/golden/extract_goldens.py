@@ -1,0 +1,271 @@
+#!/usr/bin/env python
+"""Extracts the golden vectors that gorgonia's own tests hold for the hot path into JSON fixtures.
+
+    python tests/golden/extract_goldens.py /path/to/gorgonia
+
+It READS the Go test files as text (nothing of gorgonia is executed; there is no Go toolchain
+here) and writes one JSON file per table next to this script. Only data is taken: the literal
+inputs and expected outputs of the tables named below. The fixtures are committed; this script
+is the record of where every number came from.
+
+  binop.json           binOpTests                          op_math_test.go
+  softmax_do.json      testCasesSoftMaxDo                  op_softmax_test.go
+  maxpool_asym.json    TestMaxPool2D_asymmetricPadding     nn_test.go
+  maxpool_basic.json   TestMaxPool                         nn_test.go
+  conv_issue233.json   TestIssue233_F32 / _F64             known_issues_test.go
+  leakyrelu.json       TestLeakyRelu                       nn_test.go
+  byindices.json       TestByIndicesOpDo                   op_by_indices_test.go
+  broadcast_add.json   broadcastAddTests                   operations_broadcast_test.go
+"""
+import json
+import os
+import re
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+NUM = r"[-+]?(?:\d+\.?\d*(?:[eE][-+]?\d+)?|\.\d+(?:[eE][-+]?\d+)?)"
+
+
+def strip_comments(src):
+    src = re.sub(r"/\*.*?\*/", "", src, flags=re.S)
+    return re.sub(r"//[^\n]*", "", src)
+
+
+def balanced(src, start, open_ch, close_ch):
+    """Index just past the bracket that closes the one at src[start]."""
+    depth = 0
+    for i in range(start, len(src)):
+        if src[i] == open_ch:
+            depth += 1
+        elif src[i] == close_ch:
+            depth -= 1
+            if depth == 0:
+                return i + 1
+    raise ValueError("unbalanced")
+
+
+def numbers(text):
+    return [float(x) for x in re.findall(NUM, text)]
+
+
+def region(src, start_marker, end_marker=None):
+    a = src.index(start_marker)
+    b = src.index(end_marker, a) if end_marker else len(src)
+    return src[a:b]
+
+
+def parse_value(expr):
+    """tensor.New(...) / NewF64(x) / NewF32(x) -> dict(kind, dtype, shape, data)."""
+    expr = expr.strip()
+    m = re.match(r"NewF(64|32)\((" + NUM + r")\)", expr)
+    if m:
+        return {"kind": "scalar", "dtype": "float" + m.group(1), "shape": [], "data": [float(m.group(2))]}
+    if not expr.startswith("tensor.New("):
+        raise ValueError("cannot parse value: " + expr[:60])
+    shape = None
+    m = re.search(r"WithShape\(([^)]*)\)", expr)
+    if m:
+        shape = [int(v) for v in numbers(m.group(1))]
+    m = re.search(r"WithBacking\(\s*\[\]\s*(float64|float32|int)\s*\{", expr)
+    if m:
+        end = balanced(expr, m.end() - 1, "{", "}")
+        data = numbers(expr[m.end():end - 1])
+        dtype = m.group(1)
+    else:
+        m = re.search(r"tensor\.Range\(\s*tensor\.(Float64|Float32)\s*,\s*(\d+)\s*,\s*(\d+)\s*\)", expr)
+        if not m:
+            raise ValueError("no backing: " + expr[:80])
+        data = [float(v) for v in range(int(m.group(2)), int(m.group(3)))]
+        dtype = m.group(1).lower()
+    if shape is None:
+        shape = [len(data)]
+    return {"kind": "tensor", "dtype": dtype, "shape": shape, "data": data}
+
+
+def values_in(src):
+    """All tensor.New(...) / NewF64 / NewF32 expressions of a text, in order."""
+    out = []
+    for m in re.finditer(r"tensor\.New\(|NewF(?:64|32)\(", src):
+        if out and m.start() < out[-1][1]:
+            continue  # nested inside the previous one
+        end = balanced(src, src.index("(", m.start()), "(", ")")
+        out.append((m.start(), end))
+    return [parse_value(src[a:b]) for a, b in out]
+
+
+def top_level_blocks(src):
+    """The {...} entries of a Go composite literal whose text starts at its opening brace."""
+    blocks, i, depth = [], 0, 0
+    start = None
+    body_open = src.index("{")
+    i = body_open + 1
+    while i < len(src):
+        ch = src[i]
+        if ch == "{":
+            if depth == 0:
+                start = i
+            depth += 1
+        elif ch == "}":
+            if depth == 0:
+                break
+            depth -= 1
+            if depth == 0:
+                blocks.append(src[start:i + 1])
+        i += 1
+    return blocks
+
+
+def field(block, name, pattern):
+    m = re.search(name + r"\s*:\s*" + pattern, block)
+    return m.group(1) if m else None
+
+
+def extract_binop(root):
+    src = strip_comments(open(os.path.join(root, "op_math_test.go")).read())
+    table = region(src, "var binOpTests = []binOpTest", "\nfunc ")
+    table = table[table.index("=") + 1:]
+    table = table[table.index("]binOpTest") + len("]binOpTest"):]
+    cases = []
+    for blk in top_level_blocks(table):
+        m = re.match(r"\{\s*([A-Za-z]+)\s*,", blk)
+        if m:
+            op = m.group(1)
+        elif "BatchedMatMul" in blk:
+            op = "BatchedMatMul"
+        else:
+            continue
+        vals = values_in(blk)
+        if len(vals) < 5:
+            continue
+        sm = re.search(r"tensor\.Shape\{([^}]*)\}\s*,?\s*\}\s*$", blk)
+        shape = [int(v) for v in numbers(sm.group(1))] if sm else []
+        cases.append({"op": op, "a": vals[0], "b": vals[1], "correct": vals[2], "deriv_a": vals[3],
+                      "deriv_b": vals[4], "correct_shape": shape})
+    return {"source": "op_math_test.go: binOpTests", "cases": cases}
+
+
+def extract_softmax(root):
+    src = strip_comments(open(os.path.join(root, "op_softmax_test.go")).read())
+    table = region(src, "var testCasesSoftMaxDo", "\nfunc ")
+    table = table[table.index("}{") + 1:]
+    cases = []
+    for blk in top_level_blocks(table):
+        arrays = []
+        for m in re.finditer(r"\[\]float64\s*\{", blk):
+            end = balanced(blk, m.end() - 1, "{", "}")
+            arrays.append(numbers(blk[m.end():end - 1]))
+        shape = [int(v) for v in numbers(re.search(r"tensor\.Shape\{([^}]*)\}", blk).group(1))]
+        cases.append({"input": arrays[0], "shape": shape, "expected": arrays[1]})
+    return {"source": "op_softmax_test.go: testCasesSoftMaxDo (softmax along the last axis)", "cases": cases}
+
+
+def extract_maxpool_asym(root):
+    src = strip_comments(open(os.path.join(root, "nn_test.go")).read())
+    fn = region(src, "func TestMaxPool2D_asymmetricPadding", "\nfunc ")
+    vals = values_in(fn)
+    cases = [{"input": vals[i], "output": vals[i + 1]} for i in range(0, len(vals) - 1, 2)]
+    return {"source": "nn_test.go: TestMaxPool2D_asymmetricPadding", "kernel": [2, 2], "pad": [1, 0, 1, 0],
+            "stride": [1, 1], "cases": cases}
+
+
+def extract_maxpool_basic(root):
+    src = strip_comments(open(os.path.join(root, "nn_test.go")).read())
+    fn = region(src, "func TestMaxPool(t", "\nfunc ")
+    table = fn[fn.index("}{") + 1:]
+    cases = []
+    for blk in top_level_blocks(table):
+        if "input" not in blk:
+            continue
+        cases.append({
+            "input": values_in(blk)[0],
+            "kernel": [int(v) for v in numbers(field(blk, "kernelSize", r"\[\]int\{([^}]*)\}"))],
+            "pad": [int(v) for v in numbers(field(blk, "pad", r"\[\]int\{([^}]*)\}"))],
+            "stride": [int(v) for v in numbers(field(blk, "stride", r"\[\]int\{([^}]*)\}"))],
+            "expected": numbers(field(blk, "expectedOutput", r"\[\]float64\{([^}]*)\}")),
+            "expected_shape": [int(v) for v in numbers(field(blk, "expectedShape", r"tensor\.Shape\{([^}]*)\}"))],
+        })
+    return {"source": "nn_test.go: TestMaxPool", "cases": cases}
+
+
+def extract_conv(root):
+    src = strip_comments(open(os.path.join(root, "known_issues_test.go")).read())
+    cases = []
+    for name in ("TestIssue233_F32", "TestIssue233_F64"):
+        fn = region(src, "func " + name, "\nfunc ")
+        vals = values_in(fn)
+        m = re.search(r"correct\s*:=\s*\[\]float(?:32|64)\s*\{", fn)
+        end = balanced(fn, m.end() - 1, "{", "}")
+        cases.append({"name": name, "x": vals[0], "w": vals[1], "kernel": [3, 3], "pad": [1, 1], "stride": [1, 1],
+                      "dilation": [1, 1], "correct": numbers(fn[m.end():end - 1])})
+    return {"source": "known_issues_test.go: TestIssue233_F32 / TestIssue233_F64 (Conv2d 3x3, pad 1)", "cases": cases}
+
+
+def extract_leakyrelu(root):
+    src = strip_comments(open(os.path.join(root, "nn_test.go")).read())
+    fn = region(src, "func TestLeakyRelu", "\nfunc ")
+    table = fn[fn.index("}{") + 1:]
+    cases = []
+    for blk in top_level_blocks(table):
+        vals = values_in(blk)
+        if len(vals) != 2:
+            continue
+        cases.append({"alpha": float(field(blk, "alpha", "(" + NUM + ")")), "x": vals[0], "y": vals[1]})
+    return {"source": "nn_test.go: TestLeakyRelu (compared there with InDeltaSlice 1e-6)", "cases": cases}
+
+
+def extract_byindices(root):
+    src = strip_comments(open(os.path.join(root, "op_by_indices_test.go")).read())
+    fn = region(src, "func TestByIndicesOpDo", "\nfunc ")
+    table = fn[fn.index("}{") + 1:]
+    cases = []
+    for blk in top_level_blocks(table):
+        vals = values_in(blk)
+        if len(vals) != 2:
+            continue
+        cases.append({"input": vals[0], "indices": vals[1], "axis": int(field(blk, "axis", r"(\d+)")),
+                      "expected": numbers(field(blk, "expectedOutput", r"\[\]float64\{([^}]*)\}")),
+                      "expected_shape": [int(v) for v in numbers(field(blk, "expectedShape",
+                                                                         r"tensor\.Shape\{([^}]*)\}"))]})
+    return {"source": "op_by_indices_test.go: TestByIndicesOpDo", "cases": cases}
+
+
+def extract_broadcast(root):
+    src = strip_comments(open(os.path.join(root, "operations_broadcast_test.go")).read())
+    table = region(src, "var broadcastAddTests", "\nvar ")
+    table = table[table.index("]broadcastOpTest") + len("]broadcastOpTest"):]
+    cases = []
+    for blk in top_level_blocks(table):
+        if re.search(r"err\s*:\s*true", blk):
+            continue
+        vals = values_in(blk)
+        if len(vals) != 3:
+            continue
+        left = field(blk, "left", r"\[\]byte\{([^}]*)\}")
+        right = field(blk, "right", r"\[\]byte\{([^}]*)\}")
+        cases.append({"name": field(blk, "name", r'"([^"]*)"'), "a": vals[0], "b": vals[1], "ab": vals[2],
+                      "left": [int(v) for v in numbers(left)] if left else [],
+                      "right": [int(v) for v in numbers(right)] if right else []})
+    return {"source": "operations_broadcast_test.go: broadcastAddTests (left/right = axes along which that "
+                      "operand is repeated)", "cases": cases}
+
+
+def main():
+    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    out = {
+        "binop.json": extract_binop(root),
+        "softmax_do.json": extract_softmax(root),
+        "maxpool_asym.json": extract_maxpool_asym(root),
+        "maxpool_basic.json": extract_maxpool_basic(root),
+        "conv_issue233.json": extract_conv(root),
+        "leakyrelu.json": extract_leakyrelu(root),
+        "byindices.json": extract_byindices(root),
+        "broadcast_add.json": extract_broadcast(root),
+    }
+    for name, doc in out.items():
+        with open(os.path.join(HERE, name), "w") as f:
+            json.dump(doc, f, separators=(",", ":"))
+        print(f"{name}: {len(doc['cases'])} cases, {os.path.getsize(os.path.join(HERE, name))} bytes")
+
+
+if __name__ == "__main__":
+    main()

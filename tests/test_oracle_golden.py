@@ -1,0 +1,102 @@
+"""Pins the CPU oracle to the golden vectors gorgonia's own tests hold for this path (CPU only).
+
+The fixtures under tests/golden/ were extracted from the Go test files by
+tests/golden/extract_goldens.py; each test names the table it checks."""
+import numpy as np
+import pytest
+
+from oracle import oracle
+from tests import golden_util as G
+
+
+def test_binop_table():
+    """binOpTests (op_math_test.go:23-359): values of + - * / in vv, vs, sv and ss forms, f64 and f32."""
+    cases = G.load("binop.json")["cases"]
+    assert len(cases) >= 30
+    n = 0
+    for c in cases:
+        if c["op"] == "BatchedMatMul":
+            a, b = G.arr(c["a"]), G.arr(c["b"])
+            got = oracle.batched_matmul(a, b)
+            assert got.shape == tuple(c["correct_shape"])
+            assert got.reshape(-1).tolist() == c["correct"]["data"]
+        else:
+            a, b = G.arr(c["a"]), G.arr(c["b"])
+            got = oracle.binary(G.BINOPS[c["op"]], a, b)
+            want = G.arr(c["correct"])
+            assert got.dtype == want.dtype
+            assert got.reshape(-1).tolist() == want.reshape(-1).tolist(), c
+        n += 1
+    assert n == len(cases)
+
+
+def test_softmax_table():
+    """testCasesSoftMaxDo (op_softmax_test.go:13-99): float64 goldens at the 1e-16 level."""
+    for c in G.load("softmax_do.json")["cases"]:
+        x = np.array(c["input"], np.float64).reshape(c["shape"])
+        got = oracle.softmax(x, -1)
+        np.testing.assert_allclose(got.reshape(-1), np.array(c["expected"]), rtol=1e-14, atol=0)
+        got32 = oracle.softmax(x.astype(np.float32), -1)
+        np.testing.assert_allclose(got32.reshape(-1), np.array(c["expected"]), rtol=2e-6, atol=0)
+
+
+def test_maxpool_asymmetric_padding():
+    """TestMaxPool2D_asymmetricPadding (nn_test.go:91-138): pins the south/east origin of explicit padding."""
+    d = G.load("maxpool_asym.json")
+    for c in d["cases"]:
+        x, want = G.arr(c["input"]), G.arr(c["output"])
+        got, _ = oracle.maxpool2d(x.astype(np.float32), d["kernel"], d["pad"], d["stride"])
+        assert got.shape == want.shape
+        assert np.array_equal(got, want.astype(np.float32))
+
+
+def test_maxpool_basic():
+    for c in G.load("maxpool_basic.json")["cases"]:
+        got, _ = oracle.maxpool2d(G.arr(c["input"]).astype(np.float32), c["kernel"], c["pad"], c["stride"])
+        assert list(got.shape) == c["expected_shape"] and got.reshape(-1).tolist() == c["expected"]
+
+
+def test_conv_issue233():
+    """TestIssue233_F32/_F64 (known_issues_test.go:160-239): Conv2d 3x3 pad 1 on a 5x5 ramp."""
+    for c in G.load("conv_issue233.json")["cases"]:
+        got = oracle.conv2d(G.arr(c["x"]), G.arr(c["w"]), c["pad"], c["stride"], c["dilation"])
+        assert got.reshape(-1).tolist() == c["correct"]
+
+
+def test_leaky_relu():
+    """TestLeakyRelu (nn_test.go:538-588), held there to 1e-6 absolute."""
+    for c in G.load("leakyrelu.json")["cases"]:
+        x, want = G.arr(c["x"]), G.arr(c["y"])
+        got = oracle.leaky_relu(x, c["alpha"])
+        np.testing.assert_allclose(got, want, rtol=0, atol=1e-6)
+
+
+def test_by_indices():
+    """TestByIndicesOpDo (op_by_indices_test.go:12-86), axis 0 and axis 1."""
+    for c in G.load("byindices.json")["cases"]:
+        got = oracle.gather_axis(G.arr(c["input"]), G.arr(c["indices"]), c["axis"])
+        assert list(got.shape) == c["expected_shape"] and got.reshape(-1).tolist() == c["expected"]
+
+
+def test_broadcast_add():
+    """broadcastAddTests (operations_broadcast_test.go:24-73): the six vector/matrix forms."""
+    for c in G.load("broadcast_add.json")["cases"]:
+        div, mod, small_is_a = G.broadcast_div_mod(c)
+        a, b = G.arr(c["a"]).reshape(-1), G.arr(c["b"]).reshape(-1)
+        full_shape = (c["b"] if small_is_a else c["a"])["shape"]
+        a2 = a if small_is_a else a.reshape(full_shape)
+        b2 = b.reshape(full_shape) if small_is_a else b
+        got = oracle.binary_bcast("add", a2, b2, div, mod, small_is_a)
+        assert got.reshape(-1).tolist() == c["ab"]["data"], c["name"]
+
+
+def test_fixtures_match_the_generator_if_reference_is_mounted():
+    """When the gorgonia checkout is present, the committed fixtures equal a fresh extraction."""
+    import json
+    import os
+    root = "/root/reference"
+    if not os.path.exists(os.path.join(root, "op_math_test.go")):
+        pytest.skip("gorgonia checkout not mounted")
+    from tests.golden import extract_goldens as X
+    assert X.extract_binop(root) == json.load(open(os.path.join(G.GOLDEN, "binop.json")))
+    assert X.extract_byindices(root) == json.load(open(os.path.join(G.GOLDEN, "byindices.json")))
