@@ -2,36 +2,26 @@
 // with the filters transposed -> Reshape -> Transpose(0,3,1,2)) one device entry point in place of
 // five tape instructions, three of which are CPU-only in the reference.
 //
-// Formulation. For every image b:  Y_b (K x Ho*Wo)  =  Wf (K x C*kh*kw)  .  col_b^T,
-// with col_b the im2col matrix of that image (Ho*Wo rows, C*kh*kw columns, column order channel,
-// kernel row, kernel column: op_nn.go:418-441). Written that way the product of each image lands
-// directly in NCHW order, the filters are used untouched (they are already K x C*kh*kw row-major),
-// the bias is a per-row vector and the activation fuses into the store: no transpose pass.
-//
-// Execution. Images are processed in chunks whose im2col scratch (TF32 head + tail) stays within
-// a fixed budget well below the L2 size, so the matrix multiply reads the col data of a chunk from
-// L2, not HBM: HBM sees x once and y once. Per chunk: one im2col+split launch, one batched
-// tensor-core launch (3xTF32, fp32 accumulate). float64, and shapes the tensor-core path does not
-// take, run im2col + the CUDA-core multiply with the same formulation.
+// float32 runs as an implicit GEMM on the tensor cores (conv_tc.cu): the im2col matrix is never
+// written to memory, the product lands in NCHW order, the filters are used untouched, bias and
+// activation fuse into the store. float64 and problems under 64^3 multiply-adds take the
+// CUDA-core path below: im2col of a chunk of images into arena scratch, then per image
+//   Y_b (K x Ho*Wo) = Wf (K x C*kh*kw) . col_b^T,
+// which also lands in NCHW order (column order of col: channel, kernel row, kernel column,
+// op_nn.go:418-441).
 #include <algorithm>
 
 #include "engine.h"
 #include "epilogue.cuh"
-#include "tc_operand.h"
 
 namespace b200 {
 
-int gemm_tc_core(b200_engine *e, int terms, bool a_mn, bool b_mn, long long M, long long N, long long K,
-                 const TcOperand &a, const TcOperand &b, void *C, long long ldc, long long batch, long long strideC,
-                 const Epilogue &ep);
-int split_operand_tf32(b200_engine *e, const float *src, long long rows, long long cols, long long ld,
-                       long long batch, long long batch_stride, TcOperand *out, void **blk_hi, void **blk_lo);
+int conv2d_tc(b200_engine *e, const float *x, const float *w, float *y, long long B, int C, int H, int W, int K,
+              int kh, int kw, int padH, int padW, int sH, int sW, int dH, int dW, int Ho, int Wo,
+              const Epilogue &ep);
 int gemm_simt(b200_engine *e, int dtype, int transA, int transB, long long M, long long N, long long K,
               const void *A, long long lda, const void *B, long long ldb, void *C, long long ldc, long long batch,
               long long strideA, long long strideB, long long strideC, const Epilogue &ep);
-int launch_im2col_split(b200_engine *e, const float *x, float *hi, float *lo, long long B, int C, int H, int W,
-                        int Ho, int Wo, int kh, int kw, int padH, int padW, int sH, int sW, int dH, int dW, int ld);
-
 // scratch budget for the col data of one chunk (head + tail together)
 static const long long kColChunkBytes = 64LL << 20;
 
@@ -71,39 +61,13 @@ int b200_conv2d_fwd(b200_engine *e, int dtype, const void *x, const void *w, voi
 
   const long long crs = C * kh * kw, hw = Ho * Wo;
   const size_t es = dtype_size(dtype);
-  const bool tc = dtype == B200_F32 && hw >= 16 && K * hw * crs >= 64LL * 64 * 64;
-  const long long ld = tc ? (crs + 3) / 4 * 4 : crs;
-  const long long img_bytes = hw * ld * (long long)es * (tc ? 2 : 1);
+  const bool tc = dtype == B200_F32 && B * K * hw * crs >= 64LL * 64 * 64 && B * hw < (1LL << 40);
+  const long long img_bytes = hw * crs * (long long)es;
   long long chunk = std::max<long long>(1, std::min<long long>(B, kColChunkBytes / std::max<long long>(1, img_bytes)));
 
-  if (tc) {
-    TcOperand wf, col;
-    void *wblk[2] = {nullptr, nullptr};
-    rc = split_operand_tf32(e, (const float *)w, K, crs, crs, 1, 0, &wf, &wblk[0], &wblk[1]);
-    if (rc != B200_OK) return rc;
-    wf.shared = true;
-    void *chi = nullptr, *clo = nullptr;
-    rc = b200_get(e, chunk * hw * ld * 4, &chi);
-    if (rc == B200_OK) rc = b200_get(e, chunk * hw * ld * 4, &clo);
-    for (long long b0 = 0; rc == B200_OK && b0 < B; b0 += chunk) {
-      const long long nb = std::min(chunk, B - b0);
-      rc = launch_im2col_split(e, (const float *)x + b0 * C * H * W, (float *)chi, (float *)clo, nb, (int)C, (int)H,
-                               (int)W, (int)Ho, (int)Wo, kh, kw, pad_h, pad_w, stride_h, stride_w, dil_h, dil_w,
-                               (int)ld);
-      if (rc != B200_OK) break;
-      col.p0 = chi;
-      col.p1 = clo;
-      col.ld = ld;
-      col.batch_stride = hw * ld;
-      // A = filters (K x crs, k contiguous), B = col_b stored (hw x crs): both K-major
-      rc = gemm_tc_core(e, 3, false, false, K, hw, crs, wf, col, (float *)y + b0 * K * hw, hw, nb, K * hw, ep);
-    }
-    if (chi) b200_put(e, chi, 0);
-    if (clo) b200_put(e, clo, 0);
-    b200_put(e, wblk[0], 0);
-    b200_put(e, wblk[1], 0);
-    return rc;
-  }
+  if (tc)
+    return conv2d_tc(e, (const float *)x, (const float *)w, (float *)y, B, (int)C, (int)H, (int)W, (int)K, kh, kw,
+                     pad_h, pad_w, stride_h, stride_w, dil_h, dil_w, (int)Ho, (int)Wo, ep);
 
   // CUDA-core path: plain im2col of a chunk, then Y_b = Wf . col_b^T per image
   void *colbuf = nullptr;

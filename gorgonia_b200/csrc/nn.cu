@@ -175,16 +175,6 @@ static int grid_for(b200_engine *e, long long work) {
   return (int)std::max<long long>(1, std::min<long long>((work + 255) / 256, (long long)e->sm_count * 16));
 }
 
-// used by conv.cu
-int launch_im2col_split(b200_engine *e, const float *x, float *hi, float *lo, long long B, int C, int H, int W,
-                        int Ho, int Wo, int kh, int kw, int padH, int padW, int sH, int sW, int dH, int dW, int ld) {
-  const long long total = B * Ho * Wo * (long long)ld;
-  im2col_kernel<float, true><<<grid_for(e, total), 256, 0, e->stream>>>(x, hi, lo, B, C, H, W, Ho, Wo, kh, kw, padH,
-                                                                       padW, sH, sW, dH, dW, ld);
-  B200_CHECK_LAUNCH(e, "im2col_kernel");
-  return B200_OK;
-}
-
 }  // namespace b200
 
 using namespace b200;
