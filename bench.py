@@ -360,10 +360,10 @@ def make_model(name, e, batch):
 
 
 def wl_model(ctx, args, name, main):
+    from gorgonia_b200 import shard
     total = MODEL_BATCH[name]
-    if total % ctx.world:
-        raise SystemExit(f"batch {total} does not divide over {ctx.world} ranks")
-    b = total // ctx.world                       # this rank's shard: strong scaling of a fixed batch
+    lo, hi = shard.my_shard(total, ctx.rank, ctx.world)
+    b = hi - lo                                  # this rank's shard: strong scaling of a fixed batch
     steps, warmup = (args.steps, args.warmup) if main else (5, 3)
     arena = {"mlp": 1 << 30, "lenet": 8 << 30, "yolo": 24 << 30}[name]
     e = ctx.make_engine(arena)

@@ -61,7 +61,10 @@ int b200_conv2d_fwd(b200_engine *e, int dtype, const void *x, const void *w, voi
 
   const long long crs = C * kh * kw, hw = Ho * Wo;
   const size_t es = dtype_size(dtype);
-  const bool tc = dtype == B200_F32 && B * K * hw * crs >= 64LL * 64 * 64 && B * hw < (1LL << 40);
+  // the tensor-core kernel keeps per-image offsets in 32 bits and packs tap offsets in 14 bits
+  const bool tc = dtype == B200_F32 && B * K * hw * crs >= 64LL * 64 * 64 && B * hw < (1LL << 40) &&
+                  C * H * W < (1LL << 31) && H < 16000 && W < 16000 && (long long)dil_h * kh < 16000 &&
+                  (long long)dil_w * kw < 16000;
   const long long img_bytes = hw * crs * (long long)es;
   long long chunk = std::max<long long>(1, std::min<long long>(B, kColChunkBytes / std::max<long long>(1, img_bytes)));
 

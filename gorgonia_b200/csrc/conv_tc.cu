@@ -9,10 +9,13 @@
 //                         output channel a run of consecutive addresses across a warp;
 //   N (BN columns)      = output channels, BN = 32..128;
 //   K                   = q, in blocks of 32 (one 128-byte swizzle row of float32).
-// A operand: four gather warps build each 128 x 32 slab of col directly in shared memory, in the
+// A operand: eight gather warps build each 128 x 32 slab of col directly in shared memory, in the
 // K-major 128-byte-swizzle layout the tensor core reads, already split into TF32 head and tail.
-// Thread t owns tile row t (one pixel); for a fixed q the 32 lanes of a warp read consecutive
-// input pixels, so the gather is coalesced and x is re-read from L1/L2, not HBM.
+// Two threads share a tile row (one pixel), 16 q each; for a fixed q the 32 lanes of a warp read
+// consecutive input pixels, so the gather is coalesced and x is re-read from L1/L2, not HBM. The
+// (c, r, s) decomposition of q is the same for every lane: 16 lanes compute one entry each per
+// k-block and the warp shares them by shuffle. Loads of the next k-block are issued before the
+// current one is converted and stored, so their latency overlaps the conversion.
 // B operand: the filters, split once into head/tail (K x C*kh*kw row-major is already K-major),
 // loaded by TMA.
 // Accumulation, as in the matrix multiply: hi*hi in one TMEM accumulator, the two cross terms in
@@ -20,7 +23,7 @@
 // (the tensor core's adder truncates; see gemm_tc.cu). Eight epilogue warps: two per TMEM lane
 // quarter, each folding half of the BN columns, which keeps them at 64 accumulator registers.
 //
-// Warp roles (14 warps): 0 TMA (filters), 1 MMA issuer + TMEM owner, 2-9 epilogue, 10-13 gather.
+// Warp roles (18 warps): 0 TMA (filters), 1 MMA issuer + TMEM owner, 2-9 epilogue, 10-17 gather.
 // No multicast, no clusters. Every wait is bounded; a time-out raises the engine's error word.
 #include <cuda.h>
 #include <cuda_runtime.h>
@@ -41,8 +44,9 @@ int split_operand_tf32(b200_engine *e, const float *src, long long rows, long lo
 
 constexpr int CV_BM = 128;
 constexpr int CV_BK = 32;                 // q per stage: one 128-byte row of float32
-constexpr int CV_THREADS = 448;           // 14 warps
+constexpr int CV_THREADS = 576;           // 18 warps
 constexpr int CV_GATHER_WARP0 = 10;
+constexpr int CV_GATHER_THREADS = 256;    // two threads per tile row, 16 q each
 constexpr int CV_A_BYTES = CV_BM * 128;   // one copy (head or tail) of the A slab
 
 struct ConvTcParams {
@@ -79,7 +83,9 @@ __device__ __forceinline__ void cv_tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) 
       : "memory");
 }
 
-template <int BN>
+// FAST: the common case, which lets the gather run on 32-bit indices and a per-pixel tap mask:
+// at most 32 taps per channel (kh*kw <= 32) and fewer than 2^31 input elements in total.
+template <int BN, bool FAST>
 __global__ void __launch_bounds__(CV_THREADS, 1)
     conv_tc_kernel(const __grid_constant__ CUtensorMap tmW0, const __grid_constant__ CUtensorMap tmW1,
                    const __grid_constant__ ConvTcParams p) {
@@ -103,7 +109,7 @@ __global__ void __launch_bounds__(CV_THREADS, 1)
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) {
-      ptx::mbar_init(&full_bar[s], 128 + 1);  // 128 gather threads + the TMA thread's expect_tx arrival
+      ptx::mbar_init(&full_bar[s], CV_GATHER_THREADS + 1);  // gather threads + the TMA thread's expect_tx arrival
       ptx::mbar_init(&empty_bar[s], 1);
     }
     for (int b = 0; b < 2; ++b) {
@@ -135,7 +141,7 @@ __global__ void __launch_bounds__(CV_THREADS, 1)
       for (long long tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
         const int nt = (int)(tile % p.tiles_n);
         for (int kb = 0; kb < p.num_k; ++kb) {
-          if (!ptx::mbar_wait(&empty_bar[stage], phase ^ 1)) {
+          if (!ptx::mbar_wait_relaxed(&empty_bar[stage], phase ^ 1, 64)) {
             ok = false;
             break;
           }
@@ -215,7 +221,7 @@ __global__ void __launch_bounds__(CV_THREADS, 1)
         const int buf = use & 1;
         const uint32_t acc_phase = (uint32_t)((use >> 1) & 1);
         ++use;
-        if (!ptx::mbar_wait(&acc_full[buf], acc_phase)) {
+        if (!ptx::mbar_wait_relaxed(&acc_full[buf], acc_phase)) {
           ok = false;
           break;
         }
@@ -237,8 +243,16 @@ __global__ void __launch_bounds__(CV_THREADS, 1)
       if (!ok) break;
       const long long m = (long long)mt * CV_BM + quarter * 32 + lane;
       if (m < p.Mtot) {
-        const long long b = m / p.hw;
-        const int pix = (int)(m % p.hw);
+        long long b;
+        int pix;
+        if (p.Mtot < (1LL << 31)) {  // the usual case: 32-bit division
+          const uint32_t mu = (uint32_t)m, bu = mu / (uint32_t)p.hw;
+          b = bu;
+          pix = (int)(mu - bu * (uint32_t)p.hw);
+        } else {
+          b = m / p.hw;
+          pix = (int)(m % p.hw);
+        }
         float *yb = p.y + (b * p.K) * (long long)p.hw + pix;
         const int n0 = nt * BN + half * HALF;
 #pragma unroll
@@ -250,65 +264,130 @@ __global__ void __launch_bounds__(CV_THREADS, 1)
     }
     if (!ok) s_fail = 1;
   } else {
-    // ---------------- gather: warps 10..13, thread t owns tile row t ----------------
-    const int t = threadIdx.x - CV_GATHER_WARP0 * 32;
+    // ---------------- gather: warps 10..17 ----------------
+    // thread g: tile row (g & 127), q-half (g >> 7): the 16 q's [16*half, 16*half + 16) of each block
+    const int g = threadIdx.x - CV_GATHER_WARP0 * 32;
+    const int t = g & 127, qhalf = g >> 7;
     const int khw = p.kh * p.kw;
+    const long long n_blocks = (blockIdx.x < total_tiles ? (total_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0) *
+                               (long long)p.num_k;
+
+    // per-tile pixel state of this thread
+    bool live = false;
+    int ih0 = 0, iw0 = 0;
+    const float *xpix = p.x;  // x + image base + ih0*W + iw0 (may point before the image; only
+                              // dereferenced together with offsets that land inside it)
+    int pix_idx = 0;          // FAST: the same position as an index into x
+    uint32_t tap_mask = 0;    // FAST: bit (r*kw + s) set iff that tap of this pixel lies inside the image
+    auto set_tile = [&](long long tile) {
+      const int mt = (int)(tile / p.tiles_n);
+      const long long m = (long long)mt * CV_BM + t;
+      live = m < p.Mtot;
+      long long b = 0;
+      int pix = 0;
+      if (live) {
+        if (p.Mtot < (1LL << 31)) {
+          const uint32_t mu = (uint32_t)m, bu = mu / (uint32_t)p.hw;
+          b = bu;
+          pix = (int)(mu - bu * (uint32_t)p.hw);
+        } else {
+          b = m / p.hw;
+          pix = (int)(m % p.hw);
+        }
+      }
+      const int oh = pix / p.Wo, ow = pix - oh * p.Wo;
+      ih0 = oh * p.sH - p.padH;
+      iw0 = ow * p.sW - p.padW;
+      if (FAST) {
+        pix_idx = (int)(b * (long long)p.C * p.H * p.W) + ih0 * p.W + iw0;
+        tap_mask = 0;
+        if (live)
+          for (int r = 0; r < p.kh; ++r)
+            for (int sx = 0; sx < p.kw; ++sx) {
+              const int ih = ih0 + r * p.dH, iw = iw0 + sx * p.dW;
+              if ((unsigned)ih < (unsigned)p.H && (unsigned)iw < (unsigned)p.W) tap_mask |= 1u << (r * p.kw + sx);
+            }
+      } else {
+        xpix = p.x + b * (long long)p.C * p.H * p.W + (long long)ih0 * p.W + iw0;
+      }
+    };
+    // loads the 16 values of block kb for this thread
+    auto load_block = [&](int kb, float(&v)[16]) {
+      // lane j < 16 decomposes q = 32*kb + 16*qhalf + j once for the whole warp
+      const int q = kb * CV_BK + qhalf * 16 + (lane & 15);
+      const int c = q / khw, rs = q - c * khw;
+      const int r = rs / p.kw, sx = rs - r * p.kw;
+      const int my_off = (c * p.H + r * p.dH) * p.W + sx * p.dW;
+      if (FAST) {
+        const int my_bit = q < p.crs ? rs : 32;  // 32 = no tap: a q past the end of the filter
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int off = __shfl_sync(0xffffffffu, my_off, j);
+          const int bit = __shfl_sync(0xffffffffu, my_bit, j);
+          const bool in = bit < 32 && ((tap_mask >> (bit & 31)) & 1u) != 0;
+          const float val = __ldg(p.x + (in ? pix_idx + off : 0));  // always a valid address
+          v[j] = in ? val : 0.f;
+        }
+      } else {
+        const int my_rs = q < p.crs ? ((r * p.dH) << 16) | (sx * p.dW) : 0x40004000;  // out of any image
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int off = __shfl_sync(0xffffffffu, my_off, j);
+          const int drs = __shfl_sync(0xffffffffu, my_rs, j);
+          const int ih = ih0 + (drs >> 16), iw = iw0 + (drs & 0xffff);
+          const bool in = live && (unsigned)ih < (unsigned)p.H && (unsigned)iw < (unsigned)p.W;
+          const float val = __ldg(in ? xpix + off : p.x);
+          v[j] = in ? val : 0.f;
+        }
+      }
+    };
+
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
-    for (long long tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-      const int mt = (int)(tile / p.tiles_n);
-      const long long m = (long long)mt * CV_BM + t;
-      const bool live = m < p.Mtot;
-      const long long b = live ? m / p.hw : 0;
-      const int pix = live ? (int)(m % p.hw) : 0;
-      const int oh = pix / p.Wo, ow = pix % p.Wo;
-      const int ih0 = oh * p.sH - p.padH, iw0 = ow * p.sW - p.padW;
-      const float *xb = p.x + b * (long long)p.C * p.H * p.W;
-      for (int kb = 0; kb < p.num_k; ++kb) {
-        if (!ptx::mbar_wait(&empty_bar[stage], phase ^ 1)) {
-          ok = false;
-          break;
-        }
-        // (c, r, s) of the first q of this block, then stepped incrementally
-        int q = kb * CV_BK;
-        int c = q / khw, rs = q % khw;
-        int r = rs / p.kw, s = rs % p.kw;
-        float v[CV_BK];
+    long long tile = blockIdx.x;
+    int kb = 0;
+    float vn[16];
+    if (n_blocks > 0) {
+      set_tile(tile);
+      load_block(0, vn);
+    }
+    for (long long it = 0; it < n_blocks; ++it) {
+      float v[16];
 #pragma unroll
-        for (int j = 0; j < CV_BK; ++j) {
-          const int ih = ih0 + r * p.dH, iw = iw0 + s * p.dW;
-          const bool in = live && (q + j) < p.crs && ih >= 0 && ih < p.H && iw >= 0 && iw < p.W;
-          v[j] = in ? __ldg(xb + ((long long)c * p.H + ih) * p.W + iw) : 0.f;
-          if (++s == p.kw) {
-            s = 0;
-            if (++r == p.kh) {
-              r = 0;
-              ++c;
-            }
-          }
-        }
-        const uint32_t row_hi = ptx::smem_addr(smem + (size_t)stage * STAGE_BYTES) + (uint32_t)t * 128;
-        const uint32_t row_lo = row_hi + CV_A_BYTES;
-        const uint32_t sw = (uint32_t)(t & 7);
+      for (int j = 0; j < 16; ++j) v[j] = vn[j];
+      // advance to the next block and put its loads in flight before touching shared memory
+      if (++kb == p.num_k) {
+        kb = 0;
+        tile += gridDim.x;
+        if (it + 1 < n_blocks) set_tile(tile);
+      }
+      if (it + 1 < n_blocks) load_block(kb, vn);
+      if (!ptx::mbar_wait(&empty_bar[stage], phase ^ 1)) {
+        ok = false;
+        break;
+      }
+      const uint32_t row_hi = ptx::smem_addr(smem + (size_t)stage * STAGE_BYTES) + (uint32_t)t * 128;
+      const uint32_t row_lo = row_hi + CV_A_BYTES;
+      const uint32_t sw = (uint32_t)(t & 7);
 #pragma unroll
-        for (int ch = 0; ch < 8; ++ch) {
-          float h[4], l[4];
+      for (int ch = 0; ch < 4; ++ch) {
+        float h[4], l[4];
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            h[j] = cv_tf32(v[ch * 4 + j]);
-            l[j] = cv_tf32(__fsub_rn(v[ch * 4 + j], h[j]));
-          }
-          const uint32_t off = ((uint32_t)ch ^ sw) * 16;  // 128-byte swizzle: chunk index XOR (row mod 8)
-          cv_sts128(row_hi + off, h[0], h[1], h[2], h[3]);
-          cv_sts128(row_lo + off, l[0], l[1], l[2], l[3]);
+        for (int j = 0; j < 4; ++j) {
+          h[j] = cv_tf32(v[ch * 4 + j]);
+          l[j] = cv_tf32(__fsub_rn(v[ch * 4 + j], h[j]));
         }
-        ptx::fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor core
-        ptx::mbar_arrive(&full_bar[stage]);
-        if (++stage == stages) {
-          stage = 0;
-          phase ^= 1;
-        }
+        // 128-byte swizzle: 16-byte chunk index XOR (row mod 8)
+        const uint32_t off = ((uint32_t)(qhalf * 4 + ch) ^ sw) * 16;
+        cv_sts128(row_hi + off, h[0], h[1], h[2], h[3]);
+        cv_sts128(row_lo + off, l[0], l[1], l[2], l[3]);
+      }
+      ptx::fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor core
+      ptx::mbar_arrive(&full_bar[stage]);
+      if (++stage == stages) {
+        stage = 0;
+        phase ^= 1;
       }
     }
     if (!ok) s_fail = 1;
@@ -323,10 +402,10 @@ __global__ void __launch_bounds__(CV_THREADS, 1)
   }
 }
 
-template <int BN>
+template <int BN, bool FAST>
 static int launch_conv_tc(b200_engine *e, const CUtensorMap *tm, ConvTcParams &p) {
   constexpr int STAGE_BYTES = 2 * (CV_A_BYTES + BN * 128);
-  auto kern = conv_tc_kernel<BN>;
+  auto kern = conv_tc_kernel<BN, FAST>;
   static int attr_dev_mask = 0;
   const size_t optin = std::min<size_t>(e->smem_optin, 227 * 1024);
   if (!(attr_dev_mask & (1 << (e->device & 31)))) {
@@ -376,9 +455,16 @@ int conv2d_tc(b200_engine *e, const float *x, const float *w, float *y, long lon
   rc = encode_map(e, &tm[0], 4, wf.p0, crs, K, 1, wf.ld, (long long)K * wf.ld, CV_BK, bn, false);
   if (rc == B200_OK) rc = encode_map(e, &tm[1], 4, wf.p1, crs, K, 1, wf.ld, (long long)K * wf.ld, CV_BK, bn, false);
   if (rc == B200_OK) {
-    if (bn == 128) rc = launch_conv_tc<128>(e, tm, p);
-    else if (bn == 64) rc = launch_conv_tc<64>(e, tm, p);
-    else rc = launch_conv_tc<32>(e, tm, p);
+    const bool fast = kh * kw <= 32 && B * (long long)C * H * W < (1LL << 31);
+    if (fast) {
+      if (bn == 128) rc = launch_conv_tc<128, true>(e, tm, p);
+      else if (bn == 64) rc = launch_conv_tc<64, true>(e, tm, p);
+      else rc = launch_conv_tc<32, true>(e, tm, p);
+    } else {
+      if (bn == 128) rc = launch_conv_tc<128, false>(e, tm, p);
+      else if (bn == 64) rc = launch_conv_tc<64, false>(e, tm, p);
+      else rc = launch_conv_tc<32, false>(e, tm, p);
+    }
   }
   b200_put(e, blk[0], 0);
   b200_put(e, blk[1], 0);

@@ -291,7 +291,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
         const int buf = use & 1;
         const uint32_t acc_phase = (uint32_t)((use >> 1) & 1);
         ++use;
-        if (!ptx::mbar_wait(&acc_full[buf], acc_phase)) {
+        if (!ptx::mbar_wait_relaxed(&acc_full[buf], acc_phase)) {
           ok = false;
           break;
         }
@@ -321,7 +321,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
           const int buf = use & 1;
           const uint32_t acc_phase = (uint32_t)((use >> 1) & 1);
           ++use;
-          if (!ptx::mbar_wait(&acc_full[buf], acc_phase)) {
+          if (!ptx::mbar_wait_relaxed(&acc_full[buf], acc_phase)) {
             ok = false;
             break;
           }

@@ -62,6 +62,23 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, uint64
   }
 }
 
+// The same wait for roles with slack (an epilogue that is handed work every few k-blocks, a
+// producer that runs stages ahead): it sleeps between polls, so that the polling warp does not
+// take issue slots from the warps it is waiting for.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint64_t *bar, uint32_t parity, unsigned sleep_ns = 128,
+                                                  uint64_t limit_ns = 2000000000ull) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = globaltimer_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i) {
+      __nanosleep(sleep_ns);
+      if (mbar_try_wait(bar, parity)) return true;
+    }
+    if (globaltimer_ns() - t0 > limit_ns) return false;
+  }
+}
+
 // ---- proxies / fences ---------------------------------------------------------------------------
 // generic-proxy writes to shared memory -> visible to the async proxy (TMA store, tcgen05.mma)
 __device__ __forceinline__ void fence_proxy_async_smem() {

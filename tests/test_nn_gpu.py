@@ -98,6 +98,7 @@ CONV_CASES = [
     (2, 5, 17, 19, 7, 3, 5, (2, 1), (2, 3), (1, 1)),       # odd everything
     (1, 4, 20, 20, 6, 3, 3, (2, 2), (1, 1), (2, 2)),       # dilation
     (1, 2, 5, 5, 3, 3, 3, (0, 0), (1, 1), (1, 1)),         # tiny: CUDA-core path
+    (1, 2, 20, 20, 16, 6, 6, (2, 2), (1, 1), (1, 1)),      # 36 taps per channel: the general gather path
     (70, 3, 12, 12, 20, 3, 3, (1, 1), (1, 1), (1, 1)),     # more images than one scratch chunk holds? (small)
 ]
 

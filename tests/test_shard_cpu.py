@@ -1,0 +1,76 @@
+"""The multi-rank path on CPU: two gloo ranks shard a batch, run the graph on their slices (with the
+CPU oracle standing in for the device) and the pieces reassemble to the single-rank result; the
+timing reduction takes the slowest rank."""
+import os
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from gorgonia_b200 import shard
+
+
+def test_shard_bounds_partition_the_batch():
+    for total in (0, 1, 7, 64, 256, 8192):
+        for world in (1, 2, 3, 4, 8):
+            b = shard.shard_bounds(total, world)
+            assert b[0][0] == 0 and b[-1][1] == total
+            assert all(b[i][1] == b[i + 1][0] for i in range(world - 1))
+            sizes = [y - x for x, y in b]
+            assert max(sizes) - min(sizes) <= 1
+    assert shard.shard_bounds(8192, 8) == [(i * 1024, (i + 1) * 1024) for i in range(8)]
+    with pytest.raises(ValueError):
+        shard.shard_bounds(4, 0)
+
+
+class _HostLeNet:
+    pass
+
+
+def _host_lenet():
+    from gorgonia_b200 import tapes
+    g = np.random.Generator(np.random.Philox(5))
+    h, ch = _HostLeNet(), tapes.LeNet.CH
+    h.wc_host = [tapes.he_normal(g, (ch[i + 1], ch[i], 3, 3), ch[i] * 9) for i in range(3)]
+    h.wd_host = [tapes.he_normal(g, (1152, 625), 1152), tapes.he_normal(g, (625, 10), 625)]
+    return h
+
+
+def _worker(rank, world, port, total, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from oracle import graphs
+        model = _host_lenet()                       # replicated weights: same seed on every rank
+        x = np.random.Generator(np.random.Philox(11)).random((total, 1, 28, 28), dtype=np.float32)
+        a, b = shard.my_shard(total, rank, world)
+        local = graphs.lenet(model, x[a:b])
+        whole = shard.all_gather_rows(local, total, dist)
+        slowest = shard.max_over_ranks(10.0 + rank, dist)
+        dist.barrier()
+        if rank == 0:
+            q.put((whole, slowest))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_ranks_reassemble_the_single_rank_result():
+    total, world = 9, 2                              # uneven on purpose: shards of 5 and 4
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29500 + os.getpid() % 1000
+    procs = [ctx.Process(target=_worker, args=(r, world, port, total, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    whole, slowest = q.get(timeout=120)
+    for p in procs:
+        p.join(60)
+        assert p.exitcode == 0
+    from oracle import graphs
+    x = np.random.Generator(np.random.Philox(11)).random((total, 1, 28, 28), dtype=np.float32)
+    want = graphs.lenet(_host_lenet(), x)
+    assert whole.shape == want.shape
+    assert np.array_equal(whole, want)               # samples are independent: sharding changes nothing
+    assert slowest == 11.0
