@@ -83,9 +83,14 @@ __device__ __forceinline__ void cv_tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) 
       : "memory");
 }
 
-// FAST: the common case, which lets the gather run on 32-bit indices and a per-pixel tap mask:
-// at most 32 taps per channel (kh*kw <= 32) and fewer than 2^31 input elements in total.
-template <int BN, bool FAST>
+// MODE 0: general. MODE 1 ("fast"): at most 32 taps per channel (kh*kw <= 32) and fewer than 2^31
+// input elements in total, which lets the gather run on 32-bit indices and a per-pixel tap mask.
+// MODE 2 ("tap-major"): additionally C is a multiple of 32; the reduction index is reordered to
+// q' = (tap, channel) (the filters are permuted to match when they are split), so a k-block is ONE
+// tap and 32 consecutive channels: one bounds decision per block and a constant stride between a
+// thread's elements instead of a (c, r, s) decomposition per element. Reordering a sum changes
+// its rounding, not its value; the result stays within the matrix-multiply tolerance.
+template <int BN, int MODE>
 __global__ void __launch_bounds__(CV_THREADS, 1)
     conv_tc_kernel(const __grid_constant__ CUtensorMap tmW0, const __grid_constant__ CUtensorMap tmW1,
                    const __grid_constant__ ConvTcParams p) {
@@ -277,8 +282,8 @@ __global__ void __launch_bounds__(CV_THREADS, 1)
     int ih0 = 0, iw0 = 0;
     const float *xpix = p.x;  // x + image base + ih0*W + iw0 (may point before the image; only
                               // dereferenced together with offsets that land inside it)
-    int pix_idx = 0;          // FAST: the same position as an index into x
-    uint32_t tap_mask = 0;    // FAST: bit (r*kw + s) set iff that tap of this pixel lies inside the image
+    int pix_idx = 0;          // modes 1, 2: the same position as an index into x
+    uint32_t tap_mask = 0;    // modes 1, 2: bit (r*kw + s) set iff that tap of this pixel lies inside the image
     auto set_tile = [&](long long tile) {
       const int mt = (int)(tile / p.tiles_n);
       const long long m = (long long)mt * CV_BM + t;
@@ -298,7 +303,7 @@ __global__ void __launch_bounds__(CV_THREADS, 1)
       const int oh = pix / p.Wo, ow = pix - oh * p.Wo;
       ih0 = oh * p.sH - p.padH;
       iw0 = ow * p.sW - p.padW;
-      if (FAST) {
+      if (MODE >= 1) {
         pix_idx = (int)(b * (long long)p.C * p.H * p.W) + ih0 * p.W + iw0;
         tap_mask = 0;
         if (live)
@@ -313,12 +318,27 @@ __global__ void __launch_bounds__(CV_THREADS, 1)
     };
     // loads the 16 values of block kb for this thread
     auto load_block = [&](int kb, float(&v)[16]) {
+      if (MODE == 2) {
+        const int cpb = p.C >> 5;  // k-blocks per tap
+        const int tap = kb / cpb, cb = kb - tap * cpb;
+        const int r = tap / p.kw, sx = tap - r * p.kw;
+        const bool in = ((tap_mask >> tap) & 1u) != 0;
+        const int idx = pix_idx + ((cb * 32 + qhalf * 16) * p.H + r * p.dH) * p.W + sx * p.dW;
+        const float *base = p.x + (in ? idx : 0);   // always a valid address
+        const int step = in ? p.H * p.W : 0;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const float val = __ldg(base + (long long)j * step);
+          v[j] = in ? val : 0.f;
+        }
+        return;
+      }
       // lane j < 16 decomposes q = 32*kb + 16*qhalf + j once for the whole warp
       const int q = kb * CV_BK + qhalf * 16 + (lane & 15);
       const int c = q / khw, rs = q - c * khw;
       const int r = rs / p.kw, sx = rs - r * p.kw;
       const int my_off = (c * p.H + r * p.dH) * p.W + sx * p.dW;
-      if (FAST) {
+      if (MODE == 1) {
         const int my_bit = q < p.crs ? rs : 32;  // 32 = no tap: a q past the end of the filter
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
@@ -402,10 +422,26 @@ __global__ void __launch_bounds__(CV_THREADS, 1)
   }
 }
 
-template <int BN, bool FAST>
+// w (K, C, taps) -> head/tail (K, taps, C): out[k][tap*C + c] = split(w[k][c*taps + tap])
+__global__ void __launch_bounds__(256) split_permute_filters_kernel(const float *__restrict__ w, float *__restrict__ hi,
+                                                                    float *__restrict__ lo, int K, int C, int taps) {
+  const long long total = (long long)K * C * taps;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += stride) {
+    const int c = (int)(t % C);
+    const int tap = (int)((t / C) % taps);
+    const long long k = t / ((long long)C * taps);
+    const float v = w[(k * C + c) * taps + tap];
+    const float h = cv_tf32(v);
+    hi[t] = h;
+    lo[t] = cv_tf32(__fsub_rn(v, h));
+  }
+}
+
+template <int BN, int MODE>
 static int launch_conv_tc(b200_engine *e, const CUtensorMap *tm, ConvTcParams &p) {
   constexpr int STAGE_BYTES = 2 * (CV_A_BYTES + BN * 128);
-  auto kern = conv_tc_kernel<BN, FAST>;
+  auto kern = conv_tc_kernel<BN, MODE>;
   static int attr_dev_mask = 0;
   const size_t optin = std::min<size_t>(e->smem_optin, 227 * 1024);
   if (!(attr_dev_mask & (1 << (e->device & 31)))) {
@@ -430,10 +466,30 @@ int conv2d_tc(b200_engine *e, const float *x, const float *w, float *y, long lon
               int kh, int kw, int padH, int padW, int sH, int sW, int dH, int dW, int Ho, int Wo,
               const Epilogue &ep) {
   const int crs = C * kh * kw;
+  const bool fast = kh * kw <= 32 && B * (long long)C * H * W < (1LL << 31);
+  const int mode = !fast ? 0 : (C % 32 == 0 ? 2 : 1);
   TcOperand wf;
   void *blk[2] = {nullptr, nullptr};
-  int rc = split_operand_tf32(e, w, K, crs, crs, 1, 0, &wf, &blk[0], &blk[1]);
-  if (rc != B200_OK) return rc;
+  int rc;
+  if (mode == 2) {
+    // filters split into TF32 head/tail AND reordered to (tap, channel) along the reduction index
+    rc = b200_get(e, (long long)K * crs * 4, &blk[0]);
+    if (rc == B200_OK) rc = b200_get(e, (long long)K * crs * 4, &blk[1]);
+    if (rc != B200_OK) {
+      if (blk[0]) b200_put(e, blk[0], 0);
+      return rc;
+    }
+    const long long total = (long long)K * crs;
+    const int blocks = (int)std::max<long long>(1, std::min<long long>((total + 255) / 256, e->sm_count * 16LL));
+    split_permute_filters_kernel<<<blocks, 256, 0, e->stream>>>(w, (float *)blk[0], (float *)blk[1], K, C, kh * kw);
+    B200_CHECK_LAUNCH(e, "split_permute_filters_kernel");
+    wf.p0 = blk[0];
+    wf.p1 = blk[1];
+    wf.ld = crs;
+  } else {
+    rc = split_operand_tf32(e, w, K, crs, crs, 1, 0, &wf, &blk[0], &blk[1]);
+    if (rc != B200_OK) return rc;
+  }
   int bn = 128;
   while (bn > 32 && bn / 2 >= K) bn /= 2;
   ConvTcParams p = ConvTcParams();
@@ -455,15 +511,18 @@ int conv2d_tc(b200_engine *e, const float *x, const float *w, float *y, long lon
   rc = encode_map(e, &tm[0], 4, wf.p0, crs, K, 1, wf.ld, (long long)K * wf.ld, CV_BK, bn, false);
   if (rc == B200_OK) rc = encode_map(e, &tm[1], 4, wf.p1, crs, K, 1, wf.ld, (long long)K * wf.ld, CV_BK, bn, false);
   if (rc == B200_OK) {
-    const bool fast = kh * kw <= 32 && B * (long long)C * H * W < (1LL << 31);
-    if (fast) {
-      if (bn == 128) rc = launch_conv_tc<128, true>(e, tm, p);
-      else if (bn == 64) rc = launch_conv_tc<64, true>(e, tm, p);
-      else rc = launch_conv_tc<32, true>(e, tm, p);
+    if (mode == 2) {
+      if (bn == 128) rc = launch_conv_tc<128, 2>(e, tm, p);
+      else if (bn == 64) rc = launch_conv_tc<64, 2>(e, tm, p);
+      else rc = launch_conv_tc<32, 2>(e, tm, p);
+    } else if (mode == 1) {
+      if (bn == 128) rc = launch_conv_tc<128, 1>(e, tm, p);
+      else if (bn == 64) rc = launch_conv_tc<64, 1>(e, tm, p);
+      else rc = launch_conv_tc<32, 1>(e, tm, p);
     } else {
-      if (bn == 128) rc = launch_conv_tc<128, false>(e, tm, p);
-      else if (bn == 64) rc = launch_conv_tc<64, false>(e, tm, p);
-      else rc = launch_conv_tc<32, false>(e, tm, p);
+      if (bn == 128) rc = launch_conv_tc<128, 0>(e, tm, p);
+      else if (bn == 64) rc = launch_conv_tc<64, 0>(e, tm, p);
+      else rc = launch_conv_tc<32, 0>(e, tm, p);
     }
   }
   b200_put(e, blk[0], 0);
