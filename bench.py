@@ -115,6 +115,9 @@ class Ctx:
         self.world = int(os.environ.get("WORLD_SIZE", "1"))
         self.dist = None
         if self.world > 1:
+            # NCCL_DEBUG=VERSION makes NCCL print a banner on stdout, where the one JSON line belongs
+            if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
+                os.environ["NCCL_DEBUG"] = "WARN"
             import torch.distributed as dist
             torch.cuda.set_device(self.local_rank)
             dist.init_process_group("nccl", device_id=torch.device("cuda", self.local_rank))

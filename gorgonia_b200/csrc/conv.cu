@@ -22,6 +22,87 @@ int conv2d_tc(b200_engine *e, const float *x, const float *w, float *y, long lon
 int gemm_simt(b200_engine *e, int dtype, int transA, int transB, long long M, long long N, long long K,
               const void *A, long long lda, const void *B, long long ldb, void *C, long long ldc, long long batch,
               long long strideA, long long strideB, long long strideC, const Epilogue &ep);
+// ---- direct convolution for the first layer of a network -------------------------------------
+// When C*kh*kw <= 32 and K <= 32 (LeNet conv0: 1x3x3 -> 32; tiny-YOLO conv0: 3x3x3 -> 16) a pixel
+// needs at most 32 inputs and the layer is bound by writing its output, not by arithmetic: one
+// thread per output pixel keeps its taps in registers, the filters sit in shared memory laid out
+// [q][K] so that all threads read the same address (a broadcast), and the K results of a pixel go
+// out as K stores that are each contiguous across the warp (NCHW). fp32 FMA in q order.
+template <int KP>  // filters padded to a multiple of 4, at most 32
+__global__ void __launch_bounds__(256) conv_direct_small_kernel(const float *__restrict__ x,
+                                                                const float *__restrict__ w, float *__restrict__ y,
+                                                                long long Mtot, int C, int H, int W, int K, int Ho,
+                                                                int Wo, int kh, int kw, int padH, int padW, int sH,
+                                                                int sW, int dH, int dW, Epilogue ep) {
+  __shared__ __align__(16) float ws[32 * KP];
+  const int crs = C * kh * kw, hw = Ho * Wo;
+  for (int i = threadIdx.x; i < 32 * KP; i += blockDim.x) {
+    const int q = i / KP, k = i % KP;
+    ws[i] = (q < crs && k < K) ? w[k * crs + q] : 0.f;
+  }
+  __syncthreads();
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long m = (long long)blockIdx.x * blockDim.x + threadIdx.x; m < Mtot; m += stride) {
+    const long long b = m / hw;
+    const int pix = (int)(m - b * hw);
+    const int oh = pix / Wo, ow = pix - oh * Wo;
+    const int ih0 = oh * sH - padH, iw0 = ow * sW - padW;
+    const float *xb = x + b * (long long)C * H * W;
+    float v[32];
+    int c = 0, r = 0, sx = 0;
+#pragma unroll
+    for (int q = 0; q < 32; ++q) {
+      const int ih = ih0 + r * dH, iw = iw0 + sx * dW;
+      const bool in = q < crs && (unsigned)ih < (unsigned)H && (unsigned)iw < (unsigned)W;
+      v[q] = in ? __ldg(xb + ((long long)c * H + ih) * W + iw) : 0.f;
+      if (++sx == kw) {
+        sx = 0;
+        if (++r == kh) {
+          r = 0;
+          ++c;
+        }
+      }
+    }
+    float acc[KP];
+#pragma unroll
+    for (int k = 0; k < KP; ++k) acc[k] = 0.f;
+#pragma unroll
+    for (int q = 0; q < 32; ++q) {
+      if (q < crs) {
+#pragma unroll
+        for (int k4 = 0; k4 < KP; k4 += 4) {
+          const float4 wv = *reinterpret_cast<const float4 *>(&ws[q * KP + k4]);
+          acc[k4 + 0] = fmaf(v[q], wv.x, acc[k4 + 0]);
+          acc[k4 + 1] = fmaf(v[q], wv.y, acc[k4 + 1]);
+          acc[k4 + 2] = fmaf(v[q], wv.z, acc[k4 + 2]);
+          acc[k4 + 3] = fmaf(v[q], wv.w, acc[k4 + 3]);
+        }
+      }
+    }
+    float *yb = y + (b * K) * (long long)hw + pix;
+#pragma unroll
+    for (int k = 0; k < KP; ++k)
+      if (k < K) yb[(long long)k * hw] = apply_epilogue<float>(acc[k], ep, k, 0);
+  }
+}
+
+static int conv_direct_small(b200_engine *e, const float *x, const float *w, float *y, long long B, int C, int H,
+                             int W, int K, int kh, int kw, int padH, int padW, int sH, int sW, int dH, int dW, int Ho,
+                             int Wo, const Epilogue &ep) {
+  const long long Mtot = B * Ho * Wo;
+  const int blocks = (int)std::max<long long>(1, std::min<long long>((Mtot + 255) / 256, (long long)e->sm_count * 16));
+#define B200_DIRECT(KP)                                                                                        \
+  conv_direct_small_kernel<KP><<<blocks, 256, 0, e->stream>>>(x, w, y, Mtot, C, H, W, K, Ho, Wo, kh, kw, padH, padW, \
+                                                             sH, sW, dH, dW, ep)
+  if (K <= 8) B200_DIRECT(8);
+  else if (K <= 16) B200_DIRECT(16);
+  else if (K <= 24) B200_DIRECT(24);
+  else B200_DIRECT(32);
+#undef B200_DIRECT
+  B200_CHECK_LAUNCH(e, "conv_direct_small_kernel");
+  return B200_OK;
+}
+
 // scratch budget for the col data of one chunk (head + tail together)
 static const long long kColChunkBytes = 64LL << 20;
 
@@ -68,6 +149,9 @@ int b200_conv2d_fwd(b200_engine *e, int dtype, const void *x, const void *w, voi
   const long long img_bytes = hw * crs * (long long)es;
   long long chunk = std::max<long long>(1, std::min<long long>(B, kColChunkBytes / std::max<long long>(1, img_bytes)));
 
+  if (dtype == B200_F32 && crs <= 32 && K <= 32 && H < (1LL << 30) && W < (1LL << 30))
+    return conv_direct_small(e, (const float *)x, (const float *)w, (float *)y, B, (int)C, (int)H, (int)W, (int)K, kh,
+                             kw, pad_h, pad_w, stride_h, stride_w, dil_h, dil_w, (int)Ho, (int)Wo, ep);
   if (tc)
     return conv2d_tc(e, (const float *)x, (const float *)w, (float *)y, B, (int)C, (int)H, (int)W, (int)K, kh, kw,
                      pad_h, pad_w, stride_h, stride_w, dil_h, dil_w, (int)Ho, (int)Wo, ep);

@@ -365,24 +365,26 @@ __global__ void __launch_bounds__(CV_THREADS, 1)
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
-    long long tile = blockIdx.x;
-    int kb = 0;
-    float vn[16];
-    if (n_blocks > 0) {
-      set_tile(tile);
-      load_block(0, vn);
-    }
-    for (long long it = 0; it < n_blocks; ++it) {
-      float v[16];
-#pragma unroll
-      for (int j = 0; j < 16; ++j) v[j] = vn[j];
-      // advance to the next block and put its loads in flight before touching shared memory
-      if (++kb == p.num_k) {
-        kb = 0;
-        tile += gridDim.x;
-        if (it + 1 < n_blocks) set_tile(tile);
+    // Load cursor: runs two k-blocks ahead of the block being converted, so that two blocks of
+    // loads (32 KB per CTA) are in flight while a third is converted and stored. Bytes in flight
+    // over the L2 latency is what bounds the gather.
+    long long ltile = blockIdx.x, issued = 0;
+    int lkb = 0;
+    auto issue_next = [&](float(&dst)[16]) {
+      if (issued >= n_blocks) return;
+      if (lkb == 0) set_tile(ltile);
+      load_block(lkb, dst);
+      if (++lkb == p.num_k) {
+        lkb = 0;
+        ltile += gridDim.x;
       }
-      if (it + 1 < n_blocks) load_block(kb, vn);
+      ++issued;
+    };
+    float v[16], v1[16], v2[16];
+    issue_next(v);
+    issue_next(v1);
+    for (long long it = 0; it < n_blocks; ++it) {
+      issue_next(v2);
       if (!ptx::mbar_wait(&empty_bar[stage], phase ^ 1)) {
         ok = false;
         break;
@@ -408,6 +410,11 @@ __global__ void __launch_bounds__(CV_THREADS, 1)
       if (++stage == stages) {
         stage = 0;
         phase ^= 1;
+      }
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        v[j] = v1[j];
+        v1[j] = v2[j];
       }
     }
     if (!ok) s_fail = 1;

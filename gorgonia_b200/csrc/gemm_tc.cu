@@ -441,7 +441,10 @@ static bool tc_eligible(int dtype, long long M, long long N, long long K, long l
   if (M < 1 || N < 1 || K < 1) return false;
   // tiny problems: a 128-row tile would be mostly padding and the launch is latency-bound anyway
   if (M * N * K < 64LL * 64 * 64) return false;
-  if (N < 16) return false;
+  // bf16 operands are read in place, so a narrow B cannot meet TMA's pitch rule; float32 operands
+  // are re-pitched by the split pass and any N works (the tile is padded with zero columns)
+  if (N < 16 && dtype == B200_BF16) return false;
+  if (N < 16 && M < 128) return false;
   if ((uintptr_t)C % 4 != 0) return false;
   if (dtype == B200_BF16) {
     if (((uintptr_t)A | (uintptr_t)B) % 16 != 0) return false;

@@ -56,6 +56,35 @@ __global__ void __launch_bounds__(256) maxpool_kernel(const T *__restrict__ x, T
   }
 }
 
+// The pooling every config here uses: 2x2 window, stride 2, no padding, W a multiple of 4, no mask.
+// One thread makes two neighbouring outputs from two 16-byte loads (one per input row) and writes
+// them with one 8-byte store. Same comparison order as the general kernel: row-major inside the
+// window, strict '>', starting from -FLT_MAX.
+__global__ void __launch_bounds__(256) maxpool2x2_kernel(const float *__restrict__ x, float *__restrict__ y,
+                                                         long long planes, int H, int W, int Ho, int Wo) {
+  const int pairs = Wo >> 1;  // Wo = W/2 is even because W % 4 == 0
+  const long long total = planes * Ho * pairs;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += stride) {
+    const int j = (int)(t % pairs);
+    const int ph = (int)((t / pairs) % Ho);
+    const long long plane = t / ((long long)pairs * Ho);
+    const float *in = x + (plane * H + 2 * ph) * (long long)W + 4 * j;
+    const float4 a = *reinterpret_cast<const float4 *>(in);
+    const float4 b = *reinterpret_cast<const float4 *>(in + W);
+    float m0 = -FLT_MAX, m1 = -FLT_MAX;
+    if (a.x > m0) m0 = a.x;
+    if (a.y > m0) m0 = a.y;
+    if (b.x > m0) m0 = b.x;
+    if (b.y > m0) m0 = b.y;
+    if (a.z > m1) m1 = a.z;
+    if (a.w > m1) m1 = a.w;
+    if (b.z > m1) m1 = b.z;
+    if (b.w > m1) m1 = b.w;
+    *reinterpret_cast<float2 *>(y + (plane * Ho + ph) * (long long)Wo + 2 * j) = make_float2(m0, m1);
+  }
+}
+
 // ---- im2col ------------------------------------------------------------------------------------
 // col[(b, oh, ow), (c, r, s)] = x[b, c, oh*sH - padH + r*dH, ow*sW - padW + s*dW], 0 outside.
 // One thread per column element; consecutive threads write consecutive (c, r, s), which makes
@@ -202,6 +231,14 @@ int b200_maxpool2d_fwd(b200_engine *e, int dtype, const void *x, void *y, int64_
   const int oh0 = explicit_padding ? pad_south : pad_north;
   const int ow0 = explicit_padding ? pad_east : pad_west;
   const long long total = B * C * Ho * Wo;
+  if (dtype == B200_F32 && !mask && kh == 2 && kw == 2 && stride_h == 2 && stride_w == 2 && pad_north == 0 &&
+      pad_south == 0 && pad_west == 0 && pad_east == 0 && W % 4 == 0 && (uintptr_t)x % 16 == 0 &&
+      (uintptr_t)y % 8 == 0) {
+    maxpool2x2_kernel<<<grid_for(e, total / 2), 256, 0, e->stream>>>((const float *)x, (float *)y, B * C, (int)H,
+                                                                    (int)W, (int)Ho, (int)Wo);
+    B200_CHECK_LAUNCH(e, "maxpool2x2_kernel");
+    return B200_OK;
+  }
   if (dtype == B200_F32)
     maxpool_kernel<float><<<grid_for(e, total), 256, 0, e->stream>>>((const float *)x, (float *)y, (long long *)mask,
                                                                     B * C, (int)H, (int)W, (int)Ho, (int)Wo, kh, kw,

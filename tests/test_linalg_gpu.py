@@ -21,7 +21,8 @@ def _mats(seed, M, N, K, transA, transB, dt=np.float32, scale=0.02):
 
 
 TC_SHAPES = [(128, 128, 64), (256, 256, 256), (1024, 1024, 1024), (200, 328, 136), (130, 70, 40), (64, 1000, 512),
-             (1, 512, 512), (777, 33, 1001), (256, 300, 784), (4096, 64, 27)]
+             (1, 512, 512), (777, 33, 1001), (256, 300, 784), (4096, 64, 27),
+             (512, 10, 625), (300, 3, 512)]
 
 
 @pytest.mark.parametrize("transA,transB", [(False, False), (False, True), (True, False), (True, True)])
