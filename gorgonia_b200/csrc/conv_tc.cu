@@ -61,6 +61,7 @@ struct ConvTcParams {
   int tiles_m, tiles_n;
   int stages;
   Epilogue ep;     // bias_kind ROW = per output channel
+  const float *zero;  // one word of device memory that always holds 0.0f
   int *err_flag;
 };
 
@@ -85,10 +86,10 @@ __device__ __forceinline__ void cv_tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) 
 
 // MODE 0: general. MODE 1 ("fast"): at most 32 taps per channel (kh*kw <= 32) and fewer than 2^31
 // input elements in total, which lets the gather run on 32-bit indices and a per-pixel tap mask.
-// MODE 2 ("tap-major"): additionally C is a multiple of 32; the reduction index is reordered to
-// q' = (tap, channel) (the filters are permuted to match when they are split), so a k-block is ONE
-// tap and 32 consecutive channels: one bounds decision per block and a constant stride between a
-// thread's elements instead of a (c, r, s) decomposition per element. Reordering a sum changes
+// MODE 2 ("tap-major"): additionally C is a multiple of 16; the reduction index is reordered to
+// q' = (tap, channel) (the filters are permuted to match when they are split), so the 16 elements
+// a gather thread owns in a k-block are ONE tap and 16 consecutive channels: one bounds decision
+// and a constant stride instead of a (c, r, s) decomposition per element. Reordering a sum changes
 // its rounding, not its value; the result stays within the matrix-multiply tolerance.
 template <int BN, int MODE>
 __global__ void __launch_bounds__(CV_THREADS, 1)
@@ -316,20 +317,35 @@ __global__ void __launch_bounds__(CV_THREADS, 1)
         xpix = p.x + b * (long long)p.C * p.H * p.W + (long long)ih0 * p.W + iw0;
       }
     };
-    // loads the 16 values of block kb for this thread
+    // Issues the loads of the 16 values of block kb for this thread. A tap outside the image (or a
+    // q past the end of the filter) is read from p.zero, a word that always holds 0.0f, so every
+    // load is valid and nothing has to look at the loaded values here: an instruction that
+    // consumed a load at this point would make the warp wait for it and undo the prefetch.
+    int m2_tap = 0, m2_c0 = 0, m2_r = 0, m2_sx = 0;  // MODE 2: tap / first channel of the next block
     auto load_block = [&](int kb, float(&v)[16]) {
       if (MODE == 2) {
-        const int cpb = p.C >> 5;  // k-blocks per tap
-        const int tap = kb / cpb, cb = kb - tap * cpb;
-        const int r = tap / p.kw, sx = tap - r * p.kw;
-        const bool in = ((tap_mask >> tap) & 1u) != 0;
-        const int idx = pix_idx + ((cb * 32 + qhalf * 16) * p.H + r * p.dH) * p.W + sx * p.dW;
-        const float *base = p.x + (in ? idx : 0);   // always a valid address
+        // q' = 32*kb + 16*qhalf + j = tap*C + channel; C % 16 == 0, so the 16 share one tap
+        if (kb == 0) {
+          m2_tap = (qhalf * 16) / p.C;
+          m2_c0 = qhalf * 16 - m2_tap * p.C;
+          m2_r = m2_tap / p.kw;
+          m2_sx = m2_tap - m2_r * p.kw;
+        }
+        const bool in = m2_tap < khw && ((tap_mask >> (m2_tap & 31)) & 1u) != 0;
+        const int idx = pix_idx + ((m2_c0 * p.H) + m2_r * p.dH) * p.W + m2_sx * p.dW;
+        const float *base = in ? p.x + idx : p.zero;
         const int step = in ? p.H * p.W : 0;
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const float val = __ldg(base + (long long)j * step);
-          v[j] = in ? val : 0.f;
+        for (int j = 0; j < 16; ++j) v[j] = __ldg(base + (long long)j * step);
+        // step to the next block: 32 channels further, wrapping into the next tap(s)
+        m2_c0 += CV_BK;
+        while (m2_c0 >= p.C) {
+          m2_c0 -= p.C;
+          ++m2_tap;
+          if (++m2_sx == p.kw) {
+            m2_sx = 0;
+            ++m2_r;
+          }
         }
         return;
       }
@@ -345,8 +361,7 @@ __global__ void __launch_bounds__(CV_THREADS, 1)
           const int off = __shfl_sync(0xffffffffu, my_off, j);
           const int bit = __shfl_sync(0xffffffffu, my_bit, j);
           const bool in = bit < 32 && ((tap_mask >> (bit & 31)) & 1u) != 0;
-          const float val = __ldg(p.x + (in ? pix_idx + off : 0));  // always a valid address
-          v[j] = in ? val : 0.f;
+          v[j] = __ldg(in ? p.x + (pix_idx + off) : p.zero);
         }
       } else {
         const int my_rs = q < p.crs ? ((r * p.dH) << 16) | (sx * p.dW) : 0x40004000;  // out of any image
@@ -356,8 +371,7 @@ __global__ void __launch_bounds__(CV_THREADS, 1)
           const int drs = __shfl_sync(0xffffffffu, my_rs, j);
           const int ih = ih0 + (drs >> 16), iw = iw0 + (drs & 0xffff);
           const bool in = live && (unsigned)ih < (unsigned)p.H && (unsigned)iw < (unsigned)p.W;
-          const float val = __ldg(in ? xpix + off : p.x);
-          v[j] = in ? val : 0.f;
+          v[j] = __ldg(in ? xpix + off : p.zero);
         }
       }
     };
@@ -380,15 +394,9 @@ __global__ void __launch_bounds__(CV_THREADS, 1)
       }
       ++issued;
     };
-    float v[16], v1[16], v2[16];
-    issue_next(v);
-    issue_next(v1);
-    for (long long it = 0; it < n_blocks; ++it) {
-      issue_next(v2);
-      if (!ptx::mbar_wait(&empty_bar[stage], phase ^ 1)) {
-        ok = false;
-        break;
-      }
+    // waits for the ring slot, converts one block to TF32 head/tail and publishes it
+    auto convert_store = [&](const float(&v)[16]) -> bool {
+      if (!ptx::mbar_wait(&empty_bar[stage], phase ^ 1)) return false;
       const uint32_t row_hi = ptx::smem_addr(smem + (size_t)stage * STAGE_BYTES) + (uint32_t)t * 128;
       const uint32_t row_lo = row_hi + CV_A_BYTES;
       const uint32_t sw = (uint32_t)(t & 7);
@@ -411,11 +419,23 @@ __global__ void __launch_bounds__(CV_THREADS, 1)
         stage = 0;
         phase ^= 1;
       }
-#pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        v[j] = v1[j];
-        v1[j] = v2[j];
-      }
+      return true;
+    };
+    // three register buffers in rotation, spelled out so that every index is static
+    float va[16], vb[16], vc[16];
+    issue_next(va);
+    issue_next(vb);
+    long long it = 0;
+    while (it < n_blocks) {
+      issue_next(vc);
+      if (!(ok = convert_store(va))) break;
+      if (++it >= n_blocks) break;
+      issue_next(va);
+      if (!(ok = convert_store(vb))) break;
+      if (++it >= n_blocks) break;
+      issue_next(vb);
+      if (!(ok = convert_store(vc))) break;
+      ++it;
     }
     if (!ok) s_fail = 1;
   }
@@ -474,7 +494,7 @@ int conv2d_tc(b200_engine *e, const float *x, const float *w, float *y, long lon
               const Epilogue &ep) {
   const int crs = C * kh * kw;
   const bool fast = kh * kw <= 32 && B * (long long)C * H * W < (1LL << 31);
-  const int mode = !fast ? 0 : (C % 32 == 0 ? 2 : 1);
+  const int mode = !fast ? 0 : (C % 16 == 0 ? 2 : 1);
   TcOperand wf;
   void *blk[2] = {nullptr, nullptr};
   int rc;
@@ -513,6 +533,7 @@ int conv2d_tc(b200_engine *e, const float *x, const float *w, float *y, long lon
   p.ep = ep;
   // the kernel indexes the bias by output channel, which it passes as the "row" of the epilogue
   p.err_flag = e->d_flags + 2;
+  p.zero = reinterpret_cast<const float *>(e->d_flags + 8);  // zeroed at engine creation, never written
   CUtensorMap tm[2];
   memset(tm, 0, sizeof tm);
   rc = encode_map(e, &tm[0], 4, wf.p0, crs, K, 1, wf.ld, (long long)K * wf.ld, CV_BK, bn, false);
