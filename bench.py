@@ -266,7 +266,13 @@ def wl_elementwise(ctx, args, main):
     achieved = bytes_step / step_s / 1e9     # 11 launches back to back: bytes per launch / time per launch
     res["roofline"] = {"bound": "hbm", "kernel": "pw_stream_kernel", "achieved": achieved, "peak": pk["hbm_gbs"],
                        "unit": "GB/s", "frac": achieved / pk["hbm_gbs"], "peak_source": pk["source"],
-                       "frac_of_nominal_8TBs": achieved / 8000.0, "traffic": None}
+                       "frac_of_nominal_8TBs": achieved / 8000.0,
+                       # dram__bytes_read + dram__bytes_write per launch, averaged over the 11 launches
+                       # of a step: 113.35 bytes per element and step measured by ncu at 2^26 elements
+                       # (profiles/pw_stream_kernel_elementwise_sweep_2p26.txt), scaled by element count
+                       "traffic": 113.35 * n / len(ELEMENTWISE_OPS),
+                       "algorithmic_bytes_per_launch": bytes_step / len(ELEMENTWISE_OPS),
+                       "traffic_source": "ncu at 2^26 elements, scaled by element count"}
     if args.profile or not main:
         return res
     # per-op breakdown (outside the headline region; each op bracketed by its own events)

@@ -33,35 +33,51 @@ __global__ void __launch_bounds__(256) conv_direct_small_kernel(const float *__r
                                                                 const float *__restrict__ w, float *__restrict__ y,
                                                                 long long Mtot, int C, int H, int W, int K, int Ho,
                                                                 int Wo, int kh, int kw, int padH, int padW, int sH,
-                                                                int sW, int dH, int dW, Epilogue ep) {
+                                                                int sW, int dH, int dW, Epilogue ep,
+                                                                const float *__restrict__ zero) {
   __shared__ __align__(16) float ws[32 * KP];
-  const int crs = C * kh * kw, hw = Ho * Wo;
+  __shared__ int q_off[32];  // offset of tap q relative to the pixel's window origin, inside one image
+  __shared__ int q_tap[32];  // r*kw + s of tap q, or 32 for q past the end of the filter
+  const int crs = C * kh * kw, hw = Ho * Wo, khw = kh * kw;
   for (int i = threadIdx.x; i < 32 * KP; i += blockDim.x) {
     const int q = i / KP, k = i % KP;
     ws[i] = (q < crs && k < K) ? w[k * crs + q] : 0.f;
   }
+  if (threadIdx.x < 32) {
+    const int q = threadIdx.x;
+    const int c = q / khw, rs = q - c * khw, r = rs / kw, sx = rs - r * kw;
+    q_off[q] = q < crs ? (c * H + r * dH) * W + sx * dW : 0;
+    q_tap[q] = q < crs ? rs : 32;
+  }
   __syncthreads();
   const long long stride = (long long)gridDim.x * blockDim.x;
   for (long long m = (long long)blockIdx.x * blockDim.x + threadIdx.x; m < Mtot; m += stride) {
-    const long long b = m / hw;
-    const int pix = (int)(m - b * hw);
+    long long b;
+    int pix;
+    if (Mtot < (1LL << 31)) {
+      const uint32_t mu = (uint32_t)m, bu = mu / (uint32_t)hw;
+      b = bu;
+      pix = (int)(mu - bu * (uint32_t)hw);
+    } else {
+      b = m / hw;
+      pix = (int)(m - b * hw);
+    }
     const int oh = pix / Wo, ow = pix - oh * Wo;
     const int ih0 = oh * sH - padH, iw0 = ow * sW - padW;
-    const float *xb = x + b * (long long)C * H * W;
+    // which taps of this pixel fall inside the image: one bit per (r, s)
+    uint32_t tap_mask = 0;
+    for (int r = 0; r < kh; ++r)
+      for (int sx = 0; sx < kw; ++sx) {
+        const int ih = ih0 + r * dH, iw = iw0 + sx * dW;
+        if ((unsigned)ih < (unsigned)H && (unsigned)iw < (unsigned)W) tap_mask |= 1u << (r * kw + sx);
+      }
+    const float *xpix = x + b * (long long)C * H * W + (long long)ih0 * W + iw0;
     float v[32];
-    int c = 0, r = 0, sx = 0;
 #pragma unroll
     for (int q = 0; q < 32; ++q) {
-      const int ih = ih0 + r * dH, iw = iw0 + sx * dW;
-      const bool in = q < crs && (unsigned)ih < (unsigned)H && (unsigned)iw < (unsigned)W;
-      v[q] = in ? __ldg(xb + ((long long)c * H + ih) * W + iw) : 0.f;
-      if (++sx == kw) {
-        sx = 0;
-        if (++r == kh) {
-          r = 0;
-          ++c;
-        }
-      }
+      const int tap = q_tap[q];
+      const bool in = tap < 32 && ((tap_mask >> (tap & 31)) & 1u) != 0;
+      v[q] = __ldg(in ? xpix + q_off[q] : zero);  // a word that always holds 0.0f stands for padding
     }
     float acc[KP];
 #pragma unroll
@@ -90,10 +106,11 @@ static int conv_direct_small(b200_engine *e, const float *x, const float *w, flo
                              int W, int K, int kh, int kw, int padH, int padW, int sH, int sW, int dH, int dW, int Ho,
                              int Wo, const Epilogue &ep) {
   const long long Mtot = B * Ho * Wo;
+  const float *zero = reinterpret_cast<const float *>(e->d_flags + 8);  // zeroed at engine creation, never written
   const int blocks = (int)std::max<long long>(1, std::min<long long>((Mtot + 255) / 256, (long long)e->sm_count * 16));
 #define B200_DIRECT(KP)                                                                                        \
   conv_direct_small_kernel<KP><<<blocks, 256, 0, e->stream>>>(x, w, y, Mtot, C, H, W, K, Ho, Wo, kh, kw, padH, padW, \
-                                                             sH, sW, dH, dW, ep)
+                                                             sH, sW, dH, dW, ep, zero)
   if (K <= 8) B200_DIRECT(8);
   else if (K <= 16) B200_DIRECT(16);
   else if (K <= 24) B200_DIRECT(24);
@@ -149,7 +166,7 @@ int b200_conv2d_fwd(b200_engine *e, int dtype, const void *x, const void *w, voi
   const long long img_bytes = hw * crs * (long long)es;
   long long chunk = std::max<long long>(1, std::min<long long>(B, kColChunkBytes / std::max<long long>(1, img_bytes)));
 
-  if (dtype == B200_F32 && crs <= 32 && K <= 32 && H < (1LL << 30) && W < (1LL << 30))
+  if (dtype == B200_F32 && crs <= 32 && K <= 32 && C * H * W < (1LL << 31))
     return conv_direct_small(e, (const float *)x, (const float *)w, (float *)y, B, (int)C, (int)H, (int)W, (int)K, kh,
                              kw, pad_h, pad_w, stride_h, stride_w, dil_h, dil_w, (int)Ho, (int)Wo, ep);
   if (tc)
