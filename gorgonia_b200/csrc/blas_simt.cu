@@ -34,7 +34,25 @@ __global__ void __launch_bounds__(256) gemv_n_kernel(const T *__restrict__ A, lo
     for (int j = 0; j < V; ++j) acc[j] = T(0);
     if (VEC) {
       const long long nv = N / V;
-      for (long long c = lane; c < nv; c += 32) {
+      long long c = lane;
+      // four 16-byte loads of the matrix row in flight per lane before any of them is used: the
+      // row is streamed once from HBM, and bytes in flight are what a streaming kernel lives on
+      for (; c + 96 < nv; c += 128) {
+        uint4 ra[4], rx[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) ra[u] = __ldcs(reinterpret_cast<const uint4 *>(a + (c + 32 * u) * V));
+#pragma unroll
+        for (int u = 0; u < 4; ++u) rx[u] = __ldg(reinterpret_cast<const uint4 *>(x + (c + 32 * u) * V));
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          T av[V], xv[V];
+          memcpy(av, &ra[u], 16);
+          memcpy(xv, &rx[u], 16);
+#pragma unroll
+          for (int j = 0; j < V; ++j) acc[j] = fma_(av[j], xv[j], acc[j]);
+        }
+      }
+      for (; c < nv; c += 32) {
         const uint4 ra = *reinterpret_cast<const uint4 *>(a + c * V);
         const uint4 rx = __ldg(reinterpret_cast<const uint4 *>(x + c * V));
         T av[V], xv[V];
