@@ -126,6 +126,8 @@ _SIGS = {
     "b200_memcpy_d2d": (_i, [_vp, _vp, _vp, _i64]),
     "b200_memcpy_h2d_async": (_i, [_vp, _vp, _vp, _i64]),
     "b200_memcpy_d2h_async": (_i, [_vp, _vp, _vp, _i64]),
+    "b200_upload_async": (_i, [_vp, _vp, _vp, _i64]),
+    "b200_upload_wait": (_i, [_vp]),
     "b200_memset": (_i, [_vp, _vp, _i, _i64]),
     "b200_host_alloc": (_i, [_i64, _P(_vp)]),
     "b200_host_free": (_i, [_vp]),

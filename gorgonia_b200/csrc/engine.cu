@@ -66,6 +66,9 @@ int b200_engine_create(int device, size_t arena_bytes, unsigned flags, b200_engi
     if (e->slab) cudaFree(e->slab);
     if (e->d_flags) cudaFree(e->d_flags);
     if (e->h_flags) cudaFreeHost(e->h_flags);
+    if (e->upload_done) cudaEventDestroy(e->upload_done);
+    if (e->compute_mark) cudaEventDestroy(e->compute_mark);
+    if (e->copy_stream) cudaStreamDestroy(e->copy_stream);
     if (e->stream) cudaStreamDestroy(e->stream);
     delete e;
     if (prev >= 0) cudaSetDevice(prev);
@@ -74,6 +77,11 @@ int b200_engine_create(int device, size_t arena_bytes, unsigned flags, b200_engi
   if ((err = cudaSetDevice(device)) != cudaSuccess) return fail("cudaSetDevice", err);
   if ((err = cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking)) != cudaSuccess)
     return fail("cudaStreamCreateWithFlags", err);
+  if ((err = cudaStreamCreateWithFlags(&e->copy_stream, cudaStreamNonBlocking)) != cudaSuccess)
+    return fail("cudaStreamCreateWithFlags", err);
+  if ((err = cudaEventCreateWithFlags(&e->upload_done, cudaEventDisableTiming)) != cudaSuccess ||
+      (err = cudaEventCreateWithFlags(&e->compute_mark, cudaEventDisableTiming)) != cudaSuccess)
+    return fail("cudaEventCreateWithFlags", err);
   if (arena_bytes == 0) arena_bytes = (size_t)256 << 20;
   arena_bytes = (arena_bytes + 255) / 256 * 256;
   if (flags & B200_ENGINE_MANAGED) {
@@ -115,6 +123,10 @@ int b200_engine_destroy(b200_engine *e) {
     if (e->d_flags) cudaFree(e->d_flags);
     if (e->reduce_scratch) cudaFree(e->reduce_scratch);
     if (e->h_flags) cudaFreeHost(e->h_flags);
+    cudaStreamSynchronize(e->copy_stream);
+    cudaEventDestroy(e->upload_done);
+    cudaEventDestroy(e->compute_mark);
+    cudaStreamDestroy(e->copy_stream);
     cudaStreamDestroy(e->stream);
   }
   delete e;
@@ -410,6 +422,35 @@ int b200_memset(b200_engine *e, void *dst, int value, int64_t bytes) {
   int rc = flush_pending(e);
   if (rc != B200_OK) return rc;
   B200_CHECK_CUDA(e, cudaMemsetAsync(dst, value, (size_t)bytes, e->stream));
+  return B200_OK;
+}
+
+/* ---- uploads that overlap compute ---- */
+
+int b200_upload_async(b200_engine *e, void *dst, const void *src, int64_t bytes) {
+  if (!e) return B200_ERR_INVALID;
+  std::lock_guard<std::recursive_mutex> lk(e->mu);
+  B200_REQUIRE(e, bytes >= 0, "b200_upload_async: negative size");
+  if (bytes == 0) return B200_OK;
+  B200_REQUIRE(e, dst && src, "b200_upload_async: null pointer");
+  B200_NOT_WHILE_CAPTURING(e, "b200_upload_async");
+  DeviceGuard g(e);
+  int rc = flush_pending(e);
+  if (rc != B200_OK) return rc;
+  // the copy may not overtake compute work queued so far: that work may still read `dst`
+  B200_CHECK_CUDA(e, cudaEventRecord(e->compute_mark, e->stream));
+  B200_CHECK_CUDA(e, cudaStreamWaitEvent(e->copy_stream, e->compute_mark, 0));
+  B200_CHECK_CUDA(e, cudaMemcpyAsync(dst, src, (size_t)bytes, cudaMemcpyHostToDevice, e->copy_stream));
+  B200_CHECK_CUDA(e, cudaEventRecord(e->upload_done, e->copy_stream));
+  return B200_OK;
+}
+
+int b200_upload_wait(b200_engine *e) {
+  if (!e) return B200_ERR_INVALID;
+  std::lock_guard<std::recursive_mutex> lk(e->mu);
+  B200_NOT_WHILE_CAPTURING(e, "b200_upload_wait");
+  DeviceGuard g(e);
+  B200_CHECK_CUDA(e, cudaStreamWaitEvent(e->stream, e->upload_done, 0));
   return B200_OK;
 }
 

@@ -16,6 +16,9 @@ struct b200_engine {
   int device = 0;
   unsigned flags = 0;
   cudaStream_t stream = nullptr;
+  cudaStream_t copy_stream = nullptr;      // uploads that overlap compute (b200_upload_*)
+  cudaEvent_t upload_done = nullptr;       // last upload queued on copy_stream
+  cudaEvent_t compute_mark = nullptr;      // point of the compute stream an upload must not pass
   int sm_count = 148;
   size_t smem_optin = 0;
 

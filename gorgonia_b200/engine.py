@@ -157,6 +157,13 @@ class Engine:
     def copy_h2d_async(self, t, host_ptr, nbytes=None):
         check(lib.b200_memcpy_h2d_async(self.h, t.ptr, host_ptr, t.nbytes if nbytes is None else nbytes), self.h)
 
+    def upload_async(self, t, host_ptr, nbytes=None):
+        """Host -> device on the engine's copy stream, overlapping compute queued after this call."""
+        check(lib.b200_upload_async(self.h, t.ptr, host_ptr, t.nbytes if nbytes is None else nbytes), self.h)
+
+    def upload_wait(self):
+        check(lib.b200_upload_wait(self.h), self.h)
+
     def copy_d2h_async(self, host_ptr, t, nbytes=None):
         check(lib.b200_memcpy_d2h_async(self.h, host_ptr, t.ptr, t.nbytes if nbytes is None else nbytes), self.h)
 

@@ -140,6 +140,15 @@ int b200_memcpy_d2d(b200_engine *e, void *dst, const void *src, int64_t bytes);
 int b200_memcpy_h2d_async(b200_engine *e, void *dst, const void *src, int64_t bytes);
 int b200_memcpy_d2h_async(b200_engine *e, void *dst, const void *src, int64_t bytes);
 int b200_memset(b200_engine *e, void *dst, int value, int64_t bytes);
+/* Uploads that overlap compute (the H->D half of deviceTransport.exec, vm_tape_cuda.go:227-230,
+ * without stalling the tape). b200_upload_async copies pinned host memory to the device on a
+ * second stream; it starts only after the compute work queued so far (which may still read
+ * `dst`), and compute queued AFTER the call runs concurrently with it. b200_upload_wait makes
+ * the compute stream wait for the uploads queued so far; call it before the first kernel that
+ * reads `dst`. With two input buffers used in turn, the upload of batch i+1 hides behind the
+ * forward pass of batch i. Neither call can be recorded into a tape. */
+int b200_upload_async(b200_engine *e, void *dst, const void *src, int64_t bytes);
+int b200_upload_wait(b200_engine *e);
 /* pinned host staging buffers */
 int b200_host_alloc(int64_t bytes, void **hptr);
 int b200_host_free(void *hptr);

@@ -49,6 +49,9 @@ def _worker(rank, world, port, total, q):
         local = graphs.lenet(model, x[a:b])
         whole = shard.all_gather_rows(local, total, dist)
         slowest = shard.max_over_ranks(10.0 + rank, dist)
+        grad = np.full(1000, float(rank + 1), np.float32)     # ranks hold 1s and 2s: the mean is 1.5
+        shard.allreduce_mean_(grad, dist)
+        assert np.all(grad == np.float32(1.5))
         dist.barrier()
         if rank == 0:
             q.put((whole, slowest))
