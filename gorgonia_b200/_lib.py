@@ -137,6 +137,7 @@ _SIGS = {
     "b200_pointwise": (_i, [_vp, _i, _P(PwProg), _P(_vp), _P(_vp), _i64]),
     "b200_pending": (_i, [_vp, _P(_i), _P(_i)]),
     "b200_fusion_plan": (_i, [_P(PwCall), _i, _P(_i), _P(_i), _P(_i), _P(_i), _P(_i)]),
+    "b200_set_constant": (_i, [_vp, _vp, _i]),
     "b200_gemm": (_i, [_vp, _i, _i, _i, _i64, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _i64,
                        _P(Epilogue)]),
     "b200_gemm_path": (_i, [_vp, _i, _i, _i, _i64, _i64, _i64, _i64, _i64, _i64, _vp, _vp, _vp]),

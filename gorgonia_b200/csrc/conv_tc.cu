@@ -498,7 +498,13 @@ int conv2d_tc(b200_engine *e, const float *x, const float *w, float *y, long lon
   TcOperand wf;
   void *blk[2] = {nullptr, nullptr};
   int rc;
-  if (mode == 2) {
+  CachedSplit *cached = mode == 2 ? find_cached(e, w, 1, K, C, kh * kw, crs) : nullptr;
+  if (cached) {
+    wf.p0 = cached->hi;
+    wf.p1 = cached->lo;
+    wf.ld = crs;
+    rc = B200_OK;
+  } else if (mode == 2) {
     // filters split into TF32 head/tail AND reordered to (tap, channel) along the reduction index
     rc = b200_get(e, (long long)K * crs * 4, &blk[0]);
     if (rc == B200_OK) rc = b200_get(e, (long long)K * crs * 4, &blk[1]);
@@ -513,6 +519,10 @@ int conv2d_tc(b200_engine *e, const float *x, const float *w, float *y, long lon
     wf.p0 = blk[0];
     wf.p1 = blk[1];
     wf.ld = crs;
+    if (is_constant(e, w)) {  // filters declared constant: keep the permuted split for the next call
+      add_cached(e, w, CachedSplit{1, K, C, kh * kw, crs, blk[0], blk[1], crs});
+      blk[0] = blk[1] = nullptr;
+    }
   } else {
     rc = split_operand_tf32(e, w, K, crs, crs, 1, 0, &wf, &blk[0], &blk[1]);
     if (rc != B200_OK) return rc;
@@ -553,8 +563,8 @@ int conv2d_tc(b200_engine *e, const float *x, const float *w, float *y, long lon
       else rc = launch_conv_tc<32, 0>(e, tm, p);
     }
   }
-  b200_put(e, blk[0], 0);
-  b200_put(e, blk[1], 0);
+  if (blk[0]) b200_put(e, blk[0], 0);
+  if (blk[1]) b200_put(e, blk[1], 0);
   return rc;
 }
 

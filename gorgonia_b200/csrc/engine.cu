@@ -30,11 +30,48 @@ int set_error(b200_engine *e, int code, const char *fmt, ...) {
   return code;
 }
 
+bool is_constant(b200_engine *e, const void *ptr) { return e->constants.count(ptr) != 0; }
+
+CachedSplit *find_cached(b200_engine *e, const void *ptr, int kind, long long d0, long long d1, long long d2,
+                         long long ld_in) {
+  auto it = e->constants.find(ptr);
+  if (it == e->constants.end()) return nullptr;
+  for (auto &c : it->second.derived)
+    if (c.kind == kind && c.d0 == d0 && c.d1 == d1 && c.d2 == d2 && c.ld_in == ld_in) return &c;
+  return nullptr;
+}
+
+void add_cached(b200_engine *e, const void *ptr, const CachedSplit &c) { e->constants[ptr].derived.push_back(c); }
+
+void drop_constant(b200_engine *e, const void *ptr) {
+  auto it = e->constants.find(ptr);
+  if (it == e->constants.end()) return;
+  for (auto &c : it->second.derived) {
+    // plain arena frees: whoever gets the blocks next runs later on the same stream
+    int64_t off = (char *)c.hi - (char *)e->slab;
+    if (off >= 0 && off < e->slab_bytes) e->bfc.free(off);
+    off = (char *)c.lo - (char *)e->slab;
+    if (off >= 0 && off < e->slab_bytes) e->bfc.free(off);
+  }
+  e->constants.erase(it);
+}
+
 }  // namespace b200
 
 using namespace b200;
 
 extern "C" {
+
+int b200_set_constant(b200_engine *e, const void *ptr, int is_const) {
+  if (!e) return B200_ERR_INVALID;
+  std::lock_guard<std::recursive_mutex> lk(e->mu);
+  B200_REQUIRE(e, ptr != nullptr, "b200_set_constant: null pointer");
+  if (is_const)
+    e->constants[ptr];  // creates the entry
+  else
+    drop_constant(e, ptr);
+  return B200_OK;
+}
 
 int b200_engine_create(int device, size_t arena_bytes, unsigned flags, b200_engine **out) {
   if (!out) return set_error(nullptr, B200_ERR_INVALID, "b200_engine_create: out is null");
@@ -322,6 +359,7 @@ int b200_put(b200_engine *e, void *dptr, int64_t /*bytes*/) {
   int64_t off = (char *)dptr - (char *)e->slab;
   if (off < 0 || off >= e->slab_bytes) return B200_OK;  // not ours: no-op, as in the reference
   if (e->bfc.is_live(off)) note_put(e, dptr);
+  drop_constant(e, dptr);  // a released buffer is no longer a constant; what was derived from it goes too
   e->bfc.free(off);
   return B200_OK;
 }
@@ -332,6 +370,7 @@ int b200_reset(b200_engine *e) {
   DeviceGuard g(e);
   // queued work may still read or write arena blocks: run it before the blocks are recycled
   int rc = flush_pending(e);
+  e->constants.clear();  // derived blocks live in the arena that is being reset
   e->bfc.reset();
   return rc;
 }

@@ -5,12 +5,27 @@
 #include <cstdarg>
 #include <cstdint>
 #include <cstdio>
+#include <map>
 #include <mutex>
 #include <string>
 #include <vector>
 
 #include "../../include/gorgonia_b200.h"
 #include "bfc.h"
+
+namespace b200 {
+// A derived form of a constant buffer (weights) kept for reuse: the TF32 head/tail split of a
+// matrix (kind 0) or of convolution filters permuted to (tap, channel) order (kind 1).
+struct CachedSplit {
+  int kind;
+  long long d0, d1, d2, ld_in;  // the shape it was made for
+  void *hi, *lo;                // arena blocks
+  long long ld_out;
+};
+struct ConstantEntry {
+  std::vector<CachedSplit> derived;
+};
+}  // namespace b200
 
 struct b200_engine {
   int device = 0;
@@ -26,6 +41,9 @@ struct b200_engine {
   void *slab = nullptr;
   int64_t slab_bytes = 0;
   b200::Bfc bfc;
+
+  // buffers the caller declared constant (b200_set_constant), with what was derived from them
+  std::map<const void *, b200::ConstantEntry> constants;
 
   // deferred pointwise queue
   std::vector<b200_pw_call> pending;
@@ -110,6 +128,13 @@ inline size_t dtype_size(int dtype) {
       return b200::set_error((e), B200_ERR_STATE, "%s waits for the device and cannot be recorded " \
                              "into a tape", (who));                                               \
   } while (0)
+
+// constants (engine.cu)
+CachedSplit *find_cached(b200_engine *e, const void *ptr, int kind, long long d0, long long d1, long long d2,
+                         long long ld_in);
+bool is_constant(b200_engine *e, const void *ptr);
+void add_cached(b200_engine *e, const void *ptr, const CachedSplit &c);
+void drop_constant(b200_engine *e, const void *ptr);
 
 // implemented in pointwise.cu
 int flush_pending(b200_engine *e);

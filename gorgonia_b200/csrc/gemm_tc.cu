@@ -572,6 +572,19 @@ int split_operand_tf32(b200_engine *e, const float *src, long long rows, long lo
   const long long ldo = (cols + 3) / 4 * 4;
   const long long elems = rows * ldo * batch;
   *blk_hi = *blk_lo = nullptr;
+  // a buffer declared constant (weights) is split once; the split is kept until the buffer is
+  // released or un-declared, and the caller gets no blocks to hand back
+  const bool constant = is_constant(e, src);
+  if (constant) {
+    if (CachedSplit *c = find_cached(e, src, 0, rows, cols, batch, ld)) {
+      out->p0 = c->hi;
+      out->p1 = c->lo;
+      out->ld = c->ld_out;
+      out->batch_stride = rows * c->ld_out;
+      out->shared = false;
+      return B200_OK;
+    }
+  }
   int rc = b200_get(e, elems * 4, blk_hi);
   if (rc != B200_OK) return rc;
   rc = b200_get(e, elems * 4, blk_lo);
@@ -596,6 +609,10 @@ int split_operand_tf32(b200_engine *e, const float *src, long long rows, long lo
   out->ld = ldo;
   out->batch_stride = rows * ldo;
   out->shared = false;
+  if (constant) {
+    add_cached(e, src, CachedSplit{0, rows, cols, batch, ld, *blk_hi, *blk_lo, ldo});
+    *blk_hi = *blk_lo = nullptr;  // kept: nothing for the caller to release
+  }
   return B200_OK;
 }
 

@@ -333,6 +333,11 @@ class Engine:
         check(lib.b200_ger(self.h, dtype_code(x.dtype), x.size, y.size, x.ptr, y.ptr, prealloc.ptr), self.h)
         return prealloc
 
+    def constant(self, t, flag=True):
+        """Declares a tensor constant (weights): what the engine derives from it is kept across calls."""
+        check(lib.b200_set_constant(self.h, t.ptr, int(flag)), self.h)
+        return t
+
     def tensor_bf16(self, arr):
         """Uploads a float32 array rounded to bfloat16."""
         u = to_bf16(arr)

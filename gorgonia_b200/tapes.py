@@ -71,7 +71,7 @@ class MLP(_Tape):
         self.batch, self.fused = batch, fused
         self.w_host = [glorot_uniform(g, (self.DIMS[i], self.DIMS[i + 1])) for i in range(3)]
         self.b_host = [np.zeros(self.DIMS[i + 1], np.float32) for i in range(3)]
-        self.w = [e.tensor(w) for w in self.w_host]
+        self.w = [e.constant(e.tensor(w)) for w in self.w_host]
         self.b = [e.tensor(b) for b in self.b_host]
         self.x = e.empty((batch, 784))
         self.h = [e.empty((batch, d)) for d in self.DIMS[1:]]
@@ -108,8 +108,8 @@ class LeNet(_Tape):
         self.batch, self.fused = batch, fused
         self.wc_host = [he_normal(g, (self.CH[i + 1], self.CH[i], 3, 3), self.CH[i] * 9) for i in range(3)]
         self.wd_host = [he_normal(g, (1152, 625), 1152), he_normal(g, (625, 10), 625)]
-        self.wc = [e.tensor(w) for w in self.wc_host]
-        self.wd = [e.tensor(w) for w in self.wd_host]
+        self.wc = [e.constant(e.tensor(w)) for w in self.wc_host]
+        self.wd = [e.constant(e.tensor(w)) for w in self.wd_host]
         self.x = e.empty((batch, 1, 28, 28))
         hw = (28, 14, 7)
         self.conv = [e.empty((batch, self.CH[i + 1], hw[i], hw[i])) for i in range(3)]
@@ -160,7 +160,7 @@ class TinyYolo(_Tape):
         self.w_host = [he_normal(g, (ch[i + 1], ch[i], self.k[i], self.k[i]), ch[i] * self.k[i] ** 2)
                        for i in range(9)]
         self.b_host = [(g.standard_normal(ch[i + 1]) * 0.1).astype(np.float32) for i in range(9)]
-        self.w = [e.tensor(w) for w in self.w_host]
+        self.w = [e.constant(e.tensor(w)) for w in self.w_host]
         self.b = [e.tensor(b) for b in self.b_host]
         self.x = e.empty((batch, 3, size, size))
         s = size

@@ -272,6 +272,16 @@ int b200_ger(b200_engine *e, int dtype, int64_t M, int64_t N, const void *x, con
 int b200_gemm_path(b200_engine *e, int dtype, int transA, int transB, int64_t M, int64_t N, int64_t K,
                    int64_t lda, int64_t ldb, int64_t ldc, const void *A, const void *B, const void *C);
 
+/* Declares a device buffer constant (is_constant != 0) or mutable again (0). gorgonia re-derives
+ * nothing from weights, but it re-uploads them on every run (analysis.go:151-176 puts a devTrans
+ * in front of every argument node); this engine keeps them resident, and for a buffer declared
+ * constant it also keeps what it derives from it — the TF32 head/tail split the tensor-core matrix
+ * multiply and convolution need — instead of recomputing it per call. The caller promises not to
+ * write the buffer while it is declared constant (a Go shim declares a node's value constant when
+ * it is bound with Let and un-declares it when it is rebound; solvers update weights between runs,
+ * so a training loop un-declares them). b200_put and b200_reset end the declaration. */
+int b200_set_constant(b200_engine *e, const void *ptr, int is_constant);
+
 /* ---- softmax, reductions, argmax ----------------------------------------------------------
  * A tensor is viewed as (outer, len, inner) around the axis that is reduced.
  * b200_softmax: softmaxOp.Do -> tensor.SoftMax / LogSoftMax (op_softmax.go:99-128); y has x's shape.

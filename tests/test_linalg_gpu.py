@@ -178,3 +178,34 @@ def test_gemm_argument_errors(fresh):
     a, b = e.tensor(np.ones((4, 5), np.float32)), e.tensor(np.ones((6, 7), np.float32))
     with pytest.raises(B200Error):
         e.MatMul(a, b, e.empty((4, 7)))
+
+
+def test_constant_operand_split_is_kept_until_undeclared(fresh):
+    # weights declared constant are split once; the engine must not notice a change of their
+    # contents until the declaration is withdrawn (that is the documented contract)
+    e = fresh
+    M, N, K = 256, 128, 192
+    a, b = _mats(71, M, N, K, False, False, scale=0.1)
+    ta, tb, tc = e.tensor(a), e.tensor(b), e.empty((M, N))
+    e.Signal()
+    e.constant(tb)
+    l0 = e.launches
+    e.MatMul(ta, tb, tc)
+    first = e.launches - l0
+    want = oracle.gemm(a, b)
+    assert_gemm_close(tc.numpy(), want, 1e-5)
+    l0 = e.launches
+    e.MatMul(ta, tb, tc)
+    assert e.launches - l0 == first - 1            # the split of B was not repeated
+    assert_gemm_close(tc.numpy(), want, 1e-5)
+    b2 = (b * np.float32(2.0)).astype(np.float32)
+    tb.set(b2)
+    e.constant(tb, False)                          # withdrawn: the next product sees the new values
+    e.MatMul(ta, tb, tc)
+    assert_gemm_close(tc.numpy(), oracle.gemm(a, b2), 1e-5)
+    used = e.arena_stats()["used"]
+    e.constant(tb)
+    e.MatMul(ta, tb, tc)
+    assert e.arena_stats()["used"] > used          # the kept split lives in the arena ...
+    tb.free()
+    assert e.arena_stats()["used"] < used          # ... and goes with the buffer it was derived from
