@@ -64,20 +64,26 @@ __global__ void __launch_bounds__(256) conv_direct_small_kernel(const float *__r
     }
     const int oh = pix / Wo, ow = pix - oh * Wo;
     const int ih0 = oh * sH - padH, iw0 = ow * sW - padW;
-    // which taps of this pixel fall inside the image: one bit per (r, s)
-    uint32_t tap_mask = 0;
-    for (int r = 0; r < kh; ++r)
-      for (int sx = 0; sx < kw; ++sx) {
-        const int ih = ih0 + r * dH, iw = iw0 + sx * dW;
-        if ((unsigned)ih < (unsigned)H && (unsigned)iw < (unsigned)W) tap_mask |= 1u << (r * kw + sx);
-      }
+    // which taps of this pixel fall inside the image: one bit per (r, s); all of them for a
+    // pixel whose whole window is inside, which is every pixel but the border ones
+    uint32_t tap_mask = 0xffffffffu;
+    if (ih0 < 0 || iw0 < 0 || ih0 + (kh - 1) * dH >= H || iw0 + (kw - 1) * dW >= W) {
+      tap_mask = 0;
+      for (int r = 0; r < kh; ++r)
+        for (int sx = 0; sx < kw; ++sx) {
+          const int ih = ih0 + r * dH, iw = iw0 + sx * dW;
+          if ((unsigned)ih < (unsigned)H && (unsigned)iw < (unsigned)W) tap_mask |= 1u << (r * kw + sx);
+        }
+    }
     const float *xpix = x + b * (long long)C * H * W + (long long)ih0 * W + iw0;
     float v[32];
 #pragma unroll
     for (int q = 0; q < 32; ++q) {
-      const int tap = q_tap[q];
-      const bool in = tap < 32 && ((tap_mask >> (tap & 31)) & 1u) != 0;
-      v[q] = __ldg(in ? xpix + q_off[q] : zero);  // a word that always holds 0.0f stands for padding
+      v[q] = 0.f;
+      if (q < crs) {  // the same for every thread: no divergence, and no loads for taps that do not exist
+        const bool in = ((tap_mask >> q_tap[q]) & 1u) != 0;
+        v[q] = __ldg(in ? xpix + q_off[q] : zero);  // a word that always holds 0.0f stands for padding
+      }
     }
     float acc[KP];
 #pragma unroll
@@ -96,9 +102,15 @@ __global__ void __launch_bounds__(256) conv_direct_small_kernel(const float *__r
       }
     }
     float *yb = y + (b * K) * (long long)hw + pix;
+    if (ep.bias_kind == B200_BIAS_NONE && ep.act == B200_ACT_NONE) {
 #pragma unroll
-    for (int k = 0; k < KP; ++k)
-      if (k < K) yb[(long long)k * hw] = apply_epilogue<float>(acc[k], ep, k, 0);
+      for (int k = 0; k < KP; ++k)
+        if (k < K) yb[(long long)k * hw] = acc[k];
+    } else {
+#pragma unroll
+      for (int k = 0; k < KP; ++k)
+        if (k < K) yb[(long long)k * hw] = apply_epilogue<float>(acc[k], ep, k, 0);
+    }
   }
 }
 

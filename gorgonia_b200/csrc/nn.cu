@@ -85,6 +85,28 @@ __global__ void __launch_bounds__(256) maxpool2x2_kernel(const float *__restrict
   }
 }
 
+// The same for any even W and any H: one output per thread from two 8-byte loads. A trailing
+// odd input row (H odd) is simply never read, as the output size formula drops it.
+__global__ void __launch_bounds__(256) maxpool2x2_even_kernel(const float *__restrict__ x, float *__restrict__ y,
+                                                              long long planes, int H, int W, int Ho, int Wo) {
+  const long long total = planes * Ho * Wo;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += stride) {
+    const int pw = (int)(t % Wo);
+    const int ph = (int)((t / Wo) % Ho);
+    const long long plane = t / ((long long)Wo * Ho);
+    const float *in = x + (plane * H + 2 * ph) * (long long)W + 2 * pw;
+    const float2 a = *reinterpret_cast<const float2 *>(in);
+    const float2 b = *reinterpret_cast<const float2 *>(in + W);
+    float m0 = -FLT_MAX;
+    if (a.x > m0) m0 = a.x;
+    if (a.y > m0) m0 = a.y;
+    if (b.x > m0) m0 = b.x;
+    if (b.y > m0) m0 = b.y;
+    y[t] = m0;
+  }
+}
+
 // ---- im2col ------------------------------------------------------------------------------------
 // col[(b, oh, ow), (c, r, s)] = x[b, c, oh*sH - padH + r*dH, ow*sW - padW + s*dW], 0 outside.
 // One thread per column element; consecutive threads write consecutive (c, r, s), which makes
@@ -237,6 +259,13 @@ int b200_maxpool2d_fwd(b200_engine *e, int dtype, const void *x, void *y, int64_
     maxpool2x2_kernel<<<grid_for(e, total / 2), 256, 0, e->stream>>>((const float *)x, (float *)y, B * C, (int)H,
                                                                     (int)W, (int)Ho, (int)Wo);
     B200_CHECK_LAUNCH(e, "maxpool2x2_kernel");
+    return B200_OK;
+  }
+  if (dtype == B200_F32 && !mask && kh == 2 && kw == 2 && stride_h == 2 && stride_w == 2 && pad_north == 0 &&
+      pad_south == 0 && pad_west == 0 && pad_east == 0 && W % 2 == 0 && (uintptr_t)x % 8 == 0) {
+    maxpool2x2_even_kernel<<<grid_for(e, total), 256, 0, e->stream>>>((const float *)x, (float *)y, B * C, (int)H,
+                                                                     (int)W, (int)Ho, (int)Wo);
+    B200_CHECK_LAUNCH(e, "maxpool2x2_even_kernel");
     return B200_OK;
   }
   if (dtype == B200_F32)
