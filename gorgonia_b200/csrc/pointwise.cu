@@ -470,7 +470,52 @@ __device__ __forceinline__ void pw_tile(const PwDev &p, uint32_t ring_s, uint32_
   }
 }
 
+// A full tile of a ONE-instruction program whose operands are ring slots or immediates (every
+// plain engine call: Add, Mul, Exp, ...). The program was decoded once, before the tile loop; here
+// there is nothing left but two shared loads per operand, the op and two stores.
 template <typename T, int V, int U>
+__device__ __forceinline__ void pw_tile_single(int op, bool a_imm, bool b_imm, bool unary, T imm_a, T imm_b,
+                                               uint32_t a_s, uint32_t b_s, unsigned char *out_ptr) {
+  constexpr int W = U * V;
+  constexpr uint32_t USTRIDE = PW_STREAM_THREADS * 16;
+  T a[W], b[W], r[W];
+  if (a_imm) {
+#pragma unroll
+    for (int j = 0; j < W; ++j) a[j] = imm_a;
+  } else {
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const uint4 raw = lds128(a_s + u * USTRIDE);
+      memcpy(&a[u * V], &raw, sizeof raw);
+    }
+  }
+  if (unary) {
+#pragma unroll
+    for (int j = 0; j < W; ++j) b[j] = a[j];
+  } else if (b_imm) {
+#pragma unroll
+    for (int j = 0; j < W; ++j) b[j] = imm_b;
+  } else {
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const uint4 raw = lds128(b_s + u * USTRIDE);
+      memcpy(&b[u * V], &raw, sizeof raw);
+    }
+  }
+  pw_apply<T, W>(op, a, b, r);
+#pragma unroll
+  for (int u = 0; u < U; ++u) {
+    uint4 raw;
+    memcpy(&raw, &r[u * V], sizeof raw);
+    *reinterpret_cast<uint4 *>(out_ptr + (size_t)u * USTRIDE) = raw;
+  }
+}
+
+// SINGLE: the program is one instruction over ring slots and immediates (decided on the host), and
+// full tiles take the lean path above. A separate instantiation, so that the general kernel's code
+// and register allocation are not touched by it (measured: sharing one kernel cost the fused
+// chains 5 %).
+template <typename T, int V, int U, bool SINGLE>
 __global__ void __launch_bounds__(PW_STREAM_THREADS, 2)
     pw_stream_kernel(const __grid_constant__ PwDev p, int stages, int *err_flag) {
   constexpr int TILE_CHUNKS = PW_STREAM_THREADS * U;
@@ -516,6 +561,15 @@ __global__ void __launch_bounds__(PW_STREAM_THREADS, 2)
     for (long long k = 0; k < pre; ++k) issue(k, (int)k);
   }
 
+  // decode once what a one-instruction program over ring slots and immediates needs per tile
+  const int s_op = p.op[0];
+  const bool s_unary = s_op >= B200_OP_ABS;
+  const bool s_a_imm = p.ka[0] == K_IMM, s_b_imm = p.kb[0] == K_IMM;
+  const T s_imm_a = (SINGLE && s_a_imm) ? (T)p.imm[p.xa[0]] : T(0);
+  const T s_imm_b = (SINGLE && !s_unary && s_b_imm) ? (T)p.imm[p.xb[0]] : T(0);
+  const uint32_t s_a_off = (uint32_t)p.xa[0] * SLOT_BYTES, s_b_off = (uint32_t)p.xb[0] * SLOT_BYTES;
+  unsigned char *const s_out = reinterpret_cast<unsigned char *>(p.out[0]) + (size_t)tid * 16;
+
   long long k = 0;
   int stage = 0;
   uint32_t parity = 0;
@@ -523,7 +577,10 @@ __global__ void __launch_bounds__(PW_STREAM_THREADS, 2)
     const long long c_tile = (blockIdx.x + k * (long long)gridDim.x) * TILE_CHUNKS;
     const uint32_t ring_s = smem_s + (uint32_t)stage * stage_bytes + (uint32_t)tid * 16;
     if (!ptx::mbar_wait(&full_bar[stage], parity)) s_fail = 1;
-    if (c_tile + TILE_CHUNKS <= nchunks_full)
+    if (SINGLE && c_tile + TILE_CHUNKS <= nchunks_full)
+      pw_tile_single<T, V, U>(s_op, s_a_imm, s_b_imm, s_unary, s_imm_a, s_imm_b, ring_s + s_a_off, ring_s + s_b_off,
+                              s_out + c_tile * 16);
+    else if (c_tile + TILE_CHUNKS <= nchunks_full)
       pw_tile<T, V, U, true>(p, ring_s, file_s, c_tile, tid);
     else
       pw_tile<T, V, U, false>(p, ring_s, file_s, c_tile, tid);
@@ -580,14 +637,27 @@ static int launch_stream_u(b200_engine *e, const PwDev &d, size_t budget, int st
   const long long nchunks = (d.n + V - 1) / V;
   const long long ntiles = (nchunks + TILE_CHUNKS - 1) / TILE_CHUNKS;
   const size_t smem = ((size_t)stages * d.n_full + d.n_file) * SLOT_BYTES;
-  auto kern = pw_stream_kernel<T, V, U>;
-  static int attr_dev_mask = 0;  // per instantiation: devices on which the attribute is set
-  if (!(attr_dev_mask & (1 << (e->device & 31)))) {
-    B200_CHECK_CUDA(e, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)budget));
-    attr_dev_mask |= 1 << (e->device & 31);
-  }
+  // one instruction over ring slots and immediates: every plain engine call (Add, Mul, Exp, ...)
+  const bool single = d.n_instr == 1 && d.n_file == 0 && d.n_out == 1 && d.out_of[0] == 0 &&
+                      (d.ka[0] == K_RING || d.ka[0] == K_IMM) &&
+                      (d.op[0] >= B200_OP_ABS || d.kb[0] == K_RING || d.kb[0] == K_IMM);
   const int blocks = (int)std::min<long long>(ntiles, 2LL * e->sm_count);  // two resident CTAs per SM
-  kern<<<blocks, PW_STREAM_THREADS, smem, e->stream>>>(d, stages, e->d_flags + 2);
+  static int attr_dev_mask[2] = {0, 0};  // per instantiation: devices on which the attribute is set
+  if (single) {
+    auto kern = pw_stream_kernel<T, V, U, true>;
+    if (!(attr_dev_mask[1] & (1 << (e->device & 31)))) {
+      B200_CHECK_CUDA(e, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)budget));
+      attr_dev_mask[1] |= 1 << (e->device & 31);
+    }
+    kern<<<blocks, PW_STREAM_THREADS, smem, e->stream>>>(d, stages, e->d_flags + 2);
+  } else {
+    auto kern = pw_stream_kernel<T, V, U, false>;
+    if (!(attr_dev_mask[0] & (1 << (e->device & 31)))) {
+      B200_CHECK_CUDA(e, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)budget));
+      attr_dev_mask[0] |= 1 << (e->device & 31);
+    }
+    kern<<<blocks, PW_STREAM_THREADS, smem, e->stream>>>(d, stages, e->d_flags + 2);
+  }
   B200_CHECK_LAUNCH(e, "pw_stream_kernel");
   e->flags_dirty = true;
   return B200_OK;

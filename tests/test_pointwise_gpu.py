@@ -285,3 +285,42 @@ def test_managed_arena_is_host_readable():
     host_view = np.ctypeslib.as_array(C.cast(a.ptr, C.POINTER(C.c_float)), shape=(8,))
     assert host_view.tolist() == [1, 2, 3, 4, 5, 6, 7, 8]
     e.Close()
+
+
+def test_more_than_2_to_the_31_elements():
+    # gorgonia's kernels take `int size` (elembinop.cu:8-14): 2^31 elements is out of their reach.
+    # Here counts and offsets are 64-bit: a vector of 2^31 + 1027 floats (8.6 GB) goes through the
+    # streaming kernel, and the far end, which only a 64-bit index reaches, is read back.
+    import ctypes as C
+    from gorgonia_b200 import Engine, Tensor
+    from gorgonia_b200._lib import lib, check
+    n = (1 << 31) + 1027
+    e = Engine(0, 2 * 4 * n + (64 << 20))
+    try:
+        a, b = e.empty(n), e.empty(n)
+        check(lib.b200_memset(e.h, a.ptr, 0, 4 * n), e.h)
+        e.AddScalar(a, 1.5, unsafe=True)               # a = 1.5 everywhere
+        e.MulScalar(a, 2.0, reuse=b)                   # b = 3.0
+        e.Unary("neg", b, unsafe=True)                 # b = -3.0, fused with the line above
+        tail = Tensor(e, b.ptr + 4 * (n - 2000), (2000,), np.float32, owned=False)
+        head = Tensor(e, b.ptr, (2000,), np.float32, owned=False)
+        mid = Tensor(e, b.ptr + 4 * ((1 << 31) - 1000), (2000,), np.float32, owned=False)
+        for view in (head, mid, tail):
+            assert np.all(view.numpy() == np.float32(-3.0))
+        s = e.empty(1)
+        e.ReduceAll("max", b, s)
+        assert s.numpy()[0] == np.float32(-3.0)
+    finally:
+        e.Close()
+
+
+def test_empty_inputs_are_no_ops(fresh):
+    e = fresh
+    from gorgonia_b200._lib import lib, F32, OP, VV
+    assert lib.b200_binary(e.h, OP["add"], F32, VV, None, None, None, 0.0, 0, 0) == 0
+    assert lib.b200_unary(e.h, OP["exp"], F32, None, None, 0) == 0
+    assert lib.b200_softmax(e.h, F32, None, None, 0, 5, 1, 0) == 0
+    assert lib.b200_gemm(e.h, F32, 0, 0, 0, 5, 3, None, 3, None, 5, None, 5, 1, 0, 0, 0, None) == 0
+    assert lib.b200_transpose(e.h, 4, None, None, 2, (C.c_int64 * 2)(0, 4), (C.c_int * 2)(1, 0)) == 0
+    assert lib.b200_gather_rows(e.h, None, None, None, 0, 16, 4) == 0
+    assert e.pending() == (0, 0)
