@@ -250,7 +250,9 @@ def extract_broadcast(root):
 
 
 def main():
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: extract_goldens.py <path to a gorgonia checkout>")
+    root = sys.argv[1]
     out = {
         "binop.json": extract_binop(root),
         "softmax_do.json": extract_softmax(root),
