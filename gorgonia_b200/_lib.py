@@ -21,7 +21,8 @@ class B200Error(RuntimeError):
 OK, ERR_INVALID, ERR_OOM, ERR_CUDA, ERR_UNSUPPORTED, ERR_TIMEOUT, ERR_STATE = range(7)
 F32, F64, BF16 = 0, 1, 2
 VV, VS, SV = 0, 1, 2
-ENGINE_MANAGED, ENGINE_NO_DEFER = 1, 2
+ENGINE_MANAGED, ENGINE_NO_DEFER, ENGINE_CONV_GATHER = 1, 2, 4
+CONV_SIMT, CONV_DIRECT, CONV_TC_GATHER, CONV_TC_TMA = 0, 1, 2, 3
 
 # op codes (B200_OP_* of the header)
 _BIN = ["add", "sub", "mul", "div", "pow", "mod", "lt", "gt", "lte", "gte", "eq", "ne"]
@@ -150,6 +151,7 @@ _SIGS = {
     "b200_argmax": (_i, [_vp, _i, _vp, _vp, _i64, _i64, _i64]),
     "b200_conv2d_fwd": (_i, [_vp, _i, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _i, _i, _i, _i, _i,
                              _P(Epilogue)]),
+    "b200_conv2d_path": (_i, [_vp, _i, _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _i, _i, _i, _i, _i]),
     "b200_im2col": (_i, [_vp, _i, _vp, _vp, _i64, _i64, _i64, _i64, _i, _i, _i, _i, _i, _i, _i, _i]),
     "b200_maxpool2d_fwd": (_i, [_vp, _i, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i, _i, _i, _i, _i, _i, _i, _i, _i]),
     "b200_transpose": (_i, [_vp, _i, _vp, _vp, _i, _P(_i64), _P(_i)]),

@@ -19,6 +19,11 @@ namespace b200 {
 int conv2d_tc(b200_engine *e, const float *x, const float *w, float *y, long long B, int C, int H, int W, int K,
               int kh, int kw, int padH, int padW, int sH, int sW, int dH, int dW, int Ho, int Wo,
               const Epilogue &ep);
+int conv2d_tma(b200_engine *e, const float *x, const float *w, float *y, long long B, int C, int H, int W, int K,
+               int kh, int kw, int padH, int padW, int sH, int sW, int dH, int dW, int Ho, int Wo,
+               const Epilogue &ep);
+bool conv_tma_eligible(long long B, int C, int H, int W, int kh, int kw, int padH, int padW, int sH, int sW, int dH,
+                       int dW);
 int gemm_simt(b200_engine *e, int dtype, int transA, int transB, long long M, long long N, long long K,
               const void *A, long long lda, const void *B, long long ldb, void *C, long long ldc, long long batch,
               long long strideA, long long strideB, long long strideC, const Epilogue &ep);
@@ -135,6 +140,23 @@ static int conv_direct_small(b200_engine *e, const float *x, const float *w, flo
 // scratch budget for the col data of one chunk (head + tail together)
 static const long long kColChunkBytes = 64LL << 20;
 
+// Which kernel a convolution runs on (the B200_CONV_* values of the header).
+static int conv_path(const b200_engine *e, int dtype, long long B, long long C, long long H, long long W, long long K,
+                     int kh, int kw, int pad_h, int pad_w, int stride_h, int stride_w, int dil_h, int dil_w,
+                     long long Ho, long long Wo) {
+  const long long crs = C * kh * kw, hw = Ho * Wo;
+  if (dtype == B200_F32 && crs <= 32 && K <= 32 && C * H * W < (1LL << 31)) return B200_CONV_DIRECT;
+  // the tensor-core kernels keep per-image offsets in 32 bits and pack tap offsets in 14 bits
+  const bool tc = dtype == B200_F32 && B * K * hw * crs >= 64LL * 64 * 64 && B * hw < (1LL << 40) &&
+                  C * H * W < (1LL << 31) && H < 16000 && W < 16000 && (long long)dil_h * kh < 16000 &&
+                  (long long)dil_w * kw < 16000;
+  if (!tc) return B200_CONV_SIMT;
+  if (!(e->flags & B200_ENGINE_CONV_GATHER) &&
+      conv_tma_eligible(B, (int)C, (int)H, (int)W, kh, kw, pad_h, pad_w, stride_h, stride_w, dil_h, dil_w))
+    return B200_CONV_TC_TMA;
+  return B200_CONV_TC_GATHER;
+}
+
 }  // namespace b200
 
 using namespace b200;
@@ -171,19 +193,22 @@ int b200_conv2d_fwd(b200_engine *e, int dtype, const void *x, const void *w, voi
 
   const long long crs = C * kh * kw, hw = Ho * Wo;
   const size_t es = dtype_size(dtype);
-  // the tensor-core kernel keeps per-image offsets in 32 bits and packs tap offsets in 14 bits
-  const bool tc = dtype == B200_F32 && B * K * hw * crs >= 64LL * 64 * 64 && B * hw < (1LL << 40) &&
-                  C * H * W < (1LL << 31) && H < 16000 && W < 16000 && (long long)dil_h * kh < 16000 &&
-                  (long long)dil_w * kw < 16000;
   const long long img_bytes = hw * crs * (long long)es;
   long long chunk = std::max<long long>(1, std::min<long long>(B, kColChunkBytes / std::max<long long>(1, img_bytes)));
 
-  if (dtype == B200_F32 && crs <= 32 && K <= 32 && C * H * W < (1LL << 31))
-    return conv_direct_small(e, (const float *)x, (const float *)w, (float *)y, B, (int)C, (int)H, (int)W, (int)K, kh,
-                             kw, pad_h, pad_w, stride_h, stride_w, dil_h, dil_w, (int)Ho, (int)Wo, ep);
-  if (tc)
-    return conv2d_tc(e, (const float *)x, (const float *)w, (float *)y, B, (int)C, (int)H, (int)W, (int)K, kh, kw,
-                     pad_h, pad_w, stride_h, stride_w, dil_h, dil_w, (int)Ho, (int)Wo, ep);
+  switch (conv_path(e, dtype, B, C, H, W, K, kh, kw, pad_h, pad_w, stride_h, stride_w, dil_h, dil_w, Ho, Wo)) {
+    case B200_CONV_DIRECT:
+      return conv_direct_small(e, (const float *)x, (const float *)w, (float *)y, B, (int)C, (int)H, (int)W, (int)K,
+                               kh, kw, pad_h, pad_w, stride_h, stride_w, dil_h, dil_w, (int)Ho, (int)Wo, ep);
+    case B200_CONV_TC_TMA:
+      return conv2d_tma(e, (const float *)x, (const float *)w, (float *)y, B, (int)C, (int)H, (int)W, (int)K, kh, kw,
+                        pad_h, pad_w, stride_h, stride_w, dil_h, dil_w, (int)Ho, (int)Wo, ep);
+    case B200_CONV_TC_GATHER:
+      return conv2d_tc(e, (const float *)x, (const float *)w, (float *)y, B, (int)C, (int)H, (int)W, (int)K, kh, kw,
+                       pad_h, pad_w, stride_h, stride_w, dil_h, dil_w, (int)Ho, (int)Wo, ep);
+    default:
+      break;
+  }
 
   // CUDA-core path: plain im2col of a chunk, then Y_b = Wf . col_b^T per image
   void *colbuf = nullptr;
@@ -199,6 +224,17 @@ int b200_conv2d_fwd(b200_engine *e, int dtype, const void *x, const void *w, voi
   }
   b200_put(e, colbuf, 0);
   return rc;
+}
+
+int b200_conv2d_path(b200_engine *e, int dtype, int64_t B, int64_t C, int64_t H, int64_t W, int64_t K, int kh, int kw,
+                     int pad_h, int pad_w, int stride_h, int stride_w, int dil_h, int dil_w) {
+  if (!e || B < 0 || C <= 0 || H <= 0 || W <= 0 || K <= 0 || kh <= 0 || kw <= 0 || stride_h <= 0 || stride_w <= 0 ||
+      dil_h <= 0 || dil_w <= 0 || pad_h < 0 || pad_w < 0)
+    return -1;
+  const long long Ho = (H + 2 * pad_h - (dil_h * (kh - 1) + 1)) / stride_h + 1;
+  const long long Wo = (W + 2 * pad_w - (dil_w * (kw - 1) + 1)) / stride_w + 1;
+  if (Ho <= 0 || Wo <= 0) return -1;
+  return conv_path(e, dtype, B, C, H, W, K, kh, kw, pad_h, pad_w, stride_h, stride_w, dil_h, dil_w, Ho, Wo);
 }
 
 }  // extern "C"

@@ -465,6 +465,38 @@ __global__ void __launch_bounds__(256) split_permute_filters_kernel(const float 
   }
 }
 
+// Filters (K, C, taps) split into TF32 head/tail AND reordered to (tap, channel) along the
+// reduction index. blk[] receives the arena blocks the caller must release, or nulls when the
+// result came from (or went into) the cache of a buffer declared constant.
+int conv_filters_tap_major(b200_engine *e, const float *w, int K, int C, int taps, TcOperand *wf, void **blk) {
+  const int crs = C * taps;
+  blk[0] = blk[1] = nullptr;
+  wf->ld = crs;
+  if (CachedSplit *cached = find_cached(e, w, 1, K, C, taps, crs)) {
+    wf->p0 = cached->hi;
+    wf->p1 = cached->lo;
+    return B200_OK;
+  }
+  int rc = b200_get(e, (long long)K * crs * 4, &blk[0]);
+  if (rc == B200_OK) rc = b200_get(e, (long long)K * crs * 4, &blk[1]);
+  if (rc != B200_OK) {
+    if (blk[0]) b200_put(e, blk[0], 0);
+    blk[0] = nullptr;
+    return rc;
+  }
+  const long long total = (long long)K * crs;
+  const int blocks = (int)std::max<long long>(1, std::min<long long>((total + 255) / 256, e->sm_count * 16LL));
+  split_permute_filters_kernel<<<blocks, 256, 0, e->stream>>>(w, (float *)blk[0], (float *)blk[1], K, C, taps);
+  B200_CHECK_LAUNCH(e, "split_permute_filters_kernel");
+  wf->p0 = blk[0];
+  wf->p1 = blk[1];
+  if (is_constant(e, w)) {  // filters declared constant: keep the permuted split for the next call
+    add_cached(e, w, CachedSplit{1, K, C, taps, crs, blk[0], blk[1], crs});
+    blk[0] = blk[1] = nullptr;
+  }
+  return B200_OK;
+}
+
 template <int BN, int MODE>
 static int launch_conv_tc(b200_engine *e, const CUtensorMap *tm, ConvTcParams &p) {
   constexpr int STAGE_BYTES = 2 * (CV_A_BYTES + BN * 128);
@@ -498,35 +530,11 @@ int conv2d_tc(b200_engine *e, const float *x, const float *w, float *y, long lon
   TcOperand wf;
   void *blk[2] = {nullptr, nullptr};
   int rc;
-  CachedSplit *cached = mode == 2 ? find_cached(e, w, 1, K, C, kh * kw, crs) : nullptr;
-  if (cached) {
-    wf.p0 = cached->hi;
-    wf.p1 = cached->lo;
-    wf.ld = crs;
-    rc = B200_OK;
-  } else if (mode == 2) {
-    // filters split into TF32 head/tail AND reordered to (tap, channel) along the reduction index
-    rc = b200_get(e, (long long)K * crs * 4, &blk[0]);
-    if (rc == B200_OK) rc = b200_get(e, (long long)K * crs * 4, &blk[1]);
-    if (rc != B200_OK) {
-      if (blk[0]) b200_put(e, blk[0], 0);
-      return rc;
-    }
-    const long long total = (long long)K * crs;
-    const int blocks = (int)std::max<long long>(1, std::min<long long>((total + 255) / 256, e->sm_count * 16LL));
-    split_permute_filters_kernel<<<blocks, 256, 0, e->stream>>>(w, (float *)blk[0], (float *)blk[1], K, C, kh * kw);
-    B200_CHECK_LAUNCH(e, "split_permute_filters_kernel");
-    wf.p0 = blk[0];
-    wf.p1 = blk[1];
-    wf.ld = crs;
-    if (is_constant(e, w)) {  // filters declared constant: keep the permuted split for the next call
-      add_cached(e, w, CachedSplit{1, K, C, kh * kw, crs, blk[0], blk[1], crs});
-      blk[0] = blk[1] = nullptr;
-    }
-  } else {
+  if (mode == 2)
+    rc = conv_filters_tap_major(e, w, K, C, kh * kw, &wf, blk);
+  else
     rc = split_operand_tf32(e, w, K, crs, crs, 1, 0, &wf, &blk[0], &blk[1]);
-    if (rc != B200_OK) return rc;
-  }
+  if (rc != B200_OK) return rc;
   int bn = 128;
   while (bn > 32 && bn / 2 >= K) bn /= 2;
   ConvTcParams p = ConvTcParams();

@@ -1,0 +1,463 @@
+// Implicit-GEMM 2-D convolution whose col operand is built by the TMA unit (float32 as 3xTF32).
+//
+//   y[b][k][p] = sum_q  col[(b,p)][q] * Wf[k][q],   q' = (tap, channel),  p = oh*Wo + ow
+//
+// The same tensor-core mapping as conv_tc.cu (pixels on the 128 TMEM lanes, output channels on
+// the columns, hi*hi and cross terms in two accumulators folded every 256 k by the epilogue
+// warps), but no thread gathers anything: the activations are first rewritten once, channels
+// innermost (NHWC) and split into TF32 head and tail, and every 128-pixel x CK-channel slab of col
+// is then ONE im2col-mode TMA load per head/tail. The TMA unit walks the 128 consecutive output
+// positions across rows and images, applies the tap offset, fills padding with zeros and writes
+// the slab in the swizzled K-major layout the tensor core reads. The rewrite costs 12 bytes per
+// input element; the 9 (kh*kw) re-reads of the activations come from L2.
+//
+// CK = 32 channels per k-block (128-byte rows, 128-byte swizzle), so C must be a multiple of 32.
+// (The kernel is also correct with CK = 16, 64-byte rows and swizzle, but at C = 16 the col slabs
+// are re-read from L2 nine times at 8 bytes per element and the gather kernel, which reads 4, wins.)
+// A 1x1 convolution has no re-reads to save and stays on the gather kernel too.
+// Warp roles (10 warps): 0 TMA producer, 1 MMA issuer + TMEM owner, 2-9 epilogue.
+// No multicast, no clusters. Every wait is bounded; a time-out raises the engine's error word.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstring>
+
+#include "engine.h"
+#include "epilogue.cuh"
+#include "ptx.cuh"
+#include "tc_common.cuh"
+#include "tc_operand.h"
+
+namespace b200 {
+
+// conv_tc.cu: filters split into TF32 head/tail and reordered to (tap, channel); cached for constants
+int conv_filters_tap_major(b200_engine *e, const float *w, int K, int C, int taps, TcOperand *wf, void **blk);
+
+constexpr int CT_BM = 128;
+constexpr int CT_THREADS = 320;  // 10 warps
+
+struct ConvTmaParams {
+  float *y;
+  long long Mtot;  // B * Ho * Wo
+  int K, Wo, hw;
+  int kw, padH, padW, sH, sW, dH, dW;
+  int cblocks;     // C / CK
+  int num_k;       // taps * cblocks
+  int chunk_k;     // k-blocks per accumulation chain
+  int tiles_m, tiles_n;
+  int stages;
+  Epilogue ep;     // bias_kind ROW = per output channel
+  int *err_flag;
+};
+
+__device__ __forceinline__ float ct_tf32(float v) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(v));
+  return __uint_as_float(r);
+}
+__device__ __forceinline__ void ct_tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+
+template <int BN, int CK>
+__global__ void __launch_bounds__(CT_THREADS, 1)
+    conv_tma_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmA1,
+                    const __grid_constant__ CUtensorMap tmW0, const __grid_constant__ CUtensorMap tmW1,
+                    const __grid_constant__ ConvTmaParams p) {
+  constexpr int ROW_BYTES = CK * 4;               // one pixel's (or one filter's) channels of a k-block
+  constexpr int A_BYTES = CT_BM * ROW_BYTES;      // one copy (head or tail) of the col slab
+  constexpr int B_BYTES = BN * ROW_BYTES;
+  constexpr int STAGE_BYTES = 2 * (A_BYTES + B_BYTES);
+  constexpr uint32_t SBO = 8 * ROW_BYTES;         // 8-row groups of the swizzle pattern
+  constexpr uint32_t LAYOUT = CK == 32 ? 2 : 4;   // 128-byte / 64-byte swizzle
+  constexpr int KK = CK / 8;                      // MMAs (k = 8) per k-block
+  constexpr uint32_t IDESC = make_idesc(2, 0, 0, CT_BM, BN);
+  constexpr int ACC_COLS = 2 * BN;
+  constexpr int TMEM_COLS = 2 * ACC_COLS;
+  constexpr int HALF = BN / 2;
+  constexpr int MAX_STAGES = 8;
+
+  extern __shared__ __align__(1024) unsigned char ct_smem_raw[];
+  __shared__ __align__(8) uint64_t full_bar[MAX_STAGES], empty_bar[MAX_STAGES], acc_full[2], acc_empty[2];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int s_fail;
+
+  unsigned char *smem = reinterpret_cast<unsigned char *>(((uintptr_t)ct_smem_raw + 1023) & ~(uintptr_t)1023);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int stages = p.stages;
+  const long long total_tiles = (long long)p.tiles_m * p.tiles_n;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      ptx::mbar_init(&full_bar[s], 1);
+      ptx::mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      ptx::mbar_init(&acc_full[b], 1);
+      ptx::mbar_init(&acc_empty[b], 8);  // one arrival per epilogue warp
+    }
+    ptx::fence_mbar_init();
+    s_fail = 0;
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(&tmem_base_s, TMEM_COLS);
+    ptx::tmem_relinquish();
+  }
+  if (warp == 0 && lane == 0) {
+    ptx::prefetch_tmap(&tmA0);
+    ptx::prefetch_tmap(&tmA1);
+    ptx::prefetch_tmap(&tmW0);
+    ptx::prefetch_tmap(&tmW1);
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = tmem_base_s;
+
+  if (warp == 0) {
+    // ---------------- TMA producer: col slabs (im2col mode) and filter slabs ----------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (long long tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        const int mt = (int)(tile / p.tiles_n), nt = (int)(tile % p.tiles_n);
+        // first output position of the tile -> window origin in the input
+        const long long m0 = (long long)mt * CT_BM;
+        const int n = (int)(m0 / p.hw);
+        const int pix = (int)(m0 - (long long)n * p.hw);
+        const int oh = pix / p.Wo, ow = pix - oh * p.Wo;
+        const int w0 = ow * p.sW - p.padW, h0 = oh * p.sH - p.padH;
+        int cb = 0, r = 0, sx = 0;
+        for (int kb = 0; kb < p.num_k; ++kb) {
+          if (!ptx::mbar_wait_relaxed(&empty_bar[stage], phase ^ 1, 32)) {
+            ok = false;
+            break;
+          }
+          unsigned char *sa = smem + (size_t)stage * STAGE_BYTES;
+          unsigned char *sb = sa + 2 * A_BYTES;
+          ptx::mbar_arrive_expect_tx(&full_bar[stage], STAGE_BYTES);
+          const uint16_t off_w = (uint16_t)(sx * p.dW), off_h = (uint16_t)(r * p.dH);
+          ptx::tma_load_im2col_4d(sa, &tmA0, cb * CK, w0, h0, n, off_w, off_h, &full_bar[stage]);
+          ptx::tma_load_im2col_4d(sa + A_BYTES, &tmA1, cb * CK, w0, h0, n, off_w, off_h, &full_bar[stage]);
+          ptx::tma_load_3d(sb, &tmW0, kb * CK, nt * BN, 0, &full_bar[stage]);
+          ptx::tma_load_3d(sb + B_BYTES, &tmW1, kb * CK, nt * BN, 0, &full_bar[stage]);
+          if (++cb == p.cblocks) {  // q' = (tap, channel): channel blocks run fastest
+            cb = 0;
+            if (++sx == p.kw) {
+              sx = 0;
+              ++r;
+            }
+          }
+          if (++stage == stages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+      if (!ok) s_fail = 1;
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int use = 0;
+      bool ok = true;
+      for (long long tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        for (int kc = 0; kc < p.num_k && ok; kc += p.chunk_k, ++use) {
+          const int buf = use & 1;
+          const uint32_t acc_phase = (uint32_t)((use >> 1) & 1);
+          if (!ptx::mbar_wait(&acc_empty[buf], acc_phase ^ 1)) {
+            ok = false;
+            break;
+          }
+          ptx::tc_fence_after_sync();
+          const uint32_t d_main = tmem_base + (uint32_t)(buf * ACC_COLS);
+          const uint32_t d_tail = d_main + BN;
+          const int kend = kc + p.chunk_k < p.num_k ? kc + p.chunk_k : p.num_k;
+          for (int kb = kc; kb < kend; ++kb) {
+            if (!ptx::mbar_wait(&full_bar[stage], phase)) {
+              ok = false;
+              break;
+            }
+            ptx::tc_fence_after_sync();
+            const uint32_t st = ptx::smem_addr(smem + (size_t)stage * STAGE_BYTES);
+#pragma unroll
+            for (int kk = 0; kk < KK; ++kk) {
+              const uint64_t a_hi = make_smem_desc(st + kk * 32, 16, SBO, LAYOUT);
+              const uint64_t a_lo = make_smem_desc(st + A_BYTES + kk * 32, 16, SBO, LAYOUT);
+              const uint64_t b_hi = make_smem_desc(st + 2 * A_BYTES + kk * 32, 16, SBO, LAYOUT);
+              const uint64_t b_lo = make_smem_desc(st + 2 * A_BYTES + B_BYTES + kk * 32, 16, SBO, LAYOUT);
+              const uint32_t accumulate = (kb > kc || kk > 0) ? 1u : 0u;
+              ptx::mma_tf32(d_main, a_hi, b_hi, IDESC, accumulate);
+              ptx::mma_tf32(d_tail, a_hi, b_lo, IDESC, accumulate);
+              ptx::mma_tf32(d_tail, a_lo, b_hi, IDESC, 1u);
+            }
+            ptx::mma_commit(&empty_bar[stage]);
+            if (++stage == stages) {
+              stage = 0;
+              phase ^= 1;
+            }
+          }
+          if (ok) ptx::mma_commit(&acc_full[buf]);
+        }
+      }
+      if (!ok) s_fail = 1;
+    }
+  } else {
+    // ---------------- epilogue: warps 2..9 ----------------
+    const int quarter = warp & 3;           // TMEM lanes 32*quarter .. +31
+    const int half = (warp - 2) >> 2;       // which half of the BN columns
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    int use = 0;
+    bool ok = true;
+    for (long long tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      const int mt = (int)(tile / p.tiles_n), nt = (int)(tile % p.tiles_n);
+      float acc[HALF];
+#pragma unroll
+      for (int j = 0; j < HALF; ++j) acc[j] = 0.f;
+      for (int kc = 0; kc < p.num_k && ok; kc += p.chunk_k) {
+        const int buf = use & 1;
+        const uint32_t acc_phase = (uint32_t)((use >> 1) & 1);
+        ++use;
+        if (!ptx::mbar_wait_relaxed(&acc_full[buf], acc_phase)) {
+          ok = false;
+          break;
+        }
+        ptx::tc_fence_after_sync();
+#pragma unroll
+        for (int c = 0; c < HALF; c += 16) {
+          uint32_t rm[16], rt[16];
+          ct_tmem_ld16(lane_addr + (uint32_t)(buf * ACC_COLS + half * HALF + c), rm);
+          ct_tmem_ld16(lane_addr + (uint32_t)(buf * ACC_COLS + BN + half * HALF + c), rt);
+          ptx::tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            acc[c + j] = __fadd_rn(acc[c + j], __fadd_rn(__uint_as_float(rm[j]), __uint_as_float(rt[j])));
+        }
+        ptx::tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(&acc_empty[buf]);
+      }
+      if (!ok) break;
+      const long long m = (long long)mt * CT_BM + quarter * 32 + lane;
+      if (m < p.Mtot) {
+        long long b;
+        int pix;
+        if (p.Mtot < (1LL << 31)) {  // the usual case: 32-bit division
+          const uint32_t mu = (uint32_t)m, bu = mu / (uint32_t)p.hw;
+          b = bu;
+          pix = (int)(mu - bu * (uint32_t)p.hw);
+        } else {
+          b = m / p.hw;
+          pix = (int)(m % p.hw);
+        }
+        float *yb = p.y + (b * p.K) * (long long)p.hw + pix;
+        const int n0 = nt * BN + half * HALF;
+#pragma unroll
+        for (int j = 0; j < HALF; ++j) {
+          const int n = n0 + j;
+          if (n < p.K) yb[(long long)n * p.hw] = apply_epilogue<float>(acc[j], p.ep, n, 0);
+        }
+      }
+    }
+    if (!ok) s_fail = 1;
+  }
+
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if (threadIdx.x == 0 && s_fail) atomicExch(p.err_flag, 1);
+  if (warp == 1) {
+    ptx::tc_fence_after_sync();
+    ptx::tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// x (B, C, HW) -> head/tail (B, HW, C): channels innermost, each value split into its TF32 head
+// and the TF32 rounding of the remainder. One 32 x 32 tile per step through shared memory, so both
+// the reads (along HW) and the writes (along C) are contiguous.
+__global__ void __launch_bounds__(256) nhwc_split_kernel(const float *__restrict__ x, float *__restrict__ hi,
+                                                         float *__restrict__ lo, long long B, int C, int HW) {
+  __shared__ float tile[32][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int ptiles = (HW + 31) / 32, ctiles = (C + 31) / 32;
+  const long long per_image = (long long)ptiles * ctiles, total = B * per_image;
+  for (long long t = blockIdx.x; t < total; t += gridDim.x) {
+    const long long b = t / per_image;
+    const int rem = (int)(t - b * per_image);
+    const int ct = rem / ptiles, pt = rem - ct * ptiles;
+    const int c0 = ct * 32, p0 = pt * 32;
+    const float *xb = x + b * (long long)C * HW;
+#pragma unroll
+    for (int j = ty; j < 32; j += 8) {
+      const int c = c0 + j, pp = p0 + tx;
+      tile[j][tx] = (c < C && pp < HW) ? __ldg(xb + (long long)c * HW + pp) : 0.f;
+    }
+    __syncthreads();
+    const long long ob = b * (long long)HW * C;
+#pragma unroll
+    for (int j = ty; j < 32; j += 8) {
+      const int pp = p0 + j, c = c0 + tx;
+      if (pp < HW && c < C) {
+        const float v = tile[tx][j];
+        const float h = ct_tf32(v);
+        const long long o = ob + (long long)pp * C + c;
+        hi[o] = h;
+        lo[o] = ct_tf32(__fsub_rn(v, h));
+      }
+    }
+    __syncthreads();
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+typedef CUresult (*EncodeIm2colFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                   const cuuint64_t *, const int *, const int *, cuuint32_t, cuuint32_t,
+                                   const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static void *driver_entry(const char *name) {
+  void *sym = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  if (cudaGetDriverEntryPoint(name, &sym, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+    return sym;
+  return nullptr;
+}
+
+template <int BN, int CK>
+static int launch_conv_tma(b200_engine *e, const CUtensorMap *tm, ConvTmaParams &p) {
+  constexpr int STAGE_BYTES = 2 * (CT_BM + BN) * CK * 4;
+  auto kern = conv_tma_kernel<BN, CK>;
+  static int attr_dev_mask = 0;
+  const size_t optin = std::min<size_t>(e->smem_optin, 227 * 1024);
+  if (!(attr_dev_mask & (1 << (e->device & 31)))) {
+    cudaFuncAttributes fa;
+    B200_CHECK_CUDA(e, cudaFuncGetAttributes(&fa, kern));
+    B200_CHECK_CUDA(e, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                            (int)(optin - fa.sharedSizeBytes)));
+    attr_dev_mask |= 1 << (e->device & 31);
+  }
+  p.stages = (int)std::max<size_t>(2, std::min<size_t>(8, (optin - 4096) / STAGE_BYTES));
+  const size_t smem = (size_t)p.stages * STAGE_BYTES + 1024;
+  const long long tiles = (long long)p.tiles_m * p.tiles_n;
+  const int grid = (int)std::min<long long>(tiles, e->sm_count);
+  kern<<<grid, CT_THREADS, smem, e->stream>>>(tm[0], tm[1], tm[2], tm[3], p);
+  B200_CHECK_LAUNCH(e, "conv_tma_kernel");
+  e->flags_dirty = true;
+  return B200_OK;
+}
+
+// Whether the TMA unit builds the col operand of this convolution: channels a multiple of 32,
+// more than one tap, window corners and tap offsets inside the ranges an im2col tensor map can
+// encode, and an input of at least 128 KB.
+bool conv_tma_eligible(long long B, int C, int H, int W, int kh, int kw, int padH, int padW, int sH, int sW, int dH,
+                       int dW) {
+  if (C % 32 != 0 || kh * kw == 1) return false;
+  const int spanH = (kh - 1) * dH, spanW = (kw - 1) * dW;
+  if (padH > 128 || padW > 128 || padH - spanH < -128 || padW - spanW < -128) return false;
+  if (spanH > 255 || spanW > 255) return false;
+  if (sH > 8 || sW > 8) return false;
+  if (B >= (1LL << 31)) return false;
+  if (B * C * H * W * 4 < 131072) return false;
+  return true;
+}
+
+// x (B,C,H,W) * w (K,C,kh,kw) -> y (B,K,Ho,Wo), float32. ep.bias_kind ROW = one value per channel.
+int conv2d_tma(b200_engine *e, const float *x, const float *w, float *y, long long B, int C, int H, int W, int K,
+               int kh, int kw, int padH, int padW, int sH, int sW, int dH, int dW, int Ho, int Wo,
+               const Epilogue &ep) {
+  static EncodeTiledFn enc_tiled = (EncodeTiledFn)driver_entry("cuTensorMapEncodeTiled");
+  static EncodeIm2colFn enc_im2col = (EncodeIm2colFn)driver_entry("cuTensorMapEncodeIm2col");
+  if (!enc_tiled || !enc_im2col)
+    return set_error(e, B200_ERR_CUDA, "cuTensorMapEncodeTiled / cuTensorMapEncodeIm2col are not available");
+  const int taps = kh * kw, crs = C * taps;
+  const int ck = 32;
+  const CUtensorMapSwizzle swz = CU_TENSOR_MAP_SWIZZLE_128B;
+
+  TcOperand wf;
+  void *wblk[2] = {nullptr, nullptr};
+  int rc = conv_filters_tap_major(e, w, K, C, taps, &wf, wblk);
+  if (rc != B200_OK) return rc;
+
+  // activations: NHWC, TF32 head and tail
+  const long long xbytes = B * C * H * W * 4;
+  void *xs[2] = {nullptr, nullptr};
+  rc = b200_get(e, xbytes, &xs[0]);
+  if (rc == B200_OK) rc = b200_get(e, xbytes, &xs[1]);
+  if (rc == B200_OK) {
+    const long long tiles = B * ((H * (long long)W + 31) / 32) * ((C + 31) / 32);
+    const int blocks = (int)std::max<long long>(1, std::min<long long>(tiles, e->sm_count * 16LL));
+    nhwc_split_kernel<<<blocks, 256, 0, e->stream>>>(x, (float *)xs[0], (float *)xs[1], B, C, H * W);
+    cudaError_t le = cudaGetLastError();
+    if (le != cudaSuccess) rc = set_error(e, B200_ERR_CUDA, "nhwc_split_kernel: %s", cudaGetErrorString(le));
+    else ++e->launches;
+  }
+
+  int bn = 128;
+  while (bn > 32 && bn / 2 >= K) bn /= 2;
+  ConvTmaParams p = ConvTmaParams();
+  p.y = y;
+  p.Mtot = B * Ho * Wo;
+  p.K = K; p.Wo = Wo; p.hw = Ho * Wo;
+  p.kw = kw; p.padH = padH; p.padW = padW; p.sH = sH; p.sW = sW; p.dH = dH; p.dW = dW;
+  p.cblocks = C / ck;
+  p.num_k = taps * p.cblocks;
+  p.chunk_k = 256 / ck;
+  p.tiles_m = (int)((p.Mtot + CT_BM - 1) / CT_BM);
+  p.tiles_n = (K + bn - 1) / bn;
+  p.ep = ep;
+  p.err_flag = e->d_flags + 2;
+
+  CUtensorMap tm[4];
+  memset((void *)tm, 0, sizeof tm);
+  if (rc == B200_OK) {
+    // activations as (C, W, H, N); the bounding box of window origins runs from -pad to the last
+    // origin whose window still touches the padded image
+    cuuint64_t dims[4] = {(cuuint64_t)C, (cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)B};
+    cuuint64_t strides[3] = {(cuuint64_t)C * 4, (cuuint64_t)W * C * 4, (cuuint64_t)H * W * C * 4};
+    int lower[2] = {-padW, -padH};
+    int upper[2] = {padW - (kw - 1) * dW, padH - (kh - 1) * dH};
+    cuuint32_t estr[4] = {1, (cuuint32_t)sW, (cuuint32_t)sH, 1};
+    for (int h = 0; h < 2 && rc == B200_OK; ++h) {
+      CUresult r = enc_im2col(&tm[h], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, xs[h], dims, strides, lower, upper,
+                              (cuuint32_t)ck, CT_BM, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
+                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+      if (r != CUDA_SUCCESS)
+        rc = set_error(e, B200_ERR_CUDA, "cuTensorMapEncodeIm2col failed (%d): C %d W %d H %d N %lld", (int)r, C, W,
+                       H, B);
+    }
+    // filters as (crs, K, 1), box ck x bn
+    cuuint64_t wdims[3] = {(cuuint64_t)crs, (cuuint64_t)K, 1};
+    cuuint64_t wstrides[2] = {(cuuint64_t)wf.ld * 4, (cuuint64_t)K * wf.ld * 4};
+    cuuint32_t wbox[3] = {(cuuint32_t)ck, (cuuint32_t)bn, 1};
+    cuuint32_t westr[3] = {1, 1, 1};
+    for (int h = 0; h < 2 && rc == B200_OK; ++h) {
+      CUresult r = enc_tiled(&tm[2 + h], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void *>(h ? wf.p1 : wf.p0),
+                             wdims, wstrides, wbox, westr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
+                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+      if (r != CUDA_SUCCESS) rc = set_error(e, B200_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d) for filters", (int)r);
+    }
+  }
+  if (rc == B200_OK) {
+    if (bn == 128) rc = launch_conv_tma<128, 32>(e, tm, p);
+    else if (bn == 64) rc = launch_conv_tma<64, 32>(e, tm, p);
+    else rc = launch_conv_tma<32, 32>(e, tm, p);
+  }
+  for (int h = 0; h < 2; ++h) {
+    if (xs[h]) b200_put(e, xs[h], 0);
+    if (wblk[h]) b200_put(e, wblk[h], 0);
+  }
+  return rc;
+}
+
+}  // namespace b200

@@ -122,6 +122,18 @@ __device__ __forceinline__ void tma_load_3d(void *smem_dst, const void *tmap, in
       "l"(tmap), "r"(smem_addr(bar)), "r"(x), "r"(y), "r"(z)
       : "memory");
 }
+// im2col-mode load over an NHWC tensor map (dims C, W, H, N): `pixelsPerColumn` consecutive output
+// positions starting at the window origin (w, h) of image n, walking W, then H, then N inside the
+// map's bounding box, `channelsPerPixel` channels from c each, read at the filter-tap offset
+// (off_w, off_h) from every window origin. Positions outside the image read as zero.
+__device__ __forceinline__ void tma_load_im2col_4d(void *smem_dst, const void *tmap, int c, int w, int h, int n,
+                                                   uint16_t off_w, uint16_t off_h, uint64_t *bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.im2col.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, "
+      "%6}], [%2], {%7, %8};" ::"r"(smem_addr(smem_dst)),
+      "l"(tmap), "r"(smem_addr(bar)), "r"(c), "r"(w), "r"(h), "r"(n), "h"(off_w), "h"(off_h)
+      : "memory");
+}
 __device__ __forceinline__ void prefetch_tmap(const void *tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
 }

@@ -97,8 +97,9 @@ class Tensor:
 
 
 class Engine:
-    def __init__(self, device=0, arena_bytes=1 << 30, managed=False, defer=True):
-        flags = (_lib.ENGINE_MANAGED if managed else 0) | (0 if defer else _lib.ENGINE_NO_DEFER)
+    def __init__(self, device=0, arena_bytes=1 << 30, managed=False, defer=True, conv_gather=False):
+        flags = ((_lib.ENGINE_MANAGED if managed else 0) | (0 if defer else _lib.ENGINE_NO_DEFER) |
+                 (_lib.ENGINE_CONV_GATHER if conv_gather else 0))
         h = C.c_void_p()
         rc = lib.b200_engine_create(device, arena_bytes, flags, C.byref(h))
         if rc != _lib.OK:
@@ -383,6 +384,13 @@ class Engine:
                                   pad[0], pad[1], stride[0], stride[1], dil[0], dil[1],
                                   C.byref(ep) if ep else None), self.h)
         return prealloc
+
+    def conv2d_path(self, x, w, pad=(0, 0), stride=(1, 1), dil=(1, 1)):
+        """Which kernel Conv2d would run for these operands (one of the _lib.CONV_* values)."""
+        B, Cc, H, W = x.shape
+        K, _, kh, kw = w.shape
+        return lib.b200_conv2d_path(self.h, dtype_code(x.dtype), B, Cc, H, W, K, kh, kw, pad[0], pad[1], stride[0],
+                                    stride[1], dil[0], dil[1])
 
     def Im2Col(self, x, prealloc, kernel, pad=(0, 0), stride=(1, 1), dil=(1, 1)):
         B, Cc, H, W = x.shape

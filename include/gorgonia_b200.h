@@ -67,7 +67,9 @@ enum {
   B200_ENGINE_MANAGED = 1u,  /* arena in CUDA managed memory, preferred location = device:  *
                               * host code may dereference arena pointers, as gorgonia does   *
                               * (cuda/external.go:162, cuda/engine.go:71-72)                 */
-  B200_ENGINE_NO_DEFER = 2u  /* launch each pointwise call at once instead of queueing it   */
+  B200_ENGINE_NO_DEFER = 2u, /* launch each pointwise call at once instead of queueing it   */
+  B200_ENGINE_CONV_GATHER = 4u /* tensor-core convolutions build their col operand with gather *
+                                * warps even where the TMA unit could (tests, comparisons)     */
 };
 int b200_engine_create(int device, size_t arena_bytes, unsigned flags, b200_engine **out);
 int b200_engine_destroy(b200_engine *e);
@@ -343,6 +345,14 @@ int b200_reduce_all_static(b200_engine *e, int dtype, int kind, const void *x, i
 int b200_conv2d_fwd(b200_engine *e, int dtype, const void *x, const void *w, void *y, int64_t B,
                     int64_t C, int64_t H, int64_t W, int64_t K, int kh, int kw, int pad_h, int pad_w,
                     int stride_h, int stride_w, int dil_h, int dil_w, const b200_epilogue *ep);
+/* Which kernel b200_conv2d_fwd would pick for a problem (no device work; -1 for a bad shape):
+ * CUDA cores over an im2col scratch; the direct kernel for a first layer (C*kh*kw <= 32, K <= 32);
+ * tensor cores with the col operand gathered by warps; tensor cores with the col operand built
+ * by the TMA unit in im2col mode from an NHWC copy (C a multiple of 32, more than one tap). */
+enum { B200_CONV_SIMT = 0, B200_CONV_DIRECT = 1, B200_CONV_TC_GATHER = 2, B200_CONV_TC_TMA = 3 };
+int b200_conv2d_path(b200_engine *e, int dtype, int64_t B, int64_t C, int64_t H, int64_t W, int64_t K,
+                     int kh, int kw, int pad_h, int pad_w, int stride_h, int stride_w, int dil_h,
+                     int dil_w);
 int b200_im2col(b200_engine *e, int dtype, const void *x, void *col, int64_t B, int64_t C, int64_t H,
                 int64_t W, int kh, int kw, int pad_h, int pad_w, int stride_h, int stride_w, int dil_h,
                 int dil_w);

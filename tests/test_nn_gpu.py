@@ -120,6 +120,46 @@ def test_conv2d(fresh, case):
     assert_gemm_close(y.numpy(), want2, 1e-5)
 
 
+# inputs of 128 KB or more with C a multiple of 32 and more than one tap: the col operand is built
+# by the TMA unit
+CONV_TMA_CASES = [
+    (8, 32, 20, 20, 64, 3, 3, (1, 1), (1, 1), (1, 1)),
+    (4, 32, 40, 36, 32, 3, 3, (1, 1), (1, 1), (1, 1)),     # image rows that are not a multiple of anything
+    (5, 64, 14, 14, 130, 3, 3, (1, 1), (1, 1), (1, 1)),    # two column tiles, the second ragged
+    (3, 64, 17, 19, 40, 3, 5, (2, 1), (2, 3), (1, 1)),     # odd kernel, pads and strides differ per axis
+    (2, 32, 24, 24, 24, 3, 3, (2, 2), (1, 1), (2, 2)),     # dilation
+    (4, 64, 26, 26, 125, 1, 2, (0, 1), (1, 1), (1, 1)),    # two taps in a row
+    (2, 32, 30, 30, 16, 3, 3, (0, 0), (1, 1), (1, 1)),     # no padding
+    (4, 32, 16, 18, 8, 3, 3, (3, 1), (1, 1), (1, 1)),      # padding wider than the kernel reach
+    (3, 96, 13, 13, 33, 3, 3, (1, 1), (1, 1), (1, 1)),     # 27 k-blocks: more than one accumulation chain
+    (300, 32, 7, 7, 20, 3, 3, (1, 1), (1, 1), (1, 1)),     # tiles that span several images
+]
+
+
+@pytest.mark.parametrize("gather", [False, True])
+@pytest.mark.parametrize("case", CONV_TMA_CASES)
+def test_conv2d_tensor_core_col_paths(case, gather):
+    from gorgonia_b200 import Engine, _lib
+    B, Cc, H, W, K, kh, kw, pad, stride, dil = case
+    e = Engine(device=0, arena_bytes=256 << 20, conv_gather=gather)
+    try:
+        x = util.uniform(94, (B, Cc, H, W)) - np.float32(0.5)
+        w = util.normal(95, (K, Cc, kh, kw), scale=float(np.sqrt(2.0 / (Cc * kh * kw))))
+        want = oracle.conv2d(x, w, pad, stride, dil)
+        tx, tw = e.tensor(x), e.tensor(w)
+        assert e.conv2d_path(tx, tw, pad, stride, dil) == (_lib.CONV_TC_GATHER if gather else _lib.CONV_TC_TMA)
+        y = e.empty(want.shape)
+        e.Conv2d(tx, tw, y, pad, stride, dil)
+        assert_gemm_close(y.numpy(), want, 1e-5)
+        bias = util.normal(96, K, scale=0.1)
+        e.Conv2d(tx, tw, y, pad, stride, dil, bias=e.tensor(bias), act="rectify")
+        t = (want + bias[None, :, None, None]).astype(np.float32)
+        assert_gemm_close(y.numpy(), t * (t >= 0), 1e-5)
+        e.Signal()
+    finally:
+        e.Close()
+
+
 def test_conv2d_matches_reference_pipeline(fresh):
     # Conv2d as gorgonia spells it (nn.go:264-298): Im2Col -> MatMul(transB) -> Transpose(0,3,1,2)
     e = fresh
