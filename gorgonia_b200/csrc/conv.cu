@@ -119,9 +119,115 @@ __global__ void __launch_bounds__(256) conv_direct_small_kernel(const float *__r
   }
 }
 
+// The same first-layer case at its usual geometry: 3x3 window, pad 1, stride 1, no dilation, at
+// most 3 input channels, image width a multiple of 4. One thread computes FOUR neighbouring
+// outputs of a row for 16 filters at a time: the 6 inputs of a window row (one aligned float4 and
+// the two halo words) serve 3 taps x 4 outputs, a filter word read from shared memory (a broadcast)
+// feeds 4 multiply-adds, and results leave as float4 stores. That is 4 multiply-adds per
+// non-arithmetic instruction instead of the general kernel's one, which is what bounds a layer
+// whose reduction is only 9 or 27 long. Bias and activation are compile-time variants.
+template <int C, int ACT, bool BIAS>
+__global__ void __launch_bounds__(256, 2) conv3x3_first_kernel(const float *__restrict__ x, const float *__restrict__ w,
+                                                            float *__restrict__ y, const float *__restrict__ bias,
+                                                            float alpha, long long groups, int H, int W, int K) {
+  constexpr int Q = C * 9;
+  __shared__ __align__(16) float ws[Q * 32];  // [q][k], zero for k >= K
+  __shared__ float bs[32];
+  for (int i = threadIdx.x; i < Q * 32; i += blockDim.x) {
+    const int q = i >> 5, k = i & 31;
+    ws[i] = k < K ? w[k * Q + q] : 0.f;
+  }
+  if (threadIdx.x < 32) bs[threadIdx.x] = (BIAS && threadIdx.x < K) ? bias[threadIdx.x] : 0.f;
+  __syncthreads();
+  const int Wg = W >> 2;
+  const long long per_image = (long long)H * Wg;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x; g < groups; g += stride) {
+    const long long b = g / per_image;
+    const int rem = (int)(g - b * per_image);
+    const int oh = rem / Wg, og = rem - oh * Wg, ow = og << 2;
+    const float *xb = x + b * (long long)C * H * W + ow;
+    float *yb = y + (b * K) * (long long)H * W + (long long)oh * W + ow;
+    for (int k0 = 0; k0 < K; k0 += 16) {
+      float acc[4][16];
+#pragma unroll
+      for (int pz = 0; pz < 4; ++pz)
+#pragma unroll
+        for (int k = 0; k < 16; ++k) acc[pz][k] = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < C; ++c) {  // not unrolled: one channel's 18 inputs in registers at a time
+#pragma unroll
+        for (int r = 0; r < 3; ++r) {
+          const int ih = oh - 1 + r;
+          float in[6] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+          if ((unsigned)ih < (unsigned)H) {
+            const float *row = xb + ((long long)c * H + ih) * W;
+            const float4 mid = __ldg(reinterpret_cast<const float4 *>(row));
+            in[1] = mid.x; in[2] = mid.y; in[3] = mid.z; in[4] = mid.w;
+            if (og > 0) in[0] = __ldg(row - 1);
+            if (og < Wg - 1) in[5] = __ldg(row + 4);
+          }
+#pragma unroll
+          for (int sx = 0; sx < 3; ++sx) {
+            const float *wq = &ws[(c * 9 + r * 3 + sx) * 32 + k0];
+#pragma unroll
+            for (int k4 = 0; k4 < 16; k4 += 4) {
+              const float4 wv = *reinterpret_cast<const float4 *>(wq + k4);
+#pragma unroll
+              for (int pz = 0; pz < 4; ++pz) {
+                acc[pz][k4 + 0] = fmaf(in[pz + sx], wv.x, acc[pz][k4 + 0]);
+                acc[pz][k4 + 1] = fmaf(in[pz + sx], wv.y, acc[pz][k4 + 1]);
+                acc[pz][k4 + 2] = fmaf(in[pz + sx], wv.z, acc[pz][k4 + 2]);
+                acc[pz][k4 + 3] = fmaf(in[pz + sx], wv.w, acc[pz][k4 + 3]);
+              }
+            }
+          }
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < 16; ++k) {
+        if (k0 + k < K) {
+          float o[4];
+#pragma unroll
+          for (int pz = 0; pz < 4; ++pz) {
+            float t = acc[pz][k];
+            if (BIAS) t = __fadd_rn(t, bs[k0 + k]);
+            o[pz] = apply_act<float>(t, ACT, alpha);
+          }
+          *reinterpret_cast<float4 *>(yb + (long long)(k0 + k) * H * W) = make_float4(o[0], o[1], o[2], o[3]);
+        }
+      }
+    }
+  }
+}
+
+template <int C>
+static int launch_conv3x3_first(b200_engine *e, const float *x, const float *w, float *y, long long B, int H, int W,
+                                int K, const Epilogue &ep) {
+  const long long groups = B * H * (W / 4);
+  const int blocks = (int)std::max<long long>(1, std::min<long long>((groups + 255) / 256, (long long)e->sm_count * 16));
+  const float *bias = (const float *)ep.bias;
+  const float alpha = (float)ep.alpha;
+#define B200_FIRST(ACT, BIAS) \
+  conv3x3_first_kernel<C, ACT, BIAS><<<blocks, 256, 0, e->stream>>>(x, w, y, bias, alpha, groups, H, W, K)
+  const bool hb = ep.bias_kind != B200_BIAS_NONE;
+  if (ep.act == B200_ACT_NONE) { if (hb) B200_FIRST(B200_ACT_NONE, true); else B200_FIRST(B200_ACT_NONE, false); }
+  else if (ep.act == B200_ACT_RECTIFY) { if (hb) B200_FIRST(B200_ACT_RECTIFY, true); else B200_FIRST(B200_ACT_RECTIFY, false); }
+  else { if (hb) B200_FIRST(B200_ACT_LEAKY, true); else B200_FIRST(B200_ACT_LEAKY, false); }
+#undef B200_FIRST
+  B200_CHECK_LAUNCH(e, "conv3x3_first_kernel");
+  return B200_OK;
+}
+
 static int conv_direct_small(b200_engine *e, const float *x, const float *w, float *y, long long B, int C, int H,
                              int W, int K, int kh, int kw, int padH, int padW, int sH, int sW, int dH, int dW, int Ho,
                              int Wo, const Epilogue &ep) {
+  if (kh == 3 && kw == 3 && padH == 1 && padW == 1 && sH == 1 && sW == 1 && dH == 1 && dW == 1 && C <= 3 &&
+      W % 4 == 0 && ((uintptr_t)x | (uintptr_t)y) % 16 == 0) {
+    if (C == 1) return launch_conv3x3_first<1>(e, x, w, y, B, H, W, K, ep);
+    if (C == 2) return launch_conv3x3_first<2>(e, x, w, y, B, H, W, K, ep);
+    return launch_conv3x3_first<3>(e, x, w, y, B, H, W, K, ep);
+  }
   const long long Mtot = B * Ho * Wo;
   const float *zero = reinterpret_cast<const float *>(e->d_flags + 8);  // zeroed at engine creation, never written
   const int blocks = (int)std::max<long long>(1, std::min<long long>((Mtot + 255) / 256, (long long)e->sm_count * 16));
