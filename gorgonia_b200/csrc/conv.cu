@@ -22,6 +22,10 @@ int conv2d_tc(b200_engine *e, const float *x, const float *w, float *y, long lon
 int conv2d_tma(b200_engine *e, const float *x, const float *w, float *y, long long B, int C, int H, int W, int K,
                int kh, int kw, int padH, int padW, int sH, int sW, int dH, int dW, int Ho, int Wo,
                const Epilogue &ep);
+int conv2d_win(b200_engine *e, const float *x, const float *w, float *y, long long B, int C, int H, int W, int K,
+               int kh, int kw, int padH, int padW, int dH, int dW, int Ho, int Wo, const Epilogue &ep);
+bool conv_win_eligible(const b200_engine *e, long long B, int C, int H, int W, int K, int kh, int kw, int padH,
+                       int padW, int sH, int sW, int dH, int dW, int Ho, int Wo);
 bool conv_tma_eligible(long long B, int C, int H, int W, int kh, int kw, int padH, int padW, int sH, int sW, int dH,
                        int dW);
 int gemm_simt(b200_engine *e, int dtype, int transA, int transB, long long M, long long N, long long K,
@@ -258,6 +262,10 @@ static int conv_path(const b200_engine *e, int dtype, long long B, long long C, 
                   (long long)dil_w * kw < 16000;
   if (!tc) return B200_CONV_SIMT;
   if (!(e->flags & B200_ENGINE_CONV_GATHER) &&
+      conv_win_eligible(e, B, (int)C, (int)H, (int)W, (int)K, kh, kw, pad_h, pad_w, stride_h, stride_w, dil_h, dil_w,
+                        (int)Ho, (int)Wo))
+    return B200_CONV_TC_WINDOW;
+  if (!(e->flags & B200_ENGINE_CONV_GATHER) &&
       conv_tma_eligible(B, (int)C, (int)H, (int)W, kh, kw, pad_h, pad_w, stride_h, stride_w, dil_h, dil_w))
     return B200_CONV_TC_TMA;
   return B200_CONV_TC_GATHER;
@@ -309,6 +317,9 @@ int b200_conv2d_fwd(b200_engine *e, int dtype, const void *x, const void *w, voi
     case B200_CONV_TC_TMA:
       return conv2d_tma(e, (const float *)x, (const float *)w, (float *)y, B, (int)C, (int)H, (int)W, (int)K, kh, kw,
                         pad_h, pad_w, stride_h, stride_w, dil_h, dil_w, (int)Ho, (int)Wo, ep);
+    case B200_CONV_TC_WINDOW:
+      return conv2d_win(e, (const float *)x, (const float *)w, (float *)y, B, (int)C, (int)H, (int)W, (int)K, kh, kw,
+                        pad_h, pad_w, dil_h, dil_w, (int)Ho, (int)Wo, ep);
     case B200_CONV_TC_GATHER:
       return conv2d_tc(e, (const float *)x, (const float *)w, (float *)y, B, (int)C, (int)H, (int)W, (int)K, kh, kw,
                        pad_h, pad_w, stride_h, stride_w, dil_h, dil_w, (int)Ho, (int)Wo, ep);

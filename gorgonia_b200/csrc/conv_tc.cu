@@ -98,6 +98,9 @@ __global__ void __launch_bounds__(CV_THREADS, 1)
   constexpr int B_BYTES = BN * 128;
   constexpr int STAGE_BYTES = 2 * (CV_A_BYTES + B_BYTES);
   constexpr uint32_t IDESC = make_idesc(2, 0, 0, CV_BM, BN);
+  // head x [filter head | filter tail] as ONE instruction of width 2*BN: the tail slab follows the
+  // head slab in shared memory, the cross-term accumulator follows the main one in tensor memory
+  constexpr uint32_t IDESC_WIDE = make_idesc(2, 0, 0, CV_BM, 2 * BN);
   constexpr int ACC_COLS = 2 * BN;          // main + cross-term accumulator
   constexpr int TMEM_COLS = 2 * ACC_COLS;   // double-buffered; power of two >= 128 for BN >= 32
   constexpr int HALF = BN / 2;              // columns folded by one epilogue warp
@@ -194,10 +197,8 @@ __global__ void __launch_bounds__(CV_THREADS, 1)
               const uint64_t a_hi = make_smem_desc(st + kk * 32, 16, 1024, 2);
               const uint64_t a_lo = make_smem_desc(st + CV_A_BYTES + kk * 32, 16, 1024, 2);
               const uint64_t b_hi = make_smem_desc(st + 2 * CV_A_BYTES + kk * 32, 16, 1024, 2);
-              const uint64_t b_lo = make_smem_desc(st + 2 * CV_A_BYTES + B_BYTES + kk * 32, 16, 1024, 2);
               const uint32_t accumulate = (kb > kc || kk > 0) ? 1u : 0u;
-              ptx::mma_tf32(d_main, a_hi, b_hi, IDESC, accumulate);
-              ptx::mma_tf32(d_tail, a_hi, b_lo, IDESC, accumulate);
+              ptx::mma_tf32(d_main, a_hi, b_hi, IDESC_WIDE, accumulate);
               ptx::mma_tf32(d_tail, a_lo, b_hi, IDESC, 1u);
             }
             ptx::mma_commit(&empty_bar[stage]);

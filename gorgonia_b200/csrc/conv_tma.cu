@@ -79,6 +79,9 @@ __global__ void __launch_bounds__(CT_THREADS, 1)
   constexpr uint32_t LAYOUT = CK == 32 ? 2 : 4;   // 128-byte / 64-byte swizzle
   constexpr int KK = CK / 8;                      // MMAs (k = 8) per k-block
   constexpr uint32_t IDESC = make_idesc(2, 0, 0, CT_BM, BN);
+  // head x [filter head | filter tail] as ONE instruction of width 2*BN: the tail slab follows the
+  // head slab in shared memory, the cross-term accumulator follows the main one in tensor memory
+  constexpr uint32_t IDESC_WIDE = make_idesc(2, 0, 0, CT_BM, 2 * BN);
   constexpr int ACC_COLS = 2 * BN;
   constexpr int TMEM_COLS = 2 * ACC_COLS;
   constexpr int HALF = BN / 2;
@@ -195,10 +198,8 @@ __global__ void __launch_bounds__(CT_THREADS, 1)
               const uint64_t a_hi = make_smem_desc(st + kk * 32, 16, SBO, LAYOUT);
               const uint64_t a_lo = make_smem_desc(st + A_BYTES + kk * 32, 16, SBO, LAYOUT);
               const uint64_t b_hi = make_smem_desc(st + 2 * A_BYTES + kk * 32, 16, SBO, LAYOUT);
-              const uint64_t b_lo = make_smem_desc(st + 2 * A_BYTES + B_BYTES + kk * 32, 16, SBO, LAYOUT);
               const uint32_t accumulate = (kb > kc || kk > 0) ? 1u : 0u;
-              ptx::mma_tf32(d_main, a_hi, b_hi, IDESC, accumulate);
-              ptx::mma_tf32(d_tail, a_hi, b_lo, IDESC, accumulate);
+              ptx::mma_tf32(d_main, a_hi, b_hi, IDESC_WIDE, accumulate);
               ptx::mma_tf32(d_tail, a_lo, b_hi, IDESC, 1u);
             }
             ptx::mma_commit(&empty_bar[stage]);
@@ -318,6 +319,21 @@ __global__ void __launch_bounds__(256) nhwc_split_kernel(const float *__restrict
   }
 }
 
+// Rewrites x (B, C, HW) as NHWC TF32 head/tail into two fresh arena blocks xs[0], xs[1], which the
+// caller releases.
+int conv_nhwc_split(b200_engine *e, const float *x, long long B, int C, int HW, void **xs) {
+  const long long xbytes = B * C * HW * 4;
+  xs[0] = xs[1] = nullptr;
+  int rc = b200_get(e, xbytes, &xs[0]);
+  if (rc == B200_OK) rc = b200_get(e, xbytes, &xs[1]);
+  if (rc != B200_OK) return rc;
+  const long long tiles = B * ((HW + 31) / 32) * ((C + 31) / 32);
+  const int blocks = (int)std::max<long long>(1, std::min<long long>(tiles, e->sm_count * 16LL));
+  nhwc_split_kernel<<<blocks, 256, 0, e->stream>>>(x, (float *)xs[0], (float *)xs[1], B, C, HW);
+  B200_CHECK_LAUNCH(e, "nhwc_split_kernel");
+  return B200_OK;
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -390,18 +406,8 @@ int conv2d_tma(b200_engine *e, const float *x, const float *w, float *y, long lo
   if (rc != B200_OK) return rc;
 
   // activations: NHWC, TF32 head and tail
-  const long long xbytes = B * C * H * W * 4;
   void *xs[2] = {nullptr, nullptr};
-  rc = b200_get(e, xbytes, &xs[0]);
-  if (rc == B200_OK) rc = b200_get(e, xbytes, &xs[1]);
-  if (rc == B200_OK) {
-    const long long tiles = B * ((H * (long long)W + 31) / 32) * ((C + 31) / 32);
-    const int blocks = (int)std::max<long long>(1, std::min<long long>(tiles, e->sm_count * 16LL));
-    nhwc_split_kernel<<<blocks, 256, 0, e->stream>>>(x, (float *)xs[0], (float *)xs[1], B, C, H * W);
-    cudaError_t le = cudaGetLastError();
-    if (le != cudaSuccess) rc = set_error(e, B200_ERR_CUDA, "nhwc_split_kernel: %s", cudaGetErrorString(le));
-    else ++e->launches;
-  }
+  rc = conv_nhwc_split(e, x, B, C, H * W, xs);
 
   int bn = 128;
   while (bn > 32 && bn / 2 >= K) bn /= 2;

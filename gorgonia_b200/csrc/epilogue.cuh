@@ -60,4 +60,45 @@ __device__ __forceinline__ T apply_epilogue(T acc, const Epilogue &ep, long long
   return apply_act<T>(t, ep.act, (T)ep.alpha);
 }
 
+// Stores the N accumulators one thread holds for N consecutive output channels of ONE position of
+// an NCHW tensor: y[n * plane] = act(acc[n] + bias[n]). `bias` points at this column tile's first
+// channel (shared or global memory, or null), `valid` is how many of the N channels exist. The
+// activation switch sits outside the loops so that each loop body is straight-line code.
+template <int N, int ACT, bool BIAS>
+__device__ __forceinline__ void store_channels_variant(const float (&acc)[N], float *y, long long plane, int valid,
+                                                       const float *bias, float alpha) {
+  if (valid >= N) {
+#pragma unroll
+    for (int j = 0; j < N; ++j) {
+      float t = acc[j];
+      if (BIAS) t = __fadd_rn(t, bias[j]);
+      *y = apply_act<float>(t, ACT, alpha);
+      y += plane;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < N; ++j) {
+      if (j < valid) {
+        float t = acc[j];
+        if (BIAS) t = __fadd_rn(t, bias[j]);
+        *y = apply_act<float>(t, ACT, alpha);
+      }
+      y += plane;
+    }
+  }
+}
+template <int N>
+__device__ __forceinline__ void store_channels(const float (&acc)[N], float *y, long long plane, int valid,
+                                               const float *bias, int act, float alpha) {
+  if (bias) {
+    if (act == B200_ACT_NONE) store_channels_variant<N, B200_ACT_NONE, true>(acc, y, plane, valid, bias, alpha);
+    else if (act == B200_ACT_RECTIFY) store_channels_variant<N, B200_ACT_RECTIFY, true>(acc, y, plane, valid, bias, alpha);
+    else store_channels_variant<N, B200_ACT_LEAKY, true>(acc, y, plane, valid, bias, alpha);
+  } else {
+    if (act == B200_ACT_NONE) store_channels_variant<N, B200_ACT_NONE, false>(acc, y, plane, valid, bias, alpha);
+    else if (act == B200_ACT_RECTIFY) store_channels_variant<N, B200_ACT_RECTIFY, false>(acc, y, plane, valid, bias, alpha);
+    else store_channels_variant<N, B200_ACT_LEAKY, false>(acc, y, plane, valid, bias, alpha);
+  }
+}
+
 }  // namespace b200

@@ -83,6 +83,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
   constexpr int STAGE_BYTES = NSPLIT * (A_BYTES + B_BYTES);
   constexpr int MN_PER_BOX = TC_ROW_BYTES / ES;    // m/n elements covered by one MN-major box
   constexpr uint32_t IDESC = make_idesc(TERMS == 1 ? 1 : 2, A_MN, B_MN, TC_BM, BN);
+  // 3xTF32: B's head and tail slabs are adjacent in shared memory, and so are the main and the
+  // cross-term accumulator in tensor memory, so A_head x [B_head | B_tail] is ONE instruction of
+  // width 2*BN. An instruction costs a fixed ~65 cycles on top of its arithmetic: two per k step
+  // beat three.
+  constexpr uint32_t IDESC_WIDE = make_idesc(2, A_MN, B_MN, TC_BM, TERMS == 1 ? BN : 2 * BN);
   constexpr int MAX_STAGES = 8;
   // TMEM columns of one accumulator buffer: 3xTF32 keeps the cross terms in a second accumulator
   constexpr int ACC_COLS = TERMS == 1 ? BN : 2 * BN;
@@ -237,8 +242,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
               if (TERMS == 1) {
                 ptx::mma_f16(d_main, ad[0], bd[0], IDESC, accumulate);
               } else {
-                ptx::mma_tf32(d_main, ad[0], bd[0], IDESC, accumulate);            // hi * hi
-                ptx::mma_tf32(d_tail, ad[0], bd[NSPLIT - 1], IDESC, accumulate);   // hi * lo
+                ptx::mma_tf32(d_main, ad[0], bd[0], IDESC_WIDE, accumulate);       // hi * [hi | lo]
                 ptx::mma_tf32(d_tail, ad[NSPLIT - 1], bd[0], IDESC, 1u);           // lo * hi
               }
             }

@@ -30,6 +30,21 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_
   return d;
 }
 
+// The same descriptor in two 32-bit halves, for issue loops that only ever change the address:
+// the high word (stride offset, version, layout) is fixed per operand, the low word is
+// (address >> 4) | LBO field, and a step of n bytes along a row adds n >> 4 to it.
+__device__ __forceinline__ uint32_t desc_hi(uint32_t sbo_bytes, uint32_t layout_type) {
+  return ((sbo_bytes >> 4) & 0x3FFF) | (1u << 14) | (layout_type << 29);
+}
+__device__ __forceinline__ uint32_t desc_lo(uint32_t saddr, uint32_t lbo_bytes = 16) {
+  return ((saddr >> 4) & 0x3FFF) | (((lbo_bytes >> 4) & 0x3FFF) << 16);
+}
+__device__ __forceinline__ uint64_t desc_pack(uint32_t lo, uint32_t hi) {
+  uint64_t d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
+  return d;
+}
+
 // Instruction descriptor of kind::f16 / kind::tf32: D format F32 (1) at [4,6), A format [7,10),
 // B format [10,13) (1 = BF16, 2 = TF32), A major [15], B major [16] (1 = MN-major),
 // N >> 3 at [17,23), M >> 4 at [24,29).

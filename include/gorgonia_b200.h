@@ -348,8 +348,11 @@ int b200_conv2d_fwd(b200_engine *e, int dtype, const void *x, const void *w, voi
 /* Which kernel b200_conv2d_fwd would pick for a problem (no device work; -1 for a bad shape):
  * CUDA cores over an im2col scratch; the direct kernel for a first layer (C*kh*kw <= 32, K <= 32);
  * tensor cores with the col operand gathered by warps; tensor cores with the col operand built
- * by the TMA unit in im2col mode from an NHWC copy (C a multiple of 32, more than one tap). */
-enum { B200_CONV_SIMT = 0, B200_CONV_DIRECT = 1, B200_CONV_TC_GATHER = 2, B200_CONV_TC_TMA = 3 };
+ * by the TMA unit in im2col mode from an NHWC copy (C a multiple of 32, more than one tap);
+ * tensor cores reading every tap in place from an input window held in shared memory (stride 1,
+ * C = 16, 32 or 64, output planes that 16 x 16 tiles cover well). */
+enum { B200_CONV_SIMT = 0, B200_CONV_DIRECT = 1, B200_CONV_TC_GATHER = 2, B200_CONV_TC_TMA = 3,
+       B200_CONV_TC_WINDOW = 4 };
 int b200_conv2d_path(b200_engine *e, int dtype, int64_t B, int64_t C, int64_t H, int64_t W, int64_t K,
                      int kh, int kw, int pad_h, int pad_w, int stride_h, int stride_w, int dil_h,
                      int dil_w);

@@ -125,19 +125,34 @@ def test_conv2d(fresh, case):
 CONV_TMA_CASES = [
     (8, 32, 20, 20, 64, 3, 3, (1, 1), (1, 1), (1, 1)),
     (4, 32, 40, 36, 32, 3, 3, (1, 1), (1, 1), (1, 1)),     # image rows that are not a multiple of anything
-    (5, 64, 14, 14, 130, 3, 3, (1, 1), (1, 1), (1, 1)),    # two column tiles, the second ragged
+    (5, 64, 12, 12, 130, 3, 3, (1, 1), (1, 1), (1, 1)),    # two column tiles, the second ragged
     (3, 64, 17, 19, 40, 3, 5, (2, 1), (2, 3), (1, 1)),     # odd kernel, pads and strides differ per axis
     (2, 32, 24, 24, 24, 3, 3, (2, 2), (1, 1), (2, 2)),     # dilation
     (4, 64, 26, 26, 125, 1, 2, (0, 1), (1, 1), (1, 1)),    # two taps in a row
-    (2, 32, 30, 30, 16, 3, 3, (0, 0), (1, 1), (1, 1)),     # no padding
+    (2, 32, 36, 36, 16, 3, 3, (0, 0), (1, 1), (1, 1)),     # no padding
     (4, 32, 16, 18, 8, 3, 3, (3, 1), (1, 1), (1, 1)),      # padding wider than the kernel reach
     (3, 96, 13, 13, 33, 3, 3, (1, 1), (1, 1), (1, 1)),     # 27 k-blocks: more than one accumulation chain
     (300, 32, 7, 7, 20, 3, 3, (1, 1), (1, 1), (1, 1)),     # tiles that span several images
 ]
 
 
+# stride 1, C = 16 / 32 / 64, output planes that 16 x 16 tiles cover well: every tap reads an input
+# window held in shared memory
+CONV_WIN_CASES = [
+    (4, 16, 48, 48, 32, 3, 3, (1, 1), (1, 1), (1, 1)),     # 16-channel rows (tiny-YOLO conv1 shape)
+    (3, 32, 30, 45, 64, 3, 3, (1, 1), (1, 1), (1, 1)),     # ragged tiles on both axes
+    (2, 64, 32, 32, 70, 3, 3, (1, 1), (1, 1), (1, 1)),     # two channel blocks, two column tiles
+    (5, 64, 14, 14, 130, 3, 3, (1, 1), (1, 1), (1, 1)),    # LeNet-sized planes: one tile per image
+    (4, 16, 32, 32, 24, 3, 3, (2, 2), (1, 1), (2, 2)),     # dilation
+    (4, 16, 28, 28, 16, 5, 5, (2, 2), (1, 1), (1, 1)),     # 25 taps: two accumulation chains
+    (2, 32, 46, 31, 40, 1, 3, (0, 1), (1, 1), (1, 1)),     # one row of taps
+    (2, 32, 32, 32, 8, 3, 3, (0, 0), (1, 1), (1, 1)),      # no padding
+    (2, 32, 29, 29, 8, 2, 2, (1, 1), (1, 1), (1, 1)),      # even kernel
+]
+
+
 @pytest.mark.parametrize("gather", [False, True])
-@pytest.mark.parametrize("case", CONV_TMA_CASES)
+@pytest.mark.parametrize("case", CONV_TMA_CASES + CONV_WIN_CASES)
 def test_conv2d_tensor_core_col_paths(case, gather):
     from gorgonia_b200 import Engine, _lib
     B, Cc, H, W, K, kh, kw, pad, stride, dil = case
@@ -147,7 +162,13 @@ def test_conv2d_tensor_core_col_paths(case, gather):
         w = util.normal(95, (K, Cc, kh, kw), scale=float(np.sqrt(2.0 / (Cc * kh * kw))))
         want = oracle.conv2d(x, w, pad, stride, dil)
         tx, tw = e.tensor(x), e.tensor(w)
-        assert e.conv2d_path(tx, tw, pad, stride, dil) == (_lib.CONV_TC_GATHER if gather else _lib.CONV_TC_TMA)
+        path = e.conv2d_path(tx, tw, pad, stride, dil)
+        if gather:
+            assert path == _lib.CONV_TC_GATHER
+        elif case in CONV_WIN_CASES:
+            assert path == _lib.CONV_TC_WINDOW
+        else:
+            assert path in (_lib.CONV_TC_TMA, _lib.CONV_TC_WINDOW)
         y = e.empty(want.shape)
         e.Conv2d(tx, tw, y, pad, stride, dil)
         assert_gemm_close(y.numpy(), want, 1e-5)
