@@ -319,6 +319,56 @@ __global__ void __launch_bounds__(256) nhwc_split_kernel(const float *__restrict
   }
 }
 
+// The same rewrite for planes whose size is a multiple of 4 (so every channel row starts on a
+// 16-byte boundary): a tile of CT channels x 128 positions is read as float4 along the positions
+// (512 contiguous bytes per warp and channel), turned in shared memory (row pitch 129 words: the
+// four channels a thread gathers for one position fall into distinct banks), and written as float4
+// along the channels, CT * 4 contiguous bytes per position.
+template <int CT>
+__global__ void __launch_bounds__(256) nhwc_split4_kernel(const float *__restrict__ x, float *__restrict__ hi,
+                                                          float *__restrict__ lo, long long B, int C, int HW) {
+  constexpr int PT = 128, PITCH = PT + 1;
+  __shared__ float tile[CT * PITCH];
+  const int ptiles = (HW + PT - 1) / PT, ctiles = C / CT;
+  const long long per_image = (long long)ptiles * ctiles, total = B * per_image;
+  for (long long t = blockIdx.x; t < total; t += gridDim.x) {
+    const long long b = t / per_image;
+    const int rem = (int)(t - b * per_image);
+    const int ct = rem / ptiles, pt = rem - ct * ptiles;
+    const int c0 = ct * CT, p0 = pt * PT;
+    const float *xb = x + (b * C + c0) * (long long)HW + p0;
+    // load: float4 q of channel row c covers positions 4q .. 4q+3
+#pragma unroll
+    for (int i = threadIdx.x; i < CT * (PT / 4); i += 256) {
+      const int c = i / (PT / 4), q = i - c * (PT / 4);
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (p0 + 4 * q < HW) v = __ldg(reinterpret_cast<const float4 *>(xb + (long long)c * HW) + q);
+      float *d = &tile[c * PITCH + 4 * q];
+      d[0] = v.x; d[1] = v.y; d[2] = v.z; d[3] = v.w;
+    }
+    __syncthreads();
+    // store: thread -> (position, group of 4 channels), channel groups fastest
+    float *ho = hi + (b * HW + p0) * (long long)C + c0;
+    float *lo_o = lo + (b * HW + p0) * (long long)C + c0;
+#pragma unroll
+    for (int i = threadIdx.x; i < PT * (CT / 4); i += 256) {
+      const int pp = i / (CT / 4), cg = i - pp * (CT / 4);
+      if (p0 + pp < HW) {
+        float v[4], h[4], l[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          v[k] = tile[(4 * cg + k) * PITCH + pp];
+          h[k] = ct_tf32(v[k]);
+          l[k] = ct_tf32(__fsub_rn(v[k], h[k]));
+        }
+        *reinterpret_cast<float4 *>(ho + (long long)pp * C + 4 * cg) = make_float4(h[0], h[1], h[2], h[3]);
+        *reinterpret_cast<float4 *>(lo_o + (long long)pp * C + 4 * cg) = make_float4(l[0], l[1], l[2], l[3]);
+      }
+    }
+    __syncthreads();
+  }
+}
+
 // Rewrites x (B, C, HW) as NHWC TF32 head/tail into two fresh arena blocks xs[0], xs[1], which the
 // caller releases.
 int conv_nhwc_split(b200_engine *e, const float *x, long long B, int C, int HW, void **xs) {
@@ -327,6 +377,17 @@ int conv_nhwc_split(b200_engine *e, const float *x, long long B, int C, int HW, 
   int rc = b200_get(e, xbytes, &xs[0]);
   if (rc == B200_OK) rc = b200_get(e, xbytes, &xs[1]);
   if (rc != B200_OK) return rc;
+  if (HW % 4 == 0 && C % 16 == 0 && (uintptr_t)x % 16 == 0) {
+    const int ct = C % 32 == 0 ? 32 : 16;
+    const long long tiles = B * ((HW + 127) / 128) * (C / ct);
+    const int blocks = (int)std::max<long long>(1, std::min<long long>(tiles, e->sm_count * 32LL));
+    if (ct == 32)
+      nhwc_split4_kernel<32><<<blocks, 256, 0, e->stream>>>(x, (float *)xs[0], (float *)xs[1], B, C, HW);
+    else
+      nhwc_split4_kernel<16><<<blocks, 256, 0, e->stream>>>(x, (float *)xs[0], (float *)xs[1], B, C, HW);
+    B200_CHECK_LAUNCH(e, "nhwc_split4_kernel");
+    return B200_OK;
+  }
   const long long tiles = B * ((HW + 31) / 32) * ((C + 31) / 32);
   const int blocks = (int)std::max<long long>(1, std::min<long long>(tiles, e->sm_count * 16LL));
   nhwc_split_kernel<<<blocks, 256, 0, e->stream>>>(x, (float *)xs[0], (float *)xs[1], B, C, HW);
