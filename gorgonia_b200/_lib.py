@@ -151,6 +151,8 @@ _SIGS = {
     "b200_argmax": (_i, [_vp, _i, _vp, _vp, _i64, _i64, _i64]),
     "b200_conv2d_fwd": (_i, [_vp, _i, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _i, _i, _i, _i, _i,
                              _P(Epilogue)]),
+    "b200_conv2d_maxpool_fwd": (_i, [_vp, _i, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _i, _i, _i, _i,
+                                     _i, _P(Epilogue), _i, _i, _i, _i]),
     "b200_conv2d_path": (_i, [_vp, _i, _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _i, _i, _i, _i, _i]),
     "b200_im2col": (_i, [_vp, _i, _vp, _vp, _i64, _i64, _i64, _i64, _i, _i, _i, _i, _i, _i, _i, _i]),
     "b200_maxpool2d_fwd": (_i, [_vp, _i, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i, _i, _i, _i, _i, _i, _i, _i, _i]),

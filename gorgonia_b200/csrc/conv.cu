@@ -23,7 +23,7 @@ int conv2d_tma(b200_engine *e, const float *x, const float *w, float *y, long lo
                int kh, int kw, int padH, int padW, int sH, int sW, int dH, int dW, int Ho, int Wo,
                const Epilogue &ep);
 int conv2d_win(b200_engine *e, const float *x, const float *w, float *y, long long B, int C, int H, int W, int K,
-               int kh, int kw, int padH, int padW, int dH, int dW, int Ho, int Wo, const Epilogue &ep);
+               int kh, int kw, int padH, int padW, int dH, int dW, int Ho, int Wo, const Epilogue &ep, bool pool2);
 bool conv_win_eligible(const b200_engine *e, long long B, int C, int H, int W, int K, int kh, int kw, int padH,
                        int padW, int sH, int sW, int dH, int dW, int Ho, int Wo);
 bool conv_tma_eligible(long long B, int C, int H, int W, int kh, int kw, int padH, int padW, int sH, int sW, int dH,
@@ -223,11 +223,128 @@ static int launch_conv3x3_first(b200_engine *e, const float *x, const float *w, 
   return B200_OK;
 }
 
+// The first-layer kernel with the 2x2 / stride-2 max-pool that follows it folded in (H even): a
+// thread computes a 2 x 4 block of outputs for 8 filters at a time from a 4 x 6 patch of inputs
+// per channel and stores the two pooled values of each filter as one float2. The convolution output
+// itself (four times the pooled bytes, and the largest tensor of the network) is never written.
+template <int C, int ACT, bool BIAS>
+__global__ void __launch_bounds__(256, 2) conv3x3_first_pool_kernel(const float *__restrict__ x,
+                                                                    const float *__restrict__ w,
+                                                                    float *__restrict__ y,
+                                                                    const float *__restrict__ bias, float alpha,
+                                                                    long long groups, int H, int W, int K) {
+  constexpr int Q = C * 9;
+  __shared__ __align__(16) float ws[Q * 32];  // [q][k], zero for k >= K
+  __shared__ float bs[32];
+  for (int i = threadIdx.x; i < Q * 32; i += blockDim.x) {
+    const int q = i >> 5, k = i & 31;
+    ws[i] = k < K ? w[k * Q + q] : 0.f;
+  }
+  if (threadIdx.x < 32) bs[threadIdx.x] = (BIAS && threadIdx.x < K) ? bias[threadIdx.x] : 0.f;
+  __syncthreads();
+  const int Wg = W >> 2, Hq = H >> 1, Wq = W >> 1;
+  const long long per_image = (long long)Hq * Wg;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x; g < groups; g += stride) {
+    const long long b = g / per_image;
+    const int rem = (int)(g - b * per_image);
+    const int ph = rem / Wg, og = rem - ph * Wg, ow = og << 2, oh = ph << 1;
+    const float *xb = x + b * (long long)C * H * W + ow;
+    float *yb = y + (b * K) * (long long)Hq * Wq + (long long)ph * Wq + (ow >> 1);
+    for (int k0 = 0; k0 < K; k0 += 8) {
+      float acc[2][4][8];
+#pragma unroll
+      for (int rr = 0; rr < 2; ++rr)
+#pragma unroll
+        for (int pz = 0; pz < 4; ++pz)
+#pragma unroll
+          for (int k = 0; k < 8; ++k) acc[rr][pz][k] = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < C; ++c) {
+        float in[4][6];
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+          const int ih = oh - 1 + r;
+#pragma unroll
+          for (int i = 0; i < 6; ++i) in[r][i] = 0.f;
+          if ((unsigned)ih < (unsigned)H) {
+            const float *row = xb + ((long long)c * H + ih) * W;
+            const float4 mid = __ldg(reinterpret_cast<const float4 *>(row));
+            in[r][1] = mid.x; in[r][2] = mid.y; in[r][3] = mid.z; in[r][4] = mid.w;
+            if (og > 0) in[r][0] = __ldg(row - 1);
+            if (og < Wg - 1) in[r][5] = __ldg(row + 4);
+          }
+        }
+#pragma unroll
+        for (int r = 0; r < 3; ++r) {
+#pragma unroll
+          for (int sx = 0; sx < 3; ++sx) {
+            const float *wq = &ws[(c * 9 + r * 3 + sx) * 32 + k0];
+            const float4 w0 = *reinterpret_cast<const float4 *>(wq);
+            const float4 w1 = *reinterpret_cast<const float4 *>(wq + 4);
+            const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+            for (int rr = 0; rr < 2; ++rr)
+#pragma unroll
+              for (int pz = 0; pz < 4; ++pz)
+#pragma unroll
+                for (int k = 0; k < 8; ++k) acc[rr][pz][k] = fmaf(in[rr + r][pz + sx], wv[k], acc[rr][pz][k]);
+          }
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        if (k0 + k < K) {
+          float o[2];
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            float best = -3.402823466e+38f;
+#pragma unroll
+            for (int rr = 0; rr < 2; ++rr)
+#pragma unroll
+              for (int j = 0; j < 2; ++j) {
+                float t = acc[rr][2 * half + j][k];
+                if (BIAS) t = __fadd_rn(t, bs[k0 + k]);
+                best = fmaxf(best, pool_candidate(apply_act<float>(t, ACT, alpha)));
+              }
+            o[half] = best;
+          }
+          *reinterpret_cast<float2 *>(yb + (long long)(k0 + k) * Hq * Wq) = make_float2(o[0], o[1]);
+        }
+      }
+    }
+  }
+}
+
+template <int C>
+static int launch_conv3x3_first_pool(b200_engine *e, const float *x, const float *w, float *y, long long B, int H,
+                                     int W, int K, const Epilogue &ep) {
+  const long long groups = B * (H / 2) * (W / 4);
+  const int blocks = (int)std::max<long long>(1, std::min<long long>((groups + 255) / 256, (long long)e->sm_count * 16));
+  const float *bias = (const float *)ep.bias;
+  const float alpha = (float)ep.alpha;
+#define B200_FIRSTP(ACT, BIAS) \
+  conv3x3_first_pool_kernel<C, ACT, BIAS><<<blocks, 256, 0, e->stream>>>(x, w, y, bias, alpha, groups, H, W, K)
+  const bool hb = ep.bias_kind != B200_BIAS_NONE;
+  if (ep.act == B200_ACT_NONE) { if (hb) B200_FIRSTP(B200_ACT_NONE, true); else B200_FIRSTP(B200_ACT_NONE, false); }
+  else if (ep.act == B200_ACT_RECTIFY) { if (hb) B200_FIRSTP(B200_ACT_RECTIFY, true); else B200_FIRSTP(B200_ACT_RECTIFY, false); }
+  else { if (hb) B200_FIRSTP(B200_ACT_LEAKY, true); else B200_FIRSTP(B200_ACT_LEAKY, false); }
+#undef B200_FIRSTP
+  B200_CHECK_LAUNCH(e, "conv3x3_first_pool_kernel");
+  return B200_OK;
+}
+
+// whether the specialised first-layer kernels take a convolution
+static bool conv3x3_first_ok(const void *x, const void *y, long long C, long long W, int kh, int kw, int padH, int padW,
+                             int sH, int sW, int dH, int dW) {
+  return kh == 3 && kw == 3 && padH == 1 && padW == 1 && sH == 1 && sW == 1 && dH == 1 && dW == 1 && C <= 3 &&
+         W % 4 == 0 && ((uintptr_t)x | (uintptr_t)y) % 16 == 0;
+}
+
 static int conv_direct_small(b200_engine *e, const float *x, const float *w, float *y, long long B, int C, int H,
                              int W, int K, int kh, int kw, int padH, int padW, int sH, int sW, int dH, int dW, int Ho,
                              int Wo, const Epilogue &ep) {
-  if (kh == 3 && kw == 3 && padH == 1 && padW == 1 && sH == 1 && sW == 1 && dH == 1 && dW == 1 && C <= 3 &&
-      W % 4 == 0 && ((uintptr_t)x | (uintptr_t)y) % 16 == 0) {
+  if (conv3x3_first_ok(x, y, C, W, kh, kw, padH, padW, sH, sW, dH, dW)) {
     if (C == 1) return launch_conv3x3_first<1>(e, x, w, y, B, H, W, K, ep);
     if (C == 2) return launch_conv3x3_first<2>(e, x, w, y, B, H, W, K, ep);
     return launch_conv3x3_first<3>(e, x, w, y, B, H, W, K, ep);
@@ -319,7 +436,7 @@ int b200_conv2d_fwd(b200_engine *e, int dtype, const void *x, const void *w, voi
                         pad_h, pad_w, stride_h, stride_w, dil_h, dil_w, (int)Ho, (int)Wo, ep);
     case B200_CONV_TC_WINDOW:
       return conv2d_win(e, (const float *)x, (const float *)w, (float *)y, B, (int)C, (int)H, (int)W, (int)K, kh, kw,
-                        pad_h, pad_w, dil_h, dil_w, (int)Ho, (int)Wo, ep);
+                        pad_h, pad_w, dil_h, dil_w, (int)Ho, (int)Wo, ep, false);
     case B200_CONV_TC_GATHER:
       return conv2d_tc(e, (const float *)x, (const float *)w, (float *)y, B, (int)C, (int)H, (int)W, (int)K, kh, kw,
                        pad_h, pad_w, stride_h, stride_w, dil_h, dil_w, (int)Ho, (int)Wo, ep);
@@ -340,6 +457,60 @@ int b200_conv2d_fwd(b200_engine *e, int dtype, const void *x, const void *w, voi
                    K * hw, ep);
   }
   b200_put(e, colbuf, 0);
+  return rc;
+}
+
+int b200_conv2d_maxpool_fwd(b200_engine *e, int dtype, const void *x, const void *w, void *y, int64_t B, int64_t C,
+                            int64_t H, int64_t W, int64_t K, int kh, int kw, int pad_h, int pad_w, int stride_h,
+                            int stride_w, int dil_h, int dil_w, const b200_epilogue *epi, int pool_h, int pool_w,
+                            int pool_stride_h, int pool_stride_w) {
+  if (!e) return B200_ERR_INVALID;
+  std::lock_guard<std::recursive_mutex> lk(e->mu);
+  B200_REQUIRE(e, dtype == B200_F32 || dtype == B200_F64, "b200_conv2d_maxpool_fwd: dtype %d not supported", dtype);
+  B200_REQUIRE(e, B >= 0 && C > 0 && H > 0 && W > 0 && K > 0 && kh > 0 && kw > 0 && stride_h > 0 && stride_w > 0 &&
+                      dil_h > 0 && dil_w > 0 && pad_h >= 0 && pad_w >= 0,
+               "b200_conv2d_maxpool_fwd: bad convolution shape");
+  B200_REQUIRE(e, pool_h > 0 && pool_w > 0 && pool_stride_h > 0 && pool_stride_w > 0,
+               "b200_conv2d_maxpool_fwd: bad pooling window");
+  const long long Ho = (H + 2 * pad_h - (dil_h * (kh - 1) + 1)) / stride_h + 1;
+  const long long Wo = (W + 2 * pad_w - (dil_w * (kw - 1) + 1)) / stride_w + 1;
+  B200_REQUIRE(e, Ho >= pool_h && Wo >= pool_w, "b200_conv2d_maxpool_fwd: pooling window larger than the convolution output");
+  if (B == 0) return B200_OK;
+  B200_REQUIRE(e, x && w && y, "b200_conv2d_maxpool_fwd: null pointer");
+  const bool pool2 = pool_h == 2 && pool_w == 2 && pool_stride_h == 2 && pool_stride_w == 2 && Ho % 2 == 0 &&
+                     Wo % 2 == 0 && dtype == B200_F32;
+  if (pool2) {
+    const int path = conv_path(e, dtype, B, C, H, W, K, kh, kw, pad_h, pad_w, stride_h, stride_w, dil_h, dil_w, Ho, Wo);
+    const bool first = path == B200_CONV_DIRECT &&
+                       conv3x3_first_ok(x, y, C, W, kh, kw, pad_h, pad_w, stride_h, stride_w, dil_h, dil_w);
+    if (first || path == B200_CONV_TC_WINDOW) {
+      if (epi) {
+        B200_REQUIRE(e, epi->bias_kind == B200_BIAS_NONE || epi->bias_kind == B200_BIAS_ROW,
+                     "b200_conv2d_maxpool_fwd: the bias is one value per output channel (B200_BIAS_ROW)");
+        B200_REQUIRE(e, epi->act >= 0 && epi->act <= 2, "b200_conv2d_maxpool_fwd: bad activation");
+        B200_REQUIRE(e, epi->bias_kind == 0 || epi->bias != nullptr, "b200_conv2d_maxpool_fwd: bias is null");
+      }
+      DeviceGuard g(e);
+      int rc = flush_pending(e);
+      if (rc != B200_OK) return rc;
+      const Epilogue ep = make_epilogue(epi);
+      if (path == B200_CONV_TC_WINDOW)
+        return conv2d_win(e, (const float *)x, (const float *)w, (float *)y, B, (int)C, (int)H, (int)W, (int)K, kh, kw,
+                          pad_h, pad_w, dil_h, dil_w, (int)Ho, (int)Wo, ep, true);
+      if (C == 1) return launch_conv3x3_first_pool<1>(e, (const float *)x, (const float *)w, (float *)y, B, (int)H, (int)W, (int)K, ep);
+      if (C == 2) return launch_conv3x3_first_pool<2>(e, (const float *)x, (const float *)w, (float *)y, B, (int)H, (int)W, (int)K, ep);
+      return launch_conv3x3_first_pool<3>(e, (const float *)x, (const float *)w, (float *)y, B, (int)H, (int)W, (int)K, ep);
+    }
+  }
+  // any other shape: the two operations one after the other, the convolution output in arena scratch
+  void *tmp = nullptr;
+  int rc = b200_get(e, B * K * Ho * Wo * (long long)dtype_size(dtype), &tmp);
+  if (rc != B200_OK) return rc;
+  rc = b200_conv2d_fwd(e, dtype, x, w, tmp, B, C, H, W, K, kh, kw, pad_h, pad_w, stride_h, stride_w, dil_h, dil_w, epi);
+  if (rc == B200_OK)
+    rc = b200_maxpool2d_fwd(e, dtype, tmp, y, nullptr, B, K, Ho, Wo, pool_h, pool_w, 0, 0, 0, 0, 0, pool_stride_h,
+                            pool_stride_w);
+  b200_put(e, tmp, 0);
   return rc;
 }
 

@@ -52,6 +52,7 @@ struct ConvWinParams {
   long long total_tiles;  // B * tiles_h * tiles_w * tiles_n
   int b_stages;
   Epilogue ep;       // bias_kind ROW = per output channel
+  int pool2;         // fold a 2x2 / stride-2 max-pool into the store: y is (B, K, Ho/2, Wo/2)
   int *err_flag;
 };
 
@@ -328,7 +329,15 @@ __global__ void __launch_bounds__(CW_THREADS, 1)
         for (int j = lane; j < BN; j += 32) bias_s[warp - 2][j] = n0 + j < p.K ? bias_g[n0 + j] : 0.f;
         __syncwarp();
       }
-      if (oh < p.Ho && ow < p.Wo) {
+      if (p.pool2) {
+        // Ho and Wo are even, so a pooling window lies wholly inside the image or wholly outside
+        const int Hq = p.Ho >> 1, Wq = p.Wo >> 1;
+        const long long plane = (long long)Hq * Wq;
+        const bool writer = oh < p.Ho && ow < p.Wo && (lane & 9) == 0;
+        float *yb = p.y + ((long long)b * p.K + n0) * plane + (long long)(oh >> 1) * Wq + (ow >> 1);
+        store_channels_pooled<BN>(acc, yb, plane, p.K - n0, has_bias ? bias_s[warp - 2] : nullptr, p.ep.act,
+                                  (float)p.ep.alpha, writer);
+      } else if (oh < p.Ho && ow < p.Wo) {
         const long long plane = (long long)p.Ho * p.Wo;
         float *yb = p.y + ((long long)b * p.K + n0) * plane + (long long)oh * p.Wo + ow;
         store_channels<BN>(acc, yb, plane, p.K - n0, has_bias ? bias_s[warp - 2] : nullptr, p.ep.act,
@@ -418,8 +427,9 @@ static int launch_conv_win(b200_engine *e, const CUtensorMap *tm, ConvWinParams 
 }
 
 // x (B,C,H,W) * w (K,C,kh,kw) -> y (B,K,Ho,Wo), float32, stride 1. ep.bias_kind ROW = per channel.
+// pool2 (Ho, Wo even): y is (B,K,Ho/2,Wo/2), the 2x2 / stride-2 max-pool of the activated output.
 int conv2d_win(b200_engine *e, const float *x, const float *w, float *y, long long B, int C, int H, int W, int K,
-               int kh, int kw, int padH, int padW, int dH, int dW, int Ho, int Wo, const Epilogue &ep) {
+               int kh, int kw, int padH, int padW, int dH, int dW, int Ho, int Wo, const Epilogue &ep, bool pool2) {
   static CwEncodeTiledFn enc = cw_encode_fn();
   if (!enc) return set_error(e, B200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
   const int taps = kh * kw, crs = C * taps;
@@ -448,6 +458,7 @@ int conv2d_win(b200_engine *e, const float *x, const float *w, float *y, long lo
   p.tiles_n = (K + bn - 1) / bn;
   p.total_tiles = B * p.tiles_h * p.tiles_w * p.tiles_n;
   p.ep = ep;
+  p.pool2 = pool2 ? 1 : 0;
   p.err_flag = e->d_flags + 2;
 
   CUtensorMap tm[4];

@@ -101,4 +101,43 @@ __device__ __forceinline__ void store_channels(const float (&acc)[N], float *y, 
   }
 }
 
+// ---- the same store with a 2x2 / stride-2 max-pool folded in -----------------------------------
+// maxPoolOp.do (op_nn.go:828-907) starts every window at -MaxFloat32 and replaces the running value
+// only on a strict '>': a NaN or a -Inf never wins, and a window of nothing else yields -MaxFloat32.
+// pool_candidate() maps a value to what it contributes under that rule; the plain maximum of the
+// four candidates is then exactly the reference's result.
+__device__ __forceinline__ float pool_candidate(float v) { return v > -3.402823466e+38f ? v : -3.402823466e+38f; }
+
+// The four positions of a pooling window sit in lanes l, l^1 (next column) and l^8, l^9 (next
+// row) of the warp. Every lane takes part in the exchange; lanes with `writer` set (the window's
+// first position, inside the image) store to the pooled plane.
+template <int N, int ACT, bool BIAS>
+__device__ __forceinline__ void store_channels_pooled_variant(const float (&acc)[N], float *y, long long plane,
+                                                              int valid, const float *bias, float alpha,
+                                                              bool writer) {
+#pragma unroll
+  for (int j = 0; j < N; ++j) {
+    float t = acc[j];
+    if (BIAS) t = __fadd_rn(t, bias[j]);
+    float v = pool_candidate(apply_act<float>(t, ACT, alpha));
+    v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 1));
+    v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 8));
+    if (writer && j < valid) *y = v;
+    y += plane;
+  }
+}
+template <int N>
+__device__ __forceinline__ void store_channels_pooled(const float (&acc)[N], float *y, long long plane, int valid,
+                                                      const float *bias, int act, float alpha, bool writer) {
+  if (bias) {
+    if (act == B200_ACT_NONE) store_channels_pooled_variant<N, B200_ACT_NONE, true>(acc, y, plane, valid, bias, alpha, writer);
+    else if (act == B200_ACT_RECTIFY) store_channels_pooled_variant<N, B200_ACT_RECTIFY, true>(acc, y, plane, valid, bias, alpha, writer);
+    else store_channels_pooled_variant<N, B200_ACT_LEAKY, true>(acc, y, plane, valid, bias, alpha, writer);
+  } else {
+    if (act == B200_ACT_NONE) store_channels_pooled_variant<N, B200_ACT_NONE, false>(acc, y, plane, valid, bias, alpha, writer);
+    else if (act == B200_ACT_RECTIFY) store_channels_pooled_variant<N, B200_ACT_RECTIFY, false>(acc, y, plane, valid, bias, alpha, writer);
+    else store_channels_pooled_variant<N, B200_ACT_LEAKY, false>(acc, y, plane, valid, bias, alpha, writer);
+  }
+}
+
 }  // namespace b200

@@ -385,6 +385,18 @@ class Engine:
                                   C.byref(ep) if ep else None), self.h)
         return prealloc
 
+    def Conv2dMaxPool(self, x, w, prealloc, pad=(0, 0), stride=(1, 1), dil=(1, 1), bias=None, act=None, alpha=0.0,
+                      pool=(2, 2), pool_stride=(2, 2)):
+        """Conv2d -> bias -> activation -> MaxPool2D (no pool padding) as one call; prealloc is the pooled output."""
+        B, Cc, H, W = x.shape
+        K, _, kh, kw = w.shape
+        ep = _epilogue(bias, "row", act, alpha)
+        check(lib.b200_conv2d_maxpool_fwd(self.h, dtype_code(x.dtype), x.ptr, w.ptr, prealloc.ptr, B, Cc, H, W, K, kh,
+                                          kw, pad[0], pad[1], stride[0], stride[1], dil[0], dil[1],
+                                          C.byref(ep) if ep else None, pool[0], pool[1], pool_stride[0],
+                                          pool_stride[1]), self.h)
+        return prealloc
+
     def conv2d_path(self, x, w, pad=(0, 0), stride=(1, 1), dil=(1, 1)):
         """Which kernel Conv2d would run for these operands (one of the _lib.CONV_* values)."""
         B, Cc, H, W = x.shape

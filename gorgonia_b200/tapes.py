@@ -15,8 +15,10 @@ benchmark drive the library the way a gorgonia build would:
 Every class owns its device buffers (weights stay resident across runs, unlike the reference,
 which re-uploads them after each Reset: vm_tape.go:123-134, analysis.go:151-176), exposes
 forward() = one pass of engine calls, and record()/replay() = the same pass as one recorded tape.
-`fused=True` uses the fused bias/activation stores of b200_gemm / b200_conv2d_fwd; `fused=False`
-issues one engine call per reference instruction and leaves fusing to the engine's deferred queue.
+`fused=True` uses the fused bias/activation stores of b200_gemm / b200_conv2d_fwd and, where a
+2x2/2 pool follows a convolution, b200_conv2d_maxpool_fwd (the convolution output is then never
+materialised); `fused=False` issues one engine call per reference instruction and leaves fusing to
+the engine's deferred queue.
 Weights are seeded draws (Glorot-uniform / He-normal formulas of weights.go:397-479); nothing is
 computed on the host.
 """
@@ -112,7 +114,7 @@ class LeNet(_Tape):
         self.wd = [e.constant(e.tensor(w)) for w in self.wd_host]
         self.x = e.empty((batch, 1, 28, 28))
         hw = (28, 14, 7)
-        self.conv = [e.empty((batch, self.CH[i + 1], hw[i], hw[i])) for i in range(3)]
+        self.conv = [None if fused else e.empty((batch, self.CH[i + 1], hw[i], hw[i])) for i in range(3)]
         self.cmask = [None if fused else e.empty((batch, self.CH[i + 1], hw[i], hw[i])) for i in range(3)]
         self.pool = [e.empty((batch, self.CH[i + 1], hw[i] // 2, hw[i] // 2)) for i in range(3)]
         self.fc = e.empty((batch, 625))
@@ -124,12 +126,12 @@ class LeNet(_Tape):
         e, a = self.e, self.x
         for i in range(3):
             if self.fused:
-                e.Conv2d(a, self.wc[i], self.conv[i], pad=(1, 1), act="rectify")
+                e.Conv2dMaxPool(a, self.wc[i], self.pool[i], pad=(1, 1), act="rectify")
             else:
                 e.Conv2d(a, self.wc[i], self.conv[i], pad=(1, 1))
                 e.GteScalar(self.conv[i], 0.0, reuse=self.cmask[i])
                 e.Mul(self.conv[i], self.cmask[i], unsafe=True)
-            e.MaxPool2D(self.conv[i], self.pool[i], (2, 2), (0, 0), (2, 2))
+                e.MaxPool2D(self.conv[i], self.pool[i], (2, 2), (0, 0), (2, 2))
             a = self.pool[i]
         flat = a.reshape(self.batch, 1152)
         if self.fused:
@@ -151,11 +153,11 @@ class LeNet(_Tape):
 class TinyYolo(_Tape):
     CH = (3, 16, 32, 64, 128, 256, 512, 1024, 1024, 125)
 
-    def __init__(self, engine, batch, seed=9, size=416, channels=None):
+    def __init__(self, engine, batch, seed=9, size=416, channels=None, fused=True):
         super().__init__(engine)
         e, g = engine, _rng(seed)
         ch = tuple(channels) if channels else self.CH
-        self.ch, self.batch, self.size = ch, batch, size
+        self.ch, self.batch, self.size, self.fused = ch, batch, size, fused
         self.k = [3] * 8 + [1]
         self.w_host = [he_normal(g, (ch[i + 1], ch[i], self.k[i], self.k[i]), ch[i] * self.k[i] ** 2)
                        for i in range(9)]
@@ -166,7 +168,7 @@ class TinyYolo(_Tape):
         s = size
         self.conv, self.pool = [], []
         for i in range(9):
-            self.conv.append(e.empty((batch, ch[i + 1], s, s)))
+            self.conv.append(None if fused and i < 5 else e.empty((batch, ch[i + 1], s, s)))
             if i < 5:
                 s //= 2
                 self.pool.append(e.empty((batch, ch[i + 1], s, s)))
@@ -178,6 +180,10 @@ class TinyYolo(_Tape):
         e, a = self.e, self.x
         for i in range(9):
             alpha = 1.0 if i == 8 else 0.1      # the last layer is LeakyRelu(1.0) in the reference graph
+            if self.fused and i < 5:
+                e.Conv2dMaxPool(a, self.w[i], self.pool[i], pad=(1, 1), bias=self.b[i], act="leaky", alpha=alpha)
+                a = self.pool[i]
+                continue
             e.Conv2d(a, self.w[i], self.conv[i], pad=(self.k[i] // 2, self.k[i] // 2), bias=self.b[i], act="leaky",
                      alpha=alpha)
             a = self.conv[i]

@@ -345,6 +345,19 @@ int b200_reduce_all_static(b200_engine *e, int dtype, int kind, const void *x, i
 int b200_conv2d_fwd(b200_engine *e, int dtype, const void *x, const void *w, void *y, int64_t B,
                     int64_t C, int64_t H, int64_t W, int64_t K, int kh, int kw, int pad_h, int pad_w,
                     int stride_h, int stride_w, int dil_h, int dil_w, const b200_epilogue *ep);
+/* Conv2d -> (bias, activation) -> MaxPool2D without padding as ONE call, for a tape in which the
+ * convolution output has no other consumer (nn.go:211-305 followed by op_nn.go:828-907; the LeNet and
+ * tiny-YOLO graphs of examples/convnet and examples/tiny-yolo-v2-coco are built from exactly this
+ * triple). y is (B, K, (Ho - pool_h) / pool_stride_h + 1, (Wo - pool_w) / pool_stride_w + 1). With a
+ * 2x2 / stride-2 window and even Ho, Wo the first-layer kernel and the window kernel pool inside
+ * their store and never write the convolution output; any other shape runs the two operations one
+ * after the other through arena scratch. Results equal b200_conv2d_fwd + b200_maxpool2d_fwd bit
+ * for bit. */
+int b200_conv2d_maxpool_fwd(b200_engine *e, int dtype, const void *x, const void *w, void *y,
+                            int64_t B, int64_t C, int64_t H, int64_t W, int64_t K, int kh, int kw,
+                            int pad_h, int pad_w, int stride_h, int stride_w, int dil_h, int dil_w,
+                            const b200_epilogue *ep, int pool_h, int pool_w, int pool_stride_h,
+                            int pool_stride_w);
 /* Which kernel b200_conv2d_fwd would pick for a problem (no device work; -1 for a bad shape):
  * CUDA cores over an im2col scratch; the direct kernel for a first layer (C*kh*kw <= 32, K <= 32);
  * tensor cores with the col operand gathered by warps; tensor cores with the col operand built

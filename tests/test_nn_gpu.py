@@ -181,6 +181,56 @@ def test_conv2d_tensor_core_col_paths(case, gather):
         e.Close()
 
 
+CONV_POOL_CASES = [
+    # B, C, H, W, K, kh, kw, pad, pool, pool_stride
+    (3, 1, 28, 28, 32, 3, 3, (1, 1), (2, 2), (2, 2)),      # first-layer kernel, pooled
+    (2, 3, 36, 40, 16, 3, 3, (1, 1), (2, 2), (2, 2)),      # first-layer kernel, 3 channels, 16 filters
+    (2, 2, 20, 24, 21, 3, 3, (1, 1), (2, 2), (2, 2)),      # ragged filter count
+    (4, 32, 30, 44, 64, 3, 3, (1, 1), (2, 2), (2, 2)),     # window kernel, pooled, ragged tiles
+    (4, 16, 48, 48, 40, 3, 3, (1, 1), (2, 2), (2, 2)),     # window kernel, 16-channel rows, two column tiles
+    (5, 64, 14, 14, 20, 3, 3, (1, 1), (2, 2), (2, 2)),     # window kernel, one tile per image
+    (2, 32, 15, 15, 8, 3, 3, (1, 1), (2, 2), (2, 2)),      # odd planes: the two operations in sequence
+    (2, 8, 12, 12, 6, 3, 3, (1, 1), (3, 3), (2, 2)),       # another window: the two operations in sequence
+    (3, 64, 7, 7, 16, 3, 3, (1, 1), (2, 2), (2, 2)),       # LeNet conv2: odd planes
+]
+
+
+@pytest.mark.parametrize("act", [None, "rectify", "leaky"])
+@pytest.mark.parametrize("case", CONV_POOL_CASES)
+def test_conv2d_maxpool_equals_the_two_calls(fresh, case, act):
+    e = fresh
+    B, Cc, H, W, K, kh, kw, pad, pool, ps = case
+    x = util.uniform(97, (B, Cc, H, W)) - np.float32(0.5)
+    w = util.normal(98, (K, Cc, kh, kw), scale=float(np.sqrt(2.0 / (Cc * kh * kw))))
+    bias = util.normal(99, K, scale=0.1)
+    tx, tw, tb = e.tensor(x), e.tensor(w), e.tensor(bias)
+    Ho, Wo = H + 2 * pad[0] - (kh - 1), W + 2 * pad[1] - (kw - 1)
+    conv = e.empty((B, K, Ho, Wo))
+    Hq, Wq = (Ho - pool[0]) // ps[0] + 1, (Wo - pool[1]) // ps[1] + 1
+    two, one = e.empty((B, K, Hq, Wq)), e.empty((B, K, Hq, Wq))
+    e.Conv2d(tx, tw, conv, pad, bias=tb, act=act, alpha=0.1)
+    e.MaxPool2D(conv, two, pool, (0, 0), ps)
+    e.Conv2dMaxPool(tx, tw, one, pad, bias=tb, act=act, alpha=0.1, pool=pool, pool_stride=ps)
+    assert_bits_equal(one.numpy(), two.numpy())
+    assert_bits_equal(one.numpy(), oracle.maxpool2d(conv.numpy(), pool, (0, 0), ps)[0])
+
+
+def test_conv2d_maxpool_special_values(fresh):
+    # an all-NaN / -Inf window yields -MaxFloat32, as maxPoolOp.do does
+    e = fresh
+    x = np.zeros((1, 1, 4, 4), np.float32)
+    x[0, 0, :2, :2] = np.nan
+    x[0, 0, :2, 2:] = -np.inf
+    w = np.zeros((1, 1, 3, 3), np.float32)
+    w[0, 0, 1, 1] = 1.0                                    # identity filter
+    conv, two, one = e.empty((1, 1, 4, 4)), e.empty((1, 1, 2, 2)), e.empty((1, 1, 2, 2))
+    tx, tw = e.tensor(x), e.tensor(w)
+    e.Conv2d(tx, tw, conv, (1, 1))
+    e.MaxPool2D(conv, two, (2, 2), (0, 0), (2, 2))
+    e.Conv2dMaxPool(tx, tw, one, (1, 1))
+    assert_bits_equal(one.numpy(), two.numpy())
+
+
 def test_conv2d_matches_reference_pipeline(fresh):
     # Conv2d as gorgonia spells it (nn.go:264-298): Im2Col -> MatMul(transB) -> Transpose(0,3,1,2)
     e = fresh

@@ -74,6 +74,9 @@ def test_tiny_yolo_forward(fresh):
     want = graphs.tiny_yolo(m, x)
     assert got.shape == (2, 125, 4, 4)
     assert_gemm_close(got, want, 1e-5)
+    u = tapes.TinyYolo(e, 2, size=128, fused=False)     # one call per convolution and per pool
+    u.x.set(x)
+    assert_bits_equal(u.forward().numpy(), got)
 
 
 def test_recording_refuses_calls_that_wait(fresh):
