@@ -394,7 +394,11 @@ def wl_model(ctx, args, name, main):
                       "parallelism": f"batch-sharded x{ctx.world}, weights replicated, no collective",
                       "l2": "activations larger than L2" if name != "mlp" else "flush not needed: launch-bound"},
            "gpu_launches": launches, "clocks": clocks, "steps": steps, "warmup": warmup, "scaling": "strong",
-           "roofline": {"bound": "tensor", "kernel": "gemm_tc_kernel (conv / dense layers)", "achieved": 3 * tf,
+           "roofline": {"bound": "tensor",
+                        "kernel": {"mlp": "gemm_tc_kernel (whole step)",
+                                   "lenet": "conv_win_kernel + conv_tma_kernel + gemm_tc_kernel (whole step)",
+                                   "yolo": "conv_tma_kernel + conv_win_kernel (whole step)"}[name],
+                        "achieved": 3 * tf,
                         "peak": pk["bf16_tflops"] / 2, "unit": "TFLOP/s (TF32 issued = 3 x algorithmic)",
                         "frac": 3 * tf / (pk["bf16_tflops"] / 2), "peak_source": pk["source"] + " bf16 burst / 2",
                         "traffic": None}}
