@@ -64,7 +64,8 @@ class PwProg(C.Structure):
 
 
 class Epilogue(C.Structure):
-    _fields_ = [("bias_kind", C.c_int32), ("act", C.c_int32), ("bias", C.c_void_p), ("alpha", C.c_double)]
+    _fields_ = [("bias_kind", C.c_int32), ("act", C.c_int32), ("bias", C.c_void_p), ("alpha", C.c_double),
+                ("accumulate", C.c_int32), ("reserved", C.c_int32)]
 
 
 BIAS_NONE, BIAS_COL, BIAS_ROW = 0, 1, 2
@@ -155,6 +156,9 @@ _SIGS = {
                                      _i, _P(Epilogue), _i, _i, _i, _i]),
     "b200_conv2d_path": (_i, [_vp, _i, _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _i, _i, _i, _i, _i]),
     "b200_im2col": (_i, [_vp, _i, _vp, _vp, _i64, _i64, _i64, _i64, _i, _i, _i, _i, _i, _i, _i, _i]),
+    "b200_maxpool2d_bwd": (_i, [_vp, _i, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i, _i, _i, _i, _i, _i, _i, _i, _i]),
+    "b200_col2im": (_i, [_vp, _i, _vp, _vp, _i64, _i64, _i64, _i64, _i, _i, _i, _i, _i, _i, _i, _i]),
+    "b200_softmax_bwd": (_i, [_vp, _i, _vp, _vp, _vp, _i64, _i64, _i64, _i]),
     "b200_maxpool2d_fwd": (_i, [_vp, _i, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i, _i, _i, _i, _i, _i, _i, _i, _i]),
     "b200_transpose": (_i, [_vp, _i, _vp, _vp, _i, _P(_i64), _P(_i)]),
     "b200_gather_axis": (_i, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64]),

@@ -205,7 +205,10 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(int transA, int transB, 
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const long long n = n0 + tx * 4 + j;
-      if (n < N) C[m * ldc + n] = apply_epilogue<T>(acc[i][j], ep, m, n);
+      if (n < N) {
+        const T o = apply_epilogue<T>(acc[i][j], ep, m, n);
+        C[m * ldc + n] = ep.accumulate ? epi_add<T>(C[m * ldc + n], o) : o;  // Incr mode: C += result
+      }
     }
   }
 }

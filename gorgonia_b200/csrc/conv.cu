@@ -414,6 +414,7 @@ int b200_conv2d_fwd(b200_engine *e, int dtype, const void *x, const void *w, voi
                  "b200_conv2d_fwd: the bias is one value per output channel (B200_BIAS_ROW)");
     B200_REQUIRE(e, epi->act >= 0 && epi->act <= 2, "b200_conv2d_fwd: bad activation");
     B200_REQUIRE(e, epi->bias_kind == 0 || epi->bias != nullptr, "b200_conv2d_fwd: bias is null");
+    B200_REQUIRE(e, epi->accumulate == 0, "b200_conv2d_fwd: accumulate is a matrix-product option");
   }
   if (B == 0) return B200_OK;
   B200_REQUIRE(e, x && w && y, "b200_conv2d_fwd: null pointer");
@@ -489,6 +490,7 @@ int b200_conv2d_maxpool_fwd(b200_engine *e, int dtype, const void *x, const void
                      "b200_conv2d_maxpool_fwd: the bias is one value per output channel (B200_BIAS_ROW)");
         B200_REQUIRE(e, epi->act >= 0 && epi->act <= 2, "b200_conv2d_maxpool_fwd: bad activation");
         B200_REQUIRE(e, epi->bias_kind == 0 || epi->bias != nullptr, "b200_conv2d_maxpool_fwd: bias is null");
+        B200_REQUIRE(e, epi->accumulate == 0, "b200_conv2d_maxpool_fwd: accumulate is a matrix-product option");
       }
       DeviceGuard g(e);
       int rc = flush_pending(e);

@@ -13,6 +13,7 @@ struct Epilogue {
   const void *bias = nullptr;
   int act = 0;        // B200_ACT_NONE / _RECTIFY / _LEAKY
   double alpha = 0.0;
+  int accumulate = 0; // matrix product only: add the result to what the output holds
 };
 
 inline Epilogue make_epilogue(const b200_epilogue *ep) {
@@ -22,6 +23,7 @@ inline Epilogue make_epilogue(const b200_epilogue *ep) {
     r.bias = ep->bias;
     r.act = ep->act;
     r.alpha = ep->alpha;
+    r.accumulate = ep->accumulate;
   }
   return r;
 }

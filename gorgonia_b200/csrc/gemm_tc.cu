@@ -281,12 +281,20 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
             o.y = apply_epilogue<float>(v[j + 1], p.ep, m, nbase + j + 1);
             o.z = apply_epilogue<float>(v[j + 2], p.ep, m, nbase + j + 2);
             o.w = apply_epilogue<float>(v[j + 3], p.ep, m, nbase + j + 3);
+            if (p.ep.accumulate) {  // Incr mode: the rounded result is added to what C holds
+              const float4 old = *reinterpret_cast<const float4 *>(crow + nbase + j);
+              o.x = __fadd_rn(old.x, o.x); o.y = __fadd_rn(old.y, o.y);
+              o.z = __fadd_rn(old.z, o.z); o.w = __fadd_rn(old.w, o.w);
+            }
             *reinterpret_cast<float4 *>(crow + nbase + j) = o;
           }
         } else {
 #pragma unroll
           for (int j = 0; j < 32; ++j)
-            if (nbase + j < p.N) crow[nbase + j] = apply_epilogue<float>(v[j], p.ep, m, nbase + j);
+            if (nbase + j < p.N) {
+              const float o = apply_epilogue<float>(v[j], p.ep, m, nbase + j);
+              crow[nbase + j] = p.ep.accumulate ? __fadd_rn(crow[nbase + j], o) : o;
+            }
         }
       };
 

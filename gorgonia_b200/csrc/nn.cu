@@ -222,6 +222,75 @@ __global__ void __launch_bounds__(256) gather_rows_kernel(const W *__restrict__ 
   }
 }
 
+// Gradient of the max-pool with respect to its input (maxPoolDiffOp.f32s, op_nn.go:1067-1093): the
+// reference zeroes the gradient and adds every pooled position's gradient to the input position its
+// mask entry names, walking the pooled plane in (ph, pw) order. Here one thread owns one INPUT
+// element, visits the windows that can contain it in the same (ph, pw) order and adds those whose
+// mask entry names it: the same additions in the same order, so the result is bit-identical also
+// where windows overlap, and no atomics are needed.
+template <typename T>
+__global__ void __launch_bounds__(256) maxpool_bwd_kernel(const T *__restrict__ dy, const long long *__restrict__ mask,
+                                                          T *__restrict__ dx, long long planes, int H, int W, int Ho,
+                                                          int Wo, int kh, int kw, int sH, int sW, int oh0, int ow0) {
+  const long long total = planes * H * W;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += stride) {
+    const int w = (int)(t % W);
+    const int h = (int)((t / W) % H);
+    const long long plane = t / ((long long)W * H);
+    const long long me = (long long)h * W + w;
+    // windows (ph, pw) with ph*sH - oh0 <= h < ph*sH - oh0 + kh
+    int ph_lo = h + oh0 - kh + 1;
+    ph_lo = ph_lo <= 0 ? 0 : (ph_lo + sH - 1) / sH;
+    const int ph_hi = min((h + oh0) / sH, Ho - 1);
+    int pw_lo = w + ow0 - kw + 1;
+    pw_lo = pw_lo <= 0 ? 0 : (pw_lo + sW - 1) / sW;
+    const int pw_hi = min((w + ow0) / sW, Wo - 1);
+    const long long *mk = mask + plane * Ho * Wo;
+    const T *g = dy + plane * Ho * Wo;
+    T acc = T(0);
+    for (int ph = ph_lo; ph <= ph_hi; ++ph)
+      for (int pw = pw_lo; pw <= pw_hi; ++pw)
+        if (mk[ph * Wo + pw] == me) acc = acc + g[ph * Wo + pw];
+    dx[t] = acc;
+  }
+}
+
+// col (B, Ho, Wo, C*kh*kw) accumulated back into the image (col2imOp.f32s, op_nn.go:603-637). The
+// reference walks col in memory order, so the additions that land on one pixel happen in ascending
+// (output row, output column) order. One thread owns one pixel and makes the same additions in the
+// same order: ascending output row means descending kernel row, likewise for columns.
+template <typename T>
+__global__ void __launch_bounds__(256) col2im_kernel(const T *__restrict__ col, T *__restrict__ im, long long B, int C,
+                                                     int H, int W, int Ho, int Wo, int kh, int kw, int padH, int padW,
+                                                     int sH, int sW, int dH, int dW) {
+  const long long total = B * C * H * W;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  const int crs = C * kh * kw;
+  for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += stride) {
+    const int iw = (int)(t % W);
+    const int ih = (int)((t / W) % H);
+    const int c = (int)((t / ((long long)W * H)) % C);
+    const long long b = t / ((long long)W * H * C);
+    const T *colb = col + b * (long long)Ho * Wo * crs + (long long)c * kh * kw;
+    T acc = T(0);
+    for (int r = kh - 1; r >= 0; --r) {
+      const int num_h = ih + padH - r * dH;
+      if (num_h < 0 || num_h % sH != 0) continue;
+      const int oh = num_h / sH;
+      if (oh >= Ho) continue;
+      for (int sx = kw - 1; sx >= 0; --sx) {
+        const int num_w = iw + padW - sx * dW;
+        if (num_w < 0 || num_w % sW != 0) continue;
+        const int ow = num_w / sW;
+        if (ow >= Wo) continue;
+        acc = acc + colb[((long long)oh * Wo + ow) * crs + r * kw + sx];
+      }
+    }
+    im[t] = acc;
+  }
+}
+
 static int grid_for(b200_engine *e, long long work) {
   return (int)std::max<long long>(1, std::min<long long>((work + 255) / 256, (long long)e->sm_count * 16));
 }
@@ -278,6 +347,70 @@ int b200_maxpool2d_fwd(b200_engine *e, int dtype, const void *x, void *y, int64_
                                                                      (int)Ho, (int)Wo, kh, kw, stride_h, stride_w,
                                                                      oh0, ow0);
   B200_CHECK_LAUNCH(e, "maxpool_kernel");
+  return B200_OK;
+}
+
+int b200_maxpool2d_bwd(b200_engine *e, int dtype, const void *dy, const int64_t *mask, void *dx, int64_t B, int64_t C,
+                       int64_t H, int64_t W, int kh, int kw, int pad_north, int pad_south, int pad_west,
+                       int pad_east, int explicit_padding, int stride_h, int stride_w) {
+  if (!e) return B200_ERR_INVALID;
+  std::lock_guard<std::recursive_mutex> lk(e->mu);
+  B200_REQUIRE(e, dtype == B200_F32 || dtype == B200_F64, "b200_maxpool2d_bwd: dtype %d not supported", dtype);
+  B200_REQUIRE(e, B >= 0 && C >= 0 && H > 0 && W > 0, "b200_maxpool2d_bwd: bad input shape");
+  B200_REQUIRE(e, kh > 0 && kw > 0 && stride_h > 0 && stride_w > 0, "b200_maxpool2d_bwd: bad kernel or stride");
+  B200_REQUIRE(e, pad_north >= 0 && pad_south >= 0 && pad_west >= 0 && pad_east >= 0, "b200_maxpool2d_bwd: bad pad");
+  B200_REQUIRE(e, H < (1LL << 30) && W < (1LL << 30), "b200_maxpool2d_bwd: image too large");
+  const long long Ho = (H + pad_south + pad_north - (kh - 1) - 1) / stride_h + 1;
+  const long long Wo = (W + pad_east + pad_west - (kw - 1) - 1) / stride_w + 1;
+  B200_REQUIRE(e, Ho > 0 && Wo > 0, "b200_maxpool2d_bwd: window larger than the padded image");
+  if (B * C == 0) return B200_OK;
+  B200_REQUIRE(e, dy && mask && dx, "b200_maxpool2d_bwd: null pointer");
+  DeviceGuard g(e);
+  int rc = flush_pending(e);
+  if (rc != B200_OK) return rc;
+  const int oh0 = explicit_padding ? pad_south : pad_north;
+  const int ow0 = explicit_padding ? pad_east : pad_west;
+  const long long total = B * C * H * W;
+  if (dtype == B200_F32)
+    maxpool_bwd_kernel<float><<<grid_for(e, total), 256, 0, e->stream>>>(
+        (const float *)dy, (const long long *)mask, (float *)dx, B * C, (int)H, (int)W, (int)Ho, (int)Wo, kh, kw,
+        stride_h, stride_w, oh0, ow0);
+  else
+    maxpool_bwd_kernel<double><<<grid_for(e, total), 256, 0, e->stream>>>(
+        (const double *)dy, (const long long *)mask, (double *)dx, B * C, (int)H, (int)W, (int)Ho, (int)Wo, kh, kw,
+        stride_h, stride_w, oh0, ow0);
+  B200_CHECK_LAUNCH(e, "maxpool_bwd_kernel");
+  return B200_OK;
+}
+
+int b200_col2im(b200_engine *e, int dtype, const void *col, void *im, int64_t B, int64_t C, int64_t H, int64_t W,
+                int kh, int kw, int pad_h, int pad_w, int stride_h, int stride_w, int dil_h, int dil_w) {
+  if (!e) return B200_ERR_INVALID;
+  std::lock_guard<std::recursive_mutex> lk(e->mu);
+  B200_REQUIRE(e, dtype == B200_F32 || dtype == B200_F64, "b200_col2im: dtype %d not supported", dtype);
+  B200_REQUIRE(e, B >= 0 && C > 0 && H > 0 && W > 0, "b200_col2im: bad image shape");
+  B200_REQUIRE(e, kh > 0 && kw > 0 && stride_h > 0 && stride_w > 0 && dil_h > 0 && dil_w > 0 && pad_h >= 0 &&
+                      pad_w >= 0,
+               "b200_col2im: bad kernel, stride, dilation or pad");
+  B200_REQUIRE(e, C * (long long)kh * kw < (1LL << 30) && H < (1LL << 30) && W < (1LL << 30), "b200_col2im: too large");
+  const long long Ho = (H + 2 * pad_h - (dil_h * (kh - 1) + 1)) / stride_h + 1;
+  const long long Wo = (W + 2 * pad_w - (dil_w * (kw - 1) + 1)) / stride_w + 1;
+  B200_REQUIRE(e, Ho > 0 && Wo > 0, "b200_col2im: kernel larger than the padded image");
+  if (B == 0) return B200_OK;
+  B200_REQUIRE(e, col && im, "b200_col2im: null pointer");
+  DeviceGuard g(e);
+  int rc = flush_pending(e);
+  if (rc != B200_OK) return rc;
+  const long long total = B * C * H * W;
+  if (dtype == B200_F32)
+    col2im_kernel<float><<<grid_for(e, total), 256, 0, e->stream>>>((const float *)col, (float *)im, B, (int)C, (int)H,
+                                                                   (int)W, (int)Ho, (int)Wo, kh, kw, pad_h, pad_w,
+                                                                   stride_h, stride_w, dil_h, dil_w);
+  else
+    col2im_kernel<double><<<grid_for(e, total), 256, 0, e->stream>>>((const double *)col, (double *)im, B, (int)C,
+                                                                    (int)H, (int)W, (int)Ho, (int)Wo, kh, kw, pad_h,
+                                                                    pad_w, stride_h, stride_w, dil_h, dil_w);
+  B200_CHECK_LAUNCH(e, "col2im_kernel");
   return B200_OK;
 }
 

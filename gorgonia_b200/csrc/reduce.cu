@@ -359,6 +359,65 @@ static int launch_mode(b200_engine *e, const T *x, T *y, long long outer, long l
   return B200_OK;
 }
 
+// ---- softmax / log-softmax derivative --------------------------------------------------------
+// softmaxDiffOp (op_softmax.go:262-274) hands (y, grad) to tensor.SoftMaxB / LogSoftMaxB:
+//   softmax:      dx_i = y_i * (g_i - sum_j g_j y_j)
+//   log-softmax:  dx_i = g_i - exp(y_i) * sum_j g_j
+// on a tensor viewed as (outer, len, inner). The row sum is taken in double (rows are short and
+// the subtraction that follows cancels). inner == 1: one warp per row, shuffle reduction;
+// inner > 1: one thread per (outer, inner) pair walking len with coalesced strided accesses.
+template <typename T, bool LOG>
+__global__ void __launch_bounds__(256) softmax_bwd_rows_kernel(const T *__restrict__ y, const T *__restrict__ g,
+                                                               T *__restrict__ dx, long long rows, long long len) {
+  const int lane = threadIdx.x & 31;
+  const long long warp0 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+  for (long long r = warp0; r < rows; r += nwarps) {
+    const T *yp = y + r * len, *gp = g + r * len;
+    double s = 0.0;
+    for (long long k = lane; k < len; k += 32) s += LOG ? (double)gp[k] : (double)gp[k] * (double)yp[k];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    for (long long k = lane; k < len; k += 32) {
+      const double yy = yp[k], gg = gp[k];
+      dx[r * len + k] = (T)(LOG ? gg - exp(yy) * s : yy * (gg - s));
+    }
+  }
+}
+template <typename T, bool LOG>
+__global__ void __launch_bounds__(256) softmax_bwd_strided_kernel(const T *__restrict__ y, const T *__restrict__ g,
+                                                                  T *__restrict__ dx, long long outer, long long len,
+                                                                  long long inner) {
+  const long long total = outer * inner;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += stride) {
+    const long long o = t / inner, in = t - o * inner;
+    const long long base = o * len * inner + in;
+    double s = 0.0;
+    for (long long k = 0; k < len; ++k)
+      s += LOG ? (double)g[base + k * inner] : (double)g[base + k * inner] * (double)y[base + k * inner];
+    for (long long k = 0; k < len; ++k) {
+      const double yy = y[base + k * inner], gg = g[base + k * inner];
+      dx[base + k * inner] = (T)(LOG ? gg - exp(yy) * s : yy * (gg - s));
+    }
+  }
+}
+
+template <typename T, bool LOG>
+static int launch_softmax_bwd(b200_engine *e, const T *y, const T *g, T *dx, long long outer, long long len,
+                              long long inner) {
+  if (inner == 1) {
+    const long long blocks = std::max<long long>(1, std::min<long long>((outer + 7) / 8, (long long)e->sm_count * 16));
+    softmax_bwd_rows_kernel<T, LOG><<<(int)blocks, 256, 0, e->stream>>>(y, g, dx, outer, len);
+  } else {
+    const long long total = outer * inner;
+    const long long blocks = std::max<long long>(1, std::min<long long>((total + 255) / 256, (long long)e->sm_count * 16));
+    softmax_bwd_strided_kernel<T, LOG><<<(int)blocks, 256, 0, e->stream>>>(y, g, dx, outer, len, inner);
+  }
+  B200_CHECK_LAUNCH(e, "softmax_bwd_kernel");
+  return B200_OK;
+}
+
 static int axis_op(b200_engine *e, int dtype, int mode, const void *x, void *y, int64_t outer, int64_t len,
                    int64_t inner, const char *who) {
   if (!e) return B200_ERR_INVALID;
@@ -398,6 +457,26 @@ extern "C" {
 int b200_softmax(b200_engine *e, int dtype, const void *x, void *y, int64_t outer, int64_t len, int64_t inner,
                  int is_log) {
   return axis_op(e, dtype, is_log ? 1 : 0, x, y, outer, len, inner, "b200_softmax");
+}
+
+int b200_softmax_bwd(b200_engine *e, int dtype, const void *y, const void *grad, void *dx, int64_t outer, int64_t len,
+                     int64_t inner, int is_log) {
+  if (!e) return B200_ERR_INVALID;
+  std::lock_guard<std::recursive_mutex> lk(e->mu);
+  B200_REQUIRE(e, dtype == B200_F32 || dtype == B200_F64, "b200_softmax_bwd: dtype %d not supported", dtype);
+  B200_REQUIRE(e, outer >= 0 && len >= 0 && inner >= 0, "b200_softmax_bwd: negative extent");
+  if (outer == 0 || inner == 0) return B200_OK;
+  B200_REQUIRE(e, len > 0, "b200_softmax_bwd: an axis of length 0");
+  B200_REQUIRE(e, y && grad && dx, "b200_softmax_bwd: null pointer");
+  DeviceGuard g(e);
+  int rc = flush_pending(e);
+  if (rc != B200_OK) return rc;
+  if (dtype == B200_F32) {
+    if (is_log) return launch_softmax_bwd<float, true>(e, (const float *)y, (const float *)grad, (float *)dx, outer, len, inner);
+    return launch_softmax_bwd<float, false>(e, (const float *)y, (const float *)grad, (float *)dx, outer, len, inner);
+  }
+  if (is_log) return launch_softmax_bwd<double, true>(e, (const double *)y, (const double *)grad, (double *)dx, outer, len, inner);
+  return launch_softmax_bwd<double, false>(e, (const double *)y, (const double *)grad, (double *)dx, outer, len, inner);
 }
 
 int b200_reduce(b200_engine *e, int dtype, int kind, const void *x, void *y, int64_t outer, int64_t len,

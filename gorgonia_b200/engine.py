@@ -32,14 +32,15 @@ def from_bf16(u16):
     return (u16.astype(np.uint32) << 16).view(np.float32)
 
 
-def _epilogue(bias=None, bias_kind=None, act=None, alpha=0.0):
-    if bias is None and act is None:
+def _epilogue(bias=None, bias_kind=None, act=None, alpha=0.0, accumulate=False):
+    if bias is None and act is None and not accumulate:
         return None
     ep = _lib.Epilogue()
     ep.bias_kind = 0 if bias is None else {"col": _lib.BIAS_COL, "row": _lib.BIAS_ROW}[bias_kind]
     ep.bias = None if bias is None else bias.ptr
     ep.act = {None: 0, "rectify": _lib.ACT_RECTIFY, "leaky": _lib.ACT_LEAKY}[act]
     ep.alpha = alpha
+    ep.accumulate = 1 if accumulate else 0
     return ep
 
 
@@ -288,8 +289,9 @@ class Engine:
         check(lib.b200_pointwise(self.h, dtype_code(dtype), C.byref(p), o, s, int(n)), self.h)
 
     # ---- linear algebra: Engine.MatMul / MatVecMul / Outer (cuda/linalg.go) ---------------------
-    def MatMul(self, a, b, prealloc, transA=False, transB=False, bias=None, bias_kind="col", act=None, alpha=0.0):
-        """prealloc = op(a) @ op(b). a, b are 2-D (or N-D with equal leading dims: batched, as
+    def MatMul(self, a, b, prealloc, transA=False, transB=False, bias=None, bias_kind="col", act=None, alpha=0.0,
+               incr=False):
+        """prealloc = op(a) @ op(b), or prealloc += op(a) @ op(b) with incr (Incr mode, execution.go:115-126). a, b are 2-D (or N-D with equal leading dims: batched, as
         batchedMatMul, operatorLinAlg.go:435-502). bf16 operands (tensors made by tensor_bf16)
         give a float32 result."""
         bf = getattr(a, "is_bf16", False)
@@ -311,7 +313,7 @@ class Engine:
         if prealloc.size != batch * M * N:
             raise B200Error(_lib.ERR_INVALID, "MatMul: prealloc has the wrong size")
         dt = _lib.BF16 if bf else dtype_code(a.dtype)
-        ep = _epilogue(bias, bias_kind, act, alpha)
+        ep = _epilogue(bias, bias_kind, act, alpha, accumulate=incr)
         check(lib.b200_gemm(self.h, dt, int(transA), int(transB), M, N, K, a.ptr, ac, b.ptr, bc, prealloc.ptr, N,
                             batch, ar * ac, br * bc, M * N, C.byref(ep) if ep else None), self.h)
         return prealloc
@@ -357,6 +359,13 @@ class Engine:
     def SoftMax(self, x, prealloc, axis=-1, log=False):
         o, l, i, _ = self._oli(x.shape, axis)
         check(lib.b200_softmax(self.h, dtype_code(x.dtype), x.ptr, prealloc.ptr, o, l, i, int(log)), self.h)
+        return prealloc
+
+    def SoftMaxDiff(self, y, grad, prealloc, axis=-1, log=False):
+        """softmaxDiffOp: the gradient with respect to the softmax input, from its output y and dL/dy."""
+        o, l, i, _ = self._oli(y.shape, axis)
+        check(lib.b200_softmax_bwd(self.h, dtype_code(y.dtype), y.ptr, grad.ptr, prealloc.ptr, o, l, i, int(log)),
+              self.h)
         return prealloc
 
     def Reduce(self, kind, x, prealloc, axis):
@@ -421,6 +430,25 @@ class Engine:
         check(lib.b200_maxpool2d_fwd(self.h, dtype_code(x.dtype), x.ptr, prealloc.ptr, mask.ptr if mask else None,
                                      B, Cc, H, W, kernel[0], kernel[1], pn, ps, pw, pe, explicit, stride[0],
                                      stride[1]), self.h)
+        return prealloc
+
+    def MaxPool2DDiff(self, grad, mask, prealloc, kernel, pad, stride):
+        """maxPoolDiffOp: prealloc (B,C,H,W) = gradient of the pool input; mask as MaxPool2D wrote it."""
+        B, Cc, H, W = prealloc.shape
+        if len(pad) == 2:
+            pn, ps, pw, pe, explicit = pad[0], pad[0], pad[1], pad[1], 0
+        else:
+            pn, ps, pw, pe = pad
+            explicit = 1
+        check(lib.b200_maxpool2d_bwd(self.h, dtype_code(grad.dtype), grad.ptr, mask.ptr, prealloc.ptr, B, Cc, H, W,
+                                     kernel[0], kernel[1], pn, ps, pw, pe, explicit, stride[0], stride[1]), self.h)
+        return prealloc
+
+    def Col2Im(self, col, prealloc, kernel, pad=(0, 0), stride=(1, 1), dil=(1, 1)):
+        """col2imOp: col (B, Ho, Wo, C*kh*kw) accumulated into prealloc (B,C,H,W)."""
+        B, Cc, H, W = prealloc.shape
+        check(lib.b200_col2im(self.h, dtype_code(col.dtype), col.ptr, prealloc.ptr, B, Cc, H, W, kernel[0], kernel[1],
+                              pad[0], pad[1], stride[0], stride[1], dil[0], dil[1]), self.h)
         return prealloc
 
     def Transpose(self, x, prealloc, perm):

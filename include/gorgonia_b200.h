@@ -261,6 +261,9 @@ typedef struct {
   int32_t act;        /* B200_ACT_*: Rectify x*(x>=0) (nn.go:136-163), LeakyRelu (nn.go:83-131) */
   const void *bias;   /* device vector in the output dtype */
   double alpha;       /* LeakyRelu slope */
+  int32_t accumulate; /* b200_gemm only: C = C + act(A.B + bias), the product rounded to the   *
+                       * output type before the addition (Incr mode, execution.go:115-126)     */
+  int32_t reserved;   /* must be 0 */
 } b200_epilogue;
 int b200_gemm(b200_engine *e, int dtype, int transA, int transB, int64_t M, int64_t N, int64_t K,
               const void *A, int64_t lda, const void *B, int64_t ldb, void *C, int64_t ldc,
@@ -372,6 +375,26 @@ int b200_conv2d_path(b200_engine *e, int dtype, int64_t B, int64_t C, int64_t H,
 int b200_im2col(b200_engine *e, int dtype, const void *x, void *col, int64_t B, int64_t C, int64_t H,
                 int64_t W, int kh, int kw, int pad_h, int pad_w, int stride_h, int stride_w, int dil_h,
                 int dil_w);
+/* ---- backward ops (the training variant of the tapes) ------------------------------------------
+ * b200_maxpool2d_bwd: maxPoolDiffOp.do (op_nn.go:1041-1121): dx (B,C,H,W) is zero except where a mask
+ *   entry points: dx[plane][mask[i]] += dy[plane][i], summed in (ph, pw) order. `mask` is the int64
+ *   mask b200_maxpool2d_fwd wrote for the same geometry (entries of -1 contribute nothing).
+ * b200_col2im: col2imOp.do (op_nn.go:446-637), the adjoint of b200_im2col: col (B, Ho, Wo, C*kh*kw)
+ *   accumulated into im (B,C,H,W), each pixel's additions in ascending (output row, output column)
+ *   order as the reference's walk over col makes them.
+ * b200_softmax_bwd: softmaxDiffOp (op_softmax.go:180-285) -> tensor.SoftMaxB / LogSoftMaxB on
+ *   (outer, len, inner): dx = y * (g - sum(g * y)), or for log-softmax dx = g - exp(y) * sum(g).
+ * Incr-mode matrix product (the "+=" of matMulDiff, operatorLinAlg.go:104-179, which the reference
+ * emulates as product-then-add, execution.go:115-126): b200_gemm with b200_epilogue.accumulate = 1. */
+int b200_maxpool2d_bwd(b200_engine *e, int dtype, const void *dy, const int64_t *mask, void *dx,
+                       int64_t B, int64_t C, int64_t H, int64_t W, int kh, int kw, int pad_north,
+                       int pad_south, int pad_west, int pad_east, int explicit_padding, int stride_h,
+                       int stride_w);
+int b200_col2im(b200_engine *e, int dtype, const void *col, void *im, int64_t B, int64_t C, int64_t H,
+                int64_t W, int kh, int kw, int pad_h, int pad_w, int stride_h, int stride_w, int dil_h,
+                int dil_w);
+int b200_softmax_bwd(b200_engine *e, int dtype, const void *y, const void *grad, void *dx,
+                     int64_t outer, int64_t len, int64_t inner, int is_log);
 int b200_maxpool2d_fwd(b200_engine *e, int dtype, const void *x, void *y, int64_t *mask, int64_t B,
                        int64_t C, int64_t H, int64_t W, int kh, int kw, int pad_north, int pad_south,
                        int pad_west, int pad_east, int explicit_padding, int stride_h, int stride_w);

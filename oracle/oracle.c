@@ -17,9 +17,12 @@
  * op_math_test.go, op_softmax_test.go, nn_test.go, known_issues_test.go,
  * op_by_indices_test.go, example_*_test.go and others; tests/test_oracle_golden.py).
  * PARITY UNPINNED for: last-ulp behaviour of math32's float32 transcendentals, gonum's
- * Sgemm summation order, and tensor.SoftMax's internal formulation; no bit-level vector
- * exists for them in gorgonia. Here float32 transcendentals are computed in double and
- * rounded once, and sums of products are accumulated in double.
+ * Sgemm summation order, tensor.SoftMax's internal formulation, and tensor.SoftMaxB /
+ * LogSoftMaxB (the softmax derivatives); no bit-level vector exists for them in gorgonia.
+ * Here float32 transcendentals are computed in double and rounded once, and sums of products
+ * are accumulated in double. The backward ops maxPoolDiff and col2im are integer-indexed
+ * additions whose order the repository spells out; their known answers are derived from the
+ * configurations of TestMaxPool2D and TestIm2Col (nn_test.go:13-89,140-193).
  *
  * Build: make -C oracle   (gcc -O3 -fopenmp -ffp-contract=off).
  */
@@ -390,6 +393,77 @@ void oracle_maxpool2d_f32(const float *x, float *y, int64_t *mask, int64_t B, in
       }
   }
 }
+
+/* maxPoolDiffOp.f32s / f64s (op_nn.go:1067-1121): the input gradient is zeroed, then every
+ * pooled position adds its gradient to the input position its mask entry names, in (ph, pw)
+ * order inside each (batch, channel) plane. The mask is the one the forward op recorded. A
+ * mask entry of -1 (an empty window) is skipped here; the reference would index out of range. */
+#define ORACLE_MAXPOOL_BWD(NAME, T)                                                                      \
+  void NAME(const T *dy, const int64_t *mask, T *dx, int64_t planes, int64_t hw, int64_t howo) {         \
+    _Pragma("omp parallel for schedule(static)") for (int64_t pl = 0; pl < planes; ++pl) {              \
+      T *g = dx + pl * hw;                                                                               \
+      for (int64_t i = 0; i < hw; ++i) g[i] = 0;                                                         \
+      for (int64_t i = 0; i < howo; ++i) {                                                               \
+        const int64_t at = mask[pl * howo + i];                                                          \
+        if (at >= 0 && at < hw) g[at] += dy[pl * howo + i];                                              \
+      }                                                                                                  \
+    }                                                                                                    \
+  }
+ORACLE_MAXPOOL_BWD(oracle_maxpool2d_bwd_f32, float)
+ORACLE_MAXPOOL_BWD(oracle_maxpool2d_bwd_f64, double)
+
+/* col2imOp.f32s / f64s (op_nn.go:571-637): the image is zeroed, then col (B, Ho, Wo, C*kh*kw)
+ * is walked in memory order (output row, output column, channel, kernel row, kernel column)
+ * and every entry whose tap lies inside the image is added to that pixel. The additions of one
+ * pixel therefore happen in ascending (output row, output column) order. */
+#define ORACLE_COL2IM(NAME, T)                                                                           \
+  void NAME(const T *col, T *im, int64_t B, int64_t C, int64_t H, int64_t W, int kh, int kw, int padH,   \
+            int padW, int sH, int sW, int dH, int dW) {                                                  \
+    const int64_t Ho = (H + 2 * padH - (dH * (kh - 1) + 1)) / sH + 1;                                    \
+    const int64_t Wo = (W + 2 * padW - (dW * (kw - 1) + 1)) / sW + 1;                                    \
+    const int64_t kk = C * kh * kw;                                                                      \
+    _Pragma("omp parallel for schedule(static)") for (int64_t b = 0; b < B; ++b) {                      \
+      T *imb = im + b * C * H * W;                                                                       \
+      const T *colb = col + b * Ho * Wo * kk;                                                            \
+      for (int64_t i = 0; i < C * H * W; ++i) imb[i] = 0;                                                \
+      int64_t idx = 0;                                                                                   \
+      for (int64_t oh = 0; oh < Ho; ++oh)                                                                \
+        for (int64_t ow = 0; ow < Wo; ++ow)                                                              \
+          for (int64_t c = 0; c < C; ++c)                                                                \
+            for (int r = 0; r < kh; ++r) {                                                               \
+              const int64_t ih = -padH + (int64_t)r * dH + oh * sH;                                      \
+              for (int s = 0; s < kw; ++s, ++idx) {                                                      \
+                const int64_t iw = -padW + (int64_t)s * dW + ow * sW;                                    \
+                if (ih >= 0 && ih < H && iw >= 0 && iw < W) imb[c * H * W + ih * W + iw] += colb[idx];   \
+              }                                                                                          \
+            }                                                                                            \
+    }                                                                                                    \
+  }
+ORACLE_COL2IM(oracle_col2im_f32, float)
+ORACLE_COL2IM(oracle_col2im_f64, double)
+
+/* softmaxDiffOp.UsePreallocDo -> tensor.SoftMaxB / LogSoftMaxB (op_softmax.go:262-274), on a
+ * tensor viewed as (outer, len, inner). gorgonia.org/tensor v0.9.23 is not part of the checkout;
+ * these are the published derivatives, evaluated in double:
+ *   softmax:      dx_i = y_i * (g_i - sum_j g_j y_j)
+ *   log-softmax:  dx_i = g_i - exp(y_i) * sum_j g_j
+ * PARITY UNPINNED: the reference's tests hold no vector for either (only forward outputs). */
+#define ORACLE_SOFTMAX_BWD(NAME, T, ACC, EXPF)                                                           \
+  void NAME(const T *y, const T *g, T *dx, int64_t outer, int64_t len, int64_t inner, int is_log) {      \
+    _Pragma("omp parallel for schedule(static)") for (int64_t oi = 0; oi < outer * inner; ++oi) {       \
+      const int64_t o = oi / inner, in = oi % inner;                                                     \
+      const T *yp = y + o * len * inner + in, *gp = g + o * len * inner + in;                            \
+      T *dp = dx + o * len * inner + in;                                                                 \
+      ACC s = 0;                                                                                         \
+      for (int64_t k = 0; k < len; ++k) s += is_log ? (ACC)gp[k * inner] : (ACC)gp[k * inner] * (ACC)yp[k * inner]; \
+      for (int64_t k = 0; k < len; ++k) {                                                                \
+        const ACC yy = yp[k * inner], gg = gp[k * inner];                                                \
+        dp[k * inner] = (T)(is_log ? gg - EXPF(yy) * s : yy * (gg - s));                                 \
+      }                                                                                                  \
+    }                                                                                                    \
+  }
+ORACLE_SOFTMAX_BWD(oracle_softmax_bwd_f32, float, double, exp)
+ORACLE_SOFTMAX_BWD(oracle_softmax_bwd_f64, double, long double, expl)
 
 /* softmaxOp.Do -> tensor.SoftMax / LogSoftMax along `axis` of a tensor viewed as
  * (outer, len, inner) (op_softmax.go:99-128). exp(x - max) / sum, evaluated in double. */

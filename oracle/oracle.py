@@ -166,6 +166,37 @@ def maxpool2d(x, kernel, pad, stride):
     return y, mask
 
 
+def maxpool2d_bwd(dy, mask, in_shape):
+    """Gradient of maxpool2d with respect to its input; mask as returned by maxpool2d."""
+    dy = np.ascontiguousarray(dy)
+    mask = np.ascontiguousarray(mask, dtype=np.int64)
+    B, Cc, H, W = in_shape
+    dx = np.empty(in_shape, dtype=dy.dtype)
+    getattr(_lib, "oracle_maxpool2d_bwd_" + _sfx(dy.dtype))(_p(dy), _p(mask), _p(dx), _i64(B * Cc), _i64(H * W),
+                                                            _i64(dy.shape[2] * dy.shape[3]))
+    return dx
+
+
+def col2im(col, in_shape, kh, kw, pad=(0, 0), stride=(1, 1), dil=(1, 1)):
+    """col (B, Ho, Wo, C*kh*kw) accumulated back into an image of in_shape = (B, C, H, W)."""
+    col = np.ascontiguousarray(col)
+    B, Cc, H, W = in_shape
+    im = np.empty(in_shape, dtype=col.dtype)
+    getattr(_lib, "oracle_col2im_" + _sfx(col.dtype))(_p(col), _p(im), _i64(B), _i64(Cc), _i64(H), _i64(W), kh, kw,
+                                                      pad[0], pad[1], stride[0], stride[1], dil[0], dil[1])
+    return im
+
+
+def softmax_bwd(y, grad, axis=-1, log=False):
+    y = np.ascontiguousarray(y)
+    grad = np.ascontiguousarray(grad, dtype=y.dtype)
+    axis %= y.ndim
+    o, l, i = _oli(y.shape, axis)
+    dx = np.empty_like(y)
+    getattr(_lib, "oracle_softmax_bwd_" + _sfx(y.dtype))(_p(y), _p(grad), _p(dx), _i64(o), _i64(l), _i64(i), int(log))
+    return dx
+
+
 def _oli(shape, axis):
     outer_ = int(np.prod(shape[:axis], dtype=np.int64))
     inner = int(np.prod(shape[axis + 1:], dtype=np.int64))

@@ -1,0 +1,155 @@
+"""Backward ops of the training variant: maxPoolDiff, col2im, softmaxDiff, Incr-mode MatMul.
+
+The integer-indexed ops (maxpool gradient, col2im) must equal the oracle bit for bit, also where
+windows overlap and several additions land on one element; the floating-point ones carry the
+tolerance written in each test."""
+import numpy as np
+import pytest
+
+import util
+from oracle import oracle
+from util import assert_bits_equal, assert_gemm_close
+
+pytestmark = pytest.mark.gpu
+
+POOL_BWD_CASES = [
+    # shape, kernel, pad, stride
+    ((1, 2, 3, 4), (2, 2), (0, 0), (1, 1)),          # TestMaxPool2D's configuration (nn_test.go:140-193)
+    ((2, 3, 28, 28), (2, 2), (0, 0), (2, 2)),        # the pools of LeNet / tiny-YOLO
+    ((2, 3, 13, 13), (2, 2), (1, 0, 1, 0), (1, 1)),  # tiny-YOLO's last pool: explicit padding, overlapping windows
+    ((3, 2, 9, 11), (3, 3), (1, 1), (2, 2)),         # overlapping 3x3 / 2
+    ((2, 2, 8, 8), (3, 2), (1, 0), (1, 2)),
+    ((1, 1, 7, 7), (2, 2), (0, 0), (2, 2)),          # odd planes: a row and a column belong to no window
+    ((2, 4, 6, 6), (5, 5), (2, 2), (1, 1)),          # every element sits in up to 25 windows
+]
+
+
+@pytest.mark.parametrize("dt", [np.float32, np.float64])
+@pytest.mark.parametrize("shape,kernel,pad,stride", POOL_BWD_CASES)
+def test_maxpool_bwd_bit_exact(fresh, shape, kernel, pad, stride, dt):
+    e = fresh
+    x = util.normal(61, shape, dt)
+    # ties on purpose: quantise so that several window elements share the maximum
+    x = (np.round(x * 2) / 2).astype(dt)
+    want_y, want_mask = oracle.maxpool2d(x.astype(np.float32), kernel, pad, stride)
+    y = e.empty(want_y.shape, dt)
+    mask = e.empty(want_y.shape, np.int64)
+    e.MaxPool2D(e.tensor(x), y, kernel, pad, stride, mask=mask)
+    assert np.array_equal(mask.numpy(), want_mask)
+    dy = util.normal(62, want_y.shape, dt)
+    dx = e.empty(shape, dt)
+    e.MaxPool2DDiff(e.tensor(dy), mask, dx, kernel, pad, stride)
+    assert_bits_equal(dx.numpy(), oracle.maxpool2d_bwd(dy, want_mask, shape))
+
+
+def test_maxpool_bwd_known_answer(fresh):
+    # nn_test.go:140-193: x = 0..23 as (1,2,3,4), 2x2 / stride 1, cost = Sum(y). Every window's
+    # maximum is its last element, so the gradient is 1 where h >= 1 and w >= 1 and 0 elsewhere.
+    e = fresh
+    x = np.arange(24, dtype=np.float32).reshape(1, 2, 3, 4)
+    y, mask = e.empty((1, 2, 2, 3)), e.empty((1, 2, 2, 3), np.int64)
+    e.MaxPool2D(e.tensor(x), y, (2, 2), (0, 0), (1, 1), mask=mask)
+    dx = e.empty(x.shape)
+    e.MaxPool2DDiff(e.tensor(np.ones((1, 2, 2, 3), np.float32)), mask, dx, (2, 2), (0, 0), (1, 1))
+    want = np.zeros_like(x)
+    want[:, :, 1:, 1:] = 1
+    assert_bits_equal(dx.numpy(), want)
+
+
+COL2IM_CASES = [
+    # image shape, kernel, pad, stride, dilation
+    ((2, 1, 28, 28), (4, 4), (0, 0), (1, 1), (1, 1)),   # im2colTests (nn_test.go:13-23)
+    ((2, 1, 28, 28), (3, 3), (1, 1), (2, 2), (1, 1)),
+    ((2, 1, 28, 28), (3, 3), (1, 1), (3, 3), (1, 1)),
+    ((2, 3, 9, 8), (3, 3), (1, 1), (1, 1), (1, 1)),
+    ((1, 4, 20, 20), (3, 3), (2, 2), (1, 1), (2, 2)),   # dilation
+    ((2, 5, 17, 19), (3, 5), (2, 1), (2, 3), (1, 1)),   # odd everything
+    ((3, 2, 6, 6), (1, 1), (0, 0), (1, 1), (1, 1)),     # 1x1: a plain transposition
+]
+
+
+@pytest.mark.parametrize("dt", [np.float32, np.float64])
+@pytest.mark.parametrize("shape,kernel,pad,stride,dil", COL2IM_CASES)
+def test_col2im_bit_exact(fresh, shape, kernel, pad, stride, dil, dt):
+    e = fresh
+    B, Cc, H, W = shape
+    Ho = oracle.conv_out(H, kernel[0], pad[0], stride[0], dil[0])
+    Wo = oracle.conv_out(W, kernel[1], pad[1], stride[1], dil[1])
+    col = util.normal(63, (B, Ho, Wo, Cc * kernel[0] * kernel[1]), dt)
+    im = e.empty(shape, dt)
+    e.Col2Im(e.tensor(col), im, kernel, pad, stride, dil)
+    assert_bits_equal(im.numpy(), oracle.col2im(col, shape, kernel[0], kernel[1], pad, stride, dil))
+
+
+def test_col2im_is_the_adjoint_of_im2col(fresh):
+    # <im2col(x), c> == <x, col2im(c)>, and col2im(ones) counts the windows that cover each pixel
+    e = fresh
+    shape, kernel, pad, stride = (2, 3, 12, 10), (3, 3), (1, 1), (2, 2)
+    x = util.normal(64, shape, np.float64)
+    Ho, Wo = oracle.conv_out(12, 3, 1, 2), oracle.conv_out(10, 3, 1, 2)
+    c = util.normal(65, (2, Ho, Wo, 27), np.float64)
+    col, im = e.empty(c.shape, np.float64), e.empty(shape, np.float64)
+    e.Im2Col(e.tensor(x), col, kernel, pad, stride)
+    e.Col2Im(e.tensor(c), im, kernel, pad, stride)
+    lhs, rhs = float((col.numpy() * c).sum()), float((x * im.numpy()).sum())
+    assert abs(lhs - rhs) <= 1e-12 * max(abs(lhs), 1.0)
+    ones = e.empty(shape, np.float64)
+    e.Col2Im(e.tensor(np.ones_like(c)), ones, kernel, pad, stride)
+    count = np.zeros(shape[2:])
+    for oh in range(Ho):
+        for ow in range(Wo):
+            for r in range(3):
+                for s in range(3):
+                    ih, iw = oh * 2 - 1 + r, ow * 2 - 1 + s
+                    if 0 <= ih < 12 and 0 <= iw < 10:
+                        count[ih, iw] += 1
+    assert np.array_equal(ones.numpy(), np.broadcast_to(count, shape))
+
+
+@pytest.mark.parametrize("dt", [np.float32, np.float64])
+@pytest.mark.parametrize("log", [False, True])
+@pytest.mark.parametrize("shape,axis", [((256, 10), 1), ((8192, 10), -1), ((7, 3), 1), ((33, 1000), 1),
+                                        ((5, 6, 7), 1), ((4, 5000), 1), ((10, 1), 0)])
+def test_softmax_bwd(fresh, shape, axis, log, dt):
+    # tolerance: 1e-6 (float32) / 1e-13 (float64) of max(|r|, the largest |grad| of the tensor): the
+    # difference g - sum(g*y) cancels, so an element-wise relative bound would be ill-posed
+    e = fresh
+    x = util.normal(66, shape, dt)
+    y = oracle.softmax(x, axis, log)
+    g = util.normal(67, shape, dt)
+    want = oracle.softmax_bwd(y, g, axis, log)
+    dx = e.empty(shape, dt)
+    e.SoftMaxDiff(e.tensor(y), e.tensor(g), dx, axis, log)
+    got = dx.numpy()
+    rel = 1e-6 if dt == np.float32 else 1e-13
+    lim = rel * np.maximum(np.abs(want.astype(np.float64)), float(np.abs(g).max()))
+    assert (np.abs(got.astype(np.float64) - want.astype(np.float64)) <= lim).all()
+    if not log:   # sum_i y_i = 1, so the derivative sums to zero along the axis
+        assert np.abs(got.astype(np.float64).sum(axis)).max() <= (1e-5 if dt == np.float32 else 1e-12) * np.abs(g).max()
+
+
+@pytest.mark.parametrize("shape", [(300, 200, 512), (128, 128, 64), (257, 130, 96), (33, 7, 20)])
+def test_matmul_incr_equals_product_then_add(fresh, shape):
+    # Incr mode (execution.go:115-126): the product is rounded to float32, then added to what the
+    # output holds; one call must equal MatMul into a temporary followed by Add, bit for bit
+    e = fresh
+    M, N, K = shape
+    a, b = util.normal(68, (M, K), scale=0.05), util.normal(69, (K, N), scale=0.05)
+    c0 = util.normal(70, (M, N))
+    ta, tb = e.tensor(a), e.tensor(b)
+    c = e.tensor(c0)
+    e.MatMul(ta, tb, c, incr=True)
+    tmp, ref = e.empty((M, N)), e.tensor(c0)
+    e.MatMul(ta, tb, tmp)
+    e.Add(ref, tmp, unsafe=True)
+    assert_bits_equal(c.numpy(), ref.numpy())
+    assert_gemm_close(c.numpy(), c0.astype(np.float64) + oracle.gemm(a, b).astype(np.float64), 1e-5)
+
+
+def test_matmul_incr_float64(fresh):
+    e = fresh
+    a, b = util.normal(71, (40, 30), np.float64), util.normal(72, (30, 20), np.float64)
+    c0 = util.normal(73, (40, 20), np.float64)
+    c = e.tensor(c0)
+    e.MatMul(e.tensor(a), e.tensor(b), c, incr=True)
+    assert np.abs(c.numpy() - (c0 + a @ b)).max() <= 1e-12

@@ -100,3 +100,59 @@ def test_fixtures_match_the_generator_if_a_checkout_is_given():
     from tests.golden import extract_goldens as X
     assert X.extract_binop(root) == json.load(open(os.path.join(G.GOLDEN, "binop.json")))
     assert X.extract_byindices(root) == json.load(open(os.path.join(G.GOLDEN, "byindices.json")))
+
+
+# ---- backward ops: known answers derived from the configurations of gorgonia's own tests ---------
+
+def test_oracle_maxpool_bwd_known_answer():
+    # nn_test.go:140-193 (TestMaxPool2D): x = 0..23 as (1,2,3,4), 2x2 window, stride 1, cost = Sum(y).
+    # x increases along both axes, so every window's maximum is its last element and the gradient is
+    # 1 where h >= 1 and w >= 1, 0 elsewhere.
+    x = np.arange(24, dtype=np.float32).reshape(1, 2, 3, 4)
+    y, mask = oracle.maxpool2d(x, (2, 2), (0, 0), (1, 1))
+    dx = oracle.maxpool2d_bwd(np.ones_like(y), mask, x.shape)
+    want = np.zeros_like(x)
+    want[:, :, 1:, 1:] = 1
+    assert np.array_equal(dx, want)
+
+
+@pytest.mark.parametrize("kernel,pad,stride", [((4, 4), (0, 0), (1, 1)), ((3, 3), (1, 1), (2, 2)),
+                                                ((3, 3), (1, 1), (3, 3))])
+def test_oracle_col2im_counts_windows(kernel, pad, stride):
+    # nn_test.go:13-89 (TestIm2Col): the gradient of Sum(Im2Col(x)) is col2im(ones), which counts the
+    # windows that cover each pixel; the count is recomputed here pixel by pixel.
+    shape = (2, 1, 28, 28)
+    Ho, Wo = oracle.conv_out(28, kernel[0], pad[0], stride[0]), oracle.conv_out(28, kernel[1], pad[1], stride[1])
+    ones = np.ones((2, Ho, Wo, kernel[0] * kernel[1]), np.float32)
+    got = oracle.col2im(ones, shape, kernel[0], kernel[1], pad, stride)
+    want = np.zeros((28, 28), np.float32)
+    for ih in range(28):
+        for iw in range(28):
+            n = 0
+            for r in range(kernel[0]):
+                for s in range(kernel[1]):
+                    a, b = ih + pad[0] - r, iw + pad[1] - s
+                    if a >= 0 and b >= 0 and a % stride[0] == 0 and b % stride[1] == 0 and a // stride[0] < Ho \
+                            and b // stride[1] < Wo:
+                        n += 1
+            want[ih, iw] = n
+    assert np.array_equal(got, np.broadcast_to(want, shape))
+
+
+@pytest.mark.parametrize("log", [False, True])
+def test_oracle_softmax_bwd_matches_finite_differences(log):
+    # no vector for SoftMaxB / LogSoftMaxB exists in gorgonia's tests: check the restated formula
+    # against central differences of the oracle's own forward op, in float64
+    g = np.random.Generator(np.random.Philox(11))
+    x, gr = g.standard_normal((4, 6)), g.standard_normal((4, 6))
+    y = oracle.softmax(x, -1, log)
+    got = oracle.softmax_bwd(y, gr, -1, log)
+    h = 1e-6
+    want = np.zeros_like(x)
+    for i in range(4):
+        for j in range(6):
+            xp, xm = x.copy(), x.copy()
+            xp[i, j] += h
+            xm[i, j] -= h
+            want[i, j] = ((oracle.softmax(xp, -1, log) - oracle.softmax(xm, -1, log)) * gr).sum() / (2 * h)
+    assert np.abs(got - want).max() < 1e-8
