@@ -6,9 +6,9 @@ tolerance written in each test."""
 import numpy as np
 import pytest
 
-import util
+from tests import util
 from oracle import oracle
-from util import assert_bits_equal, assert_gemm_close
+from tests.util import assert_bits_equal, assert_gemm_close
 
 pytestmark = pytest.mark.gpu
 
