@@ -354,6 +354,73 @@ def wl_gemm(ctx, args, main):
 
 
 # ------------------------------------------------------------------------------------------
+# backward ops (max-pool gradient, col2im, softmax derivative, Incr-mode MatMul)
+# ------------------------------------------------------------------------------------------
+
+BACKWARD_SHAPES = {"pool": (2048, 32, 28, 28), "col2im": (1024, 32, 14, 14), "softmax": (1 << 22, 10)}
+
+
+def wl_backward(ctx, args, main):
+    """HBM-bound backward ops at LeNet's shapes; algorithmic bytes = every operand once."""
+    steps, warmup = (args.steps, args.warmup) if main else (5, 3)
+    e = ctx.make_engine(6 << 30)
+    g = np.random.Generator(np.random.Philox(17 + ctx.rank))
+    per_op, total_bytes, total_s, launches = {}, 0.0, 0.0, 0
+    sampler = ClockSampler(ctx.local_rank) if main else None
+    # max-pool gradient: dy + mask read, dx written
+    B, Cc, H, W = BACKWARD_SHAPES["pool"]
+    x = e.tensor(g.standard_normal((B, Cc, H, W), dtype=np.float32))
+    y, mask = e.empty((B, Cc, H // 2, W // 2)), e.empty((B, Cc, H // 2, W // 2), np.int64)
+    e.MaxPool2D(x, y, (2, 2), (0, 0), (2, 2), mask=mask)
+    dx = x   # reuse the buffer
+    s_, l_ = ctx.timed(lambda: e.MaxPool2DDiff(y, mask, dx, (2, 2), (0, 0), (2, 2)), steps, warmup, sampler)
+    by = B * Cc * (H // 2) * (W // 2) * 12 + B * Cc * H * W * 4
+    per_op["maxpool_bwd"] = by / s_ / 1e9
+    total_bytes += by; total_s += s_; launches += l_
+    e.ResetAllocator()
+    # col2im: col read, image written
+    B, Cc, H, W = BACKWARD_SHAPES["col2im"]
+    col = e.tensor(g.standard_normal((B, H, W, Cc * 9), dtype=np.float32))
+    im = e.empty((B, Cc, H, W))
+    s_, l_ = ctx.timed(lambda: e.Col2Im(col, im, (3, 3), (1, 1)), steps, warmup)
+    by = B * H * W * Cc * 9 * 4 + B * Cc * H * W * 4
+    per_op["col2im"] = by / s_ / 1e9
+    total_bytes += by; total_s += s_; launches += l_
+    e.ResetAllocator()
+    # softmax derivative: y + grad read, dx written
+    R, L = BACKWARD_SHAPES["softmax"]
+    ys = e.tensor(g.random((R, L), dtype=np.float32))
+    gr = e.tensor(g.standard_normal((R, L), dtype=np.float32))
+    dxs = e.empty((R, L))
+    s_, l_ = ctx.timed(lambda: e.SoftMaxDiff(ys, gr, dxs), steps, warmup)
+    by = R * L * 12
+    per_op["softmax_bwd"] = by / s_ / 1e9
+    total_bytes += by; total_s += s_; launches += l_
+    e.ResetAllocator()
+    # Incr-mode MatMul, 4096^3
+    n = 4096
+    a = e.tensor((g.standard_normal((n, n), dtype=np.float32) * np.float32(0.02)))
+    b = e.tensor((g.standard_normal((n, n), dtype=np.float32) * np.float32(0.02)))
+    c = e.tensor(np.zeros((n, n), np.float32))
+    s_, l_ = ctx.timed(lambda: e.MatMul(a, b, c, incr=True), steps, warmup)
+    launches += l_
+    clocks = sampler.stop() if (main and ctx.rank == 0) else None
+    pk = peaks()
+    gbs = total_bytes / total_s / 1e9
+    return {"metric": "backward ops throughput (algorithmic bytes)", "unit": "GB/s", "value": ctx.world * gbs,
+            "ms_per_step": total_s * 1e3, "dtype": "f32",
+            "config": {"workload": "backward_ops", "shapes": {k: list(v) for k, v in BACKWARD_SHAPES.items()},
+                       "l2": "operands larger than L2",
+                       "parallelism": f"replicas x{ctx.world}" if ctx.world > 1 else "single GPU"},
+            "gpu_launches": launches, "clocks": clocks, "steps": steps, "warmup": warmup,
+            "per_op_gbs": {k: round(v, 1) for k, v in per_op.items()},
+            "matmul_incr_4096_tflops": 2.0 * n ** 3 / s_ / 1e12,
+            "roofline": {"bound": "hbm", "kernel": "maxpool_bwd_kernel + col2im_kernel + softmax_bwd_rows_kernel",
+                         "achieved": gbs, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": gbs / pk["hbm_gbs"],
+                         "peak_source": pk["source"], "traffic": None}}
+
+
+# ------------------------------------------------------------------------------------------
 # inference graphs
 # ------------------------------------------------------------------------------------------
 
@@ -489,7 +556,35 @@ def cpu_gemm(steps=1, n=1024):
             "sample": f"{steps} MatMul(s) of {n}^3 float32 (double accumulation)", "ms_per_step": dt * 1e3}
 
 
+def cpu_backward(steps=1):
+    """The oracle's maxpool gradient, col2im and softmax derivative on 1/16 of the GPU leg's batches."""
+    from oracle import oracle
+    g = np.random.Generator(np.random.Philox(17))
+    B, Cc, H, W = BACKWARD_SHAPES["pool"]
+    B //= 16
+    x = g.standard_normal((B, Cc, H, W), dtype=np.float32)
+    y, mask = oracle.maxpool2d(x, (2, 2), (0, 0), (2, 2))
+    B2, C2, H2, W2 = BACKWARD_SHAPES["col2im"]
+    B2 //= 16
+    col = g.standard_normal((B2, H2, W2, C2 * 9), dtype=np.float32)
+    R, L = BACKWARD_SHAPES["softmax"]
+    R //= 16
+    ys, gr = g.random((R, L), dtype=np.float32), g.standard_normal((R, L), dtype=np.float32)
+    by = (B * Cc * (H // 2) * (W // 2) * 12 + B * Cc * H * W * 4 + B2 * H2 * W2 * C2 * 9 * 4 + B2 * C2 * H2 * W2 * 4 +
+          R * L * 12)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        oracle.maxpool2d_bwd(y, mask, x.shape)
+        oracle.col2im(col, (B2, C2, H2, W2), 3, 3, (1, 1))
+        oracle.softmax_bwd(ys, gr)
+    dt = (time.perf_counter() - t0) / steps
+    return {"value": by / dt / 1e9, "unit": "GB/s", "cores": oracle.threads(), "kind": "port",
+            "sample": f"{steps} pass(es) over 1/16 of the GPU leg's batches", "ms_per_step": dt * 1e3}
+
+
 def cpu_leg(workload, steps, warmup):
+    if workload == "backward":
+        return cpu_backward(steps)
     if workload == "elementwise":
         return cpu_elementwise(steps, warmup)
     if workload == "gemm":
@@ -505,12 +600,13 @@ def run_reference(args):
     c = cpu_leg(args.workload, steps, 1 if args.workload == "elementwise" else 0)
     line = {"impl": "reference", "metric": c.pop("metric", None), "value": c["value"], "unit": c["unit"],
             "n_gpus": args.gpus, "steps": steps, "warmup": args.warmup, "ms_per_step": c.pop("ms_per_step"),
-            "higher_is_better": True, "scaling": "weak" if args.workload in ("elementwise", "gemm") else "strong",
+            "higher_is_better": True, "scaling": "weak" if args.workload in ("elementwise", "gemm", "backward") else "strong",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": args.workload, "sample": c["sample"]},
             "cpu_baseline": c, "e2e": {"value": c["value"], "unit": c["unit"], "h2d_bytes_per_step": 0,
                                        "d2h_bytes_per_step": 0}, "note": REF_NOTE}
     line["metric"] = {"elementwise": "elementwise sweep throughput (algorithmic bytes)",
+                      "backward": "backward ops throughput (algorithmic bytes)",
                       "gemm": "MatMul float32 throughput, 2*M*N*K"}.get(args.workload,
                                                                          f"{args.workload} forward throughput")
     print(json.dumps(line), flush=True)
@@ -521,6 +617,8 @@ def run_workload(ctx, args, name, main):
         return wl_elementwise(ctx, args, main)
     if name == "gemm":
         return wl_gemm(ctx, args, main)
+    if name == "backward":
+        return wl_backward(ctx, args, main)
     return wl_model(ctx, args, name, main)
 
 
@@ -529,13 +627,13 @@ def run_ours(args):
     res = run_workload(ctx, args, args.workload, True)
     others = {}
     if not args.no_others and not args.profile:
-        for name in ("elementwise", "gemm", "mlp", "lenet", "yolo"):
+        for name in ("elementwise", "gemm", "mlp", "lenet", "yolo", "backward"):
             if name == args.workload:
                 continue
             try:
                 r = run_workload(ctx, args, name, False)
                 keep = {k: r[k] for k in ("metric", "value", "unit", "ms_per_step", "config", "roofline") if k in r}
-                for k in ("bf16_tflops", "bf16_frac_of_measured_peak"):
+                for k in ("bf16_tflops", "bf16_frac_of_measured_peak", "per_op_gbs", "matmul_incr_4096_tflops"):
                     if k in r:
                         keep[k] = r[k]
                 others[name] = keep
@@ -547,8 +645,9 @@ def run_ours(args):
                 "higher_is_better": True, "scaling": res.get("scaling", "weak"), "vs_baseline": None,
                 "dtype": res["dtype"], "data": "synthetic", "config": res["config"], "roofline": res["roofline"],
                 "e2e": res.get("e2e"), "gpu_launches": res["gpu_launches"], "clocks": res["clocks"]}
-        if "per_op_gbs" in res:
-            line["per_op_gbs"] = res["per_op_gbs"]
+        for k in ("per_op_gbs", "matmul_incr_4096_tflops"):
+            if k in res:
+                line[k] = res[k]
         if ctx.world == 1 and not args.no_cpu and not args.profile:
             line["cpu_baseline"] = cpu_leg(args.workload, 3 if args.workload == "elementwise" else 1, 1)
             line["cpu_baseline"].pop("ms_per_step", None)
@@ -566,7 +665,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="elementwise", choices=["elementwise", "gemm", "mlp", "lenet", "yolo"])
+    ap.add_argument("--workload", default="elementwise", choices=["elementwise", "gemm", "mlp", "lenet", "yolo", "backward"])
     ap.add_argument("--elements", type=int, default=1 << 29)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
     ap.add_argument("--no-others", action="store_true", help="measure only the chosen workload")

@@ -291,6 +291,181 @@ __global__ void __launch_bounds__(256) col2im_kernel(const T *__restrict__ col, 
   }
 }
 
+// The gradient of the pooling every config here uses (2x2 window, stride 2, no padding, W a multiple
+// of 4): windows do not overlap, so an input element receives at most one term, 0 + dy (the
+// reference adds into a zeroed array, which turns a -0.0 gradient into +0.0; so does this). One
+// thread handles two neighbouring windows: 8 bytes of gradient and 16 of mask in, two float4 rows
+// out. Rows and columns past the last whole window (odd H) are written as zeros.
+__global__ void __launch_bounds__(256) maxpool2x2_bwd_kernel(const float *__restrict__ dy,
+                                                             const long long *__restrict__ mask,
+                                                             float *__restrict__ dx, long long planes, int H, int W,
+                                                             int Ho, int Wo) {
+  const int pairs = Wo >> 1;  // Wo = W/2 is even because W % 4 == 0
+  const int rows = (H + 1) >> 1;  // one extra, window-less row when H is odd
+  const long long total = planes * rows * pairs;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += stride) {
+    const int j = (int)(t % pairs);
+    const int ph = (int)((t / pairs) % rows);
+    const long long plane = t / ((long long)pairs * rows);
+    float *out = dx + (plane * H + 2 * ph) * (long long)W + 4 * j;
+    if (ph >= Ho) {  // the last row of an odd-height plane belongs to no window
+      *reinterpret_cast<float4 *>(out) = make_float4(0.f, 0.f, 0.f, 0.f);
+      continue;
+    }
+    const long long o = (plane * Ho + ph) * (long long)Wo + 2 * j;
+    const float2 g = *reinterpret_cast<const float2 *>(dy + o);
+    const longlong2 m = *reinterpret_cast<const longlong2 *>(mask + o);
+    const long long base = (long long)(2 * ph) * W + 4 * j;  // index of out[0] inside the plane
+    const float g0 = 0.f + g.x, g1 = 0.f + g.y;
+    float4 r0, r1;
+    r0.x = m.x == base ? g0 : 0.f;
+    r0.y = m.x == base + 1 ? g0 : 0.f;
+    r0.z = m.y == base + 2 ? g1 : 0.f;
+    r0.w = m.y == base + 3 ? g1 : 0.f;
+    r1.x = m.x == base + W ? g0 : 0.f;
+    r1.y = m.x == base + W + 1 ? g0 : 0.f;
+    r1.z = m.y == base + W + 2 ? g1 : 0.f;
+    r1.w = m.y == base + W + 3 ? g1 : 0.f;
+    *reinterpret_cast<float4 *>(out) = r0;
+    *reinterpret_cast<float4 *>(out + W) = r1;
+  }
+}
+
+// col2im for stride-1, undilated rows with the col rows staged in shared memory: a block walks one
+// image from top to bottom and keeps the kh col rows that can touch the current image row in a
+// ring (slot = output row mod kh), so every col row is read from memory exactly once, with
+// consecutive threads on consecutive addresses. The ring's pitch is padded by one word so that
+// neighbouring pixels hit different banks. Every pixel adds its taps in the reference's order
+// (ascending output row and column = descending kernel row and column).
+template <typename T, bool UNIT_W>  // UNIT_W: stride 1 and no dilation along W as well (no divisions)
+__global__ void __launch_bounds__(256) col2im_rows_kernel(const T *__restrict__ col, T *__restrict__ im, long long B,
+                                                          int C, int H, int W, int Ho, int Wo, int kh, int kw,
+                                                          int padH, int padW, int sW, int dW) {
+  extern __shared__ __align__(16) unsigned char c2i_smem[];
+  T *ring = reinterpret_cast<T *>(c2i_smem);
+  const int crs = C * kh * kw, khw = kh * kw;
+  const int pitch = crs + 1;
+  const long long row_elems = (long long)Wo * crs;
+  auto load_row = [&](long long b, int oh) {
+    const T *src = col + (b * Ho + oh) * row_elems;
+    T *dst = ring + (long long)(oh % kh) * Wo * pitch;
+    int ow = 0, q = threadIdx.x;  // element i = ow * crs + q of the row, i = threadIdx.x, + 256, ...
+    for (long long i = threadIdx.x; i < row_elems; i += blockDim.x, q += blockDim.x) {
+      while (q >= crs) {
+        q -= crs;
+        ++ow;
+      }
+      dst[ow * pitch + q] = src[i];
+    }
+  };
+  for (long long b = blockIdx.x; b < B; b += gridDim.x) {
+    for (int oh = 0; oh < padH && oh < Ho; ++oh) load_row(b, oh);  // rows above the first new one
+    for (int ih = 0; ih < H; ++ih) {
+      if (ih + padH < Ho) load_row(b, ih + padH);
+      __syncthreads();
+      T *out = im + (b * C * H + ih) * (long long)W;
+      for (int i = threadIdx.x; i < C * W; i += blockDim.x) {
+        const int c = i / W, iw = i - c * W;
+        T acc = T(0);
+        for (int r = kh - 1; r >= 0; --r) {
+          const int oh = ih + padH - r;
+          if (oh < 0 || oh >= Ho) continue;
+          const T *slot = ring + (long long)(oh % kh) * Wo * pitch + c * khw + r * kw;
+          for (int sx = kw - 1; sx >= 0; --sx) {
+            int ow;
+            if (UNIT_W) {
+              ow = iw + padW - sx;
+              if (ow < 0) continue;
+            } else {
+              const int num_w = iw + padW - sx * dW;
+              if (num_w < 0 || num_w % sW != 0) continue;
+              ow = num_w / sW;
+            }
+            if (ow >= Wo) continue;
+            acc = acc + slot[ow * pitch + sx];
+          }
+        }
+        out[(long long)c * H * W + iw] = acc;
+      }
+      __syncthreads();
+    }
+  }
+}
+
+// The float32 ring kernel with the memory side pipelined: C*kh*kw a multiple of 4, so a col row is
+// a whole number of float4 that never straddle two output columns. A thread holds up to 8 float4
+// of the NEXT col row in registers; their loads are issued before the current image row is
+// computed and land while it runs, instead of one dependent load per loop trip.
+template <bool UNIT_W>
+__global__ void __launch_bounds__(256) col2im_rows4_kernel(const float *__restrict__ col, float *__restrict__ im,
+                                                           long long B, int C, int H, int W, int Ho, int Wo, int kh,
+                                                           int kw, int padH, int padW, int sW, int dW) {
+  extern __shared__ __align__(16) unsigned char c2i4_smem[];
+  float *ring = reinterpret_cast<float *>(c2i4_smem);
+  const int crs = C * kh * kw, khw = kh * kw;
+  const int pitch = crs + 1;
+  const int row_vec = (Wo * crs) >> 2;  // float4 per col row, at most 8 * 256
+  float4 pre[8];
+  auto fetch = [&](long long b, int oh) {
+    const float4 *src = reinterpret_cast<const float4 *>(col + (b * Ho + oh) * (long long)Wo * crs);
+#pragma unroll
+    for (int v = 0; v < 8; ++v) {
+      const int i = threadIdx.x + v * 256;
+      if (i < row_vec) pre[v] = __ldg(src + i);
+    }
+  };
+  auto stash = [&](int oh) {
+    float *dst = ring + (long long)(oh % kh) * Wo * pitch;
+#pragma unroll
+    for (int v = 0; v < 8; ++v) {
+      const int i = threadIdx.x + v * 256;
+      if (i < row_vec) {
+        const int e0 = i << 2, ow = e0 / crs, q = e0 - ow * crs;
+        float *d = dst + ow * pitch + q;
+        d[0] = pre[v].x; d[1] = pre[v].y; d[2] = pre[v].z; d[3] = pre[v].w;
+      }
+    }
+  };
+  for (long long b = blockIdx.x; b < B; b += gridDim.x) {
+    for (int oh = 0; oh < padH && oh < Ho; ++oh) {  // rows above the first new one
+      fetch(b, oh);
+      stash(oh);
+    }
+    if (padH < Ho) fetch(b, padH);
+    for (int ih = 0; ih < H; ++ih) {
+      if (ih + padH < Ho) stash(ih + padH);
+      __syncthreads();
+      if (ih + 1 + padH < Ho) fetch(b, ih + 1 + padH);  // lands while this image row is computed
+      float *out = im + (b * C * H + ih) * (long long)W;
+      for (int i = threadIdx.x; i < C * W; i += blockDim.x) {
+        const int c = i / W, iw = i - c * W;
+        float acc = 0.f;
+        for (int r = kh - 1; r >= 0; --r) {
+          const int oh = ih + padH - r;
+          if (oh < 0 || oh >= Ho) continue;
+          const float *slot = ring + (long long)(oh % kh) * Wo * pitch + c * khw + r * kw;
+          for (int sx = kw - 1; sx >= 0; --sx) {
+            int ow;
+            if (UNIT_W) {
+              ow = iw + padW - sx;
+              if (ow < 0) continue;
+            } else {
+              const int num_w = iw + padW - sx * dW;
+              if (num_w < 0 || num_w % sW != 0) continue;
+              ow = num_w / sW;
+            }
+            if (ow >= Wo) continue;
+            acc = acc + slot[ow * pitch + sx];
+          }
+        }
+        out[(long long)c * H * W + iw] = acc;
+      }
+      __syncthreads();
+    }
+  }
+}
+
 static int grid_for(b200_engine *e, long long work) {
   return (int)std::max<long long>(1, std::min<long long>((work + 255) / 256, (long long)e->sm_count * 16));
 }
@@ -371,6 +546,16 @@ int b200_maxpool2d_bwd(b200_engine *e, int dtype, const void *dy, const int64_t 
   const int oh0 = explicit_padding ? pad_south : pad_north;
   const int ow0 = explicit_padding ? pad_east : pad_west;
   const long long total = B * C * H * W;
+  if (dtype == B200_F32 && kh == 2 && kw == 2 && stride_h == 2 && stride_w == 2 && pad_north == 0 && pad_south == 0 &&
+      pad_west == 0 && pad_east == 0 && W % 4 == 0 && (uintptr_t)dx % 16 == 0 && (uintptr_t)dy % 8 == 0 &&
+      (uintptr_t)mask % 16 == 0) {
+    const long long work = B * C * ((H + 1) / 2) * (Wo / 2);
+    maxpool2x2_bwd_kernel<<<grid_for(e, work), 256, 0, e->stream>>>((const float *)dy, (const long long *)mask,
+                                                                   (float *)dx, B * C, (int)H, (int)W, (int)Ho,
+                                                                   (int)Wo);
+    B200_CHECK_LAUNCH(e, "maxpool2x2_bwd_kernel");
+    return B200_OK;
+  }
   if (dtype == B200_F32)
     maxpool_bwd_kernel<float><<<grid_for(e, total), 256, 0, e->stream>>>(
         (const float *)dy, (const long long *)mask, (float *)dx, B * C, (int)H, (int)W, (int)Ho, (int)Wo, kh, kw,
@@ -402,6 +587,57 @@ int b200_col2im(b200_engine *e, int dtype, const void *col, void *im, int64_t B,
   int rc = flush_pending(e);
   if (rc != B200_OK) return rc;
   const long long total = B * C * H * W;
+  // staged variant (stride 1 and no dilation along H, fewer pad rows than kernel rows): a ring of kh
+  // col rows of Wo * (crs + 1) elements must fit in 96 KB of shared memory
+  const size_t es = dtype_size(dtype);
+  const size_t staged = (size_t)kh * Wo * (C * kh * kw + 1) * es;
+  if (staged <= 96 * 1024 && stride_h == 1 && dil_h == 1 && pad_h < kh) {
+    static int attr_dev_mask = 0;
+    if (!(attr_dev_mask & (1 << (e->device & 31)))) {
+      B200_CHECK_CUDA(e, cudaFuncSetAttribute(col2im_rows_kernel<float, true>,
+                                              cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+      B200_CHECK_CUDA(e, cudaFuncSetAttribute(col2im_rows_kernel<float, false>,
+                                              cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+      B200_CHECK_CUDA(e, cudaFuncSetAttribute(col2im_rows_kernel<double, true>,
+                                              cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+      B200_CHECK_CUDA(e, cudaFuncSetAttribute(col2im_rows_kernel<double, false>,
+                                              cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+      attr_dev_mask |= 1 << (e->device & 31);
+    }
+    const int blocks = (int)std::max<long long>(1, std::min<long long>(B, (long long)e->sm_count * 8));
+    const bool unit_w = stride_w == 1 && dil_w == 1;
+    if (dtype == B200_F32 && (C * kh * kw) % 4 == 0 && Wo * C * kh * kw <= 8 * 256 * 4 && (uintptr_t)col % 16 == 0) {
+      static int attr4_dev_mask = 0;
+      if (!(attr4_dev_mask & (1 << (e->device & 31)))) {
+        B200_CHECK_CUDA(e, cudaFuncSetAttribute(col2im_rows4_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                96 * 1024));
+        B200_CHECK_CUDA(e, cudaFuncSetAttribute(col2im_rows4_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                96 * 1024));
+        attr4_dev_mask |= 1 << (e->device & 31);
+      }
+      if (unit_w)
+        col2im_rows4_kernel<true><<<blocks, 256, staged, e->stream>>>((const float *)col, (float *)im, B, (int)C, (int)H,
+                                                                     (int)W, (int)Ho, (int)Wo, kh, kw, pad_h, pad_w,
+                                                                     stride_w, dil_w);
+      else
+        col2im_rows4_kernel<false><<<blocks, 256, staged, e->stream>>>((const float *)col, (float *)im, B, (int)C,
+                                                                      (int)H, (int)W, (int)Ho, (int)Wo, kh, kw, pad_h,
+                                                                      pad_w, stride_w, dil_w);
+      B200_CHECK_LAUNCH(e, "col2im_rows4_kernel");
+      return B200_OK;
+    }
+#define B200_C2I(T, U)                                                                                          \
+  col2im_rows_kernel<T, U><<<blocks, 256, staged, e->stream>>>((const T *)col, (T *)im, B, (int)C, (int)H, (int)W, \
+                                                               (int)Ho, (int)Wo, kh, kw, pad_h, pad_w, stride_w, dil_w)
+    if (dtype == B200_F32) {
+      if (unit_w) B200_C2I(float, true); else B200_C2I(float, false);
+    } else {
+      if (unit_w) B200_C2I(double, true); else B200_C2I(double, false);
+    }
+#undef B200_C2I
+    B200_CHECK_LAUNCH(e, "col2im_rows_kernel");
+    return B200_OK;
+  }
   if (dtype == B200_F32)
     col2im_kernel<float><<<grid_for(e, total), 256, 0, e->stream>>>((const float *)col, (float *)im, B, (int)C, (int)H,
                                                                    (int)W, (int)Ho, (int)Wo, kh, kw, pad_h, pad_w,

@@ -403,10 +403,51 @@ __global__ void __launch_bounds__(256) softmax_bwd_strided_kernel(const T *__res
   }
 }
 
+// Rows of at most 16 elements (the 10-class heads of the configs): a warp takes 32 rows at a time,
+// loads their 32 * len values of y and grad with consecutive lanes on consecutive addresses, lets
+// each lane work through one row out of shared memory, and stores the 32 * len results the same
+// coalesced way. A warp-per-row walk would leave 22 of 32 lanes idle on a 10-element row.
+template <typename T, bool LOG>
+__global__ void __launch_bounds__(128) softmax_bwd_short_kernel(const T *__restrict__ y, const T *__restrict__ g,
+                                                                T *__restrict__ dx, long long rows, int len) {
+  __shared__ T sy[4][32 * 16 + 1], sg[4][32 * 16 + 1];
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const long long warp0 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+  const long long groups = (rows + 31) / 32;
+  for (long long grp = warp0; grp < groups; grp += nwarps) {
+    const long long r0 = grp * 32;
+    const int nrows = (int)min((long long)32, rows - r0);
+    const int n = nrows * len;
+    const long long base = r0 * len;
+    for (int i = lane; i < n; i += 32) {
+      sy[w][i] = y[base + i];
+      sg[w][i] = g[base + i];
+    }
+    __syncwarp();
+    if (lane < nrows) {
+      T *yp = &sy[w][lane * len], *gp = &sg[w][lane * len];
+      double s = 0.0;
+      for (int k = 0; k < len; ++k) s += LOG ? (double)gp[k] : (double)gp[k] * (double)yp[k];
+      for (int k = 0; k < len; ++k) {
+        const double yy = yp[k], gg = gp[k];
+        gp[k] = (T)(LOG ? gg - exp(yy) * s : yy * (gg - s));
+      }
+    }
+    __syncwarp();
+    for (int i = lane; i < n; i += 32) dx[base + i] = sg[w][i];
+    __syncwarp();
+  }
+}
+
 template <typename T, bool LOG>
 static int launch_softmax_bwd(b200_engine *e, const T *y, const T *g, T *dx, long long outer, long long len,
                               long long inner) {
-  if (inner == 1) {
+  if (inner == 1 && len <= 16) {
+    const long long groups = (outer + 31) / 32;
+    const long long blocks = std::max<long long>(1, std::min<long long>((groups + 3) / 4, (long long)e->sm_count * 16));
+    softmax_bwd_short_kernel<T, LOG><<<(int)blocks, 128, 0, e->stream>>>(y, g, dx, outer, (int)len);
+  } else if (inner == 1) {
     const long long blocks = std::max<long long>(1, std::min<long long>((outer + 7) / 8, (long long)e->sm_count * 16));
     softmax_bwd_rows_kernel<T, LOG><<<(int)blocks, 256, 0, e->stream>>>(y, g, dx, outer, len);
   } else {
