@@ -110,6 +110,7 @@ __global__ void __launch_bounds__(CV_THREADS, 1)
   __shared__ __align__(8) uint64_t full_bar[MAX_STAGES], empty_bar[MAX_STAGES], acc_full[2], acc_empty[2];
   __shared__ uint32_t tmem_base_s;
   __shared__ int s_fail;
+  __shared__ float bias_s[8][BN / 2];
 
   unsigned char *smem = reinterpret_cast<unsigned char *>(((uintptr_t)cv_smem_raw + 1023) & ~(uintptr_t)1023);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -217,6 +218,8 @@ __global__ void __launch_bounds__(CV_THREADS, 1)
     const int quarter = warp & 3;           // TMEM lanes 32*quarter .. +31
     const int half = (warp - 2) >> 2;       // which half of the BN columns
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    const bool has_bias = p.ep.bias_kind != B200_BIAS_NONE;
+    const float *bias_g = reinterpret_cast<const float *>(p.ep.bias);
     int use = 0;
     bool ok = true;
     for (long long tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
@@ -249,6 +252,8 @@ __global__ void __launch_bounds__(CV_THREADS, 1)
       }
       if (!ok) break;
       const long long m = (long long)mt * CV_BM + quarter * 32 + lane;
+      const int n0 = nt * BN + half * HALF;
+      float *yb = nullptr;
       if (m < p.Mtot) {
         long long b;
         int pix;
@@ -260,14 +265,18 @@ __global__ void __launch_bounds__(CV_THREADS, 1)
           b = m / p.hw;
           pix = (int)(m % p.hw);
         }
-        float *yb = p.y + (b * p.K) * (long long)p.hw + pix;
-        const int n0 = nt * BN + half * HALF;
-#pragma unroll
-        for (int j = 0; j < HALF; ++j) {
-          const int n = n0 + j;
-          if (n < p.K) yb[(long long)n * p.hw] = apply_epilogue<float>(acc[j], p.ep, n, 0);
-        }
+        yb = p.y + (b * p.K + n0) * (long long)p.hw + pix;
       }
+      // this warp's biases, staged once per tile (lane l holds channels l and l + 32)
+      if (has_bias) {
+        __syncwarp();
+#pragma unroll
+        for (int j = lane; j < HALF; j += 32) bias_s[warp - 2][j] = n0 + j < p.K ? bias_g[n0 + j] : 0.f;
+        __syncwarp();
+      }
+      if (yb)
+        store_channels<HALF>(acc, yb, p.hw, p.K - n0, has_bias ? bias_s[warp - 2] : nullptr, p.ep.act,
+                             (float)p.ep.alpha);
     }
     if (!ok) s_fail = 1;
   } else {
