@@ -466,8 +466,158 @@ __global__ void __launch_bounds__(256) col2im_rows4_kernel(const float *__restri
   }
 }
 
+// ---- BatchNormOp (op_nn.go:1346-1640) on (B, C, S) -------------------------------------------------
+// Three launches. (1) partial sums of x and x^2 per (channel, group of samples) in double; (2) one
+// thread per channel folds the groups in a fixed order and makes everything that is per channel:
+// saveMean = sum / n rounded to the tensor's type, saveVar = sum (x - saveMean)^2 (from the two sums:
+// sum x^2 - 2 m sum x + n m^2, in double), the running statistics, alpha = 1 / sqrt(var + eps) and
+// beta = -mean * alpha in the tensor's type as the reference computes them; (3) y = x * alpha + beta,
+// a product then a sum, plane by plane so that no element pays an index division. The reference sums
+// sequentially in the tensor's type; the double sums here are closer to the exact value.
+constexpr int BN_GROUPS = 64;
+
+template <typename T>
+__global__ void __launch_bounds__(256) bn_partial_kernel(const T *__restrict__ x, long long B, int C, long long S,
+                                                         double *__restrict__ part) {
+  const int c = blockIdx.x, grp = blockIdx.y;
+  const long long per = (B + BN_GROUPS - 1) / BN_GROUPS;
+  const long long b0 = grp * per, b1 = min(B, b0 + per);
+  double s1 = 0.0, s2 = 0.0;
+  if (S >= 32) {
+    for (long long b = b0; b < b1; ++b) {
+      const T *p = x + (b * C + c) * S;
+      for (long long d = threadIdx.x; d < S; d += blockDim.x) {
+        const double v = p[d];
+        s1 += v;
+        s2 += v * v;
+      }
+    }
+  } else {  // short planes (a matrix has S = 1): threads spread over (sample, position) pairs
+    for (long long i = b0 * S + threadIdx.x; i < b1 * S; i += blockDim.x) {
+      const long long b = i / S, d = i - b * S;
+      const double v = x[(b * C + c) * S + d];
+      s1 += v;
+      s2 += v * v;
+    }
+  }
+  __shared__ double sh1[8], sh2[8];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+    s2 += __shfl_xor_sync(0xffffffffu, s2, o);
+  }
+  if ((threadIdx.x & 31) == 0) {
+    sh1[threadIdx.x >> 5] = s1;
+    sh2[threadIdx.x >> 5] = s2;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double a = 0.0, b2 = 0.0;
+    for (int w = 0; w < 8; ++w) {
+      a += sh1[w];
+      b2 += sh2[w];
+    }
+    part[((long long)c * BN_GROUPS + grp) * 2] = a;
+    part[((long long)c * BN_GROUPS + grp) * 2 + 1] = b2;
+  }
+}
+
+template <typename T>
+__global__ void bn_finish_kernel(const double *__restrict__ part, int C, long long n, int training, T momentum, T eps,
+                                 T *__restrict__ running_mean, T *__restrict__ running_var, T *__restrict__ save_mean,
+                                 T *__restrict__ save_var, T *__restrict__ alpha_beta) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  T mean, inv;
+  if (training) {
+    double s1 = 0.0, s2 = 0.0;
+    for (int gq = 0; gq < BN_GROUPS; ++gq) {
+      s1 += part[((long long)c * BN_GROUPS + gq) * 2];
+      s2 += part[((long long)c * BN_GROUPS + gq) * 2 + 1];
+    }
+    const T m = (T)(s1 / (double)n);
+    const double md = (double)m;
+    double vd = s2 - 2.0 * md * s1 + (double)n * md * md;
+    if (vd < 0.0) vd = 0.0;
+    const T v = (T)vd;
+    save_mean[c] = m;
+    save_var[c] = v;
+    running_mean[c] = momentum * m + (T(1) - momentum) * running_mean[c];
+    running_var[c] = momentum * (v / (T)(n - 1)) + (T(1) - momentum) * running_var[c];
+    mean = m;
+    inv = T(1) / sqrt(v / (T)n + eps);
+  } else {
+    mean = running_mean[c];
+    inv = T(1) / sqrt(running_var[c] + eps);
+  }
+  alpha_beta[2 * c] = inv;
+  alpha_beta[2 * c + 1] = -mean * inv;
+}
+
+__device__ __forceinline__ float bn_mul(float a, float b) { return __fmul_rn(a, b); }
+__device__ __forceinline__ double bn_mul(double a, double b) { return __dmul_rn(a, b); }
+__device__ __forceinline__ float bn_add(float a, float b) { return __fadd_rn(a, b); }
+__device__ __forceinline__ double bn_add(double a, double b) { return __dadd_rn(a, b); }
+
+// GROUP threads (a warp or a whole block) walk one (sample, channel) plane at a time
+template <typename T, int GROUP>
+__global__ void __launch_bounds__(256) bn_apply_kernel(const T *__restrict__ x, T *__restrict__ y, long long planes,
+                                                       int C, long long S, const T *__restrict__ alpha_beta) {
+  const long long group0 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) / GROUP;
+  const long long ngroups = ((long long)gridDim.x * blockDim.x) / GROUP;
+  const int lane = threadIdx.x % GROUP;
+  for (long long pl = group0; pl < planes; pl += ngroups) {
+    const int c = (int)(pl % C);
+    const T a = alpha_beta[2 * c], b = alpha_beta[2 * c + 1];
+    const T *xp = x + pl * S;
+    T *yp = y + pl * S;
+    for (long long d = lane; d < S; d += GROUP) yp[d] = bn_add(bn_mul(xp[d], a), b);
+  }
+}
+
 static int grid_for(b200_engine *e, long long work) {
   return (int)std::max<long long>(1, std::min<long long>((work + 255) / 256, (long long)e->sm_count * 16));
+}
+
+template <typename T>
+static int batchnorm_fwd_t(b200_engine *e, const T *x, T *y, long long B, int C, long long S, int training,
+                           double momentum, double eps, T *running_mean, T *running_var, T *save_mean, T *save_var) {
+  void *part = nullptr, *ab = nullptr;
+  int rc = b200_get(e, (long long)C * BN_GROUPS * 2 * sizeof(double), &part);
+  if (rc == B200_OK) rc = b200_get(e, (long long)C * 2 * sizeof(T), &ab);
+  if (rc != B200_OK) {
+    if (part) b200_put(e, part, 0);
+    return rc;
+  }
+  auto done = [&](int r) {
+    b200_put(e, part, 0);
+    b200_put(e, ab, 0);
+    return r;
+  };
+  if (training) {
+    bn_partial_kernel<T><<<dim3(C, BN_GROUPS), 256, 0, e->stream>>>(x, B, C, S, (double *)part);
+    cudaError_t le = cudaGetLastError();
+    if (le != cudaSuccess) return done(set_error(e, B200_ERR_CUDA, "bn_partial_kernel: %s", cudaGetErrorString(le)));
+    e->launches++;
+  }
+  bn_finish_kernel<T><<<(C + 127) / 128, 128, 0, e->stream>>>((const double *)part, C, B * S, training, (T)momentum,
+                                                              (T)eps, running_mean, running_var, save_mean, save_var,
+                                                              (T *)ab);
+  cudaError_t le = cudaGetLastError();
+  if (le != cudaSuccess) return done(set_error(e, B200_ERR_CUDA, "bn_finish_kernel: %s", cudaGetErrorString(le)));
+  e->launches++;
+  const long long planes = B * C;
+  if (S >= 2048) {
+    const int blocks = (int)std::max<long long>(1, std::min<long long>(planes, (long long)e->sm_count * 16));
+    bn_apply_kernel<T, 256><<<blocks, 256, 0, e->stream>>>(x, y, planes, C, S, (const T *)ab);
+  } else {
+    const int blocks = (int)std::max<long long>(1, std::min<long long>((planes + 7) / 8, (long long)e->sm_count * 16));
+    bn_apply_kernel<T, 32><<<blocks, 256, 0, e->stream>>>(x, y, planes, C, S, (const T *)ab);
+  }
+  le = cudaGetLastError();
+  if (le != cudaSuccess) return done(set_error(e, B200_ERR_CUDA, "bn_apply_kernel: %s", cudaGetErrorString(le)));
+  e->launches++;
+  return done(B200_OK);
 }
 
 }  // namespace b200
@@ -523,6 +673,28 @@ int b200_maxpool2d_fwd(b200_engine *e, int dtype, const void *x, void *y, int64_
                                                                      oh0, ow0);
   B200_CHECK_LAUNCH(e, "maxpool_kernel");
   return B200_OK;
+}
+
+int b200_batchnorm_fwd(b200_engine *e, int dtype, const void *x, void *y, int64_t B, int64_t C, int64_t S, int training,
+                       double momentum, double epsilon, void *running_mean, void *running_var, void *save_mean,
+                       void *save_var) {
+  if (!e) return B200_ERR_INVALID;
+  std::lock_guard<std::recursive_mutex> lk(e->mu);
+  B200_REQUIRE(e, dtype == B200_F32 || dtype == B200_F64, "b200_batchnorm_fwd: dtype %d not supported", dtype);
+  B200_REQUIRE(e, B >= 0 && C > 0 && S > 0 && C < (1LL << 30), "b200_batchnorm_fwd: bad shape");
+  if (B == 0) return B200_OK;
+  B200_REQUIRE(e, x && y && running_mean && running_var, "b200_batchnorm_fwd: null pointer");
+  B200_REQUIRE(e, !training || (save_mean && save_var), "b200_batchnorm_fwd: training needs save_mean and save_var");
+  B200_REQUIRE(e, !training || B * S > 1, "b200_batchnorm_fwd: training needs more than one value per channel");
+  DeviceGuard g(e);
+  int rc = flush_pending(e);
+  if (rc != B200_OK) return rc;
+  if (dtype == B200_F32)
+    return batchnorm_fwd_t<float>(e, (const float *)x, (float *)y, B, (int)C, S, training, momentum, epsilon,
+                                  (float *)running_mean, (float *)running_var, (float *)save_mean, (float *)save_var);
+  return batchnorm_fwd_t<double>(e, (const double *)x, (double *)y, B, (int)C, S, training, momentum, epsilon,
+                                 (double *)running_mean, (double *)running_var, (double *)save_mean,
+                                 (double *)save_var);
 }
 
 int b200_maxpool2d_bwd(b200_engine *e, int dtype, const void *dy, const int64_t *mask, void *dx, int64_t B, int64_t C,

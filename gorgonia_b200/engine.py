@@ -432,6 +432,18 @@ class Engine:
                                      stride[1]), self.h)
         return prealloc
 
+    def BatchNorm(self, x, prealloc, running_mean, running_var, save_mean=None, save_var=None, training=True,
+                  momentum=0.9, epsilon=1e-5):
+        """BatchNormOp on (B, C, ...): normalisation only; scale and bias are separate broadcast ops."""
+        B, Cc = x.shape[0], x.shape[1]
+        S = 1
+        for d in x.shape[2:]:
+            S *= d
+        check(lib.b200_batchnorm_fwd(self.h, dtype_code(x.dtype), x.ptr, prealloc.ptr, B, Cc, S, int(training),
+                                     momentum, epsilon, running_mean.ptr, running_var.ptr,
+                                     save_mean.ptr if save_mean else None, save_var.ptr if save_var else None), self.h)
+        return prealloc
+
     def MaxPool2DDiff(self, grad, mask, prealloc, kernel, pad, stride):
         """maxPoolDiffOp: prealloc (B,C,H,W) = gradient of the pool input; mask as MaxPool2D wrote it."""
         B, Cc, H, W = prealloc.shape

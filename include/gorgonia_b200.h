@@ -386,6 +386,17 @@ int b200_im2col(b200_engine *e, int dtype, const void *x, void *col, int64_t B, 
  *   (outer, len, inner): dx = y * (g - sum(g * y)), or for log-softmax dx = g - exp(y) * sum(g).
  * Incr-mode matrix product (the "+=" of matMulDiff, operatorLinAlg.go:104-179, which the reference
  * emulates as product-then-add, execution.go:115-126): b200_gemm with b200_epilogue.accumulate = 1. */
+/* b200_batchnorm_fwd: BatchNormOp.Do (op_nn.go:1158-1640) on x viewed as (B, C, S), S = product of the
+ *   spatial extents (1 for a matrix). The reference has a cuDNN CUDADoer for it only in ops/nn
+ *   (ops/nn/batchnorm_cuda.go); this is the cuDNN-free one. training != 0: per-channel saveMean = mean(x),
+ *   saveVar = sum (x - mean)^2, running = momentum * new + (1 - momentum) * running with the unbiased
+ *   variance saveVar / (n - 1), y = (x - mean) / sqrt(saveVar / n + epsilon). training == 0:
+ *   y = (x - running_mean) / sqrt(running_var + epsilon). Output as x * alpha + beta (a product, then
+ *   a sum, as the reference rounds it). Scale and bias are separate graph ops (nn.go:430-436), i.e.
+ *   b200_binary_bcast calls. All four statistics vectors are device arrays of C elements. */
+int b200_batchnorm_fwd(b200_engine *e, int dtype, const void *x, void *y, int64_t B, int64_t C,
+                       int64_t S, int training, double momentum, double epsilon, void *running_mean,
+                       void *running_var, void *save_mean, void *save_var);
 int b200_maxpool2d_bwd(b200_engine *e, int dtype, const void *dy, const int64_t *mask, void *dx,
                        int64_t B, int64_t C, int64_t H, int64_t W, int kh, int kw, int pad_north,
                        int pad_south, int pad_west, int pad_east, int explicit_padding, int stride_h,

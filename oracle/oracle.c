@@ -465,6 +465,51 @@ ORACLE_COL2IM(oracle_col2im_f64, double)
 ORACLE_SOFTMAX_BWD(oracle_softmax_bwd_f32, float, double, exp)
 ORACLE_SOFTMAX_BWD(oracle_softmax_bwd_f64, double, long double, expl)
 
+/* BatchNormOp.f32s / f64s with updateStats and calculateAlphaAndBeta (op_nn.go:1346-1640), input
+ * (B, C, S) with S = the spatial size (1 for a matrix). Training: per channel, saveMean = sum / n
+ * and saveVar = sum (x - mean)^2, both accumulated in the tensor's own type in (sample, position)
+ * order; running = momentum * new + (1 - momentum) * running with the unbiased variance
+ * saveVar / (n - 1); alpha = 1 / sqrt(saveVar / n + eps). Inference: alpha = 1 / sqrt(runningVar
+ * + eps), mean = runningMean. Output = x * alpha + beta with beta = -mean * alpha, a product then a
+ * sum. Scale and bias are separate graph ops (nn.go:430-436) and not part of this. */
+#define ORACLE_BATCHNORM(NAME, T, SQRT)                                                                   \
+  void NAME(const T *x, T *y, int64_t B, int64_t C, int64_t S, int training, double momentum_, double eps_, \
+            T *running_mean, T *running_var, T *save_mean, T *save_var) {                                 \
+    const T momentum = (T)momentum_, eps = (T)eps_;                                                       \
+    const int64_t n = B * S;                                                                              \
+    _Pragma("omp parallel for schedule(static)") for (int64_t c = 0; c < C; ++c) {                       \
+      T mean, inv;                                                                                        \
+      if (training) {                                                                                     \
+        T m = 0, v = 0;                                                                                   \
+        for (int64_t s = 0; s < B; ++s)                                                                   \
+          for (int64_t d = 0; d < S; ++d) m += x[(s * C + c) * S + d];                                    \
+        m /= (T)n;                                                                                        \
+        for (int64_t s = 0; s < B; ++s)                                                                   \
+          for (int64_t d = 0; d < S; ++d) {                                                               \
+            const T xv = x[(s * C + c) * S + d];                                                          \
+            v += (xv - m) * (xv - m);                                                                     \
+          }                                                                                               \
+        save_mean[c] = m;                                                                                 \
+        save_var[c] = v;                                                                                  \
+        running_mean[c] = momentum * m + ((T)1 - momentum) * running_mean[c];                             \
+        running_var[c] = momentum * (v / (T)(n - 1)) + ((T)1 - momentum) * running_var[c];                \
+        mean = m;                                                                                         \
+        inv = (T)1 / SQRT(v / (T)n + eps);                                                                \
+      } else {                                                                                            \
+        mean = running_mean[c];                                                                           \
+        inv = (T)1 / SQRT(running_var[c] + eps);                                                          \
+      }                                                                                                   \
+      const T beta = -mean * inv;                                                                         \
+      for (int64_t s = 0; s < B; ++s)                                                                     \
+        for (int64_t d = 0; d < S; ++d) {                                                                 \
+          const T p = x[(s * C + c) * S + d] * inv;                                                       \
+          y[(s * C + c) * S + d] = p + beta;                                                              \
+        }                                                                                                 \
+    }                                                                                                     \
+  }
+ORACLE_BATCHNORM(oracle_batchnorm_f32, float, sqrtf)
+ORACLE_BATCHNORM(oracle_batchnorm_f64, double, sqrt)
+
 /* softmaxOp.Do -> tensor.SoftMax / LogSoftMax along `axis` of a tensor viewed as
  * (outer, len, inner) (op_softmax.go:99-128). exp(x - max) / sum, evaluated in double. */
 void oracle_softmax_f32(const float *x, float *y, int64_t outer, int64_t len, int64_t inner, int is_log) {

@@ -197,6 +197,21 @@ def softmax_bwd(y, grad, axis=-1, log=False):
     return dx
 
 
+def batchnorm(x, running_mean, running_var, training=True, momentum=0.9, eps=1e-5):
+    """BatchNormOp on (B, C, ...) -> (y, save_mean, save_var); running_mean / running_var are
+    updated in place when training."""
+    x = np.ascontiguousarray(x)
+    B, Cc = x.shape[0], x.shape[1]
+    S = int(np.prod(x.shape[2:], dtype=np.int64)) if x.ndim > 2 else 1
+    y = np.empty_like(x)
+    sm, sv = np.zeros(Cc, x.dtype), np.zeros(Cc, x.dtype)
+    assert running_mean.dtype == x.dtype and running_var.dtype == x.dtype
+    getattr(_lib, "oracle_batchnorm_" + _sfx(x.dtype))(_p(x), _p(y), _i64(B), _i64(Cc), _i64(S), int(training),
+                                                       C.c_double(momentum), C.c_double(eps), _p(running_mean),
+                                                       _p(running_var), _p(sm), _p(sv))
+    return y, sm, sv
+
+
 def _oli(shape, axis):
     outer_ = int(np.prod(shape[:axis], dtype=np.int64))
     inner = int(np.prod(shape[axis + 1:], dtype=np.int64))

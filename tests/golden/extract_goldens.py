@@ -16,6 +16,7 @@ is the record of where every number came from.
   leakyrelu.json       TestLeakyRelu                       nn_test.go
   byindices.json       TestByIndicesOpDo                   op_by_indices_test.go
   broadcast_add.json   broadcastAddTests                   operations_broadcast_test.go
+  batchnorm.json       bnAllCases                          nn_amd64_test.go
 """
 import json
 import os
@@ -249,6 +250,48 @@ def extract_broadcast(root):
                       "operand is repeated)", "cases": cases}
 
 
+def extract_batchnorm(root):
+    """bnAllCases (nn_amd64_test.go:8-...): input / scale / bias initialisers and, after ONE training run from
+    running mean 0 and running variance 1, the running statistics and the output of
+    ((BatchNorm(x) * scale + bias) reshaped to (B, F)) x fcWeight^T, fcWeight (B, F) filled by ScaleInit."""
+    src = strip_comments(open(os.path.join(root, "nn_amd64_test.go")).read())
+    table = src[src.index("}{", src.index("var bnAllCases")) + 1:]
+
+    def init(expr):
+        expr = expr.strip()
+        m = re.match(r"RangedFromWithStep\((" + NUM + r")\s*,\s*(" + NUM + r")\)", expr)
+        if m:
+            return {"kind": "ranged", "start": float(m.group(1)), "step": float(m.group(2))}
+        if expr.startswith("Ones()"):
+            return {"kind": "ones"}
+        if expr.startswith("Zeroes()"):
+            return {"kind": "zeroes"}
+        m = re.match(r"\[\]float(?:32|64)\{([^}]*)\}", expr)
+        if m:
+            return {"kind": "literal", "data": numbers(m.group(1))}
+        raise ValueError("cannot parse initialiser: " + expr[:60])
+
+    cases = []
+    for blk in top_level_blocks(table):
+        if "ExpectedTrainResult" not in blk:
+            continue
+        def arr(name):
+            return numbers(field(blk, name, r"\[\]float(?:32|64)\{([^}]*)\}"))
+        cases.append({
+            "desc": field(blk, "desc", r'"([^"]*)"'),
+            "dtype": "float32" if "tensor.Float32" in field(blk, "Dtype", r"(tensor\.Float\d+)") else "float64",
+            "x": init(field(blk, "X", r"((?:RangedFromWithStep\([^)]*\))|(?:\[\]float(?:32|64)\{[^}]*\}))")),
+            "x_shape": [int(v) for v in numbers(field(blk, "XShape", r"tensor\.Shape\{([^}]*)\}"))],
+            "scale": init(field(blk, "ScaleInit", r"((?:RangedFromWithStep\([^)]*\))|(?:Ones\(\))|(?:Zeroes\(\)))")),
+            "bias": init(field(blk, "BiasInit", r"((?:RangedFromWithStep\([^)]*\))|(?:Ones\(\))|(?:Zeroes\(\)))")),
+            "train_result": arr("ExpectedTrainResult"),
+            "running_mean": arr("ExpectedMean"),
+            "running_var": arr("ExpectedVariance"),
+        })
+    return {"source": "nn_amd64_test.go: bnAllCases, checked there with dawson.AllClose (nn_test.go:319-440); momentum 0.9, "
+                      "epsilon 1e-5", "cases": cases}
+
+
 def main():
     if len(sys.argv) != 2:
         raise SystemExit("usage: extract_goldens.py <path to a gorgonia checkout>")
@@ -262,6 +305,7 @@ def main():
         "leakyrelu.json": extract_leakyrelu(root),
         "byindices.json": extract_byindices(root),
         "broadcast_add.json": extract_broadcast(root),
+        "batchnorm.json": extract_batchnorm(root),
     }
     for name, doc in out.items():
         with open(os.path.join(HERE, name), "w") as f:

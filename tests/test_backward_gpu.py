@@ -153,3 +153,55 @@ def test_matmul_incr_float64(fresh):
     c = e.tensor(c0)
     e.MatMul(e.tensor(a), e.tensor(b), c, incr=True)
     assert np.abs(c.numpy() - (c0 + a @ b)).max() <= 1e-12
+
+
+# ---- BatchNormOp (the cuDNN-free forward) -----------------------------------------------------
+
+from tests import golden_util as G  # noqa: E402
+from tests.test_oracle_golden import bn_case_arrays  # noqa: E402
+
+
+@pytest.mark.parametrize("case", G.load("batchnorm.json")["cases"], ids=lambda c: c["desc"] + " " + c["dtype"])
+def test_batchnorm_goldens(fresh, case):
+    # nn_test.go:319-440 / nn_amd64_test.go: one training run from running mean 0, running variance 1
+    e = fresh
+    dt, x, scale, bias, fc = bn_case_arrays(case)
+    Cc = x.shape[1]
+    rm, rv = e.tensor(np.zeros(Cc, dt)), e.tensor(np.ones(Cc, dt))
+    sm, sv = e.empty((Cc,), dt), e.empty((Cc,), dt)
+    y = e.empty(x.shape, dt)
+    e.BatchNorm(e.tensor(x), y, rm, rv, sm, sv, training=True, momentum=0.9, epsilon=1e-5)
+    tol = 1e-5 if dt == np.float32 else 1e-9
+    assert np.allclose(rm.numpy(), np.asarray(case["running_mean"], dt), rtol=tol, atol=tol)
+    assert np.allclose(rv.numpy(), np.asarray(case["running_var"], dt), rtol=tol, atol=tol)
+    out = ((y.numpy() * scale).astype(dt) + bias).astype(dt).reshape(x.shape[0], -1) @ fc.T
+    assert np.allclose(out, np.asarray(case["train_result"], dt).reshape(out.shape), rtol=10 * tol, atol=10 * tol)
+
+
+@pytest.mark.parametrize("dt", [np.float32, np.float64])
+@pytest.mark.parametrize("shape", [(64, 10), (300, 625), (8, 3, 5, 7), (16, 32, 14, 14), (2, 4, 64, 64), (70, 1, 3, 3)])
+def test_batchnorm_training_and_inference(fresh, shape, dt):
+    # statistics: 2e-6 (float32) / 1e-12 (float64) of their magnitude: the reference sums sequentially
+    # in the tensor's type, the device in double; output: the pointwise tolerance on the scale of the
+    # largest |y|; inference (given statistics, no sums) is bit-exact
+    e = fresh
+    x = (util.normal(81, shape, dt) * dt(1.7) + dt(0.3)).astype(dt)
+    Cc = shape[1]
+    rm0, rv0 = util.normal(82, Cc, dt), (np.abs(util.normal(83, Cc, dt)) + dt(0.5)).astype(dt)
+    rm_o, rv_o = rm0.copy(), rv0.copy()
+    want, sm_o, sv_o = oracle.batchnorm(x, rm_o, rv_o, training=True, momentum=0.9, eps=1e-5)
+    rm, rv = e.tensor(rm0), e.tensor(rv0)
+    sm, sv, y = e.empty((Cc,), dt), e.empty((Cc,), dt), e.empty(shape, dt)
+    tx = e.tensor(x)
+    e.BatchNorm(tx, y, rm, rv, sm, sv, training=True, momentum=0.9, epsilon=1e-5)
+    st = 2e-6 if dt == np.float32 else 1e-12
+    for got, ref in ((sm.numpy(), sm_o), (sv.numpy(), sv_o), (rm.numpy(), rm_o), (rv.numpy(), rv_o)):
+        assert np.abs(got.astype(np.float64) - ref).max() <= st * max(1.0, np.abs(ref).max()) * (10 if ref is sv_o else 1)
+    lim = (1e-5 if dt == np.float32 else 1e-11) * max(1.0, float(np.abs(want).max()))
+    assert np.abs(y.numpy().astype(np.float64) - want).max() <= lim
+    # inference with the statistics the oracle ended with: no sums involved, bit-exact
+    rm2, rv2 = e.tensor(rm_o), e.tensor(rv_o)
+    e.BatchNorm(tx, y, rm2, rv2, training=False, momentum=0.9, epsilon=1e-5)
+    want_inf, _, _ = oracle.batchnorm(x, rm_o.copy(), rv_o.copy(), training=False, momentum=0.9, eps=1e-5)
+    assert_bits_equal(y.numpy(), want_inf)
+    assert_bits_equal(rm2.numpy(), rm_o)       # untouched

@@ -156,3 +156,46 @@ def test_oracle_softmax_bwd_matches_finite_differences(log):
             xm[i, j] -= h
             want[i, j] = ((oracle.softmax(xp, -1, log) - oracle.softmax(xm, -1, log)) * gr).sum() / (2 * h)
     assert np.abs(got - want).max() < 1e-8
+
+
+# ---- BatchNormOp: the ten cases of bnAllCases ----------------------------------------------------
+
+def _bn_init(spec, n, dt):
+    if spec["kind"] == "ranged":      # RangedFromWithStep (weights.go:56-120): repeated addition in the tensor's type
+        out, st, inc = np.empty(n, dt), dt(spec["start"]), dt(spec["step"])
+        for i in range(n):
+            out[i] = st
+            st = dt(st + inc)
+        return out
+    if spec["kind"] == "ones":
+        return np.ones(n, dt)
+    if spec["kind"] == "zeroes":
+        return np.zeros(n, dt)
+    return np.asarray(spec["data"], dtype=dt)
+
+
+def bn_case_arrays(case):
+    dt = np.float32 if case["dtype"] == "float32" else np.float64
+    shape = tuple(case["x_shape"])
+    n = int(np.prod(shape))
+    x = _bn_init(case["x"], n, dt).reshape(shape)
+    bshape = (1, shape[1]) + (1,) * (len(shape) - 2)
+    scale = _bn_init(case["scale"], shape[1], dt).reshape(bshape)
+    bias = _bn_init(case["bias"], shape[1], dt).reshape(bshape)
+    fc = _bn_init(case["scale"], n, dt).reshape(shape[0], n // shape[0])
+    return dt, x, scale, bias, fc
+
+
+@pytest.mark.parametrize("case", G.load("batchnorm.json")["cases"], ids=lambda c: c["desc"] + " " + c["dtype"])
+def test_oracle_batchnorm_goldens(case):
+    # nn_test.go:319-440: one training run from running mean 0 / running variance 1; the test reads the
+    # running statistics and ((BatchNorm(x) * scale + bias) as (B, F)) x fcWeight^T
+    dt, x, scale, bias, fc = bn_case_arrays(case)
+    rm, rv = np.zeros(x.shape[1], dt), np.ones(x.shape[1], dt)
+    y, _, _ = oracle.batchnorm(x, rm, rv, training=True, momentum=0.9, eps=1e-5)
+    tol = 1e-5 if dt == np.float32 else 1e-9
+    assert np.allclose(rm, np.asarray(case["running_mean"], dt), rtol=tol, atol=tol)
+    assert np.allclose(rv, np.asarray(case["running_var"], dt), rtol=tol, atol=tol)
+    out = ((y * scale).astype(dt) + bias).astype(dt).reshape(x.shape[0], -1) @ fc.T
+    want = np.asarray(case["train_result"], dt).reshape(out.shape)
+    assert np.allclose(out, want, rtol=10 * tol, atol=10 * tol)
