@@ -357,7 +357,8 @@ def wl_gemm(ctx, args, main):
 # backward ops (max-pool gradient, col2im, softmax derivative, Incr-mode MatMul)
 # ------------------------------------------------------------------------------------------
 
-BACKWARD_SHAPES = {"pool": (2048, 32, 28, 28), "col2im": (1024, 32, 14, 14), "softmax": (1 << 22, 10)}
+BACKWARD_SHAPES = {"pool": (2048, 32, 28, 28), "col2im": (1024, 32, 14, 14), "softmax": (1 << 22, 10),
+                   "batchnorm": (2048, 64, 14, 14)}
 
 
 def wl_backward(ctx, args, main):
@@ -397,6 +398,17 @@ def wl_backward(ctx, args, main):
     per_op["softmax_bwd"] = by / s_ / 1e9
     total_bytes += by; total_s += s_; launches += l_
     e.ResetAllocator()
+    # BatchNorm, training mode: x is read twice (the statistics must exist before the first output), y written
+    B, Cc, H, W = BACKWARD_SHAPES["batchnorm"]
+    xb = e.tensor(g.standard_normal((B, Cc, H, W), dtype=np.float32))
+    yb = e.empty((B, Cc, H, W))
+    rm, rv = e.tensor(np.zeros(Cc, np.float32)), e.tensor(np.ones(Cc, np.float32))
+    sm, sv = e.empty((Cc,)), e.empty((Cc,))
+    s_, l_ = ctx.timed(lambda: e.BatchNorm(xb, yb, rm, rv, sm, sv), steps, warmup)
+    by = B * Cc * H * W * 12
+    per_op["batchnorm_train"] = by / s_ / 1e9
+    total_bytes += by; total_s += s_; launches += l_
+    e.ResetAllocator()
     # Incr-mode MatMul, 4096^3
     n = 4096
     a = e.tensor((g.standard_normal((n, n), dtype=np.float32) * np.float32(0.02)))
@@ -415,7 +427,7 @@ def wl_backward(ctx, args, main):
             "gpu_launches": launches, "clocks": clocks, "steps": steps, "warmup": warmup,
             "per_op_gbs": {k: round(v, 1) for k, v in per_op.items()},
             "matmul_incr_4096_tflops": 2.0 * n ** 3 / s_ / 1e12,
-            "roofline": {"bound": "hbm", "kernel": "maxpool_bwd_kernel + col2im_kernel + softmax_bwd_rows_kernel",
+            "roofline": {"bound": "hbm", "kernel": "maxpool2x2_bwd_kernel + col2im_rows4_kernel + softmax_bwd_short_kernel + bn_*_kernel",
                          "achieved": gbs, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": gbs / pk["hbm_gbs"],
                          "peak_source": pk["source"], "traffic": None}}
 
@@ -557,7 +569,7 @@ def cpu_gemm(steps=1, n=1024):
 
 
 def cpu_backward(steps=1):
-    """The oracle's maxpool gradient, col2im and softmax derivative on 1/16 of the GPU leg's batches."""
+    """The oracle's maxpool gradient, col2im, softmax derivative and batch-norm on 1/16 of the GPU leg's batches."""
     from oracle import oracle
     g = np.random.Generator(np.random.Philox(17))
     B, Cc, H, W = BACKWARD_SHAPES["pool"]
@@ -570,13 +582,17 @@ def cpu_backward(steps=1):
     R, L = BACKWARD_SHAPES["softmax"]
     R //= 16
     ys, gr = g.random((R, L), dtype=np.float32), g.standard_normal((R, L), dtype=np.float32)
+    B3, C3, H3, W3 = BACKWARD_SHAPES["batchnorm"]
+    B3 //= 16
+    xb = g.standard_normal((B3, C3, H3, W3), dtype=np.float32)
     by = (B * Cc * (H // 2) * (W // 2) * 12 + B * Cc * H * W * 4 + B2 * H2 * W2 * C2 * 9 * 4 + B2 * C2 * H2 * W2 * 4 +
-          R * L * 12)
+          R * L * 12 + B3 * C3 * H3 * W3 * 12)
     t0 = time.perf_counter()
     for _ in range(steps):
         oracle.maxpool2d_bwd(y, mask, x.shape)
         oracle.col2im(col, (B2, C2, H2, W2), 3, 3, (1, 1))
         oracle.softmax_bwd(ys, gr)
+        oracle.batchnorm(xb, np.zeros(C3, np.float32), np.ones(C3, np.float32))
     dt = (time.perf_counter() - t0) / steps
     return {"value": by / dt / 1e9, "unit": "GB/s", "cores": oracle.threads(), "kind": "port",
             "sample": f"{steps} pass(es) over 1/16 of the GPU leg's batches", "ms_per_step": dt * 1e3}

@@ -483,7 +483,18 @@ __global__ void __launch_bounds__(256) bn_partial_kernel(const T *__restrict__ x
   const long long per = (B + BN_GROUPS - 1) / BN_GROUPS;
   const long long b0 = grp * per, b1 = min(B, b0 + per);
   double s1 = 0.0, s2 = 0.0;
-  if (S >= 32) {
+  if (sizeof(T) == 4 && S % 4 == 0 && (uintptr_t)x % 16 == 0 && (b1 - b0) * (S >> 2) < (1LL << 31)) {
+    // float planes as float4; the threads spread over (sample, float4) pairs so that short planes
+    // keep the whole block busy
+    const uint32_t S4 = (uint32_t)(S >> 2), total4 = (uint32_t)(b1 > b0 ? (b1 - b0) * S4 : 0);
+    for (uint32_t i = threadIdx.x; i < total4; i += blockDim.x) {
+      const uint32_t bb = i / S4, d = i - bb * S4;
+      const float4 q = __ldg(reinterpret_cast<const float4 *>(x + ((b0 + bb) * C + c) * S) + d);
+      const double v0 = q.x, v1 = q.y, v2 = q.z, v3 = q.w;
+      s1 += (v0 + v1) + (v2 + v3);
+      s2 += (v0 * v0 + v1 * v1) + (v2 * v2 + v3 * v3);
+    }
+  } else if (S >= 32) {
     for (long long b = b0; b < b1; ++b) {
       const T *p = x + (b * C + c) * S;
       for (long long d = threadIdx.x; d < S; d += blockDim.x) {
@@ -562,7 +573,8 @@ __device__ __forceinline__ double bn_add(double a, double b) { return __dadd_rn(
 // GROUP threads (a warp or a whole block) walk one (sample, channel) plane at a time
 template <typename T, int GROUP>
 __global__ void __launch_bounds__(256) bn_apply_kernel(const T *__restrict__ x, T *__restrict__ y, long long planes,
-                                                       int C, long long S, const T *__restrict__ alpha_beta) {
+                                                       int C, long long S, const T *__restrict__ alpha_beta,
+                                                       bool vec4) {
   const long long group0 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) / GROUP;
   const long long ngroups = ((long long)gridDim.x * blockDim.x) / GROUP;
   const int lane = threadIdx.x % GROUP;
@@ -571,7 +583,21 @@ __global__ void __launch_bounds__(256) bn_apply_kernel(const T *__restrict__ x, 
     const T a = alpha_beta[2 * c], b = alpha_beta[2 * c + 1];
     const T *xp = x + pl * S;
     T *yp = y + pl * S;
-    for (long long d = lane; d < S; d += GROUP) yp[d] = bn_add(bn_mul(xp[d], a), b);
+    if (sizeof(T) == 4 && vec4) {  // S % 4 == 0 and both tensors 16-byte aligned: float4 in, float4 out
+      const float4 *x4 = reinterpret_cast<const float4 *>(xp);
+      float4 *y4 = reinterpret_cast<float4 *>(yp);
+      const float fa = (float)a, fb = (float)b;
+      for (long long d = lane; d < (S >> 2); d += GROUP) {
+        float4 q = __ldg(x4 + d);
+        q.x = __fadd_rn(__fmul_rn(q.x, fa), fb);
+        q.y = __fadd_rn(__fmul_rn(q.y, fa), fb);
+        q.z = __fadd_rn(__fmul_rn(q.z, fa), fb);
+        q.w = __fadd_rn(__fmul_rn(q.w, fa), fb);
+        y4[d] = q;
+      }
+    } else {
+      for (long long d = lane; d < S; d += GROUP) yp[d] = bn_add(bn_mul(xp[d], a), b);
+    }
   }
 }
 
@@ -607,12 +633,13 @@ static int batchnorm_fwd_t(b200_engine *e, const T *x, T *y, long long B, int C,
   if (le != cudaSuccess) return done(set_error(e, B200_ERR_CUDA, "bn_finish_kernel: %s", cudaGetErrorString(le)));
   e->launches++;
   const long long planes = B * C;
+  const bool vec4 = S % 4 == 0 && ((uintptr_t)x | (uintptr_t)y) % 16 == 0;
   if (S >= 2048) {
     const int blocks = (int)std::max<long long>(1, std::min<long long>(planes, (long long)e->sm_count * 16));
-    bn_apply_kernel<T, 256><<<blocks, 256, 0, e->stream>>>(x, y, planes, C, S, (const T *)ab);
+    bn_apply_kernel<T, 256><<<blocks, 256, 0, e->stream>>>(x, y, planes, C, S, (const T *)ab, vec4);
   } else {
     const int blocks = (int)std::max<long long>(1, std::min<long long>((planes + 7) / 8, (long long)e->sm_count * 16));
-    bn_apply_kernel<T, 32><<<blocks, 256, 0, e->stream>>>(x, y, planes, C, S, (const T *)ab);
+    bn_apply_kernel<T, 32><<<blocks, 256, 0, e->stream>>>(x, y, planes, C, S, (const T *)ab, vec4);
   }
   le = cudaGetLastError();
   if (le != cudaSuccess) return done(set_error(e, B200_ERR_CUDA, "bn_apply_kernel: %s", cudaGetErrorString(le)));
