@@ -157,6 +157,7 @@ _SIGS = {
     "b200_conv2d_path": (_i, [_vp, _i, _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _i, _i, _i, _i, _i]),
     "b200_im2col": (_i, [_vp, _i, _vp, _vp, _i64, _i64, _i64, _i64, _i, _i, _i, _i, _i, _i, _i, _i]),
     "b200_batchnorm_fwd": (_i, [_vp, _i, _vp, _vp, _i64, _i64, _i64, _i, C.c_double, C.c_double, _vp, _vp, _vp, _vp]),
+    "b200_batchnorm_bwd": (_i, [_vp, _i, _vp, _vp, _vp, _i64, _i64, _i64, _i, C.c_double, _vp, _vp, _vp]),
     "b200_maxpool2d_bwd": (_i, [_vp, _i, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i, _i, _i, _i, _i, _i, _i, _i, _i]),
     "b200_col2im": (_i, [_vp, _i, _vp, _vp, _i64, _i64, _i64, _i64, _i, _i, _i, _i, _i, _i, _i, _i]),
     "b200_softmax_bwd": (_i, [_vp, _i, _vp, _vp, _vp, _i64, _i64, _i64, _i]),

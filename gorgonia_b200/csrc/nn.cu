@@ -601,6 +601,97 @@ __global__ void __launch_bounds__(256) bn_apply_kernel(const T *__restrict__ x, 
   }
 }
 
+// ---- batchnormDiffOp (op_nn.go:1727-1940): the input gradient of BatchNormOp --------------------
+// Same three-launch shape as the forward op: partial sums of dy and x*dy per (channel, sample group)
+// in double; one thread per channel folds them into gradMean = sum dy / n, dotp = sum (x - mean) dy,
+// k = dotp * invstd^2 / n in the tensor's type; the output pass then evaluates the reference's
+// expression, including its order of subtractions, which differs between the matrix and the
+// spatial branch, and its choice of variance in inference mode.
+template <typename T>
+__global__ void __launch_bounds__(256) bn_bwd_partial_kernel(const T *__restrict__ x, const T *__restrict__ dy,
+                                                             long long B, int C, long long S,
+                                                             double *__restrict__ part) {
+  const int c = blockIdx.x, grp = blockIdx.y;
+  const long long per = (B + BN_GROUPS - 1) / BN_GROUPS;
+  const long long b0 = grp * per, b1 = min(B, b0 + per);
+  double s1 = 0.0, s2 = 0.0;
+  for (long long i = b0 * S + threadIdx.x; i < b1 * S; i += blockDim.x) {
+    const long long b = i / S, d = i - b * S;
+    const long long at = (b * C + c) * S + d;
+    const double g = dy[at];
+    s1 += g;
+    s2 += (double)x[at] * g;
+  }
+  __shared__ double sh1[8], sh2[8];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+    s2 += __shfl_xor_sync(0xffffffffu, s2, o);
+  }
+  if ((threadIdx.x & 31) == 0) {
+    sh1[threadIdx.x >> 5] = s1;
+    sh2[threadIdx.x >> 5] = s2;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double a = 0.0, b2 = 0.0;
+    for (int w = 0; w < 8; ++w) {
+      a += sh1[w];
+      b2 += sh2[w];
+    }
+    part[((long long)c * BN_GROUPS + grp) * 2] = a;
+    part[((long long)c * BN_GROUPS + grp) * 2 + 1] = b2;
+  }
+}
+
+template <typename T>
+__global__ void bn_bwd_finish_kernel(const double *__restrict__ part, int C, long long n, long long S, int training,
+                                     T eps, const T *__restrict__ running_var, const T *__restrict__ save_mean,
+                                     const T *__restrict__ save_var, T *__restrict__ coef) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  double s1 = 0.0, s2 = 0.0;
+  for (int gq = 0; gq < BN_GROUPS; ++gq) {
+    s1 += part[((long long)c * BN_GROUPS + gq) * 2];
+    s2 += part[((long long)c * BN_GROUPS + gq) * 2 + 1];
+  }
+  const T mean = save_mean[c];
+  const T sum = (T)s1, dotp = (T)(s2 - (double)mean * s1);
+  T invstd = T(1) / sqrt(save_var[c] / (T)n + eps);
+  if (!training && S == 1) invstd = T(1) / sqrt(running_var[c] + eps);
+  coef[4 * c] = mean;
+  coef[4 * c + 1] = (T)(dotp * invstd * invstd) / (T)n;  // k
+  coef[4 * c + 2] = sum / (T)n;                          // gradMean
+  coef[4 * c + 3] = invstd;
+}
+
+__device__ __forceinline__ float bn_sub(float a, float b) { return __fsub_rn(a, b); }
+__device__ __forceinline__ double bn_sub(double a, double b) { return __dsub_rn(a, b); }
+
+template <typename T>
+__global__ void __launch_bounds__(256) bn_bwd_apply_kernel(const T *__restrict__ x, const T *__restrict__ dy,
+                                                           T *__restrict__ dx, long long planes, int C, long long S,
+                                                           int training, const T *__restrict__ coef) {
+  const long long warp0 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  for (long long pl = warp0; pl < planes; pl += nwarps) {
+    const int c = (int)(pl % C);
+    const T mean = coef[4 * c], k = coef[4 * c + 1], gm = coef[4 * c + 2], inv = coef[4 * c + 3];
+    const T *xp = x + pl * S, *gp = dy + pl * S;
+    T *op = dx + pl * S;
+    for (long long d = lane; d < S; d += 32) {
+      if (!training) {
+        op[d] = bn_mul(gp[d], inv);
+      } else {
+        const T t = bn_mul(bn_sub(xp[d], mean), k);
+        const T u = S == 1 ? bn_sub(bn_sub(gp[d], t), gm) : bn_sub(bn_sub(gp[d], gm), t);
+        op[d] = bn_mul(u, inv);
+      }
+    }
+  }
+}
+
 static int grid_for(b200_engine *e, long long work) {
   return (int)std::max<long long>(1, std::min<long long>((work + 255) / 256, (long long)e->sm_count * 16));
 }
@@ -643,6 +734,39 @@ static int batchnorm_fwd_t(b200_engine *e, const T *x, T *y, long long B, int C,
   }
   le = cudaGetLastError();
   if (le != cudaSuccess) return done(set_error(e, B200_ERR_CUDA, "bn_apply_kernel: %s", cudaGetErrorString(le)));
+  e->launches++;
+  return done(B200_OK);
+}
+
+template <typename T>
+static int batchnorm_bwd_t(b200_engine *e, const T *x, const T *dy, T *dx, long long B, int C, long long S,
+                           int training, double eps, const T *running_var, const T *save_mean, const T *save_var) {
+  void *part = nullptr, *coef = nullptr;
+  int rc = b200_get(e, (long long)C * BN_GROUPS * 2 * sizeof(double), &part);
+  if (rc == B200_OK) rc = b200_get(e, (long long)C * 4 * sizeof(T), &coef);
+  if (rc != B200_OK) {
+    if (part) b200_put(e, part, 0);
+    return rc;
+  }
+  auto done = [&](int r) {
+    b200_put(e, part, 0);
+    b200_put(e, coef, 0);
+    return r;
+  };
+  bn_bwd_partial_kernel<T><<<dim3(C, BN_GROUPS), 256, 0, e->stream>>>(x, dy, B, C, S, (double *)part);
+  cudaError_t le = cudaGetLastError();
+  if (le != cudaSuccess) return done(set_error(e, B200_ERR_CUDA, "bn_bwd_partial_kernel: %s", cudaGetErrorString(le)));
+  e->launches++;
+  bn_bwd_finish_kernel<T><<<(C + 127) / 128, 128, 0, e->stream>>>((const double *)part, C, B * S, S, training, (T)eps,
+                                                                  running_var, save_mean, save_var, (T *)coef);
+  le = cudaGetLastError();
+  if (le != cudaSuccess) return done(set_error(e, B200_ERR_CUDA, "bn_bwd_finish_kernel: %s", cudaGetErrorString(le)));
+  e->launches++;
+  const long long planes = B * C;
+  const int blocks = (int)std::max<long long>(1, std::min<long long>((planes + 7) / 8, (long long)e->sm_count * 16));
+  bn_bwd_apply_kernel<T><<<blocks, 256, 0, e->stream>>>(x, dy, dx, planes, C, S, training, (const T *)coef);
+  le = cudaGetLastError();
+  if (le != cudaSuccess) return done(set_error(e, B200_ERR_CUDA, "bn_bwd_apply_kernel: %s", cudaGetErrorString(le)));
   e->launches++;
   return done(B200_OK);
 }
@@ -722,6 +846,25 @@ int b200_batchnorm_fwd(b200_engine *e, int dtype, const void *x, void *y, int64_
   return batchnorm_fwd_t<double>(e, (const double *)x, (double *)y, B, (int)C, S, training, momentum, epsilon,
                                  (double *)running_mean, (double *)running_var, (double *)save_mean,
                                  (double *)save_var);
+}
+
+int b200_batchnorm_bwd(b200_engine *e, int dtype, const void *x, const void *dy, void *dx, int64_t B, int64_t C,
+                       int64_t S, int training, double epsilon, const void *running_var, const void *save_mean,
+                       const void *save_var) {
+  if (!e) return B200_ERR_INVALID;
+  std::lock_guard<std::recursive_mutex> lk(e->mu);
+  B200_REQUIRE(e, dtype == B200_F32 || dtype == B200_F64, "b200_batchnorm_bwd: dtype %d not supported", dtype);
+  B200_REQUIRE(e, B >= 0 && C > 0 && S > 0 && C < (1LL << 30), "b200_batchnorm_bwd: bad shape");
+  if (B == 0) return B200_OK;
+  B200_REQUIRE(e, x && dy && dx && running_var && save_mean && save_var, "b200_batchnorm_bwd: null pointer");
+  DeviceGuard g(e);
+  int rc = flush_pending(e);
+  if (rc != B200_OK) return rc;
+  if (dtype == B200_F32)
+    return batchnorm_bwd_t<float>(e, (const float *)x, (const float *)dy, (float *)dx, B, (int)C, S, training, epsilon,
+                                  (const float *)running_var, (const float *)save_mean, (const float *)save_var);
+  return batchnorm_bwd_t<double>(e, (const double *)x, (const double *)dy, (double *)dx, B, (int)C, S, training, epsilon,
+                                 (const double *)running_var, (const double *)save_mean, (const double *)save_var);
 }
 
 int b200_maxpool2d_bwd(b200_engine *e, int dtype, const void *dy, const int64_t *mask, void *dx, int64_t B, int64_t C,

@@ -444,6 +444,16 @@ class Engine:
                                      save_mean.ptr if save_mean else None, save_var.ptr if save_var else None), self.h)
         return prealloc
 
+    def BatchNormDiff(self, x, grad, prealloc, running_var, save_mean, save_var, training=True, epsilon=1e-5):
+        """batchnormDiffOp: the gradient with respect to the BatchNorm input."""
+        B, Cc = x.shape[0], x.shape[1]
+        S = 1
+        for d in x.shape[2:]:
+            S *= d
+        check(lib.b200_batchnorm_bwd(self.h, dtype_code(x.dtype), x.ptr, grad.ptr, prealloc.ptr, B, Cc, S,
+                                     int(training), epsilon, running_var.ptr, save_mean.ptr, save_var.ptr), self.h)
+        return prealloc
+
     def MaxPool2DDiff(self, grad, mask, prealloc, kernel, pad, stride):
         """maxPoolDiffOp: prealloc (B,C,H,W) = gradient of the pool input; mask as MaxPool2D wrote it."""
         B, Cc, H, W = prealloc.shape

@@ -397,6 +397,14 @@ int b200_im2col(b200_engine *e, int dtype, const void *x, void *col, int64_t B, 
 int b200_batchnorm_fwd(b200_engine *e, int dtype, const void *x, void *y, int64_t B, int64_t C,
                        int64_t S, int training, double momentum, double epsilon, void *running_mean,
                        void *running_var, void *save_mean, void *save_var);
+/* b200_batchnorm_bwd: batchnormDiffOp (op_nn.go:1727-1940): the gradient with respect to the
+ *   BatchNormOp input from x, dy and the statistics the forward call saved. training != 0:
+ *   dx = (dy - mean(dy) - (x - mean) * k) / std with k = sum((x - mean) dy) / (n * var_eps);
+ *   training == 0: dx = dy / std. The reference's two branches (matrix, spatial) differ in the order of
+ *   the subtractions and in which variance the inference case reads; both are reproduced. */
+int b200_batchnorm_bwd(b200_engine *e, int dtype, const void *x, const void *dy, void *dx, int64_t B,
+                       int64_t C, int64_t S, int training, double epsilon, const void *running_var,
+                       const void *save_mean, const void *save_var);
 int b200_maxpool2d_bwd(b200_engine *e, int dtype, const void *dy, const int64_t *mask, void *dx,
                        int64_t B, int64_t C, int64_t H, int64_t W, int kh, int kw, int pad_north,
                        int pad_south, int pad_west, int pad_east, int explicit_padding, int stride_h,

@@ -510,6 +510,47 @@ ORACLE_SOFTMAX_BWD(oracle_softmax_bwd_f64, double, long double, expl)
 ORACLE_BATCHNORM(oracle_batchnorm_f32, float, sqrtf)
 ORACLE_BATCHNORM(oracle_batchnorm_f64, double, sqrt)
 
+/* batchnormDiffOp.f32s / f64s (op_nn.go:1727-1940): the input gradient of BatchNormOp. Per channel,
+ * sum = sum dy and dotp = sum (x - mean) dy accumulated in the tensor's type in (sample, position)
+ * order; invstd = 1 / sqrt(saveVar / n + eps); k = dotp * invstd^2 / n; gradMean = sum / n;
+ *   training:  dx = (dy - gradMean - (x - mean) * k) * invstd     (S > 1)
+ *              dx = (dy - (x - mean) * k - gradMean) * invstd     (S = 1: the matrix branch subtracts in
+ *                                                                  the other order)
+ *   inference: dx = dy * invstd, invstd from the saved variance when S > 1 and from the running
+ *              variance when S = 1, as the two branches of the reference have it. */
+#define ORACLE_BATCHNORM_BWD(NAME, T, SQRT)                                                               \
+  void NAME(const T *x, const T *dy, T *dx, int64_t B, int64_t C, int64_t S, int training, double eps_,   \
+            const T *running_var, const T *save_mean, const T *save_var) {                                \
+    const T eps = (T)eps_;                                                                                \
+    const int64_t n = B * S;                                                                              \
+    _Pragma("omp parallel for schedule(static)") for (int64_t c = 0; c < C; ++c) {                       \
+      T sum = 0, dotp = 0;                                                                                \
+      const T mean = save_mean[c];                                                                        \
+      for (int64_t s = 0; s < B; ++s)                                                                     \
+        for (int64_t d = 0; d < S; ++d) {                                                                 \
+          const int64_t i = (s * C + c) * S + d;                                                          \
+          sum += dy[i];                                                                                   \
+          dotp += S == 1 ? (x[i] - mean) * dy[i] : (x[i] * dy[i] - mean * dy[i]);                         \
+        }                                                                                                 \
+      T invstd = (T)1 / SQRT(save_var[c] / (T)n + eps);                                                   \
+      if (!training && S == 1) invstd = (T)1 / SQRT(running_var[c] + eps);                                \
+      const T k = (T)(dotp * invstd * invstd) / (T)n;                                                     \
+      const T grad_mean = sum / (T)n;                                                                     \
+      for (int64_t s = 0; s < B; ++s)                                                                     \
+        for (int64_t d = 0; d < S; ++d) {                                                                 \
+          const int64_t i = (s * C + c) * S + d;                                                          \
+          if (!training) {                                                                                \
+            dx[i] = dy[i] * invstd;                                                                       \
+          } else {                                                                                        \
+            const T t = (x[i] - mean) * k;                                                                \
+            dx[i] = S == 1 ? (dy[i] - t - grad_mean) * invstd : (dy[i] - grad_mean - t) * invstd;         \
+          }                                                                                               \
+        }                                                                                                 \
+    }                                                                                                     \
+  }
+ORACLE_BATCHNORM_BWD(oracle_batchnorm_bwd_f32, float, sqrtf)
+ORACLE_BATCHNORM_BWD(oracle_batchnorm_bwd_f64, double, sqrt)
+
 /* softmaxOp.Do -> tensor.SoftMax / LogSoftMax along `axis` of a tensor viewed as
  * (outer, len, inner) (op_softmax.go:99-128). exp(x - max) / sum, evaluated in double. */
 void oracle_softmax_f32(const float *x, float *y, int64_t outer, int64_t len, int64_t inner, int is_log) {

@@ -212,6 +212,19 @@ def batchnorm(x, running_mean, running_var, training=True, momentum=0.9, eps=1e-
     return y, sm, sv
 
 
+def batchnorm_bwd(x, dy, running_var, save_mean, save_var, training=True, eps=1e-5):
+    """batchnormDiffOp: the gradient with respect to the BatchNormOp input."""
+    x = np.ascontiguousarray(x)
+    dy = np.ascontiguousarray(dy, dtype=x.dtype)
+    B, Cc = x.shape[0], x.shape[1]
+    S = int(np.prod(x.shape[2:], dtype=np.int64)) if x.ndim > 2 else 1
+    dx = np.empty_like(x)
+    getattr(_lib, "oracle_batchnorm_bwd_" + _sfx(x.dtype))(_p(x), _p(dy), _p(dx), _i64(B), _i64(Cc), _i64(S),
+                                                           int(training), C.c_double(eps), _p(running_var),
+                                                           _p(save_mean), _p(save_var))
+    return dx
+
+
 def _oli(shape, axis):
     outer_ = int(np.prod(shape[:axis], dtype=np.int64))
     inner = int(np.prod(shape[axis + 1:], dtype=np.int64))

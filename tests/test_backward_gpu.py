@@ -205,3 +205,25 @@ def test_batchnorm_training_and_inference(fresh, shape, dt):
     want_inf, _, _ = oracle.batchnorm(x, rm_o.copy(), rv_o.copy(), training=False, momentum=0.9, eps=1e-5)
     assert_bits_equal(y.numpy(), want_inf)
     assert_bits_equal(rm2.numpy(), rm_o)       # untouched
+
+
+@pytest.mark.parametrize("training", [True, False])
+@pytest.mark.parametrize("dt", [np.float32, np.float64])
+@pytest.mark.parametrize("shape", [(64, 10), (300, 33), (8, 3, 5, 7), (16, 32, 14, 14), (70, 1, 3, 3)])
+def test_batchnorm_bwd(fresh, shape, dt, training):
+    # tolerance: 1e-5 (float32) / 1e-11 (float64) of the largest |dx|: sums in double on the device,
+    # sequential in the tensor's type in the reference; inference mode is a product per element
+    e = fresh
+    x = (util.normal(84, shape, dt) * dt(1.3) + dt(0.2)).astype(dt)
+    dy = util.normal(85, shape, dt)
+    Cc = shape[1]
+    rm, rv = np.zeros(Cc, dt), np.ones(Cc, dt)
+    _, sm, sv = oracle.batchnorm(x, rm, rv, training=True)
+    want = oracle.batchnorm_bwd(x, dy, rv, sm, sv, training=training)
+    dx = e.empty(shape, dt)
+    e.BatchNormDiff(e.tensor(x), e.tensor(dy), dx, e.tensor(rv), e.tensor(sm), e.tensor(sv), training=training)
+    if not training:
+        assert_bits_equal(dx.numpy(), want)
+    else:
+        lim = (1e-5 if dt == np.float32 else 1e-11) * max(1.0, float(np.abs(want).max()))
+        assert np.abs(dx.numpy().astype(np.float64) - want).max() <= lim
