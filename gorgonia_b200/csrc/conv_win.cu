@@ -15,8 +15,8 @@
 //
 // Accumulation as in the other tensor-core kernels: hi*hi in one TMEM accumulator, the two cross
 // terms in a second, chains cut every 256 k and folded in fp32 registers by the epilogue warps.
-// Warp roles (11 warps): 0 window producer, 1 MMA issuer + TMEM owner, 2-9 epilogue (4 lane
-// quarters x 2 tile halves), 10 filter producer. No multicast, no clusters; every wait is bounded.
+// Warp roles (12 warps): 0 window producer, 1 and 11 MMA issuers (left / right tile half; 1 owns
+// tensor memory), 2-9 epilogue (4 lane quarters x 2 tile halves), 10 filter producer. No multicast, no clusters; every wait is bounded.
 #include <cuda.h>
 #include <cuda_runtime.h>
 
@@ -34,7 +34,8 @@ namespace b200 {
 int conv_filters_tap_major(b200_engine *e, const float *w, int K, int C, int taps, TcOperand *wf, void **blk);
 int conv_nhwc_split(b200_engine *e, const float *x, long long B, int C, int HW, void **xs);
 
-constexpr int CW_THREADS = 352;  // 11 warps
+constexpr int CW_THREADS = 384;  // 12 warps
+constexpr int CW_ISSUERS = 2;    // one MMA-issuing warp per tile half
 constexpr int CW_TILE = 16;      // output tile edge
 constexpr int CW_WIN_STAGES = 2;
 constexpr int CW_MAX_BSTAGES = 12;
@@ -107,14 +108,14 @@ __global__ void __launch_bounds__(CW_THREADS, 1)
   if (threadIdx.x == 0) {
     for (int s = 0; s < CW_WIN_STAGES; ++s) {
       ptx::mbar_init(&win_full[s], 1);
-      ptx::mbar_init(&win_empty[s], 1);
+      ptx::mbar_init(&win_empty[s], CW_ISSUERS);
     }
     for (int s = 0; s < b_stages; ++s) {
       ptx::mbar_init(&b_full[s], 1);
-      ptx::mbar_init(&b_empty[s], 1);
+      ptx::mbar_init(&b_empty[s], CW_ISSUERS);
     }
     for (int b = 0; b < 2; ++b) {
-      ptx::mbar_init(&acc_full[b], 1);
+      ptx::mbar_init(&acc_full[b], CW_ISSUERS);
       ptx::mbar_init(&acc_empty[b], 8);  // one arrival per epilogue warp
     }
     ptx::fence_mbar_init();
@@ -194,10 +195,15 @@ __global__ void __launch_bounds__(CW_THREADS, 1)
       }
       if (!ok) s_fail = 1;
     }
-  } else if (warp == 1) {
-    // ---------------- MMA issuer ----------------
+  } else if (warp == 1 || warp == 11) {
+    // ---------------- MMA issuers ----------------
+    // Two warps, one per 16 x 8 half of the tile: each waits on the same stages and issues only its
+    // half's instructions into its half's accumulators, and the stage / accumulator barriers count
+    // one arrival per issuer. An issuing thread spends about as long on an instruction as the
+    // tensor core does at these widths, so two of them keep it fed where one did not.
     // The whole warp runs the loops and votes on every wait, so that stage indices, addresses and
     // descriptors are warp-uniform values; one elected lane issues the tensor-core instructions.
+    const uint32_t mh = warp == 1 ? 0u : 1u;
     int ws = 0, bs = 0;
     uint32_t wphase = 0, bphase = 0;
     int use = 0;
@@ -234,24 +240,19 @@ __global__ void __launch_bounds__(CW_THREADS, 1)
             const uint32_t b_lo32 = desc_lo(sb);
             const uint32_t first = in_chain > 0 ? 1u : 0u;
             if (lane == 0) {
-              constexpr uint32_t AH = (8u * ROW_BYTES) >> 4;  // right half: 8 window rows further
+              const uint32_t ah = mh * ((8u * ROW_BYTES) >> 4);  // right half: 8 window rows further
+              const uint32_t d = d_base + mh * (2 * BN);
 #pragma unroll
               for (int kk = 0; kk < KK; ++kk) {
                 const uint64_t b_hi = desc_pack(b_lo32 + 2u * kk, b_hi32);
-                const uint64_t a_hi0 = desc_pack(a_lo32 + 2u * kk, a_hi32);
-                const uint64_t a_hi1 = desc_pack(a_lo32 + AH + 2u * kk, a_hi32);
-                const uint64_t a_lo0 = desc_pack(a_lo32_tail + 2u * kk, a_hi32);
-                const uint64_t a_lo1 = desc_pack(a_lo32_tail + AH + 2u * kk, a_hi32);
+                const uint64_t a_hi = desc_pack(a_lo32 + ah + 2u * kk, a_hi32);
+                const uint64_t a_lo = desc_pack(a_lo32_tail + ah + 2u * kk, a_hi32);
                 const uint32_t accumulate = kk > 0 ? 1u : first;
-                const uint32_t d0 = d_base, d1 = d_base + 2 * BN;
                 // head x [head | tail] of the filters is ONE instruction of width 2*BN: the filter
                 // tail slab follows the head slab in shared memory, the cross-term accumulator
-                // follows the main one in tensor memory. An instruction costs a fixed ~65 cycles
-                // on top of its arithmetic, so two instructions per k step beat three.
-                ptx::mma_tf32(d0, a_hi0, b_hi, IDESC2, accumulate);
-                ptx::mma_tf32(d1, a_hi1, b_hi, IDESC2, accumulate);
-                ptx::mma_tf32(d0 + BN, a_lo0, b_hi, IDESC, 1u);
-                ptx::mma_tf32(d1 + BN, a_lo1, b_hi, IDESC, 1u);
+                // follows the main one in tensor memory.
+                ptx::mma_tf32(d, a_hi, b_hi, IDESC2, accumulate);
+                ptx::mma_tf32(d + BN, a_lo, b_hi, IDESC, 1u);
               }
               ptx::mma_commit(&b_empty[bs]);
             }
