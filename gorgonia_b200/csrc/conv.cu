@@ -123,6 +123,21 @@ __global__ void __launch_bounds__(256) conv_direct_small_kernel(const float *__r
   }
 }
 
+// Two fp32 fused multiply-adds in one instruction (fma.rn.f32x2 on 64-bit register pairs): the
+// first-layer kernels are bound by instruction issue, and this halves their FMA count. Each lane of
+// the pair rounds exactly as fmaf does.
+__device__ __forceinline__ unsigned long long pack2(float lo, float hi) {
+  unsigned long long r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(unsigned long long v, float &lo, float &hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ void fma2(unsigned long long &d, unsigned long long a, unsigned long long b) {
+  asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(d) : "l"(a), "l"(b));
+}
+
 // The same first-layer case at its usual geometry: 3x3 window, pad 1, stride 1, no dilation, at
 // most 3 input channels, image width a multiple of 4. One thread computes FOUR neighbouring
 // outputs of a row for 16 filters at a time: the 6 inputs of a window row (one aligned float4 and
@@ -153,11 +168,11 @@ __global__ void __launch_bounds__(256, 2) conv3x3_first_kernel(const float *__re
     const float *xb = x + b * (long long)C * H * W + ow;
     float *yb = y + (b * K) * (long long)H * W + (long long)oh * W + ow;
     for (int k0 = 0; k0 < K; k0 += 16) {
-      float acc[4][16];
+      unsigned long long accp[4][8];  // filter pairs (k, k+1) packed for fma.rn.f32x2
 #pragma unroll
       for (int pz = 0; pz < 4; ++pz)
 #pragma unroll
-        for (int k = 0; k < 16; ++k) acc[pz][k] = 0.f;
+        for (int k = 0; k < 8; ++k) accp[pz][k] = 0ull;
 #pragma unroll 1
       for (int c = 0; c < C; ++c) {  // not unrolled: one channel's 18 inputs in registers at a time
 #pragma unroll
@@ -171,23 +186,30 @@ __global__ void __launch_bounds__(256, 2) conv3x3_first_kernel(const float *__re
             if (og > 0) in[0] = __ldg(row - 1);
             if (og < Wg - 1) in[5] = __ldg(row + 4);
           }
+          unsigned long long in2[6];
+#pragma unroll
+          for (int i = 0; i < 6; ++i) in2[i] = pack2(in[i], in[i]);
 #pragma unroll
           for (int sx = 0; sx < 3; ++sx) {
             const float *wq = &ws[(c * 9 + r * 3 + sx) * 32 + k0];
 #pragma unroll
             for (int k4 = 0; k4 < 16; k4 += 4) {
               const float4 wv = *reinterpret_cast<const float4 *>(wq + k4);
+              const unsigned long long w01 = pack2(wv.x, wv.y), w23 = pack2(wv.z, wv.w);
 #pragma unroll
               for (int pz = 0; pz < 4; ++pz) {
-                acc[pz][k4 + 0] = fmaf(in[pz + sx], wv.x, acc[pz][k4 + 0]);
-                acc[pz][k4 + 1] = fmaf(in[pz + sx], wv.y, acc[pz][k4 + 1]);
-                acc[pz][k4 + 2] = fmaf(in[pz + sx], wv.z, acc[pz][k4 + 2]);
-                acc[pz][k4 + 3] = fmaf(in[pz + sx], wv.w, acc[pz][k4 + 3]);
+                fma2(accp[pz][k4 / 2], in2[pz + sx], w01);
+                fma2(accp[pz][k4 / 2 + 1], in2[pz + sx], w23);
               }
             }
           }
         }
       }
+      float acc[4][16];
+#pragma unroll
+      for (int pz = 0; pz < 4; ++pz)
+#pragma unroll
+        for (int k = 0; k < 8; ++k) unpack2(accp[pz][k], acc[pz][2 * k], acc[pz][2 * k + 1]);
 #pragma unroll
       for (int k = 0; k < 16; ++k) {
         if (k0 + k < K) {
@@ -252,28 +274,29 @@ __global__ void __launch_bounds__(256, 2) conv3x3_first_pool_kernel(const float 
     const float *xb = x + b * (long long)C * H * W + ow;
     float *yb = y + (b * K) * (long long)Hq * Wq + (long long)ph * Wq + (ow >> 1);
     for (int k0 = 0; k0 < K; k0 += 8) {
-      float acc[2][4][8];
+      unsigned long long accp[2][4][4];  // filter pairs (k, k+1) packed
 #pragma unroll
       for (int rr = 0; rr < 2; ++rr)
 #pragma unroll
         for (int pz = 0; pz < 4; ++pz)
 #pragma unroll
-          for (int k = 0; k < 8; ++k) acc[rr][pz][k] = 0.f;
+          for (int k = 0; k < 4; ++k) accp[rr][pz][k] = 0ull;
 #pragma unroll 1
       for (int c = 0; c < C; ++c) {
-        float in[4][6];
+        unsigned long long in2[4][6];  // every input duplicated into both lanes of a pair
 #pragma unroll
         for (int r = 0; r < 4; ++r) {
           const int ih = oh - 1 + r;
-#pragma unroll
-          for (int i = 0; i < 6; ++i) in[r][i] = 0.f;
+          float in[6] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
           if ((unsigned)ih < (unsigned)H) {
             const float *row = xb + ((long long)c * H + ih) * W;
             const float4 mid = __ldg(reinterpret_cast<const float4 *>(row));
-            in[r][1] = mid.x; in[r][2] = mid.y; in[r][3] = mid.z; in[r][4] = mid.w;
-            if (og > 0) in[r][0] = __ldg(row - 1);
-            if (og < Wg - 1) in[r][5] = __ldg(row + 4);
+            in[1] = mid.x; in[2] = mid.y; in[3] = mid.z; in[4] = mid.w;
+            if (og > 0) in[0] = __ldg(row - 1);
+            if (og < Wg - 1) in[5] = __ldg(row + 4);
           }
+#pragma unroll
+          for (int i = 0; i < 6; ++i) in2[r][i] = pack2(in[i], in[i]);
         }
 #pragma unroll
         for (int r = 0; r < 3; ++r) {
@@ -282,16 +305,24 @@ __global__ void __launch_bounds__(256, 2) conv3x3_first_pool_kernel(const float 
             const float *wq = &ws[(c * 9 + r * 3 + sx) * 32 + k0];
             const float4 w0 = *reinterpret_cast<const float4 *>(wq);
             const float4 w1 = *reinterpret_cast<const float4 *>(wq + 4);
-            const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+            const unsigned long long wp[4] = {pack2(w0.x, w0.y), pack2(w0.z, w0.w), pack2(w1.x, w1.y),
+                                              pack2(w1.z, w1.w)};
 #pragma unroll
             for (int rr = 0; rr < 2; ++rr)
 #pragma unroll
               for (int pz = 0; pz < 4; ++pz)
 #pragma unroll
-                for (int k = 0; k < 8; ++k) acc[rr][pz][k] = fmaf(in[rr + r][pz + sx], wv[k], acc[rr][pz][k]);
+                for (int k = 0; k < 4; ++k) fma2(accp[rr][pz][k], in2[rr + r][pz + sx], wp[k]);
           }
         }
       }
+      float acc[2][4][8];
+#pragma unroll
+      for (int rr = 0; rr < 2; ++rr)
+#pragma unroll
+        for (int pz = 0; pz < 4; ++pz)
+#pragma unroll
+          for (int k = 0; k < 4; ++k) unpack2(accp[rr][pz][k], acc[rr][pz][2 * k], acc[rr][pz][2 * k + 1]);
 #pragma unroll
       for (int k = 0; k < 8; ++k) {
         if (k0 + k < K) {
