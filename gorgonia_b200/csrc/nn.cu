@@ -107,6 +107,35 @@ __global__ void __launch_bounds__(256) maxpool2x2_even_kernel(const float *__res
   }
 }
 
+// Any other 2x2 pooling without a mask (odd planes, stride 1, gorgonia's explicit padding): one
+// output per thread, the four window positions unrolled with their bounds checks, index arithmetic
+// in 32 bits (the caller checks that the element counts fit). Same comparison order as the general
+// kernel: row-major inside the clipped window, strict '>', starting from -FLT_MAX.
+__global__ void __launch_bounds__(256) maxpool2x2_any_kernel(const float *__restrict__ x, float *__restrict__ y,
+                                                             uint32_t planes, int H, int W, int Ho, int Wo, int sH,
+                                                             int sW, int oh0, int ow0) {
+  const uint32_t per = (uint32_t)Ho * Wo, total = planes * per, hw = (uint32_t)H * W;
+  const uint32_t stride = gridDim.x * blockDim.x;
+  for (uint32_t t = blockIdx.x * blockDim.x + threadIdx.x; t < total; t += stride) {
+    const uint32_t plane = t / per, r = t - plane * per;
+    const int ph = (int)(r / (uint32_t)Wo), pw = (int)(r - (uint32_t)ph * Wo);
+    const int h0 = ph * sH - oh0, w0 = pw * sW - ow0;
+    const float *in = x + (size_t)plane * hw;
+    float best = -FLT_MAX;
+#pragma unroll
+    for (int dh = 0; dh < 2; ++dh)
+#pragma unroll
+      for (int dw = 0; dw < 2; ++dw) {
+        const int hi = h0 + dh, wi = w0 + dw;
+        if ((unsigned)hi < (unsigned)H && (unsigned)wi < (unsigned)W) {
+          const float v = __ldg(in + hi * W + wi);
+          if (v > best) best = v;
+        }
+      }
+    y[t] = best;
+  }
+}
+
 // ---- im2col ------------------------------------------------------------------------------------
 // col[(b, oh, ow), (c, r, s)] = x[b, c, oh*sH - padH + r*dH, ow*sW - padW + s*dW], 0 outside.
 // One thread per column element; consecutive threads write consecutive (c, r, s), which makes
@@ -811,6 +840,13 @@ int b200_maxpool2d_fwd(b200_engine *e, int dtype, const void *x, void *y, int64_
     maxpool2x2_even_kernel<<<grid_for(e, total), 256, 0, e->stream>>>((const float *)x, (float *)y, B * C, (int)H,
                                                                      (int)W, (int)Ho, (int)Wo);
     B200_CHECK_LAUNCH(e, "maxpool2x2_even_kernel");
+    return B200_OK;
+  }
+  if (dtype == B200_F32 && !mask && kh == 2 && kw == 2 && total < (1LL << 31) && B * C * H * W < (1LL << 32)) {
+    maxpool2x2_any_kernel<<<grid_for(e, total), 256, 0, e->stream>>>((const float *)x, (float *)y, (uint32_t)(B * C),
+                                                                    (int)H, (int)W, (int)Ho, (int)Wo, stride_h,
+                                                                    stride_w, oh0, ow0);
+    B200_CHECK_LAUNCH(e, "maxpool2x2_any_kernel");
     return B200_OK;
   }
   if (dtype == B200_F32)
