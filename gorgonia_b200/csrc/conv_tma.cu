@@ -378,6 +378,50 @@ __global__ void __launch_bounds__(256) nhwc_split4_kernel(const float *__restric
   }
 }
 
+// The same rewrite for small planes of any size (7x7, 13x13): a block takes 32 channels of one
+// image, which are 32 * HW contiguous floats starting on a 16-byte boundary whatever HW is, loads
+// them as float4, and writes every position's 32 channels as float4. The shared-memory pitch is
+// HW rounded up to 1 (mod 8), which spreads the (position, channel group) reads over all banks.
+__global__ void __launch_bounds__(256) nhwc_split_img_kernel(const float *__restrict__ x, float *__restrict__ hi,
+                                                             float *__restrict__ lo, long long B, int C, int HW,
+                                                             int pitch) {
+  extern __shared__ __align__(16) float img[];
+  const int chunks = C >> 5;
+  const long long total = B * chunks;
+  const int n4 = (32 * HW) >> 2;
+  for (long long t = blockIdx.x; t < total; t += gridDim.x) {
+    const long long b = t / chunks;
+    const int c0 = (int)(t - b * chunks) << 5;
+    const float4 *src = reinterpret_cast<const float4 *>(x + (b * C + c0) * (long long)HW);
+    for (int i = threadIdx.x; i < n4; i += 256) {
+      const float4 v = __ldg(src + i);
+      const int e0 = i << 2;
+      const float vv[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {  // the four elements may straddle two channel rows
+        const int e = e0 + k, c = e / HW, pp = e - c * HW;
+        img[c * pitch + pp] = vv[k];
+      }
+    }
+    __syncthreads();
+    float *ho = hi + (b * HW) * (long long)C + c0;
+    float *lo_o = lo + (b * HW) * (long long)C + c0;
+    for (int i = threadIdx.x; i < HW * 8; i += 256) {
+      const int pp = i >> 3, cg = i & 7;
+      float h[4], l[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float v = img[(4 * cg + k) * pitch + pp];
+        h[k] = ct_tf32(v);
+        l[k] = ct_tf32(__fsub_rn(v, h[k]));
+      }
+      *reinterpret_cast<float4 *>(ho + (long long)pp * C + 4 * cg) = make_float4(h[0], h[1], h[2], h[3]);
+      *reinterpret_cast<float4 *>(lo_o + (long long)pp * C + 4 * cg) = make_float4(l[0], l[1], l[2], l[3]);
+    }
+    __syncthreads();
+  }
+}
+
 // Rewrites x (B, C, HW) as NHWC TF32 head/tail into two fresh arena blocks xs[0], xs[1], which the
 // caller releases.
 int conv_nhwc_split(b200_engine *e, const float *x, long long B, int C, int HW, void **xs) {
@@ -395,6 +439,16 @@ int conv_nhwc_split(b200_engine *e, const float *x, long long B, int C, int HW, 
     else
       nhwc_split4_kernel<16><<<blocks, 256, 0, e->stream>>>(x, (float *)xs[0], (float *)xs[1], B, C, HW);
     B200_CHECK_LAUNCH(e, "nhwc_split4_kernel");
+    return B200_OK;
+  }
+  if (C % 32 == 0 && HW <= 360 && (uintptr_t)x % 16 == 0) {  // 32 * pitch floats fit the default 48 KB
+    int pitch = HW;
+    while (pitch % 8 != 1) ++pitch;
+    const long long work = B * (C / 32);
+    const int blocks = (int)std::max<long long>(1, std::min<long long>(work, e->sm_count * 16LL));
+    nhwc_split_img_kernel<<<blocks, 256, (size_t)32 * pitch * 4, e->stream>>>(x, (float *)xs[0], (float *)xs[1], B, C,
+                                                                             HW, pitch);
+    B200_CHECK_LAUNCH(e, "nhwc_split_img_kernel");
     return B200_OK;
   }
   const long long tiles = B * ((HW + 31) / 32) * ((C + 31) / 32);
