@@ -154,6 +154,8 @@ _SIGS = {
                              _P(Epilogue)]),
     "b200_conv2d_maxpool_fwd": (_i, [_vp, _i, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _i, _i, _i, _i,
                                      _i, _P(Epilogue), _i, _i, _i, _i]),
+    "b200_conv2d_chain_fwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _i,
+                                   _i, _i, _i, _i, _P(Epilogue), _i]),
     "b200_conv2d_path": (_i, [_vp, _i, _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _i, _i, _i, _i, _i]),
     "b200_im2col": (_i, [_vp, _i, _vp, _vp, _i64, _i64, _i64, _i64, _i, _i, _i, _i, _i, _i, _i, _i]),
     "b200_batchnorm_fwd": (_i, [_vp, _i, _vp, _vp, _i64, _i64, _i64, _i, C.c_double, C.c_double, _vp, _vp, _vp, _vp]),

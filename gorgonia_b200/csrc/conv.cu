@@ -21,9 +21,11 @@ int conv2d_tc(b200_engine *e, const float *x, const float *w, float *y, long lon
               const Epilogue &ep);
 int conv2d_tma(b200_engine *e, const float *x, const float *w, float *y, long long B, int C, int H, int W, int K,
                int kh, int kw, int padH, int padW, int sH, int sW, int dH, int dW, int Ho, int Wo,
-               const Epilogue &ep);
+               const Epilogue &ep, const float *x_hi, const float *x_lo, float *y_hi, float *y_lo);
 int conv2d_win(b200_engine *e, const float *x, const float *w, float *y, long long B, int C, int H, int W, int K,
-               int kh, int kw, int padH, int padW, int dH, int dW, int Ho, int Wo, const Epilogue &ep, bool pool2);
+               int kh, int kw, int padH, int padW, int dH, int dW, int Ho, int Wo, const Epilogue &ep, bool pool2,
+               const float *x_hi, const float *x_lo, float *y_hi, float *y_lo);
+int conv_nhwc_split_into(b200_engine *e, const float *x, long long B, int C, int HW, float *hi, float *lo);
 bool conv_win_eligible(const b200_engine *e, long long B, int C, int H, int W, int K, int kh, int kw, int padH,
                        int padW, int sH, int sW, int dH, int dW, int Ho, int Wo);
 bool conv_tma_eligible(long long B, int C, int H, int W, int kh, int kw, int padH, int padW, int sH, int sW, int dH,
@@ -254,7 +256,9 @@ __global__ void __launch_bounds__(256, 2) conv3x3_first_pool_kernel(const float 
                                                                     const float *__restrict__ w,
                                                                     float *__restrict__ y,
                                                                     const float *__restrict__ bias, float alpha,
-                                                                    long long groups, int H, int W, int K) {
+                                                                    long long groups, int H, int W, int K,
+                                                                    float *__restrict__ y_hi,
+                                                                    float *__restrict__ y_lo) {
   constexpr int Q = C * 9;
   __shared__ __align__(16) float ws[Q * 32];  // [q][k], zero for k >= K
   __shared__ float bs[32];
@@ -323,25 +327,42 @@ __global__ void __launch_bounds__(256, 2) conv3x3_first_pool_kernel(const float 
         for (int pz = 0; pz < 4; ++pz)
 #pragma unroll
           for (int k = 0; k < 4; ++k) unpack2(accp[rr][pz][k], acc[rr][pz][2 * k], acc[rr][pz][2 * k + 1]);
+      float pooled[2][8];
 #pragma unroll
       for (int k = 0; k < 8; ++k) {
-        if (k0 + k < K) {
-          float o[2];
 #pragma unroll
-          for (int half = 0; half < 2; ++half) {
-            float best = -3.402823466e+38f;
+        for (int half = 0; half < 2; ++half) {
+          float best = -3.402823466e+38f;
 #pragma unroll
-            for (int rr = 0; rr < 2; ++rr)
+          for (int rr = 0; rr < 2; ++rr)
 #pragma unroll
-              for (int j = 0; j < 2; ++j) {
-                float t = acc[rr][2 * half + j][k];
-                if (BIAS) t = __fadd_rn(t, bs[k0 + k]);
-                best = fmaxf(best, pool_candidate(apply_act<float>(t, ACT, alpha)));
-              }
-            o[half] = best;
-          }
-          *reinterpret_cast<float2 *>(yb + (long long)(k0 + k) * Hq * Wq) = make_float2(o[0], o[1]);
+            for (int j = 0; j < 2; ++j) {
+              float t = acc[rr][2 * half + j][k];
+              if (BIAS) t = __fadd_rn(t, bs[(k0 + k) & 31]);
+              best = fmaxf(best, pool_candidate(apply_act<float>(t, ACT, alpha)));
+            }
+          pooled[half][k] = best;
         }
+        if (y && k0 + k < K)
+          *reinterpret_cast<float2 *>(yb + (long long)(k0 + k) * Hq * Wq) = make_float2(pooled[0][k], pooled[1][k]);
+      }
+      if (y_hi) {  // the same values as NHWC TF32 head / tail for the next convolution (K a multiple of 4)
+        const long long pos = (b * Hq + ph) * (long long)Wq + (ow >> 1);
+#pragma unroll
+        for (int half = 0; half < 2; ++half)
+#pragma unroll
+          for (int k4 = 0; k4 < 8; k4 += 4)
+            if (k0 + k4 < K) {
+              float h[4], l[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                h[j] = epi_tf32(pooled[half][k4 + j]);
+                l[j] = epi_tf32(__fsub_rn(pooled[half][k4 + j], h[j]));
+              }
+              const long long at = (pos + half) * K + k0 + k4;
+              *reinterpret_cast<float4 *>(y_hi + at) = make_float4(h[0], h[1], h[2], h[3]);
+              *reinterpret_cast<float4 *>(y_lo + at) = make_float4(l[0], l[1], l[2], l[3]);
+            }
       }
     }
   }
@@ -349,13 +370,14 @@ __global__ void __launch_bounds__(256, 2) conv3x3_first_pool_kernel(const float 
 
 template <int C>
 static int launch_conv3x3_first_pool(b200_engine *e, const float *x, const float *w, float *y, long long B, int H,
-                                     int W, int K, const Epilogue &ep) {
+                                     int W, int K, const Epilogue &ep, float *y_hi = nullptr, float *y_lo = nullptr) {
   const long long groups = B * (H / 2) * (W / 4);
   const int blocks = (int)std::max<long long>(1, std::min<long long>((groups + 255) / 256, (long long)e->sm_count * 16));
   const float *bias = (const float *)ep.bias;
   const float alpha = (float)ep.alpha;
 #define B200_FIRSTP(ACT, BIAS) \
-  conv3x3_first_pool_kernel<C, ACT, BIAS><<<blocks, 256, 0, e->stream>>>(x, w, y, bias, alpha, groups, H, W, K)
+  conv3x3_first_pool_kernel<C, ACT, BIAS><<<blocks, 256, 0, e->stream>>>(x, w, y, bias, alpha, groups, H, W, K, y_hi, \
+                                                                         y_lo)
   const bool hb = ep.bias_kind != B200_BIAS_NONE;
   if (ep.act == B200_ACT_NONE) { if (hb) B200_FIRSTP(B200_ACT_NONE, true); else B200_FIRSTP(B200_ACT_NONE, false); }
   else if (ep.act == B200_ACT_RECTIFY) { if (hb) B200_FIRSTP(B200_ACT_RECTIFY, true); else B200_FIRSTP(B200_ACT_RECTIFY, false); }
@@ -465,10 +487,11 @@ int b200_conv2d_fwd(b200_engine *e, int dtype, const void *x, const void *w, voi
                                kh, kw, pad_h, pad_w, stride_h, stride_w, dil_h, dil_w, (int)Ho, (int)Wo, ep);
     case B200_CONV_TC_TMA:
       return conv2d_tma(e, (const float *)x, (const float *)w, (float *)y, B, (int)C, (int)H, (int)W, (int)K, kh, kw,
-                        pad_h, pad_w, stride_h, stride_w, dil_h, dil_w, (int)Ho, (int)Wo, ep);
+                        pad_h, pad_w, stride_h, stride_w, dil_h, dil_w, (int)Ho, (int)Wo, ep, nullptr, nullptr, nullptr,
+                        nullptr);
     case B200_CONV_TC_WINDOW:
       return conv2d_win(e, (const float *)x, (const float *)w, (float *)y, B, (int)C, (int)H, (int)W, (int)K, kh, kw,
-                        pad_h, pad_w, dil_h, dil_w, (int)Ho, (int)Wo, ep, false);
+                        pad_h, pad_w, dil_h, dil_w, (int)Ho, (int)Wo, ep, false, nullptr, nullptr, nullptr, nullptr);
     case B200_CONV_TC_GATHER:
       return conv2d_tc(e, (const float *)x, (const float *)w, (float *)y, B, (int)C, (int)H, (int)W, (int)K, kh, kw,
                        pad_h, pad_w, stride_h, stride_w, dil_h, dil_w, (int)Ho, (int)Wo, ep);
@@ -529,7 +552,7 @@ int b200_conv2d_maxpool_fwd(b200_engine *e, int dtype, const void *x, const void
       const Epilogue ep = make_epilogue(epi);
       if (path == B200_CONV_TC_WINDOW)
         return conv2d_win(e, (const float *)x, (const float *)w, (float *)y, B, (int)C, (int)H, (int)W, (int)K, kh, kw,
-                          pad_h, pad_w, dil_h, dil_w, (int)Ho, (int)Wo, ep, true);
+                          pad_h, pad_w, dil_h, dil_w, (int)Ho, (int)Wo, ep, true, nullptr, nullptr, nullptr, nullptr);
       if (C == 1) return launch_conv3x3_first_pool<1>(e, (const float *)x, (const float *)w, (float *)y, B, (int)H, (int)W, (int)K, ep);
       if (C == 2) return launch_conv3x3_first_pool<2>(e, (const float *)x, (const float *)w, (float *)y, B, (int)H, (int)W, (int)K, ep);
       return launch_conv3x3_first_pool<3>(e, (const float *)x, (const float *)w, (float *)y, B, (int)H, (int)W, (int)K, ep);
@@ -544,6 +567,80 @@ int b200_conv2d_maxpool_fwd(b200_engine *e, int dtype, const void *x, const void
     rc = b200_maxpool2d_fwd(e, dtype, tmp, y, nullptr, B, K, Ho, Wo, pool_h, pool_w, 0, 0, 0, 0, 0, pool_stride_h,
                             pool_stride_w);
   b200_put(e, tmp, 0);
+  return rc;
+}
+
+int b200_conv2d_chain_fwd(b200_engine *e, const void *x, const void *x_hi, const void *x_lo, const void *w, void *y,
+                          void *y_hi, void *y_lo, int64_t B, int64_t C, int64_t H, int64_t W, int64_t K, int kh, int kw,
+                          int pad_h, int pad_w, int stride_h, int stride_w, int dil_h, int dil_w,
+                          const b200_epilogue *epi, int pool2) {
+  if (!e) return B200_ERR_INVALID;
+  std::lock_guard<std::recursive_mutex> lk(e->mu);
+  B200_REQUIRE(e, B >= 0 && C > 0 && H > 0 && W > 0 && K > 0 && kh > 0 && kw > 0 && stride_h > 0 && stride_w > 0 &&
+                      dil_h > 0 && dil_w > 0 && pad_h >= 0 && pad_w >= 0,
+               "b200_conv2d_chain_fwd: bad convolution shape");
+  B200_REQUIRE(e, (x_hi == nullptr) == (x_lo == nullptr) && (y_hi == nullptr) == (y_lo == nullptr),
+               "b200_conv2d_chain_fwd: a head needs its tail");
+  B200_REQUIRE(e, x || x_hi, "b200_conv2d_chain_fwd: no input");
+  B200_REQUIRE(e, y || y_hi, "b200_conv2d_chain_fwd: no output");
+  B200_REQUIRE(e, !y_hi || K % 4 == 0, "b200_conv2d_chain_fwd: the split output needs K to be a multiple of 4");
+  B200_REQUIRE(e, w, "b200_conv2d_chain_fwd: null filters");
+  const long long Ho = (H + 2 * pad_h - (dil_h * (kh - 1) + 1)) / stride_h + 1;
+  const long long Wo = (W + 2 * pad_w - (dil_w * (kw - 1) + 1)) / stride_w + 1;
+  B200_REQUIRE(e, Ho > 0 && Wo > 0, "b200_conv2d_chain_fwd: kernel larger than the padded image");
+  B200_REQUIRE(e, !pool2 || (Ho >= 2 && Wo >= 2), "b200_conv2d_chain_fwd: nothing to pool");
+  if (epi) {
+    B200_REQUIRE(e, epi->bias_kind == B200_BIAS_NONE || epi->bias_kind == B200_BIAS_ROW,
+                 "b200_conv2d_chain_fwd: the bias is one value per output channel (B200_BIAS_ROW)");
+    B200_REQUIRE(e, epi->act >= 0 && epi->act <= 2, "b200_conv2d_chain_fwd: bad activation");
+    B200_REQUIRE(e, epi->bias_kind == 0 || epi->bias != nullptr, "b200_conv2d_chain_fwd: bias is null");
+    B200_REQUIRE(e, epi->accumulate == 0, "b200_conv2d_chain_fwd: accumulate is a matrix-product option");
+  }
+  if (B == 0) return B200_OK;
+  const int path = conv_path(e, B200_F32, B, C, H, W, K, kh, kw, pad_h, pad_w, stride_h, stride_w, dil_h, dil_w, Ho, Wo);
+  const bool even = Ho % 2 == 0 && Wo % 2 == 0;
+  const float *xf = (const float *)x, *wf = (const float *)w;
+  float *yf = (float *)y;
+  if ((path == B200_CONV_TC_WINDOW && (!pool2 || even)) || (path == B200_CONV_TC_TMA && !pool2) ||
+      (path == B200_CONV_DIRECT && pool2 && even && x &&
+       conv3x3_first_ok(x, y, C, W, kh, kw, pad_h, pad_w, stride_h, stride_w, dil_h, dil_w))) {
+    DeviceGuard g(e);
+    int rc = flush_pending(e);
+    if (rc != B200_OK) return rc;
+    const Epilogue ep = make_epilogue(epi);
+    if (path == B200_CONV_TC_WINDOW)
+      return conv2d_win(e, xf, wf, yf, B, (int)C, (int)H, (int)W, (int)K, kh, kw, pad_h, pad_w, dil_h, dil_w, (int)Ho,
+                        (int)Wo, ep, pool2 != 0, (const float *)x_hi, (const float *)x_lo, (float *)y_hi,
+                        (float *)y_lo);
+    if (path == B200_CONV_TC_TMA)
+      return conv2d_tma(e, xf, wf, yf, B, (int)C, (int)H, (int)W, (int)K, kh, kw, pad_h, pad_w, stride_h, stride_w,
+                        dil_h, dil_w, (int)Ho, (int)Wo, ep, (const float *)x_hi, (const float *)x_lo, (float *)y_hi,
+                        (float *)y_lo);
+    if (C == 1) return launch_conv3x3_first_pool<1>(e, xf, wf, yf, B, (int)H, (int)W, (int)K, ep, (float *)y_hi, (float *)y_lo);
+    if (C == 2) return launch_conv3x3_first_pool<2>(e, xf, wf, yf, B, (int)H, (int)W, (int)K, ep, (float *)y_hi, (float *)y_lo);
+    return launch_conv3x3_first_pool<3>(e, xf, wf, yf, B, (int)H, (int)W, (int)K, ep, (float *)y_hi, (float *)y_lo);
+  }
+  // any other shape: the plain calls, then the rewrite pass; both need the tensors in NCHW
+  if (!x)
+    return set_error(e, B200_ERR_UNSUPPORTED,
+                     "b200_conv2d_chain_fwd: this shape runs on a kernel that reads NCHW; pass x as well");
+  const long long Hq = pool2 ? (Ho - 2) / 2 + 1 : Ho, Wq = pool2 ? (Wo - 2) / 2 + 1 : Wo;
+  void *tmp = nullptr;
+  int rc = B200_OK;
+  if (!y) {
+    rc = b200_get(e, B * K * Hq * Wq * 4, &tmp);
+    if (rc != B200_OK) return rc;
+    yf = (float *)tmp;
+  }
+  rc = pool2 ? b200_conv2d_maxpool_fwd(e, B200_F32, x, w, yf, B, C, H, W, K, kh, kw, pad_h, pad_w, stride_h, stride_w,
+                                       dil_h, dil_w, epi, 2, 2, 2, 2)
+             : b200_conv2d_fwd(e, B200_F32, x, w, yf, B, C, H, W, K, kh, kw, pad_h, pad_w, stride_h, stride_w, dil_h,
+                               dil_w, epi);
+  if (rc == B200_OK && y_hi) {
+    DeviceGuard g(e);
+    rc = conv_nhwc_split_into(e, yf, B, (int)K, (int)(Hq * Wq), (float *)y_hi, (float *)y_lo);
+  }
+  if (tmp) b200_put(e, tmp, 0);
   return rc;
 }
 

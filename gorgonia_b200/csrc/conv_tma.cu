@@ -38,7 +38,8 @@ constexpr int CT_BM = 128;
 constexpr int CT_THREADS = 320;  // 10 warps
 
 struct ConvTmaParams {
-  float *y;
+  float *y;               // NCHW output, or null when only the split form is wanted
+  float *y_hi, *y_lo;     // the output as NHWC TF32 head / tail for the next convolution, or null
   long long Mtot;  // B * Ho * Wo
   int K, Wo, hw;
   int kw, padH, padW, sH, sW, dH, dW;
@@ -266,7 +267,7 @@ __global__ void __launch_bounds__(CT_THREADS, 1)
           b = m / p.hw;
           pix = (int)(m % p.hw);
         }
-        yb = p.y + (b * p.K + n0) * (long long)p.hw + pix;
+        yb = p.y ? p.y + (b * p.K + n0) * (long long)p.hw + pix : nullptr;
       }
       // this warp's biases, staged once per tile (lane l holds channels l and l + 32)
       if (has_bias) {
@@ -275,7 +276,11 @@ __global__ void __launch_bounds__(CT_THREADS, 1)
         for (int j = lane; j < HALF; j += 32) bias_s[warp - 2][j] = n0 + j < p.K ? bias_g[n0 + j] : 0.f;
         __syncwarp();
       }
-      if (yb)
+      if (p.y_hi)  // position m of the flattened (b, oh, ow) index is row m of the NHWC tensor
+        store_channels_split<HALF, false>(acc, yb, p.hw, p.K - n0, has_bias ? bias_s[warp - 2] : nullptr, p.ep.act,
+                                          (float)p.ep.alpha, m < p.Mtot, p.y_hi + (m < p.Mtot ? m : 0) * p.K + n0,
+                                          p.y_lo + (m < p.Mtot ? m : 0) * p.K + n0);
+      else if (yb)
         store_channels<HALF>(acc, yb, p.hw, p.K - n0, has_bias ? bias_s[warp - 2] : nullptr, p.ep.act,
                              (float)p.ep.alpha);
     }
@@ -424,12 +429,16 @@ __global__ void __launch_bounds__(256) nhwc_split_img_kernel(const float *__rest
 
 // Rewrites x (B, C, HW) as NHWC TF32 head/tail into two fresh arena blocks xs[0], xs[1], which the
 // caller releases.
+static int launch_nhwc_split(b200_engine *e, const float *x, long long B, int C, int HW, void **xs);
 int conv_nhwc_split(b200_engine *e, const float *x, long long B, int C, int HW, void **xs) {
   const long long xbytes = B * C * HW * 4;
   xs[0] = xs[1] = nullptr;
   int rc = b200_get(e, xbytes, &xs[0]);
   if (rc == B200_OK) rc = b200_get(e, xbytes, &xs[1]);
   if (rc != B200_OK) return rc;
+  return launch_nhwc_split(e, x, B, C, HW, xs);
+}
+static int launch_nhwc_split(b200_engine *e, const float *x, long long B, int C, int HW, void **xs) {
   if (HW % 4 == 0 && C % 16 == 0 && (uintptr_t)x % 16 == 0) {
     const int ct = C % 32 == 0 ? 32 : 16;
     const long long tiles = B * ((HW + 127) / 128) * (C / ct);
@@ -456,6 +465,12 @@ int conv_nhwc_split(b200_engine *e, const float *x, long long B, int C, int HW, 
   nhwc_split_kernel<<<blocks, 256, 0, e->stream>>>(x, (float *)xs[0], (float *)xs[1], B, C, HW);
   B200_CHECK_LAUNCH(e, "nhwc_split_kernel");
   return B200_OK;
+}
+
+// The same rewrite into buffers the caller owns (B * C * HW floats each).
+int conv_nhwc_split_into(b200_engine *e, const float *x, long long B, int C, int HW, float *hi, float *lo) {
+  void *xs[2] = {hi, lo};
+  return launch_nhwc_split(e, x, B, C, HW, xs);
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
@@ -515,7 +530,7 @@ bool conv_tma_eligible(long long B, int C, int H, int W, int kh, int kw, int pad
 // x (B,C,H,W) * w (K,C,kh,kw) -> y (B,K,Ho,Wo), float32. ep.bias_kind ROW = one value per channel.
 int conv2d_tma(b200_engine *e, const float *x, const float *w, float *y, long long B, int C, int H, int W, int K,
                int kh, int kw, int padH, int padW, int sH, int sW, int dH, int dW, int Ho, int Wo,
-               const Epilogue &ep) {
+               const Epilogue &ep, const float *x_hi, const float *x_lo, float *y_hi, float *y_lo) {
   static EncodeTiledFn enc_tiled = (EncodeTiledFn)driver_entry("cuTensorMapEncodeTiled");
   static EncodeIm2colFn enc_im2col = (EncodeIm2colFn)driver_entry("cuTensorMapEncodeIm2col");
   if (!enc_tiled || !enc_im2col)
@@ -531,12 +546,19 @@ int conv2d_tma(b200_engine *e, const float *x, const float *w, float *y, long lo
 
   // activations: NHWC, TF32 head and tail
   void *xs[2] = {nullptr, nullptr};
-  rc = conv_nhwc_split(e, x, B, C, H * W, xs);
+  const void *xin[2] = {x_hi, x_lo};  // the caller's pre-split input, or this call's own rewrite
+  if (!x_hi) {
+    rc = conv_nhwc_split(e, x, B, C, H * W, xs);
+    xin[0] = xs[0];
+    xin[1] = xs[1];
+  }
 
   int bn = 128;
   while (bn > 32 && bn / 2 >= K) bn /= 2;
   ConvTmaParams p = ConvTmaParams();
   p.y = y;
+  p.y_hi = y_hi;
+  p.y_lo = y_lo;
   p.Mtot = B * Ho * Wo;
   p.K = K; p.Wo = Wo; p.hw = Ho * Wo;
   p.kw = kw; p.padH = padH; p.padW = padW; p.sH = sH; p.sW = sW; p.dH = dH; p.dW = dW;
@@ -559,7 +581,8 @@ int conv2d_tma(b200_engine *e, const float *x, const float *w, float *y, long lo
     int upper[2] = {padW - (kw - 1) * dW, padH - (kh - 1) * dH};
     cuuint32_t estr[4] = {1, (cuuint32_t)sW, (cuuint32_t)sH, 1};
     for (int h = 0; h < 2 && rc == B200_OK; ++h) {
-      CUresult r = enc_im2col(&tm[h], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, xs[h], dims, strides, lower, upper,
+      CUresult r = enc_im2col(&tm[h], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<void *>(xin[h]), dims, strides,
+                              lower, upper,
                               (cuuint32_t)ck, CT_BM, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
       if (r != CUDA_SUCCESS)

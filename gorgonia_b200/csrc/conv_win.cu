@@ -41,7 +41,8 @@ constexpr int CW_WIN_STAGES = 2;
 constexpr int CW_MAX_BSTAGES = 12;
 
 struct ConvWinParams {
-  float *y;
+  float *y;               // NCHW output, or null when only the split form is wanted
+  float *y_hi, *y_lo;     // the (pooled) output as NHWC TF32 head / tail for the next convolution, or null
   int K, Ho, Wo;
   int kh, kw, dH, dW, padH, padW;
   int win_w;         // window pitch in rows: 16 + (kw-1)*dW
@@ -330,19 +331,30 @@ __global__ void __launch_bounds__(CW_THREADS, 1)
         for (int j = lane; j < BN; j += 32) bias_s[warp - 2][j] = n0 + j < p.K ? bias_g[n0 + j] : 0.f;
         __syncwarp();
       }
+      const float *bias_w = has_bias ? bias_s[warp - 2] : nullptr;
       if (p.pool2) {
         // Ho and Wo are even, so a pooling window lies wholly inside the image or wholly outside
         const int Hq = p.Ho >> 1, Wq = p.Wo >> 1;
         const long long plane = (long long)Hq * Wq;
         const bool writer = oh < p.Ho && ow < p.Wo && (lane & 9) == 0;
-        float *yb = p.y + ((long long)b * p.K + n0) * plane + (long long)(oh >> 1) * Wq + (ow >> 1);
-        store_channels_pooled<BN>(acc, yb, plane, p.K - n0, has_bias ? bias_s[warp - 2] : nullptr, p.ep.act,
-                                  (float)p.ep.alpha, writer);
+        const long long pos = writer ? ((long long)b * Hq + (oh >> 1)) * Wq + (ow >> 1) : 0;
+        float *yb = p.y ? p.y + ((long long)b * p.K + n0) * plane + (long long)(oh >> 1) * Wq + (ow >> 1) : nullptr;
+        if (p.y_hi)
+          store_channels_split<BN, true>(acc, yb, plane, p.K - n0, bias_w, p.ep.act, (float)p.ep.alpha, writer,
+                                         p.y_hi + pos * p.K + n0, p.y_lo + pos * p.K + n0);
+        else
+          store_channels_pooled<BN>(acc, yb, plane, p.K - n0, bias_w, p.ep.act, (float)p.ep.alpha, writer);
+      } else if (p.y_hi) {
+        const long long plane = (long long)p.Ho * p.Wo;
+        const bool writer = oh < p.Ho && ow < p.Wo;
+        const long long pos = writer ? ((long long)b * p.Ho + oh) * p.Wo + ow : 0;
+        float *yb = p.y ? p.y + ((long long)b * p.K + n0) * plane + (long long)oh * p.Wo + ow : nullptr;
+        store_channels_split<BN, false>(acc, yb, plane, p.K - n0, bias_w, p.ep.act, (float)p.ep.alpha, writer,
+                                        p.y_hi + pos * p.K + n0, p.y_lo + pos * p.K + n0);
       } else if (oh < p.Ho && ow < p.Wo) {
         const long long plane = (long long)p.Ho * p.Wo;
         float *yb = p.y + ((long long)b * p.K + n0) * plane + (long long)oh * p.Wo + ow;
-        store_channels<BN>(acc, yb, plane, p.K - n0, has_bias ? bias_s[warp - 2] : nullptr, p.ep.act,
-                           (float)p.ep.alpha);
+        store_channels<BN>(acc, yb, plane, p.K - n0, bias_w, p.ep.act, (float)p.ep.alpha);
       }
     }
     if (!ok) s_fail = 1;
@@ -429,8 +441,11 @@ static int launch_conv_win(b200_engine *e, const CUtensorMap *tm, ConvWinParams 
 
 // x (B,C,H,W) * w (K,C,kh,kw) -> y (B,K,Ho,Wo), float32, stride 1. ep.bias_kind ROW = per channel.
 // pool2 (Ho, Wo even): y is (B,K,Ho/2,Wo/2), the 2x2 / stride-2 max-pool of the activated output.
+// x_hi / x_lo: the input already in NHWC TF32 head / tail form (x is then unused). y_hi / y_lo: the
+// (pooled) output additionally in that form, K a multiple of 4; y may then be null.
 int conv2d_win(b200_engine *e, const float *x, const float *w, float *y, long long B, int C, int H, int W, int K,
-               int kh, int kw, int padH, int padW, int dH, int dW, int Ho, int Wo, const Epilogue &ep, bool pool2) {
+               int kh, int kw, int padH, int padW, int dH, int dW, int Ho, int Wo, const Epilogue &ep, bool pool2,
+               const float *x_hi, const float *x_lo, float *y_hi, float *y_lo) {
   static CwEncodeTiledFn enc = cw_encode_fn();
   if (!enc) return set_error(e, B200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
   const int taps = kh * kw, crs = C * taps;
@@ -443,10 +458,17 @@ int conv2d_win(b200_engine *e, const float *x, const float *w, float *y, long lo
   int rc = conv_filters_tap_major(e, w, K, C, taps, &wf, wblk);
   if (rc != B200_OK) return rc;
   void *xs[2] = {nullptr, nullptr};
-  rc = conv_nhwc_split(e, x, B, C, H * W, xs);
+  const void *xin[2] = {x_hi, x_lo};  // the caller's pre-split input, or this call's own rewrite
+  if (!x_hi) {
+    rc = conv_nhwc_split(e, x, B, C, H * W, xs);
+    xin[0] = xs[0];
+    xin[1] = xs[1];
+  }
 
   ConvWinParams p = ConvWinParams();
   p.y = y;
+  p.y_hi = y_hi;
+  p.y_lo = y_lo;
   p.K = K; p.Ho = Ho; p.Wo = Wo;
   p.kh = kh; p.kw = kw; p.dH = dH; p.dW = dW; p.padH = padH; p.padW = padW;
   p.win_w = win_w;
@@ -471,7 +493,7 @@ int conv2d_win(b200_engine *e, const float *x, const float *w, float *y, long lo
     cuuint32_t box[4] = {(cuuint32_t)ck, (cuuint32_t)win_w, (cuuint32_t)win_h, 1};
     cuuint32_t estr[4] = {1, 1, 1, 1};
     for (int h = 0; h < 2 && rc == B200_OK; ++h) {
-      CUresult r = enc(&tm[h], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, xs[h], dims, strides, box, estr,
+      CUresult r = enc(&tm[h], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<void *>(xin[h]), dims, strides, box, estr,
                        CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
       if (r != CUDA_SUCCESS)

@@ -142,4 +142,67 @@ __device__ __forceinline__ void store_channels_pooled(const float (&acc)[N], flo
   }
 }
 
+// ---- the same stores, additionally (or only) in the form the NEXT convolution reads -------------
+// The tensor-core convolutions read their input channels-innermost (NHWC), split into a TF32 head
+// and the TF32 rounding of the remainder. A thread that holds N consecutive channels of one
+// position can write exactly that, 16 bytes at a time, and spare the separate rewrite pass.
+// nh / nl point at this position's channel n0 in the head / tail tensors; y (NCHW) may be null.
+// POOL folds the 2x2 / stride-2 max-pool in as above. `valid` must be a multiple of 4.
+__device__ __forceinline__ float epi_tf32(float v) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(v));
+  return __uint_as_float(r);
+}
+template <int N, int ACT, bool BIAS, bool POOL>
+__device__ __forceinline__ void store_channels_split_variant(const float (&acc)[N], float *y, long long plane,
+                                                             int valid, const float *bias, float alpha, bool writer,
+                                                             float *nh, float *nl) {
+#pragma unroll
+  for (int j0 = 0; j0 < N; j0 += 4) {
+    float o[4];
+#pragma unroll
+    for (int jj = 0; jj < 4; ++jj) {
+      float t = acc[j0 + jj];
+      if (BIAS) t = __fadd_rn(t, bias[j0 + jj]);
+      float v = apply_act<float>(t, ACT, alpha);
+      if (POOL) {
+        v = pool_candidate(v);
+        v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 1));
+        v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 8));
+      }
+      o[jj] = v;
+    }
+    if (writer && j0 < valid) {
+      if (y) {
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) y[(long long)(j0 + jj) * plane] = o[jj];
+      }
+      float h[4], l[4];
+#pragma unroll
+      for (int jj = 0; jj < 4; ++jj) {
+        h[jj] = epi_tf32(o[jj]);
+        l[jj] = epi_tf32(__fsub_rn(o[jj], h[jj]));
+      }
+      *reinterpret_cast<float4 *>(nh + j0) = make_float4(h[0], h[1], h[2], h[3]);
+      *reinterpret_cast<float4 *>(nl + j0) = make_float4(l[0], l[1], l[2], l[3]);
+    }
+  }
+}
+template <int N, bool POOL>
+__device__ __forceinline__ void store_channels_split(const float (&acc)[N], float *y, long long plane, int valid,
+                                                     const float *bias, int act, float alpha, bool writer, float *nh,
+                                                     float *nl) {
+#define B200_SPLIT_CASE(A, BI) store_channels_split_variant<N, A, BI, POOL>(acc, y, plane, valid, bias, alpha, writer, nh, nl)
+  if (bias) {
+    if (act == B200_ACT_NONE) B200_SPLIT_CASE(B200_ACT_NONE, true);
+    else if (act == B200_ACT_RECTIFY) B200_SPLIT_CASE(B200_ACT_RECTIFY, true);
+    else B200_SPLIT_CASE(B200_ACT_LEAKY, true);
+  } else {
+    if (act == B200_ACT_NONE) B200_SPLIT_CASE(B200_ACT_NONE, false);
+    else if (act == B200_ACT_RECTIFY) B200_SPLIT_CASE(B200_ACT_RECTIFY, false);
+    else B200_SPLIT_CASE(B200_ACT_LEAKY, false);
+  }
+#undef B200_SPLIT_CASE
+}
+
 }  // namespace b200

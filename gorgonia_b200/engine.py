@@ -406,6 +406,20 @@ class Engine:
                                           pool_stride[1]), self.h)
         return prealloc
 
+    def Conv2dChain(self, x, w, y, in_shape, pad=(0, 0), stride=(1, 1), dil=(1, 1), bias=None, act=None, alpha=0.0,
+                    pool2=False, x_split=None, y_split=None):
+        """One link of a chain of convolutions. x / y: NCHW tensors or None; x_split / y_split: (head, tail)
+        tensor pairs in NHWC TF32-split form or None; in_shape = (B, C, H, W) of the input."""
+        B, Cc, H, W = in_shape
+        K, _, kh, kw = w.shape
+        ep = _epilogue(bias, "row", act, alpha)
+        check(lib.b200_conv2d_chain_fwd(self.h, x.ptr if x is not None else None,
+                                        x_split[0].ptr if x_split else None, x_split[1].ptr if x_split else None,
+                                        w.ptr, y.ptr if y is not None else None,
+                                        y_split[0].ptr if y_split else None, y_split[1].ptr if y_split else None,
+                                        B, Cc, H, W, K, kh, kw, pad[0], pad[1], stride[0], stride[1], dil[0], dil[1],
+                                        C.byref(ep) if ep else None, int(pool2)), self.h)
+
     def conv2d_path(self, x, w, pad=(0, 0), stride=(1, 1), dil=(1, 1)):
         """Which kernel Conv2d would run for these operands (one of the _lib.CONV_* values)."""
         B, Cc, H, W = x.shape

@@ -15,10 +15,11 @@ benchmark drive the library the way a gorgonia build would:
 Every class owns its device buffers (weights stay resident across runs, unlike the reference,
 which re-uploads them after each Reset: vm_tape.go:123-134, analysis.go:151-176), exposes
 forward() = one pass of engine calls, and record()/replay() = the same pass as one recorded tape.
-`fused=True` uses the fused bias/activation stores of b200_gemm / b200_conv2d_fwd and, where a
-2x2/2 pool follows a convolution, b200_conv2d_maxpool_fwd (the convolution output is then never
-materialised); `fused=False` issues one engine call per reference instruction and leaves fusing to
-the engine's deferred queue.
+`fused=True` uses the fused bias/activation stores of b200_gemm and runs the convolutions as links
+of b200_conv2d_chain_fwd: a 2x2/2 pool that follows a convolution is folded into it (the
+convolution output is then never materialised) and a tensor that only the next convolution reads
+is written directly in the layout that convolution's kernel reads; `fused=False` issues one
+engine call per reference instruction and leaves fusing to the engine's deferred queue.
 Weights are seeded draws (Glorot-uniform / He-normal formulas of weights.go:397-479); nothing is
 computed on the host.
 """
@@ -62,6 +63,63 @@ class _Tape:
         if self.tape is not None:
             self.e.tape_destroy(self.tape)
             self.tape = None
+
+
+class _ConvChain:
+    """Plans a run of convolutions (each optionally followed by a 2x2/2 max-pool) as links of
+    b200_conv2d_chain_fwd: which links fold their pool in, and which tensors between links exist in
+    NCHW, in the NHWC TF32-split form the tensor-core kernels read, or both."""
+
+    def __init__(self, engine, batch, in_shape, layers):
+        # layers: dicts with w, pad, bias, act, alpha, pool ('2x2/2' | None)
+        from . import _lib
+        e = engine
+        self.e, self.layers = e, layers
+        shape = (batch,) + tuple(in_shape)
+        split_paths = (_lib.CONV_TC_WINDOW, _lib.CONV_TC_TMA)
+        for L in layers:
+            K, _, kh, kw = L["w"].shape
+            B, Cc, H, W = shape
+            Ho, Wo = H + 2 * L["pad"][0] - (kh - 1), W + 2 * L["pad"][1] - (kw - 1)
+            L["in_shape"] = shape
+            L["path"] = e.conv2d_path(_Shape(shape), L["w"], L["pad"])
+            even = Ho % 2 == 0 and Wo % 2 == 0
+            first = L["path"] == _lib.CONV_DIRECT and Cc <= 3 and kh == 3 and kw == 3 and L["pad"] == (1, 1) and W % 4 == 0
+            L["fuse_pool"] = bool(L["pool"]) and even and (L["path"] == _lib.CONV_TC_WINDOW or first)
+            L["conv_shape"] = (B, K, Ho, Wo)
+            shape = (B, K, Ho // 2, Wo // 2) if L["pool"] else (B, K, Ho, Wo)
+            L["out_shape"] = shape
+        for i, L in enumerate(layers):
+            nxt = layers[i + 1] if i + 1 < len(layers) else None
+            direct_feed = not L["pool"] or L["fuse_pool"]       # the link's own output is what the next conv reads
+            L["want_split"] = bool(nxt) and nxt["path"] in split_paths and direct_feed and L["w"].shape[0] % 4 == 0
+            # NCHW is needed by a separate pool, by a next link whose kernel reads NCHW, and at the end
+            L["want_nchw"] = not L["want_split"] or not direct_feed or nxt is None
+        for L in layers:
+            B, K, Ho, Wo = L["conv_shape"]
+            ob = L["out_shape"]
+            L["y"] = e.empty(L["conv_shape"] if (L["pool"] and not L["fuse_pool"]) else ob) if L["want_nchw"] else None
+            L["pooled"] = e.empty(ob) if (L["pool"] and not L["fuse_pool"]) else None
+            L["split"] = (e.empty((ob[0], ob[2], ob[3], ob[1])), e.empty((ob[0], ob[2], ob[3], ob[1]))) \
+                if L["want_split"] else None
+
+    def forward(self, x):
+        e, a, a_split = self.e, x, None
+        for L in self.layers:
+            e.Conv2dChain(a, L["w"], L["y"], L["in_shape"], pad=L["pad"], bias=L["bias"], act=L["act"], alpha=L["alpha"],
+                          pool2=L["fuse_pool"], x_split=a_split, y_split=L["split"])
+            a, a_split = L["y"], L["split"]
+            if L["pooled"] is not None:
+                e.MaxPool2D(L["y"], L["pooled"], (2, 2), (0, 0), (2, 2))
+                a = L["pooled"]
+        return a
+
+
+class _Shape:
+    """Stands in for a tensor where only shape and dtype are asked for."""
+
+    def __init__(self, shape):
+        self.shape, self.dtype = shape, np.dtype(np.float32)
 
 
 class MLP(_Tape):
@@ -116,7 +174,10 @@ class LeNet(_Tape):
         hw = (28, 14, 7)
         self.conv = [None if fused else e.empty((batch, self.CH[i + 1], hw[i], hw[i])) for i in range(3)]
         self.cmask = [None if fused else e.empty((batch, self.CH[i + 1], hw[i], hw[i])) for i in range(3)]
-        self.pool = [e.empty((batch, self.CH[i + 1], hw[i] // 2, hw[i] // 2)) for i in range(3)]
+        self.pool = [None if fused else e.empty((batch, self.CH[i + 1], hw[i] // 2, hw[i] // 2)) for i in range(3)]
+        self.chain = _ConvChain(e, batch, (1, 28, 28), [
+            {"w": self.wc[i], "pad": (1, 1), "bias": None, "act": "rectify", "alpha": 0.0, "pool": "2x2/2"}
+            for i in range(3)]) if fused else None
         self.fc = e.empty((batch, 625))
         self.fmask = None if fused else e.empty((batch, 625))
         self.logits = e.empty((batch, 10))
@@ -124,15 +185,15 @@ class LeNet(_Tape):
 
     def forward(self):
         e, a = self.e, self.x
-        for i in range(3):
-            if self.fused:
-                e.Conv2dMaxPool(a, self.wc[i], self.pool[i], pad=(1, 1), act="rectify")
-            else:
+        if self.fused:
+            a = self.chain.forward(a)
+        else:
+            for i in range(3):
                 e.Conv2d(a, self.wc[i], self.conv[i], pad=(1, 1))
                 e.GteScalar(self.conv[i], 0.0, reuse=self.cmask[i])
                 e.Mul(self.conv[i], self.cmask[i], unsafe=True)
                 e.MaxPool2D(self.conv[i], self.pool[i], (2, 2), (0, 0), (2, 2))
-            a = self.pool[i]
+                a = self.pool[i]
         flat = a.reshape(self.batch, 1152)
         if self.fused:
             e.MatMul(flat, self.wd[0], self.fc, act="rectify")
@@ -168,22 +229,31 @@ class TinyYolo(_Tape):
         s = size
         self.conv, self.pool = [], []
         for i in range(9):
-            self.conv.append(None if fused and i < 5 else e.empty((batch, ch[i + 1], s, s)))
+            self.conv.append(None if fused else e.empty((batch, ch[i + 1], s, s)))
             if i < 5:
                 s //= 2
-                self.pool.append(e.empty((batch, ch[i + 1], s, s)))
+                self.pool.append(None if fused else e.empty((batch, ch[i + 1], s, s)))
             elif i == 5:
                 self.pool.append(e.empty((batch, ch[i + 1], s, s)))
-        self.out = self.conv[8]
+        if fused:
+            def layer(i):
+                return {"w": self.w[i], "pad": (self.k[i] // 2, self.k[i] // 2), "bias": self.b[i], "act": "leaky",
+                        "alpha": 1.0 if i == 8 else 0.1, "pool": "2x2/2" if i < 5 else None}
+            # two runs of links, cut by the 2x2 / stride-1 pool with explicit padding after layer 5
+            self.chain_a = _ConvChain(e, batch, (3, size, size), [layer(i) for i in range(6)])
+            self.chain_b = _ConvChain(e, batch, (ch[6], s, s), [layer(i) for i in range(6, 9)])
+            self.out = self.chain_b.layers[-1]["y"]
+        else:
+            self.out = self.conv[8]
 
     def forward(self):
         e, a = self.e, self.x
+        if self.fused:
+            a = self.chain_a.forward(a)
+            e.MaxPool2D(a, self.pool[5], (2, 2), (1, 0, 1, 0), (1, 1))
+            return self.chain_b.forward(self.pool[5])
         for i in range(9):
             alpha = 1.0 if i == 8 else 0.1      # the last layer is LeakyRelu(1.0) in the reference graph
-            if self.fused and i < 5:
-                e.Conv2dMaxPool(a, self.w[i], self.pool[i], pad=(1, 1), bias=self.b[i], act="leaky", alpha=alpha)
-                a = self.pool[i]
-                continue
             e.Conv2d(a, self.w[i], self.conv[i], pad=(self.k[i] // 2, self.k[i] // 2), bias=self.b[i], act="leaky",
                      alpha=alpha)
             a = self.conv[i]

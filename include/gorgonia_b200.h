@@ -361,6 +361,21 @@ int b200_conv2d_maxpool_fwd(b200_engine *e, int dtype, const void *x, const void
                             int pad_h, int pad_w, int stride_h, int stride_w, int dil_h, int dil_w,
                             const b200_epilogue *ep, int pool_h, int pool_w, int pool_stride_h,
                             int pool_stride_w);
+/* One link of a CHAIN of convolutions (float32), for a tape in which a convolution's result is read
+ * only by the next convolution (possibly through a 2x2 / stride-2 max-pool: pool2 != 0), as in the
+ * convnet and tiny-YOLO graphs. Same arithmetic as b200_conv2d_fwd / b200_conv2d_maxpool_fwd; the
+ * tensors between links may additionally, or only, exist in the layout the tensor-core kernels read:
+ * channels innermost (B, H, W, C), every value split into its TF32 head and the TF32 rounding of
+ * the remainder. A link that writes that form (y_hi, y_lo; K a multiple of 4; y may be NULL) from
+ * its epilogue, and a next link that reads it (x_hi, x_lo; x may be NULL), together skip the
+ * rewrite pass each tensor-core convolution otherwise starts with. Shapes whose kernel reads NCHW
+ * need x and answer B200_ERR_UNSUPPORTED without it; shapes whose kernel cannot write the split
+ * form get it from a rewrite pass. Results are bit-identical to the unchained calls. */
+int b200_conv2d_chain_fwd(b200_engine *e, const void *x, const void *x_hi, const void *x_lo,
+                          const void *w, void *y, void *y_hi, void *y_lo, int64_t B, int64_t C,
+                          int64_t H, int64_t W, int64_t K, int kh, int kw, int pad_h, int pad_w,
+                          int stride_h, int stride_w, int dil_h, int dil_w, const b200_epilogue *ep,
+                          int pool2);
 /* Which kernel b200_conv2d_fwd would pick for a problem (no device work; -1 for a bad shape):
  * CUDA cores over an im2col scratch; the direct kernel for a first layer (C*kh*kw <= 32, K <= 32);
  * tensor cores with the col operand gathered by warps; tensor cores with the col operand built

@@ -231,6 +231,66 @@ def test_conv2d_maxpool_special_values(fresh):
     assert_bits_equal(one.numpy(), two.numpy())
 
 
+def test_conv2d_chain_equals_the_unchained_calls(fresh):
+    # three links: first-layer kernel + pool -> window kernel + pool -> im2col-TMA kernel; the tensors
+    # between them exist only in the NHWC TF32-split form. Bit-equal to Conv2dMaxPool / Conv2d.
+    from gorgonia_b200 import _lib
+    e = fresh
+    B = 16
+    x = util.uniform(101, (B, 3, 32, 32)) - np.float32(0.5)
+    w0 = util.normal(102, (32, 3, 3, 3), scale=0.3)
+    w1 = util.normal(103, (64, 32, 3, 3), scale=0.1)
+    w2 = util.normal(104, (40, 64, 3, 3), scale=0.08)
+    b0, b1, b2 = util.normal(105, 32, scale=0.1), util.normal(106, 64, scale=0.1), util.normal(107, 40, scale=0.1)
+    tx, tw0, tw1, tw2 = e.tensor(x), e.tensor(w0), e.tensor(w1), e.tensor(w2)
+    tb0, tb1, tb2 = e.tensor(b0), e.tensor(b1), e.tensor(b2)
+    # unchained
+    p0, p1, y2 = e.empty((B, 32, 16, 16)), e.empty((B, 64, 8, 8)), e.empty((B, 40, 8, 8))
+    e.Conv2dMaxPool(tx, tw0, p0, (1, 1), bias=tb0, act="leaky", alpha=0.1)
+    e.Conv2dMaxPool(p0, tw1, p1, (1, 1), bias=tb1, act="rectify")
+    e.Conv2d(p1, tw2, y2, (1, 1), bias=tb2)
+    assert e.conv2d_path(p0, tw1, (1, 1)) == _lib.CONV_TC_WINDOW and e.conv2d_path(p1, tw2, (1, 1)) == _lib.CONV_TC_TMA
+    # chained: no NCHW tensor between the links; the second link also keeps an NCHW copy, to be compared
+    s0 = (e.empty((B, 16, 16, 32)), e.empty((B, 16, 16, 32)))
+    s1 = (e.empty((B, 8, 8, 64)), e.empty((B, 8, 8, 64)))
+    q1, z2 = e.empty((B, 64, 8, 8)), e.empty((B, 40, 8, 8))
+    e.Conv2dChain(tx, tw0, None, (B, 3, 32, 32), (1, 1), bias=tb0, act="leaky", alpha=0.1, pool2=True, y_split=s0)
+    e.Conv2dChain(None, tw1, q1, (B, 32, 16, 16), (1, 1), bias=tb1, act="rectify", pool2=True, x_split=s0, y_split=s1)
+    e.Conv2dChain(None, tw2, z2, (B, 64, 8, 8), (1, 1), bias=tb2, x_split=s1)
+    assert_bits_equal(q1.numpy(), p1.numpy())
+    assert_bits_equal(z2.numpy(), y2.numpy())
+    # the split form itself: head + tail reproduce the NCHW tensor to 2^-21, head is its TF32 rounding
+    nhwc = np.transpose(p1.numpy(), (0, 2, 3, 1))
+    hi, lo = s1[0].numpy(), s1[1].numpy()
+    assert np.all((hi.view(np.uint32) & 0x1FFF) == 0)
+    assert np.abs((hi.astype(np.float64) + lo) - nhwc).max() <= 2.0 ** -21 * max(1.0, float(np.abs(nhwc).max()))
+
+
+def test_conv2d_chain_fallbacks(fresh):
+    from gorgonia_b200 import B200Error, _lib
+    e = fresh
+    # a link whose kernel reads NCHW (8 channels: gather path) still delivers the split form, by a rewrite pass
+    B = 12
+    x = util.uniform(108, (B, 8, 24, 24)) - np.float32(0.5)
+    w = util.normal(109, (32, 8, 3, 3), scale=0.2)
+    w2 = util.normal(110, (16, 32, 3, 3), scale=0.1)
+    tx, tw, tw2 = e.tensor(x), e.tensor(w), e.tensor(w2)
+    assert e.conv2d_path(tx, tw, (1, 1)) == _lib.CONV_TC_GATHER
+    p = e.empty((B, 32, 12, 12))
+    e.Conv2dMaxPool(tx, tw, p, (1, 1), act="rectify")
+    ref = e.empty((B, 16, 12, 12))
+    e.Conv2d(p, tw2, ref, (1, 1))
+    sp = (e.empty((B, 12, 12, 32)), e.empty((B, 12, 12, 32)))
+    got = e.empty((B, 16, 12, 12))
+    e.Conv2dChain(tx, tw, None, (B, 8, 24, 24), (1, 1), act="rectify", pool2=True, y_split=sp)
+    e.Conv2dChain(None, tw2, got, (B, 32, 12, 12), (1, 1), x_split=sp)
+    assert_bits_equal(got.numpy(), ref.numpy())
+    # without the NCHW input such a link cannot run
+    with pytest.raises(B200Error) as ei:
+        e.Conv2dChain(None, tw, p, (B, 8, 24, 24), (1, 1), x_split=sp)
+    assert ei.value.code == _lib.ERR_UNSUPPORTED
+
+
 def test_conv2d_matches_reference_pipeline(fresh):
     # Conv2d as gorgonia spells it (nn.go:264-298): Im2Col -> MatMul(transB) -> Transpose(0,3,1,2)
     e = fresh
