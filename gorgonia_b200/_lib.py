@@ -142,6 +142,8 @@ _SIGS = {
     "b200_set_constant": (_i, [_vp, _vp, _i]),
     "b200_gemm": (_i, [_vp, _i, _i, _i, _i64, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _i64,
                        _P(Epilogue)]),
+    "b200_gemm_chain": (_i, [_vp, _i, _i64, _i64, _i64, _vp, _vp, _vp, _i64, _vp, _i64, _vp, _vp, _vp, _i64, _i64,
+                             _P(Epilogue)]),
     "b200_gemm_path": (_i, [_vp, _i, _i, _i, _i64, _i64, _i64, _i64, _i64, _i64, _vp, _vp, _vp]),
     "b200_gemv": (_i, [_vp, _i, _i, _i64, _i64, _vp, _i64, _vp, _vp]),
     "b200_ger": (_i, [_vp, _i, _i64, _i64, _vp, _vp, _vp]),

@@ -55,8 +55,10 @@ constexpr int TC_ROW_BYTES = 128;  // one swizzle row: 64 bf16 or 32 fp32 along 
 
 struct GemmTcParams {
   long long M, N, K, batch;
-  void *C;
+  void *C;                      // may be null when only the split form is wanted
   long long ldc, strideC;
+  float *C_hi, *C_lo;           // C additionally as TF32 head / tail with row pitch ld_split, or null
+  long long ld_split;
   int tiles_m, tiles_n, num_k;  // num_k = k-blocks of BK elements
   int chunk_k;                  // k-blocks accumulated in tensor memory before the epilogue folds them
   int group_m;                  // rasterisation: m-blocks per group
@@ -273,6 +275,32 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
       auto store32 = [&](const float(&v)[32], int c) {
         if (m >= p.M) return;
         const long long nbase = n0 + c;
+        if (p.C_hi) {
+          // the result as the next product's A operand: TF32 head and tail, 16 bytes at a time;
+          // columns between N and the pitch hold zeros
+          float *hrow = p.C_hi + m * p.ld_split, *lrow = p.C_lo + m * p.ld_split;
+#pragma unroll
+          for (int j = 0; j < 32; j += 4) {
+            if (nbase + j >= p.ld_split) break;
+            float h[4], l[4];
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+              float o = 0.f;
+              if (nbase + j + t < p.N) {
+                o = apply_epilogue<float>(v[j + t], p.ep, m, nbase + j + t);
+                if (p.C) crow[nbase + j + t] = o;
+              }
+              uint32_t hb;
+              asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hb) : "f"(o));
+              h[t] = __uint_as_float(hb);
+              asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hb) : "f"(__fsub_rn(o, h[t])));
+              l[t] = __uint_as_float(hb);
+            }
+            *reinterpret_cast<float4 *>(hrow + nbase + j) = make_float4(h[0], h[1], h[2], h[3]);
+            *reinterpret_cast<float4 *>(lrow + nbase + j) = make_float4(l[0], l[1], l[2], l[3]);
+          }
+          return;
+        }
         if (p.c_vec && nbase + 32 <= p.N) {
 #pragma unroll
           for (int j = 0; j < 32; j += 4) {
@@ -507,7 +535,7 @@ static int launch_tc_layout(b200_engine *e, bool a_mn, bool b_mn, const CUtensor
 // m / n index contiguous (see the file comment).
 int gemm_tc_core(b200_engine *e, int terms, bool a_mn, bool b_mn, long long M, long long N, long long K,
                  const TcOperand &a, const TcOperand &b, void *C, long long ldc, long long batch, long long strideC,
-                 const Epilogue &ep) {
+                 const Epilogue &ep, float *C_hi = nullptr, float *C_lo = nullptr, long long ld_split = 0) {
   const int es = terms == 1 ? 2 : 4;
   const int bk = TC_ROW_BYTES / es;
   // tile width: the widest that still gives every SM a tile, to keep small problems spread out
@@ -548,6 +576,9 @@ int gemm_tc_core(b200_engine *e, int terms, bool a_mn, bool b_mn, long long M, l
   p.C = C;
   p.ldc = ldc;
   p.strideC = strideC;
+  p.C_hi = C_hi;
+  p.C_lo = C_lo;
+  p.ld_split = ld_split;
   p.tiles_m = tiles_m;
   p.tiles_n = tiles_n;
   p.num_k = (int)((K + bk - 1) / bk);
@@ -555,7 +586,7 @@ int gemm_tc_core(b200_engine *e, int terms, bool a_mn, bool b_mn, long long M, l
   // keeps the truncation bias of the tensor core's adder near 5e-7 relative.
   p.chunk_k = terms == 1 ? p.num_k : 8;
   p.group_m = std::min(tiles_m, 8);
-  p.c_vec = (ldc % 4 == 0 && (uintptr_t)C % 16 == 0 && (batch == 1 || strideC % 4 == 0)) ? 1 : 0;
+  p.c_vec = (C && ldc % 4 == 0 && (uintptr_t)C % 16 == 0 && (batch == 1 || strideC % 4 == 0)) ? 1 : 0;
   p.a_zmul = a.shared ? 0 : 1;
   p.b_zmul = b.shared ? 0 : 1;
   p.ep = ep;
@@ -661,6 +692,80 @@ static int gemm_tc(b200_engine *e, int dtype, int transA, int transB, long long 
 using namespace b200;
 
 extern "C" {
+
+int b200_gemm_chain(b200_engine *e, int transB, int64_t M, int64_t N, int64_t K, const void *A, const void *A_hi,
+                    const void *A_lo, int64_t lda, const void *B, int64_t ldb, void *C, void *C_hi, void *C_lo,
+                    int64_t ldc, int64_t ld_split, const b200_epilogue *epi) {
+  if (!e) return B200_ERR_INVALID;
+  std::lock_guard<std::recursive_mutex> lk(e->mu);
+  B200_REQUIRE(e, M >= 0 && N > 0 && K > 0, "b200_gemm_chain: bad extent");
+  B200_REQUIRE(e, (A_hi == nullptr) == (A_lo == nullptr) && (C_hi == nullptr) == (C_lo == nullptr),
+               "b200_gemm_chain: a head needs its tail");
+  B200_REQUIRE(e, A || A_hi, "b200_gemm_chain: no A");
+  B200_REQUIRE(e, C || C_hi, "b200_gemm_chain: no output");
+  B200_REQUIRE(e, B, "b200_gemm_chain: B is null");
+  B200_REQUIRE(e, lda >= K && ldb >= (transB ? K : N) && (!C || ldc >= N), "b200_gemm_chain: leading dimension too small");
+  B200_REQUIRE(e, !A_hi || (lda % 4 == 0 && ((uintptr_t)A_hi | (uintptr_t)A_lo) % 16 == 0),
+               "b200_gemm_chain: a split A needs a pitch that is a multiple of 4 and 16-byte aligned pointers");
+  B200_REQUIRE(e, !C_hi || (ld_split >= N && ld_split % 4 == 0 && ((uintptr_t)C_hi | (uintptr_t)C_lo) % 16 == 0),
+               "b200_gemm_chain: the split output needs a pitch >= N that is a multiple of 4 and aligned pointers");
+  if (epi) {
+    B200_REQUIRE(e, epi->bias_kind >= 0 && epi->bias_kind <= 2 && epi->act >= 0 && epi->act <= 2,
+                 "b200_gemm_chain: bad epilogue");
+    B200_REQUIRE(e, epi->bias_kind == 0 || epi->bias != nullptr, "b200_gemm_chain: bias is null");
+    B200_REQUIRE(e, epi->accumulate == 0, "b200_gemm_chain: accumulate cannot be combined with a chain");
+  }
+  if (M == 0) return B200_OK;
+  DeviceGuard g(e);
+  int rc = flush_pending(e);
+  if (rc != B200_OK) return rc;
+  const Epilogue ep = make_epilogue(epi);
+  const void *probe = A ? A : A_hi;
+  if (tc_eligible(B200_F32, M, N, K, lda, ldb, ldc, 1, 0, 0, probe, B, C ? C : C_hi)) {
+    TcOperand a, b;
+    void *blk[4] = {nullptr, nullptr, nullptr, nullptr};
+    if (A_hi) {
+      a.p0 = A_hi;
+      a.p1 = A_lo;
+      a.ld = lda;
+      a.batch_stride = M * lda;
+    } else {
+      rc = split_operand_tf32(e, (const float *)A, M, K, lda, 1, 0, &a, &blk[0], &blk[1]);
+    }
+    const long long b_rows = transB ? N : K, b_cols = transB ? K : N;
+    if (rc == B200_OK) rc = split_operand_tf32(e, (const float *)B, b_rows, b_cols, ldb, 1, 0, &b, &blk[2], &blk[3]);
+    if (rc == B200_OK)
+      rc = gemm_tc_core(e, 3, false, transB == 0, M, N, K, a, b, C, ldc, 1, M * ldc, ep, (float *)C_hi, (float *)C_lo,
+                        ld_split);
+    for (void *s2 : blk)
+      if (s2) b200_put(e, s2, 0);
+    return rc;
+  }
+  // small or oddly shaped: the plain product, then the rewrite pass; both need the tensors unsplit
+  if (!A)
+    return set_error(e, B200_ERR_UNSUPPORTED,
+                     "b200_gemm_chain: this shape runs on the CUDA-core kernel, which reads an unsplit A; pass A");
+  void *tmp = nullptr;
+  float *cf = (float *)C;
+  long long ldc_eff = ldc;
+  if (!C) {
+    rc = b200_get(e, M * N * 4, &tmp);
+    if (rc != B200_OK) return rc;
+    cf = (float *)tmp;
+    ldc_eff = N;
+  }
+  rc = gemm_simt(e, B200_F32, 0, transB, M, N, K, A, lda, B, ldb, cf, ldc_eff, 1, 0, 0, 0, ep);
+  if (rc == B200_OK && C_hi) {
+    const long long elems = M * ld_split;
+    const int blocks = (int)std::max<long long>(1, std::min<long long>((elems + 255) / 256, e->sm_count * 16LL));
+    split_tf32_kernel<<<blocks, 256, 0, e->stream>>>(cf, ldc_eff, 0, (float *)C_hi, (float *)C_lo, M, N, ld_split, 1);
+    cudaError_t le = cudaGetLastError();
+    if (le != cudaSuccess) rc = set_error(e, B200_ERR_CUDA, "launch of split_tf32_kernel failed: %s", cudaGetErrorString(le));
+    else e->launches++;
+  }
+  if (tmp) b200_put(e, tmp, 0);
+  return rc;
+}
 
 int b200_gemm_path(b200_engine *e, int dtype, int transA, int transB, int64_t M, int64_t N, int64_t K, int64_t lda,
                    int64_t ldb, int64_t ldc, const void *A, const void *B, const void *C) {

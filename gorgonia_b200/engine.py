@@ -318,6 +318,18 @@ class Engine:
                             batch, ar * ac, br * bc, M * N, C.byref(ep) if ep else None), self.h)
         return prealloc
 
+    def MatMulChain(self, a, b, c, M, N, K, transB=False, bias=None, bias_kind="col", act=None, alpha=0.0,
+                    a_split=None, c_split=None, ld_split=0):
+        """One link of a chain of dense layers. a / c: row-major tensors or None; a_split / c_split: (head, tail)
+        pairs with row pitch K (rounded up to a multiple of 4 by the link that wrote them) / ld_split."""
+        ep = _epilogue(bias, bias_kind, act, alpha)
+        lda = a.shape[-1] if a is not None else a_split[0].shape[-1]
+        check(lib.b200_gemm_chain(self.h, int(transB), M, N, K, a.ptr if a is not None else None,
+                                  a_split[0].ptr if a_split else None, a_split[1].ptr if a_split else None, lda,
+                                  b.ptr, b.shape[-1], c.ptr if c is not None else None,
+                                  c_split[0].ptr if c_split else None, c_split[1].ptr if c_split else None,
+                                  N, ld_split, C.byref(ep) if ep else None), self.h)
+
     def gemm_path(self, a, b, c, transA=False, transB=False):
         bf = getattr(a, "is_bf16", False)
         ar, ac = a.shape[-2:]

@@ -115,6 +115,38 @@ class _ConvChain:
         return a
 
 
+class _DenseChain:
+    """Plans a stack of dense layers act(a @ W + b) as links of b200_gemm_chain: an activation that
+    only the next tensor-core product reads is written split into TF32 head and tail by the link
+    that makes it, and never in plain form."""
+
+    def __init__(self, engine, batch, layers):
+        # layers: dicts with w (K, N), bias, act; the last layer's plain output is always kept
+        e = engine
+        self.e, self.batch, self.layers = e, batch, layers
+        for L in layers:
+            K, N = L["w"].shape
+            probe_a, probe_c = _Shape((batch, K)), _Shape((batch, N))
+            probe_a.ptr = probe_c.ptr = L["w"].ptr       # only alignment is looked at
+            L["tc"] = e.gemm_path(probe_a, L["w"], probe_c) == 1
+        for i, L in enumerate(layers):
+            nxt = layers[i + 1] if i + 1 < len(layers) else None
+            K, N = L["w"].shape
+            L["want_split"] = L["tc"] and nxt is not None and nxt["tc"]
+            L["pitch"] = (N + 3) // 4 * 4
+            L["c"] = None if L["want_split"] else e.empty((batch, N))
+            L["split"] = (e.empty((batch, L["pitch"])), e.empty((batch, L["pitch"]))) if L["want_split"] else None
+
+    def forward(self, a):
+        e, a_split = self.e, None
+        for L in self.layers:
+            K, N = L["w"].shape
+            e.MatMulChain(a, L["w"], L["c"], self.batch, N, K, bias=L["bias"], bias_kind="col", act=L["act"],
+                          a_split=a_split, c_split=L["split"], ld_split=L["pitch"] if L["split"] else 0)
+            a, a_split = L["c"], L["split"]
+        return a
+
+
 class _Shape:
     """Stands in for a tensor where only shape and dtype are asked for."""
 
@@ -137,19 +169,20 @@ class MLP(_Tape):
         self.h = [e.empty((batch, d)) for d in self.DIMS[1:]]
         self.mask = [e.empty((batch, d)) for d in self.DIMS[1:3]]
         self.out = e.empty((batch, 10))
+        self.chain = _DenseChain(e, batch, [
+            {"w": self.w[i], "bias": self.b[i], "act": None if i == 2 else "rectify"} for i in range(3)]) if fused else None
 
     def forward(self):
         e, a = self.e, self.x
+        if self.fused:
+            e.SoftMax(self.chain.forward(a), self.out)
+            return self.out
         for i in range(3):
-            last = i == 2
-            if self.fused:
-                e.MatMul(a, self.w[i], self.h[i], bias=self.b[i], bias_kind="col", act=None if last else "rectify")
-            else:
-                e.MatMul(a, self.w[i], self.h[i])
-                e.BroadcastBinary("add", self.h[i], self.b[i], 1, self.DIMS[i + 1], unsafe=True)
-                if not last:   # Rectify (nn.go:154-162): gte(x, 0) as float, then mul
-                    e.GteScalar(self.h[i], 0.0, reuse=self.mask[i])
-                    e.Mul(self.h[i], self.mask[i], unsafe=True)
+            e.MatMul(a, self.w[i], self.h[i])
+            e.BroadcastBinary("add", self.h[i], self.b[i], 1, self.DIMS[i + 1], unsafe=True)
+            if i < 2:   # Rectify (nn.go:154-162): gte(x, 0) as float, then mul
+                e.GteScalar(self.h[i], 0.0, reuse=self.mask[i])
+                e.Mul(self.h[i], self.mask[i], unsafe=True)
             a = self.h[i]
         e.SoftMax(a, self.out)
         return self.out
@@ -178,6 +211,8 @@ class LeNet(_Tape):
         self.chain = _ConvChain(e, batch, (1, 28, 28), [
             {"w": self.wc[i], "pad": (1, 1), "bias": None, "act": "rectify", "alpha": 0.0, "pool": "2x2/2"}
             for i in range(3)]) if fused else None
+        self.dense = _DenseChain(e, batch, [{"w": self.wd[0], "bias": None, "act": "rectify"},
+                                            {"w": self.wd[1], "bias": None, "act": None}]) if fused else None
         self.fc = e.empty((batch, 625))
         self.fmask = None if fused else e.empty((batch, 625))
         self.logits = e.empty((batch, 10))
@@ -196,11 +231,11 @@ class LeNet(_Tape):
                 a = self.pool[i]
         flat = a.reshape(self.batch, 1152)
         if self.fused:
-            e.MatMul(flat, self.wd[0], self.fc, act="rectify")
-        else:
-            e.MatMul(flat, self.wd[0], self.fc)
-            e.GteScalar(self.fc, 0.0, reuse=self.fmask)
-            e.Mul(self.fc, self.fmask, unsafe=True)
+            e.SoftMax(self.dense.forward(flat), self.out)
+            return self.out
+        e.MatMul(flat, self.wd[0], self.fc)
+        e.GteScalar(self.fc, 0.0, reuse=self.fmask)
+        e.Mul(self.fc, self.fmask, unsafe=True)
         e.MatMul(self.fc, self.wd[1], self.logits)
         e.SoftMax(self.logits, self.out)
         return self.out

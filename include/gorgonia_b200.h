@@ -269,6 +269,18 @@ int b200_gemm(b200_engine *e, int dtype, int transA, int transB, int64_t M, int6
               const void *A, int64_t lda, const void *B, int64_t ldb, void *C, int64_t ldc,
               int64_t batch, int64_t strideA, int64_t strideB, int64_t strideC,
               const b200_epilogue *ep);
+/* One link of a CHAIN of float32 matrix products C = act(A.op(B) + bias) (a stack of dense layers:
+ * examples/286/main.go:72-99, examples/convnet/main.go:138-159), the counterpart of
+ * b200_conv2d_chain_fwd. The tensor-core product reads its operands split into a TF32 head and
+ * tail; a link can write its result in that form (C_hi, C_lo, row pitch ld_split >= N, a multiple of
+ * 4; C may be NULL) and the next link reads it as its A (A_hi, A_lo with lda = that pitch; A may be
+ * NULL), which spares the split pass over every activation. Columns N .. ld_split-1 are zero-filled.
+ * Shapes that run on the CUDA-core kernel need A and answer B200_ERR_UNSUPPORTED without it.
+ * Results are bit-identical to b200_gemm. */
+int b200_gemm_chain(b200_engine *e, int transB, int64_t M, int64_t N, int64_t K, const void *A,
+                    const void *A_hi, const void *A_lo, int64_t lda, const void *B, int64_t ldb,
+                    void *C, void *C_hi, void *C_lo, int64_t ldc, int64_t ld_split,
+                    const b200_epilogue *ep);
 int b200_gemv(b200_engine *e, int dtype, int transA, int64_t M, int64_t N, const void *A,
               int64_t lda, const void *x, void *y);
 int b200_ger(b200_engine *e, int dtype, int64_t M, int64_t N, const void *x, const void *y, void *A);

@@ -209,3 +209,53 @@ def test_constant_operand_split_is_kept_until_undeclared(fresh):
     assert e.arena_stats()["used"] > used          # the kept split lives in the arena ...
     tb.free()
     assert e.arena_stats()["used"] < used          # ... and goes with the buffer it was derived from
+
+
+def test_matmul_chain_equals_the_unchained_calls(fresh):
+    # three dense layers; the activations between them exist only as TF32 head/tail pairs written by
+    # the producing link's epilogue. Bit-equal to MatMul with the same fused bias / activation.
+    e = fresh
+    M, dims = 512, (784, 300, 100, 64)
+    x = util.normal(201, (M, dims[0]))
+    ws = [util.normal(202 + i, (dims[i], dims[i + 1]), scale=0.05) for i in range(3)]
+    bs = [util.normal(210 + i, dims[i + 1], scale=0.1) for i in range(3)]
+    tx, tw, tb = e.tensor(x), [e.tensor(w) for w in ws], [e.tensor(b) for b in bs]
+    h = [e.empty((M, d)) for d in dims[1:]]
+    a = tx
+    for i in range(3):
+        e.MatMul(a, tw[i], h[i], bias=tb[i], bias_kind="col", act="rectify" if i < 2 else None)
+        a = h[i]
+    s0 = (e.empty((M, 300)), e.empty((M, 300)))
+    s1 = (e.empty((M, 100)), e.empty((M, 100)))
+    keep1, out = e.empty((M, 100)), e.empty((M, 64))
+    e.MatMulChain(tx, tw[0], None, M, 300, 784, bias=tb[0], act="rectify", c_split=s0, ld_split=300)
+    e.MatMulChain(None, tw[1], keep1, M, 100, 300, bias=tb[1], act="rectify", a_split=s0, c_split=s1, ld_split=100)
+    e.MatMulChain(None, tw[2], out, M, 64, 100, bias=tb[2], a_split=s1)
+    assert_bits_equal(keep1.numpy(), h[1].numpy())
+    assert_bits_equal(out.numpy(), h[2].numpy())
+    hi, lo = s1[0].numpy(), s1[1].numpy()
+    assert np.all((hi.view(np.uint32) & 0x1FFF) == 0)
+    assert np.abs((hi.astype(np.float64) + lo) - h[1].numpy()).max() <= 2.0 ** -21 * max(1.0, float(np.abs(h[1].numpy()).max()))
+
+
+def test_matmul_chain_ragged_pitch_and_fallback(fresh):
+    from gorgonia_b200 import B200Error, _lib
+    e = fresh
+    M, K, N = 300, 200, 625                      # N not a multiple of 4: pitch 628, zero-filled tail columns
+    a, b = util.normal(220, (M, K), scale=0.1), util.normal(221, (K, N), scale=0.1)
+    b2 = util.normal(222, (N, 40), scale=0.1)
+    ta, tb, tb2 = e.tensor(a), e.tensor(b), e.tensor(b2)
+    c, ref = e.empty((M, N)), e.empty((M, 40))
+    e.MatMul(ta, tb, c, act="rectify")
+    e.MatMul(c, tb2, ref)
+    sp = (e.tensor(np.full((M, 628), 7.0, np.float32)), e.tensor(np.full((M, 628), 7.0, np.float32)))
+    got = e.empty((M, 40))
+    e.MatMulChain(ta, tb, None, M, N, K, act="rectify", c_split=sp, ld_split=628)
+    e.MatMulChain(None, tb2, got, M, 40, N, a_split=sp)
+    assert_bits_equal(got.numpy(), ref.numpy())
+    assert np.all(sp[0].numpy()[:, 625:] == 0) and np.all(sp[1].numpy()[:, 625:] == 0)
+    # a product too small for the tensor cores needs the unsplit A
+    small = e.empty((8, 4))
+    with pytest.raises(B200Error) as ei:
+        e.MatMulChain(None, e.tensor(util.normal(223, (628, 4))), small, 8, 4, 628, a_split=sp)
+    assert ei.value.code == _lib.ERR_UNSUPPORTED
