@@ -171,6 +171,8 @@ _SIGS = {
     "b200_gather_rows": (_i, [_vp, _vp, _vp, _vp, _i64, _i64, _i64]),
     "b200_has_nan": (_i, [_vp, _i, _vp, _i64, _P(_i)]),
     "b200_has_inf": (_i, [_vp, _i, _vp, _i64, _P(_i)]),
+    "b200_selftest_wait": (_i, [_vp, _i64]),
+    "b200_tf32_peak": (_i, [_vp, _i, _P(C.c_double)]),
 }
 
 

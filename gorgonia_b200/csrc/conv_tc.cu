@@ -31,6 +31,8 @@
 #include <algorithm>
 #include <cstring>
 
+#include <atomic>
+
 #include "engine.h"
 #include "epilogue.cuh"
 #include "ptx.cuh"
@@ -511,7 +513,7 @@ template <int BN, int MODE>
 static int launch_conv_tc(b200_engine *e, const CUtensorMap *tm, ConvTcParams &p) {
   constexpr int STAGE_BYTES = 2 * (CV_A_BYTES + BN * 128);
   auto kern = conv_tc_kernel<BN, MODE>;
-  static int attr_dev_mask = 0;
+  static std::atomic<int> attr_dev_mask{0};  // devices on which the attribute is set; engines on other threads share it
   const size_t optin = std::min<size_t>(e->smem_optin, 227 * 1024);
   if (!(attr_dev_mask & (1 << (e->device & 31)))) {
     cudaFuncAttributes fa;

@@ -23,6 +23,8 @@
 #include <algorithm>
 #include <cstring>
 
+#include <atomic>
+
 #include "engine.h"
 #include "epilogue.cuh"
 #include "ptx.cuh"
@@ -493,7 +495,7 @@ template <int BN, int CK>
 static int launch_conv_tma(b200_engine *e, const CUtensorMap *tm, ConvTmaParams &p) {
   constexpr int STAGE_BYTES = 2 * (CT_BM + BN) * CK * 4;
   auto kern = conv_tma_kernel<BN, CK>;
-  static int attr_dev_mask = 0;
+  static std::atomic<int> attr_dev_mask{0};  // devices on which the attribute is set; engines on other threads share it
   const size_t optin = std::min<size_t>(e->smem_optin, 227 * 1024);
   if (!(attr_dev_mask & (1 << (e->device & 31)))) {
     cudaFuncAttributes fa;

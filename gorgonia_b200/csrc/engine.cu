@@ -37,23 +37,82 @@ CachedSplit *find_cached(b200_engine *e, const void *ptr, int kind, long long d0
   auto it = e->constants.find(ptr);
   if (it == e->constants.end()) return nullptr;
   for (auto &c : it->second.derived)
-    if (c.kind == kind && c.d0 == d0 && c.d1 == d1 && c.d2 == d2 && c.ld_in == ld_in) return &c;
+    if (c.kind == kind && c.d0 == d0 && c.d1 == d1 && c.d2 == d2 && c.ld_in == ld_in) {
+      pin_cached(e, c);  // whoever asks is about to launch a kernel that reads it
+      return &c;
+    }
   return nullptr;
 }
 
-void add_cached(b200_engine *e, const void *ptr, const CachedSplit &c) { e->constants[ptr].derived.push_back(c); }
+void add_cached(b200_engine *e, const void *ptr, const CachedSplit &c) {
+  e->constants[ptr].derived.push_back(c);
+  pin_cached(e, c);
+}
+
+void arena_release(b200_engine *e, int64_t off) {
+  if (!e->bfc.is_live(off)) return;
+  if (e->capturing) {
+    // the recording's kernels keep this address: reusable inside the recording, the tape's afterwards
+    const int64_t sz = e->bfc.live_size(off);
+    auto range = e->capture_free.equal_range(sz);
+    for (auto it = range.first; it != range.second; ++it)
+      if (it->second == off) return;  // handed back twice
+    e->capture_free.insert({sz, off});
+    return;
+  }
+  if (e->pins.count(off)) {
+    e->zombies.insert(off);  // a recorded tape still reads it
+    return;
+  }
+  // a plain arena free: whoever gets the block next runs later on the same stream
+  e->bfc.free(off);
+}
+
+void pin_cached(b200_engine *e, const CachedSplit &c) {
+  if (!e->capturing) return;
+  for (const void *p : {(const void *)c.hi, (const void *)c.lo}) {
+    const int64_t off = (const char *)p - (const char *)e->slab;
+    if (p && off >= 0 && off < e->slab_bytes) e->capture_pins.push_back(off);
+  }
+}
 
 void drop_constant(b200_engine *e, const void *ptr) {
   auto it = e->constants.find(ptr);
   if (it == e->constants.end()) return;
   for (auto &c : it->second.derived) {
-    // plain arena frees: whoever gets the blocks next runs later on the same stream
     int64_t off = (char *)c.hi - (char *)e->slab;
-    if (off >= 0 && off < e->slab_bytes) e->bfc.free(off);
+    if (off >= 0 && off < e->slab_bytes) arena_release(e, off);
     off = (char *)c.lo - (char *)e->slab;
-    if (off >= 0 && off < e->slab_bytes) e->bfc.free(off);
+    if (off >= 0 && off < e->slab_bytes) arena_release(e, off);
   }
   e->constants.erase(it);
+}
+
+int sync_stream_checked(b200_engine *e) {
+  if (e->flags_dirty) {
+    // kernels with bounded waits report a wait that ran out through d_flags[2]
+    // d_flags[3]: a gather met an index outside its range; a replayed tape cannot say so itself
+    B200_CHECK_CUDA(e, cudaMemcpyAsync(e->h_flags + 2, e->d_flags + 2, 2 * sizeof(int), cudaMemcpyDeviceToHost,
+                                       e->stream));
+    B200_CHECK_CUDA(e, cudaStreamSynchronize(e->stream));
+    e->flags_dirty = false;
+    const bool gather = e->gather_dirty;
+    e->gather_dirty = false;
+    if (e->h_flags[2] != 0) {
+      e->h_flags[2] = 0;
+      cudaMemsetAsync(e->d_flags + 2, 0, sizeof(int), e->stream);
+      return set_error(e, B200_ERR_TIMEOUT, "a device-side wait ran out of time; results of the last "
+                       "kernels are incomplete");
+    }
+    if (gather && e->h_flags[3] != 0) {
+      cudaMemsetAsync(e->d_flags + 3, 0, sizeof(int), e->stream);
+      return set_error(e, B200_ERR_INVALID, "a replayed tape holds a gather whose index lies outside its "
+                       "range; those rows were not written");
+    }
+    return B200_OK;
+  }
+  B200_CHECK_CUDA(e, cudaStreamSynchronize(e->stream));
+  return B200_OK;
 }
 
 }  // namespace b200
@@ -192,22 +251,7 @@ int b200_sync(b200_engine *e) {
   DeviceGuard g(e);
   int rc = flush_pending(e);
   if (rc != B200_OK) return rc;
-  if (e->flags_dirty) {
-    // kernels with bounded waits report a wait that ran out through d_flags[2]
-    B200_CHECK_CUDA(e, cudaMemcpyAsync(e->h_flags + 2, e->d_flags + 2, sizeof(int), cudaMemcpyDeviceToHost,
-                                       e->stream));
-    B200_CHECK_CUDA(e, cudaStreamSynchronize(e->stream));
-    e->flags_dirty = false;
-    if (e->h_flags[2] != 0) {
-      e->h_flags[2] = 0;
-      cudaMemsetAsync(e->d_flags + 2, 0, sizeof(int), e->stream);
-      return set_error(e, B200_ERR_TIMEOUT, "a device-side wait ran out of time; results of the last "
-                       "kernels are incomplete");
-    }
-    return B200_OK;
-  }
-  B200_CHECK_CUDA(e, cudaStreamSynchronize(e->stream));
-  return B200_OK;
+  return sync_stream_checked(e);
 }
 
 /* ---- tapes: a recorded sequence of engine calls replayed with one call ---- */
@@ -216,7 +260,22 @@ struct b200_tape {
   cudaGraph_t graph = nullptr;
   cudaGraphExec_t exec = nullptr;
   uint64_t launches = 0;  // kernels recorded, so that replays keep the launch counter honest
+  // Arena blocks the recorded kernels use although nobody else holds them any more: scratch the
+  // library took and handed back while recording, and buffers the caller released while recording.
+  // They stay allocated until the tape is destroyed (gorgonia frees a register at its last use,
+  // vm_tape.go:639-653; a replay is a use).
+  std::vector<int64_t> held;
+  std::vector<int64_t> pinned;  // derived forms of constants the tape reads (see b200_engine::pins)
+  uint64_t arena_epoch = 0;
+  bool has_gather = false;
 };
+
+// Ends the special treatment of blocks released during a recording that produced no tape.
+static void abandon_capture_blocks(b200_engine *e) {
+  for (auto &kv : e->capture_free) e->bfc.free(kv.second);
+  e->capture_free.clear();
+  e->capture_pins.clear();
+}
 
 int b200_tape_begin(b200_engine *e) {
   if (!e) return B200_ERR_INVALID;
@@ -227,6 +286,9 @@ int b200_tape_begin(b200_engine *e) {
   if (rc != B200_OK) return rc;
   B200_CHECK_CUDA(e, cudaStreamBeginCapture(e->stream, cudaStreamCaptureModeRelaxed));
   e->capturing = true;
+  e->capture_free.clear();
+  e->capture_pins.clear();
+  e->capture_has_gather = false;
   e->capture_launch_base = e->launches;
   return B200_OK;
 }
@@ -244,10 +306,12 @@ int b200_tape_end(b200_engine *e, b200_tape **out) {
   e->capturing = false;
   if (rc != B200_OK) {
     if (graph) cudaGraphDestroy(graph);
+    abandon_capture_blocks(e);
     return rc;
   }
   if (ce != cudaSuccess) {
     cudaGetLastError();
+    abandon_capture_blocks(e);
     return set_error(e, B200_ERR_CUDA, "cudaStreamEndCapture failed: %s", cudaGetErrorString(ce));
   }
   b200_tape *t = new b200_tape();
@@ -259,8 +323,15 @@ int b200_tape_end(b200_engine *e, b200_tape **out) {
     cudaGetLastError();
     cudaGraphDestroy(graph);
     delete t;
+    abandon_capture_blocks(e);
     return set_error(e, B200_ERR_CUDA, "cudaGraphInstantiate failed: %s", cudaGetErrorString(ce));
   }
+  t->arena_epoch = e->arena_epoch;
+  t->has_gather = e->capture_has_gather;
+  for (auto &kv : e->capture_free) t->held.push_back(kv.second);
+  e->capture_free.clear();
+  t->pinned.swap(e->capture_pins);
+  for (int64_t off : t->pinned) e->pins[off]++;
   *out = t;
   return B200_OK;
 }
@@ -270,12 +341,16 @@ int b200_tape_launch(b200_engine *e, b200_tape *t) {
   std::lock_guard<std::recursive_mutex> lk(e->mu);
   B200_REQUIRE(e, t && t->exec, "b200_tape_launch: null tape");
   if (e->capturing) return set_error(e, B200_ERR_STATE, "b200_tape_launch: a tape is being recorded");
+  if (t->arena_epoch != e->arena_epoch)
+    return set_error(e, B200_ERR_STATE, "b200_tape_launch: the arena was reset after this tape was recorded; "
+                     "its buffers may belong to someone else now");
   DeviceGuard g(e);
   int rc = flush_pending(e);
   if (rc != B200_OK) return rc;
   B200_CHECK_CUDA(e, cudaGraphLaunch(t->exec, e->stream));
   e->launches += t->launches;
   e->flags_dirty = true;
+  if (t->has_gather) e->gather_dirty = true;
   return B200_OK;
 }
 
@@ -287,6 +362,16 @@ int b200_tape_destroy(b200_engine *e, b200_tape *t) {
     cudaStreamSynchronize(e->stream);
     if (t->exec) cudaGraphExecDestroy(t->exec);
     if (t->graph) cudaGraphDestroy(t->graph);
+    if (t->arena_epoch == e->arena_epoch) {
+      for (int64_t off : t->held) arena_release(e, off);
+      for (int64_t off : t->pinned) {
+        auto it = e->pins.find(off);
+        if (it == e->pins.end()) continue;
+        if (--it->second > 0) continue;
+        e->pins.erase(it);
+        if (e->zombies.erase(off)) arena_release(e, off);
+      }
+    }
   }
   delete t;
   return B200_OK;
@@ -340,6 +425,16 @@ int b200_get(b200_engine *e, int64_t bytes, void **dptr) {
   *dptr = nullptr;
   B200_REQUIRE(e, bytes > 0, "b200_get: cannot allocate %lld bytes", (long long)bytes);
   int64_t off = 0;
+  if (e->capturing && !e->capture_free.empty()) {
+    // blocks released earlier in this recording: their last recorded user runs before this one
+    const int64_t need = (bytes + e->bfc.align() - 1) / e->bfc.align() * e->bfc.align();
+    auto it = e->capture_free.lower_bound(need);
+    if (it != e->capture_free.end() && it->first <= need + need / 4) {
+      *dptr = (char *)e->slab + it->second;
+      e->capture_free.erase(it);
+      return B200_OK;
+    }
+  }
   int rc = e->bfc.alloc(bytes, &off);
   if (rc == -2) {
     // Queued writes to buffers that were already handed back keep nothing alive, but a flush
@@ -360,17 +455,24 @@ int b200_put(b200_engine *e, void *dptr, int64_t /*bytes*/) {
   if (off < 0 || off >= e->slab_bytes) return B200_OK;  // not ours: no-op, as in the reference
   if (e->bfc.is_live(off)) note_put(e, dptr);
   drop_constant(e, dptr);  // a released buffer is no longer a constant; what was derived from it goes too
-  e->bfc.free(off);
+  arena_release(e, off);
   return B200_OK;
 }
 
 int b200_reset(b200_engine *e) {
   if (!e) return B200_ERR_INVALID;
   std::lock_guard<std::recursive_mutex> lk(e->mu);
+  if (e->capturing)
+    return set_error(e, B200_ERR_STATE, "b200_reset: a tape is being recorded");
   DeviceGuard g(e);
   // queued work may still read or write arena blocks: run it before the blocks are recycled
   int rc = flush_pending(e);
   e->constants.clear();  // derived blocks live in the arena that is being reset
+  // tapes recorded before this point keep addresses that are about to be handed out again:
+  // they must not be replayed, and they give nothing back when they are destroyed
+  e->arena_epoch++;
+  e->pins.clear();
+  e->zombies.clear();
   e->bfc.reset();
   return rc;
 }
@@ -430,7 +532,7 @@ static int copy_common(b200_engine *e, void *dst, const void *src, int64_t bytes
   int rc = flush_pending(e);
   if (rc != B200_OK) return rc;
   B200_CHECK_CUDA(e, cudaMemcpyAsync(dst, src, (size_t)bytes, kind, e->stream));
-  if (wait) B200_CHECK_CUDA(e, cudaStreamSynchronize(e->stream));
+  if (wait) return sync_stream_checked(e);  // the bytes just read may come from a kernel whose wait ran out
   return B200_OK;
 }
 

@@ -7,6 +7,7 @@
 #include <cstdio>
 #include <map>
 #include <mutex>
+#include <set>
 #include <string>
 #include <vector>
 
@@ -62,6 +63,16 @@ struct b200_engine {
   void (*gemm_state_free)(void *) = nullptr;
 
   bool capturing = false;   // between b200_tape_begin and b200_tape_end
+  bool capture_has_gather = false;  // the recording holds a gather, whose index check replays with it
+  bool gather_dirty = false;        // such a tape was replayed since the last synchronising call
+  // A recorded tape keeps the addresses its kernels were launched with, so arena blocks handed
+  // back while recording stay allocated: they may serve later requests of the same recording
+  // (stream order), and at b200_tape_end they become the tape's until b200_tape_destroy.
+  std::multimap<int64_t, int64_t> capture_free;  // size -> offset
+  std::vector<int64_t> capture_pins;             // blocks derived from constants that the recording reads
+  std::map<int64_t, int> pins;                   // offset -> live tapes reading it
+  std::set<int64_t> zombies;                     // released while pinned: freed with the last tape
+  uint64_t arena_epoch = 0;                      // bumped by b200_reset; older tapes own nothing
   uint64_t launches = 0;
   uint64_t capture_launch_base = 0;
   std::string last_error;
@@ -135,6 +146,14 @@ CachedSplit *find_cached(b200_engine *e, const void *ptr, int kind, long long d0
 bool is_constant(b200_engine *e, const void *ptr);
 void add_cached(b200_engine *e, const void *ptr, const CachedSplit &c);
 void drop_constant(b200_engine *e, const void *ptr);
+// Hands an arena block back, honouring a recording in progress and tapes that still read it.
+void arena_release(b200_engine *e, int64_t off);
+// Called with a derived form that a launch is about to read: a recording keeps it alive.
+void pin_cached(b200_engine *e, const CachedSplit &c);
+
+// Waits for the engine's stream; B200_ERR_TIMEOUT if a kernel launched since the last check gave
+// up a bounded wait. Every entry point that synchronises goes through it.
+int sync_stream_checked(b200_engine *e);
 
 // implemented in pointwise.cu
 int flush_pending(b200_engine *e);

@@ -33,6 +33,8 @@
 #include <algorithm>
 #include <cstring>
 
+#include <atomic>
+
 #include "engine.h"
 #include "epilogue.cuh"
 #include "ptx.cuh"
@@ -404,6 +406,64 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
 }
 
 // ------------------------------------------------------------------------------------------
+// What the tensor cores can do with kind::tf32 when nothing else is in the way: every SM issues
+// 128 x 256 x 8 MMAs back to back on operands that already sit in shared memory, with no loads
+// and no epilogue. The rate it reaches is the denominator of the float32 tensor rooflines.
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(128, 1) tf32_peak_kernel(int batches, int *err_flag) {
+  constexpr int BN = 256, PER_BATCH = 16;
+  extern __shared__ __align__(1024) unsigned char pk_smem_raw[];
+  __shared__ __align__(8) uint64_t bar[2];
+  __shared__ uint32_t tmem_base_s;
+  unsigned char *smem = reinterpret_cast<unsigned char *>(((uintptr_t)pk_smem_raw + 1023) & ~(uintptr_t)1023);
+  // operands: TF32 values of both signs and mixed magnitude (all-zero operands would flatter the clocks)
+  uint32_t *w = reinterpret_cast<uint32_t *>(smem);
+  for (int i = threadIdx.x; i < (TC_BM + BN) * TC_ROW_BYTES / 4; i += blockDim.x) {
+    const uint32_t h = (uint32_t)i * 2654435761u + blockIdx.x * 40503u;
+    w[i] = (h & 0x80000000u) | (0x3F000000u + ((h >> 3) & 0x00FFE000u));
+  }
+  ptx::fence_proxy_async_smem();
+  const int warp = threadIdx.x >> 5;
+  if (threadIdx.x == 0) {
+    ptx::mbar_init(&bar[0], 1);
+    ptx::mbar_init(&bar[1], 1);
+    ptx::fence_mbar_init();
+  }
+  if (warp == 0) {
+    ptx::tmem_alloc(&tmem_base_s, 512);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = tmem_base_s;
+  if (threadIdx.x == 0) {
+    constexpr uint32_t IDESC = make_idesc(2, false, false, TC_BM, BN);
+    const uint32_t sa = ptx::smem_addr(smem), sb = sa + TC_BM * TC_ROW_BYTES;
+    bool ok = true;
+    for (int b = 0; b < batches && ok; ++b) {
+#pragma unroll
+      for (int i = 0; i < PER_BATCH; ++i) {
+        const uint32_t off = (uint32_t)(i & 3) * 32;  // the four 8-wide k-slices of the 32-wide slab
+        ptx::mma_tf32(tmem_base + (uint32_t)((i >> 2) & 1) * BN, make_smem_desc(sa + off, 16, 1024, 2),
+                      make_smem_desc(sb + off, 16, 1024, 2), IDESC, (b | i) ? 1u : 0u);
+      }
+      ptx::mma_commit(&bar[b & 1]);
+      // one batch stays in flight: wait for the batch before this one
+      if (b > 0) ok = ptx::mbar_wait(&bar[(b - 1) & 1], (uint32_t)(((b - 1) >> 1) & 1));
+    }
+    if (ok && batches > 0) ok = ptx::mbar_wait(&bar[(batches - 1) & 1], (uint32_t)(((batches - 1) >> 1) & 1));
+    if (!ok) atomicExch(err_flag, 1);
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) {
+    ptx::tc_fence_after_sync();
+    ptx::tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// ------------------------------------------------------------------------------------------
 // TF32 split: x -> (head, tail), both TF32 values in fp32 containers, written densely with the
 // row length padded to a multiple of 4 elements (so that TMA row pitches stay 16-byte multiples)
 // ------------------------------------------------------------------------------------------
@@ -441,15 +501,14 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t
 
 static EncodeTiledFn get_encode_fn() {
   static EncodeTiledFn fn = nullptr;
-  static bool tried = false;
-  if (!tried) {
-    tried = true;
+  static std::once_flag once;
+  std::call_once(once, [] {
     void *sym = nullptr;
     cudaDriverEntryPointQueryResult q;
     if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
         q == cudaDriverEntryPointSuccess)
       fn = (EncodeTiledFn)sym;
-  }
+  });
   return fn;
 }
 
@@ -505,7 +564,7 @@ static int launch_tc(b200_engine *e, const CUtensorMap *tm, const GemmTcParams &
   (void)ES;
   auto kern = gemm_tc_kernel<TERMS, BN, A_MN, B_MN>;
   const size_t smem = (size_t)p.stages * STAGE_BYTES + 1024;
-  static int attr_dev_mask = 0;
+  static std::atomic<int> attr_dev_mask{0};  // devices on which the attribute is set; engines on other threads share it
   if (!(attr_dev_mask & (1 << (e->device & 31)))) {
     // opt in to the large dynamic carve-out: what the SM offers minus this kernel's static part
     cudaFuncAttributes fa;
@@ -707,8 +766,8 @@ int b200_gemm_chain(b200_engine *e, int transB, int64_t M, int64_t N, int64_t K,
   B200_REQUIRE(e, lda >= K && ldb >= (transB ? K : N) && (!C || ldc >= N), "b200_gemm_chain: leading dimension too small");
   B200_REQUIRE(e, !A_hi || (lda % 4 == 0 && ((uintptr_t)A_hi | (uintptr_t)A_lo) % 16 == 0),
                "b200_gemm_chain: a split A needs a pitch that is a multiple of 4 and 16-byte aligned pointers");
-  B200_REQUIRE(e, !C_hi || (ld_split >= N && ld_split % 4 == 0 && ((uintptr_t)C_hi | (uintptr_t)C_lo) % 16 == 0),
-               "b200_gemm_chain: the split output needs a pitch >= N that is a multiple of 4 and aligned pointers");
+  B200_REQUIRE(e, !C_hi || (ld_split == (N + 3) / 4 * 4 && ((uintptr_t)C_hi | (uintptr_t)C_lo) % 16 == 0),
+               "b200_gemm_chain: the split output needs the pitch N rounded up to a multiple of 4 and aligned pointers");
   if (epi) {
     B200_REQUIRE(e, epi->bias_kind >= 0 && epi->bias_kind <= 2 && epi->act >= 0 && epi->act <= 2,
                  "b200_gemm_chain: bad epilogue");
@@ -767,6 +826,45 @@ int b200_gemm_chain(b200_engine *e, int transB, int64_t M, int64_t N, int64_t K,
   return rc;
 }
 
+int b200_tf32_peak(b200_engine *e, int batches, double *tflops) {
+  if (!e) return B200_ERR_INVALID;
+  std::lock_guard<std::recursive_mutex> lk(e->mu);
+  B200_REQUIRE(e, tflops != nullptr, "b200_tf32_peak: null pointer");
+  B200_REQUIRE(e, batches >= 1 && batches <= 1000000, "b200_tf32_peak: 1 .. 1000000 batches of 16 instructions");
+  B200_NOT_WHILE_CAPTURING(e, "b200_tf32_peak");
+  DeviceGuard g(e);
+  int rc = flush_pending(e);
+  if (rc != B200_OK) return rc;
+  const size_t smem = (size_t)(TC_BM + 256) * TC_ROW_BYTES + 1024;
+  B200_CHECK_CUDA(e, cudaFuncSetAttribute(tf32_peak_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  cudaEvent_t ev0, ev1;
+  B200_CHECK_CUDA(e, cudaEventCreate(&ev0));
+  B200_CHECK_CUDA(e, cudaEventCreate(&ev1));
+  float best = 0.f;
+  for (int rep = 0; rep < 4 && rc == B200_OK; ++rep) {  // the first repetition warms up
+    cudaEventRecord(ev0, e->stream);
+    tf32_peak_kernel<<<e->sm_count, 128, smem, e->stream>>>(batches, e->d_flags + 2);
+    cudaError_t le = cudaGetLastError();
+    if (le != cudaSuccess) {
+      rc = set_error(e, B200_ERR_CUDA, "launch of tf32_peak_kernel failed: %s", cudaGetErrorString(le));
+      break;
+    }
+    e->launches++;
+    e->flags_dirty = true;
+    cudaEventRecord(ev1, e->stream);
+    rc = sync_stream_checked(e);
+    float ms = 0.f;
+    if (rc == B200_OK && cudaEventElapsedTime(&ms, ev0, ev1) == cudaSuccess && rep > 0 && (best == 0.f || ms < best))
+      best = ms;
+  }
+  cudaEventDestroy(ev0);
+  cudaEventDestroy(ev1);
+  if (rc != B200_OK) return rc;
+  const double flops = 2.0 * TC_BM * 256 * 8 * 16.0 * batches * e->sm_count;
+  *tflops = best > 0.f ? flops / (best * 1e-3) / 1e12 : 0.0;
+  return B200_OK;
+}
+
 int b200_gemm_path(b200_engine *e, int dtype, int transA, int transB, int64_t M, int64_t N, int64_t K, int64_t lda,
                    int64_t ldb, int64_t ldc, const void *A, const void *B, const void *C) {
   (void)e;
@@ -803,8 +901,13 @@ int b200_gemm(b200_engine *e, int dtype, int transA, int transB, int64_t M, int6
     return gemm_simt(e, dtype, transA, transB, M, N, 0, C, lda, C, ldb, C, ldc, batch, 0, 0, strideC, ep);
   }
   B200_REQUIRE(e, A && B, "b200_gemm: null operand");
-  if (tc_eligible(dtype, M, N, K, lda, ldb, ldc, batch, strideA, strideB, A, B, C))
-    return gemm_tc(e, dtype, transA, transB, M, N, K, A, lda, B, ldb, C, ldc, batch, strideA, strideB, strideC, ep);
+  if (tc_eligible(dtype, M, N, K, lda, ldb, ldc, batch, strideA, strideB, A, B, C)) {
+    rc = gemm_tc(e, dtype, transA, transB, M, N, K, A, lda, B, ldb, C, ldc, batch, strideA, strideB, strideC, ep);
+    // The float32 tensor-core path keeps TF32 splits of both operands in arena scratch (about
+    // 2 x (|A| + |B|) bytes). The reference's MatMul needs no workspace, so an arena too full for
+    // the splits still gets its product, from the CUDA-core kernel, which needs none.
+    if (rc != B200_ERR_OOM || dtype != B200_F32) return rc;
+  }
   if (dtype == B200_BF16)
     return set_error(e, B200_ERR_UNSUPPORTED,
                      "b200_gemm: bf16 operands need 16-byte aligned bases and row pitches (lda %lld, ldb %lld) and "

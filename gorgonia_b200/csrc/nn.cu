@@ -8,6 +8,8 @@
 #include <algorithm>
 #include <cfloat>
 
+#include <atomic>
+
 #include "engine.h"
 
 namespace b200 {
@@ -970,7 +972,7 @@ int b200_col2im(b200_engine *e, int dtype, const void *col, void *im, int64_t B,
   const size_t es = dtype_size(dtype);
   const size_t staged = (size_t)kh * Wo * (C * kh * kw + 1) * es;
   if (staged <= 96 * 1024 && stride_h == 1 && dil_h == 1 && pad_h < kh) {
-    static int attr_dev_mask = 0;
+    static std::atomic<int> attr_dev_mask{0};  // devices on which the attribute is set; engines on other threads share it
     if (!(attr_dev_mask & (1 << (e->device & 31)))) {
       B200_CHECK_CUDA(e, cudaFuncSetAttribute(col2im_rows_kernel<float, true>,
                                               cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
@@ -1169,9 +1171,14 @@ int b200_gather_axis(b200_engine *e, const void *x, const int64_t *idx, void *y,
         (const unsigned char *)x, (const long long *)idx, (unsigned char *)y, outer, n_idx, row_bytes, n_rows, bad);
   }
   B200_CHECK_LAUNCH(e, "gather_rows_kernel");
-  if (e->capturing) return B200_OK;  // a recorded gather cannot report bad indices; it skips those rows
+  if (e->capturing) {
+    // the check replays with the tape: the synchronising call after a replay reports it
+    e->capture_has_gather = true;
+    return B200_OK;
+  }
   B200_CHECK_CUDA(e, cudaMemcpyAsync(e->h_flags + 3, bad, sizeof(int), cudaMemcpyDeviceToHost, e->stream));
-  B200_CHECK_CUDA(e, cudaStreamSynchronize(e->stream));
+  rc = sync_stream_checked(e);
+  if (rc != B200_OK) return rc;
   if (e->h_flags[3])
     return set_error(e, B200_ERR_INVALID, "b200_gather_axis: an index lies outside [0, %lld)", (long long)n_rows);
   return B200_OK;

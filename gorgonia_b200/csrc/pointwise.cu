@@ -21,6 +21,8 @@
 #include <cmath>
 #include <cstring>
 
+#include <atomic>
+
 #include "engine.h"
 #include "ptx.cuh"
 
@@ -642,7 +644,7 @@ static int launch_stream_u(b200_engine *e, const PwDev &d, size_t budget, int st
                       (d.ka[0] == K_RING || d.ka[0] == K_IMM) &&
                       (d.op[0] >= B200_OP_ABS || d.kb[0] == K_RING || d.kb[0] == K_IMM);
   const int blocks = (int)std::min<long long>(ntiles, 2LL * e->sm_count);  // two resident CTAs per SM
-  static int attr_dev_mask[2] = {0, 0};  // per instantiation: devices on which the attribute is set
+  static std::atomic<int> attr_dev_mask[2];  // per instantiation: devices on which the attribute is set
   if (single) {
     auto kern = pw_stream_kernel<T, V, U, true>;
     if (!(attr_dev_mask[1] & (1 << (e->device & 31)))) {

@@ -330,6 +330,12 @@ class Engine:
                                   c_split[0].ptr if c_split else None, c_split[1].ptr if c_split else None,
                                   N, ld_split, C.byref(ep) if ep else None), self.h)
 
+    def tf32_peak(self, batches=4096):
+        """TFLOP/s of back-to-back kind::tf32 MMAs on every SM with no loads and no epilogue."""
+        v = C.c_double()
+        check(lib.b200_tf32_peak(self.h, int(batches), C.byref(v)), self.h)
+        return v.value
+
     def gemm_path(self, a, b, c, transA=False, transB=False):
         bf = getattr(a, "is_bf16", False)
         ar, ac = a.shape[-2:]

@@ -81,8 +81,16 @@ const char *b200_last_error(const b200_engine *e);
 /* Engine.DoWork (cuda/external.go:223-226): launch whatever the deferred queue holds. */
 int b200_flush(b200_engine *e);
 /* Engine.Signal + Sync (cuda/external.go:46-50,229-276): flush, then wait for the stream.
- * Asynchronous device errors surface here. */
+ * Asynchronous device errors surface here, and so does a bounded device-side wait that ran out
+ * (B200_ERR_TIMEOUT: the results of the kernels since the last synchronising call are incomplete;
+ * the engine stays usable). Every entry point that waits for the stream reports it the same way:
+ * b200_memcpy_h2d / _d2h, b200_has_nan / _inf, b200_gather_axis. */
 int b200_sync(b200_engine *e);
+/* Launches one warp that waits, with the library's bounded wait and a limit of `limit_us`
+ * microseconds (1 .. 10000), on a barrier nobody arrives at. The wait gives up, the kernel returns
+ * normally, and the next synchronising call returns B200_ERR_TIMEOUT. It exists so that the
+ * time-out path can be exercised without a stuck kernel; no counterpart in gorgonia. */
+int b200_selftest_wait(b200_engine *e, int64_t limit_us);
 /* Number of kernels this engine has launched since creation (tests and bench count with it). */
 uint64_t b200_launch_count(const b200_engine *e);
 
@@ -91,8 +99,14 @@ uint64_t b200_launch_count(const b200_engine *e);
  * vm_tape.go:213-347) costs one host call per instruction. A forward tape whose shapes and buffers
  * do not change between runs can instead be recorded once and replayed with ONE call:
  * between b200_tape_begin and b200_tape_end every engine call is recorded (into a CUDA graph on
- * the engine's stream) instead of executed; b200_tape_launch replays it. The buffers the recorded
- * calls named must stay allocated, at the same addresses, for as long as the tape is used.
+ * the engine's stream) instead of executed; b200_tape_launch replays it. Buffers the caller still
+ * holds when recording ends must stay allocated, at the same addresses, for as long as the tape is
+ * used. Everything else the recorded kernels touch belongs to the tape: arena scratch the library
+ * took and handed back while recording, buffers the caller released with b200_put while recording,
+ * and forms derived from constant buffers stay allocated until b200_tape_destroy, so allocations
+ * made between replays can never be given those bytes (gorgonia frees a register at its last use,
+ * vm_tape.go:639-653; every replay is a use). b200_reset ends that ownership: tapes recorded before
+ * it refuse to launch (B200_ERR_STATE), and it is refused while recording.
  * Entry points that wait for the device (b200_sync, the synchronous copies, b200_has_nan/inf)
  * return B200_ERR_STATE while recording; the _async copies can be recorded. Run the sequence once
  * unrecorded first, so that one-time set-up (kernel attributes, lazily created scratch) is done. */
@@ -246,7 +260,9 @@ int b200_has_inf(b200_engine *e, int dtype, const void *x, int64_t n, int *resul
  *   (K x M, resp. N x K). batch >= 1 matrices lie strideX elements apart.
  *   dtype B200_F32: float32 in and out; large aligned problems run on the tensor cores as
  *     3xTF32 (each operand split into a TF32 head and tail, three products, fp32 accumulate),
- *     the rest on CUDA cores in fp32.
+ *     the rest on CUDA cores in fp32. The splits live in arena scratch for the duration of the
+ *     call (about 2 x (|A| + |B|) bytes); when the arena cannot supply them the CUDA-core kernel
+ *     computes the product instead, so the call never fails for lack of workspace.
  *   dtype B200_BF16: bfloat16 A and B, float32 C, fp32 accumulate on the tensor cores.
  *   dtype B200_F64: CUDA cores.
  *   `ep` (may be NULL) fuses a bias add and an activation into the store.
@@ -269,11 +285,16 @@ int b200_gemm(b200_engine *e, int dtype, int transA, int transB, int64_t M, int6
               const void *A, int64_t lda, const void *B, int64_t ldb, void *C, int64_t ldc,
               int64_t batch, int64_t strideA, int64_t strideB, int64_t strideC,
               const b200_epilogue *ep);
+/* Measures what this GPU's tensor cores sustain with kind::tf32 instructions alone: every SM issues
+ * `batches` x 16 MMAs of 128 x 256 x 8 on operands resident in shared memory, no loads, no epilogue;
+ * best of three timed launches, in TFLOP/s of TF32 work. The float32 (3xTF32) rooflines of the
+ * benchmark use it as their denominator. Synchronises. No counterpart in gorgonia. */
+int b200_tf32_peak(b200_engine *e, int batches, double *tflops);
 /* One link of a CHAIN of float32 matrix products C = act(A.op(B) + bias) (a stack of dense layers:
  * examples/286/main.go:72-99, examples/convnet/main.go:138-159), the counterpart of
  * b200_conv2d_chain_fwd. The tensor-core product reads its operands split into a TF32 head and
- * tail; a link can write its result in that form (C_hi, C_lo, row pitch ld_split >= N, a multiple of
- * 4; C may be NULL) and the next link reads it as its A (A_hi, A_lo with lda = that pitch; A may be
+ * tail; a link can write its result in that form (C_hi, C_lo, row pitch ld_split = N rounded up to a
+ * multiple of 4; C may be NULL) and the next link reads it as its A (A_hi, A_lo with lda = that pitch; A may be
  * NULL), which spares the split pass over every activation. Columns N .. ld_split-1 are zero-filled.
  * Shapes that run on the CUDA-core kernel need A and answer B200_ERR_UNSUPPORTED without it.
  * Results are bit-identical to b200_gemm. */
@@ -345,6 +366,9 @@ int b200_reduce_all_static(b200_engine *e, int dtype, int kind, const void *x, i
  *   Ho = (H + 2 pad_h - (dil_h (kh-1) + 1)) / stride_h + 1 (op_nn.go:311-315). The reference builds it
  *   from Im2Col, Reshape, MatMul, Reshape, Transpose; float32 runs on the tensor cores (3xTF32).
  *   `ep` (may be NULL): per-output-channel bias (B200_BIAS_ROW) and activation fused into the store.
+ *   Workspace: the tensor-core kernels read an NHWC TF32 head/tail copy of x kept in arena scratch
+ *   for the duration of the call (8 bytes per input element) plus the split filters; B200_ERR_OOM
+ *   if the arena cannot supply it.
  * b200_im2col: im2colOp.do (op_nn.go:317-444): col (B, Ho, Wo, C*kh*kw), inner order channel, kernel
  *   row, kernel column; taps outside the image are 0.
  * b200_maxpool2d_fwd: maxPoolOp.do (op_nn.go:828-907). Output (H + pad_north + pad_south - kh) /
@@ -355,7 +379,9 @@ int b200_reduce_all_static(b200_engine *e, int dtype, int kind, const void *x, i
  *   axis perm[d]; elem_bytes 2, 4 or 8; rank <= 8.
  * b200_gather_axis: byIndicesOp.Do -> tensor.ByIndices along any axis (op_by_indices.go:90-97), the
  *   tensor viewed as (outer, n_rows, row): y[o,i,:] = x[o,idx[i],:], idx int64 on the device. An
- *   index outside [0, n_rows) is an error (checked on the device, reported by this call).
+ *   index outside [0, n_rows) is an error (checked on the device, reported by this call). Recorded
+ *   into a tape, the call cannot wait for the check: a replay skips such rows, and the next call that
+ *   waits for the stream (b200_sync, b200_memcpy_d2h, ...) returns B200_ERR_INVALID.
  *   b200_gather_rows is the axis-0 form (outer = 1). */
 int b200_conv2d_fwd(b200_engine *e, int dtype, const void *x, const void *w, void *y, int64_t B,
                     int64_t C, int64_t H, int64_t W, int64_t K, int kh, int kw, int pad_h, int pad_w,

@@ -50,6 +50,18 @@ int oracle_threads(void) {
 #endif
 }
 
+/* Launchers such as torchrun export OMP_NUM_THREADS=1 to their children; a timed CPU leg that is
+ * meant to use the whole host sets its thread count here instead. Returns the count in effect. */
+int oracle_set_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+  return omp_get_max_threads();
+#else
+  (void)n;
+  return 1;
+#endif
+}
+
 /* ---- scalar semantics -----------------------------------------------------------------
  * binary: operatorPointwise_binary.go:40-293 (scalar lambdas) and
  *         operatorPointwise_binary_const.go:5-22 (tensor.Add.. / tensor.Lt..); compare ops

@@ -46,6 +46,11 @@ def threads():
     return int(_lib.oracle_threads())
 
 
+def set_threads(n):
+    """Number of OpenMP threads the oracle uses from now on (overrides OMP_NUM_THREADS)."""
+    return int(_lib.oracle_set_threads(int(n)))
+
+
 def binary(op, a, b):
     """a, b: arrays of the same shape, or 0-d / python scalars for the scalar operand."""
     a_s, b_s = np.ndim(a) == 0, np.ndim(b) == 0
