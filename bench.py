@@ -848,7 +848,7 @@ def parity_model(name, m, x):
 
 def wl_model(ctx, args, name, main):
     from gorgonia_b200 import shard
-    total = MODEL_BATCH[name]
+    total = args.batch if (args.batch and main) else MODEL_BATCH[name]
     lo, hi = shard.my_shard(total, ctx.rank, ctx.world)
     b = hi - lo                                  # this rank's shard: strong scaling of a fixed batch
     steps, warmup = (args.steps, args.warmup) if main else (5, 3)
@@ -1095,6 +1095,9 @@ def main():
     ap.add_argument("--workload", default="yolo",
                     choices=["yolo", "lenet", "mlp", "elementwise", "gemm", "linalg", "backward"])
     ap.add_argument("--elements", type=int, default=1 << 29)
+    ap.add_argument("--batch", type=int, default=0,
+                    help="global batch of the chosen inference graph instead of the config's (to look at one "
+                         "GPU's shard of a multi-GPU run on a single GPU)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
     ap.add_argument("--no-others", action="store_true", help="measure only the chosen workload")
     ap.add_argument("--profile", action="store_true",

@@ -14,7 +14,9 @@
 // CK = 32 channels per k-block (128-byte rows, 128-byte swizzle), so C must be a multiple of 32.
 // (The kernel is also correct with CK = 16, 64-byte rows and swizzle, but at C = 16 the col slabs
 // are re-read from L2 nine times at 8 bytes per element and the gather kernel, which reads 4, wins.)
-// A 1x1 convolution has no re-reads to save and stays on the gather kernel too.
+// A 1x1 convolution has no re-reads to save, but it runs here as well: in a chain its input arrives
+// already split, and the last layers of a network have few tiles, which this kernel can share out
+// over all SMs along k (see ConvTmaParams::streamk).
 // Warp roles (10 warps): 0 TMA producer, 1 MMA issuer + TMEM owner, 2-9 epilogue.
 // No multicast, no clusters. Every wait is bounded; a time-out raises the engine's error word.
 #include <cuda.h>
@@ -50,9 +52,60 @@ struct ConvTmaParams {
   int chunk_k;     // k-blocks per accumulation chain
   int tiles_m, tiles_n;
   int stages;
+  // Work split. streamk == 0: CTA c takes tiles c, c + grid, ... whole. streamk == 1: the
+  // (tile, k-block) units of the whole problem, tile-major, are cut into `grid` equal contiguous
+  // shares, so a launch with fewer tiles than SMs (or a ragged last wave) still keeps every SM busy
+  // for the same time. A share that covers only part of a tile's k range leaves its fp32 partial
+  // tile in `ws`; whichever CTA delivers a tile's last missing part adds the parts in k order
+  // (so the result does not depend on who that is) and stores the tile.
+  int streamk;
+  long long units;  // tiles * num_k
+  float *ws;        // partial tiles: slot 2c (a part that begins CTA c's share) and 2c + 1 (one that ends it)
+  int *tile_count;  // parts delivered per tile, zeroed before the launch
   Epilogue ep;     // bias_kind ROW = per output channel
   int *err_flag;
 };
+
+// The pieces of work of one CTA, in the order every warp role walks them.
+struct CtPieces {
+  long long tile, total_tiles, u, u1;
+  int stride, num_k, stream;
+  __device__ CtPieces(const ConvTmaParams &p, long long tiles) {
+    stream = p.streamk;
+    num_k = p.num_k;
+    total_tiles = tiles;
+    tile = blockIdx.x;
+    stride = gridDim.x;
+    u = (long long)blockIdx.x * p.units / gridDim.x;
+    u1 = (long long)(blockIdx.x + 1) * p.units / gridDim.x;
+  }
+  // k-blocks [kb0, kb1) of tile t
+  __device__ bool next(long long &t, int &kb0, int &kb1) {
+    if (!stream) {
+      if (tile >= total_tiles) return false;
+      t = tile;
+      kb0 = 0;
+      kb1 = num_k;
+      tile += stride;
+      return true;
+    }
+    if (u >= u1) return false;
+    t = u / num_k;
+    kb0 = (int)(u - t * num_k);
+    const long long rem = u1 - u;
+    kb1 = (num_k - kb0) <= rem ? num_k : kb0 + (int)rem;
+    u += kb1 - kb0;
+    return true;
+  }
+};
+
+// The CTA whose share holds unit `unit` (shares start at c * units / grid).
+__device__ __forceinline__ int ct_cta_of(long long unit, long long units, int grid) {
+  int c = (int)(unit * grid / units);
+  while (c + 1 < grid && (long long)(c + 1) * units / grid <= unit) ++c;
+  while (c > 0 && (long long)c * units / grid > unit) --c;
+  return c;
+}
 
 __device__ __forceinline__ float ct_tf32(float v) {
   uint32_t r;
@@ -92,8 +145,9 @@ __global__ void __launch_bounds__(CT_THREADS, 1)
 
   extern __shared__ __align__(1024) unsigned char ct_smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[MAX_STAGES], empty_bar[MAX_STAGES], acc_full[2], acc_empty[2];
+  __shared__ __align__(8) uint64_t epi_bar;  // the 8 epilogue warps meet here when a partial tile is handed over
   __shared__ uint32_t tmem_base_s;
-  __shared__ int s_fail;
+  __shared__ int s_fail, s_last;
   __shared__ float bias_s[8][BN / 2];
 
   unsigned char *smem = reinterpret_cast<unsigned char *>(((uintptr_t)ct_smem_raw + 1023) & ~(uintptr_t)1023);
@@ -110,8 +164,10 @@ __global__ void __launch_bounds__(CT_THREADS, 1)
       ptx::mbar_init(&acc_full[b], 1);
       ptx::mbar_init(&acc_empty[b], 8);  // one arrival per epilogue warp
     }
+    ptx::mbar_init(&epi_bar, 8);
     ptx::fence_mbar_init();
     s_fail = 0;
+    s_last = 0;
   }
   if (warp == 1) {
     ptx::tmem_alloc(&tmem_base_s, TMEM_COLS);
@@ -134,7 +190,10 @@ __global__ void __launch_bounds__(CT_THREADS, 1)
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (long long tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      CtPieces pieces(p, total_tiles);
+      long long tile;
+      int kb0, kb1;
+      while (ok && pieces.next(tile, kb0, kb1)) {
         const int mt = (int)(tile / p.tiles_n), nt = (int)(tile % p.tiles_n);
         // first output position of the tile -> window origin in the input
         const long long m0 = (long long)mt * CT_BM;
@@ -142,8 +201,9 @@ __global__ void __launch_bounds__(CT_THREADS, 1)
         const int pix = (int)(m0 - (long long)n * p.hw);
         const int oh = pix / p.Wo, ow = pix - oh * p.Wo;
         const int w0 = ow * p.sW - p.padW, h0 = oh * p.sH - p.padH;
-        int cb = 0, r = 0, sx = 0;
-        for (int kb = 0; kb < p.num_k; ++kb) {
+        const int tap0 = kb0 / p.cblocks;
+        int cb = kb0 - tap0 * p.cblocks, r = tap0 / p.kw, sx = tap0 - (tap0 / p.kw) * p.kw;
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!ptx::mbar_wait_relaxed(&empty_bar[stage], phase ^ 1, 32)) {
             ok = false;
             break;
@@ -178,8 +238,11 @@ __global__ void __launch_bounds__(CT_THREADS, 1)
       uint32_t phase = 0;
       int use = 0;
       bool ok = true;
-      for (long long tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-        for (int kc = 0; kc < p.num_k && ok; kc += p.chunk_k, ++use) {
+      CtPieces pieces(p, total_tiles);
+      long long tile;
+      int kb0, kb1;
+      while (ok && pieces.next(tile, kb0, kb1)) {
+        for (int kc = kb0; kc < kb1 && ok; kc += p.chunk_k, ++use) {
           const int buf = use & 1;
           const uint32_t acc_phase = (uint32_t)((use >> 1) & 1);
           if (!ptx::mbar_wait(&acc_empty[buf], acc_phase ^ 1)) {
@@ -189,7 +252,7 @@ __global__ void __launch_bounds__(CT_THREADS, 1)
           ptx::tc_fence_after_sync();
           const uint32_t d_main = tmem_base + (uint32_t)(buf * ACC_COLS);
           const uint32_t d_tail = d_main + BN;
-          const int kend = kc + p.chunk_k < p.num_k ? kc + p.chunk_k : p.num_k;
+          const int kend = kc + p.chunk_k < kb1 ? kc + p.chunk_k : kb1;
           for (int kb = kc; kb < kend; ++kb) {
             if (!ptx::mbar_wait(&full_bar[stage], phase)) {
               ok = false;
@@ -225,13 +288,25 @@ __global__ void __launch_bounds__(CT_THREADS, 1)
     const bool has_bias = p.ep.bias_kind != B200_BIAS_NONE;
     const float *bias_g = reinterpret_cast<const float *>(p.ep.bias);
     int use = 0;
+    uint32_t epi_phase = 0;
     bool ok = true;
-    for (long long tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+    // the epilogue warps' own rendezvous: an mbarrier, so that this wait is bounded like every other
+    auto epi_sync = [&]() -> bool {
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(&epi_bar);
+      const bool done = ptx::mbar_wait_relaxed(&epi_bar, epi_phase, 32);
+      epi_phase ^= 1;
+      return done;
+    };
+    CtPieces pieces(p, total_tiles);
+    long long tile;
+    int kb0, kb1;
+    while (ok && pieces.next(tile, kb0, kb1)) {
       const int mt = (int)(tile / p.tiles_n), nt = (int)(tile % p.tiles_n);
       float acc[HALF];
 #pragma unroll
       for (int j = 0; j < HALF; ++j) acc[j] = 0.f;
-      for (int kc = 0; kc < p.num_k && ok; kc += p.chunk_k) {
+      for (int kc = kb0; kc < kb1 && ok; kc += p.chunk_k) {
         const int buf = use & 1;
         const uint32_t acc_phase = (uint32_t)((use >> 1) & 1);
         ++use;
@@ -253,6 +328,41 @@ __global__ void __launch_bounds__(CT_THREADS, 1)
         ptx::tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(&acc_empty[buf]);
+      }
+      if (kb0 != 0 || kb1 != p.num_k) {
+        // part of a tile: leave it in the workspace; the CTA that delivers the last part finishes the tile
+        const long long tile_u0 = tile * p.num_k;
+        const long long my_u0 = (long long)blockIdx.x * p.units / gridDim.x;
+        const size_t slot_floats = (size_t)CT_BM * BN;
+        const size_t within = ((size_t)(warp - 2) * HALF) * 32 + lane;
+        if (ok) {
+          float *wsp = p.ws + (size_t)(2 * blockIdx.x + (my_u0 >= tile_u0 + kb0 ? 0 : 1)) * slot_floats + within;
+#pragma unroll
+          for (int j = 0; j < HALF; ++j) __stcg(wsp + j * 32, acc[j]);
+        } else {
+          s_fail = 1;
+        }
+        __threadfence();
+        const int c_first = ct_cta_of(tile_u0, p.units, gridDim.x);
+        const int c_last = ct_cta_of(tile_u0 + p.num_k - 1, p.units, gridDim.x);
+        bool met = epi_sync();
+        if (warp == 2 && lane == 0)
+          s_last = (atomicAdd(p.tile_count + tile, 1) == c_last - c_first) ? 1 : 0;
+        met = epi_sync() && met;
+        if (!met || *(volatile int *)&s_fail) {
+          ok = false;
+          break;
+        }
+        if (!*(volatile int *)&s_last) continue;
+        __threadfence();
+#pragma unroll
+        for (int j = 0; j < HALF; ++j) acc[j] = 0.f;
+        for (int c = c_first; c <= c_last; ++c) {  // k order: CTA c's share precedes CTA c + 1's
+          const long long cu0 = (long long)c * p.units / gridDim.x;
+          const float *src = p.ws + (size_t)(2 * c + (cu0 >= tile_u0 ? 0 : 1)) * slot_floats + within;
+#pragma unroll
+          for (int j = 0; j < HALF; ++j) acc[j] = __fadd_rn(acc[j], __ldcg(src + j * 32));
+        }
       }
       if (!ok) break;
       const long long m = (long long)mt * CT_BM + quarter * 32 + lane;
@@ -507,19 +617,44 @@ static int launch_conv_tma(b200_engine *e, const CUtensorMap *tm, ConvTmaParams 
   p.stages = (int)std::max<size_t>(2, std::min<size_t>(8, (optin - 4096) / STAGE_BYTES));
   const size_t smem = (size_t)p.stages * STAGE_BYTES + 1024;
   const long long tiles = (long long)p.tiles_m * p.tiles_n;
-  const int grid = (int)std::min<long long>(tiles, e->sm_count);
+  int grid = (int)std::min<long long>(tiles, e->sm_count);
+  // Whole tiles per CTA leave SMs idle when the tiles do not fill the last wave: with fewer tiles
+  // than SMs, or e.g. 169 tiles on 148 SMs. Below 85 % occupancy of the waves the k range is shared
+  // out instead (see ConvTmaParams::streamk), at least two k-blocks per CTA.
+  const long long waves = (tiles + e->sm_count - 1) / e->sm_count;
+  void *ws = nullptr;
+  p.streamk = 0;
+  p.units = tiles * p.num_k;
+  if (p.num_k >= 4 && (double)tiles < 0.85 * (double)(waves * e->sm_count) && !(e->flags & B200_ENGINE_NO_STREAMK)) {
+    grid = (int)std::max<long long>(1, std::min<long long>(e->sm_count, p.units / 2));
+    const long long ws_bytes = 2LL * grid * CT_BM * BN * 4;
+    const long long cnt_bytes = (tiles * 4 + 255) / 256 * 256;
+    int rc = b200_get(e, cnt_bytes + ws_bytes, &ws);
+    if (rc == B200_OK) {
+      p.streamk = 1;
+      p.tile_count = (int *)ws;
+      p.ws = (float *)((char *)ws + cnt_bytes);
+      B200_CHECK_CUDA(e, cudaMemsetAsync(ws, 0, (size_t)cnt_bytes, e->stream));
+    } else {
+      grid = (int)std::min<long long>(tiles, e->sm_count);  // no room for the partial tiles: whole tiles per CTA
+    }
+  }
   kern<<<grid, CT_THREADS, smem, e->stream>>>(tm[0], tm[1], tm[2], tm[3], p);
-  B200_CHECK_LAUNCH(e, "conv_tma_kernel");
+  cudaError_t le = cudaGetLastError();
+  if (ws) b200_put(e, ws, 0);  // stream order: whoever gets the block next runs after this kernel
+  if (le != cudaSuccess)
+    return set_error(e, B200_ERR_CUDA, "launch of conv_tma_kernel failed: %s", cudaGetErrorString(le));
+  e->launches++;
   e->flags_dirty = true;
   return B200_OK;
 }
 
 // Whether the TMA unit builds the col operand of this convolution: channels a multiple of 32,
-// more than one tap, window corners and tap offsets inside the ranges an im2col tensor map can
+// window corners and tap offsets inside the ranges an im2col tensor map can
 // encode, and an input of at least 128 KB.
 bool conv_tma_eligible(long long B, int C, int H, int W, int kh, int kw, int padH, int padW, int sH, int sW, int dH,
                        int dW) {
-  if (C % 32 != 0 || kh * kw == 1) return false;
+  if (C % 32 != 0) return false;
   const int spanH = (kh - 1) * dH, spanW = (kw - 1) * dW;
   if (padH > 128 || padW > 128 || padH - spanH < -128 || padW - spanW < -128) return false;
   if (spanH > 255 || spanW > 255) return false;

@@ -68,8 +68,11 @@ enum {
                               * host code may dereference arena pointers, as gorgonia does   *
                               * (cuda/external.go:162, cuda/engine.go:71-72)                 */
   B200_ENGINE_NO_DEFER = 2u, /* launch each pointwise call at once instead of queueing it   */
-  B200_ENGINE_CONV_GATHER = 4u /* tensor-core convolutions build their col operand with gather *
-                                * warps even where the TMA unit could (tests, comparisons)     */
+  B200_ENGINE_CONV_GATHER = 4u, /* tensor-core convolutions build their col operand with gather *
+                                 * warps even where the TMA unit could (tests, comparisons)    */
+  B200_ENGINE_NO_STREAMK = 8u   /* tensor-core kernels never share a tile's k range between    *
+                                 * CTAs: every output element is then summed in one fixed      *
+                                 * order whatever the batch size (tests, comparisons)          */
 };
 int b200_engine_create(int device, size_t arena_bytes, unsigned flags, b200_engine **out);
 int b200_engine_destroy(b200_engine *e);
