@@ -52,60 +52,14 @@ struct ConvTmaParams {
   int chunk_k;     // k-blocks per accumulation chain
   int tiles_m, tiles_n;
   int stages;
-  // Work split. streamk == 0: CTA c takes tiles c, c + grid, ... whole. streamk == 1: the
-  // (tile, k-block) units of the whole problem, tile-major, are cut into `grid` equal contiguous
-  // shares, so a launch with fewer tiles than SMs (or a ragged last wave) still keeps every SM busy
-  // for the same time. A share that covers only part of a tile's k range leaves its fp32 partial
-  // tile in `ws`; whichever CTA delivers a tile's last missing part adds the parts in k order
-  // (so the result does not depend on who that is) and stores the tile.
+  // how the work is shared between the CTAs (TilePieces, tc_common.cuh)
   int streamk;
-  long long units;  // tiles * num_k
+  int units;        // tiles * num_k (0 when the k range is not shared)
   float *ws;        // partial tiles: slot 2c (a part that begins CTA c's share) and 2c + 1 (one that ends it)
   int *tile_count;  // parts delivered per tile, zeroed before the launch
   Epilogue ep;     // bias_kind ROW = per output channel
   int *err_flag;
 };
-
-// The pieces of work of one CTA, in the order every warp role walks them.
-struct CtPieces {
-  long long tile, total_tiles, u, u1;
-  int stride, num_k, stream;
-  __device__ CtPieces(const ConvTmaParams &p, long long tiles) {
-    stream = p.streamk;
-    num_k = p.num_k;
-    total_tiles = tiles;
-    tile = blockIdx.x;
-    stride = gridDim.x;
-    u = (long long)blockIdx.x * p.units / gridDim.x;
-    u1 = (long long)(blockIdx.x + 1) * p.units / gridDim.x;
-  }
-  // k-blocks [kb0, kb1) of tile t
-  __device__ bool next(long long &t, int &kb0, int &kb1) {
-    if (!stream) {
-      if (tile >= total_tiles) return false;
-      t = tile;
-      kb0 = 0;
-      kb1 = num_k;
-      tile += stride;
-      return true;
-    }
-    if (u >= u1) return false;
-    t = u / num_k;
-    kb0 = (int)(u - t * num_k);
-    const long long rem = u1 - u;
-    kb1 = (num_k - kb0) <= rem ? num_k : kb0 + (int)rem;
-    u += kb1 - kb0;
-    return true;
-  }
-};
-
-// The CTA whose share holds unit `unit` (shares start at c * units / grid).
-__device__ __forceinline__ int ct_cta_of(long long unit, long long units, int grid) {
-  int c = (int)(unit * grid / units);
-  while (c + 1 < grid && (long long)(c + 1) * units / grid <= unit) ++c;
-  while (c > 0 && (long long)c * units / grid > unit) --c;
-  return c;
-}
 
 __device__ __forceinline__ float ct_tf32(float v) {
   uint32_t r;
@@ -190,9 +144,8 @@ __global__ void __launch_bounds__(CT_THREADS, 1)
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      CtPieces pieces(p, total_tiles);
-      long long tile;
-      int kb0, kb1;
+      TilePieces pieces(p.streamk, p.units, p.num_k, (int)total_tiles);
+      int tile, kb0, kb1;
       while (ok && pieces.next(tile, kb0, kb1)) {
         const int mt = (int)(tile / p.tiles_n), nt = (int)(tile % p.tiles_n);
         // first output position of the tile -> window origin in the input
@@ -238,9 +191,8 @@ __global__ void __launch_bounds__(CT_THREADS, 1)
       uint32_t phase = 0;
       int use = 0;
       bool ok = true;
-      CtPieces pieces(p, total_tiles);
-      long long tile;
-      int kb0, kb1;
+      TilePieces pieces(p.streamk, p.units, p.num_k, (int)total_tiles);
+      int tile, kb0, kb1;
       while (ok && pieces.next(tile, kb0, kb1)) {
         for (int kc = kb0; kc < kb1 && ok; kc += p.chunk_k, ++use) {
           const int buf = use & 1;
@@ -298,9 +250,8 @@ __global__ void __launch_bounds__(CT_THREADS, 1)
       epi_phase ^= 1;
       return done;
     };
-    CtPieces pieces(p, total_tiles);
-    long long tile;
-    int kb0, kb1;
+    TilePieces pieces(p.streamk, p.units, p.num_k, (int)total_tiles);
+    int tile, kb0, kb1;
     while (ok && pieces.next(tile, kb0, kb1)) {
       const int mt = (int)(tile / p.tiles_n), nt = (int)(tile % p.tiles_n);
       float acc[HALF];
@@ -331,20 +282,19 @@ __global__ void __launch_bounds__(CT_THREADS, 1)
       }
       if (kb0 != 0 || kb1 != p.num_k) {
         // part of a tile: leave it in the workspace; the CTA that delivers the last part finishes the tile
-        const long long tile_u0 = tile * p.num_k;
-        const long long my_u0 = (long long)blockIdx.x * p.units / gridDim.x;
+        const int tile_u0 = tile * p.num_k;
         const size_t slot_floats = (size_t)CT_BM * BN;
         const size_t within = ((size_t)(warp - 2) * HALF) * 32 + lane;
         if (ok) {
-          float *wsp = p.ws + (size_t)(2 * blockIdx.x + (my_u0 >= tile_u0 + kb0 ? 0 : 1)) * slot_floats + within;
+          float *wsp = p.ws + (size_t)share_slot(blockIdx.x, tile_u0, p.units, gridDim.x) * slot_floats + within;
 #pragma unroll
           for (int j = 0; j < HALF; ++j) __stcg(wsp + j * 32, acc[j]);
         } else {
           s_fail = 1;
         }
         __threadfence();
-        const int c_first = ct_cta_of(tile_u0, p.units, gridDim.x);
-        const int c_last = ct_cta_of(tile_u0 + p.num_k - 1, p.units, gridDim.x);
+        const int c_first = share_of_unit(tile_u0, p.units, gridDim.x);
+        const int c_last = share_of_unit(tile_u0 + p.num_k - 1, p.units, gridDim.x);
         bool met = epi_sync();
         if (warp == 2 && lane == 0)
           s_last = (atomicAdd(p.tile_count + tile, 1) == c_last - c_first) ? 1 : 0;
@@ -358,10 +308,9 @@ __global__ void __launch_bounds__(CT_THREADS, 1)
 #pragma unroll
         for (int j = 0; j < HALF; ++j) acc[j] = 0.f;
         for (int c = c_first; c <= c_last; ++c) {  // k order: CTA c's share precedes CTA c + 1's
-          const long long cu0 = (long long)c * p.units / gridDim.x;
-          const float *src = p.ws + (size_t)(2 * c + (cu0 >= tile_u0 ? 0 : 1)) * slot_floats + within;
+          const float *src = p.ws + (size_t)share_slot(c, tile_u0, p.units, gridDim.x) * slot_floats + within;
 #pragma unroll
-          for (int j = 0; j < HALF; ++j) acc[j] = __fadd_rn(acc[j], __ldcg(src + j * 32));
+          for (int j = 0; j < HALF; ++j) acc[j] = __fadd_rn(acc[j], ptx::ld_cg_ordered(src + j * 32));
         }
       }
       if (!ok) break;
@@ -619,19 +568,21 @@ static int launch_conv_tma(b200_engine *e, const CUtensorMap *tm, ConvTmaParams 
   const long long tiles = (long long)p.tiles_m * p.tiles_n;
   int grid = (int)std::min<long long>(tiles, e->sm_count);
   // Whole tiles per CTA leave SMs idle when the tiles do not fill the last wave: with fewer tiles
-  // than SMs, or e.g. 169 tiles on 148 SMs. Below 85 % occupancy of the waves the k range is shared
-  // out instead (see ConvTmaParams::streamk), at least two k-blocks per CTA.
-  const long long waves = (tiles + e->sm_count - 1) / e->sm_count;
+  // than SMs, or e.g. 169 tiles on 148 SMs. Then the k range is shared out instead (TilePieces).
   void *ws = nullptr;
   p.streamk = 0;
-  p.units = tiles * p.num_k;
-  if (p.num_k >= 4 && (double)tiles < 0.85 * (double)(waves * e->sm_count) && !(e->flags & B200_ENGINE_NO_STREAMK)) {
-    grid = (int)std::max<long long>(1, std::min<long long>(e->sm_count, p.units / 2));
+  p.units = 0;
+  if (tiles >= (1LL << 31))
+    return set_error(e, B200_ERR_UNSUPPORTED, "convolution: %lld output tiles are more than one launch takes", tiles);
+  int sk_grid = grid;
+  if (!(e->flags & B200_ENGINE_NO_STREAMK) && streamk_pays(tiles, p.num_k, e->sm_count, &sk_grid)) {
+    grid = sk_grid;
     const long long ws_bytes = 2LL * grid * CT_BM * BN * 4;
     const long long cnt_bytes = (tiles * 4 + 255) / 256 * 256;
     int rc = b200_get(e, cnt_bytes + ws_bytes, &ws);
     if (rc == B200_OK) {
       p.streamk = 1;
+      p.units = (int)(tiles * p.num_k);  // small: k sharing is for launches of few tiles
       p.tile_count = (int *)ws;
       p.ws = (float *)((char *)ws + cnt_bytes);
       B200_CHECK_CUDA(e, cudaMemsetAsync(ws, 0, (size_t)cnt_bytes, e->stream));

@@ -2,14 +2,15 @@
 // in tensor memory. Stands where Engine.MatMul calls cuBLAS Sgemm in gorgonia
 // (cuda/linalg.go:110-229) and where batchedMatMul loops over slices (operatorLinAlg.go:435-502).
 //
-// One persistent CTA per SM, 6 warps with fixed roles:
+// One persistent CTA per SM, 10 warps with fixed roles:
 //   warp 0     TMA producer: one lane queues the A and B boxes of each k-block into a ring of
 //              shared-memory stages (128-byte swizzle) and arms the stage's "full" mbarrier;
 //   warp 1     MMA issuer: one lane issues tcgen05.mma for each 32-byte k-slice of a stage,
 //              commits the stage's "empty" mbarrier when the tensor core has read it, and commits
 //              the accumulator's "full" mbarrier after the last k-block. Owns the TMEM allocation;
-//   warps 2-5  epilogue: each drains its 32-lane quarter of the accumulator with tcgen05.ld,
-//              applies the fused bias/activation and stores rows of C with 128-bit stores.
+//   warps 2-9  epilogue: each drains one half of the columns of its 32-lane quarter of the
+//              accumulator with tcgen05.ld, applies the fused bias/activation and stores rows of C
+//              with 128-bit stores.
 // The accumulator is double-buffered in TMEM (2 x BN columns), so the epilogue of tile i runs
 // while the MMAs of tile i+1 are issued.
 //
@@ -52,7 +53,7 @@ int gemm_simt(b200_engine *e, int dtype, int transA, int transB, long long M, lo
 // ------------------------------------------------------------------------------------------
 
 constexpr int TC_BM = 128;
-constexpr int TC_THREADS = 192;
+constexpr int TC_THREADS = 320;  // 10 warps: TMA, MMA, 8 epilogue
 constexpr int TC_ROW_BYTES = 128;  // one swizzle row: 64 bf16 or 32 fp32 along the contiguous dim
 
 struct GemmTcParams {
@@ -67,6 +68,11 @@ struct GemmTcParams {
   int stages;
   int c_vec;                    // 1: rows of C can be stored with 128-bit stores
   int a_zmul, b_zmul;           // 0: the operand is shared by all batch entries (z coordinate 0)
+  // how the work is shared between the CTAs (TilePieces, tc_common.cuh); 3xTF32 only
+  int streamk;
+  int units;                    // tiles * num_k (0 when the k range is not shared)
+  float *ws;                    // partial tiles, 2 slots of TC_BM x BN floats per CTA
+  int *tile_count;              // parts delivered per tile, zeroed before the launch
   Epilogue ep;
   int *err_flag;
 };
@@ -99,8 +105,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
 
   extern __shared__ __align__(1024) unsigned char tc_smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[MAX_STAGES], empty_bar[MAX_STAGES], acc_full[2], acc_empty[2];
+  __shared__ __align__(8) uint64_t epi_bar;  // the 8 epilogue warps meet here when a partial tile is handed over
   __shared__ uint32_t tmem_base_s;
-  __shared__ int s_fail;
+  __shared__ int s_fail, s_last;
 
   // the ring must start on a 1024-byte boundary for the 128-byte swizzle
   unsigned char *smem = reinterpret_cast<unsigned char *>(((uintptr_t)tc_smem_raw + 1023) & ~(uintptr_t)1023);
@@ -116,10 +123,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
     }
     for (int b = 0; b < 2; ++b) {
       ptx::mbar_init(&acc_full[b], 1);
-      ptx::mbar_init(&acc_empty[b], 4);  // one arrival per epilogue warp
+      ptx::mbar_init(&acc_empty[b], 8);  // one arrival per epilogue warp
     }
+    ptx::mbar_init(&epi_bar, 8);
     ptx::fence_mbar_init();
     s_fail = 0;
+    s_last = 0;
   }
   if (warp == 1) {
     ptx::tmem_alloc(&tmem_base_s, TMEM_COLS);
@@ -158,10 +167,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (long long tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      TilePieces pieces(p.streamk, p.units, p.num_k, (int)total_tiles);
+      int tile, kb0, kb1;
+      while (ok && pieces.next(tile, kb0, kb1)) {
         int bz, mb, nb;
         decode(tile, bz, mb, nb);
-        for (int kb = 0; kb < p.num_k; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!ptx::mbar_wait(&empty_bar[stage], phase ^ 1)) {
             ok = false;
             break;
@@ -207,8 +218,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
       uint32_t phase = 0;
       int use = 0;  // accumulator-buffer uses so far (one per k-chunk)
       bool ok = true;
-      for (long long tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-        for (int kc = 0; kc < p.num_k && ok; kc += p.chunk_k, ++use) {
+      TilePieces pieces(p.streamk, p.units, p.num_k, (int)total_tiles);
+      int tile, kb0, kb1;
+      while (ok && pieces.next(tile, kb0, kb1)) {
+        for (int kc = kb0; kc < kb1 && ok; kc += p.chunk_k, ++use) {
           const int buf = use & 1;
           const uint32_t acc_phase = (uint32_t)((use >> 1) & 1);
           // the epilogue must have drained this accumulator buffer (first use passes at once)
@@ -219,7 +232,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
           ptx::tc_fence_after_sync();
           const uint32_t d_main = tmem_base + (uint32_t)(buf * ACC_COLS);
           const uint32_t d_tail = d_main + BN;  // 3xTF32 only: the small cross terms
-          const int kend = kc + p.chunk_k < p.num_k ? kc + p.chunk_k : p.num_k;
+          const int kend = kc + p.chunk_k < kb1 ? kc + p.chunk_k : kb1;
           for (int kb = kc; kb < kend; ++kb) {
             if (!ptx::mbar_wait(&full_bar[stage], phase)) {
               ok = false;
@@ -262,21 +275,37 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
       if (!ok) s_fail = 1;
     }
   } else {
-    // ---------------- epilogue: warps 2..5 ----------------
-    const int quarter = warp & 3;  // the TMEM lanes this warp may read: 32*quarter .. +31
+    // ---------------- epilogue: warps 2..9 ----------------
+    constexpr int HALF = BN / 2;
+    const int quarter = warp & 3;        // the TMEM lanes this warp may read: 32*quarter .. +31
+    const int half = (warp - 2) >> 2;    // which half of the tile's columns it takes
+    const int ch0 = half * HALF;
     int use = 0;
+    uint32_t epi_phase = 0;
     bool ok = true;
-    for (long long tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-      int bz, mb, nb;
-      decode(tile, bz, mb, nb);
-      const long long m = (long long)mb * TC_BM + quarter * 32 + lane;
-      float *crow = reinterpret_cast<float *>(p.C) + (long long)bz * p.strideC + m * p.ldc;
-      const long long n0 = (long long)nb * BN;
+    // the epilogue warps' own rendezvous: an mbarrier, so that this wait is bounded like every other
+    auto epi_sync = [&]() -> bool {
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(&epi_bar);
+      const bool done = ptx::mbar_wait_relaxed(&epi_bar, epi_phase, 32);
+      epi_phase ^= 1;
+      return done;
+    };
+    TilePieces pieces(p.streamk, p.units, p.num_k, (int)total_tiles);
+    int tile, kb0, kb1;
+    while (ok && pieces.next(tile, kb0, kb1)) {
       const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
 
+      // where the tile lies is worked out when a store needs it, not before the k loop: the fold
+      // below wants every register it can get
       auto store32 = [&](const float(&v)[32], int c) {
+        int bz, mb, nb;
+        decode(tile, bz, mb, nb);
+        const long long m = (long long)mb * TC_BM + quarter * 32 + lane;
+        float *crow = reinterpret_cast<float *>(p.C) + (long long)bz * p.strideC + m * p.ldc;
+        const long long n0 = (long long)nb * BN;
         if (m >= p.M) return;
-        const long long nbase = n0 + c;
+        const long long nbase = n0 + ch0 + c;
         if (p.C_hi) {
           // the result as the next product's A operand: TF32 head and tail, 16 bytes at a time;
           // columns between N and the pitch hold zeros
@@ -339,9 +368,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
         }
         ptx::tc_fence_after_sync();
 #pragma unroll 1
-        for (int c = 0; c < BN; c += 32) {
+        for (int c = 0; c < HALF; c += 32) {
           uint32_t r[32];
-          ptx::tmem_ld_32x32(lane_addr + (uint32_t)(buf * ACC_COLS + c), r);
+          ptx::tmem_ld_32x32(lane_addr + (uint32_t)(buf * ACC_COLS + ch0 + c), r);
           ptx::tmem_ld_wait();
           float v[32];
 #pragma unroll
@@ -356,10 +385,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
         // with the length of the accumulation chain. Chains are therefore cut into k-chunks; each
         // chunk's two accumulators (main and cross terms) are folded here into fp32 registers
         // with round-to-nearest adds while the next chunk is being multiplied.
-        float acc[TERMS == 3 ? BN : 1];
+        float acc[TERMS == 3 ? HALF : 1];
 #pragma unroll
-        for (int j = 0; j < (TERMS == 3 ? BN : 1); ++j) acc[j] = 0.f;
-        for (int kc = 0; kc < p.num_k && ok; kc += p.chunk_k) {
+        for (int j = 0; j < (TERMS == 3 ? HALF : 1); ++j) acc[j] = 0.f;
+        for (int kc = kb0; kc < kb1 && ok; kc += p.chunk_k) {
           const int buf = use & 1;
           const uint32_t acc_phase = (uint32_t)((use >> 1) & 1);
           ++use;
@@ -369,22 +398,55 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
           }
           ptx::tc_fence_after_sync();
 #pragma unroll
-          for (int c = 0; c < (TERMS == 3 ? BN : 0); c += 32) {
-            uint32_t rm[32], rt[32];
-            ptx::tmem_ld_32x32(lane_addr + (uint32_t)(buf * ACC_COLS + c), rm);
-            ptx::tmem_ld_32x32(lane_addr + (uint32_t)(buf * ACC_COLS + BN + c), rt);
+          for (int c = 0; c < (TERMS == 3 ? HALF : 0); c += 16) {
+            uint32_t rm[16], rt[16];
+            ptx::tmem_ld_32x16(lane_addr + (uint32_t)(buf * ACC_COLS + ch0 + c), rm);
+            ptx::tmem_ld_32x16(lane_addr + (uint32_t)(buf * ACC_COLS + BN + ch0 + c), rt);
             ptx::tmem_ld_wait();
 #pragma unroll
-            for (int j = 0; j < 32; ++j)
+            for (int j = 0; j < 16; ++j)
               acc[c + j] = __fadd_rn(acc[c + j], __fadd_rn(__uint_as_float(rm[j]), __uint_as_float(rt[j])));
           }
           ptx::tc_fence_before_sync();
           __syncwarp();
           if (lane == 0) ptx::mbar_arrive(&acc_empty[buf]);
         }
+        if (kb0 != 0 || kb1 != p.num_k) {
+          // part of a tile: leave it in the workspace; the CTA that delivers the last part finishes the tile
+          constexpr int NACC = TERMS == 3 ? HALF : 1;
+          const int tile_u0 = tile * p.num_k;
+          const size_t slot_floats = (size_t)TC_BM * BN;
+          const size_t within = ((size_t)(warp - 2) * HALF) * 32 + lane;
+          if (ok) {
+            float *wsp = p.ws + (size_t)share_slot(blockIdx.x, tile_u0, p.units, gridDim.x) * slot_floats + within;
+#pragma unroll
+            for (int j = 0; j < NACC; ++j) __stcg(wsp + j * 32, acc[j]);
+          } else {
+            s_fail = 1;
+          }
+          __threadfence();
+          const int c_first = share_of_unit(tile_u0, p.units, gridDim.x);
+          const int c_last = share_of_unit(tile_u0 + p.num_k - 1, p.units, gridDim.x);
+          bool met = epi_sync();
+          if (warp == 2 && lane == 0) s_last = (atomicAdd(p.tile_count + tile, 1) == c_last - c_first) ? 1 : 0;
+          met = epi_sync() && met;
+          if (!met || *(volatile int *)&s_fail) {
+            ok = false;
+            break;
+          }
+          if (!*(volatile int *)&s_last) continue;
+          __threadfence();
+#pragma unroll
+          for (int j = 0; j < NACC; ++j) acc[j] = 0.f;
+          for (int c = c_first; c <= c_last; ++c) {  // k order: CTA c's share precedes CTA c + 1's
+            const float *src = p.ws + (size_t)share_slot(c, tile_u0, p.units, gridDim.x) * slot_floats + within;
+#pragma unroll
+            for (int j = 0; j < NACC; ++j) acc[j] = __fadd_rn(acc[j], ptx::ld_cg_ordered(src + j * 32));
+          }
+        }
         if (ok) {
 #pragma unroll
-          for (int c = 0; c < (TERMS == 3 ? BN : 0); c += 32) {
+          for (int c = 0; c < (TERMS == 3 ? HALF : 0); c += 32) {
             float v[32];
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] = acc[c + j];
@@ -599,8 +661,13 @@ int gemm_tc_core(b200_engine *e, int terms, bool a_mn, bool b_mn, long long M, l
   const int bk = TC_ROW_BYTES / es;
   // tile width: the widest that still gives every SM a tile, to keep small problems spread out
   const int tiles_m = (int)((M + TC_BM - 1) / TC_BM);
+  const bool may_share_k = terms == 3 && !(e->flags & B200_ENGINE_NO_STREAMK);
   int bn = terms == 1 ? 256 : 128;
-  while (bn > 64 && (long long)tiles_m * ((N + bn - 1) / bn) * batch < e->sm_count) bn /= 2;
+  // tile width: without k sharing, the widest that still gives every SM a tile, to keep small
+  // problems spread out; with it (3xTF32) the widest the matrix fills, since wide MMAs cost less per
+  // flop and the k range spreads the work instead
+  if (!may_share_k)
+    while (bn > 64 && (long long)tiles_m * ((N + bn - 1) / bn) * batch < e->sm_count) bn /= 2;
   while (bn > 64 && bn / 2 >= N) bn /= 2;
   const int tiles_n = (int)((N + bn - 1) / bn);
 
@@ -655,15 +722,42 @@ int gemm_tc_core(b200_engine *e, int terms, bool a_mn, bool b_mn, long long M, l
   const size_t budget = std::min<size_t>(e->smem_optin, 227 * 1024) - 4096;  // static part + alignment slack
   p.stages = (int)std::max<size_t>(2, std::min<size_t>(8, budget / stage_bytes));
   const long long total_tiles = (long long)tiles_m * tiles_n * batch;
-  const int grid = (int)std::min<long long>(total_tiles, e->sm_count);
+  if (total_tiles >= (1LL << 31))
+    return set_error(e, B200_ERR_UNSUPPORTED, "b200_gemm: %lld output tiles are more than one launch takes", total_tiles);
+  int grid = (int)std::min<long long>(total_tiles, e->sm_count);
+  p.streamk = 0;
+  p.units = 0;
+  p.ws = nullptr;
+  p.tile_count = nullptr;
 
   if (terms == 1) {
     if (bn == 256) return launch_tc_layout<1, 256>(e, a_mn, b_mn, tm, p, grid);
     if (bn == 128) return launch_tc_layout<1, 128>(e, a_mn, b_mn, tm, p, grid);
     return launch_tc_layout<1, 64>(e, a_mn, b_mn, tm, p, grid);
   }
-  if (bn == 128) return launch_tc_layout<3, 128>(e, a_mn, b_mn, tm, p, grid);
-  return launch_tc_layout<3, 64>(e, a_mn, b_mn, tm, p, grid);
+  // whole tiles per CTA would leave SMs idle: share out the k range instead (TilePieces)
+  void *ws = nullptr;
+  int sk_grid = grid;
+  if (may_share_k && streamk_pays(total_tiles, p.num_k, e->sm_count, &sk_grid)) {
+    const long long ws_bytes = 2LL * sk_grid * TC_BM * bn * 4;
+    const long long cnt_bytes = (total_tiles * 4 + 255) / 256 * 256;
+    if (b200_get(e, cnt_bytes + ws_bytes, &ws) == B200_OK) {
+      p.streamk = 1;
+      p.units = (int)(total_tiles * p.num_k);  // small: k sharing is for launches of few tiles
+      grid = sk_grid;
+      p.tile_count = (int *)ws;
+      p.ws = (float *)((char *)ws + cnt_bytes);
+      cudaError_t me = cudaMemsetAsync(ws, 0, (size_t)cnt_bytes, e->stream);
+      if (me != cudaSuccess) {
+        b200_put(e, ws, 0);
+        return set_error(e, B200_ERR_CUDA, "cudaMemsetAsync failed: %s", cudaGetErrorString(me));
+      }
+    }  // else: no room for the partial tiles, whole tiles per CTA
+  }
+  const int rc = bn == 128 ? launch_tc_layout<3, 128>(e, a_mn, b_mn, tm, p, grid)
+                           : launch_tc_layout<3, 64>(e, a_mn, b_mn, tm, p, grid);
+  if (ws) b200_put(e, ws, 0);  // stream order: whoever gets the block next runs after this kernel
+  return rc;
 }
 
 // Splits a row-major fp32 matrix (rows x cols, pitch ld, `batch` of them) into TF32 head and tail

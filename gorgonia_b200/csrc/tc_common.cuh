@@ -54,6 +54,68 @@ __host__ __device__ constexpr uint32_t make_idesc(int fmt, int a_mn, int b_mn, i
 }
 
 
+// ---- sharing a launch's work between the CTAs ---------------------------------------------------
+// whole == 1: CTA c takes tiles c, c + grid, ... and every k-block of each. whole == 0 ("stream-K"):
+// the (tile, k-block) units of the whole problem, tile-major, are cut into `grid` equal contiguous
+// shares, so a launch with fewer tiles than SMs, or with a ragged last wave, still keeps every SM
+// busy for the same time. A share that holds only part of a tile's k range leaves its fp32 partial
+// tile in a workspace; whichever CTA delivers a tile's last missing part adds the parts in k order
+// (the result therefore does not depend on who that is) and stores the tile. Every warp role of a
+// kernel walks the same pieces through this iterator.
+struct TilePieces {
+  // 32-bit throughout: the host refuses launches of 2^31 tiles or units
+  int tile, total_tiles, u, u1, num_k, stream;
+  __device__ TilePieces(int streamk, int units, int num_k_, int tiles) {
+    stream = streamk;
+    num_k = num_k_;
+    total_tiles = tiles;
+    tile = blockIdx.x;
+    u = (int)((long long)blockIdx.x * units / gridDim.x);
+    u1 = (int)((long long)(blockIdx.x + 1) * units / gridDim.x);
+  }
+  // the next piece: k-blocks [kb0, kb1) of tile t
+  __device__ bool next(int &t, int &kb0, int &kb1) {
+    if (!stream) {
+      if (tile >= total_tiles) return false;
+      t = tile;
+      kb0 = 0;
+      kb1 = num_k;
+      tile += gridDim.x;
+      return true;
+    }
+    if (u >= u1) return false;
+    t = u / num_k;
+    kb0 = u - t * num_k;
+    const int rem = u1 - u;
+    kb1 = (num_k - kb0) <= rem ? num_k : kb0 + rem;
+    u += kb1 - kb0;
+    return true;
+  }
+};
+
+// The CTA whose share holds unit `unit` (shares start at c * units / grid).
+__device__ __forceinline__ int share_of_unit(int unit, int units, int grid) {
+  int c = (int)((long long)unit * grid / units);
+  while (c + 1 < grid && (int)((long long)(c + 1) * units / grid) <= unit) ++c;
+  while (c > 0 && (int)((long long)c * units / grid) > unit) --c;
+  return c;
+}
+// Workspace slot of the part of a tile (whose first unit is tile_u0) that CTA c holds: 2c if the
+// part begins c's share, 2c + 1 if it ends it (a share has at most one of each).
+__device__ __forceinline__ int share_slot(int c, int tile_u0, int units, int grid) {
+  return 2 * c + ((int)((long long)c * units / grid) >= tile_u0 ? 0 : 1);
+}
+
+// Whether a launch of `tiles` tiles of `num_k` k-blocks shares out the k range, and over how many
+// CTAs: only when whole tiles would fill less than 85 % of the waves, with at least two k-blocks per CTA.
+inline bool streamk_pays(long long tiles, int num_k, int sm_count, int *grid) {
+  const long long waves = (tiles + sm_count - 1) / sm_count;
+  if (num_k < 4 || (double)tiles >= 0.85 * (double)(waves * sm_count)) return false;
+  const long long g = tiles * num_k / 2;
+  *grid = (int)(g < 1 ? 1 : (g > sm_count ? sm_count : g));
+  return true;
+}
+
 // A 3-D tensor map (contiguous dim, rows, batch) over a row-major matrix with `ld` elements per
 // row, 128-byte swizzle (atom32: the 32-byte-atom variant that 32-bit MN-major operands need).
 // es = element size in bytes (2: bfloat16, 4: float32). Defined in gemm_tc.cu.

@@ -9,9 +9,11 @@ per 128-wide tile) and a whole-result property closes the gap:
 
   - matrix products: (A.B).v == A.(B.v) for a random sign vector v, evaluated in double on the host,
     which no skipped, repeated or misplaced tile survives;
-  - graphs: the batch is a small set of distinct images repeated; the oracle checks the distinct
-    ones and every repetition must equal its original bit for bit (each output element has one
-    reduction order whatever tile it lands in).
+  - graphs: the batch is a small set of distinct images repeated, and every repetition is held to
+    the oracle's result for its original. Where no tile's k range is shared between CTAs every
+    output element has one summation order whatever tile it lands in, and the repetitions are
+    bit-equal (LeNet at 8192); where it is shared (the late tiny-YOLO layers) they agree within the
+    tolerance.
 
 Tolerances as everywhere: 1e-5 * max(|r|, rms(r)) for float32 products, 1e-2 on that scale for
 bfloat16 operands, bit-exact for Outer."""
@@ -203,8 +205,8 @@ def test_tiny_yolo_at_benchmark_batch(roomy):
     m.x.set(np.tile(x2, (B // 2, 1, 1, 1)))
     got = m.forward().numpy()
     assert got.shape == (B, 125, 13, 13)
-    assert_gemm_close(got[:2], graphs.tiny_yolo(m, x2), 1e-5)
-    assert_bits_equal(got.reshape(B // 2, 2, 125, 13, 13), np.broadcast_to(got[:2], (B // 2, 2, 125, 13, 13)).copy())
+    want = graphs.tiny_yolo(m, x2)
+    assert_gemm_close(got.reshape(B // 2, 2, 125, 13, 13), np.broadcast_to(want, (B // 2, 2, 125, 13, 13)), 1e-5)
     m.record()
     m.replay()
     assert_bits_equal(m.out.numpy(), got)
@@ -221,8 +223,7 @@ def test_tiny_yolo_small_shards(roomy):
         m.x.set(np.tile(x2, (B // 2, 1, 1, 1)))
         got = m.forward().numpy()
         if ref is None:
-            ref = got[:2].copy()
-            assert_gemm_close(ref, graphs.tiny_yolo(m, x2), 1e-5)
+            ref = graphs.tiny_yolo(m, x2)
         assert_gemm_close(got.reshape(B // 2, 2, 125, 13, 13), np.broadcast_to(ref, (B // 2, 2, 125, 13, 13)), 1e-5)
         e.Signal()
         e.ResetAllocator()
