@@ -213,9 +213,65 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(int transA, int transB, 
   }
 }
 
+// ---- products with very few output columns (a classifier's last layer: 256 x 100 by 100 x 10) -----
+// A 64 x 64 tile would be mostly padding and the whole product would sit on a handful of SMs. Here a
+// warp owns one row of C: lane l takes k = l, l + 32, ... for all N <= 16 columns, the 32 partial
+// sums per column are folded by shuffles in a fixed order, and lane n stores column n.
+template <typename T>
+__global__ void __launch_bounds__(256) gemm_skinny_kernel(int transB, long long M, int N, long long K,
+                                                          const T *__restrict__ A, long long lda,
+                                                          const T *__restrict__ B, long long ldb, T *__restrict__ C,
+                                                          long long ldc, long long strideA, long long strideB,
+                                                          long long strideC, Epilogue ep) {
+  constexpr int NMAX = 16;
+  A += (long long)blockIdx.y * strideA;
+  B += (long long)blockIdx.y * strideB;
+  C += (long long)blockIdx.y * strideC;
+  const int lane = threadIdx.x & 31;
+  const long long warps = (long long)gridDim.x * (blockDim.x >> 5);
+  for (long long m = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); m < M; m += warps) {
+    T acc[NMAX];
+#pragma unroll
+    for (int n = 0; n < NMAX; ++n) acc[n] = T(0);
+    const T *arow = A + m * lda;
+    for (long long k = lane; k < K; k += 32) {
+      const T a = arow[k];
+#pragma unroll
+      for (int n = 0; n < NMAX; ++n)
+        if (n < N) acc[n] = fma_(a, transB ? B[(long long)n * ldb + k] : B[k * ldb + n], acc[n]);
+    }
+    T mine = T(0);
+#pragma unroll
+    for (int n = 0; n < NMAX; ++n) {
+      T v = acc[n];
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+      if (lane == n) mine = v;
+    }
+    if (lane < N) {
+      const T o = apply_epilogue<T>(mine, ep, m, lane);
+      C[m * ldc + lane] = ep.accumulate ? epi_add<T>(C[m * ldc + lane], o) : o;
+    }
+  }
+}
+
 int gemm_simt(b200_engine *e, int dtype, int transA, int transB, long long M, long long N, long long K,
               const void *A, long long lda, const void *B, long long ldb, void *C, long long ldc, long long batch,
               long long strideA, long long strideB, long long strideC, const Epilogue &ep) {
+  if (!transA && N <= 16 && M >= 32 && K >= 1 && batch <= 65535) {
+    const unsigned blocks = (unsigned)std::max<long long>(1, std::min<long long>((M + 7) / 8, (long long)e->sm_count * 8));
+    dim3 sgrid(blocks, (unsigned)batch);
+    if (dtype == B200_F32)
+      gemm_skinny_kernel<float><<<sgrid, 256, 0, e->stream>>>(transB, M, (int)N, K, (const float *)A, lda,
+                                                             (const float *)B, ldb, (float *)C, ldc, strideA, strideB,
+                                                             strideC, ep);
+    else
+      gemm_skinny_kernel<double><<<sgrid, 256, 0, e->stream>>>(transB, M, (int)N, K, (const double *)A, lda,
+                                                              (const double *)B, ldb, (double *)C, ldc, strideA,
+                                                              strideB, strideC, ep);
+    B200_CHECK_LAUNCH(e, "gemm_skinny_kernel");
+    return B200_OK;
+  }
   dim3 grid((unsigned)((N + 63) / 64), (unsigned)((M + 63) / 64), (unsigned)batch);
   if (dtype == B200_F32)
     gemm_simt_kernel<float><<<grid, 256, 0, e->stream>>>(transA, transB, M, N, K, (const float *)A, lda,

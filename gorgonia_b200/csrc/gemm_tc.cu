@@ -663,11 +663,10 @@ int gemm_tc_core(b200_engine *e, int terms, bool a_mn, bool b_mn, long long M, l
   const int tiles_m = (int)((M + TC_BM - 1) / TC_BM);
   const bool may_share_k = terms == 3 && !(e->flags & B200_ENGINE_NO_STREAMK);
   int bn = terms == 1 ? 256 : 128;
-  // tile width: without k sharing, the widest that still gives every SM a tile, to keep small
-  // problems spread out; with it (3xTF32) the widest the matrix fills, since wide MMAs cost less per
-  // flop and the k range spreads the work instead
-  if (!may_share_k)
-    while (bn > 64 && (long long)tiles_m * ((N + bn - 1) / bn) * batch < e->sm_count) bn /= 2;
+  // tile width: the widest that still gives every SM a tile. A problem too small for that gets the
+  // narrow tiles whether or not its k range is shared out as well: one SM pulls operands from L2 at a
+  // fixed rate, so more CTAs on more SMs shorten the k loop of each
+  while (bn > 64 && (long long)tiles_m * ((N + bn - 1) / bn) * batch < e->sm_count) bn /= 2;
   while (bn > 64 && bn / 2 >= N) bn /= 2;
   const int tiles_n = (int)((N + bn - 1) / bn);
 

@@ -107,12 +107,20 @@ __device__ __forceinline__ int share_slot(int c, int tile_u0, int units, int gri
 }
 
 // Whether a launch of `tiles` tiles of `num_k` k-blocks shares out the k range, and over how many
-// CTAs: only when whole tiles would fill less than 85 % of the waves, with at least two k-blocks per CTA.
+// CTAs. It pays when whole tiles would fill less than 85 % of the waves. The CTA that finishes a
+// tile reads its parts one after the other (about a microsecond each: one SM's share of the L2
+// bandwidth), while a k-block costs about 0.6 microseconds, so a tile is cut into at most
+// sqrt(0.6 num_k) parts: beyond that the fix-up costs more than the shorter k loop saves.
 inline bool streamk_pays(long long tiles, int num_k, int sm_count, int *grid) {
   const long long waves = (tiles + sm_count - 1) / sm_count;
   if (num_k < 4 || (double)tiles >= 0.85 * (double)(waves * sm_count)) return false;
-  const long long g = tiles * num_k / 2;
-  *grid = (int)(g < 1 ? 1 : (g > sm_count ? sm_count : g));
+  int parts = 1;
+  while ((parts + 1) * (parts + 1) <= 0.6 * num_k) ++parts;
+  long long g = tiles * parts;
+  if (g > sm_count) g = sm_count;
+  if (g > tiles * (long long)num_k / 2) g = tiles * (long long)num_k / 2;
+  if (g <= tiles && tiles <= sm_count) return false;  // nothing to share out
+  *grid = (int)(g < 1 ? 1 : g);
   return true;
 }
 

@@ -10,10 +10,9 @@ per 128-wide tile) and a whole-result property closes the gap:
   - matrix products: (A.B).v == A.(B.v) for a random sign vector v, evaluated in double on the host,
     which no skipped, repeated or misplaced tile survives;
   - graphs: the batch is a small set of distinct images repeated, and every repetition is held to
-    the oracle's result for its original. Where no tile's k range is shared between CTAs every
-    output element has one summation order whatever tile it lands in, and the repetitions are
-    bit-equal (LeNet at 8192); where it is shared (the late tiny-YOLO layers) they agree within the
-    tolerance.
+    the oracle's result for its original (a launch that shares tiles' k ranges between CTAs sums
+    different tiles in different groupings, so repetitions agree within the tolerance, not bit for
+    bit).
 
 Tolerances as everywhere: 1e-5 * max(|r|, rms(r)) for float32 products, 1e-2 on that scale for
 bfloat16 operands, bit-exact for Outer."""
@@ -180,9 +179,8 @@ def test_lenet_at_benchmark_batch(roomy):
     m.x.set(np.tile(x64, (B // 64, 1, 1, 1)))
     got = m.forward().numpy()
     want = graphs.lenet(m, x64)
-    assert_gemm_close(got[:64], want, 1e-5)
-    assert np.array_equal(got[:64].argmax(1), want.argmax(1))
-    assert_bits_equal(got.reshape(B // 64, 64, 10), np.broadcast_to(got[:64], (B // 64, 64, 10)).copy())
+    assert_gemm_close(got.reshape(B // 64, 64, 10), np.broadcast_to(want, (B // 64, 64, 10)), 1e-5)
+    assert np.array_equal(got.reshape(B // 64, 64, 10).argmax(2), np.broadcast_to(want.argmax(1), (B // 64, 64)))
     # and 64 images spread over the batch with nothing repeated
     xr = util.uniform(371, (B, 1, 28, 28))
     m.x.set(xr)
