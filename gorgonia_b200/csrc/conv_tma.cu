@@ -56,7 +56,7 @@ struct ConvTmaParams {
   int streamk;
   int units;        // tiles * num_k (0 when the k range is not shared)
   float *ws;        // partial tiles: slot 2c (a part that begins CTA c's share) and 2c + 1 (one that ends it)
-  int *tile_count;  // parts delivered per tile, zeroed before the launch
+  int *tile_count;  // parts delivered per tile; zero between launches
   Epilogue ep;     // bias_kind ROW = per output channel
   int *err_flag;
 };
@@ -296,8 +296,10 @@ __global__ void __launch_bounds__(CT_THREADS, 1)
         const int c_first = share_of_unit(tile_u0, p.units, gridDim.x);
         const int c_last = share_of_unit(tile_u0 + p.num_k - 1, p.units, gridDim.x);
         bool met = epi_sync();
-        if (warp == 2 && lane == 0)
+        if (warp == 2 && lane == 0) {
           s_last = (atomicAdd(p.tile_count + tile, 1) == c_last - c_first) ? 1 : 0;
+          if (s_last) p.tile_count[tile] = 0;  // zero again for the next launch
+        }
         met = epi_sync() && met;
         if (!met || *(volatile int *)&s_fail) {
           ok = false;
@@ -575,20 +577,15 @@ static int launch_conv_tma(b200_engine *e, const CUtensorMap *tm, ConvTmaParams 
   if (tiles >= (1LL << 31))
     return set_error(e, B200_ERR_UNSUPPORTED, "convolution: %lld output tiles are more than one launch takes", tiles);
   int sk_grid = grid;
-  if (!(e->flags & B200_ENGINE_NO_STREAMK) && streamk_pays(tiles, p.num_k, e->sm_count, &sk_grid)) {
-    grid = sk_grid;
-    const long long ws_bytes = 2LL * grid * CT_BM * BN * 4;
-    const long long cnt_bytes = (tiles * 4 + 255) / 256 * 256;
-    int rc = b200_get(e, cnt_bytes + ws_bytes, &ws);
-    if (rc == B200_OK) {
+  if (!(e->flags & B200_ENGINE_NO_STREAMK) && tiles <= b200_engine::kSkCounters &&
+      streamk_pays(tiles, p.num_k, e->sm_count, &sk_grid)) {
+    if (b200_get(e, 2LL * sk_grid * CT_BM * BN * 4, &ws) == B200_OK) {
+      grid = sk_grid;
       p.streamk = 1;
       p.units = (int)(tiles * p.num_k);  // small: k sharing is for launches of few tiles
-      p.tile_count = (int *)ws;
-      p.ws = (float *)((char *)ws + cnt_bytes);
-      B200_CHECK_CUDA(e, cudaMemsetAsync(ws, 0, (size_t)cnt_bytes, e->stream));
-    } else {
-      grid = (int)std::min<long long>(tiles, e->sm_count);  // no room for the partial tiles: whole tiles per CTA
-    }
+      p.tile_count = e->sk_counters;
+      p.ws = (float *)ws;
+    }  // else: no room for the partial tiles, whole tiles per CTA
   }
   kern<<<grid, CT_THREADS, smem, e->stream>>>(tm[0], tm[1], tm[2], tm[3], p);
   cudaError_t le = cudaGetLastError();

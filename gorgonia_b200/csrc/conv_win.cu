@@ -338,14 +338,19 @@ __global__ void __launch_bounds__(CW_THREADS, 1)
         // Ho and Wo are even, so a pooling window lies wholly inside the image or wholly outside
         const int Hq = p.Ho >> 1, Wq = p.Wo >> 1;
         const long long plane = (long long)Hq * Wq;
-        const bool writer = oh < p.Ho && ow < p.Wo && (lane & 9) == 0;
-        const long long pos = writer ? ((long long)b * Hq + (oh >> 1)) * Wq + (ow >> 1) : 0;
+        const bool inside = oh < p.Ho && ow < p.Wo;
+        const long long pos = inside ? ((long long)b * Hq + (oh >> 1)) * Wq + (ow >> 1) : 0;
         float *yb = p.y ? p.y + ((long long)b * p.K + n0) * plane + (long long)(oh >> 1) * Wq + (ow >> 1) : nullptr;
-        if (p.y_hi)
-          store_channels_split<BN, true>(acc, yb, plane, p.K - n0, bias_w, p.ep.act, (float)p.ep.alpha, writer,
-                                         p.y_hi + pos * p.K + n0, p.y_lo + pos * p.K + n0);
-        else
-          store_channels_pooled<BN>(acc, yb, plane, p.K - n0, bias_w, p.ep.act, (float)p.ep.alpha, writer);
+        float *nh = p.y_hi ? p.y_hi + pos * p.K + n0 : nullptr, *nl = p.y_hi ? p.y_lo + pos * p.K + n0 : nullptr;
+        // the short way (the window's four lanes share the channels out); the long way for warps that
+        // met a number that is not finite
+        if (!store_channels_pool4<BN>(acc, yb, plane, p.K - n0, bias_w, p.ep.act, (float)p.ep.alpha, inside, nh, nl)) {
+          const bool writer = inside && (lane & 9) == 0;
+          if (p.y_hi)
+            store_channels_split<BN, true>(acc, yb, plane, p.K - n0, bias_w, p.ep.act, (float)p.ep.alpha, writer, nh, nl);
+          else
+            store_channels_pooled<BN>(acc, yb, plane, p.K - n0, bias_w, p.ep.act, (float)p.ep.alpha, writer);
+        }
       } else if (p.y_hi) {
         const long long plane = (long long)p.Ho * p.Wo;
         const bool writer = oh < p.Ho && ow < p.Wo;

@@ -101,6 +101,8 @@ int sync_stream_checked(b200_engine *e) {
     if (e->h_flags[2] != 0) {
       e->h_flags[2] = 0;
       cudaMemsetAsync(e->d_flags + 2, 0, sizeof(int), e->stream);
+      // a kernel that gave up may have left tiles half delivered: re-arm the arrival counters
+      cudaMemsetAsync(e->sk_counters, 0, b200_engine::kSkCounters * sizeof(int), e->stream);
       return set_error(e, B200_ERR_TIMEOUT, "a device-side wait ran out of time; results of the last "
                        "kernels are incomplete");
     }
@@ -161,6 +163,7 @@ int b200_engine_create(int device, size_t arena_bytes, unsigned flags, b200_engi
     set_error(nullptr, B200_ERR_CUDA, "%s failed: %s", what, cudaGetErrorString(ce));
     if (e->slab) cudaFree(e->slab);
     if (e->d_flags) cudaFree(e->d_flags);
+    if (e->sk_counters) cudaFree(e->sk_counters);
     if (e->h_flags) cudaFreeHost(e->h_flags);
     if (e->upload_done) cudaEventDestroy(e->upload_done);
     if (e->compute_mark) cudaEventDestroy(e->compute_mark);
@@ -199,6 +202,10 @@ int b200_engine_create(int device, size_t arena_bytes, unsigned flags, b200_engi
   if ((err = cudaMalloc((void **)&e->d_flags, 16 * sizeof(int))) != cudaSuccess)
     return fail("cudaMalloc(flags)", err);
   if ((err = cudaMemset(e->d_flags, 0, 16 * sizeof(int))) != cudaSuccess) return fail("cudaMemset", err);
+  if ((err = cudaMalloc((void **)&e->sk_counters, b200_engine::kSkCounters * sizeof(int))) != cudaSuccess)
+    return fail("cudaMalloc(counters)", err);
+  if ((err = cudaMemset(e->sk_counters, 0, b200_engine::kSkCounters * sizeof(int))) != cudaSuccess)
+    return fail("cudaMemset", err);
   if ((err = cudaHostAlloc((void **)&e->h_flags, 16 * sizeof(int), cudaHostAllocDefault)) != cudaSuccess)
     return fail("cudaHostAlloc", err);
   memset(e->h_flags, 0, 16 * sizeof(int));
@@ -217,6 +224,7 @@ int b200_engine_destroy(b200_engine *e) {
     if (e->gemm_state && e->gemm_state_free) e->gemm_state_free(e->gemm_state);
     if (e->slab) cudaFree(e->slab);
     if (e->d_flags) cudaFree(e->d_flags);
+    if (e->sk_counters) cudaFree(e->sk_counters);
     if (e->reduce_scratch) cudaFree(e->reduce_scratch);
     if (e->h_flags) cudaFreeHost(e->h_flags);
     cudaStreamSynchronize(e->copy_stream);

@@ -57,6 +57,10 @@ struct b200_engine {
   bool flags_dirty = false; // a kernel that may raise d_flags[2] (bounded wait ran out) was launched
 
   void *reduce_scratch = nullptr;  // partials + ticket of the whole-tensor reduction (reduce.cu)
+  // Arrival counters of the tensor-core kernels that share tiles' k ranges between CTAs (one per
+  // tile). Zero between launches: the CTA that completes a tile puts its counter back to zero.
+  int *sk_counters = nullptr;
+  static constexpr int kSkCounters = 1 << 16;
 
   // lazily created resources of other translation units (gemm.cu etc.)
   void *gemm_state = nullptr;

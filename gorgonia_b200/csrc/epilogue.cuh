@@ -153,6 +153,91 @@ __device__ __forceinline__ float epi_tf32(float v) {
   asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(v));
   return __uint_as_float(r);
 }
+// ---- the pooled store, the short way --------------------------------------------------------------
+// Bias add, Rectify and LeakyRelu with a slope >= 0 never reverse the order of two numbers, so the
+// maximum of the four activated values of a pooling window is the activated maximum of the four raw
+// sums. The four lanes of a window therefore first exchange raw sums, halving twice what each lane
+// keeps (lane bit 0 picks a half of the channels, lane bit 3 a half of that), and every lane then
+// applies bias and activation to N/4 channels only and stores them, in NCHW (y) and / or in the split
+// NHWC form (nh, nl). A quarter of the arithmetic and three eighths of the shuffles of the long way.
+// The equivalence needs finite numbers (an infinite sum turns into NaN under the reference's
+// x*(x>=0) forms and then never wins a window): if any result of the warp is not finite the function
+// stores nothing and returns false, and the caller takes the long way, which follows the reference
+// step by step. `inside`: this lane's pooling window lies in the image. The result is warp-uniform.
+template <int N, int ACT, bool BIAS>
+__device__ __forceinline__ bool store_channels_pool4_variant(const float (&acc)[N], float *y, long long plane,
+                                                             int valid, const float *bias, float alpha, bool inside,
+                                                             float *nh, float *nl) {
+  static_assert(N % 16 == 0, "a lane keeps N / 4 channels, stored four at a time");
+  const int lane = threadIdx.x & 31;
+  const bool b0 = (lane & 1) != 0, b1 = (lane & 8) != 0;
+  float h[N / 2];
+#pragma unroll
+  for (int j = 0; j < N / 2; ++j) {
+    const float keep = b0 ? acc[j + N / 2] : acc[j];
+    const float send = b0 ? acc[j] : acc[j + N / 2];
+    h[j] = fmaxf(keep, __shfl_xor_sync(0xffffffffu, send, 1));
+  }
+  float q[N / 4];
+#pragma unroll
+  for (int j = 0; j < N / 4; ++j) {
+    const float keep = b1 ? h[j + N / 4] : h[j];
+    const float send = b1 ? h[j] : h[j + N / 4];
+    q[j] = fmaxf(keep, __shfl_xor_sync(0xffffffffu, send, 8));
+  }
+  const int cb = (b0 ? N / 2 : 0) + (b1 ? N / 4 : 0);  // first channel this lane keeps
+  bool bad = false;
+#pragma unroll
+  for (int j = 0; j < N / 4; ++j) {
+    float t = q[j];
+    if (BIAS) t = __fadd_rn(t, bias[cb + j]);
+    t = apply_act<float>(t, ACT, alpha);
+    q[j] = t;
+    bad |= !(fabsf(t) <= 3.402823466e+38f);
+  }
+  if (__any_sync(0xffffffffu, bad)) return false;
+  if (inside) {
+    if (y) {
+#pragma unroll
+      for (int j = 0; j < N / 4; ++j)
+        if (cb + j < valid) y[(long long)(cb + j) * plane] = q[j];
+    }
+    if (nh) {
+#pragma unroll
+      for (int j0 = 0; j0 < N / 4; j0 += 4) {
+        if (cb + j0 < valid) {
+          float hh[4], ll[4];
+#pragma unroll
+          for (int jj = 0; jj < 4; ++jj) {
+            hh[jj] = epi_tf32(q[j0 + jj]);
+            ll[jj] = epi_tf32(__fsub_rn(q[j0 + jj], hh[jj]));
+          }
+          *reinterpret_cast<float4 *>(nh + cb + j0) = make_float4(hh[0], hh[1], hh[2], hh[3]);
+          *reinterpret_cast<float4 *>(nl + cb + j0) = make_float4(ll[0], ll[1], ll[2], ll[3]);
+        }
+      }
+    }
+  }
+  return true;
+}
+template <int N>
+__device__ __forceinline__ bool store_channels_pool4(const float (&acc)[N], float *y, long long plane, int valid,
+                                                     const float *bias, int act, float alpha, bool inside, float *nh,
+                                                     float *nl) {
+  if (act == B200_ACT_LEAKY && !(alpha >= 0.f)) return false;  // a negative slope reverses the order of negatives
+#define B200_POOL4_CASE(A, BI) return store_channels_pool4_variant<N, A, BI>(acc, y, plane, valid, bias, alpha, inside, nh, nl)
+  if (bias) {
+    if (act == B200_ACT_NONE) B200_POOL4_CASE(B200_ACT_NONE, true);
+    else if (act == B200_ACT_RECTIFY) B200_POOL4_CASE(B200_ACT_RECTIFY, true);
+    else B200_POOL4_CASE(B200_ACT_LEAKY, true);
+  } else {
+    if (act == B200_ACT_NONE) B200_POOL4_CASE(B200_ACT_NONE, false);
+    else if (act == B200_ACT_RECTIFY) B200_POOL4_CASE(B200_ACT_RECTIFY, false);
+    else B200_POOL4_CASE(B200_ACT_LEAKY, false);
+  }
+#undef B200_POOL4_CASE
+}
+
 template <int N, int ACT, bool BIAS, bool POOL>
 __device__ __forceinline__ void store_channels_split_variant(const float (&acc)[N], float *y, long long plane,
                                                              int valid, const float *bias, float alpha, bool writer,

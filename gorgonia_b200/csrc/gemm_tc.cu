@@ -72,7 +72,7 @@ struct GemmTcParams {
   int streamk;
   int units;                    // tiles * num_k (0 when the k range is not shared)
   float *ws;                    // partial tiles, 2 slots of TC_BM x BN floats per CTA
-  int *tile_count;              // parts delivered per tile, zeroed before the launch
+  int *tile_count;              // parts delivered per tile; zero between launches
   Epilogue ep;
   int *err_flag;
 };
@@ -428,7 +428,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
           const int c_first = share_of_unit(tile_u0, p.units, gridDim.x);
           const int c_last = share_of_unit(tile_u0 + p.num_k - 1, p.units, gridDim.x);
           bool met = epi_sync();
-          if (warp == 2 && lane == 0) s_last = (atomicAdd(p.tile_count + tile, 1) == c_last - c_first) ? 1 : 0;
+          if (warp == 2 && lane == 0) {
+            s_last = (atomicAdd(p.tile_count + tile, 1) == c_last - c_first) ? 1 : 0;
+            if (s_last) p.tile_count[tile] = 0;  // zero again for the next launch
+          }
           met = epi_sync() && met;
           if (!met || *(volatile int *)&s_fail) {
             ok = false;
@@ -737,20 +740,14 @@ int gemm_tc_core(b200_engine *e, int terms, bool a_mn, bool b_mn, long long M, l
   // whole tiles per CTA would leave SMs idle: share out the k range instead (TilePieces)
   void *ws = nullptr;
   int sk_grid = grid;
-  if (may_share_k && streamk_pays(total_tiles, p.num_k, e->sm_count, &sk_grid)) {
-    const long long ws_bytes = 2LL * sk_grid * TC_BM * bn * 4;
-    const long long cnt_bytes = (total_tiles * 4 + 255) / 256 * 256;
-    if (b200_get(e, cnt_bytes + ws_bytes, &ws) == B200_OK) {
+  if (may_share_k && total_tiles <= b200_engine::kSkCounters &&
+      streamk_pays(total_tiles, p.num_k, e->sm_count, &sk_grid)) {
+    if (b200_get(e, 2LL * sk_grid * TC_BM * bn * 4, &ws) == B200_OK) {
       p.streamk = 1;
       p.units = (int)(total_tiles * p.num_k);  // small: k sharing is for launches of few tiles
       grid = sk_grid;
-      p.tile_count = (int *)ws;
-      p.ws = (float *)((char *)ws + cnt_bytes);
-      cudaError_t me = cudaMemsetAsync(ws, 0, (size_t)cnt_bytes, e->stream);
-      if (me != cudaSuccess) {
-        b200_put(e, ws, 0);
-        return set_error(e, B200_ERR_CUDA, "cudaMemsetAsync failed: %s", cudaGetErrorString(me));
-      }
+      p.tile_count = e->sk_counters;
+      p.ws = (float *)ws;
     }  // else: no room for the partial tiles, whole tiles per CTA
   }
   const int rc = bn == 128 ? launch_tc_layout<3, 128>(e, a_mn, b_mn, tm, p, grid)

@@ -107,20 +107,26 @@ __device__ __forceinline__ int share_slot(int c, int tile_u0, int units, int gri
 }
 
 // Whether a launch of `tiles` tiles of `num_k` k-blocks shares out the k range, and over how many
-// CTAs. It pays when whole tiles would fill less than 85 % of the waves. The CTA that finishes a
-// tile reads its parts one after the other (about a microsecond each: one SM's share of the L2
-// bandwidth), while a k-block costs about 0.6 microseconds, so a tile is cut into at most
-// sqrt(0.6 num_k) parts: beyond that the fix-up costs more than the shorter k loop saves.
+// CTAs. Measured on B200: a k-block costs a CTA about 0.6 microseconds (one SM's share of the L2
+// bandwidth), the CTA that finishes a tile reads its parts one after the other at about a
+// microsecond each, and handing partial tiles over costs about 3 microseconds per launch. A tile is
+// cut into at most sqrt(0.6 num_k) parts (beyond that the fix-up costs more than the shorter k loop
+// saves), and the k range is shared only where this estimate says it saves a tenth of the time.
 inline bool streamk_pays(long long tiles, int num_k, int sm_count, int *grid) {
-  const long long waves = (tiles + sm_count - 1) / sm_count;
-  if (num_k < 4 || (double)tiles >= 0.85 * (double)(waves * sm_count)) return false;
+  if (num_k < 4 || tiles < 1) return false;
   int parts = 1;
   while ((parts + 1) * (parts + 1) <= 0.6 * num_k) ++parts;
   long long g = tiles * parts;
   if (g > sm_count) g = sm_count;
   if (g > tiles * (long long)num_k / 2) g = tiles * (long long)num_k / 2;
-  if (g <= tiles && tiles <= sm_count) return false;  // nothing to share out
-  *grid = (int)(g < 1 ? 1 : g);
+  if (g < 1) return false;
+  const long long waves = (tiles + sm_count - 1) / sm_count;
+  const double t_whole = 0.6 * (double)waves * num_k;
+  const long long units = tiles * (long long)num_k;
+  const double parts_per_tile = g > tiles ? (double)((g + tiles - 1) / tiles) : 2.0;
+  const double t_shared = 0.6 * (double)((units + g - 1) / g) + parts_per_tile + 3.0;
+  if (t_shared >= 0.9 * t_whole) return false;
+  *grid = (int)g;
   return true;
 }
 
