@@ -166,6 +166,7 @@ _SIGS = {
     "b200_col2im": (_i, [_vp, _i, _vp, _vp, _i64, _i64, _i64, _i64, _i, _i, _i, _i, _i, _i, _i, _i]),
     "b200_softmax_bwd": (_i, [_vp, _i, _vp, _vp, _vp, _i64, _i64, _i64, _i]),
     "b200_maxpool2d_fwd": (_i, [_vp, _i, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i, _i, _i, _i, _i, _i, _i, _i, _i]),
+    "b200_maxpool2d_split_fwd": (_i, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i, _i, _i, _i, _i, _i, _i, _i, _i]),
     "b200_transpose": (_i, [_vp, _i, _vp, _vp, _i, _P(_i64), _P(_i)]),
     "b200_gather_axis": (_i, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64]),
     "b200_gather_rows": (_i, [_vp, _vp, _vp, _vp, _i64, _i64, _i64]),

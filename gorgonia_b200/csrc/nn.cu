@@ -58,6 +58,68 @@ __global__ void __launch_bounds__(256) maxpool_kernel(const T *__restrict__ x, T
   }
 }
 
+// Max-pool whose result goes to a tensor-core convolution: written channels-innermost (NHWC) as a
+// TF32 head and the TF32 rounding of the remainder, the form those kernels read, and optionally in
+// NCHW as well. A block takes 32 channels x 32 pooled positions of one image: it pools along the
+// positions (contiguous reads per channel), turns the tile in shared memory and writes along the
+// channels (contiguous 128-byte rows per position). Same comparison order as maxpool_kernel.
+__device__ __forceinline__ float pool_tf32(float v) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(v));
+  return __uint_as_float(r);
+}
+__global__ void __launch_bounds__(256) maxpool_split_kernel(const float *__restrict__ x, float *__restrict__ y,
+                                                            float *__restrict__ hi, float *__restrict__ lo,
+                                                            long long B, int C, int H, int W, int Ho, int Wo, int kh,
+                                                            int kw, int sH, int sW, int oh0, int ow0) {
+  __shared__ float tile[32][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int HWo = Ho * Wo;
+  const int ptiles = (HWo + 31) / 32, ctiles = (C + 31) / 32;
+  const long long per_image = (long long)ptiles * ctiles, total = B * per_image;
+  for (long long t = blockIdx.x; t < total; t += gridDim.x) {
+    const long long b = t / per_image;
+    const int rem = (int)(t - b * per_image);
+    const int ct = rem / ptiles, pt = rem - ct * ptiles;
+    const int c0 = ct * 32, p0 = pt * 32;
+    const int pp = p0 + tx;
+    const int ph = pp / Wo, pw = pp - ph * Wo;
+    int hs = ph * sH - oh0, ws = pw * sW - ow0;
+    const int he = min(hs + kh, H), we = min(ws + kw, W);
+    hs = max(hs, 0);
+    ws = max(ws, 0);
+#pragma unroll
+    for (int j = ty; j < 32; j += 8) {
+      const int c = c0 + j;
+      float best = -FLT_MAX;
+      if (c < C && pp < HWo) {
+        const float *in = x + (b * C + c) * (long long)H * W;
+        for (int hh = hs; hh < he; ++hh)
+          for (int ww = ws; ww < we; ++ww) {
+            const float v = __ldg(in + hh * W + ww);
+            if (v > best) best = v;
+          }
+        if (y) y[(b * C + c) * (long long)HWo + pp] = best;
+      }
+      tile[j][tx] = best;
+    }
+    __syncthreads();
+    const long long ob = b * (long long)HWo * C;
+#pragma unroll
+    for (int j = ty; j < 32; j += 8) {
+      const int q = p0 + j, c = c0 + tx;
+      if (q < HWo && c < C) {
+        const float v = tile[tx][j];
+        const float h = pool_tf32(v);
+        const long long o = ob + (long long)q * C + c;
+        hi[o] = h;
+        lo[o] = pool_tf32(__fsub_rn(v, h));
+      }
+    }
+    __syncthreads();
+  }
+}
+
 // The pooling every config here uses: 2x2 window, stride 2, no padding, W a multiple of 4, no mask.
 // One thread makes two neighbouring outputs from two 16-byte loads (one per input row) and writes
 // them with one 8-byte store. Same comparison order as the general kernel: row-major inside the
@@ -807,6 +869,34 @@ static int batchnorm_bwd_t(b200_engine *e, const T *x, const T *dy, T *dx, long 
 using namespace b200;
 
 extern "C" {
+
+int b200_maxpool2d_split_fwd(b200_engine *e, const void *x, void *y, void *y_hi, void *y_lo, int64_t B, int64_t C,
+                             int64_t H, int64_t W, int kh, int kw, int pad_north, int pad_south, int pad_west,
+                             int pad_east, int explicit_padding, int stride_h, int stride_w) {
+  if (!e) return B200_ERR_INVALID;
+  std::lock_guard<std::recursive_mutex> lk(e->mu);
+  B200_REQUIRE(e, B >= 0 && C >= 0 && H > 0 && W > 0, "b200_maxpool2d_split_fwd: bad input shape");
+  B200_REQUIRE(e, kh > 0 && kw > 0 && stride_h > 0 && stride_w > 0, "b200_maxpool2d_split_fwd: bad kernel or stride");
+  B200_REQUIRE(e, pad_north >= 0 && pad_south >= 0 && pad_west >= 0 && pad_east >= 0,
+               "b200_maxpool2d_split_fwd: bad pad");
+  B200_REQUIRE(e, H < 32768 && W < 32768 && C < (1LL << 30), "b200_maxpool2d_split_fwd: image too large");
+  const long long Ho = (H + pad_south + pad_north - (kh - 1) - 1) / stride_h + 1;
+  const long long Wo = (W + pad_east + pad_west - (kw - 1) - 1) / stride_w + 1;
+  B200_REQUIRE(e, Ho > 0 && Wo > 0, "b200_maxpool2d_split_fwd: window larger than the padded image");
+  if (B * C == 0) return B200_OK;
+  B200_REQUIRE(e, x && y_hi && y_lo, "b200_maxpool2d_split_fwd: null pointer");
+  DeviceGuard g(e);
+  int rc = flush_pending(e);
+  if (rc != B200_OK) return rc;
+  const long long tiles = B * ((Ho * Wo + 31) / 32) * ((C + 31) / 32);
+  const int blocks = (int)std::max<long long>(1, std::min<long long>(tiles, (long long)e->sm_count * 16));
+  maxpool_split_kernel<<<blocks, 256, 0, e->stream>>>((const float *)x, (float *)y, (float *)y_hi, (float *)y_lo, B,
+                                                      (int)C, (int)H, (int)W, (int)Ho, (int)Wo, kh, kw, stride_h,
+                                                      stride_w, explicit_padding ? pad_south : pad_north,
+                                                      explicit_padding ? pad_east : pad_west);
+  B200_CHECK_LAUNCH(e, "maxpool_split_kernel");
+  return B200_OK;
+}
 
 int b200_maxpool2d_fwd(b200_engine *e, int dtype, const void *x, void *y, int64_t *mask, int64_t B, int64_t C,
                        int64_t H, int64_t W, int kh, int kw, int pad_north, int pad_south, int pad_west,

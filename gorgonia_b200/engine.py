@@ -464,6 +464,20 @@ class Engine:
                                      stride[1]), self.h)
         return prealloc
 
+    def MaxPool2DSplit(self, x, prealloc, split, kernel, pad, stride):
+        """MaxPool2D whose result goes to a convolution chain: split = (head, tail) NHWC tensors; prealloc
+        (NCHW) may be None."""
+        B, Cc, H, W = x.shape
+        if len(pad) == 2:
+            pn, ps, pw, pe, explicit = pad[0], pad[0], pad[1], pad[1], 0
+        else:
+            pn, ps, pw, pe = pad
+            explicit = 1
+        check(lib.b200_maxpool2d_split_fwd(self.h, x.ptr, prealloc.ptr if prealloc is not None else None,
+                                           split[0].ptr, split[1].ptr, B, Cc, H, W, kernel[0], kernel[1], pn, ps, pw,
+                                           pe, explicit, stride[0], stride[1]), self.h)
+        return split
+
     def BatchNorm(self, x, prealloc, running_mean, running_var, save_mean=None, save_var=None, training=True,
                   momentum=0.9, epsilon=1e-5):
         """BatchNormOp on (B, C, ...): normalisation only; scale and bias are separate broadcast ops."""

@@ -95,24 +95,39 @@ class _ConvChain:
             L["want_split"] = bool(nxt) and nxt["path"] in split_paths and direct_feed and L["w"].shape[0] % 4 == 0
             # NCHW is needed by a separate pool, by a next link whose kernel reads NCHW, and at the end
             L["want_nchw"] = not L["want_split"] or not direct_feed or nxt is None
-        for L in layers:
+        for i, L in enumerate(layers):
+            nxt = layers[i + 1] if i + 1 < len(layers) else None
             B, K, Ho, Wo = L["conv_shape"]
             ob = L["out_shape"]
-            L["y"] = e.empty(L["conv_shape"] if (L["pool"] and not L["fuse_pool"]) else ob) if L["want_nchw"] else None
-            L["pooled"] = e.empty(ob) if (L["pool"] and not L["fuse_pool"]) else None
+            sep_pool = bool(L["pool"]) and not L["fuse_pool"]
+            L["y"] = e.empty(L["conv_shape"] if sep_pool else ob) if L["want_nchw"] else None
             L["split"] = (e.empty((ob[0], ob[2], ob[3], ob[1])), e.empty((ob[0], ob[2], ob[3], ob[1]))) \
                 if L["want_split"] else None
+            # a separate pool in front of a kernel that reads the split form writes that form itself
+            L["pool_split"] = None
+            if sep_pool and nxt is not None and nxt["path"] in split_paths:
+                L["pool_split"] = (e.empty((ob[0], ob[2], ob[3], ob[1])), e.empty((ob[0], ob[2], ob[3], ob[1])))
+            L["pooled"] = e.empty(ob) if (sep_pool and L["pool_split"] is None) else None
 
-    def forward(self, x):
-        e, a, a_split = self.e, x, None
+    def forward(self, x, x_split=None):
+        e, a, a_split = self.e, x, x_split
         for L in self.layers:
             e.Conv2dChain(a, L["w"], L["y"], L["in_shape"], pad=L["pad"], bias=L["bias"], act=L["act"], alpha=L["alpha"],
                           pool2=L["fuse_pool"], x_split=a_split, y_split=L["split"])
             a, a_split = L["y"], L["split"]
-            if L["pooled"] is not None:
+            if L["pool_split"] is not None:
+                a_split = e.MaxPool2DSplit(L["y"], None, L["pool_split"], (2, 2), (0, 0), (2, 2))
+                a = None
+            elif L["pooled"] is not None:
                 e.MaxPool2D(L["y"], L["pooled"], (2, 2), (0, 0), (2, 2))
                 a = L["pooled"]
         return a
+
+    @property
+    def reads_split(self):
+        """Whether the first link's kernel reads the NHWC TF32-split form."""
+        from . import _lib
+        return self.layers[0]["path"] in (_lib.CONV_TC_WINDOW, _lib.CONV_TC_TMA)
 
 
 class _DenseChain:
@@ -270,6 +285,7 @@ class TinyYolo(_Tape):
                 self.pool.append(None if fused else e.empty((batch, ch[i + 1], s, s)))
             elif i == 5:
                 self.pool.append(e.empty((batch, ch[i + 1], s, s)))
+        self.pool5_split = None
         if fused:
             def layer(i):
                 return {"w": self.w[i], "pad": (self.k[i] // 2, self.k[i] // 2), "bias": self.b[i], "act": "leaky",
@@ -277,6 +293,8 @@ class TinyYolo(_Tape):
             # two runs of links, cut by the 2x2 / stride-1 pool with explicit padding after layer 5
             self.chain_a = _ConvChain(e, batch, (3, size, size), [layer(i) for i in range(6)])
             self.chain_b = _ConvChain(e, batch, (ch[6], s, s), [layer(i) for i in range(6, 9)])
+            if self.chain_b.reads_split:
+                self.pool5_split = (e.empty((batch, s, s, ch[6])), e.empty((batch, s, s, ch[6])))
             self.out = self.chain_b.layers[-1]["y"]
         else:
             self.out = self.conv[8]
@@ -285,6 +303,9 @@ class TinyYolo(_Tape):
         e, a = self.e, self.x
         if self.fused:
             a = self.chain_a.forward(a)
+            if self.pool5_split is not None:
+                e.MaxPool2DSplit(a, None, self.pool5_split, (2, 2), (1, 0, 1, 0), (1, 1))
+                return self.chain_b.forward(None, self.pool5_split)
             e.MaxPool2D(a, self.pool[5], (2, 2), (1, 0, 1, 0), (1, 1))
             return self.chain_b.forward(self.pool[5])
         for i in range(9):

@@ -470,6 +470,12 @@ int b200_col2im(b200_engine *e, int dtype, const void *col, void *im, int64_t B,
                 int dil_w);
 int b200_softmax_bwd(b200_engine *e, int dtype, const void *y, const void *grad, void *dx,
                      int64_t outer, int64_t len, int64_t inner, int is_log);
+/* b200_maxpool2d_fwd for float32 whose result feeds a link of b200_conv2d_chain_fwd: the pooled tensor
+ * is written as the NHWC TF32 head / tail pair that link reads (y_hi, y_lo: B x Ho x Wo x C each) and,
+ * if y is not NULL, in NCHW too. One pass instead of the pool followed by the rewrite. */
+int b200_maxpool2d_split_fwd(b200_engine *e, const void *x, void *y, void *y_hi, void *y_lo, int64_t B,
+                             int64_t C, int64_t H, int64_t W, int kh, int kw, int pad_north, int pad_south,
+                             int pad_west, int pad_east, int explicit_padding, int stride_h, int stride_w);
 int b200_maxpool2d_fwd(b200_engine *e, int dtype, const void *x, void *y, int64_t *mask, int64_t B,
                        int64_t C, int64_t H, int64_t W, int kh, int kw, int pad_north, int pad_south,
                        int pad_west, int pad_east, int explicit_padding, int stride_h, int stride_w);

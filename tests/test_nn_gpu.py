@@ -378,3 +378,27 @@ def test_by_indices(fresh):
         assert_bits_equal(y.numpy(), oracle.gather_rows(x, idx))
     with pytest.raises(B200Error):
         e.ByIndices(e.tensor(x), e.tensor(np.array([0, 100], np.int64)), e.empty((2,)))
+
+
+@pytest.mark.parametrize("case", [((3, 40, 13, 13), (2, 2), (1, 0, 1, 0), (1, 1)),     # tiny-YOLO's stride-1 pool
+                                  ((2, 64, 52, 52), (2, 2), (0, 0), (2, 2)),
+                                  ((2, 33, 9, 11), (3, 3), (1, 1), (2, 2))])            # ragged channel / position tiles
+def test_maxpool_split_form(fresh, case):
+    # the pool that feeds a convolution chain writes NCHW (optional) and the NHWC TF32 head/tail pair
+    e = fresh
+    shape, kernel, pad, stride = case
+    x = util.normal(130, shape)
+    want, _ = oracle.maxpool2d(x, kernel, pad, stride)
+    B, Cc, Ho, Wo = want.shape
+    y, hi, lo = e.empty(want.shape), e.empty((B, Ho, Wo, Cc)), e.empty((B, Ho, Wo, Cc))
+    e.MaxPool2DSplit(e.tensor(x), y, (hi, lo), kernel, pad, stride)
+    assert_bits_equal(y.numpy(), want)
+    nhwc = np.transpose(want, (0, 2, 3, 1))
+    h, l = hi.numpy(), lo.numpy()
+    assert np.all((h.view(np.uint32) & 0x1FFF) == 0) and np.all((l.view(np.uint32) & 0x1FFF) == 0)
+    assert np.abs((h.astype(np.float64) + l) - nhwc).max() <= 2.0 ** -21 * float(np.abs(nhwc).max())
+    # without the NCHW copy
+    hi2, lo2 = e.empty((B, Ho, Wo, Cc)), e.empty((B, Ho, Wo, Cc))
+    e.MaxPool2DSplit(e.tensor(x), None, (hi2, lo2), kernel, pad, stride)
+    assert_bits_equal(hi2.numpy(), h)
+    assert_bits_equal(lo2.numpy(), l)
