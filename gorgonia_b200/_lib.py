@@ -136,6 +136,10 @@ _SIGS = {
     "b200_binary": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp, _d, _i, _i64]),
     "b200_unary": (_i, [_vp, _i, _i, _vp, _vp, _i64]),
     "b200_binary_bcast": (_i, [_vp, _i, _i, _vp, _vp, _vp, _i64, _i64, _i64, _i]),
+    "b200_binary_incr": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp, _d, _i, _i64]),
+    "b200_unary_incr": (_i, [_vp, _i, _i, _vp, _vp, _i64]),
+    "b200_dropout_fwd": (_i, [_vp, _i, _vp, _vp, _i64, _d, _vp, C.c_uint64, C.c_uint64]),
+    "b200_dropout_bwd": (_i, [_vp, _i, _vp, _vp, _vp, _i64, _d]),
     "b200_pointwise": (_i, [_vp, _i, _P(PwProg), _P(_vp), _P(_vp), _i64]),
     "b200_pending": (_i, [_vp, _P(_i), _P(_i)]),
     "b200_fusion_plan": (_i, [_P(PwCall), _i, _P(_i), _P(_i), _P(_i), _P(_i), _P(_i)]),

@@ -1191,6 +1191,42 @@ int b200_binary(b200_engine *e, int op, int dtype, int form, void *dst, const vo
   return enqueue(e, c);
 }
 
+// ExternalOp.Do in Incr mode (execution.go:113-127): CUDADo into a temporary, then an unsafe add of
+// the temporary into op.Incr. Queued as exactly those two calls; the temporary is handed back before
+// the queue is flushed, so the fused kernel keeps it in registers and never stores it.
+int b200_binary_incr(b200_engine *e, int op, int dtype, int form, void *incr, const void *a, const void *b,
+                     double scalar, int scalar_on_device, int64_t n) {
+  if (!e) return B200_ERR_INVALID;
+  std::lock_guard<std::recursive_mutex> lk(e->mu);
+  B200_REQUIRE(e, dtype == B200_F32 || dtype == B200_F64, "b200_binary_incr: dtype %d not supported", dtype);
+  B200_REQUIRE(e, n >= 0, "b200_binary_incr: negative element count");
+  if (n == 0) return B200_OK;
+  B200_REQUIRE(e, incr != nullptr, "b200_binary_incr: incr is null");
+  void *tmp = nullptr;
+  int rc = b200_get(e, n * (int64_t)dtype_size(dtype), &tmp);
+  if (rc != B200_OK) return rc;
+  rc = b200_binary(e, op, dtype, form, tmp, a, b, scalar, scalar_on_device, n);
+  if (rc == B200_OK) rc = b200_binary(e, B200_OP_ADD, dtype, B200_VV, incr, incr, tmp, 0.0, 0, n);
+  b200_put(e, tmp, 0);
+  return rc;
+}
+
+int b200_unary_incr(b200_engine *e, int op, int dtype, void *incr, const void *a, int64_t n) {
+  if (!e) return B200_ERR_INVALID;
+  std::lock_guard<std::recursive_mutex> lk(e->mu);
+  B200_REQUIRE(e, dtype == B200_F32 || dtype == B200_F64, "b200_unary_incr: dtype %d not supported", dtype);
+  B200_REQUIRE(e, n >= 0, "b200_unary_incr: negative element count");
+  if (n == 0) return B200_OK;
+  B200_REQUIRE(e, incr != nullptr, "b200_unary_incr: incr is null");
+  void *tmp = nullptr;
+  int rc = b200_get(e, n * (int64_t)dtype_size(dtype), &tmp);
+  if (rc != B200_OK) return rc;
+  rc = b200_unary(e, op, dtype, tmp, a, n);
+  if (rc == B200_OK) rc = b200_binary(e, B200_OP_ADD, dtype, B200_VV, incr, incr, tmp, 0.0, 0, n);
+  b200_put(e, tmp, 0);
+  return rc;
+}
+
 int b200_unary(b200_engine *e, int op, int dtype, void *dst, const void *a, int64_t n) {
   if (!e) return B200_ERR_INVALID;
   std::lock_guard<std::recursive_mutex> lk(e->mu);

@@ -266,6 +266,33 @@ class Engine:
         check(lib.b200_unary(self.h, _lib.OP[op], dtype_code(a.dtype), dst.ptr, a.ptr, a.size), self.h)
         return dst
 
+    def BinaryIncr(self, op, a, b, incr):
+        """Incr mode (execution.go:113-127): incr += op(a, b); a or b may be a python scalar."""
+        a_s, b_s = not isinstance(a, Tensor), not isinstance(b, Tensor)
+        t = b if a_s else a
+        if incr.size != t.size or incr.dtype != t.dtype:
+            raise B200Error(_lib.ERR_INVALID, f"{op}: incr tensor does not match the operand")
+        form = _lib.SV if a_s else (_lib.VS if b_s else _lib.VV)
+        check(lib.b200_binary_incr(self.h, _lib.OP[op], dtype_code(t.dtype), form, incr.ptr,
+                                   None if a_s else a.ptr, None if b_s else b.ptr,
+                                   float(a) if a_s else (float(b) if b_s else 0.0), 0, t.size), self.h)
+        return incr
+
+    def UnaryIncr(self, op, a, incr):
+        check(lib.b200_unary_incr(self.h, _lib.OP[op], dtype_code(a.dtype), incr.ptr, a.ptr, a.size), self.h)
+        return incr
+
+    def Dropout(self, x, prealloc, prob, uniforms=None, seed=0, offset=0):
+        """dropoutOp in training mode; `uniforms`: a tensor of draws in [0, 1), else Philox keyed by seed."""
+        check(lib.b200_dropout_fwd(self.h, dtype_code(x.dtype), x.ptr, prealloc.ptr, x.size, float(prob),
+                                   uniforms.ptr if uniforms is not None else None, int(seed), int(offset)), self.h)
+        return prealloc
+
+    def DropoutDiff(self, grad, out, prealloc, prob):
+        check(lib.b200_dropout_bwd(self.h, dtype_code(grad.dtype), grad.ptr, out.ptr, prealloc.ptr, grad.size,
+                                   float(prob)), self.h)
+        return prealloc
+
     def Pointwise(self, prog, outs, srcs, n, dtype=np.float32):
         """prog: dict(instr=[(op, a_ref, b_ref)], imm=[...], out=[instr idx], bcast={src: (div, mod)})."""
         p = _lib.PwProg()

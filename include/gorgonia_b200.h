@@ -240,13 +240,36 @@ typedef struct {
   int32_t op, dtype, form; /* form: B200_VV / B200_VS / B200_SV, or 3 for a unary op */
   int32_t bcast;           /* 0 none, 1 operand b is broadcast, 2 operand a is broadcast */
   uint64_t dst, a, b;      /* device addresses */
-  uint64_t scalar_ptr;     /* non-zero: scalar operand is read from this device address */
+  uint64_t scalar_ptr;     /* Incr mode of ExternalOp.Do (execution.go:113-127; NewAddOp / NewSubOp / NewHadamardProdOp,
+ * op_math_cuda.go:245-308): incr = incr + op(a, b), the result of the op rounded to the tensor's type
+ * before the addition, as "CUDADo into a temporary, then an unsafe add" does. One fused kernel when
+ * the queue is deferred; the temporary is never written to memory. Same operand forms as b200_binary
+ * and b200_unary. */
+int b200_binary_incr(b200_engine *e, int op, int dtype, int form, void *incr, const void *a,
+                     const void *b, double scalar, int scalar_on_device, int64_t n);
+int b200_unary_incr(b200_engine *e, int op, int dtype, void *incr, const void *a, int64_t n);
+/* non-zero: scalar operand is read from this device address */
   double scalar;
   int64_t n, bdiv, bmod;
 } b200_pw_call;
 int b200_pending(b200_engine *e, int *n_calls, int *n_kernels);
 int b200_fusion_plan(const b200_pw_call *calls, int n_calls, const int *released_at,
                      int *kernel_of_call, int *n_kernels, int *loads, int *stores);
+
+/* Dropout without cuDNN: dropoutOp.do and dropoutDiffOp (op_dropout.go:106-128,205-240), in place of
+ * the cuDNN calls of ops/nn/dropout_cuda.go:76-149.
+ * b200_dropout_fwd: y[i] = r[i] < keep ? x[i] / keep : 0 with keep = 1 - probability rounded to the
+ *   tensor's type. r comes from `uniforms` (a device array of n values in [0, 1) in the tensor's type;
+ *   gorgonia injects its generator the same way) or, with uniforms == NULL, from Philox-4x32-10 keyed
+ *   by `seed` with the element index + `offset` as the counter: stateless, the same draw on every
+ *   replay. probability == 0 copies x (the reference hands the input through).
+ * b200_dropout_bwd: dx[i] = (probability != 0 && out[i] != 0) ? dy[i] / probability : 0, where `out`
+ *   is what the forward pass wrote: the reference finds the kept elements by their non-zero output
+ *   and divides by the DROP probability; both are reproduced as written. */
+int b200_dropout_fwd(b200_engine *e, int dtype, const void *x, void *y, int64_t n, double probability,
+                     const void *uniforms, uint64_t seed, uint64_t offset);
+int b200_dropout_bwd(b200_engine *e, int dtype, const void *dy, const void *out, void *dx, int64_t n,
+                     double probability);
 
 /* Engine.HasNaN / HasInf (cuda/engine.go:144-191; kernels cuda modules/src/misc.cu:13-55).
  * *result is 1 if any element is NaN (resp. ±Inf), else 0. Synchronises. */

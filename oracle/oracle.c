@@ -695,3 +695,66 @@ void oracle_gather_rows(const void *x, const int64_t *idx, void *y, int64_t n_id
   for (int64_t i = 0; i < n_idx; ++i)
     memcpy((char *)y + i * row_bytes, (const char *)x + idx[i] * row_bytes, (size_t)row_bytes);
 }
+
+
+/* ---- dropout: dropoutOp.do and dropoutDiffOp.UsePreallocDo (op_dropout.go:106-128,205-240) ------
+ * r[i] comes from `uniforms` (the injected generator of the reference's own test) or from
+ * Philox-4x32-10 (Salmon et al., SC'11) keyed by `seed`, counter = element index + offset: float32
+ * takes word i % 4 of block i / 4 (top 24 bits), float64 the word pair 2 (i % 2), 2 (i % 2) + 1 of
+ * block i / 2 (53 bits). */
+static void philox4x32_10(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3, uint32_t k0, uint32_t k1,
+                          uint32_t out[4]) {
+  for (int round = 0; round < 10; ++round) {
+    const uint64_t p0 = (uint64_t)0xD2511F53u * c0, p1 = (uint64_t)0xCD9E8D57u * c2;
+    const uint32_t n0 = (uint32_t)(p1 >> 32) ^ c1 ^ k0, n1 = (uint32_t)p1;
+    const uint32_t n2 = (uint32_t)(p0 >> 32) ^ c3 ^ k1, n3 = (uint32_t)p0;
+    c0 = n0; c1 = n1; c2 = n2; c3 = n3;
+    k0 += 0x9E3779B9u;
+    k1 += 0xBB67AE85u;
+  }
+  out[0] = c0; out[1] = c1; out[2] = c2; out[3] = c3;
+}
+
+float oracle_philox_uniform_f32(uint64_t seed, uint64_t i) {
+  uint32_t r[4];
+  const uint64_t blk = i >> 2;
+  philox4x32_10((uint32_t)blk, (uint32_t)(blk >> 32), 0u, 0u, (uint32_t)seed, (uint32_t)(seed >> 32), r);
+  return (float)(r[i & 3] >> 8) * 5.9604644775390625e-08f;
+}
+
+double oracle_philox_uniform_f64(uint64_t seed, uint64_t i) {
+  uint32_t r[4];
+  const uint64_t blk = i >> 1;
+  philox4x32_10((uint32_t)blk, (uint32_t)(blk >> 32), 0u, 0u, (uint32_t)seed, (uint32_t)(seed >> 32), r);
+  const uint32_t a = r[2 * (i & 1)], b = r[2 * (i & 1) + 1];
+  return ((double)(a >> 5) * 67108864.0 + (double)(b >> 6)) * 1.1102230246251565e-16;
+}
+
+void oracle_dropout_f32(const float *x, float *y, int64_t n, double prob, const float *uniforms, uint64_t seed,
+                        uint64_t offset) {
+  const float keep = (float)(1.0 - prob);
+  for (int64_t i = 0; i < n; ++i) {
+    if (prob == 0.0) { y[i] = x[i]; continue; }       /* the op hands its input through (op_dropout.go:81-83) */
+    const float r = uniforms ? uniforms[i] : oracle_philox_uniform_f32(seed, offset + (uint64_t)i);
+    y[i] = r < keep ? x[i] / keep : 0.0f;            /* a fresh tensor holds zeros where nothing is written */
+  }
+}
+
+void oracle_dropout_f64(const double *x, double *y, int64_t n, double prob, const double *uniforms, uint64_t seed,
+                        uint64_t offset) {
+  const double keep = 1.0 - prob;
+  for (int64_t i = 0; i < n; ++i) {
+    if (prob == 0.0) { y[i] = x[i]; continue; }
+    const double r = uniforms ? uniforms[i] : oracle_philox_uniform_f64(seed, offset + (uint64_t)i);
+    y[i] = r < keep ? x[i] / keep : 0.0;
+  }
+}
+
+/* the reference divides by the drop probability and finds kept elements by their non-zero output */
+void oracle_dropout_bwd_f32(const float *dy, const float *out, float *dx, int64_t n, double prob) {
+  for (int64_t i = 0; i < n; ++i) dx[i] = (prob != 0 && out[i] != 0) ? dy[i] / (float)prob : 0.0f;
+}
+
+void oracle_dropout_bwd_f64(const double *dy, const double *out, double *dx, int64_t n, double prob) {
+  for (int64_t i = 0; i < n; ++i) dx[i] = (prob != 0 && out[i] != 0) ? dy[i] / prob : 0.0;
+}

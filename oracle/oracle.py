@@ -230,6 +230,25 @@ def batchnorm_bwd(x, dy, running_var, save_mean, save_var, training=True, eps=1e
     return dx
 
 
+def dropout(x, prob, uniforms=None, seed=0, offset=0):
+    """dropoutOp in training mode: uniforms (same shape and dtype as x) or Philox keyed by seed."""
+    x = np.ascontiguousarray(x)
+    y = np.empty_like(x)
+    u = None if uniforms is None else np.ascontiguousarray(uniforms, dtype=x.dtype)
+    getattr(_lib, "oracle_dropout_" + _sfx(x.dtype))(_p(x), _p(y), _i64(x.size), C.c_double(prob),
+                                                     _p(u) if u is not None else None, C.c_uint64(seed),
+                                                     C.c_uint64(offset))
+    return y
+
+
+def dropout_bwd(dy, out, prob):
+    dy = np.ascontiguousarray(dy)
+    out = np.ascontiguousarray(out, dtype=dy.dtype)
+    dx = np.empty_like(dy)
+    getattr(_lib, "oracle_dropout_bwd_" + _sfx(dy.dtype))(_p(dy), _p(out), _p(dx), _i64(dy.size), C.c_double(prob))
+    return dx
+
+
 def _oli(shape, axis):
     outer_ = int(np.prod(shape[:axis], dtype=np.int64))
     inner = int(np.prod(shape[axis + 1:], dtype=np.int64))

@@ -17,6 +17,7 @@ is the record of where every number came from.
   byindices.json       TestByIndicesOpDo                   op_by_indices_test.go
   broadcast_add.json   broadcastAddTests                   operations_broadcast_test.go
   batchnorm.json       bnAllCases                          nn_amd64_test.go
+  dropout.json         TestDropoutAll                      op_dropout_test.go
 """
 import json
 import os
@@ -292,6 +293,25 @@ def extract_batchnorm(root):
                       "epsilon 1e-5", "cases": cases}
 
 
+def extract_dropout(root):
+    """TestDropoutAll (op_dropout_test.go:14-68): x = ones(5), an injected generator that cycles through
+    `rand`, cost = Mean(y); expected y, dcost/dy and dcost/dx."""
+    src = strip_comments(open(os.path.join(root, "op_dropout_test.go")).read())
+    table = region(src, "var tests = []struct", "for _, tt := range tests")
+    table = table[table.index("}{") + 1:]
+    cases = []
+    for blk in top_level_blocks(table):
+        m = re.match(r"\{\s*(Float64|Float32)\s*,\s*(" + NUM + r")\s*,(.*)\}\s*$", blk.strip(), flags=re.S)
+        if not m:
+            continue
+        lists = re.findall(r"\[\]float(?:32|64)\{([^}]*)\}", m.group(3))
+        if len(lists) != 4:
+            raise ValueError("dropout case with %d lists" % len(lists))
+        cases.append({"dtype": m.group(1).lower(), "prob": float(m.group(2)), "rand": numbers(lists[0]),
+                      "y": numbers(lists[1]), "y_grad": numbers(lists[2]), "x_grad": numbers(lists[3])})
+    return {"source": "op_dropout_test.go: TestDropoutAll; x = Ones() of shape (5), cost = Mean(y)", "cases": cases}
+
+
 def main():
     if len(sys.argv) != 2:
         raise SystemExit("usage: extract_goldens.py <path to a gorgonia checkout>")
@@ -306,6 +326,7 @@ def main():
         "byindices.json": extract_byindices(root),
         "broadcast_add.json": extract_broadcast(root),
         "batchnorm.json": extract_batchnorm(root),
+        "dropout.json": extract_dropout(root),
     }
     for name, doc in out.items():
         with open(os.path.join(HERE, name), "w") as f:

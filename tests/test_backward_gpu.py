@@ -227,3 +227,45 @@ def test_batchnorm_bwd(fresh, shape, dt, training):
     else:
         lim = (1e-5 if dt == np.float32 else 1e-11) * max(1.0, float(np.abs(want).max()))
         assert np.abs(dx.numpy().astype(np.float64) - want).max() <= lim
+
+
+def test_dropout_goldens_on_the_device(fresh):
+    # TestDropoutAll (op_dropout_test.go:14-68) with its injected generator as a device array
+    from tests import golden_util as G
+    e = fresh
+    for c in G.load("dropout.json")["cases"]:
+        dt = G.DT[c["dtype"]]
+        tx, tr = e.tensor(np.ones(5, dt)), e.tensor(np.array(c["rand"], dt))
+        y, dx = e.empty(5, dt), e.empty(5, dt)
+        e.Dropout(tx, y, c["prob"], uniforms=tr)
+        assert y.numpy().tolist() == c["y"], c
+        e.DropoutDiff(e.tensor(np.array(c["y_grad"], dt)), y, dx, c["prob"])
+        assert np.allclose(dx.numpy(), np.array(c["x_grad"], dt), rtol=1e-6 if dt == np.float32 else 1e-15, atol=0)
+
+
+@pytest.mark.parametrize("dt", [np.float32, np.float64])
+def test_dropout_stateless_generator_matches_the_oracle(fresh, dt):
+    e = fresh
+    n = (1 << 20) + 3
+    x = util.normal(80, n, dt)
+    tx, y, dx = e.tensor(x), e.empty(n, dt), e.empty(n, dt)
+    e.Dropout(tx, y, 0.25, seed=0x1234567890ABCDEF, offset=7)
+    want = oracle.dropout(x, 0.25, seed=0x1234567890ABCDEF, offset=7)
+    assert_bits_equal(y.numpy(), want)
+    assert abs(float((want != 0).mean()) - 0.75) < 0.005
+    dy = util.normal(81, n, dt)
+    e.DropoutDiff(e.tensor(dy), y, dx, 0.25)
+    assert_bits_equal(dx.numpy(), oracle.dropout_bwd(dy, want, 0.25))
+    # probability 0 hands the input through; a recorded tape replays the same draw
+    e.Dropout(tx, y, 0.0)
+    assert_bits_equal(y.numpy(), x)
+    e.Signal()
+    e.tape_begin()
+    e.Dropout(tx, y, 0.5, seed=99)
+    t = e.tape_end()
+    e.tape_launch(t)
+    first = y.numpy()
+    e.tape_launch(t)
+    assert_bits_equal(y.numpy(), first)
+    assert_bits_equal(first, oracle.dropout(x, 0.5, seed=99))
+    e.tape_destroy(t)

@@ -99,7 +99,12 @@ def test_fixtures_match_the_generator_if_a_checkout_is_given():
         pytest.skip("set GORGONIA_SRC to a gorgonia checkout to run this check")
     from tests.golden import extract_goldens as X
     assert X.extract_binop(root) == json.load(open(os.path.join(G.GOLDEN, "binop.json")))
-    assert X.extract_byindices(root) == json.load(open(os.path.join(G.GOLDEN, "byindices.json")))
+    for name, fn in (("byindices", X.extract_byindices), ("softmax_do", X.extract_softmax),
+                     ("maxpool_asym", X.extract_maxpool_asym), ("maxpool_basic", X.extract_maxpool_basic),
+                     ("conv_issue233", X.extract_conv), ("leakyrelu", X.extract_leakyrelu),
+                     ("broadcast_add", X.extract_broadcast), ("batchnorm", X.extract_batchnorm),
+                     ("dropout", X.extract_dropout)):
+        assert fn(root) == json.load(open(os.path.join(G.GOLDEN, name + ".json"))), name
 
 
 # ---- backward ops: known answers derived from the configurations of gorgonia's own tests ---------
@@ -199,3 +204,31 @@ def test_oracle_batchnorm_goldens(case):
     out = ((y * scale).astype(dt) + bias).astype(dt).reshape(x.shape[0], -1) @ fc.T
     want = np.asarray(case["train_result"], dt).reshape(out.shape)
     assert np.allclose(out, want, rtol=10 * tol, atol=10 * tol)
+
+
+def test_dropout_goldens():
+    """TestDropoutAll (op_dropout_test.go:14-68): x = ones(5), the injected generator cycles through `rand`,
+    cost = Mean(y), so dcost/dy = 1/5; forward output and input gradient as the reference expects them
+    (the gradient divides by the drop probability, and is 0 where the output is 0)."""
+    for c in G.load("dropout.json")["cases"]:
+        dt = G.DT[c["dtype"]]
+        x = np.ones(5, dt)
+        y = oracle.dropout(x, c["prob"], uniforms=np.array(c["rand"], dt))
+        assert y.tolist() == c["y"], c
+        dy = np.array(c["y_grad"], dt)
+        dx = oracle.dropout_bwd(dy, y, c["prob"])
+        want = np.array(c["x_grad"], dt)
+        assert np.allclose(dx, want, rtol=1e-6 if dt == np.float32 else 1e-15, atol=0), (c, dx)
+
+
+def test_dropout_philox_statistics():
+    # the stateless generator: uniform on [0, 1), the kept share matches 1 - p, replays are identical
+    x = np.ones(200_000, np.float32)
+    y = oracle.dropout(x, 0.3, seed=1234)
+    kept = float((y != 0).mean())
+    assert abs(kept - 0.7) < 0.005
+    assert np.all((y == 0) | (y == np.float32(1) / np.float32(0.7)))
+    assert np.array_equal(y, oracle.dropout(x, 0.3, seed=1234))
+    assert not np.array_equal(y, oracle.dropout(x, 0.3, seed=1235))
+    # an offset continues the same stream
+    assert np.array_equal(oracle.dropout(x[:1000], 0.3, seed=1234, offset=5000), y[5000:6000])

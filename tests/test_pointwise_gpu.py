@@ -324,3 +324,44 @@ def test_empty_inputs_are_no_ops(fresh):
     assert lib.b200_transpose(e.h, 4, None, None, 2, (C.c_int64 * 2)(0, 4), (C.c_int * 2)(1, 0)) == 0
     assert lib.b200_gather_rows(e.h, None, None, None, 0, 16, 4) == 0
     assert e.pending() == (0, 0)
+
+
+@pytest.mark.parametrize("dt", [np.float32, np.float64])
+@pytest.mark.parametrize("n", [5, 4099, util.STREAM_SIZE])
+def test_incr_mode_is_op_then_add(fresh, n, dt):
+    # ExternalOp.Do in Incr mode (execution.go:113-127): CUDADo into a temporary, then an unsafe add into
+    # op.Incr. One fused kernel here, the temporary never stored, the arena back where it was.
+    e = fresh
+    a, b, c = util.normal(31, n, dt), util.normal(32, n, dt), util.normal(33, n, dt)
+    ta, tb, tc = e.tensor(a), e.tensor(b), e.tensor(c)
+    e.Signal()
+    used, l0 = e.arena_stats()["used"], e.launches
+    e.BinaryIncr("mul", ta, tb, tc)
+    assert e.pending() == (2, 1)
+    got = tc.numpy()
+    assert e.launches == l0 + 1
+    assert e.arena_stats()["used"] == used
+    assert_bits_equal(got, oracle.binary("add", c, oracle.binary("mul", a, b)))
+    # scalar forms and a unary op
+    e.BinaryIncr("sub", ta, 2.5, tc)
+    want = oracle.binary("add", got, oracle.binary("sub", a, dt(2.5)))
+    assert_bits_equal(tc.numpy(), want)
+    e.BinaryIncr("div", 2.0, tb, tc)
+    want = oracle.binary("add", want, oracle.binary("div", dt(2.0), b))
+    assert_bits_equal(tc.numpy(), want)
+    e.UnaryIncr("tanh", ta, tc)
+    assert_pointwise_close(tc.numpy(), oracle.binary("add", want, oracle.unary("tanh", a)), 2e-6 if dt == np.float32 else 1e-13)
+
+
+def test_incr_mode_unfused_engine_gives_the_same_bits():
+    from gorgonia_b200 import Engine
+    n = 100_003
+    a, b, c = util.normal(34, n), util.normal(35, n), util.normal(36, n)
+    outs = []
+    for defer in (True, False):
+        e = Engine(0, 64 << 20, defer=defer)
+        ta, tb, tc = e.tensor(a), e.tensor(b), e.tensor(c)
+        e.BinaryIncr("pow", e.tensor(np.abs(a) + np.float32(0.1)), tb, tc)
+        outs.append(tc.numpy())
+        e.Close()
+    assert_bits_equal(outs[0], outs[1])
