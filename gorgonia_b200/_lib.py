@@ -94,7 +94,18 @@ lib = _load()
 _vp, _i, _i64, _d, _u = C.c_void_p, C.c_int, C.c_int64, C.c_double, C.c_uint
 _P = C.POINTER
 
+ALLREDUCE_FN = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_size_t)
+
 _SIGS = {
+    "b200_comm_create": (_i, [ALLREDUCE_FN, _vp, _i, _i, _P(_vp)]),
+    "b200_comm_create_nccl": (_i, [_vp, _vp, _i, _i, _P(_vp)]),
+    "b200_nccl_unique_id": (_i, [_vp]),
+    "b200_comm_destroy": (_i, [_vp]),
+    "b200_comm_world": (_i, [_vp]),
+    "b200_comm_rank": (_i, [_vp]),
+    "b200_comm_last_error": (C.c_char_p, [_vp]),
+    "b200_allreduce_mean": (_i, [_vp, _vp, _vp, _i64, _i]),
+    "b200_comm_allreduce_mean_host": (_i, [_vp, _vp, _i64, _i]),
     "b200_engine_create": (_i, [_i, C.c_size_t, _u, _P(_vp)]),
     "b200_engine_destroy": (_i, [_vp]),
     "b200_engine_device": (_i, [_vp]),

@@ -271,6 +271,33 @@ int b200_dropout_fwd(b200_engine *e, int dtype, const void *x, void *y, int64_t 
 int b200_dropout_bwd(b200_engine *e, int dtype, const void *dy, const void *out, void *dx, int64_t n,
                      double probability);
 
+/* ---- the training variant's collective ----------------------------------------------------------
+ * The mean of a flat gradient bucket over the ranks, taken after the last backward kernel and before
+ * Solver.Step (solvers.go:13-15). gorgonia itself has no distributed path (README.md:21; its
+ * data-parallel precedent is example_concurrent_training_test.go:80-115); the forward path never
+ * calls this. The transport is a function pointer: in-place sum of `count` elements of `dtype` at
+ * `buf` over all ranks, enqueued on `stream` (a cudaStream_t as an integer; 0 for host buffers),
+ * returning 0 on success.
+ * b200_comm_create        wraps any such function (the host program's own, or a test's).
+ * b200_comm_create_nccl   binds NCCL (loaded at run time by its soname) for the engine's device; id128
+ *                         is the 128-byte ncclUniqueId that rank 0 made with b200_nccl_unique_id and
+ *                         handed to the other ranks by whatever rendezvous the host program has.
+ * b200_allreduce_mean     device bucket: flushes the engine's queue, runs the transport on the
+ *                         engine's stream, then divides by the number of ranks on the same stream.
+ *                         A transport failure is B200_ERR_CUDA and leaves the bucket unscaled.
+ * b200_comm_allreduce_mean_host  the same on a host buffer, for CPU ranks (tests of the plumbing). */
+typedef struct b200_comm b200_comm;
+typedef int (*b200_allreduce_fn)(void *ctx, void *buf, int64_t count, int dtype, uintptr_t stream);
+int b200_comm_create(b200_allreduce_fn fn, void *ctx, int rank, int world, b200_comm **out);
+int b200_comm_create_nccl(b200_engine *e, const void *id128, int rank, int world, b200_comm **out);
+int b200_nccl_unique_id(void *id128);
+int b200_comm_destroy(b200_comm *c);
+int b200_comm_world(const b200_comm *c);
+int b200_comm_rank(const b200_comm *c);
+const char *b200_comm_last_error(const b200_comm *c);
+int b200_allreduce_mean(b200_engine *e, b200_comm *c, void *dptr, int64_t n, int dtype);
+int b200_comm_allreduce_mean_host(b200_comm *c, void *buf, int64_t n, int dtype);
+
 /* Engine.HasNaN / HasInf (cuda/engine.go:144-191; kernels cuda modules/src/misc.cu:13-55).
  * *result is 1 if any element is NaN (resp. ±Inf), else 0. Synchronises. */
 int b200_has_nan(b200_engine *e, int dtype, const void *x, int64_t n, int *result);

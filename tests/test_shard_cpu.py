@@ -50,13 +50,58 @@ def _worker(rank, world, port, total, q):
         whole = shard.all_gather_rows(local, total, dist)
         slowest = shard.max_over_ranks(10.0 + rank, dist)
         grad = np.full(1000, float(rank + 1), np.float32)     # ranks hold 1s and 2s: the mean is 1.5
-        shard.allreduce_mean_(grad, dist)
+        shard.allreduce_mean_(grad, dist)                      # through b200_comm_* with a gloo transport
         assert np.all(grad == np.float32(1.5))
+        _comm_error_paths(rank, world)
         dist.barrier()
         if rank == 0:
             q.put((whole, slowest))
     finally:
         dist.destroy_process_group()
+
+
+def _comm_error_paths(rank, world):
+    """Failures are made on the host: a transport that reports an error code on one rank after the
+    exchange took place, and one that raises. The failing rank gets B200_ERR_CUDA and an unscaled
+    bucket, the other rank its mean; nobody hangs because every rank still takes part in the exchange."""
+    from gorgonia_b200 import _lib
+    from gorgonia_b200._lib import B200Error
+
+    def summed(view):
+        dist.all_reduce(torch.from_numpy(view), op=dist.ReduceOp.SUM)
+
+    def fails_on_rank_1(view):
+        summed(view)
+        return 7 if rank == 1 else 0
+
+    def raises_on_rank_0(view):
+        summed(view)
+        if rank == 0:
+            raise RuntimeError("link down")
+
+    for transport, bad_rank in ((fails_on_rank_1, 1), (raises_on_rank_0, 0)):
+        comm = shard.Comm.from_callable(transport, rank, world)
+        assert comm.world == world
+        g = np.full(64, float(rank + 1), np.float64)
+        if rank == bad_rank:
+            with pytest.raises(B200Error) as ei:
+                comm.allreduce_mean_(g)
+            assert ei.value.code == _lib.ERR_CUDA and "not a mean" in str(ei.value)
+            assert np.all(g == 3.0)                          # summed by the transport, not divided
+        else:
+            comm.allreduce_mean_(g)
+            assert np.all(g == 1.5)
+        # the communicator stays usable after a failure
+        comm.close()
+    ok = shard.Comm.from_callable(lambda v: summed(v), rank, world)
+    g = np.arange(8, dtype=np.float32) * (rank + 1)
+    ok.allreduce_mean_(g)
+    assert np.array_equal(g, np.arange(8, dtype=np.float32) * 1.5)
+    empty = np.zeros(0, np.float32)
+    ok.allreduce_mean_(empty)                                # nothing to do, no exchange
+    ok.close()
+    with pytest.raises(B200Error):
+        shard.Comm.from_callable(summed, 5, world)           # rank outside the world
 
 
 def test_two_ranks_reassemble_the_single_rank_result():
