@@ -258,7 +258,7 @@ __global__ void __launch_bounds__(256) gemm_skinny_kernel(int transB, long long 
 int gemm_simt(b200_engine *e, int dtype, int transA, int transB, long long M, long long N, long long K,
               const void *A, long long lda, const void *B, long long ldb, void *C, long long ldc, long long batch,
               long long strideA, long long strideB, long long strideC, const Epilogue &ep) {
-  if (!transA && N <= 16 && M >= 32 && K >= 1 && batch <= 65535) {
+  if (!transA && N <= 16 && K >= 1 && batch <= 65535) {  // whatever M is: one summation order per shape class
     const unsigned blocks = (unsigned)std::max<long long>(1, std::min<long long>((M + 7) / 8, (long long)e->sm_count * 8));
     dim3 sgrid(blocks, (unsigned)batch);
     if (dtype == B200_F32)
