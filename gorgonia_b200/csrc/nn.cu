@@ -68,6 +68,7 @@ __device__ __forceinline__ float pool_tf32(float v) {
   asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(v));
   return __uint_as_float(r);
 }
+template <bool K2>  // K2: a 2 x 2 window, whose four loads are issued together
 __global__ void __launch_bounds__(256) maxpool_split_kernel(const float *__restrict__ x, float *__restrict__ y,
                                                             float *__restrict__ hi, float *__restrict__ lo,
                                                             long long B, int C, int H, int W, int Ho, int Wo, int kh,
@@ -85,23 +86,54 @@ __global__ void __launch_bounds__(256) maxpool_split_kernel(const float *__restr
     const int pp = p0 + tx;
     const int ph = pp / Wo, pw = pp - ph * Wo;
     int hs = ph * sH - oh0, ws = pw * sW - ow0;
-    const int he = min(hs + kh, H), we = min(ws + kw, W);
-    hs = max(hs, 0);
-    ws = max(ws, 0);
+    if (K2) {
+      // window rows hs, hs + 1 and columns ws, ws + 1, each inside the image or not; loads go to clamped
+      // addresses and the ones outside are dropped afterwards, so that all sixteen are in flight at once
+      const bool r0 = hs >= 0 && hs < H, r1 = hs + 1 >= 0 && hs + 1 < H;
+      const bool q0 = ws >= 0 && ws < W, q1 = ws + 1 >= 0 && ws + 1 < W;
+      const int h0c = min(max(hs, 0), H - 1), h1c = min(max(hs + 1, 0), H - 1);
+      const int w0c = min(max(ws, 0), W - 1), w1c = min(max(ws + 1, 0), W - 1);
+      float v[4][4];
 #pragma unroll
-    for (int j = ty; j < 32; j += 8) {
-      const int c = c0 + j;
-      float best = -FLT_MAX;
-      if (c < C && pp < HWo) {
+      for (int jj = 0; jj < 4; ++jj) {
+        const int c = min(c0 + ty + 8 * jj, C - 1);
         const float *in = x + (b * C + c) * (long long)H * W;
-        for (int hh = hs; hh < he; ++hh)
-          for (int ww = ws; ww < we; ++ww) {
-            const float v = __ldg(in + hh * W + ww);
-            if (v > best) best = v;
-          }
-        if (y) y[(b * C + c) * (long long)HWo + pp] = best;
+        const bool live = pp < HWo;
+        v[jj][0] = live ? __ldg(in + h0c * W + w0c) : 0.f;
+        v[jj][1] = live ? __ldg(in + h0c * W + w1c) : 0.f;
+        v[jj][2] = live ? __ldg(in + h1c * W + w0c) : 0.f;
+        v[jj][3] = live ? __ldg(in + h1c * W + w1c) : 0.f;
       }
-      tile[j][tx] = best;
+#pragma unroll
+      for (int jj = 0; jj < 4; ++jj) {
+        const int j = ty + 8 * jj, c = c0 + j;
+        float best = -FLT_MAX;   // row-major window order, strict '>': the reference's comparison
+        if (r0 && q0 && v[jj][0] > best) best = v[jj][0];
+        if (r0 && q1 && v[jj][1] > best) best = v[jj][1];
+        if (r1 && q0 && v[jj][2] > best) best = v[jj][2];
+        if (r1 && q1 && v[jj][3] > best) best = v[jj][3];
+        if (y && c < C && pp < HWo) y[(b * C + c) * (long long)HWo + pp] = best;
+        tile[j][tx] = best;
+      }
+    } else {
+      const int he = min(hs + kh, H), we = min(ws + kw, W);
+      hs = max(hs, 0);
+      ws = max(ws, 0);
+#pragma unroll
+      for (int j = ty; j < 32; j += 8) {
+        const int c = c0 + j;
+        float best = -FLT_MAX;
+        if (c < C && pp < HWo) {
+          const float *in = x + (b * C + c) * (long long)H * W;
+          for (int hh = hs; hh < he; ++hh)
+            for (int ww = ws; ww < we; ++ww) {
+              const float v = __ldg(in + hh * W + ww);
+              if (v > best) best = v;
+            }
+          if (y) y[(b * C + c) * (long long)HWo + pp] = best;
+        }
+        tile[j][tx] = best;
+      }
     }
     __syncthreads();
     const long long ob = b * (long long)HWo * C;
@@ -889,11 +921,16 @@ int b200_maxpool2d_split_fwd(b200_engine *e, const void *x, void *y, void *y_hi,
   int rc = flush_pending(e);
   if (rc != B200_OK) return rc;
   const long long tiles = B * ((Ho * Wo + 31) / 32) * ((C + 31) / 32);
-  const int blocks = (int)std::max<long long>(1, std::min<long long>(tiles, (long long)e->sm_count * 16));
-  maxpool_split_kernel<<<blocks, 256, 0, e->stream>>>((const float *)x, (float *)y, (float *)y_hi, (float *)y_lo, B,
-                                                      (int)C, (int)H, (int)W, (int)Ho, (int)Wo, kh, kw, stride_h,
-                                                      stride_w, explicit_padding ? pad_south : pad_north,
-                                                      explicit_padding ? pad_east : pad_west);
+  const int blocks = (int)std::max<long long>(1, std::min<long long>(tiles, (long long)e->sm_count * 32));
+  const int oh0 = explicit_padding ? pad_south : pad_north, ow0 = explicit_padding ? pad_east : pad_west;
+  if (kh == 2 && kw == 2)
+    maxpool_split_kernel<true><<<blocks, 256, 0, e->stream>>>((const float *)x, (float *)y, (float *)y_hi,
+                                                              (float *)y_lo, B, (int)C, (int)H, (int)W, (int)Ho,
+                                                              (int)Wo, kh, kw, stride_h, stride_w, oh0, ow0);
+  else
+    maxpool_split_kernel<false><<<blocks, 256, 0, e->stream>>>((const float *)x, (float *)y, (float *)y_hi,
+                                                               (float *)y_lo, B, (int)C, (int)H, (int)W, (int)Ho,
+                                                               (int)Wo, kh, kw, stride_h, stride_w, oh0, ow0);
   B200_CHECK_LAUNCH(e, "maxpool_split_kernel");
   return B200_OK;
 }
