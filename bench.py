@@ -426,9 +426,9 @@ def wl_elementwise(ctx, args, main):
     hout = e.host_alloc(4 * n)
     del x, y, base
     ops = gpu_sweep_ops(e, T)
-    sampler = ClockSampler(ctx.local_rank) if main else None
+    sampler = ClockSampler(ctx.local_rank)
     step_s, launches = ctx.timed(lambda: gpu_sweep_step(e, ops), steps, warmup, sampler)
-    clocks = sampler.stop() if (main and ctx.rank == 0) else None
+    clocks = sampler.stop() if ctx.rank == 0 else None
     bytes_step = BYTES_PER_ELEM_STEP * n
     res = {"metric": "elementwise sweep throughput (algorithmic bytes)", "unit": "GB/s",
            "value": ctx.world * bytes_step / step_s / 1e9, "ms_per_step": step_s * 1e3, "dtype": "f32",
@@ -581,9 +581,9 @@ def wl_gemm(ctx, args, main):
     hc = e.host_alloc(4 * n * n)
     e.copy_h2d_async(ta, ha)
     e.copy_h2d_async(tb, hb)
-    sampler = ClockSampler(ctx.local_rank) if main else None
+    sampler = ClockSampler(ctx.local_rank)
     step_s, launches = ctx.timed(lambda: e.MatMul(ta, tb, tc), steps, warmup, sampler)
-    clocks = sampler.stop() if (main and ctx.rank == 0) else None
+    clocks = sampler.stop() if ctx.rank == 0 else None
     flops = 2.0 * n ** 3
     pk = peaks()
     tf = flops / step_s / 1e12
@@ -742,7 +742,7 @@ def wl_backward(ctx, args, main):
     e = ctx.make_engine(6 << 30)
     g = np.random.Generator(np.random.Philox(17 + ctx.rank))
     per_op, total_bytes, total_s, launches = {}, 0.0, 0.0, 0
-    sampler = ClockSampler(ctx.local_rank) if main else None
+    sampler = ClockSampler(ctx.local_rank)
     # max-pool gradient: dy + mask read, dx written
     B, Cc, H, W = BACKWARD_SHAPES["pool"]
     x = e.tensor(g.standard_normal((B, Cc, H, W), dtype=np.float32))
@@ -791,7 +791,7 @@ def wl_backward(ctx, args, main):
     c = e.tensor(np.zeros((n, n), np.float32))
     s_, l_ = ctx.timed(lambda: e.MatMul(a, b, c, incr=True), steps, warmup)
     launches += l_
-    clocks = sampler.stop() if (main and ctx.rank == 0) else None
+    clocks = sampler.stop() if ctx.rank == 0 else None
     pk = peaks()
     gbs = total_bytes / total_s / 1e9
     return {"metric": "backward ops throughput (algorithmic bytes)", "unit": "GB/s", "value": ctx.world * gbs,
@@ -820,6 +820,42 @@ def model_input(name, batch, seed):
 def make_model(name, e, batch):
     from gorgonia_b200 import tapes
     return {"mlp": tapes.MLP, "lenet": tapes.LeNet, "yolo": tapes.TinyYolo}[name](e, batch)
+
+
+def dominant_kernel(ctx, name, m, b):
+    """Times the launch that takes the largest share of a graph's step on its own: tiny-YOLO's layer 7
+    (1024 -> 1024 channels on 13 x 13, conv_tma_kernel), LeNet's conv1 + pool (conv_win_kernel). Ten
+    launches between CUDA events on the engine's stream, after the step itself has run."""
+    if name == "mlp":
+        return None
+    e = ctx.engine
+    if name == "yolo":
+        chain, i, kern = m.chain_b, 1, "conv_tma_kernel<128, 32> (layer 7: 1024 -> 1024 channels, 3x3, 13x13)"
+    else:
+        chain, i, kern = m.chain, 1, "conv_win_kernel<64, 32> (conv1 + pool: 32 -> 64 channels, 3x3, 14x14)"
+    L, prev = chain.layers[i], chain.layers[i - 1]
+    x_split = prev["pool_split"] if prev.get("pool_split") is not None else prev["split"]
+    x_plain = prev["pooled"] if prev.get("pooled") is not None else prev["y"]
+
+    def launch():
+        e.Conv2dChain(x_plain if x_split is None else None, L["w"], L["y"], L["in_shape"], pad=L["pad"], bias=L["bias"],
+                      act=L["act"], alpha=L["alpha"], pool2=L["fuse_pool"], x_split=x_split, y_split=L["split"])
+    launch()
+    e.Signal()
+    e.record(ctx.ev[0])
+    for _ in range(10):
+        launch()
+    e.record(ctx.ev[1])
+    us = e.elapsed_ms(*ctx.ev) * 100.0
+    B, Cc, H, W = L["in_shape"]
+    K, _, kh, kw = L["w"].shape
+    flops = 2.0 * B * H * W * K * Cc * kh * kw        # stride 1, same padding
+    out = {"kernel": kern, "us": us, "flops": flops, "tflops": flops / (us * 1e-6) / 1e12}
+    if name == "yolo" and b == 64:
+        out["traffic"] = 547.3e6
+        out["traffic_source"] = ("dram__bytes_read.sum + dram__bytes_write.sum of this launch under ncu "
+                                 "(profiles/conv_tma_kernel_yolo_layer7.txt)")
+    return out
 
 
 def parity_model(name, m, x):
@@ -861,15 +897,16 @@ def wl_model(ctx, args, name, main):
     e.copy_h2d_async(m.x, hx)
     # device-resident: one recorded tape per step
     m.record()
-    sampler = ClockSampler(ctx.local_rank) if main else None
+    sampler = ClockSampler(ctx.local_rank)
     step_s, launches = ctx.timed(m.replay, steps, warmup, sampler)
-    clocks = sampler.stop() if (main and ctx.rank == 0) else None
+    clocks = sampler.stop() if ctx.rank == 0 else None
     pk = peaks()
     tf = m.flops_per_sample * b / step_s / 1e12
     peak32, peak32_src = tf32_peak(e, pk)
     parity = None
     if ctx.rank == 0 and not args.profile:
         parity = parity_model(name, m, x)
+    dom = dominant_kernel(ctx, name, m, b) if not args.profile else None
     res = {"metric": f"{name} forward throughput", "unit": "samples/s", "value": total / step_s,
            "ms_per_step": step_s * 1e3, "dtype": "f32 (matrix products as 3xTF32, fp32 accumulate)",
            "config": {"workload": f"{name}_forward", "global_batch": total, "batch_per_gpu": b,
@@ -885,6 +922,13 @@ def wl_model(ctx, args, name, main):
                         "peak": peak32, "unit": "TFLOP/s (TF32 issued = 3 x algorithmic)",
                         "frac": 3 * tf / peak32, "peak_source": peak32_src,
                         "frac_of_bf16_burst_over_2": 3 * tf / (pk["bf16_tflops"] / 2), "traffic": None}}
+    if dom is not None:
+        # the dominant kernel of the step, timed alone: its own launches between CUDA events
+        whole = {k: res["roofline"][k] for k in ("kernel", "achieved", "frac")}
+        res["roofline"].update({"kernel": dom["kernel"], "achieved": 3 * dom["tflops"], "frac": 3 * dom["tflops"] / peak32,
+                                "us_per_launch": dom["us"], "share_of_step": dom["us"] * 1e-6 / step_s,
+                                "algorithmic_flops_per_launch": dom["flops"], "traffic": dom.get("traffic"),
+                                "traffic_source": dom.get("traffic_source"), "whole_step": whole})
     if args.profile:
         m.close()
         return res
