@@ -299,6 +299,27 @@ class TinyYolo(_Tape):
         else:
             self.out = self.conv[8]
 
+    def load_weights(self, kernels, biases):
+        """Replaces the seeded weights, e.g. by what darknet.load_tiny_yolo_v2 read from a file. What the
+        engine derived from the old values is dropped by withdrawing and renewing the constant
+        declaration; a tape recorded earlier reads those derived forms, so it is recorded again."""
+        e = self.e
+        e.Signal()
+        had_tape = self.tape is not None
+        self.close()
+        for i in range(9):
+            w, b = np.ascontiguousarray(kernels[i], np.float32), np.ascontiguousarray(biases[i], np.float32)
+            if w.shape != self.w[i].shape or b.shape != self.b[i].shape:
+                raise ValueError(f"layer {i}: got {w.shape} / {b.shape}, the tape has {self.w[i].shape} / {self.b[i].shape}")
+            e.constant(self.w[i], False)
+            self.w[i].set(w)
+            self.b[i].set(b)
+            e.constant(self.w[i])
+            self.w_host[i], self.b_host[i] = w, b
+        if had_tape:
+            self.record()
+        return self
+
     def forward(self):
         e, a = self.e, self.x
         if self.fused:

@@ -232,3 +232,39 @@ def test_dropout_philox_statistics():
     assert not np.array_equal(y, oracle.dropout(x, 0.3, seed=1235))
     # an offset continues the same stream
     assert np.array_equal(oracle.dropout(x[:1000], 0.3, seed=1234, offset=5000), y[5000:6000])
+
+
+def _oldsoftmax_grad(a, g, axis):
+    """The gradient of gorgonia's second softmax formulation, oldsoftmax = Exp -> Sum -> broadcast Div
+    (op_softmax_test.go:239-282), composed from the primitive differentiation rules in double:
+    Div: d(e/s)/de = 1/s, d(e/s)/ds = -e/s^2; Sum: its gradient is repeated along the axis; Exp: de/da = e."""
+    a = a.astype(np.float64)
+    e = np.exp(a)
+    s = e.sum(axis=axis, keepdims=True)
+    de = g / s
+    ds = -(g * e / (s * s)).sum(axis=axis, keepdims=True)
+    return (de + ds) * e
+
+
+@pytest.mark.parametrize("dt", [np.float32, np.float64])
+def test_softmax_bwd_agrees_with_the_old_softmax_composition(dt):
+    # TestOld_NewSoftmax (op_softmax_test.go:284-330) builds both formulations on this input with cost =
+    # Sum(softmax): the gradient is zero up to rounding, whichever way it is formed
+    a = np.array([0.1, 0.1, 0.3, 0.1, 0.4], dt)
+    y = oracle.softmax(a)
+    dx = oracle.softmax_bwd(y, np.ones_like(a))
+    assert np.abs(dx).max() <= (1e-7 if dt == np.float32 else 1e-16)
+    assert np.abs(_oldsoftmax_grad(a, np.ones(5), 0)).max() <= 1e-16
+    # with an upstream gradient that does not cancel, on matrices and on a middle axis
+    for shape, axis in (((5,), 0), ((7, 10), 1), ((4, 6, 3), 1)):
+        x = np.random.Generator(np.random.Philox(5)).standard_normal(shape).astype(dt)
+        g = np.random.Generator(np.random.Philox(6)).standard_normal(shape).astype(dt)
+        got = oracle.softmax_bwd(oracle.softmax(x, axis), g, axis)
+        want = _oldsoftmax_grad(x, g.astype(np.float64), axis)
+        assert np.allclose(got, want, rtol=2e-5 if dt == np.float32 else 1e-12, atol=2e-6 if dt == np.float32 else 1e-14)
+        # log-softmax = Log(oldsoftmax): one more primitive rule, d log(y) = g / y
+        yl = oracle.softmax(x, axis, log=True)
+        gotl = oracle.softmax_bwd(yl, g, axis, log=True)
+        ysm = np.exp(yl.astype(np.float64))
+        wantl = _oldsoftmax_grad(x, g.astype(np.float64) / ysm, axis)
+        assert np.allclose(gotl, wantl, rtol=2e-5 if dt == np.float32 else 1e-11, atol=2e-5 if dt == np.float32 else 1e-13)

@@ -234,3 +234,33 @@ def test_bounded_wait_that_runs_out_is_reported(fresh):
     assert ei.value.code == _lib.ERR_TIMEOUT
     e.AddScalar(a, 1.0, unsafe=True)
     assert a.numpy().tolist() == [1, 2, 3, 4, 5, 6, 7, 8]
+
+
+def test_tiny_yolo_with_weights_from_a_darknet_file(fresh, tmp_path):
+    # weights travel file -> host fold -> device; the forward pass then matches the oracle run with the
+    # same folded weights, also through the tape (recorded again by load_weights)
+    from gorgonia_b200 import darknet
+    e = fresh
+    ch = (3, 16, 32, 64, 32, 64, 32, 64, 32, 20)
+    m = tapes.TinyYolo(e, 2, size=64, channels=ch)
+    x = util.uniform(140, (2, 3, 64, 64))
+    m.x.set(x)
+    m.record()
+    g = util.rng(141)
+    layers = []
+    for i, shape in enumerate(darknet.layer_shapes(ch)):
+        L = {"bias": (g.standard_normal(shape[0]) * 0.1).astype(np.float32),
+             "kernel": (g.standard_normal(shape) * np.sqrt(2.0 / np.prod(shape[1:]))).astype(np.float32)}
+        if i < 8:
+            L.update(gamma=(1 + 0.1 * g.standard_normal(shape[0])).astype(np.float32),
+                     mean=(0.1 * g.standard_normal(shape[0])).astype(np.float32),
+                     var=(g.random(shape[0]) + 0.5).astype(np.float32))
+        layers.append(L)
+    path = str(tmp_path / "net.weights")
+    darknet.write_tiny_yolo_v2(path, layers)
+    m.load_weights(*darknet.load_tiny_yolo_v2(path, ch))
+    got = m.forward().numpy()
+    assert_gemm_close(got, graphs.tiny_yolo(m, x), 1e-5)
+    m.replay()
+    assert_bits_equal(m.out.numpy(), got)
+    m.close()
