@@ -38,21 +38,6 @@ namespace b200 {
 // conv_tc.cu: filters split into TF32 head/tail and reordered to (tap, channel); cached for constants
 int conv_filters_tap_major(b200_engine *e, const float *w, int K, int C, int taps, TcOperand *wf, void **blk);
 
-// conv_tma_pair.cu: the same convolution run by pairs of CTAs that share their filter slabs
-struct ConvPairParams {
-  float *y;
-  float *y_hi, *y_lo;
-  long long Mtot;
-  int K, Wo, hw;
-  int kw, padH, padW, sH, sW, dH, dW;
-  int cblocks, num_k, chunk_k;
-  int tiles_m, tiles_n, stages;
-  Epilogue ep;
-  int *err_flag;
-};
-bool conv_pair_pays(const b200_engine *e, int K, long long tiles_m, long long tiles_n);
-int launch_conv_tma_pair(b200_engine *e, const CUtensorMap *tm, ConvPairParams &p);
-
 constexpr int CT_BM = 128;
 constexpr int CT_THREADS = 320;  // 10 warps
 
@@ -701,35 +686,7 @@ int conv2d_tma(b200_engine *e, const float *x, const float *w, float *y, long lo
       if (r != CUDA_SUCCESS) rc = set_error(e, B200_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d) for filters", (int)r);
     }
   }
-  const bool pair = rc == B200_OK && bn == 128 && !(e->flags & B200_ENGINE_NO_PAIRS) &&
-                    conv_pair_pays(e, K, p.tiles_m, p.tiles_n);
-  if (pair) {
-    // many tiles: pairs of CTAs that load half of each filter slab and hand it to each other
-    cuuint64_t wdims[3] = {(cuuint64_t)crs, (cuuint64_t)K, 1};
-    cuuint64_t wstrides[2] = {(cuuint64_t)wf.ld * 4, (cuuint64_t)K * wf.ld * 4};
-    cuuint32_t wbox[3] = {(cuuint32_t)ck, 64, 1};
-    cuuint32_t westr[3] = {1, 1, 1};
-    CUtensorMap tp[4];
-    tp[0] = tm[0];
-    tp[1] = tm[1];
-    for (int h = 0; h < 2 && rc == B200_OK; ++h) {
-      CUresult r = enc_tiled(&tp[2 + h], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void *>(h ? wf.p1 : wf.p0),
-                             wdims, wstrides, wbox, westr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
-                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-      if (r != CUDA_SUCCESS) rc = set_error(e, B200_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d) for filter halves", (int)r);
-    }
-    if (rc == B200_OK) {
-      ConvPairParams q = ConvPairParams();
-      q.y = p.y; q.y_hi = p.y_hi; q.y_lo = p.y_lo;
-      q.Mtot = p.Mtot; q.K = p.K; q.Wo = p.Wo; q.hw = p.hw;
-      q.kw = p.kw; q.padH = p.padH; q.padW = p.padW; q.sH = p.sH; q.sW = p.sW; q.dH = p.dH; q.dW = p.dW;
-      q.cblocks = p.cblocks; q.num_k = p.num_k; q.chunk_k = p.chunk_k;
-      q.tiles_m = p.tiles_m; q.tiles_n = p.tiles_n;
-      q.ep = p.ep;
-      q.err_flag = p.err_flag;
-      rc = launch_conv_tma_pair(e, tp, q);
-    }
-  } else if (rc == B200_OK) {
+  if (rc == B200_OK) {
     if (bn == 128) rc = launch_conv_tma<128, 32>(e, tm, p);
     else if (bn == 64) rc = launch_conv_tma<64, 32>(e, tm, p);
     else rc = launch_conv_tma<32, 32>(e, tm, p);

@@ -87,35 +87,6 @@ __device__ __forceinline__ bool mbar_wait_relaxed(uint64_t *bar, uint32_t parity
   }
 }
 
-// ---- thread-block clusters: the peer CTA's shared memory and barriers ----------------------------
-__device__ __forceinline__ uint32_t cluster_ctarank() {
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-  return r;
-}
-// The shared::cluster address of `smem_cta_addr` (a shared::cta address of this CTA) in CTA `rank`.
-__device__ __forceinline__ uint32_t mapa(uint32_t smem_cta_addr, uint32_t rank) {
-  uint32_t r;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_cta_addr), "r"(rank));
-  return r;
-}
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
-}
-// Bulk copy from this CTA's shared memory into a peer's, completing `bytes` on the peer's mbarrier
-// (no multicast: one source, one destination). 16-byte aligned addresses, size a multiple of 16.
-__device__ __forceinline__ void bulk_s2peer(uint32_t dst_cluster_addr, const void *smem_src, uint32_t bytes,
-                                            uint32_t bar_cluster_addr) {
-  asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                   dst_cluster_addr),
-               "r"(smem_addr(smem_src)), "r"(bytes), "r"(bar_cluster_addr)
-               : "memory");
-}
-// All threads of all CTAs of the cluster.
-__device__ __forceinline__ void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-
 // ---- proxies / fences ---------------------------------------------------------------------------
 // generic-proxy writes to shared memory -> visible to the async proxy (TMA store, tcgen05.mma)
 __device__ __forceinline__ void fence_proxy_async_smem() {

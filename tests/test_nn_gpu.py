@@ -402,27 +402,3 @@ def test_maxpool_split_form(fresh, case):
     e.MaxPool2DSplit(e.tensor(x), None, (hi2, lo2), kernel, pad, stride)
     assert_bits_equal(hi2.numpy(), h)
     assert_bits_equal(lo2.numpy(), l)
-
-
-@pytest.mark.parametrize("case", [((15, 64, 52, 52), 128),      # 317 position tiles: an odd tail for the last pair
-                                  ((12, 64, 40, 40), 192),      # two column tiles, the second half empty
-                                  ((5, 128, 52, 52), 256)])     # 18 k-blocks per tap row, two full column tiles
-def test_convolution_on_cta_pairs_equals_single_ctas(case):
-    # large launches run on pairs of CTAs that hand each other half of every filter slab; the arithmetic per
-    # tile is the same, so the result must equal the one-CTA-per-tile kernel bit for bit, and the oracle
-    from gorgonia_b200 import Engine
-    shape, K = case
-    x = util.uniform(150, shape) - np.float32(0.5)
-    w = util.normal(151, (K, shape[1], 3, 3), scale=0.05)
-    bias = util.normal(152, K, scale=0.1)
-    outs = []
-    for pairs in (True, False):
-        e = Engine(0, 1 << 30, pairs=pairs)
-        y = e.empty((shape[0], K, shape[2], shape[3]))
-        e.Conv2d(e.tensor(x), e.tensor(w), y, pad=(1, 1), bias=e.tensor(bias), act="leaky", alpha=0.1)
-        outs.append(y.numpy())
-        e.Signal()
-        e.Close()
-    assert_bits_equal(outs[0], outs[1])
-    want = oracle.leaky_relu((oracle.conv2d(x, w, (1, 1)) + bias[None, :, None, None]).astype(np.float32), 0.1)
-    assert_gemm_close(outs[0], want, 1e-5)
