@@ -94,10 +94,27 @@ __device__ __forceinline__ double add_rn(double a, double b) { return __dadd_rn(
 __device__ __forceinline__ float sub_rn(float a, float b) { return __fsub_rn(a, b); }
 __device__ __forceinline__ double sub_rn(double a, double b) { return __dsub_rn(a, b); }
 
+__device__ __forceinline__ float rcp_approx(float d) {  // 1 ulp, subnormal results kept
+  float r;
+  asm("rcp.approx.f32 %0, %1;" : "=f"(r) : "f"(d));
+  return r;
+}
+// Without the subnormal handling, for arguments and results known to be normal:
+__device__ __forceinline__ float rcp_approx_ftz(float d) {
+  float r;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(d));
+  return r;
+}
+__device__ __forceinline__ float ex2_approx_ftz(float d) {  // relative error below 2^-22
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(d));
+  return r;
+}
+
 __device__ __forceinline__ float sigmoid_(float x) {
   if (x < -88.f) return 0.f;
   if (x > 15.f) return 1.f;
-  return 1.f / (1.f + expf(-x));
+  return rcp_approx(1.f + expf(-x));  // expf within 2 ulp, the reciprocal within 1
 }
 __device__ __forceinline__ double sigmoid_(double x) {
   if (x < -709.0) return 0.0;
@@ -114,6 +131,74 @@ __device__ __forceinline__ double softplus_(double x) {
   if (x > 16.0) return x;
   return log1p(exp(x));
 }
+
+// tanh in float32 without a branch: below 0.55 an odd polynomial (x + x z q(z), z = x^2, fitted to
+// 7e-8 relative), above it 1 - 2 / (e^{2|x|} + 1), where the errors of the fast exponential and
+// reciprocal are scaled by 2 / (e^{2|x|} + 1) <= 0.5 against a result >= 0.5: 3e-7 relative in all.
+__device__ __forceinline__ float tanh_(float x) {
+  const float ax = fabsf(x);
+  const float z = __fmul_rn(x, x);
+  float q = -0.006188455503433943f;
+  q = __fmaf_rn(q, z, 0.021012423560023308f);
+  q = __fmaf_rn(q, z, -0.05383826792240143f);
+  q = __fmaf_rn(q, z, 0.1333245486021042f);
+  q = __fmaf_rn(q, z, -0.3333331346511841f);
+  const float small = __fmaf_rn(ax, __fmul_rn(z, q), ax);
+  const float E = ex2_approx_ftz(__fmul_rn(ax, 2.8853900817779268f));  // e^{2|x|} >= 1; +inf from |x| > 44.4
+  const float big = __fmaf_rn(-2.f, rcp_approx_ftz(__fadd_rn(E, 1.f)), 1.f);
+  return copysignf(ax < 0.55f ? small : big, x);  // a NaN takes the second arm and stays a NaN; -0 stays -0
+}
+__device__ __forceinline__ double tanh_(double x) { return tanh(x); }
+
+// x^y in float32 for positive normal x: 2^(y log2 x) with log2 x carried as a pair of floats.
+//   x = 2^e m, m in [sqrt(1/2), sqrt 2); s = (m - 1) / (m + 1) as sh + sl (the rounding of m + 1 and
+//   of the quotient are recovered with fused multiply-adds); log2 m = (2 / ln 2) (s + s^3/3 + ... +
+//   s^11/11), the first term as an exact product pair, the rest (below 1 % of it) in plain floats;
+//   L = e + log2 m as Lh + Ll; p = y L as ph + pl with the product's rounding error recovered;
+//   result = ex2(ph - n + pl) 2^n, n = rint(ph).
+// The pair carries log2 x to about 2^-30 relative, so the result is within 8e-8 of the exact power
+// before the final ex2.approx (2^-22), for every |y log2 x| < 125. Anything else (x <= 0, subnormal,
+// infinite or NaN; a result near the ends of the exponent range; y infinite or NaN) goes to powf.
+__device__ __forceinline__ float pow_(float x, float y) {
+  const int bits = __float_as_int(x);
+  if ((unsigned)(bits - 0x00800000) < 0x7F000000u) {
+    const int e = (bits - 0x3F3504F3) >> 23;
+    const float m = __int_as_float(bits - (e << 23));
+    const float ef = (float)e;
+    const float f = __fsub_rn(m, 1.f);                 // exact
+    const float d = __fadd_rn(m, 1.f);
+    const float dl = __fsub_rn(m, __fsub_rn(d, 1.f));  // m + 1 == d + dl exactly
+    const float r = rcp_approx_ftz(d);                 // d in [1.7, 2.42)
+    const float sh = __fmul_rn(f, r);
+    const float res = __fmaf_rn(-sh, dl, __fmaf_rn(-sh, d, f));
+    const float sl = __fmul_rn(res, r);
+    const float s2 = __fmul_rn(sh, sh);
+    float Q = 1.f / 11.f;
+    Q = __fmaf_rn(Q, s2, 1.f / 9.f);
+    Q = __fmaf_rn(Q, s2, 1.f / 7.f);
+    Q = __fmaf_rn(Q, s2, 1.f / 5.f);
+    Q = __fmaf_rn(Q, s2, 1.f / 3.f);
+    Q = __fmul_rn(Q, s2);
+    constexpr float ch = 2.8853900817779268f;             // 2 / ln 2 rounded to float
+    constexpr float cl = (float)(2.8853900817779268 - (double)ch);
+    const float th = __fmul_rn(ch, sh);
+    float tl = __fmaf_rn(ch, sh, -th);
+    tl = __fmaf_rn(ch, sl, tl);
+    tl = __fmaf_rn(cl, sh, tl);
+    tl = __fmaf_rn(th, Q, tl);
+    const float Lh = __fadd_rn(ef, th);
+    const float Ll = __fadd_rn(__fadd_rn(__fsub_rn(ef, Lh), th), tl);
+    const float ph = __fmul_rn(y, Lh);
+    const float pl = __fmaf_rn(y, Ll, __fmaf_rn(y, Lh, -ph));
+    if (fabsf(ph) < 125.f) {
+      const float n = rintf(ph);
+      const float v = ex2_approx_ftz(__fadd_rn(__fsub_rn(ph, n), pl));  // argument within [-0.5, 0.5]
+      return __int_as_float(__float_as_int(v) + ((int)n << 23));
+    }
+  }
+  return powf(x, y);
+}
+__device__ __forceinline__ double pow_(double x, double y) { return pow(x, y); }
 
 #define PW_LOOP(expr)                 \
   _Pragma("unroll") for (int j = 0; j < V; ++j) { \
@@ -132,7 +217,7 @@ __device__ __forceinline__ void pw_apply(int op, const T (&a)[V], const T (&b)[V
     case B200_OP_SUB: PW_LOOP(sub_rn(x, y))
     case B200_OP_MUL: PW_LOOP(mul_rn(x, y))
     case B200_OP_DIV: PW_LOOP(x / y)
-    case B200_OP_POW: PW_LOOP(pow(x, y))
+    case B200_OP_POW: PW_LOOP(pow_(x, y))
     case B200_OP_MOD: PW_LOOP(fmod(x, y))
     case B200_OP_LT: PW_LOOP(x < y ? one : zero)
     case B200_OP_GT: PW_LOOP(x > y ? one : zero)
@@ -155,7 +240,7 @@ __device__ __forceinline__ void pw_apply(int op, const T (&a)[V], const T (&b)[V
     case B200_OP_INV: PW_LOOP(one / x)
     case B200_OP_INVSQRT: PW_LOOP(one / sqrt(x))
     case B200_OP_CUBE: PW_LOOP(mul_rn(mul_rn(x, x), x))
-    case B200_OP_TANH: PW_LOOP(tanh(x))
+    case B200_OP_TANH: PW_LOOP(tanh_(x))
     case B200_OP_SIGMOID: PW_LOOP(sigmoid_(x))
     case B200_OP_LOG1P: PW_LOOP(log1p(x))
     case B200_OP_EXPM1: PW_LOOP(expm1(x))

@@ -106,6 +106,50 @@ def test_unary(fresh, op, dt):
         tr.free()
 
 
+def test_pow_float32_over_the_whole_domain(fresh):
+    # the float32 power runs a pair-arithmetic fast path for positive normal bases and hands every
+    # other case to the library routine: both, and the hand-over, against the oracle
+    e = fresh
+    g = util.rng(77)
+    n = 1 << 18
+    cases = [
+        (np.exp(g.uniform(-80, 80, n)), g.uniform(-1.5, 1.5, n)),            # bases over the exponent range
+        (np.exp(g.uniform(-3, 3, n)), g.uniform(-45, 45, n)),                 # results up to the ends of the range
+        (1 + g.uniform(-2e-3, 2e-3, n), g.uniform(-3e4, 3e4, n)),             # bases next to 1, huge exponents
+        (np.exp(g.uniform(-1, 1, n)), np.rint(g.uniform(-8, 8, n))),          # whole exponents
+        (g.standard_normal(n), np.rint(g.uniform(-5, 5, n))),                 # negative bases, whole exponents
+        (g.standard_normal(n), g.standard_normal(n)),                         # negative bases: NaN where the oracle says so
+        (g.uniform(1e-45, 1e-38, n), g.uniform(-1, 1, n)),                    # subnormal bases
+    ]
+    sp = np.array([0.0, -0.0, 1.0, -1.0, np.inf, -np.inf, np.nan, 2.0, 0.5, 3e-45, 3.4e38, 1.2e-38], dtype=np.float32)
+    cases.append((np.repeat(sp, sp.size), np.tile(np.concatenate([sp[:9], np.array([3.0, -3.0, 0.25], np.float32)]), sp.size)))
+    for a, b in cases:
+        a, b = a.astype(np.float32), b.astype(np.float32)
+        with np.errstate(all="ignore"):
+            want = oracle.binary("pow", a, b)
+        ta, tb, tr = e.tensor(a), e.tensor(b), e.empty(a.size)
+        e.Pow(ta, tb, reuse=tr)
+        assert_pointwise_close(tr.numpy(), want)
+        for t in (ta, tb, tr):
+            t.free()
+
+
+def test_tanh_float32_arms_and_ends(fresh):
+    # the polynomial arm, the exponential arm, their seam at 0.55, saturation and special values
+    e = fresh
+    g = util.rng(78)
+    x = np.concatenate([g.uniform(-0.56, 0.56, 1 << 16), g.uniform(0.54, 0.56, 1 << 14), g.uniform(-12, 12, 1 << 16),
+                        g.uniform(-100, 100, 1 << 12), np.exp(g.uniform(-60, -3, 1 << 12)),
+                        np.array([0.0, -0.0, np.inf, -np.inf, np.nan, 0.55, -0.55, 44.3, 44.5, 3e-45, -1e-38])])
+    x = x.astype(np.float32)
+    tx = e.tensor(x)
+    e.Unary("tanh", tx, unsafe=True)
+    got = tx.numpy()
+    assert_pointwise_close(got, oracle.unary("tanh", x))
+    assert np.signbit(got[x == 0]).tolist() == np.signbit(x[x == 0]).tolist()   # tanh(-0) = -0
+    assert (np.abs(got[~np.isnan(x)]) <= 1).all()
+
+
 def test_safe_mode_is_an_error(fresh):
     # cuda/arith.go:47-48: neither reuse nor unsafe -> error
     from gorgonia_b200 import B200Error
