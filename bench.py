@@ -224,12 +224,13 @@ class Ctx:
             dist.init_process_group("nccl", device_id=torch.device("cuda", self.local_rank))
             self.dist = dist
         self.engine = None
+        self.pairs = not getattr(args, "no_pairs", False)
 
     def make_engine(self, arena_bytes):
         from gorgonia_b200 import Engine
         if self.engine is not None:
             self.engine.Close()
-        self.engine = Engine(device=self.local_rank, arena_bytes=int(arena_bytes))
+        self.engine = Engine(device=self.local_rank, arena_bytes=int(arena_bytes), pairs=self.pairs)
         self.ev = (self.engine.event(), self.engine.event())
         self._flush = None
         return self.engine
@@ -1144,6 +1145,8 @@ def main():
                          "GPU's shard of a multi-GPU run on a single GPU)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
     ap.add_argument("--no-others", action="store_true", help="measure only the chosen workload")
+    ap.add_argument("--no-pairs", action="store_true",
+                    help="tensor-core kernels never pair CTAs up on 256-row tiles (for comparisons)")
     ap.add_argument("--profile", action="store_true",
                     help="only warm-up and the device-resident timed steps (for runs under a profiler)")
     args = ap.parse_args()

@@ -21,7 +21,7 @@ class B200Error(RuntimeError):
 OK, ERR_INVALID, ERR_OOM, ERR_CUDA, ERR_UNSUPPORTED, ERR_TIMEOUT, ERR_STATE = range(7)
 F32, F64, BF16 = 0, 1, 2
 VV, VS, SV = 0, 1, 2
-ENGINE_MANAGED, ENGINE_NO_DEFER, ENGINE_CONV_GATHER, ENGINE_NO_STREAMK = 1, 2, 4, 8
+ENGINE_MANAGED, ENGINE_NO_DEFER, ENGINE_CONV_GATHER, ENGINE_NO_STREAMK, ENGINE_NO_PAIRS = 1, 2, 4, 8, 16
 CONV_SIMT, CONV_DIRECT, CONV_TC_GATHER, CONV_TC_TMA, CONV_TC_WINDOW = 0, 1, 2, 3, 4
 
 # op codes (B200_OP_* of the header)

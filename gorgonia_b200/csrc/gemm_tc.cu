@@ -24,7 +24,19 @@
 // fp32 into the same accumulator, smallest terms first. The split is one streaming pass into
 // arena scratch; the main loop then loads four tiles per stage and issues three MMAs per slice.
 //
-// No TMA multicast and no cluster launch anywhere: every CTA loads its own tiles from local HBM.
+// CTA pairs (PAIR, bf16 only): large problems run as clusters of two CTAs on neighbouring SMs that
+// share one 256-row tile: each CTA loads its own 128 rows of A and only half of the tile's B rows,
+// the even CTA issues tcgen05.mma.cta_group::2 (M = 256), which reads both halves of B across the
+// pair, and each CTA drains its own 128 rows of the accumulator. A CTA then brings a third less
+// into shared memory per k-block. The stage's "full" barrier lives in the even CTA and counts the
+// bytes of both CTAs' loads; "empty" and "accumulator full" exist in both and the even CTA's commits
+// name each in turn; "accumulator empty" lives in the even CTA and takes the arrivals of both
+// epilogues. 3xTF32 does not pair up: its wide instruction A_head x [B_head | B_tail] would take
+// B_head from one CTA and B_tail from the other, A_tail x B_head then needs half of B_head in each
+// at one common offset, i.e. a second, half-size slab, and with 7/8 of the bytes per CTA the pair
+// measured no faster than two CTAs on their own.
+//
+// No TMA multicast anywhere: every CTA loads its own tiles from local HBM.
 // Every mbarrier wait is bounded; a wait that runs out raises the engine's error word and all
 // roles leave their loops, TMEM is released and the kernel returns.
 #include <cuda.h>
@@ -73,31 +85,37 @@ struct GemmTcParams {
   int units;                    // tiles * num_k (0 when the k range is not shared)
   float *ws;                    // partial tiles, 2 slots of TC_BM x BN floats per CTA
   int *tile_count;              // parts delivered per tile; zero between launches
+  int workers;                  // CTAs, or CTA pairs, that share the tiles out
   Epilogue ep;
   int *err_flag;
 };
 
 // TERMS = 1: bf16 operands (kind::f16). TERMS = 3: fp32 as 3xTF32 (kind::tf32), tensor maps
 // 0/1 = head/tail of A, 2/3 = head/tail of B.
-template <int TERMS, int BN, bool A_MN, bool B_MN>
+// PAIR: two CTAs per 256-row tile (see the file comment); then B's map has a box of BN / 2 rows.
+template <int TERMS, int BN, bool A_MN, bool B_MN, bool PAIR>
 __global__ void __launch_bounds__(TC_THREADS, 1)
     gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmA1,
                    const __grid_constant__ CUtensorMap tmB0, const __grid_constant__ CUtensorMap tmB1,
                    const __grid_constant__ GemmTcParams p) {
+  static_assert(!PAIR || TERMS == 1, "only bf16 tiles are shared by a pair of CTAs");
   constexpr int ES = TERMS == 1 ? 2 : 4;           // operand element size
   constexpr int BK = TC_ROW_BYTES / ES;            // k elements per stage: 64 bf16 / 32 fp32
   constexpr int UK = 32 / ES;                      // k elements per MMA: 16 / 8
   constexpr int NSPLIT = TERMS == 1 ? 1 : 2;       // copies of each operand per stage (head, tail)
   constexpr int A_BYTES = TC_BM * TC_ROW_BYTES;    // 16 KB
   constexpr int B_BYTES = BN * TC_ROW_BYTES;
-  constexpr int STAGE_BYTES = NSPLIT * (A_BYTES + B_BYTES);
+  constexpr int BH_BYTES = B_BYTES / 2;            // half of the tile's B rows
+  // what one CTA holds per stage. Alone: every copy of A and B. In a pair: its A rows and its half of B
+  constexpr int STAGE_BYTES = !PAIR ? NSPLIT * (A_BYTES + B_BYTES) : A_BYTES + BH_BYTES;
   constexpr int MN_PER_BOX = TC_ROW_BYTES / ES;    // m/n elements covered by one MN-major box
-  constexpr uint32_t IDESC = make_idesc(TERMS == 1 ? 1 : 2, A_MN, B_MN, TC_BM, BN);
+  constexpr int MMA_M = PAIR ? 2 * TC_BM : TC_BM;
+  constexpr uint32_t IDESC = make_idesc(TERMS == 1 ? 1 : 2, A_MN, B_MN, MMA_M, BN);
   // 3xTF32: B's head and tail slabs are adjacent in shared memory, and so are the main and the
   // cross-term accumulator in tensor memory, so A_head x [B_head | B_tail] is ONE instruction of
   // width 2*BN. An instruction costs a fixed ~65 cycles on top of its arithmetic: two per k step
   // beat three.
-  constexpr uint32_t IDESC_WIDE = make_idesc(2, A_MN, B_MN, TC_BM, TERMS == 1 ? BN : 2 * BN);
+  constexpr uint32_t IDESC_WIDE = make_idesc(2, A_MN, B_MN, MMA_M, TERMS == 1 ? BN : 2 * BN);
   constexpr int MAX_STAGES = 8;
   // TMEM columns of one accumulator buffer: 3xTF32 keeps the cross terms in a second accumulator
   constexpr int ACC_COLS = TERMS == 1 ? BN : 2 * BN;
@@ -113,6 +131,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
   unsigned char *smem = reinterpret_cast<unsigned char *>(((uintptr_t)tc_smem_raw + 1023) & ~(uintptr_t)1023);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int stages = p.stages;
+  const uint32_t rank = PAIR ? ptx::cluster_ctarank() : 0u;  // 0: the CTA that issues the pair's MMAs
+  const int worker = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
   const long long tiles_per_batch = (long long)p.tiles_m * p.tiles_n;
   const long long total_tiles = tiles_per_batch * p.batch;
 
@@ -123,7 +143,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
     }
     for (int b = 0; b < 2; ++b) {
       ptx::mbar_init(&acc_full[b], 1);
-      ptx::mbar_init(&acc_empty[b], 8);  // one arrival per epilogue warp
+      ptx::mbar_init(&acc_empty[b], PAIR ? 16 : 8);  // one arrival per epilogue warp (of both CTAs)
     }
     ptx::mbar_init(&epi_bar, 8);
     ptx::fence_mbar_init();
@@ -131,8 +151,13 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
     s_last = 0;
   }
   if (warp == 1) {
-    ptx::tmem_alloc(&tmem_base_s, TMEM_COLS);
-    ptx::tmem_relinquish();
+    if (PAIR) {
+      ptx::tmem_alloc_pair(&tmem_base_s, TMEM_COLS);
+      ptx::tmem_relinquish_pair();
+    } else {
+      ptx::tmem_alloc(&tmem_base_s, TMEM_COLS);
+      ptx::tmem_relinquish();
+    }
   }
   if (warp == 0 && lane == 0) {
     ptx::prefetch_tmap(&tmA0);
@@ -144,8 +169,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
   }
   ptx::tc_fence_before_sync();
   __syncthreads();
+  if (PAIR) ptx::cluster_sync();  // the other CTA's barriers are initialised before anything reaches them
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = tmem_base_s;
+  // shared::cluster address of a barrier of the even CTA / of the other CTA
+  auto at_leader = [&](uint64_t *bar) { return PAIR ? ptx::map_to_rank(ptx::smem_addr(bar), 0u) : ptx::smem_addr(bar); };
+  auto at_peer = [&](uint64_t *bar) { return ptx::map_to_rank(ptx::smem_addr(bar), rank ^ 1u); };
 
   // tile index -> (batch, m block, n block); m blocks are walked in groups so that the CTAs of
   // one wave share B columns and A rows in L2
@@ -167,7 +196,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      TilePieces pieces(p.streamk, p.units, p.num_k, (int)total_tiles);
+      TilePieces pieces(p.streamk, p.units, p.num_k, (int)total_tiles, worker, p.workers);
       int tile, kb0, kb1;
       while (ok && pieces.next(tile, kb0, kb1)) {
         int bz, mb, nb;
@@ -178,29 +207,53 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
             break;
           }
           unsigned char *st = smem + (size_t)stage * STAGE_BYTES;
-          ptx::mbar_arrive_expect_tx(&full_bar[stage], STAGE_BYTES);
           const int k0 = kb * BK;
-#pragma unroll
-          for (int h = 0; h < NSPLIT; ++h) {
-            const CUtensorMap *ta = h == 0 ? &tmA0 : &tmA1;
-            const CUtensorMap *tb = h == 0 ? &tmB0 : &tmB1;
-            unsigned char *sa = st + h * A_BYTES;
-            unsigned char *sb = st + NSPLIT * A_BYTES + h * B_BYTES;
+          if (PAIR) {
+            // the even CTA arms the stage for the bytes of both CTAs; the odd CTA's bytes may land
+            // first, which only drives the pending count below zero for a moment
+            if (rank == 0) ptx::mbar_arrive_expect_tx(&full_bar[stage], 2 * STAGE_BYTES);
+            const uint32_t fb = at_leader(&full_bar[stage]);
+            const int m0 = (mb * 2 + (int)rank) * TC_BM;
             if (!A_MN) {
-              ptx::tma_load_3d(sa, ta, k0, mb * TC_BM, bz * p.a_zmul, &full_bar[stage]);
+              ptx::tma_load_3d_pair(st, &tmA0, k0, m0, bz * p.a_zmul, fb);
             } else {
 #pragma unroll
               for (int q = 0; q < TC_BM / MN_PER_BOX; ++q)
-                ptx::tma_load_3d(sa + q * (BK * TC_ROW_BYTES), ta, mb * TC_BM + q * MN_PER_BOX, k0,
-                                 bz * p.a_zmul, &full_bar[stage]);
+                ptx::tma_load_3d_pair(st + q * (BK * TC_ROW_BYTES), &tmA0, m0 + q * MN_PER_BOX, k0, bz * p.a_zmul, fb);
             }
+            unsigned char *sb = st + A_BYTES;
+            const int nh = nb * BN + (int)rank * (BN / 2);  // this CTA's half of the tile's B rows
             if (!B_MN) {
-              ptx::tma_load_3d(sb, tb, k0, nb * BN, bz * p.b_zmul, &full_bar[stage]);
+              ptx::tma_load_3d_pair(sb, &tmB0, k0, nh, bz * p.b_zmul, fb);  // box of BN / 2 rows
             } else {
 #pragma unroll
-              for (int q = 0; q < BN / MN_PER_BOX; ++q)
-                ptx::tma_load_3d(sb + q * (BK * TC_ROW_BYTES), tb, nb * BN + q * MN_PER_BOX, k0,
-                                 bz * p.b_zmul, &full_bar[stage]);
+              for (int q = 0; q < BN / 2 / MN_PER_BOX; ++q)
+                ptx::tma_load_3d_pair(sb + q * (BK * TC_ROW_BYTES), &tmB0, nh + q * MN_PER_BOX, k0, bz * p.b_zmul, fb);
+            }
+          } else {
+            ptx::mbar_arrive_expect_tx(&full_bar[stage], STAGE_BYTES);
+#pragma unroll
+            for (int h = 0; h < NSPLIT; ++h) {
+              const CUtensorMap *ta = h == 0 ? &tmA0 : &tmA1;
+              const CUtensorMap *tb = h == 0 ? &tmB0 : &tmB1;
+              unsigned char *sa = st + h * A_BYTES;
+              unsigned char *sb = st + NSPLIT * A_BYTES + h * B_BYTES;
+              if (!A_MN) {
+                ptx::tma_load_3d(sa, ta, k0, mb * TC_BM, bz * p.a_zmul, &full_bar[stage]);
+              } else {
+#pragma unroll
+                for (int q = 0; q < TC_BM / MN_PER_BOX; ++q)
+                  ptx::tma_load_3d(sa + q * (BK * TC_ROW_BYTES), ta, mb * TC_BM + q * MN_PER_BOX, k0,
+                                   bz * p.a_zmul, &full_bar[stage]);
+              }
+              if (!B_MN) {
+                ptx::tma_load_3d(sb, tb, k0, nb * BN, bz * p.b_zmul, &full_bar[stage]);
+              } else {
+#pragma unroll
+                for (int q = 0; q < BN / MN_PER_BOX; ++q)
+                  ptx::tma_load_3d(sb + q * (BK * TC_ROW_BYTES), tb, nb * BN + q * MN_PER_BOX, k0,
+                                   bz * p.b_zmul, &full_bar[stage]);
+              }
             }
           }
           if (++stage == stages) {
@@ -212,13 +265,29 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
       if (!ok) s_fail = 1;
     }
   } else if (warp == 1) {
-    // ---------------- MMA issuer ----------------
-    if (lane == 0) {
+    // ---------------- MMA issuer (of a pair: the even CTA's only) ----------------
+    if (lane == 0 && rank == 0) {
       int stage = 0;
       uint32_t phase = 0;
       int use = 0;  // accumulator-buffer uses so far (one per k-chunk)
       bool ok = true;
-      TilePieces pieces(p.streamk, p.units, p.num_k, (int)total_tiles);
+      // descriptors of stage 0, k-slice 0; a later stage adds its byte offset >> 4, a later k-slice
+      // 32 bytes along a K-major row or UK k-rows of an MN-major block (the steps the helpers take)
+      constexpr int A_STEP = (A_MN ? UK * TC_ROW_BYTES : 32) >> 4, B_STEP = (B_MN ? UK * TC_ROW_BYTES : 32) >> 4;
+      const uint32_t st0 = ptx::smem_addr(smem);
+      uint64_t a_desc0[NSPLIT], b_desc0[NSPLIT];
+#pragma unroll
+      for (int h = 0; h < NSPLIT; ++h) {
+        a_desc0[h] = make_smem_desc(st0 + h * A_BYTES, A_MN ? BK * TC_ROW_BYTES : 16, (A_MN && ES == 4) ? 512 : 1024,
+                                    (A_MN && ES == 4) ? 1 : 2);
+        // pair: this CTA's half of B
+        b_desc0[h] = make_smem_desc(st0 + NSPLIT * A_BYTES + h * B_BYTES, B_MN ? BK * TC_ROW_BYTES : 16,
+                                    (B_MN && ES == 4) ? 512 : 1024, (B_MN && ES == 4) ? 1 : 2);
+      }
+      const uint32_t full0 = ptx::smem_addr(&full_bar[0]), empty0 = ptx::smem_addr(&empty_bar[0]);
+      const uint32_t empty0_peer = PAIR ? ptx::map_to_rank(empty0, 1u) : 0u;
+      uint32_t ready = 0;  // the poll behind the previous k-block saw this stage's barrier complete
+      TilePieces pieces(p.streamk, p.units, p.num_k, (int)total_tiles, worker, p.workers);
       int tile, kb0, kb1;
       while (ok && pieces.next(tile, kb0, kb1)) {
         for (int kc = kb0; kc < kb1 && ok; kc += p.chunk_k, ++use) {
@@ -234,42 +303,35 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
           const uint32_t d_tail = d_main + BN;  // 3xTF32 only: the small cross terms
           const int kend = kc + p.chunk_k < kb1 ? kc + p.chunk_k : kb1;
           for (int kb = kc; kb < kend; ++kb) {
-            if (!ptx::mbar_wait(&full_bar[stage], phase)) {
+            if (!ready && !ptx::mbar_wait(&full_bar[stage], phase)) {
               ok = false;
               break;
             }
             ptx::tc_fence_after_sync();
-            const uint32_t st = ptx::smem_addr(smem + (size_t)stage * STAGE_BYTES);
-#pragma unroll
-            for (int kk = 0; kk < BK / UK; ++kk) {
-              // k-slice kk: 32 bytes further along a K-major row, UK k-rows further in an MN-major block
-              const uint32_t a_off = A_MN ? kk * UK * TC_ROW_BYTES : kk * 32;
-              const uint32_t b_off = B_MN ? kk * UK * TC_ROW_BYTES : kk * 32;
-              const uint32_t a_lbo = A_MN ? BK * TC_ROW_BYTES : 16;
-              const uint32_t b_lbo = B_MN ? BK * TC_ROW_BYTES : 16;
-              uint64_t ad[NSPLIT], bd[NSPLIT];
-#pragma unroll
-              for (int h = 0; h < NSPLIT; ++h) {
-                ad[h] = make_smem_desc(st + h * A_BYTES + a_off, a_lbo, (A_MN && ES == 4) ? 512 : 1024,
-                                       (A_MN && ES == 4) ? 1 : 2);
-                bd[h] = make_smem_desc(st + NSPLIT * A_BYTES + h * B_BYTES + b_off, b_lbo,
-                                       (B_MN && ES == 4) ? 512 : 1024, (B_MN && ES == 4) ? 1 : 2);
-              }
-              const uint32_t accumulate = (kb > kc || kk > 0) ? 1u : 0u;
-              if (TERMS == 1) {
-                ptx::mma_f16(d_main, ad[0], bd[0], IDESC, accumulate);
-              } else {
-                ptx::mma_tf32(d_main, ad[0], bd[0], IDESC_WIDE, accumulate);       // hi * [hi | lo]
-                ptx::mma_tf32(d_tail, ad[NSPLIT - 1], bd[0], IDESC, 1u);           // lo * hi
-              }
-            }
-            ptx::mma_commit(&empty_bar[stage]);  // the stage is free once these MMAs have read it
-            if (++stage == stages) {
-              stage = 0;
-              phase ^= 1;
+            const int ns = stage + 1 == stages ? 0 : stage + 1;
+            const uint32_t nphase = ns == 0 ? phase ^ 1u : phase;
+            const uint64_t soff = (uint64_t)((uint32_t)stage * (uint32_t)(STAGE_BYTES >> 4));  // stays inside the address field
+            const uint32_t eb = empty0 + (uint32_t)stage * 8u, ebp = empty0_peer + (uint32_t)stage * 8u;
+            const uint32_t nf = full0 + (uint32_t)ns * 8u;
+            const uint32_t first = kb > kc ? 1u : 0u;  // the chunk's first MMA overwrites the accumulator
+            if (TERMS == 1)
+              ready = ptx::kblock_f16<PAIR, A_STEP, B_STEP>(d_main, a_desc0[0] + soff, b_desc0[0] + soff, IDESC, first, eb,
+                                                            ebp, nf, nphase);
+            else  // hi * [hi | lo] into d_main (width 2 BN), lo * hi into d_tail
+              ready = ptx::kblock_tf32x3<false, A_STEP, B_STEP>(d_main, d_tail, a_desc0[0] + soff, a_desc0[NSPLIT - 1] + soff,
+                                                                b_desc0[0] + soff, b_desc0[0] + soff, IDESC_WIDE, IDESC, first,
+                                                                eb, ebp, nf, nphase);
+            stage = ns;
+            phase = nphase;
+          }
+          if (ok) {  // this chunk's accumulators are complete
+            if (PAIR) {
+              ptx::mma_commit_pair(ptx::smem_addr(&acc_full[buf]));
+              ptx::mma_commit_pair(at_peer(&acc_full[buf]));
+            } else {
+              ptx::mma_commit(&acc_full[buf]);
             }
           }
-          if (ok) ptx::mma_commit(&acc_full[buf]);  // this chunk's accumulators are complete
         }
       }
       if (!ok) s_fail = 1;
@@ -291,7 +353,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
       epi_phase ^= 1;
       return done;
     };
-    TilePieces pieces(p.streamk, p.units, p.num_k, (int)total_tiles);
+    TilePieces pieces(p.streamk, p.units, p.num_k, (int)total_tiles, worker, p.workers);
     int tile, kb0, kb1;
     while (ok && pieces.next(tile, kb0, kb1)) {
       const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
@@ -301,7 +363,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
       auto store32 = [&](const float(&v)[32], int c) {
         int bz, mb, nb;
         decode(tile, bz, mb, nb);
-        const long long m = (long long)mb * TC_BM + quarter * 32 + lane;
+        const long long m = (long long)(PAIR ? mb * 2 + (int)rank : mb) * TC_BM + quarter * 32 + lane;
         float *crow = reinterpret_cast<float *>(p.C) + (long long)bz * p.strideC + m * p.ldc;
         const long long n0 = (long long)nb * BN;
         if (m >= p.M) return;
@@ -379,7 +441,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
         }
         ptx::tc_fence_before_sync();
         __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(&acc_empty[buf]);
+        if (lane == 0) {
+          if (PAIR) ptx::mbar_arrive_cluster(at_leader(&acc_empty[buf]));
+          else ptx::mbar_arrive(&acc_empty[buf]);
+        }
       } else {
         // 3xTF32: the tensor core adds into its accumulator with truncation, a bias that grows
         // with the length of the accumulation chain. Chains are therefore cut into k-chunks; each
@@ -409,7 +474,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
           }
           ptx::tc_fence_before_sync();
           __syncwarp();
-          if (lane == 0) ptx::mbar_arrive(&acc_empty[buf]);
+          if (lane == 0) {
+            if (PAIR) ptx::mbar_arrive_cluster(at_leader(&acc_empty[buf]));
+            else ptx::mbar_arrive(&acc_empty[buf]);
+          }
         }
         if (kb0 != 0 || kb1 != p.num_k) {
           // part of a tile: leave it in the workspace; the CTA that delivers the last part finishes the tile
@@ -418,15 +486,15 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
           const size_t slot_floats = (size_t)TC_BM * BN;
           const size_t within = ((size_t)(warp - 2) * HALF) * 32 + lane;
           if (ok) {
-            float *wsp = p.ws + (size_t)share_slot(blockIdx.x, tile_u0, p.units, gridDim.x) * slot_floats + within;
+            float *wsp = p.ws + (size_t)share_slot(worker, tile_u0, p.units, p.workers) * slot_floats + within;
 #pragma unroll
             for (int j = 0; j < NACC; ++j) __stcg(wsp + j * 32, acc[j]);
           } else {
             s_fail = 1;
           }
           __threadfence();
-          const int c_first = share_of_unit(tile_u0, p.units, gridDim.x);
-          const int c_last = share_of_unit(tile_u0 + p.num_k - 1, p.units, gridDim.x);
+          const int c_first = share_of_unit(tile_u0, p.units, p.workers);
+          const int c_last = share_of_unit(tile_u0 + p.num_k - 1, p.units, p.workers);
           bool met = epi_sync();
           if (warp == 2 && lane == 0) {
             s_last = (atomicAdd(p.tile_count + tile, 1) == c_last - c_first) ? 1 : 0;
@@ -442,7 +510,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
 #pragma unroll
           for (int j = 0; j < NACC; ++j) acc[j] = 0.f;
           for (int c = c_first; c <= c_last; ++c) {  // k order: CTA c's share precedes CTA c + 1's
-            const float *src = p.ws + (size_t)share_slot(c, tile_u0, p.units, gridDim.x) * slot_floats + within;
+            const float *src = p.ws + (size_t)share_slot(c, tile_u0, p.units, p.workers) * slot_floats + within;
 #pragma unroll
             for (int j = 0; j < NACC; ++j) acc[j] = __fadd_rn(acc[j], ptx::ld_cg_ordered(src + j * 32));
           }
@@ -463,10 +531,14 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
 
   ptx::tc_fence_before_sync();
   __syncthreads();
+  // a pair: neither CTA leaves, or gives its tensor memory back, while the other may still read its
+  // shared memory or arrive on its barriers (every wait above is bounded, so both get here)
+  if (PAIR) ptx::cluster_sync();
   if (threadIdx.x == 0 && s_fail) atomicExch(p.err_flag, 1);
   if (warp == 1) {
     ptx::tc_fence_after_sync();
-    ptx::tmem_dealloc(tmem_base, TMEM_COLS);
+    if (PAIR) ptx::tmem_dealloc_pair(tmem_base, TMEM_COLS);
+    else ptx::tmem_dealloc(tmem_base, TMEM_COLS);
   }
 }
 
@@ -646,14 +718,17 @@ static bool tc_eligible(int dtype, long long M, long long N, long long K, long l
   return true;
 }
 
-template <int TERMS, int BN, bool A_MN, bool B_MN>
+// Bytes of one ring stage in one CTA (the kernel's STAGE_BYTES).
+static size_t tc_stage_bytes(int terms, int bn, bool pair) {
+  const size_t a = (size_t)TC_BM * TC_ROW_BYTES, b = (size_t)bn * TC_ROW_BYTES;
+  return pair ? a + b / 2 : (terms == 1 ? 1 : 2) * (a + b);
+}
+
+// grid = CTAs; pairs launch as clusters of two.
+template <int TERMS, int BN, bool A_MN, bool B_MN, bool PAIR>
 static int launch_tc(b200_engine *e, const CUtensorMap *tm, const GemmTcParams &p, int grid) {
-  constexpr int ES = TERMS == 1 ? 2 : 4;
-  constexpr int NSPLIT = TERMS == 1 ? 1 : 2;
-  constexpr int STAGE_BYTES = NSPLIT * (TC_BM + BN) * TC_ROW_BYTES;
-  (void)ES;
-  auto kern = gemm_tc_kernel<TERMS, BN, A_MN, B_MN>;
-  const size_t smem = (size_t)p.stages * STAGE_BYTES + 1024;
+  auto kern = gemm_tc_kernel<TERMS, BN, A_MN, B_MN, PAIR>;
+  const size_t smem = (size_t)p.stages * tc_stage_bytes(TERMS, BN, PAIR) + 1024;
   static std::atomic<int> attr_dev_mask{0};  // devices on which the attribute is set; engines on other threads share it
   if (!(attr_dev_mask & (1 << (e->device & 31)))) {
     // opt in to the large dynamic carve-out: what the SM offers minus this kernel's static part
@@ -664,19 +739,47 @@ static int launch_tc(b200_engine *e, const CUtensorMap *tm, const GemmTcParams &
                                             (int)(optin - fa.sharedSizeBytes)));
     attr_dev_mask |= 1 << (e->device & 31);
   }
-  kern<<<grid, TC_THREADS, smem, e->stream>>>(tm[0], tm[1], tm[2], tm[3], p);
+  if (PAIR) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(TC_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = e->stream;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    // Only clusters that are resident together may share the tiles out evenly: a GPU whose SMs do
+    // not all pair up would otherwise run the left-over clusters as a second round.
+    static std::atomic<int> max_clusters[32];
+    int mc = max_clusters[e->device & 31];
+    if (mc == 0) {
+      B200_CHECK_CUDA(e, cudaOccupancyMaxActiveClusters(&mc, kern, &cfg));
+      if (mc < 1) return set_error(e, B200_ERR_CUDA, "gemm_tc_kernel: no pair of CTAs fits this device");
+      max_clusters[e->device & 31] = mc;
+    }
+    GemmTcParams pp = p;
+    pp.workers = std::min(p.workers, mc);
+    cfg.gridDim = dim3((unsigned)(2 * pp.workers));
+    B200_CHECK_CUDA(e, cudaLaunchKernelEx(&cfg, kern, tm[0], tm[1], tm[2], tm[3], pp));
+  } else {
+    kern<<<grid, TC_THREADS, smem, e->stream>>>(tm[0], tm[1], tm[2], tm[3], p);
+  }
   B200_CHECK_LAUNCH(e, "gemm_tc_kernel");
   e->flags_dirty = true;
   return B200_OK;
 }
 
-template <int TERMS, int BN>
+template <int TERMS, int BN, bool PAIR = false>
 static int launch_tc_layout(b200_engine *e, bool a_mn, bool b_mn, const CUtensorMap *tm, const GemmTcParams &p,
                             int grid) {
-  if (!a_mn && !b_mn) return launch_tc<TERMS, BN, false, false>(e, tm, p, grid);
-  if (!a_mn && b_mn) return launch_tc<TERMS, BN, false, true>(e, tm, p, grid);
-  if (a_mn && !b_mn) return launch_tc<TERMS, BN, true, false>(e, tm, p, grid);
-  return launch_tc<TERMS, BN, true, true>(e, tm, p, grid);
+  if (!a_mn && !b_mn) return launch_tc<TERMS, BN, false, false, PAIR>(e, tm, p, grid);
+  if (!a_mn && b_mn) return launch_tc<TERMS, BN, false, true, PAIR>(e, tm, p, grid);
+  if (a_mn && !b_mn) return launch_tc<TERMS, BN, true, false, PAIR>(e, tm, p, grid);
+  return launch_tc<TERMS, BN, true, true, PAIR>(e, tm, p, grid);
 }
 
 
@@ -697,6 +800,12 @@ int gemm_tc_core(b200_engine *e, int terms, bool a_mn, bool b_mn, long long M, l
   while (bn > 64 && (long long)tiles_m * ((N + bn - 1) / bn) * batch < e->sm_count) bn /= 2;
   while (bn > 64 && bn / 2 >= N) bn /= 2;
   const int tiles_n = (int)((N + bn - 1) / bn);
+  // CTA pairs on 256-row tiles (bf16), when the widest tiles are in use and there are enough of
+  // them to keep every pair busy for several rounds (a pair's tile is twice the size: the last
+  // round's idle time doubles with it)
+  const int pairs = e->sm_count / 2;
+  const long long pair_tiles = (M + 2 * TC_BM - 1) / (2 * TC_BM) * tiles_n * batch;
+  const bool pair = !(e->flags & B200_ENGINE_NO_PAIRS) && terms == 1 && bn == 256 && pair_tiles >= 4LL * pairs;
 
   CUtensorMap tm[4];
   memset(tm, 0, sizeof tm);
@@ -710,8 +819,9 @@ int gemm_tc_core(b200_engine *e, int terms, bool a_mn, bool b_mn, long long M, l
     else
       rc = encode_map(e, &tm[h], es, ap, M, K, a_batch, a.ld, a.batch_stride, mn_box, bk, es == 4);
     if (rc != B200_OK) return rc;
-    if (!b_mn)
-      rc = encode_map(e, &tm[2 + h], es, bp, K, N, b_batch, b.ld, b.batch_stride, bk, bn, false);
+    if (!b_mn)  // a pair's bf16 CTAs load half of the tile's B rows each
+      rc = encode_map(e, &tm[2 + h], es, bp, K, N, b_batch, b.ld, b.batch_stride, bk,
+                      pair ? bn / 2 : bn, false);
     else
       rc = encode_map(e, &tm[2 + h], es, bp, N, K, b_batch, b.ld, b.batch_stride, mn_box, bk, es == 4);
     if (rc != B200_OK) return rc;
@@ -744,8 +854,7 @@ int gemm_tc_core(b200_engine *e, int terms, bool a_mn, bool b_mn, long long M, l
   p.b_zmul = b.shared ? 0 : 1;
   p.ep = ep;
   p.err_flag = e->d_flags + 2;
-  const int nsplit = terms == 1 ? 1 : 2;
-  const size_t stage_bytes = (size_t)nsplit * (TC_BM + bn) * TC_ROW_BYTES;
+  const size_t stage_bytes = tc_stage_bytes(terms, bn, pair);
   const size_t budget = std::min<size_t>(e->smem_optin, 227 * 1024) - 4096;  // static part + alignment slack
   p.stages = (int)std::max<size_t>(2, std::min<size_t>(8, budget / stage_bytes));
   const long long total_tiles = (long long)tiles_m * tiles_n * batch;
@@ -756,6 +865,13 @@ int gemm_tc_core(b200_engine *e, int terms, bool a_mn, bool b_mn, long long M, l
   p.units = 0;
   p.ws = nullptr;
   p.tile_count = nullptr;
+  p.workers = grid;
+  if (pair) {
+    p.tiles_m = (int)((M + 2 * TC_BM - 1) / (2 * TC_BM));
+    p.group_m = std::min(p.tiles_m, 4);  // the same 8 x 128 rows of A per raster group
+    p.workers = (int)std::min<long long>(pair_tiles, pairs);
+    return launch_tc_layout<1, 256, true>(e, a_mn, b_mn, tm, p, 2 * p.workers);
+  }
 
   if (terms == 1) {
     if (bn == 256) return launch_tc_layout<1, 256>(e, a_mn, b_mn, tm, p, grid);
@@ -771,6 +887,7 @@ int gemm_tc_core(b200_engine *e, int terms, bool a_mn, bool b_mn, long long M, l
       p.streamk = 1;
       p.units = (int)(total_tiles * p.num_k);  // small: k sharing is for launches of few tiles
       grid = sk_grid;
+      p.workers = grid;
       p.tile_count = e->sk_counters;
       p.ws = (float *)ws;
     }  // else: no room for the partial tiles, whole tiles per CTA

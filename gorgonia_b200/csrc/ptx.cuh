@@ -220,5 +220,185 @@ __device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16])
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+// ---- CTA pairs: a cluster of two CTAs on neighbouring SMs driving one tcgen05.mma (cta_group::2) --
+// The even CTA of the pair (cluster rank 0) issues the instructions; they read A from each CTA's
+// own shared memory (128 rows each, M = 256), the first half of B's rows from rank 0 and the second
+// half from rank 1, and leave each CTA's 128 rows of D in that CTA's tensor memory. Nothing below is
+// a multicast: every load writes the issuing CTA's own shared memory, and a commit names one barrier.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// The shared::cluster address of the same shared-memory location in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t saddr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+  return r;
+}
+// Cluster-wide rendezvous of all threads (hardware barrier; a CTA that has exited counts as arrived).
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Arrives on an mbarrier given by its shared::cluster address (this CTA's or the other's).
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_caddr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_caddr) : "memory");
+}
+// Tile-mode load into this CTA's shared memory whose byte count is credited to the mbarrier at
+// `bar_caddr`, which may live in the other CTA of the pair.
+__device__ __forceinline__ void tma_load_3d_pair(void *smem_dst, const void *tmap, int x, int y, int z,
+                                                 uint32_t bar_caddr) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, "
+      "%5}], [%2];" ::"r"(smem_addr(smem_dst)),
+      "l"(tmap), "r"(bar_caddr), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_im2col_4d_pair(void *smem_dst, const void *tmap, int c, int w, int h, int n,
+                                                        uint16_t off_w, uint16_t off_h, uint32_t bar_caddr) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.im2col.mbarrier::complete_tx::bytes [%0], [%1, "
+      "{%3, %4, %5, %6}], [%2], {%7, %8};" ::"r"(smem_addr(smem_dst)),
+      "l"(tmap), "r"(bar_caddr), "r"(c), "r"(w), "r"(h), "r"(n), "h"(off_w), "h"(off_h)
+      : "memory");
+}
+// Tensor-memory allocation for the pair: one warp of EACH CTA executes it (same warp index, same
+// shared-memory offset for the result), and likewise the release.
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t *smem_result, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(smem_result)),
+               "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void mma_f16_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
+      "}" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void mma_tf32_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                              uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t"
+      "}" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrives on the mbarrier at `bar_caddr` (either CTA's) once the pair's MMAs issued so far are done.
+__device__ __forceinline__ void mma_commit_pair(uint32_t bar_caddr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_caddr)
+               : "memory");
+}
+
+
+// ---- one k-block of MMAs as one run of instructions ----------------------------------------------
+// The thread that issues the MMAs is a serial bottleneck: an mbarrier poll comes back after about
+// 100 cycles, a tcgen05.mma takes about 60 to issue and a commit about 90, against 512 (bf16) or 768
+// (3xTF32) cycles of tensor work per k-block. These helpers keep that thread's path short: the four
+// k-slices of a stage are issued from descriptors that only step an immediate, the commit that frees
+// the stage follows at once, and the poll of the NEXT stage's "full" barrier (non-blocking
+// test_wait) is started first and its answer read last, so that its latency passes behind the
+// issue. Returns 1 if the next stage was seen complete.
+//   CG: "1" or "2" (cta_group); SA / SB: descriptor step between k-slices (bytes >> 4).
+// The second commit of a pair names the other CTA's barrier; empty_peer is ignored when CG is 1.
+
+template <bool PAIR, int SA, int SB>
+__device__ __forceinline__ uint32_t kblock_f16(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc_first,
+                                               uint32_t empty_bar, uint32_t empty_peer, uint32_t next_full,
+                                               uint32_t next_parity) {
+  uint32_t ready;
+#define B200_KB_F16(CG, SECOND_COMMIT)                                                                   \
+  asm volatile(                                                                                        \
+      "{\n\t"                                                                                          \
+      ".reg .pred pn, pa, p1;\n\t"                                                                     \
+      ".reg .b64 a1, b1;\n\t"                                                                          \
+      "setp.ne.b32 pa, %4, 0;\n\t"                                                                     \
+      "setp.eq.b32 p1, %4, %4;\n\t"                                                                    \
+      "mbarrier.test_wait.parity.shared::cta.b64 pn, [%7], %8;\n\t"                                    \
+      "tcgen05.mma.cta_group::" CG ".kind::f16 [%1], %2, %3, %5, pa;\n\t"                              \
+      "add.s64 a1, %2, %9;\n\t"                                                                        \
+      "add.s64 b1, %3, %10;\n\t"                                                                       \
+      "tcgen05.mma.cta_group::" CG ".kind::f16 [%1], a1, b1, %5, p1;\n\t"                              \
+      "add.s64 a1, a1, %9;\n\t"                                                                        \
+      "add.s64 b1, b1, %10;\n\t"                                                                       \
+      "tcgen05.mma.cta_group::" CG ".kind::f16 [%1], a1, b1, %5, p1;\n\t"                              \
+      "add.s64 a1, a1, %9;\n\t"                                                                        \
+      "add.s64 b1, b1, %10;\n\t"                                                                       \
+      "tcgen05.mma.cta_group::" CG ".kind::f16 [%1], a1, b1, %5, p1;\n\t"                              \
+      "tcgen05.commit.cta_group::" CG ".mbarrier::arrive::one.shared::cluster.b64 [%6];\n\t" SECOND_COMMIT \
+      "selp.u32 %0, 1, 0, pn;\n\t"                                                                     \
+      "}"                                                                                              \
+      : "=r"(ready)                                                                                    \
+      : "r"(d), "l"(a), "l"(b), "r"(acc_first), "r"(idesc), "r"(empty_bar), "r"(next_full), "r"(next_parity),  \
+        "n"(SA), "n"(SB), "r"(empty_peer)                                                              \
+      : "memory")
+  if (PAIR)
+    B200_KB_F16("2", "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%11];\n\t");
+  else
+    B200_KB_F16("1", "");
+#undef B200_KB_F16
+  return ready;
+}
+
+// 3xTF32: per k-slice a_head x b_wide (width 2 BN, into d_main) and a_tail x b_narrow (width BN,
+// into d_tail, always accumulating).
+template <bool PAIR, int SA, int SB>
+__device__ __forceinline__ uint32_t kblock_tf32x3(uint32_t d_main, uint32_t d_tail, uint64_t a_head, uint64_t a_tail,
+                                                  uint64_t b_wide, uint64_t b_narrow, uint32_t idesc_wide,
+                                                  uint32_t idesc, uint32_t acc_first, uint32_t empty_bar,
+                                                  uint32_t empty_peer, uint32_t next_full, uint32_t next_parity) {
+  uint32_t ready;
+#define B200_KB_STEP(CG)                                                       \
+  "add.s64 ah, ah, %14;\n\t"                                                   \
+  "add.s64 al, al, %14;\n\t"                                                   \
+  "add.s64 bw, bw, %15;\n\t"                                                   \
+  "add.s64 bn, bn, %15;\n\t"                                                   \
+  "tcgen05.mma.cta_group::" CG ".kind::tf32 [%1], ah, bw, %7, p1;\n\t"         \
+  "tcgen05.mma.cta_group::" CG ".kind::tf32 [%2], al, bn, %8, p1;\n\t"
+#define B200_KB_TF32(CG, SECOND_COMMIT)                                                                  \
+  asm volatile(                                                                                        \
+      "{\n\t"                                                                                          \
+      ".reg .pred pn, pa, p1;\n\t"                                                                     \
+      ".reg .b64 ah, al, bw, bn;\n\t"                                                                  \
+      "setp.ne.b32 pa, %9, 0;\n\t"                                                                     \
+      "setp.eq.b32 p1, %9, %9;\n\t"                                                                    \
+      "mbarrier.test_wait.parity.shared::cta.b64 pn, [%12], %13;\n\t"                                  \
+      "tcgen05.mma.cta_group::" CG ".kind::tf32 [%1], %3, %5, %7, pa;\n\t"                             \
+      "tcgen05.mma.cta_group::" CG ".kind::tf32 [%2], %4, %6, %8, p1;\n\t"                             \
+      "mov.b64 ah, %3;\n\t"                                                                            \
+      "mov.b64 al, %4;\n\t"                                                                            \
+      "mov.b64 bw, %5;\n\t"                                                                            \
+      "mov.b64 bn, %6;\n\t" B200_KB_STEP(CG) B200_KB_STEP(CG) B200_KB_STEP(CG)                         \
+      "tcgen05.commit.cta_group::" CG ".mbarrier::arrive::one.shared::cluster.b64 [%10];\n\t" SECOND_COMMIT \
+      "selp.u32 %0, 1, 0, pn;\n\t"                                                                     \
+      "}"                                                                                              \
+      : "=r"(ready)                                                                                    \
+      : "r"(d_main), "r"(d_tail), "l"(a_head), "l"(a_tail), "l"(b_wide), "l"(b_narrow), "r"(idesc_wide),      \
+        "r"(idesc), "r"(acc_first), "r"(empty_bar), "r"(empty_peer), "r"(next_full), "r"(next_parity),       \
+        "n"(SA), "n"(SB)                                                                               \
+      : "memory")
+  if (PAIR)
+    B200_KB_TF32("2", "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%11];\n\t");
+  else
+    B200_KB_TF32("1", "");
+#undef B200_KB_TF32
+#undef B200_KB_STEP
+  return ready;
+}
+
 }  // namespace ptx
 }  // namespace b200

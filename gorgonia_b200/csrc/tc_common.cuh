@@ -65,14 +65,19 @@ __host__ __device__ constexpr uint32_t make_idesc(int fmt, int a_mn, int b_mn, i
 struct TilePieces {
   // 32-bit throughout: the host refuses launches of 2^31 tiles or units
   int tile, total_tiles, u, u1, num_k, stream;
-  __device__ TilePieces(int streamk, int units, int num_k_, int tiles) {
+  int workers;
+  // worker w of `workers` (CTAs, or CTA pairs that take a tile together)
+  __device__ TilePieces(int streamk, int units, int num_k_, int tiles, int w, int workers_) {
     stream = streamk;
     num_k = num_k_;
     total_tiles = tiles;
-    tile = blockIdx.x;
-    u = (int)((long long)blockIdx.x * units / gridDim.x);
-    u1 = (int)((long long)(blockIdx.x + 1) * units / gridDim.x);
+    workers = workers_;
+    tile = w;
+    u = (int)((long long)w * units / workers);
+    u1 = (int)((long long)(w + 1) * units / workers);
   }
+  __device__ TilePieces(int streamk, int units, int num_k_, int tiles)
+      : TilePieces(streamk, units, num_k_, tiles, (int)blockIdx.x, (int)gridDim.x) {}
   // the next piece: k-blocks [kb0, kb1) of tile t
   __device__ bool next(int &t, int &kb0, int &kb1) {
     if (!stream) {
@@ -80,7 +85,7 @@ struct TilePieces {
       t = tile;
       kb0 = 0;
       kb1 = num_k;
-      tile += gridDim.x;
+      tile += workers;
       return true;
     }
     if (u >= u1) return false;

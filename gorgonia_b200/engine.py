@@ -98,9 +98,11 @@ class Tensor:
 
 
 class Engine:
-    def __init__(self, device=0, arena_bytes=1 << 30, managed=False, defer=True, conv_gather=False, streamk=True):
+    def __init__(self, device=0, arena_bytes=1 << 30, managed=False, defer=True, conv_gather=False, streamk=True,
+                 pairs=True):
         flags = ((_lib.ENGINE_MANAGED if managed else 0) | (0 if defer else _lib.ENGINE_NO_DEFER) |
-                 (_lib.ENGINE_CONV_GATHER if conv_gather else 0) | (0 if streamk else _lib.ENGINE_NO_STREAMK))
+                 (_lib.ENGINE_CONV_GATHER if conv_gather else 0) | (0 if streamk else _lib.ENGINE_NO_STREAMK) |
+                 (0 if pairs else _lib.ENGINE_NO_PAIRS))
         h = C.c_void_p()
         rc = lib.b200_engine_create(device, arena_bytes, flags, C.byref(h))
         if rc != _lib.OK:

@@ -70,9 +70,12 @@ enum {
   B200_ENGINE_NO_DEFER = 2u, /* launch each pointwise call at once instead of queueing it   */
   B200_ENGINE_CONV_GATHER = 4u, /* tensor-core convolutions build their col operand with gather *
                                  * warps even where the TMA unit could (tests, comparisons)    */
-  B200_ENGINE_NO_STREAMK = 8u   /* tensor-core kernels never share a tile's k range between    *
+  B200_ENGINE_NO_STREAMK = 8u,  /* tensor-core kernels never share a tile's k range between    *
                                  * CTAs: every output element is then summed in one fixed      *
                                  * order whatever the batch size (tests, comparisons)          */
+  B200_ENGINE_NO_PAIRS = 16u    /* tensor-core kernels never run as pairs of CTAs on one       *
+                                 * 256-row tile (tests, comparisons); results are the same     *
+                                 * bits either way                                             */
 };
 int b200_engine_create(int device, size_t arena_bytes, unsigned flags, b200_engine **out);
 int b200_engine_destroy(b200_engine *e);

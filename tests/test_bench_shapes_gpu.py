@@ -113,6 +113,27 @@ def test_matmul_bf16_wide_tiles(roomy, shape, tile):
     _sampled_product_check(got, a, b, 1e-4, tile=128)
 
 
+@pytest.mark.parametrize("transA,transB", [(False, False), (False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("shape", [(4096, 4864, 256), (3992, 4872, 192)])
+def test_matmul_bf16_cta_pairs(shape, transA, transB):
+    # 16 x 19 tiles of 256 x 256 (the second shape ragged in rows and columns) are enough for the launch
+    # to run as pairs of CTAs on 256-row tiles (cluster of two, tcgen05 cta_group::2): against the oracle,
+    # and bit for bit against an engine that never pairs CTAs up, in all four operand layouts
+    from gorgonia_b200 import Engine
+    M, N, K = shape
+    a = from_bf16(to_bf16(util.normal(325, (K, M) if transA else (M, K), scale=0.02)))
+    b = from_bf16(to_bf16(util.normal(326, (N, K) if transB else (K, N), scale=0.02)))
+    got = {}
+    for pairs in (True, False):
+        e = Engine(device=0, arena_bytes=1 << 30, pairs=pairs)
+        ta, tb, tc = e.tensor_bf16(a), e.tensor_bf16(b), e.empty((M, N))
+        e.MatMul(ta, tb, tc, transA, transB)
+        got[pairs] = tc.numpy()
+        e.Close()
+    assert_bits_equal(got[True], got[False])
+    assert_gemm_close(got[True], oracle.gemm(a, b, transA, transB), 1e-4)
+
+
 @pytest.mark.parametrize("bf16", [False, True])
 def test_batch_of_64_products_512(roomy, bf16):
     e = roomy
