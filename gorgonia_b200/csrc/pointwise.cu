@@ -94,11 +94,6 @@ __device__ __forceinline__ double add_rn(double a, double b) { return __dadd_rn(
 __device__ __forceinline__ float sub_rn(float a, float b) { return __fsub_rn(a, b); }
 __device__ __forceinline__ double sub_rn(double a, double b) { return __dsub_rn(a, b); }
 
-__device__ __forceinline__ float rcp_approx(float d) {  // 1 ulp, subnormal results kept
-  float r;
-  asm("rcp.approx.f32 %0, %1;" : "=f"(r) : "f"(d));
-  return r;
-}
 // Without the subnormal handling, for arguments and results known to be normal:
 __device__ __forceinline__ float rcp_approx_ftz(float d) {
   float r;
@@ -111,10 +106,16 @@ __device__ __forceinline__ float ex2_approx_ftz(float d) {  // relative error be
   return r;
 }
 
+// 1 / (1 + e^-x) from t = e^-|x| <= 1: 1 / (1 + t) for x >= 0 and t / (1 + t) below, so that the
+// reciprocal's argument lies in [1, 2] (the fast reciprocal, 1 ulp) and a result below the normal
+// range comes out of the last multiplication as the subnormal it is. expf is within 2 ulp: 4 ulp in all.
 __device__ __forceinline__ float sigmoid_(float x) {
-  if (x < -88.f) return 0.f;
-  if (x > 15.f) return 1.f;
-  return rcp_approx(1.f + expf(-x));  // expf within 2 ulp, the reciprocal within 1
+  const float t = expf(-fabsf(x));
+  const float r = rcp_approx_ftz(__fadd_rn(1.f, t));
+  float s = x >= 0.f ? r : __fmul_rn(t, r);  // a NaN takes the second arm and stays a NaN
+  if (x < -88.f) s = 0.f;
+  if (x > 15.f) s = 1.f;
+  return s;
 }
 __device__ __forceinline__ double sigmoid_(double x) {
   if (x < -709.0) return 0.0;
@@ -717,6 +718,35 @@ static int lower_ref(b200_engine *e, const b200_pw_prog *prog, uint8_t ref, int 
   return B200_OK;
 }
 
+// one instruction over ring slots and immediates: every plain engine call (Add, Mul, Exp, ...)
+static bool pw_is_single(const PwDev &d) {
+  return d.n_instr == 1 && d.n_file == 0 && d.n_out == 1 && d.out_of[0] == 0 &&
+         (d.ka[0] == K_RING || d.ka[0] == K_IMM) && (d.op[0] >= B200_OP_ABS || d.kb[0] == K_RING || d.kb[0] == K_IMM);
+}
+
+// One full-size source and one instruction (a unary op, a tensor-scalar op): tiles of four chunks per
+// thread. With a single 16-byte stream per thread the per-tile work (barrier, ring bookkeeping, op
+// dispatch) weighs twice as much per element as it does for two sources, and the ring has room.
+template <typename T, int V>
+static int launch_stream_wide(b200_engine *e, const PwDev &d, size_t budget, int stages) {
+  constexpr int U = 4;
+  constexpr int TILE_CHUNKS = PW_STREAM_THREADS * U;
+  const long long nchunks = (d.n + V - 1) / V;
+  const long long ntiles = (nchunks + TILE_CHUNKS - 1) / TILE_CHUNKS;
+  const size_t smem = (size_t)stages * TILE_CHUNKS * 16;
+  const int blocks = (int)std::min<long long>(ntiles, 2LL * e->sm_count);
+  static std::atomic<int> attr_dev_mask{0};
+  auto kern = pw_stream_kernel<T, V, U, true>;
+  if (!(attr_dev_mask & (1 << (e->device & 31)))) {
+    B200_CHECK_CUDA(e, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)budget));
+    attr_dev_mask |= 1 << (e->device & 31);
+  }
+  kern<<<blocks, PW_STREAM_THREADS, smem, e->stream>>>(d, stages, e->d_flags + 2);
+  B200_CHECK_LAUNCH(e, "pw_stream_kernel");
+  e->flags_dirty = true;
+  return B200_OK;
+}
+
 template <typename T, int V, int U>
 static int launch_stream_u(b200_engine *e, const PwDev &d, size_t budget, int stages) {
   constexpr int TILE_CHUNKS = PW_STREAM_THREADS * U;
@@ -724,10 +754,7 @@ static int launch_stream_u(b200_engine *e, const PwDev &d, size_t budget, int st
   const long long nchunks = (d.n + V - 1) / V;
   const long long ntiles = (nchunks + TILE_CHUNKS - 1) / TILE_CHUNKS;
   const size_t smem = ((size_t)stages * d.n_full + d.n_file) * SLOT_BYTES;
-  // one instruction over ring slots and immediates: every plain engine call (Add, Mul, Exp, ...)
-  const bool single = d.n_instr == 1 && d.n_file == 0 && d.n_out == 1 && d.out_of[0] == 0 &&
-                      (d.ka[0] == K_RING || d.ka[0] == K_IMM) &&
-                      (d.op[0] >= B200_OP_ABS || d.kb[0] == K_RING || d.kb[0] == K_IMM);
+  const bool single = pw_is_single(d);
   const int blocks = (int)std::min<long long>(ntiles, 2LL * e->sm_count);  // two resident CTAs per SM
   static std::atomic<int> attr_dev_mask[2];  // per instantiation: devices on which the attribute is set
   if (single) {
@@ -755,6 +782,13 @@ template <typename T, int V>
 static int launch_stream(b200_engine *e, const PwDev &d) {
   // two CTAs share an SM: each gets just under half of its shared memory
   const size_t budget = std::min<size_t>(e->smem_optin > 4096 ? e->smem_optin - 4096 : 0, 220 * 1024) / 2;
+  if (d.n_full == 1 && pw_is_single(d)) {
+    const size_t slot = (size_t)PW_STREAM_THREADS * 4 * 16;
+    const long long nchunks = (d.n + V - 1) / V;
+    // wide tiles only where every CTA still gets several of them
+    if (budget / slot >= 3 && nchunks >= 8LL * 2 * e->sm_count * PW_STREAM_THREADS * 4)
+      return launch_stream_wide<T, V>(e, d, budget, (int)std::min<size_t>(budget / slot, PW_MAX_STAGES));
+  }
   for (int u = 2; u >= 1; --u) {
     const size_t slot = (size_t)PW_STREAM_THREADS * u * 16;
     if (budget < d.n_file * slot) continue;

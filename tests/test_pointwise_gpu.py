@@ -150,6 +150,20 @@ def test_tanh_float32_arms_and_ends(fresh):
     assert (np.abs(got[~np.isnan(x)]) <= 1).all()
 
 
+def test_sigmoid_float32_both_arms_and_ends(fresh):
+    # 1 / (1 + t) above zero, t / (1 + t) below, the thresholds of the reference, results below the
+    # normal range, special values
+    e = fresh
+    g = util.rng(79)
+    x = np.concatenate([g.uniform(-20, 20, 1 << 16), g.uniform(-88, -80, 1 << 12), g.uniform(14, 16, 1 << 10),
+                        g.standard_normal(1 << 16) * 1e-3,
+                        np.array([0.0, -0.0, np.inf, -np.inf, np.nan, -88.0, -87.99, -87.5, -87.3, 15.0, 15.01, 3e-45])])
+    x = x.astype(np.float32)
+    tx = e.tensor(x)
+    e.Unary("sigmoid", tx, unsafe=True)
+    assert_pointwise_close(tx.numpy(), oracle.unary("sigmoid", x))
+
+
 def test_safe_mode_is_an_error(fresh):
     # cuda/arith.go:47-48: neither reuse nor unsafe -> error
     from gorgonia_b200 import B200Error
