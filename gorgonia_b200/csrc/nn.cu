@@ -11,6 +11,7 @@
 #include <atomic>
 
 #include "engine.h"
+#include "ptx.cuh"
 
 namespace b200 {
 
@@ -521,7 +522,11 @@ __global__ void __launch_bounds__(256) col2im_rows_kernel(const T *__restrict__ 
 // The float32 ring kernel with the memory side pipelined: C*kh*kw a multiple of 4, so a col row is
 // a whole number of float4 that never straddle two output columns. A thread holds up to 8 float4
 // of the NEXT col row in registers; their loads are issued before the current image row is
-// computed and land while it runs, instead of one dependent load per loop trip.
+// computed and land while it runs, instead of one dependent load per loop trip. Where a thread's
+// float4 land in a ring row, and which (channel, column) outputs it computes, is the same for every
+// row of every image: both are worked out once, so no element pays an index division. The ring
+// holds kh + 1 rows: the row being stashed is then never one the row being computed reads, and one
+// barrier per image row is enough.
 template <bool UNIT_W>
 __global__ void __launch_bounds__(256) col2im_rows4_kernel(const float *__restrict__ col, float *__restrict__ im,
                                                            long long B, int C, int H, int W, int Ho, int Wo, int kh,
@@ -531,28 +536,63 @@ __global__ void __launch_bounds__(256) col2im_rows4_kernel(const float *__restri
   const int crs = C * kh * kw, khw = kh * kw;
   const int pitch = crs + 1;
   const int row_vec = (Wo * crs) >> 2;  // float4 per col row, at most 8 * 256
+  const int slots = kh + 1, slot_floats = Wo * pitch;
   float4 pre[8];
+  int stash_at[8];  // offset of float4 v of a col row inside a ring row, or -1
+#pragma unroll
+  for (int v = 0; v < 8; ++v) {
+    const int i = threadIdx.x + v * 256;
+    const int e0 = i << 2, ow = e0 / crs;
+    stash_at[v] = i < row_vec ? ow * pitch + (e0 - ow * crs) : -1;
+  }
+  constexpr int NOUT = 4;  // outputs per thread and image row kept in registers; more take the slow loop
+  int out_c[NOUT], out_w[NOUT];
+#pragma unroll
+  for (int k = 0; k < NOUT; ++k) {
+    const int i = threadIdx.x + k * 256;
+    out_c[k] = i < C * W ? i / W : -1;
+    out_w[k] = i - (i / W) * W;
+  }
   auto fetch = [&](long long b, int oh) {
     const float4 *src = reinterpret_cast<const float4 *>(col + (b * Ho + oh) * (long long)Wo * crs);
 #pragma unroll
-    for (int v = 0; v < 8; ++v) {
-      const int i = threadIdx.x + v * 256;
-      if (i < row_vec) pre[v] = __ldg(src + i);
-    }
+    for (int v = 0; v < 8; ++v)
+      if (stash_at[v] >= 0) pre[v] = __ldg(src + threadIdx.x + v * 256);
   };
   auto stash = [&](int oh) {
-    float *dst = ring + (long long)(oh % kh) * Wo * pitch;
+    float *dst = ring + (oh % slots) * slot_floats;
 #pragma unroll
-    for (int v = 0; v < 8; ++v) {
-      const int i = threadIdx.x + v * 256;
-      if (i < row_vec) {
-        const int e0 = i << 2, ow = e0 / crs, q = e0 - ow * crs;
-        float *d = dst + ow * pitch + q;
+    for (int v = 0; v < 8; ++v)
+      if (stash_at[v] >= 0) {
+        float *d = dst + stash_at[v];
         d[0] = pre[v].x; d[1] = pre[v].y; d[2] = pre[v].z; d[3] = pre[v].w;
       }
+  };
+  // the sum of one output, taps in the reference's order (bottom-right tap first)
+  auto gather = [&](int ih, int c, int iw) {
+    float acc = 0.f;
+    for (int r = kh - 1; r >= 0; --r) {
+      const int oh = ih + padH - r;
+      if (oh < 0 || oh >= Ho) continue;
+      const float *slot = ring + (oh % slots) * slot_floats + c * khw + r * kw;
+      for (int sx = kw - 1; sx >= 0; --sx) {
+        int ow;
+        if (UNIT_W) {
+          ow = iw + padW - sx;
+          if (ow < 0) continue;
+        } else {
+          const int num_w = iw + padW - sx * dW;
+          if (num_w < 0 || num_w % sW != 0) continue;
+          ow = num_w / sW;
+        }
+        if (ow >= Wo) continue;
+        acc = acc + slot[ow * pitch + sx];
+      }
     }
+    return acc;
   };
   for (long long b = blockIdx.x; b < B; b += gridDim.x) {
+    __syncthreads();  // the previous image's last rows have been read
     for (int oh = 0; oh < padH && oh < Ho; ++oh) {  // rows above the first new one
       fetch(b, oh);
       stash(oh);
@@ -563,31 +603,164 @@ __global__ void __launch_bounds__(256) col2im_rows4_kernel(const float *__restri
       __syncthreads();
       if (ih + 1 + padH < Ho) fetch(b, ih + 1 + padH);  // lands while this image row is computed
       float *out = im + (b * C * H + ih) * (long long)W;
-      for (int i = threadIdx.x; i < C * W; i += blockDim.x) {
+#pragma unroll
+      for (int k = 0; k < NOUT; ++k)
+        if (out_c[k] >= 0) out[(long long)out_c[k] * H * W + out_w[k]] = gather(ih, out_c[k], out_w[k]);
+      for (int i = threadIdx.x + NOUT * 256; i < C * W; i += blockDim.x) {
         const int c = i / W, iw = i - c * W;
+        out[(long long)c * H * W + iw] = gather(ih, c, iw);
+      }
+    }
+  }
+}
+
+// The 3 x 3-class case (stride 1, no dilation, float32, C*kh*kw a multiple of 4) with the memory side
+// taken off the threads altogether. A col row (one output row of positions: Wo * crs floats) is one
+// bulk asynchronous copy into a ring of R shared-memory rows, queued by one thread up to R - kh rows
+// ahead across image boundaries, its landing signalled by an mbarrier; nobody holds col data in
+// registers. The rows lie unpadded, so consecutive channels of one position are kh*kw words apart:
+// a warp takes 32 consecutive channels of one column (bank-conflict free for odd kh*kw), sums the
+// taps in the reference's order (bottom-right first, acc = acc + v from 0), and puts the value into a
+// shared-memory copy of the image, which leaves for HBM as one linear pass per image. One barrier
+// per image row; every mbarrier wait is bounded.
+constexpr int C2I_MAX_RING = 8;
+constexpr int C2I_THREADS = 512;
+
+template <int KH, int KW>
+__global__ void __launch_bounds__(C2I_THREADS, 2) col2im_bulk_kernel(const float *__restrict__ col, float *__restrict__ im,
+                                                          long long B, int C, int H, int W, int Ho, int Wo, int padH,
+                                                          int padW, int R, int *err_flag) {
+  extern __shared__ __align__(128) unsigned char c2ib_smem[];
+  __shared__ __align__(8) uint64_t full[C2I_MAX_RING];
+  __shared__ int s_fail;
+  constexpr int KHW = KH * KW;
+  const int crs = C * KHW;
+  const int row_floats = Wo * crs;
+  const uint32_t row_bytes = (uint32_t)row_floats * 4u;
+  float *ring = reinterpret_cast<float *>(c2ib_smem);
+  float *outimg = ring + (size_t)R * row_floats;
+  const int plane = H * W, img_floats = C * plane;
+
+  const long long my_images = blockIdx.x < B ? (B - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+  if (threadIdx.x == 0) {
+    for (int s2 = 0; s2 < R; ++s2) ptx::mbar_init(&full[s2], 1);
+    ptx::fence_mbar_init();
+    s_fail = 0;
+  }
+  __syncthreads();
+  // Every index below advances by one step at a time: nothing in the loops divides.
+  long long issued = 0;                      // thread 0 only: rows queued so far,
+  long long iss_k = 0;                       // the image (of this block) and row the next one is,
+  int iss_oh = 0, iss_slot = 0;              // and the ring slot it goes to
+  auto issue_upto = [&](long long freed) {
+    while (iss_k < my_images && issued - freed < R) {
+      const long long b = blockIdx.x + iss_k * gridDim.x;
+      ptx::mbar_arrive_expect_tx(&full[iss_slot], row_bytes);
+      ptx::bulk_g2s(ring + (size_t)iss_slot * row_floats, col + (b * Ho + iss_oh) * (long long)row_floats, row_bytes,
+                    &full[iss_slot]);
+      ++issued;
+      if (++iss_oh == Ho) {
+        iss_oh = 0;
+        ++iss_k;
+      }
+      if (++iss_slot == R) iss_slot = 0;
+    }
+  };
+  if (threadIdx.x == 0) issue_upto(0);
+
+  // the (channel, column) outputs of this thread in an image row: channel fastest
+  constexpr int NOUT = 2;
+  int out_c[NOUT], out_w[NOUT];
+#pragma unroll
+  for (int k = 0; k < NOUT; ++k) {
+    const int i = threadIdx.x + k * C2I_THREADS;
+    out_w[k] = i / C;
+    out_c[k] = i < C * W ? i - out_w[k] * C : -1;
+  }
+  long long waited = 0;  // rows whose barrier this thread has seen complete,
+  int w_slot = 0;        // the slot of the next one
+  uint32_t w_phase = 0;  // and the parity its barrier completes with
+  int img_slot0 = 0;     // ring slot of the current image's row 0
+  long long row0 = 0;    // that row's place in the block's sequence
+  bool ok = true;
+  for (long long k = 0; k < my_images && ok; ++k) {
+    const long long b = blockIdx.x + k * gridDim.x;
+    int cur = (img_slot0 + padH) % R;  // slot of row ih + padH (a row past the last one exists only as an index)
+    for (int ih = 0; ih < H; ++ih) {
+      const int newest = ih + padH < Ho - 1 ? ih + padH : Ho - 1;
+      bool landed = true;
+      while (waited <= row0 + newest) {
+        if (!ptx::mbar_wait(&full[w_slot], w_phase)) {
+          landed = false;
+          break;
+        }
+        ++waited;
+        if (++w_slot == R) {
+          w_slot = 0;
+          w_phase ^= 1u;
+        }
+      }
+      auto gather = [&](int c, int iw) {
         float acc = 0.f;
-        for (int r = kh - 1; r >= 0; --r) {
+#pragma unroll
+        for (int r = KH - 1; r >= 0; --r) {
           const int oh = ih + padH - r;
           if (oh < 0 || oh >= Ho) continue;
-          const float *slot = ring + (long long)(oh % kh) * Wo * pitch + c * khw + r * kw;
-          for (int sx = kw - 1; sx >= 0; --sx) {
-            int ow;
-            if (UNIT_W) {
-              ow = iw + padW - sx;
-              if (ow < 0) continue;
-            } else {
-              const int num_w = iw + padW - sx * dW;
-              if (num_w < 0 || num_w % sW != 0) continue;
-              ow = num_w / sW;
-            }
-            if (ow >= Wo) continue;
-            acc = acc + slot[ow * pitch + sx];
+          const int slot = cur - r < 0 ? cur - r + R : cur - r;
+          const float *rowp = ring + slot * row_floats + c * KHW + r * KW;
+#pragma unroll
+          for (int sx = KW - 1; sx >= 0; --sx) {
+            const int ow = iw + padW - sx;
+            if (ow < 0 || ow >= Wo) continue;
+            acc = acc + rowp[ow * crs + sx];
           }
         }
-        out[(long long)c * H * W + iw] = acc;
+        return acc;
+      };
+      if (landed) {
+#pragma unroll
+        for (int q = 0; q < NOUT; ++q)
+          if (out_c[q] >= 0) outimg[out_c[q] * plane + ih * W + out_w[q]] = gather(out_c[q], out_w[q]);
+        for (int i = threadIdx.x + NOUT * C2I_THREADS; i < C * W; i += C2I_THREADS) {
+          const int iw = i / C, c = i - iw * C;
+          outimg[c * plane + ih * W + iw] = gather(c, iw);
+        }
       }
-      __syncthreads();
+      // this row's reads are over; a wait that ran out in any thread ends the block for all of them
+      if (!__syncthreads_and(landed ? 1 : 0)) {
+        ok = false;
+        break;
+      }
+      if (threadIdx.x == 0) {
+        // rows of this image that no later output row reads; after the last output row, all of them
+        int dead = ih + padH - (KH - 1) + 1;
+        dead = ih == H - 1 ? Ho : (dead < 0 ? 0 : (dead > Ho ? Ho : dead));
+        issue_upto(row0 + dead);
+      }
+      if (++cur == R) cur = 0;
     }
+    if (!ok) break;
+    // the image is complete in shared memory (the barrier above): one linear pass to HBM
+    float *dst = im + b * (long long)img_floats;
+    if ((img_floats & 3) == 0 && ((uintptr_t)dst & 15) == 0) {
+      for (int i = threadIdx.x; i < (img_floats >> 2); i += C2I_THREADS)
+        reinterpret_cast<float4 *>(dst)[i] = reinterpret_cast<const float4 *>(outimg)[i];
+    } else {
+      for (int i = threadIdx.x; i < img_floats; i += C2I_THREADS) dst[i] = outimg[i];
+    }
+    __syncthreads();  // before the next image's first row overwrites the copy
+    row0 += Ho;
+    img_slot0 = (img_slot0 + Ho) % R;
+  }
+  if (!ok) s_fail = 1;
+  __syncthreads();
+  if (threadIdx.x == 0 && s_fail) {
+    // A wait ran out. Report it, and give the copies still queued a last bounded chance to land before
+    // this block's shared memory goes away.
+    atomicExch(err_flag, 1);
+    const long long first = issued > R ? issued - R : 0;
+    for (long long q = first; q < issued; ++q)
+      ptx::mbar_wait(&full[(int)(q % R)], (uint32_t)((q / R) & 1), 100000000ull);
   }
 }
 
@@ -1113,7 +1286,34 @@ int b200_col2im(b200_engine *e, int dtype, const void *col, void *im, int64_t B,
     }
     const int blocks = (int)std::max<long long>(1, std::min<long long>(B, (long long)e->sm_count * 8));
     const bool unit_w = stride_w == 1 && dil_w == 1;
-    if (dtype == B200_F32 && (C * kh * kw) % 4 == 0 && Wo * C * kh * kw <= 8 * 256 * 4 && (uintptr_t)col % 16 == 0) {
+    if (dtype == B200_F32 && kh == 3 && kw == 3 && unit_w && (C * 9) % 4 == 0 && (uintptr_t)col % 16 == 0 && pad_h <= 2) {
+      // bulk-copy ring: as many rows as fit beside the image copy, at most 8 (five rows ahead of the three in use)
+      const size_t row_b = (size_t)Wo * C * 9 * 4, img_b = (size_t)C * H * W * 4;
+      // two blocks per SM where five ring rows and the image fit in half of its shared memory, else one
+      const size_t whole = std::min<size_t>(e->smem_optin, 227 * 1024) - 2048;
+      const size_t room = img_b + 5 * row_b <= whole / 2 - 1024 ? whole / 2 - 1024 : whole;
+      if (img_b + 5 * row_b <= room) {
+        const int R = (int)std::min<size_t>(C2I_MAX_RING, (room - img_b) / row_b);
+        const size_t smem = (size_t)R * row_b + img_b;
+        static std::atomic<int> attrb_dev_mask{0};
+        if (!(attrb_dev_mask & (1 << (e->device & 31)))) {
+          B200_CHECK_CUDA(e, cudaFuncSetAttribute(col2im_bulk_kernel<3, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                  (int)whole));
+          attrb_dev_mask |= 1 << (e->device & 31);
+        }
+        const long long per_sm = std::max<long long>(1, (long long)(whole / (smem + 1024)));
+        const int bblocks = (int)std::max<long long>(1, std::min<long long>(B, (long long)e->sm_count * per_sm));
+        col2im_bulk_kernel<3, 3><<<bblocks, C2I_THREADS, smem, e->stream>>>((const float *)col, (float *)im, B, (int)C, (int)H,
+                                                                    (int)W, (int)Ho, (int)Wo, pad_h, pad_w, R,
+                                                                    e->d_flags + 2);
+        B200_CHECK_LAUNCH(e, "col2im_bulk_kernel");
+        e->flags_dirty = true;
+        return B200_OK;
+      }
+    }
+    const size_t staged4 = (size_t)(kh + 1) * Wo * (C * kh * kw + 1) * es;  // its ring holds one row more
+    if (dtype == B200_F32 && (C * kh * kw) % 4 == 0 && Wo * C * kh * kw <= 8 * 256 * 4 && (uintptr_t)col % 16 == 0 &&
+        staged4 <= 96 * 1024) {
       static int attr4_dev_mask = 0;
       if (!(attr4_dev_mask & (1 << (e->device & 31)))) {
         B200_CHECK_CUDA(e, cudaFuncSetAttribute(col2im_rows4_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -1123,11 +1323,11 @@ int b200_col2im(b200_engine *e, int dtype, const void *col, void *im, int64_t B,
         attr4_dev_mask |= 1 << (e->device & 31);
       }
       if (unit_w)
-        col2im_rows4_kernel<true><<<blocks, 256, staged, e->stream>>>((const float *)col, (float *)im, B, (int)C, (int)H,
+        col2im_rows4_kernel<true><<<blocks, 256, staged4, e->stream>>>((const float *)col, (float *)im, B, (int)C, (int)H,
                                                                      (int)W, (int)Ho, (int)Wo, kh, kw, pad_h, pad_w,
                                                                      stride_w, dil_w);
       else
-        col2im_rows4_kernel<false><<<blocks, 256, staged, e->stream>>>((const float *)col, (float *)im, B, (int)C,
+        col2im_rows4_kernel<false><<<blocks, 256, staged4, e->stream>>>((const float *)col, (float *)im, B, (int)C,
                                                                       (int)H, (int)W, (int)Ho, (int)Wo, kh, kw, pad_h,
                                                                       pad_w, stride_w, dil_w);
       B200_CHECK_LAUNCH(e, "col2im_rows4_kernel");
