@@ -410,19 +410,49 @@ __global__ void __launch_bounds__(256) softmax_bwd_strided_kernel(const T *__res
 template <typename T, bool LOG>
 __global__ void __launch_bounds__(128) softmax_bwd_short_kernel(const T *__restrict__ y, const T *__restrict__ g,
                                                                 T *__restrict__ dx, long long rows, int len) {
-  __shared__ T sy[4][32 * 16 + 1], sg[4][32 * 16 + 1];
+  __shared__ __align__(16) T sy[4][32 * 16], sg[4][32 * 16];
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
   const long long warp0 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
   const long long groups = (rows + 31) / 32;
+  // whole groups move 16 bytes per lane and instruction, with every load of a group in flight before
+  // the first one is used (a group of 32 rows is 32 * len elements, a whole number of 16-byte pieces
+  // when len is even for float32 / any len for pairs of float64 rows)
+  constexpr int PER = 16 / (int)sizeof(T);        // elements in 16 bytes
+  constexpr int MAXV = (32 * 16 / PER + 31) / 32;  // 16-byte pieces per lane and array, at most
+  const bool vec_ok = ((32 * len) % PER) == 0 && (((uintptr_t)y | (uintptr_t)g | (uintptr_t)dx) & 15) == 0 &&
+                      ((32LL * len * sizeof(T)) & 15) == 0;
   for (long long grp = warp0; grp < groups; grp += nwarps) {
     const long long r0 = grp * 32;
     const int nrows = (int)min((long long)32, rows - r0);
     const int n = nrows * len;
     const long long base = r0 * len;
-    for (int i = lane; i < n; i += 32) {
-      sy[w][i] = y[base + i];
-      sg[w][i] = g[base + i];
+    const bool vec = vec_ok && nrows == 32;
+    if (vec) {
+      const int nv = n / PER;
+      const uint4 *yv = reinterpret_cast<const uint4 *>(y + base), *gv = reinterpret_cast<const uint4 *>(g + base);
+      uint4 ry[MAXV], rg[MAXV];
+#pragma unroll
+      for (int v = 0; v < MAXV; ++v) {
+        const int i = lane + v * 32;
+        if (i < nv) {
+          ry[v] = __ldg(yv + i);
+          rg[v] = __ldg(gv + i);
+        }
+      }
+#pragma unroll
+      for (int v = 0; v < MAXV; ++v) {
+        const int i = lane + v * 32;
+        if (i < nv) {
+          reinterpret_cast<uint4 *>(sy[w])[i] = ry[v];
+          reinterpret_cast<uint4 *>(sg[w])[i] = rg[v];
+        }
+      }
+    } else {
+      for (int i = lane; i < n; i += 32) {
+        sy[w][i] = y[base + i];
+        sg[w][i] = g[base + i];
+      }
     }
     __syncwarp();
     if (lane < nrows) {
@@ -435,7 +465,13 @@ __global__ void __launch_bounds__(128) softmax_bwd_short_kernel(const T *__restr
       }
     }
     __syncwarp();
-    for (int i = lane; i < n; i += 32) dx[base + i] = sg[w][i];
+    if (vec) {
+      const int nv = n / PER;
+      uint4 *dv = reinterpret_cast<uint4 *>(dx + base);
+      for (int i = lane; i < nv; i += 32) dv[i] = reinterpret_cast<const uint4 *>(sg[w])[i];
+    } else {
+      for (int i = lane; i < n; i += 32) dx[base + i] = sg[w][i];
+    }
     __syncwarp();
   }
 }
