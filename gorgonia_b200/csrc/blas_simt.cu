@@ -155,20 +155,35 @@ __global__ void __launch_bounds__(256) ger_kernel(const T *__restrict__ x, const
                                                   long long M, long long N) {
   constexpr int V = 16 / sizeof(T);
   if (VEC) {
+    // A block walks rows blockIdx.x, blockIdx.x + gridDim.x, ...; its threads keep up to eight 16-byte
+    // pieces of y in registers across the rows (a strip of 2048 pieces), so a row costs a thread one
+    // scalar load of x and eight multiplies and stores, and nothing is divided.
     const long long nv = N / V;
-    const long long total = M * nv;
-    const long long stride = (long long)gridDim.x * blockDim.x;
-    for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += stride) {
-      const long long i = t / nv, c = t % nv;
-      const T xi = x[i];
-      const uint4 ry = __ldg(reinterpret_cast<const uint4 *>(y + c * V));
-      T yv[V], o[V];
-      memcpy(yv, &ry, 16);
+    for (long long c0 = 0; c0 < nv; c0 += 8 * 256) {
+      T yv[8][V];
 #pragma unroll
-      for (int j = 0; j < V; ++j) o[j] = xi * yv[j];
-      uint4 ro;
-      memcpy(&ro, o, 16);
-      *reinterpret_cast<uint4 *>(A + i * N + c * V) = ro;
+      for (int u = 0; u < 8; ++u) {
+        const long long c = c0 + threadIdx.x + 256 * u;
+        uint4 ry = make_uint4(0, 0, 0, 0);
+        if (c < nv) ry = __ldg(reinterpret_cast<const uint4 *>(y + c * V));
+        memcpy(yv[u], &ry, 16);
+      }
+      for (long long i = blockIdx.x; i < M; i += gridDim.x) {
+        const T xi = x[i];
+        T *row = A + i * N;
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const long long c = c0 + threadIdx.x + 256 * u;
+          if (c < nv) {
+            T o[V];
+#pragma unroll
+            for (int j = 0; j < V; ++j) o[j] = xi * yv[u][j];
+            uint4 ro;
+            memcpy(&ro, o, 16);
+            *reinterpret_cast<uint4 *>(row + c * V) = ro;
+          }
+        }
+      }
     }
   } else {
     const long long total = M * N;
@@ -419,7 +434,8 @@ int b200_ger(b200_engine *e, int dtype, int64_t M, int64_t N, const void *x, con
   const size_t es = dtype_size(dtype);
   const bool vec = N % (16 / es) == 0 && (uintptr_t)A % 16 == 0 && (uintptr_t)y % 16 == 0;
   const long long work = vec ? M * (N / (16 / (long long)es)) : M * N;
-  const int blocks = (int)std::max<long long>(1, std::min<long long>((work + 255) / 256, (long long)e->sm_count * 16));
+  int blocks = (int)std::max<long long>(1, std::min<long long>((work + 255) / 256, (long long)e->sm_count * 16));
+  if (vec) blocks = (int)std::max<long long>(1, std::min<long long>(M, (long long)e->sm_count * 8));  // rows per block
   if (dtype == B200_F32) {
     if (vec)
       ger_kernel<float, true><<<blocks, 256, 0, e->stream>>>((const float *)x, (const float *)y, (float *)A, M, N);
