@@ -155,9 +155,11 @@ __global__ void __launch_bounds__(256) ger_kernel(const T *__restrict__ x, const
                                                   long long M, long long N) {
   constexpr int V = 16 / sizeof(T);
   if (VEC) {
-    // A block walks rows blockIdx.x, blockIdx.x + gridDim.x, ...; its threads keep up to eight 16-byte
-    // pieces of y in registers across the rows (a strip of 2048 pieces), so a row costs a thread one
-    // scalar load of x and eight multiplies and stores, and nothing is divided.
+    // A block takes groups of four consecutive rows (group blockIdx.x, blockIdx.x + gridDim.x, ...; the
+    // host launches many more blocks than are resident at once, so groups are handed out as blocks
+    // retire); its threads keep up to eight 16-byte pieces of y in registers across the rows (a strip
+    // of 2048 pieces), so a row costs a thread one scalar load of x and eight multiplies and stores,
+    // and nothing is divided.
     const long long nv = N / V;
     for (long long c0 = 0; c0 < nv; c0 += 8 * 256) {
       T yv[8][V];
@@ -168,7 +170,8 @@ __global__ void __launch_bounds__(256) ger_kernel(const T *__restrict__ x, const
         if (c < nv) ry = __ldg(reinterpret_cast<const uint4 *>(y + c * V));
         memcpy(yv[u], &ry, 16);
       }
-      for (long long i = blockIdx.x; i < M; i += gridDim.x) {
+      for (long long i4 = (long long)blockIdx.x * 4; i4 < M; i4 += (long long)gridDim.x * 4)
+      for (long long i = i4; i < i4 + 4 && i < M; ++i) {
         const T xi = x[i];
         T *row = A + i * N;
 #pragma unroll
@@ -352,11 +355,11 @@ static int gemv_typed(b200_engine *e, int transA, long long M, long long N, cons
   const long long cap = (long long)e->sm_count * 8;
   if (!transA) {
     const bool vec = lda % (16 / sizeof(T)) == 0 && (uintptr_t)A % 16 == 0 && (uintptr_t)x % 16 == 0;
-    // as many warps as give every warp the same number of rows (16384 rows on 9472 warp slots would
-    // leave most warps with one row while the launch lasts as long as the ones with two)
-    const long long rounds = (M + cap * 8 - 1) / (cap * 8);
-    const long long warps = (M + rounds - 1) / rounds;
-    const int blocks = (int)std::max<long long>(1, (warps + 7) / 8);
+    // One row per warp and many more blocks than fit the GPU at once: blocks are then handed out as
+    // earlier ones retire. A grid that is resident all at once with a fixed share of rows per warp
+    // measured 15 % slower at 16384 x 16384 (800 to 1184 blocks: 4.8 TB/s; 1400 and more: 5.6), the
+    // share of the SMs that got an extra block setting the time.
+    const int blocks = (int)std::max<long long>(1, std::min<long long>((M + 7) / 8, cap * 8));
     if (vec)
       gemv_n_kernel<T, true><<<blocks, 256, 0, e->stream>>>(A, lda, x, y, M, N);
     else
@@ -435,7 +438,7 @@ int b200_ger(b200_engine *e, int dtype, int64_t M, int64_t N, const void *x, con
   const bool vec = N % (16 / es) == 0 && (uintptr_t)A % 16 == 0 && (uintptr_t)y % 16 == 0;
   const long long work = vec ? M * (N / (16 / (long long)es)) : M * N;
   int blocks = (int)std::max<long long>(1, std::min<long long>((work + 255) / 256, (long long)e->sm_count * 16));
-  if (vec) blocks = (int)std::max<long long>(1, std::min<long long>(M, (long long)e->sm_count * 8));  // rows per block
+  if (vec) blocks = (int)std::max<long long>(1, std::min<long long>((M + 3) / 4, (long long)e->sm_count * 64));  // groups of four rows
   if (dtype == B200_F32) {
     if (vec)
       ger_kernel<float, true><<<blocks, 256, 0, e->stream>>>((const float *)x, (const float *)y, (float *)A, M, N);

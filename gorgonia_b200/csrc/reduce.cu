@@ -481,7 +481,8 @@ static int launch_softmax_bwd(b200_engine *e, const T *y, const T *g, T *dx, lon
                               long long inner) {
   if (inner == 1 && len <= 16) {
     const long long groups = (outer + 31) / 32;
-    const long long blocks = std::max<long long>(1, std::min<long long>((groups + 3) / 4, (long long)e->sm_count * 16));
+    // more blocks than are resident at once: groups of rows are then handed out as blocks retire
+    const long long blocks = std::max<long long>(1, std::min<long long>((groups + 3) / 4, (long long)e->sm_count * 64));
     softmax_bwd_short_kernel<T, LOG><<<(int)blocks, 128, 0, e->stream>>>(y, g, dx, outer, (int)len);
   } else if (inner == 1) {
     const long long blocks = std::max<long long>(1, std::min<long long>((outer + 7) / 8, (long long)e->sm_count * 16));
