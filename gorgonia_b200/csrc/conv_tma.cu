@@ -55,6 +55,7 @@ struct ConvTmaParams {
   // how the work is shared between the CTAs (TilePieces, tc_common.cuh)
   int streamk;
   int units;        // tiles * num_k (0 when the k range is not shared)
+  int sk_first, sk_workers;  // k ranges are shared from this tile on, among this many CTAs (TilePieces)
   float *ws;        // partial tiles: slot 2c (a part that begins CTA c's share) and 2c + 1 (one that ends it)
   int *tile_count;  // parts delivered per tile; zero between launches
   Epilogue ep;     // bias_kind ROW = per output channel
@@ -144,7 +145,7 @@ __global__ void __launch_bounds__(CT_THREADS, 1)
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      TilePieces pieces(p.streamk, p.units, p.num_k, (int)total_tiles);
+      TilePieces pieces(p.streamk, p.units, p.num_k, (int)total_tiles, (int)blockIdx.x, (int)gridDim.x, p.sk_first, p.sk_workers);
       int tile, kb0, kb1;
       while (ok && pieces.next(tile, kb0, kb1)) {
         const int mt = (int)(tile / p.tiles_n), nt = (int)(tile % p.tiles_n);
@@ -191,7 +192,7 @@ __global__ void __launch_bounds__(CT_THREADS, 1)
       uint32_t phase = 0;
       int use = 0;
       bool ok = true;
-      TilePieces pieces(p.streamk, p.units, p.num_k, (int)total_tiles);
+      TilePieces pieces(p.streamk, p.units, p.num_k, (int)total_tiles, (int)blockIdx.x, (int)gridDim.x, p.sk_first, p.sk_workers);
       int tile, kb0, kb1;
       while (ok && pieces.next(tile, kb0, kb1)) {
         for (int kc = kb0; kc < kb1 && ok; kc += p.chunk_k, ++use) {
@@ -250,7 +251,7 @@ __global__ void __launch_bounds__(CT_THREADS, 1)
       epi_phase ^= 1;
       return done;
     };
-    TilePieces pieces(p.streamk, p.units, p.num_k, (int)total_tiles);
+    TilePieces pieces(p.streamk, p.units, p.num_k, (int)total_tiles, (int)blockIdx.x, (int)gridDim.x, p.sk_first, p.sk_workers);
     int tile, kb0, kb1;
     while (ok && pieces.next(tile, kb0, kb1)) {
       const int mt = (int)(tile / p.tiles_n), nt = (int)(tile % p.tiles_n);
@@ -282,23 +283,23 @@ __global__ void __launch_bounds__(CT_THREADS, 1)
       }
       if (kb0 != 0 || kb1 != p.num_k) {
         // part of a tile: leave it in the workspace; the CTA that delivers the last part finishes the tile
-        const int tile_u0 = tile * p.num_k;
+        const int tile_u0 = (tile - p.sk_first) * p.num_k;  // among the units that are shared out
         const size_t slot_floats = (size_t)CT_BM * BN;
         const size_t within = ((size_t)(warp - 2) * HALF) * 32 + lane;
         if (ok) {
-          float *wsp = p.ws + (size_t)share_slot(blockIdx.x, tile_u0, p.units, gridDim.x) * slot_floats + within;
+          float *wsp = p.ws + (size_t)share_slot(blockIdx.x, tile_u0, p.units, p.sk_workers) * slot_floats + within;
 #pragma unroll
           for (int j = 0; j < HALF; ++j) __stcg(wsp + j * 32, acc[j]);
         } else {
           s_fail = 1;
         }
         __threadfence();
-        const int c_first = share_of_unit(tile_u0, p.units, gridDim.x);
-        const int c_last = share_of_unit(tile_u0 + p.num_k - 1, p.units, gridDim.x);
+        const int c_first = share_of_unit(tile_u0, p.units, p.sk_workers);
+        const int c_last = share_of_unit(tile_u0 + p.num_k - 1, p.units, p.sk_workers);
         bool met = epi_sync();
         if (warp == 2 && lane == 0) {
-          s_last = (atomicAdd(p.tile_count + tile, 1) == c_last - c_first) ? 1 : 0;
-          if (s_last) p.tile_count[tile] = 0;  // zero again for the next launch
+          s_last = (atomicAdd(p.tile_count + (tile - p.sk_first), 1) == c_last - c_first) ? 1 : 0;
+          if (s_last) p.tile_count[tile - p.sk_first] = 0;  // zero again for the next launch
         }
         met = epi_sync() && met;
         if (!met || *(volatile int *)&s_fail) {
@@ -310,7 +311,7 @@ __global__ void __launch_bounds__(CT_THREADS, 1)
 #pragma unroll
         for (int j = 0; j < HALF; ++j) acc[j] = 0.f;
         for (int c = c_first; c <= c_last; ++c) {  // k order: CTA c's share precedes CTA c + 1's
-          const float *src = p.ws + (size_t)share_slot(c, tile_u0, p.units, gridDim.x) * slot_floats + within;
+          const float *src = p.ws + (size_t)share_slot(c, tile_u0, p.units, p.sk_workers) * slot_floats + within;
 #pragma unroll
           for (int j = 0; j < HALF; ++j) acc[j] = __fadd_rn(acc[j], ptx::ld_cg_ordered(src + j * 32));
         }
@@ -574,6 +575,8 @@ static int launch_conv_tma(b200_engine *e, const CUtensorMap *tm, ConvTmaParams 
   void *ws = nullptr;
   p.streamk = 0;
   p.units = 0;
+  p.sk_first = 0;
+  p.sk_workers = grid;
   if (tiles >= (1LL << 31))
     return set_error(e, B200_ERR_UNSUPPORTED, "convolution: %lld output tiles are more than one launch takes", tiles);
   int sk_grid = grid;
@@ -583,9 +586,21 @@ static int launch_conv_tma(b200_engine *e, const CUtensorMap *tm, ConvTmaParams 
       grid = sk_grid;
       p.streamk = 1;
       p.units = (int)(tiles * p.num_k);  // small: k sharing is for launches of few tiles
+      p.sk_workers = grid;
       p.tile_count = e->sk_counters;
       p.ws = (float *)ws;
     }  // else: no room for the partial tiles, whole tiles per CTA
+  } else if (int first = 0, sk = 0; !(e->flags & B200_ENGINE_NO_STREAMK) && tiles % e->sm_count <= b200_engine::kSkCounters &&
+                                    streamk_tail_pays(tiles, p.num_k, e->sm_count, &first, &sk)) {
+    // several waves of tiles and a ragged last one: the full waves whole, the rest along k
+    if (b200_get(e, 2LL * sk * CT_BM * BN * 4, &ws) == B200_OK) {
+      p.streamk = 1;
+      p.sk_first = first;
+      p.sk_workers = sk;
+      p.units = (int)((tiles - first) * p.num_k);
+      p.tile_count = e->sk_counters;
+      p.ws = (float *)ws;
+    }
   }
   kern<<<grid, CT_THREADS, smem, e->stream>>>(tm[0], tm[1], tm[2], tm[3], p);
   cudaError_t le = cudaGetLastError();

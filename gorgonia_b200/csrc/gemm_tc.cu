@@ -86,6 +86,7 @@ struct GemmTcParams {
   float *ws;                    // partial tiles, 2 slots of TC_BM x BN floats per CTA
   int *tile_count;              // parts delivered per tile; zero between launches
   int workers;                  // CTAs, or CTA pairs, that share the tiles out
+  int sk_first, sk_workers;     // k ranges are shared from this tile on, among this many CTAs (TilePieces)
   Epilogue ep;
   int *err_flag;
 };
@@ -196,7 +197,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      TilePieces pieces(p.streamk, p.units, p.num_k, (int)total_tiles, worker, p.workers);
+      TilePieces pieces(p.streamk, p.units, p.num_k, (int)total_tiles, worker, p.workers, p.sk_first, p.sk_workers);
       int tile, kb0, kb1;
       while (ok && pieces.next(tile, kb0, kb1)) {
         int bz, mb, nb;
@@ -287,7 +288,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
       const uint32_t full0 = ptx::smem_addr(&full_bar[0]), empty0 = ptx::smem_addr(&empty_bar[0]);
       const uint32_t empty0_peer = PAIR ? ptx::map_to_rank(empty0, 1u) : 0u;
       uint32_t ready = 0;  // the poll behind the previous k-block saw this stage's barrier complete
-      TilePieces pieces(p.streamk, p.units, p.num_k, (int)total_tiles, worker, p.workers);
+      TilePieces pieces(p.streamk, p.units, p.num_k, (int)total_tiles, worker, p.workers, p.sk_first, p.sk_workers);
       int tile, kb0, kb1;
       while (ok && pieces.next(tile, kb0, kb1)) {
         for (int kc = kb0; kc < kb1 && ok; kc += p.chunk_k, ++use) {
@@ -353,7 +354,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
       epi_phase ^= 1;
       return done;
     };
-    TilePieces pieces(p.streamk, p.units, p.num_k, (int)total_tiles, worker, p.workers);
+    TilePieces pieces(p.streamk, p.units, p.num_k, (int)total_tiles, worker, p.workers, p.sk_first, p.sk_workers);
     int tile, kb0, kb1;
     while (ok && pieces.next(tile, kb0, kb1)) {
       const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
@@ -482,23 +483,23 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
         if (kb0 != 0 || kb1 != p.num_k) {
           // part of a tile: leave it in the workspace; the CTA that delivers the last part finishes the tile
           constexpr int NACC = TERMS == 3 ? HALF : 1;
-          const int tile_u0 = tile * p.num_k;
+          const int tile_u0 = (tile - p.sk_first) * p.num_k;  // among the units that are shared out
           const size_t slot_floats = (size_t)TC_BM * BN;
           const size_t within = ((size_t)(warp - 2) * HALF) * 32 + lane;
           if (ok) {
-            float *wsp = p.ws + (size_t)share_slot(worker, tile_u0, p.units, p.workers) * slot_floats + within;
+            float *wsp = p.ws + (size_t)share_slot(worker, tile_u0, p.units, p.sk_workers) * slot_floats + within;
 #pragma unroll
             for (int j = 0; j < NACC; ++j) __stcg(wsp + j * 32, acc[j]);
           } else {
             s_fail = 1;
           }
           __threadfence();
-          const int c_first = share_of_unit(tile_u0, p.units, p.workers);
-          const int c_last = share_of_unit(tile_u0 + p.num_k - 1, p.units, p.workers);
+          const int c_first = share_of_unit(tile_u0, p.units, p.sk_workers);
+          const int c_last = share_of_unit(tile_u0 + p.num_k - 1, p.units, p.sk_workers);
           bool met = epi_sync();
           if (warp == 2 && lane == 0) {
-            s_last = (atomicAdd(p.tile_count + tile, 1) == c_last - c_first) ? 1 : 0;
-            if (s_last) p.tile_count[tile] = 0;  // zero again for the next launch
+            s_last = (atomicAdd(p.tile_count + (tile - p.sk_first), 1) == c_last - c_first) ? 1 : 0;
+            if (s_last) p.tile_count[tile - p.sk_first] = 0;  // zero again for the next launch
           }
           met = epi_sync() && met;
           if (!met || *(volatile int *)&s_fail) {
@@ -510,7 +511,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
 #pragma unroll
           for (int j = 0; j < NACC; ++j) acc[j] = 0.f;
           for (int c = c_first; c <= c_last; ++c) {  // k order: CTA c's share precedes CTA c + 1's
-            const float *src = p.ws + (size_t)share_slot(c, tile_u0, p.units, p.workers) * slot_floats + within;
+            const float *src = p.ws + (size_t)share_slot(c, tile_u0, p.units, p.sk_workers) * slot_floats + within;
 #pragma unroll
             for (int j = 0; j < NACC; ++j) acc[j] = __fadd_rn(acc[j], ptx::ld_cg_ordered(src + j * 32));
           }
@@ -866,6 +867,8 @@ int gemm_tc_core(b200_engine *e, int terms, bool a_mn, bool b_mn, long long M, l
   p.ws = nullptr;
   p.tile_count = nullptr;
   p.workers = grid;
+  p.sk_first = 0;
+  p.sk_workers = grid;
   if (pair) {
     p.tiles_m = (int)((M + 2 * TC_BM - 1) / (2 * TC_BM));
     p.group_m = std::min(p.tiles_m, 4);  // the same 8 x 128 rows of A per raster group
@@ -888,9 +891,21 @@ int gemm_tc_core(b200_engine *e, int terms, bool a_mn, bool b_mn, long long M, l
       p.units = (int)(total_tiles * p.num_k);  // small: k sharing is for launches of few tiles
       grid = sk_grid;
       p.workers = grid;
+      p.sk_workers = grid;
       p.tile_count = e->sk_counters;
       p.ws = (float *)ws;
     }  // else: no room for the partial tiles, whole tiles per CTA
+  } else if (int first = 0, sk = 0; may_share_k && total_tiles - total_tiles / e->sm_count * e->sm_count <= b200_engine::kSkCounters &&
+                                    streamk_tail_pays(total_tiles, p.num_k, e->sm_count, &first, &sk)) {
+    // several waves of tiles and a ragged last one: the full waves whole, the rest along k
+    if (b200_get(e, 2LL * sk * TC_BM * bn * 4, &ws) == B200_OK) {
+      p.streamk = 1;
+      p.sk_first = first;
+      p.sk_workers = sk;
+      p.units = (int)((total_tiles - first) * p.num_k);
+      p.tile_count = e->sk_counters;
+      p.ws = (float *)ws;
+    }
   }
   const int rc = bn == 128 ? launch_tc_layout<3, 128>(e, a_mn, b_mn, tm, p, grid)
                            : launch_tc_layout<3, 64>(e, a_mn, b_mn, tm, p, grid);

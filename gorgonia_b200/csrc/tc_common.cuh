@@ -55,42 +55,49 @@ __host__ __device__ constexpr uint32_t make_idesc(int fmt, int a_mn, int b_mn, i
 
 
 // ---- sharing a launch's work between the CTAs ---------------------------------------------------
-// whole == 1: CTA c takes tiles c, c + grid, ... and every k-block of each. whole == 0 ("stream-K"):
-// the (tile, k-block) units of the whole problem, tile-major, are cut into `grid` equal contiguous
-// shares, so a launch with fewer tiles than SMs, or with a ragged last wave, still keeps every SM
-// busy for the same time. A share that holds only part of a tile's k range leaves its fp32 partial
-// tile in a workspace; whichever CTA delivers a tile's last missing part adds the parts in k order
-// (the result therefore does not depend on who that is) and stores the tile. Every warp role of a
-// kernel walks the same pieces through this iterator.
+// stream == 0: worker c takes tiles c, c + workers, ... and every k-block of each. stream == 1
+// ("stream-K"): tiles [0, first) are taken whole in that same way, and the (tile, k-block) units of
+// the tiles from `first` on, tile-major, are cut into `sk_workers` equal contiguous shares (workers
+// beyond that number get none), so a launch with fewer tiles than SMs (first == 0), or the ragged
+// last wave of a larger one (first == the tiles of the full waves), still keeps every SM busy for
+// the same time. A share that holds only part of a tile's k range leaves its fp32 partial tile in a
+// workspace; whichever CTA delivers a tile's last missing part adds the parts in k order (the result
+// therefore does not depend on who that is) and stores the tile. Every warp role of a kernel walks
+// the same pieces through this iterator. Sharing out ALL tiles of a launch of several waves was
+// measured and is not done: tiny-YOLO's step went from 2.49 to 3.28 ms (the CTAs then work on tiles
+// that are far apart at any one time, and at different k offsets, so the operand slabs that
+// neighbouring tiles have in common are no longer asked for together).
 struct TilePieces {
   // 32-bit throughout: the host refuses launches of 2^31 tiles or units
-  int tile, total_tiles, u, u1, num_k, stream;
-  int workers;
+  int tile, whole_end, u, u1, num_k, stream, workers, first;
   // worker w of `workers` (CTAs, or CTA pairs that take a tile together)
-  __device__ TilePieces(int streamk, int units, int num_k_, int tiles, int w, int workers_) {
+  __device__ TilePieces(int streamk, int units, int num_k_, int tiles, int w, int workers_, int first_ = 0,
+                        int sk_workers = 0) {
     stream = streamk;
     num_k = num_k_;
-    total_tiles = tiles;
     workers = workers_;
+    first = streamk ? first_ : 0;
+    whole_end = streamk ? first_ : tiles;
     tile = w;
-    u = (int)((long long)w * units / workers);
-    u1 = (int)((long long)(w + 1) * units / workers);
+    if (sk_workers <= 0) sk_workers = workers_;
+    u = w < sk_workers ? (int)((long long)w * units / sk_workers) : units;
+    u1 = w < sk_workers ? (int)((long long)(w + 1) * units / sk_workers) : units;
   }
   __device__ TilePieces(int streamk, int units, int num_k_, int tiles)
       : TilePieces(streamk, units, num_k_, tiles, (int)blockIdx.x, (int)gridDim.x) {}
   // the next piece: k-blocks [kb0, kb1) of tile t
   __device__ bool next(int &t, int &kb0, int &kb1) {
-    if (!stream) {
-      if (tile >= total_tiles) return false;
+    if (tile < whole_end) {
       t = tile;
       kb0 = 0;
       kb1 = num_k;
       tile += workers;
       return true;
     }
-    if (u >= u1) return false;
-    t = u / num_k;
-    kb0 = u - t * num_k;
+    if (!stream || u >= u1) return false;
+    const int tr = u / num_k;
+    t = first + tr;
+    kb0 = u - tr * num_k;
     const int rem = u1 - u;
     kb1 = (num_k - kb0) <= rem ? num_k : kb0 + rem;
     u += kb1 - kb0;
@@ -132,6 +139,20 @@ inline bool streamk_pays(long long tiles, int num_k, int sm_count, int *grid) {
   const double t_shared = 0.6 * (double)((units + g - 1) / g) + parts_per_tile + 3.0;
   if (t_shared >= 0.9 * t_whole) return false;
   *grid = (int)g;
+  return true;
+}
+
+// The same question for a launch of more tiles than SMs: whether the tiles beyond the full waves
+// (tiles % sm_count of them) share their k range out. *first = the tiles taken whole, *sk = the CTAs
+// that take a share.
+inline bool streamk_tail_pays(long long tiles, int num_k, int sm_count, int *first, int *sk) {
+  if (tiles <= sm_count) return false;
+  const long long rem = tiles % sm_count;
+  if (rem == 0) return false;
+  int g = sm_count;
+  if (!streamk_pays(rem, num_k, sm_count, &g)) return false;
+  *first = (int)(tiles - rem);
+  *sk = g;
   return true;
 }
 
