@@ -84,6 +84,27 @@ def test_matmul_f32_wide_tiles_many_per_cta(roomy, shape):
     _sampled_product_check(got, a, b, 1e-5)
 
 
+def test_matmul_f32_ragged_last_wave(roomy):
+    # 85 x 8 = 680 tiles on 148 SMs: four full waves of whole tiles, then 88 tiles whose k range is shared out
+    # over all CTAs (the launch shape of tiny-YOLO's late layers at the benchmark batch)
+    e = roomy
+    M, N, K = 10880, 1024, 1024
+    a = util.normal(305, (M, K), scale=0.02)
+    b = util.normal(306, (K, N), scale=0.02)
+    ta, tb, tc = e.tensor(a), e.tensor(b), e.empty((M, N))
+    e.MatMul(ta, tb, tc)
+    got = tc.numpy()
+    _sampled_product_check(got, a, b, 1e-5)
+    # an engine that never shares k ranges agrees within the tolerance (not bit for bit: the shared tiles
+    # are summed in other groupings)
+    from gorgonia_b200 import Engine
+    e2 = Engine(device=0, arena_bytes=1 << 30, streamk=False)
+    ua, ub, uc = e2.tensor(a), e2.tensor(b), e2.empty((M, N))
+    e2.MatMul(ua, ub, uc)
+    assert_gemm_close(got, uc.numpy(), 1e-5)
+    e2.Close()
+
+
 def test_matmul_f32_incr_4096(roomy):
     # the Incr-mode benchmark shape: C += A.B equals MatMul followed by Add, bit for bit
     e = roomy
