@@ -164,6 +164,28 @@ def test_sigmoid_float32_both_arms_and_ends(fresh):
     assert_pointwise_close(tx.numpy(), oracle.unary("sigmoid", x))
 
 
+@pytest.mark.parametrize("dt", DTYPES)
+def test_single_source_ops_on_wide_tiles(fresh, dt):
+    # programs with one full-size source and one instruction run with four 16-byte chunks per thread and tile once
+    # every CTA gets several such tiles: a size above that threshold with a ragged last tile and a ragged last
+    # chunk, for a unary op, a tensor-scalar op in both operand orders, and the unsafe (in-place) form
+    e = fresh
+    n = (5 << 22) + 3 if dt == np.float32 else (5 << 21) + 1
+    x = util.normal(501, n, dt)
+    tx, tr = e.tensor(x), e.empty(n, dt)
+    e.Unary("tanh", tx, reuse=tr)
+    assert_pointwise_close(tr.numpy(), oracle.unary("tanh", x))
+    e.Unary("neg", tx, reuse=tr)
+    assert_bits_equal(tr.numpy(), oracle.unary("neg", x))
+    s = dt(1.25)
+    e._binary_scalar("sub", tx, s, leftTensor=True, reuse=tr)
+    assert_bits_equal(tr.numpy(), oracle.binary("sub", x, s))
+    e._binary_scalar("sub", tx, s, leftTensor=False, reuse=tr)
+    assert_bits_equal(tr.numpy(), oracle.binary("sub", s, x))
+    e.Unary("exp", tx, unsafe=True)
+    assert_pointwise_close(tx.numpy(), oracle.unary("exp", x))
+
+
 def test_safe_mode_is_an_error(fresh):
     # cuda/arith.go:47-48: neither reuse nor unsafe -> error
     from gorgonia_b200 import B200Error
