@@ -65,6 +65,12 @@ COL2IM_CASES = [
     ((1, 4, 20, 20), (3, 3), (2, 2), (1, 1), (2, 2)),   # dilation
     ((2, 5, 17, 19), (3, 5), (2, 1), (2, 3), (1, 1)),   # odd everything
     ((3, 2, 6, 6), (1, 1), (0, 0), (1, 1), (1, 1)),     # 1x1: a plain transposition
+    # 3 x 3, unit stride, C * 9 a multiple of 4: float32 takes the bulk-copy ring kernel
+    ((5, 32, 14, 14), (3, 3), (1, 1), (1, 1), (1, 1)),  # LeNet's conv1
+    ((700, 4, 10, 12), (3, 3), (1, 1), (1, 1), (1, 1)), # more images than resident blocks: the ring runs across images
+    ((3, 8, 9, 11), (3, 3), (0, 0), (1, 1), (1, 1)),    # no padding: fewer col rows than image rows
+    ((3, 8, 7, 6), (3, 3), (2, 2), (1, 1), (1, 1)),     # full padding: more col rows than image rows
+    ((2, 4, 2, 4), (3, 3), (1, 1), (1, 1), (1, 1)),     # an image shorter than the window
 ]
 
 
