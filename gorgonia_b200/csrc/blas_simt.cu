@@ -73,6 +73,71 @@ __global__ void __launch_bounds__(256) gemv_n_kernel(const T *__restrict__ A, lo
   }
 }
 
+// ---- y = A x for long rows: x staged in shared memory -------------------------------------------------
+// The warp-per-row kernel reads as many bytes of x (from L1/L2) as of A. Here the eight warps of a block take
+// eight consecutive rows and share each 32 KB piece of x through shared memory, so x passes through the load
+// pipe once per block instead of once per warp. Every row's sums are formed in the same order as in
+// gemv_n_kernel: the results are the same bits.
+template <typename T>
+__global__ void __launch_bounds__(256) gemv_n_smemx_kernel(const T *__restrict__ A, long long lda,
+                                                           const T *__restrict__ x, T *__restrict__ y, long long M,
+                                                           long long N) {
+  constexpr int V = 16 / sizeof(T);
+  constexpr int CH = 2048;  // 16-byte pieces of x per chunk
+  __shared__ uint4 xs[CH];
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const long long nv = N / V;
+  const uint4 *x4 = reinterpret_cast<const uint4 *>(x);
+  for (long long row0 = (long long)blockIdx.x * 8; row0 < M; row0 += (long long)gridDim.x * 8) {
+    const long long r = row0 + w;
+    const bool live = r < M;
+    const T *a = A + (live ? r : 0) * lda;
+    T acc[V];
+#pragma unroll
+    for (int j = 0; j < V; ++j) acc[j] = T(0);
+    for (long long c0 = 0; c0 < nv; c0 += CH) {
+      const int len = (int)(nv - c0 < CH ? nv - c0 : CH);
+      __syncthreads();  // the previous piece of x has been used by every warp
+      for (int i = threadIdx.x; i < len; i += 256) xs[i] = __ldg(x4 + c0 + i);
+      __syncthreads();
+      if (live) {
+        const uint4 *a4 = reinterpret_cast<const uint4 *>(a) + c0;
+        int c = lane;
+        // the 128-piece steps of gemv_n_kernel continue across chunks (CH is a multiple of 128)
+        for (; c + 96 < len && c0 + c + 96 < nv; c += 128) {
+          uint4 ra[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) ra[u] = __ldcs(a4 + c + 32 * u);
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            T av[V], xv[V];
+            memcpy(av, &ra[u], 16);
+            memcpy(xv, &xs[c + 32 * u], 16);
+#pragma unroll
+            for (int j = 0; j < V; ++j) acc[j] = fma_(av[j], xv[j], acc[j]);
+          }
+        }
+        for (; c < len; c += 32) {
+          const uint4 ra = a4[c];
+          T av[V], xv[V];
+          memcpy(av, &ra, 16);
+          memcpy(xv, &xs[c], 16);
+#pragma unroll
+          for (int j = 0; j < V; ++j) acc[j] = fma_(av[j], xv[j], acc[j]);
+        }
+      }
+    }
+    if (live) {
+      for (long long c = nv * V + lane; c < N; c += 32) acc[0] = fma_(a[c], x[c], acc[0]);
+      T s = acc[0];
+#pragma unroll
+      for (int j = 1; j < V; ++j) s += acc[j];
+      for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+      if (lane == 0) y[r] = s;
+    }
+  }
+}
+
 // ---- y = A^T x : column strips, partial sums per row chunk, then a fold ---------------------------
 template <typename T>
 __global__ void __launch_bounds__(256) gemv_t_partial_kernel(const T *__restrict__ A, long long lda,
@@ -360,7 +425,12 @@ static int gemv_typed(b200_engine *e, int transA, long long M, long long N, cons
     // measured 15 % slower at 16384 x 16384 (800 to 1184 blocks: 4.8 TB/s; 1400 and more: 5.6), the
     // share of the SMs that got an extra block setting the time.
     const int blocks = (int)std::max<long long>(1, std::min<long long>((M + 7) / 8, cap * 8));
-    if (vec)
+    // few long rows (every block resident from the start): the variant that shares x through shared memory
+    // measured 5.6 against 4.8 TB/s at 8192 x 32768; with more blocks than fit, the plain kernel is ahead
+    // (5.6 against 5.5 at 16384 x 16384, 5.3 against 5.2 at 40000 x 6000). The two give the same bits.
+    if (vec && N >= 4096 && (M + 7) / 8 <= cap)
+      gemv_n_smemx_kernel<T><<<blocks, 256, 0, e->stream>>>(A, lda, x, y, M, N);
+    else if (vec)
       gemv_n_kernel<T, true><<<blocks, 256, 0, e->stream>>>(A, lda, x, y, M, N);
     else
       gemv_n_kernel<T, false><<<blocks, 256, 0, e->stream>>>(A, lda, x, y, M, N);

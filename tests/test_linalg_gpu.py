@@ -145,7 +145,8 @@ def test_batched_matmul(fresh):
 
 
 @pytest.mark.parametrize("dt", [np.float32, np.float64])
-@pytest.mark.parametrize("shape", [(1, 1), (3, 5), (128, 128), (1000, 257), (513, 4096), (4100, 31)])
+@pytest.mark.parametrize("shape", [(1, 1), (3, 5), (128, 128), (1000, 257), (513, 4096), (4100, 31),
+                                   (300, 4100), (9, 8196), (21, 20484)])   # long rows: x shared through shared memory
 def test_matvecmul(fresh, shape, dt):
     e = fresh
     M, N = shape
